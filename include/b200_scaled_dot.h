@@ -1,0 +1,173 @@
+/* b200_scaled_dot.h -- C ABI of libb200_scaled_dot.so.
+ *
+ * A B200 (sm_100a) replacement for the GPU half of XLA's quantized scaled dot: the work that
+ * `CublasLtMatmulThunk::ExecuteOnStream` hands to cuBLASLt for the custom calls
+ * `__cublas$lt$matmul$f8` and (s8 x s8) `__cublas$lt$matmul`.
+ *
+ * Two layers are exported:
+ *   1. plain entry points taking a parameter struct of raw device pointers and sizes;
+ *   2. XLA FFI handlers (`XLA_FFI_Error* fn(XLA_FFI_CallFrame*)`) that decode a call frame and
+ *      call layer 1 -- these are what an XLA process registers as custom-call targets.
+ *
+ * Conventions: every matrix is dense and row-major; transposition is expressed through the
+ * contracting-dimension index exactly as `DotDimensionNumbers` does.  Pointers are device
+ * pointers valid on the current CUDA device; the caller owns every buffer.  Work is enqueued on
+ * the given stream and nothing synchronises.  Return value: 0 on success, otherwise an
+ * `absl::StatusCode` / `XLA_FFI_Error_Code` number (3 INVALID_ARGUMENT, 12 UNIMPLEMENTED,
+ * 13 INTERNAL ...), with a message copied into `err` when `err_len > 0`.
+ */
+#ifndef B200_SCALED_DOT_H_
+#define B200_SCALED_DOT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types use xla::PrimitiveType numbers (= XLA_FFI_DataType, xla/ffi/api/c_api.h:233-266). */
+enum {
+  B200SD_S8 = 2,
+  B200SD_S32 = 4,
+  B200SD_F16 = 10,
+  B200SD_F32 = 11,
+  B200SD_BF16 = 16,
+  B200SD_F8E5M2 = 19,
+  B200SD_F8E4M3FN = 20
+};
+
+/* GemmBackendConfig.Epilogue (xla/service/gpu/backend_configs.proto:106-117). */
+enum {
+  B200SD_EPILOGUE_DEFAULT = 1,
+  B200SD_EPILOGUE_BIAS = 2,
+  B200SD_EPILOGUE_RELU = 3,
+  B200SD_EPILOGUE_BIAS_RELU = 4,
+  B200SD_EPILOGUE_GELU = 5,
+  B200SD_EPILOGUE_GELU_AUX = 6,       /* not implemented: returns UNIMPLEMENTED */
+  B200SD_EPILOGUE_BIAS_GELU = 7,
+  B200SD_EPILOGUE_BIAS_GELU_AUX = 8   /* not implemented: returns UNIMPLEMENTED */
+};
+
+/* Kernel choice; plays the role of GemmBackendConfig.selected_algorithm. */
+enum { B200SD_KERNEL_AUTO = 0, B200SD_KERNEL_DENSE = 1, B200SD_KERNEL_SKINNY = 2 };
+
+/* Arguments of one FP8 scaled dot.
+ *
+ *   D = cast( d_scale * act( alpha * a_scale * b_scale * dot(A, B) + beta * C + bias ) )
+ *   amax = max | act(...) |                     (value before d_scale, f32)
+ *
+ * Mirrors what `cuda::BlasLt::MatmulPlan::ExecuteOnStream` passes to cublasLtMatmul
+ * (xla/stream_executor/cuda/cuda_blas_lt.cc:456-576) and the operand meaning fixed by
+ * `ThunkEmitter::EmitCublasLtMatmulF8` (xla/service/gpu/thunk_emitter.cc:776-862).
+ * A is [m,k] when lhs_contracting_dim == 1, [k,m] when 0; B is [k,n] when rhs_contracting_dim
+ * == 0, [n,k] when 1.  m, n and k must be multiples of 16 (the rewriter pads to 16,
+ * xla/backends/gpu/transforms/gemm_rewriter.cc:1556-1580).
+ */
+typedef struct B200SD_ScaledDotF8 {
+  size_t struct_size;            /* sizeof(B200SD_ScaledDotF8), for forward compatibility */
+  const void* a;
+  const void* b;
+  const void* c;                 /* optional matrix bias [m,n], used when beta != 0 */
+  const void* bias;              /* optional vector bias [n] */
+  const float* a_scale;          /* device scalars; NULL means 1.0 */
+  const float* b_scale;
+  const float* d_scale;
+  void* d;                       /* [m,n] */
+  float* amax;                   /* optional device scalar, overwritten */
+  void* workspace;               /* scratch owned by the caller (the custom call's s8[] result) */
+  size_t workspace_bytes;
+  int64_t m, n, k;
+  int32_t a_dtype, b_dtype;      /* B200SD_F8E4M3FN or B200SD_F8E5M2, not both e5m2 */
+  int32_t c_dtype, bias_dtype;   /* B200SD_BF16, B200SD_F16 or B200SD_F32 */
+  int32_t d_dtype;               /* BF16, F16, F32, F8E4M3FN or F8E5M2 */
+  int32_t lhs_contracting_dim;   /* 0 or 1 */
+  int32_t rhs_contracting_dim;   /* 0 or 1 */
+  int32_t epilogue;              /* B200SD_EPILOGUE_* */
+  float alpha, beta;
+  int32_t kernel;                /* B200SD_KERNEL_* */
+} B200SD_ScaledDotF8;
+
+/* Arguments of one s8 x s8 dot with s32 accumulation, optionally followed by the dequantising
+ * multiply XLA emits as a separate loop fusion (gemm_rewriter.cc:897-901 refuses to fuse it):
+ *   acc = dot(A, B)                                  exact, s32
+ *   D   = cast( f32(acc) * a_row_scale[m] * b_col_scale[n] )
+ * d_dtype S32 returns acc itself (what `__cublas$lt$matmul` with I32 compute returns,
+ * xla/stream_executor/cuda/cuda_blas_lt.cc:444-445).  `acc_out`, when not NULL, additionally
+ * receives acc so that the s32 intermediate can be checked bit for bit.
+ */
+typedef struct B200SD_DotS8 {
+  size_t struct_size;
+  const void* a;
+  const void* b;
+  const float* a_row_scale;      /* optional [m] */
+  const float* b_col_scale;      /* optional [n] */
+  void* d;
+  int32_t* acc_out;              /* optional s32 [m,n] */
+  int64_t m, n, k;
+  int32_t d_dtype;               /* S32, F32 or BF16 */
+  int32_t lhs_contracting_dim;
+  int32_t rhs_contracting_dim;
+} B200SD_DotS8;
+
+/* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the
+ * first launch on a device; call it yourself before capturing a stream into a CUDA graph. */
+int b200sd_init_device(char* err, size_t err_len);
+
+/* Replaces the cublasLtMatmul call of xla/stream_executor/cuda/cuda_blas_lt.cc:559-564 (FP8). */
+int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char* err, size_t err_len);
+
+/* Replaces the same call for s8 x s8 -> s32 (type table at cuda_blas_lt.cc:444-445). */
+int b200sd_dot_s8(const B200SD_DotS8* args, void* cuda_stream, char* err, size_t err_len);
+
+/* Validate everything about a call except the pointer values (which may be NULL): types, shapes,
+ * epilogue, the supported type table (`TypesAreSupportedByCublasLt`,
+ * xla/backends/gpu/transforms/gemm_rewriter.cc:2425-2677).  No device access; this is what the FFI
+ * handlers run in the `instantiate` stage. */
+int b200sd_check_scaled_dot_f8(const B200SD_ScaledDotF8* args, char* err, size_t err_len);
+int b200sd_check_dot_s8(const B200SD_DotS8* args, char* err, size_t err_len);
+
+/* Bytes of workspace the split-K kernel wants for a problem (0 when the dense kernel is used).
+ * XLA always provides 32 MiB (xla/service/gpu/matmul_utils.h:103), which covers every case. */
+size_t b200sd_workspace_bytes(int64_t m, int64_t n, int64_t k);
+
+/* Which kernel B200SD_KERNEL_AUTO picks; the static stand-in for the cuBLASLt autotuner
+ * (xla/backends/gpu/autotuner/cublaslt.cc:84-189). */
+int b200sd_select_kernel(int64_t m, int64_t n, int64_t k);
+
+/* Number of kernels this library has launched in the calling process (for benchmarks). */
+uint64_t b200sd_launch_count(void);
+
+/* Synchronises the device, then returns and clears the bit mask kernels set when one of their
+ * bounded waits expired (0 = healthy).  The host-visible half of failure detection; stands where
+ * the reference relies on its execution watchdog (xla/service/gpu/execution_watchdog.h:43-61). */
+int b200sd_device_status(uint32_t* bits, char* err, size_t err_len);
+
+/* Launches a one-thread kernel that waits `limit_ns` on a barrier nobody signals and then reports
+ * through the status word (value 16).  Lets a test watch a wait expire without faulting anything. */
+int b200sd_wait_probe(uint64_t limit_ns, void* cuda_stream, char* err, size_t err_len);
+
+/* ---- XLA FFI handlers (typed FFI, api_version = API_VERSION_TYPED_FFI) -----------------------
+ * Signature: XLA_FFI_Error* (*)(XLA_FFI_CallFrame*), xla/ffi/api/c_api.h:517.  Declared with
+ * void* here so that this header does not depend on XLA's.  Register them under the custom-call
+ * targets "b200$scaled_dot$f8" and "b200$dot$s8" (platform "CUDA"); they accept the operand and
+ * result arrangements of `__cublas$lt$matmul$f8` (xla/service/gpu/thunk_emitter.cc:776-862).
+ * The *_instantiate / *_initialize symbols are the optional stages of the handler bundle
+ * (c_api.h:520-526). */
+#ifndef B200SD_NO_FFI_DECLS
+void* b200sd_ffi_scaled_dot_f8(void* call_frame);
+void* b200sd_ffi_scaled_dot_f8_instantiate(void* call_frame);
+void* b200sd_ffi_scaled_dot_f8_initialize(void* call_frame);
+void* b200sd_ffi_dot_s8(void* call_frame);
+void* b200sd_ffi_dot_s8_instantiate(void* call_frame);
+void* b200sd_ffi_dot_s8_initialize(void* call_frame);
+#endif
+
+/* Registers both bundles with the given `const XLA_FFI_Api*` (what XLA_FFI_REGISTER_HANDLER does,
+ * xla/ffi/api/api.h:2881-2893).  Returns 0 or an error code. */
+int b200sd_ffi_register(const void* xla_ffi_api, char* err, size_t err_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SCALED_DOT_H_ */

@@ -1,0 +1,93 @@
+"""Regenerates tests/golden/*.json from the reference checkout.
+
+Run in the authoring container only (`python tests/golden/make_golden.py
+[reference_root]`); the JSON it writes is committed so that the test-suite
+never needs the reference tree at run time.
+
+Sources, read as text:
+  * xla/tests/convert_test.cc -- the `{input, expected_roundtrip}` tables of
+    ConvertF16F8e5m2Roundtrip, ConvertF32F8e5m2Roundtrip,
+    ConvertF16F8e4m3fnRoundtrip and ConvertF32F8e4m3fnRoundtrip (C hex-float
+    literals, `nan`, `inf`).
+  * xla/stream_executor/cuda/cuda_blas_lt_test.cc -- the S8S8S32 / S8S8F32
+    known answer: m = n = k = 32, all-ones operands, every output == k.
+"""
+import json
+import math
+import os
+import re
+import sys
+
+ROOT = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def parse_literal(tok: str) -> float:
+    tok = tok.strip()
+    neg = tok.startswith("-")
+    body = tok.lstrip("+-")
+    if body == "nan":
+        return math.nan
+    if body == "inf":
+        return -math.inf if neg else math.inf
+    v = float.fromhex(body) if body.lower().startswith("0x") else float(body)
+    return -v if neg else v
+
+
+def table_of(src: str, test_name: str):
+    start = src.index(f"TEST_F(ConvertTest, {test_name})")
+    begin = src.index("test_cases[] = {", start)
+    end = src.index("};", begin)
+    rows = []
+    for m in re.finditer(r"\{\s*([^,{}]+?)\s*,\s*([^,{}]+?)\s*\}", src[begin:end]):
+        rows.append((parse_literal(m.group(1)), parse_literal(m.group(2))))
+    return rows
+
+
+def enc(v: float):
+    """JSON-safe exact spelling of a double."""
+    if math.isnan(v):
+        return "nan"
+    if math.isinf(v):
+        return "-inf" if v < 0 else "inf"
+    return v.hex()
+
+
+def main():
+    src = open(os.path.join(ROOT, "xla/tests/convert_test.cc")).read()
+    out = {"source": "xla/tests/convert_test.cc", "tables": {}}
+    for name, kind, via in [
+        ("ConvertF16F8e5m2Roundtrip", "e5m2", "f16"),
+        ("ConvertF32F8e5m2Roundtrip", "e5m2", "f32"),
+        ("ConvertF16F8e4m3fnRoundtrip", "e4m3fn", "f16"),
+        ("ConvertF32F8e4m3fnRoundtrip", "e4m3fn", "f32"),
+    ]:
+        rows = table_of(src, name)
+        assert len(rows) >= 15, (name, len(rows))
+        out["tables"][name] = {
+            "fp8": kind,
+            "via": via,
+            "line": src[: src.index(f"TEST_F(ConvertTest, {name})")].count("\n") + 1,
+            "cases": [[enc(a), enc(b)] for a, b in rows],
+        }
+    with open(os.path.join(HERE, "fp8_convert_roundtrip.json"), "w") as f:
+        json.dump(out, f, indent=1)
+
+    blas = open(os.path.join(ROOT, "xla/stream_executor/cuda/cuda_blas_lt_test.cc")).read()
+    m = re.search(r"int64_t m = (\d+), n = (\d+), k = (\d+);", blas)
+    dims = [int(g) for g in m.groups()]
+    assert "std::vector<int8_t> host_a(m * k, 1)" in blas or "(m * k, 1)" in blas
+    known = {
+        "source": "xla/stream_executor/cuda/cuda_blas_lt_test.cc",
+        "tests": ["S8S8S32Gemm", "S8S8F32Gemm"],
+        "m": dims[0], "n": dims[1], "k": dims[2],
+        "a_fill": 1, "b_fill": 1, "alpha": 1.0, "beta": 0.0,
+        "expected_every_element": dims[2],
+    }
+    with open(os.path.join(HERE, "s8_known_answer.json"), "w") as f:
+        json.dump(known, f, indent=1)
+    print("wrote", sorted(os.listdir(HERE)))
+
+
+if __name__ == "__main__":
+    main()

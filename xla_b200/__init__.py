@@ -1,0 +1,21 @@
+"""B200-native replacement for XLA's quantized scaled-dot custom calls.
+
+The product is the shared library `xla_b200/lib/libb200_scaled_dot.so` (hand-written sm_100a
+kernels behind XLA FFI handlers, declared in `include/b200_scaled_dot.h`).  This package is the
+host-side mirror used to drive it without an XLA build: a stand-in for the XLA side of the FFI
+(`ffi_runtime`), the custom-call front end (`scaled_dot`) and the two sharded launch patterns
+(`sharding`).  There is no CPU or PyTorch fallback: importing the native layer fails loudly when
+the library has not been built.
+"""
+
+from . import _native  # noqa: F401  (fails loudly if the library is missing)
+from .scaled_dot import (  # noqa: F401
+    Epilogue,
+    GemmBackendConfig,
+    ScaledDotCall,
+    Int8DotCall,
+    cublas_lt_matmul_f8,
+    cublas_lt_matmul_s8,
+    device_status,
+    launch_count,
+)

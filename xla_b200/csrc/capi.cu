@@ -1,0 +1,282 @@
+// Plain C entry points of libb200_scaled_dot.so: argument validation (the checks the reference
+// spreads over GemmRewriter::CreateF8CustomCall, TypesAreSupportedByCublasLt and
+// cuda::BlasLt::GetMatmulPlan), kernel selection (instead of the cuBLASLt autotuner) and launch.
+#include <atomic>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/b200_scaled_dot.h"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b200sd {
+
+// Status word the kernels OR their error bits into (one instance per device that loads the
+// library).  Kernels receive its device address as an argument.
+__device__ uint32_t g_device_status;
+
+Status InitDenseKernels();
+Status InitSkinnyKernels();
+
+namespace {
+
+struct DeviceState {
+  std::once_flag once;
+  Status init_status;
+  int sm_count = 0;
+  uint32_t* status_word = nullptr;
+};
+DeviceState g_state[64];
+std::atomic<uint64_t> g_launches{0};
+
+int CopyStatus(const Status& s, char* err, size_t err_len) {
+  if (err != nullptr && err_len > 0) {
+    const size_t n = s.message.size() < err_len - 1 ? s.message.size() : err_len - 1;
+    std::memcpy(err, s.message.data(), n);
+    err[n] = '\0';
+  }
+  return s.code;
+}
+
+bool IsF8(int32_t t) { return t == kF8E4M3FN || t == kF8E5M2; }
+
+__global__ void wait_probe_kernel(uint64_t limit_ns, uint32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    // Nobody ever arrives on `bar`: the wait below can only end through its time limit.
+    (void)mbar_wait(&bar, 0, &abort_flag, status, kStatusProbeTimeout, limit_ns);
+  }
+}
+
+}  // namespace
+
+Status InitDevice(int device) {
+  if (device < 0 || device >= 64) return Status::Error(kInvalidArgument, "device ordinal out of range");
+  DeviceState& st = g_state[device];
+  std::call_once(st.once, [&] {
+    cudaDeviceProp prop{};
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+      st.init_status = Status::Error(kInternal, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+      return;
+    }
+    if (prop.major != 10) {
+      st.init_status = Status::Error(kFailedPrecondition,
+                                     "libb200_scaled_dot needs an sm_100 (Blackwell B200) device, found sm_" +
+                                         std::to_string(prop.major) + std::to_string(prop.minor));
+      return;
+    }
+    st.sm_count = prop.multiProcessorCount;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.status_word), g_device_status);
+    if (e != cudaSuccess) {
+      st.init_status = Status::Error(kInternal, std::string("cudaGetSymbolAddress(status): ") + cudaGetErrorString(e));
+      return;
+    }
+    st.init_status = InitDenseKernels();
+    if (st.init_status.ok()) st.init_status = InitSkinnyKernels();
+  });
+  return st.init_status;
+}
+
+int DeviceSmCount() {
+  int device = 0;
+  cudaGetDevice(&device);
+  return (device >= 0 && device < 64 && g_state[device].sm_count > 0) ? g_state[device].sm_count : 148;
+}
+
+uint32_t* StatusWordPtr() {
+  int device = 0;
+  cudaGetDevice(&device);
+  return (device >= 0 && device < 64) ? g_state[device].status_word : nullptr;
+}
+
+Status ReadDeviceStatus(uint32_t* bits) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaDeviceSynchronize: ") + cudaGetErrorString(e));
+  uint32_t v = 0, zero = 0;
+  e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(v));
+  if (e == cudaSuccess && v != 0) e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero));
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("status word copy: ") + cudaGetErrorString(e));
+  *bits = v;
+  return Status::Ok();
+}
+
+Status LaunchWaitProbe(uint64_t limit_ns, cudaStream_t stream) {
+  if (limit_ns > 1000000000ull) return Status::Error(kInvalidArgument, "probe limit above one second");
+  int device = 0;
+  cudaGetDevice(&device);
+  Status st = InitDevice(device);
+  if (!st.ok()) return st;
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_ns, StatusWordPtr());
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("wait_probe_kernel launch: ") + cudaGetErrorString(e));
+  return Status::Ok();
+}
+
+// Static kernel choice.  Decode-shaped problems (few rows of A, a weight matrix that has to be
+// streamed once from HBM) go to the split-K kernel, everything else to the dense kernel.
+int SelectKernel(int64_t m, int64_t n, int64_t k) {
+  if (m <= 128 && n >= 1024 && k >= 1024 && SkinnyWorkspaceBytes(m, n, k) > 0) return kKernelSkinny;
+  return kKernelDense;
+}
+
+Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointers = true) {
+  if (a.struct_size < sizeof(B200SD_ScaledDotF8)) return Status::Error(kInvalidArgument, "B200SD_ScaledDotF8.struct_size is smaller than this library's struct");
+  if (check_pointers && (a.a == nullptr || a.b == nullptr || a.d == nullptr)) return Status::Error(kInvalidArgument, "a, b and d must not be null");
+  if (!IsF8(a.a_dtype) || !IsF8(a.b_dtype)) return Status::Error(kInvalidArgument, "operands must be F8E4M3FN or F8E5M2");
+  if (a.a_dtype == kF8E5M2 && a.b_dtype == kF8E5M2) return Status::Error(kUnimplemented, "F8E5M2 x F8E5M2 is not a supported FP8 dot (one operand must be F8E4M3FN)");
+  const int32_t d = a.d_dtype;
+  if (!(d == kBF16 || d == kF16 || d == kF32 || d == kF8E4M3FN || d == kF8E5M2)) return Status::Error(kInvalidArgument, "output type must be BF16, F16, F32, F8E4M3FN or F8E5M2");
+  if (d == kF8E5M2 && a.a_dtype == kF8E4M3FN && a.b_dtype == kF8E4M3FN) return Status::Error(kUnimplemented, "F8E4M3FN x F8E4M3FN -> F8E5M2 is not in the supported type table");
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return Status::Error(kInvalidArgument, "m, n and k must be positive");
+  if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16 (pad as the rewriter does)");
+  if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
+  if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
+  bool has_bias = false;
+  int32_t act = kActNone;
+  switch (a.epilogue) {
+    case B200SD_EPILOGUE_DEFAULT: break;
+    case B200SD_EPILOGUE_BIAS: has_bias = true; break;
+    case B200SD_EPILOGUE_RELU: act = kActRelu; break;
+    case B200SD_EPILOGUE_BIAS_RELU: has_bias = true; act = kActRelu; break;
+    case B200SD_EPILOGUE_GELU: act = kActGelu; break;
+    case B200SD_EPILOGUE_BIAS_GELU: has_bias = true; act = kActGelu; break;
+    case B200SD_EPILOGUE_GELU_AUX:
+    case B200SD_EPILOGUE_BIAS_GELU_AUX: return Status::Error(kUnimplemented, "epilogues with an auxiliary output are not implemented");
+    default: return Status::Error(kInvalidArgument, "unknown epilogue " + std::to_string(a.epilogue));
+  }
+  if (has_bias) {
+    if (check_pointers && a.bias == nullptr) return Status::Error(kInvalidArgument, "epilogue adds a vector bias but bias is null");
+    if (!(a.bias_dtype == kBF16 || a.bias_dtype == kF16 || a.bias_dtype == kF32)) return Status::Error(kInvalidArgument, "bias must be BF16, F16 or F32");
+  }
+  if (a.beta != 0.0f) {
+    if (check_pointers && a.c == nullptr) return Status::Error(kInvalidArgument, "beta != 0 but c is null");
+    if (!(a.c_dtype == kBF16 || a.c_dtype == kF16 || a.c_dtype == kF32)) return Status::Error(kInvalidArgument, "c must be BF16, F16 or F32");
+  }
+  g->m = a.m; g->n = a.n; g->k = a.k;
+  g->int8 = false;
+  g->a_dtype = a.a_dtype; g->b_dtype = a.b_dtype;
+  g->a_mn_major = a.lhs_contracting_dim == 0;
+  g->b_mn_major = a.rhs_contracting_dim == 0;
+  g->a = a.a; g->b = a.b;
+  g->a_scale = a.a_scale; g->b_scale = a.b_scale; g->d_scale = a.d_scale;
+  g->alpha = a.alpha; g->beta = a.beta;
+  g->c = a.beta != 0.0f ? a.c : nullptr; g->c_dtype = a.c_dtype;
+  g->bias = has_bias ? a.bias : nullptr; g->bias_dtype = a.bias_dtype;
+  g->activation = act;
+  g->amax = a.amax;
+  g->d = a.d; g->d_dtype = a.d_dtype;
+  g->workspace = a.workspace; g->workspace_bytes = a.workspace_bytes;
+  return Status::Ok();
+}
+
+Status ValidateS8(const B200SD_DotS8& a, GemmProblem* g, bool check_pointers = true) {
+  if (a.struct_size < sizeof(B200SD_DotS8)) return Status::Error(kInvalidArgument, "B200SD_DotS8.struct_size is smaller than this library's struct");
+  if (check_pointers && (a.a == nullptr || a.b == nullptr || a.d == nullptr)) return Status::Error(kInvalidArgument, "a, b and d must not be null");
+  if (!(a.d_dtype == kS32 || a.d_dtype == kF32 || a.d_dtype == kBF16)) return Status::Error(kInvalidArgument, "output type must be S32, F32 or BF16");
+  if (a.d_dtype == kS32 && (a.a_row_scale || a.b_col_scale)) return Status::Error(kInvalidArgument, "dequantisation scales need a floating-point output type");
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return Status::Error(kInvalidArgument, "m, n and k must be positive");
+  if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16");
+  if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
+  if (a.k > 133144) return Status::Error(kInvalidArgument, "k too large for exact s32 accumulation of s8 products");
+  if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
+  g->m = a.m; g->n = a.n; g->k = a.k;
+  g->int8 = true;
+  g->a_dtype = kS8; g->b_dtype = kS8;
+  g->a_mn_major = a.lhs_contracting_dim == 0;
+  g->b_mn_major = a.rhs_contracting_dim == 0;
+  g->a = a.a; g->b = a.b;
+  g->a_row_scale = a.a_row_scale; g->b_col_scale = a.b_col_scale;
+  g->d_s32 = a.acc_out;
+  g->d = a.d; g->d_dtype = a.d_dtype;
+  return Status::Ok();
+}
+
+}  // namespace b200sd
+
+using namespace b200sd;
+
+extern "C" {
+
+int b200sd_init_device(char* err, size_t err_len) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return CopyStatus(Status::Error(kInternal, std::string("cudaGetDevice: ") + cudaGetErrorString(e)), err, err_len);
+  return CopyStatus(InitDevice(device), err, err_len);
+}
+
+int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char* err, size_t err_len) {
+  if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
+  GemmProblem g;
+  Status st = ValidateF8(*args, &g);
+  if (!st.ok()) return CopyStatus(st, err, err_len);
+  int kernel = args->kernel;
+  if (kernel == B200SD_KERNEL_AUTO) kernel = SelectKernel(g.m, g.n, g.k);
+  if (kernel == B200SD_KERNEL_SKINNY) {
+    // The split-K kernel covers the plain scaled dot only; fall back to the dense kernel for the rest
+    // or when the caller's workspace is too small.
+    const bool plain = g.c == nullptr && g.bias == nullptr && g.activation == kActNone && g.amax == nullptr &&
+                       !g.a_mn_major && g.b_mn_major && g.m <= 128 && g.a_dtype == kF8E4M3FN &&
+                       g.b_dtype == kF8E4M3FN;
+    const size_t need = SkinnyWorkspaceBytes(g.m, g.n, g.k);
+    if (!plain || need == 0 || g.workspace == nullptr || g.workspace_bytes < need) {
+      if (args->kernel == B200SD_KERNEL_SKINNY)
+        return CopyStatus(Status::Error(kInvalidArgument, "the split-K kernel needs m <= 128, row-major A[m,k] and B[k,n], e4m3 operands, "
+                                                          "no bias/activation/amax and a workspace of b200sd_workspace_bytes()"),
+                          err, err_len);
+      kernel = B200SD_KERNEL_DENSE;
+    }
+  }
+  LaunchStats stats;
+  st = kernel == B200SD_KERNEL_SKINNY ? LaunchSkinny(g, static_cast<cudaStream_t>(cuda_stream), &stats)
+                                      : LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats);
+  if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
+  return CopyStatus(st, err, err_len);
+}
+
+int b200sd_dot_s8(const B200SD_DotS8* args, void* cuda_stream, char* err, size_t err_len) {
+  if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
+  GemmProblem g;
+  Status st = ValidateS8(*args, &g);
+  if (!st.ok()) return CopyStatus(st, err, err_len);
+  LaunchStats stats;
+  st = LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats);
+  if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
+  return CopyStatus(st, err, err_len);
+}
+
+int b200sd_check_scaled_dot_f8(const B200SD_ScaledDotF8* args, char* err, size_t err_len) {
+  if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
+  GemmProblem g;
+  return CopyStatus(ValidateF8(*args, &g, /*check_pointers=*/false), err, err_len);
+}
+
+int b200sd_check_dot_s8(const B200SD_DotS8* args, char* err, size_t err_len) {
+  if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
+  GemmProblem g;
+  return CopyStatus(ValidateS8(*args, &g, /*check_pointers=*/false), err, err_len);
+}
+
+size_t b200sd_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+  return SelectKernel(m, n, k) == kKernelSkinny ? SkinnyWorkspaceBytes(m, n, k) : 0;
+}
+
+int b200sd_select_kernel(int64_t m, int64_t n, int64_t k) { return SelectKernel(m, n, k); }
+
+uint64_t b200sd_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b200sd_device_status(uint32_t* bits, char* err, size_t err_len) {
+  if (bits == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "bits is null"), err, err_len);
+  return CopyStatus(ReadDeviceStatus(bits), err, err_len);
+}
+
+int b200sd_wait_probe(uint64_t limit_ns, void* cuda_stream, char* err, size_t err_len) {
+  return CopyStatus(LaunchWaitProbe(limit_ns, static_cast<cudaStream_t>(cuda_stream)), err, err_len);
+}
+
+}  // extern "C"

@@ -1,0 +1,534 @@
+// Dense quantized GEMM for sm_100a: the kernel behind XLA's `__cublas$lt$matmul$f8` pattern
+// (FP8 e4m3fn / e5m2 operands, f32 accumulate) and the s8 x s8 -> s32 dot, with the whole epilogue
+// fused.  Replaces the library call at xla/stream_executor/cuda/cuda_blas_lt.cc:559-564.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: streams 128x128-byte A tiles and 256x128-byte B tiles into a
+//               4-stage ring of 128B-swizzled shared memory.
+//   warp 1      allocates all 512 TMEM columns, then one elected thread issues
+//               tcgen05.mma (M=128, N=256, K=32; four per stage) into one of two f32/s32
+//               accumulators and commits stage-free / accumulator-ready mbarriers.
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one row per thread), apply
+//               scale / beta*C / bias / ReLU or GELU / amax / d_scale / cast, store D.  The other
+//               accumulator is being filled by the next tile's main loop meanwhile.
+// Every wait is bounded; on expiry the kernel records a status bit and drains.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <string>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b200sd {
+
+namespace {
+
+constexpr int kBM = 128;          // rows of D per tile (= TMEM lanes)
+constexpr int kBN = 256;          // columns of D per tile (= TMEM columns per accumulator)
+constexpr int kBK = 128;          // bytes (= 8-bit elements) of K per stage: one 128B swizzle row
+constexpr int kUmmaK = 32;        // K per tcgen05.mma for 8-bit operands
+constexpr int kStages = 4;
+constexpr int kAccBufs = 2;
+constexpr int kAStageBytes = kBM * kBK;          // 16 KiB
+constexpr int kBStageBytes = kBN * kBK;          // 32 KiB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kTmemCols = 512;
+
+struct __align__(16) DenseAux {
+  uint64_t full_bar[kStages];
+  uint64_t empty_bar[kStages];
+  uint64_t acc_full_bar[kAccBufs];
+  uint64_t acc_empty_bar[kAccBufs];
+  uint32_t tmem_base;
+  int abort_flag;
+  float bias_s[4][kBN];      // one private copy per epilogue warp: no CTA-level barrier needed
+  float colscale_s[4][kBN];
+};
+
+constexpr size_t kDenseSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(DenseAux);
+
+struct DenseArgs {
+  int64_t m, n, k;
+  int32_t num_m_tiles, num_n_tiles, num_k_blocks, raster_group;
+  int32_t a_mn_major, b_mn_major;
+  uint32_t idesc;
+  const float* a_scale;
+  const float* b_scale;
+  const float* d_scale;
+  float alpha, beta;
+  const void* c;
+  int32_t c_dtype;
+  const void* bias;
+  int32_t bias_dtype;
+  int32_t activation;
+  float* amax;
+  const float* a_row_scale;
+  const float* b_col_scale;
+  int32_t* d_s32;
+  void* d;
+  int32_t d_dtype;
+  int32_t vec_store_ok;  // D rows start 16-byte aligned and N is a multiple of the vector width
+  uint32_t* status;      // device status word (error bits)
+};
+
+__device__ __forceinline__ float load_as_f32(const void* base, int32_t dtype, int64_t idx) {
+  switch (dtype) {
+    case kF32: return static_cast<const float*>(base)[idx];
+    case kBF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+    case kF16: return __half2float(static_cast<const __half*>(base)[idx]);
+    default: return 0.0f;
+  }
+}
+
+// tanh-form GELU, spelled like the HLO the rewriter matches
+// (xla/backends/gpu/transforms/gemm_rewriter.cc:924-971).
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float x3 = x * x * x;
+  const float inner = 0.797884583f * (x + 0.044715f * x3);
+  return x * (0.5f * (1.0f + tanhf(inner)));
+}
+
+__device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, int32_t* mt, int32_t* nt) {
+  // Groups of `raster_group` row-tiles are swept column by column so that the CTAs running at the
+  // same time share A row-panels and B column-panels in L2.
+  const int32_t per_group = p.raster_group * p.num_n_tiles;
+  const int32_t g = tile / per_group;
+  const int32_t first_m = g * p.raster_group;
+  const int32_t gsize = min(p.raster_group, p.num_m_tiles - first_m);
+  const int32_t r = tile - g * per_group;
+  *mt = first_m + r % gsize;
+  *nt = r / gsize;
+}
+
+// Converts and stores 32 consecutive columns of one row.
+__device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float (&v)[32], int64_t row, int64_t col0,
+                                                int32_t ncols) {
+  const int64_t off = row * p.n + col0;
+  if (p.d_dtype == kF8E4M3FN || p.d_dtype == kF8E5M2) {
+    const __nv_fp8_interpretation_t fmt = p.d_dtype == kF8E4M3FN ? __NV_E4M3 : __NV_E5M2;
+    uint8_t* out = static_cast<uint8_t*>(p.d) + off;
+    if (ncols == 32 && p.vec_store_ok) {
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i], v[4 * i + 1]), __NV_SATFINITE, fmt);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i + 2], v[4 * i + 3]), __NV_SATFINITE, fmt);
+        w[i] = lo | (hi << 16);
+      }
+      reinterpret_cast<uint4*>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+      for (int i = 0; i < ncols; ++i) out[i] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, fmt);
+    }
+  } else if (p.d_dtype == kBF16 || p.d_dtype == kF16) {
+    uint16_t* out = static_cast<uint16_t*>(p.d) + off;
+    const bool bf = p.d_dtype == kBF16;
+    if (ncols == 32 && p.vec_store_ok) {
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (bf) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        } else {
+          const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        reinterpret_cast<uint4*>(out)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    } else {
+      for (int i = 0; i < ncols; ++i) {
+        if (bf) {
+          const __nv_bfloat16 h = __float2bfloat16_rn(v[i]);
+          out[i] = *reinterpret_cast<const uint16_t*>(&h);
+        } else {
+          const __half h = __float2half_rn(v[i]);
+          out[i] = *reinterpret_cast<const uint16_t*>(&h);
+        }
+      }
+    }
+  } else {  // kF32
+    float* out = static_cast<float*>(p.d) + off;
+    if (ncols == 32 && p.vec_store_ok) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(out)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+      for (int i = 0; i < ncols; ++i) out[i] = v[i];
+    }
+  }
+}
+
+template <bool kInt8>
+__global__ void __launch_bounds__(kThreads, 1)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const DenseArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kAStageBytes;
+  DenseAux* aux = reinterpret_cast<DenseAux*>(smem + kStages * kStageBytes);
+  volatile int* abort_flag = &aux->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int32_t num_tiles = p.num_m_tiles * p.num_n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&aux->full_bar[s], 1);
+      mbar_init(&aux->empty_bar[s], 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(&aux->acc_full_bar[b], 1);
+      mbar_init(&aux->acc_empty_bar[b], kEpilogueThreads);
+    }
+    aux->abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&aux->tmem_base, kTmemCols);
+    tmem_relinquish_alloc();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = aux->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int32_t mt, nt;
+        tile_coords(tile, p, &mt, &nt);
+        for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          if (!ok) break;
+          uint64_t* full = &aux->full_bar[stage];
+          mbar_arrive_expect_tx(full, kStageBytes);
+          uint8_t* sa = smem_a + stage * kAStageBytes;
+          uint8_t* sb = smem_b + stage * kBStageBytes;
+          if (p.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, full, mt * kBM, kb * kBK);
+          } else {
+            tma_load_2d(sa, &tmap_a, full, kb * kBK, mt * kBM);
+          }
+          if (p.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, full, nt * kBN, kb * kBK);
+            tma_load_2d(sb + kBStageBytes / 2, &tmap_b, full, nt * kBN + 128, kb * kBK);
+          } else {
+            tma_load_2d(sb, &tmap_b, full, kb * kBK, nt * kBN);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Abort path: let loads that were already issued land before the CTA's memory is released.
+        for (int s = 0; s < kStages; ++s) {
+          for (int i = 0; i < 100000 && !mbar_try_wait(&aux->full_bar[s], 0) && !mbar_try_wait(&aux->full_bar[s], 1); ++i) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t a_lbo = 16384, b_lbo = 16384, sbo = 1024;
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), a_lbo, sbo);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), b_lbo, sbo);
+      // Encoded (>>4) advance of the start address per K=32 step: 32 bytes along a K-major row,
+      // 32 rows of 128 bytes for an MN-major operand.
+      const uint32_t a_kstep = p.a_mn_major ? (kUmmaK * 128) >> 4 : kUmmaK >> 4;
+      const uint32_t b_kstep = p.b_mn_major ? (kUmmaK * 128) >> 4 : kUmmaK >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
+          const uint64_t b_desc = b_desc0 + uint64_t((stage * kBStageBytes) >> 4);
+#pragma unroll
+          for (int j = 0; j < kBK / kUmmaK; ++j) {
+            const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+            if (kInt8) {
+              umma_i8(d_tmem, a_desc + uint64_t(j * a_kstep), b_desc + uint64_t(j * b_kstep), p.idesc, accumulate);
+            } else {
+              umma_f8(d_tmem, a_desc + uint64_t(j * a_kstep), b_desc + uint64_t(j * b_kstep), p.idesc, accumulate);
+            }
+          }
+          umma_commit(&aux->empty_bar[stage]);   // stage reusable once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&aux->acc_full_bar[acc]);    // accumulator complete
+        if (++acc == kAccBufs) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                      // TMEM lane quarter this warp may access
+    float* bias_w = aux->bias_s[q];
+    float* colscale_w = aux->colscale_s[q];
+    float scale = p.alpha;
+    float d_scale = 1.0f;
+    if (!kInt8) {
+      if (p.a_scale) scale *= __ldg(p.a_scale);
+      if (p.b_scale) scale *= __ldg(p.b_scale);
+      if (p.d_scale) d_scale = __ldg(p.d_scale);
+    }
+    uint32_t amax_bits = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int32_t mt, nt;
+      tile_coords(tile, p, &mt, &nt);
+      const int64_t col_base = int64_t(nt) * kBN;
+      // Stage the per-column vectors of this tile (each warp keeps its own copy).
+      __syncwarp();
+      for (int i = lane; i < kBN; i += 32) {
+        const int64_t col = col_base + i;
+        if (p.bias) bias_w[i] = col < p.n ? load_as_f32(p.bias, p.bias_dtype, col) : 0.0f;
+        if (kInt8 && p.b_col_scale) colscale_w[i] = col < p.n ? __ldg(p.b_col_scale + col) : 0.0f;
+      }
+      __syncwarp();
+
+      // Lane 0 does the bounded wait; the warp then agrees on the outcome so that the
+      // warp-collective TMEM loads below never run with a partial warp.
+      if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
+      tc_fence_after_sync();
+
+      const int64_t row = int64_t(mt) * kBM + q * 32 + lane;
+      const bool row_ok = row < p.m;
+      float row_scale = 1.0f;
+      if (kInt8 && p.a_row_scale && row_ok) row_scale = __ldg(p.a_row_scale + row);
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN);
+
+#pragma unroll 1
+      for (int cchunk = 0; cchunk < kBN / 32; ++cchunk) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + cchunk * 32, r);
+        tmem_ld_wait();
+        const int64_t col0 = col_base + cchunk * 32;
+        if (col0 >= p.n) continue;
+        const int32_t ncols = static_cast<int32_t>(min(int64_t(32), p.n - col0));
+        if (!row_ok) continue;
+        float v[32];
+        if (kInt8) {
+          if (p.d_s32) {
+            int32_t* out = p.d_s32 + row * p.n + col0;
+            if (ncols == 32 && p.vec_store_ok) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<uint4*>(out)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            } else {
+              for (int i = 0; i < ncols; ++i) out[i] = static_cast<int32_t>(r[i]);
+            }
+          }
+          if (p.d == nullptr) continue;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __int2float_rn(static_cast<int32_t>(r[i]));
+            if (p.a_row_scale) x = x * row_scale;
+            if (p.b_col_scale) x = x * colscale_w[cchunk * 32 + i];
+            v[i] = x;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(r[i]) * scale;
+            if (p.c != nullptr && i < ncols) x += p.beta * load_as_f32(p.c, p.c_dtype, row * p.n + col0 + i);
+            if (p.bias) x += bias_w[cchunk * 32 + i];
+            if (p.activation == kActRelu) {
+              x = (x != x) ? x : fmaxf(x, 0.0f);
+            } else if (p.activation == kActGelu) {
+              x = gelu_tanh(x);
+            }
+            if (p.amax != nullptr && i < ncols) amax_bits = max(amax_bits, __float_as_uint(fabsf(x)));
+            v[i] = x * d_scale;
+          }
+        }
+        store_row_chunk(p, v, row, col0, ncols);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&aux->acc_empty_bar[acc]);
+      if (++acc == kAccBufs) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+    if (!kInt8 && p.amax != nullptr) {
+      // The bit pattern of a non-negative float orders like the float; NaN patterns sit above
+      // +inf, so an integer max propagates NaN the way XLA's `maximum` does.
+      amax_bits = __reduce_max_sync(0xffffffffu, amax_bits);
+      if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), amax_bits);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn GetEncodeTiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+// A row-major [rows, cols] byte matrix viewed as a 2-D tensor with `cols` innermost; box =
+// box_cols x box_rows, 128-byte swizzle, out-of-range elements read as zero.
+Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, uint32_t box_cols,
+                         uint32_t box_rows) {
+  EncodeTiledFn encode = GetEncodeTiled();
+  if (encode == nullptr) return Status::Error(kInternal, "cuTensorMapEncodeTiled is not available from this driver");
+  if (cols % 16 != 0) return Status::Error(kInvalidArgument, "the minor dimension of an 8-bit operand must be a multiple of 16");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return Status::Error(kInvalidArgument, "operand base address must be 16-byte aligned");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols)};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                            elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Status::Error(kInternal, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
+  return Status::Ok();
+}
+
+Status InitDenseKernels() {
+  cudaError_t e = cudaFuncSetAttribute(dense_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(kDenseSmemBytes));
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(dense_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(kDenseSmemBytes));
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(dense): ") + cudaGetErrorString(e));
+  return Status::Ok();
+}
+
+uint32_t FormatCode(int32_t dtype) {
+  // kind::f8f6f4: e4m3 = 0, e5m2 = 1; kind::i8: s8 = 1.
+  return dtype == kF8E5M2 ? 1u : (dtype == kS8 ? 1u : 0u);
+}
+
+Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats) {
+  int device = 0;
+  cudaGetDevice(&device);
+  Status st = InitDevice(device);
+  if (!st.ok()) return st;
+
+  CUtensorMap tmap_a, tmap_b;
+  if (g.a_mn_major) {
+    st = MakeByteMatrixMap(&tmap_a, g.a, g.k, g.m, 128, kBK);       // [k, m], box 128(m) x 128(k)
+  } else {
+    st = MakeByteMatrixMap(&tmap_a, g.a, g.m, g.k, kBK, kBM);       // [m, k], box 128(k) x 128(m)
+  }
+  if (!st.ok()) return st;
+  if (g.b_mn_major) {
+    st = MakeByteMatrixMap(&tmap_b, g.b, g.k, g.n, 128, kBK);       // [k, n], box 128(n) x 128(k), two per stage
+  } else {
+    st = MakeByteMatrixMap(&tmap_b, g.b, g.n, g.k, kBK, kBN);       // [n, k], box 128(k) x 256(n)
+  }
+  if (!st.ok()) return st;
+
+  DenseArgs p{};
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.num_m_tiles = int32_t((g.m + kBM - 1) / kBM);
+  p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
+  p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
+  p.raster_group = 16;
+  p.a_mn_major = g.a_mn_major; p.b_mn_major = g.b_mn_major;
+  p.idesc = make_idesc(g.int8 ? 2u : 1u, FormatCode(g.a_dtype), FormatCode(g.b_dtype), g.a_mn_major, g.b_mn_major,
+                       kBM, kBN);
+  p.a_scale = g.a_scale; p.b_scale = g.b_scale; p.d_scale = g.d_scale;
+  p.alpha = g.alpha; p.beta = g.beta;
+  p.c = (g.beta != 0.0f) ? g.c : nullptr; p.c_dtype = g.c_dtype;
+  p.bias = g.bias; p.bias_dtype = g.bias_dtype;
+  p.activation = g.activation;
+  p.amax = g.amax;
+  p.a_row_scale = g.a_row_scale; p.b_col_scale = g.b_col_scale;
+  p.d_s32 = g.d_s32;
+  p.d = g.d; p.d_dtype = g.d_dtype;
+  if (g.int8 && g.d_dtype == kS32) {   // the accumulator itself is the result
+    p.d_s32 = static_cast<int32_t*>(g.d);
+    p.d = nullptr;
+  }
+  // Vector stores need 16-byte aligned row starts for every output that is written.
+  auto aligned = [&](const void* ptr, int64_t elt) {
+    return ptr == nullptr || ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (g.n * elt) % 16 == 0);
+  };
+  const int64_t d_elt = (g.d_dtype == kF8E4M3FN || g.d_dtype == kF8E5M2) ? 1 : (g.d_dtype == kF32 || g.d_dtype == kS32) ? 4 : 2;
+  p.vec_store_ok = aligned(p.d, d_elt) && aligned(p.d_s32, 4);
+  p.status = StatusWordPtr();
+
+  const int64_t tiles = int64_t(p.num_m_tiles) * p.num_n_tiles;
+  const int grid = int(tiles < DeviceSmCount() ? tiles : DeviceSmCount());
+  if (g.amax != nullptr) {
+    cudaError_t e = cudaMemsetAsync(g.amax, 0, sizeof(float), stream);
+    if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(amax): ") + cudaGetErrorString(e));
+  }
+  if (g.int8) {
+    dense_gemm_kernel<true><<<grid, kThreads, kDenseSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  } else {
+    dense_gemm_kernel<false><<<grid, kThreads, kDenseSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("dense_gemm_kernel launch: ") + cudaGetErrorString(e));
+  if (stats) {
+    stats->kernel = kKernelDense;
+    stats->grid = grid;
+    stats->launches = 1;
+  }
+  return Status::Ok();
+}
+
+}  // namespace b200sd

@@ -1,0 +1,321 @@
+// XLA FFI handlers: the drop-in boundary.  An XLA process registers these under the custom-call
+// targets "b200$scaled_dot$f8" and "b200$dot$s8"; a GemmRewriter that emits those targets instead
+// of "__cublas$lt$matmul$f8" / "__cublas$lt$matmul" (xla/service/gpu/cublas_cudnn.h) gets this
+// library in place of CublasLtMatmulThunk + cuBLASLt.
+//
+// Call-frame contract (operand order of ThunkEmitter::EmitCublasLtMatmulF8,
+// xla/service/gpu/thunk_emitter.cc:776-862):
+//   operands  a, b, [c iff beta != 0], a_scale, b_scale, [bias iff the epilogue adds one],
+//             [d_scale iff D is F8E4M3FN / F8E5M2]
+//   results   D, [amax f32[] iff damax_output], [workspace s8[n]]
+//   attrs     GemmBackendConfig fields (xla/service/gpu/backend_configs.proto:88-135) as a flat
+//             dictionary: alpha_real, beta (f64 or f32), epilogue (i32/i64, enum number),
+//             lhs_contracting_dim, rhs_contracting_dim (i64/i32), damax_output (bool),
+//             selected_config (i64, optional; 0 = automatic kernel choice).
+// XLA_FFI_Buffer carries no layout (xla/ffi/api/c_api.h:273-281): every buffer is row-major and
+// transposition is expressed by the contracting dimensions alone.
+//
+// Stages (xla/ffi/api/c_api.h:413-455): `instantiate` checks types, shapes and attributes with
+// no device access; `initialize` does the per-device set-up; `execute` only enqueues work on the
+// stream XLA provides -- no allocation and no synchronisation, so the handler is declared
+// command-buffer compatible (xla/ffi/api/api.h:251-268).
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <optional>
+#include <string>
+
+#define B200SD_NO_FFI_DECLS 1
+#include "../../include/b200_scaled_dot.h"
+#include "xla/ffi/api/ffi.h"
+
+namespace ffi = xla::ffi;
+
+namespace {
+
+ffi::Error MakeError(int code, const std::string& msg) {
+  return ffi::Error(static_cast<ffi::ErrorCode>(code), msg);
+}
+
+// Integer attributes arrive as i64 or i32 depending on how the backend_config was spelled.
+std::optional<int64_t> GetInt(const ffi::Dictionary& attrs, std::string_view name) {
+  if (attrs.contains<int64_t>(name)) return *attrs.get<int64_t>(name);
+  if (attrs.contains<int32_t>(name)) return static_cast<int64_t>(*attrs.get<int32_t>(name));
+  return std::nullopt;
+}
+std::optional<double> GetFloat(const ffi::Dictionary& attrs, std::string_view name) {
+  if (attrs.contains<double>(name)) return *attrs.get<double>(name);
+  if (attrs.contains<float>(name)) return static_cast<double>(*attrs.get<float>(name));
+  return std::nullopt;
+}
+bool GetBool(const ffi::Dictionary& attrs, std::string_view name, bool dflt) {
+  if (attrs.contains<bool>(name)) return *attrs.get<bool>(name);
+  return dflt;
+}
+
+bool EpilogueAddsVectorBias(int64_t e) {
+  return e == B200SD_EPILOGUE_BIAS || e == B200SD_EPILOGUE_BIAS_RELU || e == B200SD_EPILOGUE_BIAS_GELU ||
+         e == B200SD_EPILOGUE_BIAS_GELU_AUX;
+}
+bool IsF8(ffi::DataType t) { return t == ffi::DataType::F8E4M3FN || t == ffi::DataType::F8E5M2; }
+bool IsScalar(const ffi::AnyBuffer& b) { return b.element_count() == 1; }
+
+struct DecodedF8 {
+  B200SD_ScaledDotF8 args;
+};
+
+// Decodes and checks a scaled-dot call frame.  Works with null data pointers (instantiate stage).
+ffi::Error DecodeF8(ffi::RemainingArgs operands, ffi::RemainingRets results, const ffi::Dictionary& attrs,
+                    B200SD_ScaledDotF8* out) {
+  B200SD_ScaledDotF8 a{};
+  a.struct_size = sizeof(a);
+  a.alpha = static_cast<float>(GetFloat(attrs, "alpha_real").value_or(1.0));
+  a.beta = static_cast<float>(GetFloat(attrs, "beta").value_or(0.0));
+  if (GetFloat(attrs, "alpha_imag").value_or(0.0) != 0.0)
+    return MakeError(3, "alpha_imag must be 0 for an FP8 dot");
+  a.epilogue = static_cast<int32_t>(GetInt(attrs, "epilogue").value_or(B200SD_EPILOGUE_DEFAULT));
+  a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(1));
+  a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(0));
+  a.kernel = static_cast<int32_t>(GetInt(attrs, "selected_config").value_or(B200SD_KERNEL_AUTO));
+  const bool damax = GetBool(attrs, "damax_output", false);
+  const bool has_c = a.beta != 0.0f;
+  const bool has_bias = EpilogueAddsVectorBias(a.epilogue);
+
+  if (results.size() < 1) return MakeError(3, "expected at least one result (D)");
+  auto d = results.get<ffi::AnyBuffer>(0);
+  if (!d.has_value()) return d.error();
+  const bool d_is_f8 = IsF8((*d)->element_type());
+  const size_t want_operands = 4 + (has_c ? 1 : 0) + (has_bias ? 1 : 0) + (d_is_f8 ? 1 : 0);
+  if (operands.size() != want_operands)
+    return MakeError(3, "expected " + std::to_string(want_operands) + " operands (a, b, [c], a_scale, b_scale, [bias], [d_scale]) for this "
+                        "backend_config, got " + std::to_string(operands.size()));
+  const size_t want_results_min = 1 + (damax ? 1 : 0);
+  if (results.size() < want_results_min || results.size() > want_results_min + 1)
+    return MakeError(3, "expected results (D, [amax], [workspace]), got " + std::to_string(results.size()));
+
+  size_t idx = 0;
+  auto lhs = operands.get<ffi::AnyBuffer>(idx++);
+  auto rhs = operands.get<ffi::AnyBuffer>(idx++);
+  if (!lhs.has_value()) return lhs.error();
+  if (!rhs.has_value()) return rhs.error();
+  if (lhs->dimensions().size() != 2 || rhs->dimensions().size() != 2 || (*d)->dimensions().size() != 2)
+    return MakeError(12, "only rank-2 operands are implemented (batched dots are not)");
+  if (a.lhs_contracting_dim != 0 && a.lhs_contracting_dim != 1) return MakeError(3, "lhs_contracting_dim must be 0 or 1");
+  if (a.rhs_contracting_dim != 0 && a.rhs_contracting_dim != 1) return MakeError(3, "rhs_contracting_dim must be 0 or 1");
+  a.k = lhs->dimensions()[a.lhs_contracting_dim];
+  a.m = lhs->dimensions()[1 - a.lhs_contracting_dim];
+  a.n = rhs->dimensions()[1 - a.rhs_contracting_dim];
+  if (rhs->dimensions()[a.rhs_contracting_dim] != a.k) return MakeError(3, "contracting dimensions of a and b differ");
+  if ((*d)->dimensions()[0] != a.m || (*d)->dimensions()[1] != a.n) return MakeError(3, "result shape is not [m, n]");
+  a.a = lhs->untyped_data();
+  a.b = rhs->untyped_data();
+  a.a_dtype = static_cast<int32_t>(lhs->element_type());
+  a.b_dtype = static_cast<int32_t>(rhs->element_type());
+  a.d = (*d)->untyped_data();
+  a.d_dtype = static_cast<int32_t>((*d)->element_type());
+
+  if (has_c) {
+    auto c = operands.get<ffi::AnyBuffer>(idx++);
+    if (!c.has_value()) return c.error();
+    if (c->dimensions().size() != 2 || c->dimensions()[0] != a.m || c->dimensions()[1] != a.n)
+      return MakeError(3, "matrix bias c must have shape [m, n]");
+    a.c = c->untyped_data();
+    a.c_dtype = static_cast<int32_t>(c->element_type());
+  }
+  auto a_scale = operands.get<ffi::AnyBuffer>(idx++);
+  auto b_scale = operands.get<ffi::AnyBuffer>(idx++);
+  if (!a_scale.has_value()) return a_scale.error();
+  if (!b_scale.has_value()) return b_scale.error();
+  if (a_scale->element_type() != ffi::DataType::F32 || b_scale->element_type() != ffi::DataType::F32 ||
+      !IsScalar(*a_scale) || !IsScalar(*b_scale))
+    return MakeError(3, "a_scale and b_scale must be f32 scalars");
+  a.a_scale = static_cast<const float*>(a_scale->untyped_data());
+  a.b_scale = static_cast<const float*>(b_scale->untyped_data());
+  if (has_bias) {
+    auto bias = operands.get<ffi::AnyBuffer>(idx++);
+    if (!bias.has_value()) return bias.error();
+    if (bias->element_count() != static_cast<size_t>(a.n)) return MakeError(3, "vector bias must have n elements");
+    a.bias = bias->untyped_data();
+    a.bias_dtype = static_cast<int32_t>(bias->element_type());
+  }
+  if (d_is_f8) {
+    auto d_scale = operands.get<ffi::AnyBuffer>(idx++);
+    if (!d_scale.has_value()) return d_scale.error();
+    if (d_scale->element_type() != ffi::DataType::F32 || !IsScalar(*d_scale))
+      return MakeError(3, "d_scale must be an f32 scalar");
+    a.d_scale = static_cast<const float*>(d_scale->untyped_data());
+  }
+  size_t ridx = 1;
+  if (damax) {
+    auto amax = results.get<ffi::AnyBuffer>(ridx++);
+    if (!amax.has_value()) return amax.error();
+    if ((*amax)->element_type() != ffi::DataType::F32 || !IsScalar(**amax))
+      return MakeError(3, "amax result must be an f32 scalar");
+    a.amax = static_cast<float*>((*amax)->untyped_data());
+  }
+  if (ridx < results.size()) {
+    auto ws = results.get<ffi::AnyBuffer>(ridx++);
+    if (!ws.has_value()) return ws.error();
+    a.workspace = (*ws)->untyped_data();
+    a.workspace_bytes = (*ws)->size_bytes();
+  }
+  *out = a;
+  return ffi::Error::Success();
+}
+
+ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, const ffi::Dictionary& attrs,
+                    B200SD_DotS8* out) {
+  B200SD_DotS8 a{};
+  a.struct_size = sizeof(a);
+  a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(1));
+  a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(0));
+  const bool emit_s32 = GetBool(attrs, "emit_s32", false);
+  if (GetFloat(attrs, "alpha_real").value_or(1.0) != 1.0 || GetFloat(attrs, "beta").value_or(0.0) != 0.0)
+    return MakeError(12, "alpha and beta are not fused into integer dots (the reference does not either)");
+  if (operands.size() != 2 && operands.size() != 4)
+    return MakeError(3, "expected operands (a, b) or (a, b, a_row_scale, b_col_scale), got " + std::to_string(operands.size()));
+  const size_t want_results = 1 + (emit_s32 ? 1 : 0);
+  if (results.size() < want_results || results.size() > want_results + 1)
+    return MakeError(3, "expected results (D, [acc s32 iff emit_s32], [workspace]), got " + std::to_string(results.size()));
+  auto lhs = operands.get<ffi::AnyBuffer>(0);
+  auto rhs = operands.get<ffi::AnyBuffer>(1);
+  auto d = results.get<ffi::AnyBuffer>(0);
+  if (!lhs.has_value()) return lhs.error();
+  if (!rhs.has_value()) return rhs.error();
+  if (!d.has_value()) return d.error();
+  if (lhs->element_type() != ffi::DataType::S8 || rhs->element_type() != ffi::DataType::S8)
+    return MakeError(3, "operands must be S8");
+  if (lhs->dimensions().size() != 2 || rhs->dimensions().size() != 2 || (*d)->dimensions().size() != 2)
+    return MakeError(12, "only rank-2 operands are implemented");
+  if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return MakeError(3, "contracting dimensions must be 0 or 1");
+  a.k = lhs->dimensions()[a.lhs_contracting_dim];
+  a.m = lhs->dimensions()[1 - a.lhs_contracting_dim];
+  a.n = rhs->dimensions()[1 - a.rhs_contracting_dim];
+  if (rhs->dimensions()[a.rhs_contracting_dim] != a.k) return MakeError(3, "contracting dimensions of a and b differ");
+  if ((*d)->dimensions()[0] != a.m || (*d)->dimensions()[1] != a.n) return MakeError(3, "result shape is not [m, n]");
+  a.a = lhs->untyped_data();
+  a.b = rhs->untyped_data();
+  a.d = (*d)->untyped_data();
+  a.d_dtype = static_cast<int32_t>((*d)->element_type());
+  if (operands.size() == 4) {
+    auto rs = operands.get<ffi::AnyBuffer>(2);
+    auto cs = operands.get<ffi::AnyBuffer>(3);
+    if (!rs.has_value()) return rs.error();
+    if (!cs.has_value()) return cs.error();
+    if (rs->element_type() != ffi::DataType::F32 || cs->element_type() != ffi::DataType::F32 ||
+        rs->element_count() != static_cast<size_t>(a.m) || cs->element_count() != static_cast<size_t>(a.n))
+      return MakeError(3, "a_row_scale must be f32[m] and b_col_scale f32[n]");
+    a.a_row_scale = static_cast<const float*>(rs->untyped_data());
+    a.b_col_scale = static_cast<const float*>(cs->untyped_data());
+  }
+  if (emit_s32) {
+    auto acc = results.get<ffi::AnyBuffer>(1);
+    if (!acc.has_value()) return acc.error();
+    if ((*acc)->element_type() != ffi::DataType::S32 || (*acc)->dimensions().size() != 2 ||
+        (*acc)->dimensions()[0] != a.m || (*acc)->dimensions()[1] != a.n)
+      return MakeError(3, "the emit_s32 result must be s32[m, n]");
+    a.acc_out = static_cast<int32_t*>((*acc)->untyped_data());
+  }
+  *out = a;
+  return ffi::Error::Success();
+}
+
+ffi::Error FromCode(int code, const char* msg) {
+  return code == 0 ? ffi::Error::Success() : MakeError(code, msg);
+}
+
+// ---- b200$scaled_dot$f8 --------------------------------------------------------------------
+ffi::Error ScaledDotF8Instantiate(ffi::RemainingArgs operands, ffi::RemainingRets results, ffi::Dictionary attrs) {
+  B200SD_ScaledDotF8 a;
+  ffi::Error e = DecodeF8(operands, results, attrs, &a);
+  if (e.failure()) return e;
+  char msg[512];
+  return FromCode(b200sd_check_scaled_dot_f8(&a, msg, sizeof(msg)), msg);
+}
+ffi::Error InitializeDevice() {
+  char msg[512];
+  return FromCode(b200sd_init_device(msg, sizeof(msg)), msg);
+}
+ffi::Error ScaledDotF8Execute(cudaStream_t stream, ffi::RemainingArgs operands, ffi::RemainingRets results,
+                              ffi::Dictionary attrs) {
+  B200SD_ScaledDotF8 a;
+  ffi::Error e = DecodeF8(operands, results, attrs, &a);
+  if (e.failure()) return e;
+  char msg[512];
+  return FromCode(b200sd_scaled_dot_f8(&a, stream, msg, sizeof(msg)), msg);
+}
+
+// ---- b200$dot$s8 ---------------------------------------------------------------------------
+ffi::Error DotS8Instantiate(ffi::RemainingArgs operands, ffi::RemainingRets results, ffi::Dictionary attrs) {
+  B200SD_DotS8 a;
+  ffi::Error e = DecodeS8(operands, results, attrs, &a);
+  if (e.failure()) return e;
+  char msg[512];
+  return FromCode(b200sd_check_dot_s8(&a, msg, sizeof(msg)), msg);
+}
+ffi::Error DotS8Execute(cudaStream_t stream, ffi::RemainingArgs operands, ffi::RemainingRets results,
+                        ffi::Dictionary attrs) {
+  B200SD_DotS8 a;
+  ffi::Error e = DecodeS8(operands, results, attrs, &a);
+  if (e.failure()) return e;
+  char msg[512];
+  return FromCode(b200sd_dot_s8(&a, stream, msg, sizeof(msg)), msg);
+}
+
+}  // namespace
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_scaled_dot_f8_instantiate, ScaledDotF8Instantiate,
+                              ffi::Ffi::BindInstantiate().RemainingArgs().RemainingRets().Attrs());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_scaled_dot_f8_initialize, InitializeDevice, ffi::Ffi::BindInitialize());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_scaled_dot_f8, ScaledDotF8Execute,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .RemainingArgs()
+                                  .RemainingRets()
+                                  .Attrs(),
+                              {ffi::Traits::kCmdBufferCompatible});
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_dot_s8_instantiate, DotS8Instantiate,
+                              ffi::Ffi::BindInstantiate().RemainingArgs().RemainingRets().Attrs());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_dot_s8_initialize, InitializeDevice, ffi::Ffi::BindInitialize());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_dot_s8, DotS8Execute,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .RemainingArgs()
+                                  .RemainingRets()
+                                  .Attrs(),
+                              {ffi::Traits::kCmdBufferCompatible});
+
+extern "C" int b200sd_ffi_register(const void* xla_ffi_api, char* err, size_t err_len) {
+  const XLA_FFI_Api* api = static_cast<const XLA_FFI_Api*>(xla_ffi_api);
+  if (api == nullptr) {
+    if (err && err_len) snprintf(err, err_len, "XLA_FFI_Api pointer is null");
+    return 3;
+  }
+  struct Target {
+    const char* name;
+    XLA_FFI_Handler_Bundle bundle;
+  } targets[] = {
+      {"b200$scaled_dot$f8",
+       {b200sd_ffi_scaled_dot_f8_instantiate, nullptr, b200sd_ffi_scaled_dot_f8_initialize, b200sd_ffi_scaled_dot_f8}},
+      {"b200$dot$s8", {b200sd_ffi_dot_s8_instantiate, nullptr, b200sd_ffi_dot_s8_initialize, b200sd_ffi_dot_s8}},
+  };
+  for (const Target& t : targets) {
+    XLA_FFI_Error* e = ffi::Ffi::RegisterStaticHandler(api, t.name, "CUDA", t.bundle,
+                                                       XLA_FFI_HANDLER_TRAITS_COMMAND_BUFFER_COMPATIBLE);
+    if (e != nullptr) {
+      XLA_FFI_Error_GetDetails_Args details{};
+      details.struct_size = XLA_FFI_Error_GetDetails_Args_STRUCT_SIZE;
+      details.error = e;
+      api->XLA_FFI_Error_GetDetails(&details);
+      if (err && err_len) snprintf(err, err_len, "registering %s: %s", t.name, details.message ? details.message : "?");
+      const int code = static_cast<int>(details.errc);
+      XLA_FFI_Error_Destroy_Args destroy{};
+      destroy.struct_size = XLA_FFI_Error_Destroy_Args_STRUCT_SIZE;
+      destroy.error = e;
+      api->XLA_FFI_Error_Destroy(&destroy);
+      return code ? code : 13;
+    }
+  }
+  return 0;
+}

@@ -1,0 +1,111 @@
+// Internal host-side interface between the C-ABI layer and the CUDA kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace b200sd {
+
+// xla::PrimitiveType numbers (mirrored by XLA_FFI_DataType, xla/ffi/api/c_api.h:233-266).
+enum PrimitiveType : int32_t {
+  kInvalidType = 0,
+  kS8 = 2,
+  kS32 = 4,
+  kF16 = 10,
+  kF32 = 11,
+  kBF16 = 16,
+  kF8E5M2 = 19,
+  kF8E4M3FN = 20,
+};
+
+// Activation applied after the optional bias.
+enum Activation : int32_t { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+
+// Status codes use the numbering of XLA_FFI_Error_Code (xla/ffi/api/c_api.h:168-186), which is
+// absl::StatusCode's.
+enum Code : int32_t {
+  kOk = 0,
+  kInvalidArgument = 3,
+  kDeadlineExceeded = 4,
+  kResourceExhausted = 8,
+  kFailedPrecondition = 9,
+  kUnimplemented = 12,
+  kInternal = 13,
+};
+
+struct Status {
+  int32_t code = kOk;
+  std::string message;
+  bool ok() const { return code == kOk; }
+  static Status Ok() { return {}; }
+  static Status Error(int32_t c, std::string m) { return Status{c, std::move(m)}; }
+};
+
+// A fully validated GEMM: D[m,n] = epilogue(sum_k A(m,k) * B(k,n)).  All matrices are dense
+// row-major in memory; `a_mn_major` says A is stored [k,m] (contracting dimension 0) and
+// `b_mn_major` that B is stored [k,n] (contracting dimension 0).
+struct GemmProblem {
+  int64_t m = 0, n = 0, k = 0;
+  bool int8 = false;                 // s8 x s8 -> s32 accumulate, else FP8 -> f32 accumulate
+  int32_t a_dtype = kF8E4M3FN, b_dtype = kF8E4M3FN;
+  bool a_mn_major = false, b_mn_major = true;
+  const void* a = nullptr;
+  const void* b = nullptr;
+
+  // FP8 epilogue: x = alpha * a_scale * b_scale * acc + beta * C + bias; act; amax; * d_scale; cast.
+  const float* a_scale = nullptr;    // device scalars, nullptr = 1.0
+  const float* b_scale = nullptr;
+  const float* d_scale = nullptr;
+  float alpha = 1.0f, beta = 0.0f;
+  const void* c = nullptr;
+  int32_t c_dtype = kInvalidType;
+  const void* bias = nullptr;        // [n]
+  int32_t bias_dtype = kInvalidType;
+  int32_t activation = kActNone;
+  float* amax = nullptr;             // device scalar, overwritten
+
+  // int8 epilogue: y = float(acc) * a_row_scale[m] * b_col_scale[n] (either may be nullptr).
+  const float* a_row_scale = nullptr;
+  const float* b_col_scale = nullptr;
+  int32_t* d_s32 = nullptr;          // optional raw accumulator output
+
+  void* d = nullptr;
+  int32_t d_dtype = kBF16;
+
+  void* workspace = nullptr;         // caller-owned scratch for the split-K kernel
+  size_t workspace_bytes = 0;
+};
+
+// Kernel selection (stands in for cuBLASLt's algorithm index).
+enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2 };
+
+struct LaunchStats {
+  int32_t kernel = 0;     // KernelKind actually used
+  int32_t grid = 0;
+  int32_t launches = 0;   // kernels launched (memset nodes not counted)
+};
+
+// One-time per-device set-up (function attributes, SM count).  Not a stream operation; must not
+// be called for the first time while the stream is being captured.
+Status InitDevice(int device);
+
+Status LaunchDense(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats);
+Status LaunchSkinny(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats);
+size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k);
+
+// Reads (and clears) the device status word the kernels OR their error bits into.  Synchronises
+// the device.
+Status ReadDeviceStatus(uint32_t* bits);
+
+// Runs a tiny kernel whose only wait is on a barrier nobody arrives at, with the given limit, and
+// reports through the status word.  Exercises the bounded-wait path without any fault.
+Status LaunchWaitProbe(uint64_t limit_ns, cudaStream_t stream);
+
+int DeviceSmCount();
+
+// Device address of the current device's status word (valid after InitDevice).
+uint32_t* StatusWordPtr();
+
+}  // namespace b200sd

@@ -1,0 +1,395 @@
+// Decode-shaped FP8 scaled dot for sm_100a: D[m,n] = (a_scale*b_scale) * A[m,k] . W[k,n] with
+// m <= 128 rows of activations and a weight matrix that is read from HBM exactly once.  The same
+// `__cublas$lt$matmul$f8` call (xla/stream_executor/cuda/cuda_blas_lt.cc:559-564) in the regime
+// where it is bound by memory bandwidth.
+//
+// The roles of the operands are swapped so that W fills the 128-row side of the tensor-core
+// instruction: each tile computes D^T[128 n, m] = W^T . A^T with W taken MN-major straight from
+// its row-major [k,n] storage and A as the (narrow) N operand.  Work is split stream-K style:
+// the (n-tile, k-block) units are dealt out evenly to one persistent CTA per SM, so every SM
+// streams the same number of W bytes.  A CTA whose range ends inside a tile computes that piece
+// FIRST, writes the f32 partial to the caller's workspace and raises a flag; the CTA that owns
+// the tile's last k-block adds the partials of the (lower-numbered) CTAs before it and writes D.
+// Waiting therefore only ever targets CTAs that were scheduled earlier and finished that piece
+// long ago; the wait is bounded all the same.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <string>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b200sd {
+namespace {
+
+constexpr int kTileN = 128;        // weight columns per tile (= TMEM lanes)
+constexpr int kBK = 128;           // k per stage
+constexpr int kUmmaK = 32;
+constexpr int kStages = 6;
+constexpr int kWStageBytes = kBK * kTileN;   // 16 KiB
+constexpr int kAStageBytes = 128 * kBK;      // up to 128 activation rows, 16 KiB
+constexpr int kStageBytes = kWStageBytes + kAStageBytes;
+constexpr int kThreads = 192;
+constexpr int kAccBufs = 2;
+constexpr int kTmemCols = 256;     // two accumulators of up to 128 columns
+constexpr int kMaxCtas = 256;
+constexpr size_t kFlagBytes = size_t(kMaxCtas) * 4 * sizeof(uint32_t);   // one flag per CTA per epilogue warp
+
+struct __align__(16) SkinnyAux {
+  uint64_t full_bar[kStages];
+  uint64_t empty_bar[kStages];
+  uint64_t acc_full_bar[kAccBufs];
+  uint64_t acc_empty_bar[kAccBufs];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kSkinnySmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(SkinnyAux);
+
+struct SkinnyArgs {
+  int32_t m;                 // activation rows (multiple of 16, <= 128)
+  int64_t n, k;
+  int32_t num_n_tiles, num_k_blocks;
+  int64_t total_units;       // num_n_tiles * num_k_blocks
+  uint32_t idesc;
+  const float* a_scale;
+  const float* b_scale;
+  float alpha;
+  void* d;
+  int32_t d_dtype;
+  uint32_t* flags;           // [grid][4], zeroed before the launch
+  float* partials;           // [grid][m][128]
+  uint32_t* status;
+};
+
+__device__ __forceinline__ int64_t unit_begin(int64_t cta, int64_t total, int64_t grid) { return cta * total / grid; }
+
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void store_out(const SkinnyArgs& p, int64_t idx, float x) {
+  if (p.d_dtype == kBF16) {
+    static_cast<__nv_bfloat16*>(p.d)[idx] = __float2bfloat16_rn(x);
+  } else if (p.d_dtype == kF16) {
+    static_cast<__half*>(p.d)[idx] = __float2half_rn(x);
+  } else {
+    static_cast<float*>(p.d)[idx] = x;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                   const SkinnyArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_w = smem;
+  uint8_t* smem_a = smem + kStages * kWStageBytes;
+  SkinnyAux* aux = reinterpret_cast<SkinnyAux*>(smem + kStages * kStageBytes);
+  volatile int* abort_flag = &aux->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t cta = blockIdx.x, grid = gridDim.x;
+  const int64_t u_begin = unit_begin(cta, p.total_units, grid);
+  const int64_t u_end = unit_begin(cta + 1, p.total_units, grid);
+  const uint32_t stage_tx_bytes = kWStageBytes + uint32_t(p.m) * kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&aux->full_bar[s], 1);
+      mbar_init(&aux->empty_bar[s], 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(&aux->acc_full_bar[b], 1);
+      mbar_init(&aux->acc_empty_bar[b], 128);
+    }
+    aux->abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_a);
+  }
+  if (warp == 1) {
+    tmem_alloc(&aux->tmem_base, kTmemCols);
+    tmem_relinquish_alloc();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = aux->tmem_base;
+
+  // The CTA walks its unit range [u_begin, u_end) backwards, one tile-segment at a time:
+  //   segment = units of one tile, [max(u_begin, tile*KB), min(u_end, (tile+1)*KB)).
+  // All three roles derive the same segment sequence from these two numbers.
+  const int64_t kb_per_tile = p.num_k_blocks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t seg_end = u_end;
+      while (seg_end > u_begin && ok) {
+        const int64_t tile = (seg_end - 1) / kb_per_tile;
+        const int64_t seg_begin = max(u_begin, tile * kb_per_tile);
+        for (int64_t u = seg_begin; u < seg_end; ++u) {
+          const int32_t kb = int32_t(u - tile * kb_per_tile);
+          ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          if (!ok) break;
+          uint64_t* full = &aux->full_bar[stage];
+          mbar_arrive_expect_tx(full, stage_tx_bytes);
+          tma_load_2d(smem_w + stage * kWStageBytes, &tmap_w, full, int32_t(tile) * kTileN, kb * kBK);
+          tma_load_2d(smem_a + stage * kAStageBytes, &tmap_a, full, kb * kBK, 0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        seg_end = seg_begin;
+      }
+      if (!ok) {
+        for (int s = 0; s < kStages; ++s) {
+          for (int i = 0; i < 100000 && !mbar_try_wait(&aux->full_bar[s], 0) && !mbar_try_wait(&aux->full_bar[s], 1); ++i) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint64_t w_desc0 = make_smem_desc_sw128(smem_u32(smem_w), 16384, 1024);   // MN-major
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), 16, 1024);      // K-major
+      const uint32_t w_kstep = (kUmmaK * 128) >> 4;
+      const uint32_t a_kstep = kUmmaK >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      int64_t seg_end = u_end;
+      while (seg_end > u_begin && ok) {
+        const int64_t tile = (seg_end - 1) / kb_per_tile;
+        const int64_t seg_begin = max(u_begin, tile * kb_per_tile);
+        ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * 128;
+        for (int64_t u = seg_begin; u < seg_end; ++u) {
+          ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t w_desc = w_desc0 + uint64_t((stage * kWStageBytes) >> 4);
+          const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
+#pragma unroll
+          for (int j = 0; j < kBK / kUmmaK; ++j) {
+            umma_f8(d_tmem, w_desc + uint64_t(j * w_kstep), a_desc + uint64_t(j * a_kstep), p.idesc,
+                    (u > seg_begin || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&aux->empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&aux->acc_full_bar[acc]);
+        if (++acc == kAccBufs) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        seg_end = seg_begin;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    float scale = p.alpha;
+    if (p.a_scale) scale *= __ldg(p.a_scale);
+    if (p.b_scale) scale *= __ldg(p.b_scale);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    int64_t seg_end = u_end;
+    while (seg_end > u_begin) {
+      const int64_t tile = (seg_end - 1) / kb_per_tile;
+      const int64_t tile_first = tile * kb_per_tile;
+      const int64_t seg_begin = max(u_begin, tile_first);
+      const bool owns_tail = seg_end == tile_first + kb_per_tile;   // holds the tile's last k-block
+      const bool owns_head = seg_begin == tile_first;
+
+      if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);
+      tc_fence_after_sync();
+
+      const int nl = q * 32 + lane;                          // lane of the accumulator = column of the tile
+      const int64_t col = tile * kTileN + nl;
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * 128);
+
+      if (!owns_tail) {
+        // Partial piece: park it in this CTA's workspace slot and publish.
+        float* slot = p.partials + (cta * p.m) * kTileN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < p.m; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) __stcg(slot + (c0 + i) * kTileN + nl, __uint_as_float(r[i]));
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(p.flags + cta * 4 + q, 1u);
+      } else {
+        // Finishing piece.  Wait for the CTAs that hold the earlier k-blocks of this tile.
+        int64_t first_contrib = cta;   // lowest CTA index that contributed to this tile
+        if (!owns_head) {
+          first_contrib = cta - 1;
+          while (unit_begin(first_contrib, p.total_units, grid) > tile_first) --first_contrib;
+          if (lane == 0) {
+            for (int64_t c = cta - 1; c >= first_contrib && ok; --c) {
+              const uint32_t* f = p.flags + c * 4 + q;
+              uint64_t t0 = 0;
+              uint32_t polls = 0;
+              while (ld_acquire_gpu(f) == 0u) {
+                if ((++polls & 1023u) == 0) {
+                  const uint64_t now = global_timer_ns();
+                  if (t0 == 0) t0 = now;
+                  if (*abort_flag || now - t0 > kWaitLimitNs) {
+                    *abort_flag = 1;
+                    atomicOr(p.status, kStatusFixupTimeout);
+                    ok = false;
+                    break;
+                  }
+                }
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          __threadfence();
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < p.m; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c0, r);
+          tmem_ld_wait();
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+          for (int64_t c = first_contrib; c < cta; ++c) {
+            const float* slot = p.partials + (c * p.m) * kTileN;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += __ldcg(slot + (c0 + i) * kTileN + nl);
+          }
+          if (col < p.n) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) store_out(p, int64_t(c0 + i) * p.n + col, v[i] * scale);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&aux->acc_empty_bar[acc]);
+      if (++acc == kAccBufs) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+      seg_end = seg_begin;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, uint32_t box_cols,
+                         uint32_t box_rows);
+
+Status InitSkinnyKernels() {
+  cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(kSkinnySmemBytes));
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(skinny): ") + cudaGetErrorString(e));
+  return Status::Ok();
+}
+
+size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k) {
+  if (m <= 0 || m > 128 || m % 16 != 0 || n <= 0 || k <= 0) return 0;
+  return kFlagBytes + size_t(kMaxCtas) * size_t(m) * kTileN * sizeof(float);
+}
+
+Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats) {
+  int device = 0;
+  cudaGetDevice(&device);
+  Status st = InitDevice(device);
+  if (!st.ok()) return st;
+  if (g.int8 || g.a_mn_major || !g.b_mn_major || g.m > 128 || g.m % 16 != 0)
+    return Status::Error(kInvalidArgument, "split-K kernel: unsupported operand arrangement");
+  const size_t need = SkinnyWorkspaceBytes(g.m, g.n, g.k);
+  if (g.workspace == nullptr || g.workspace_bytes < need)
+    return Status::Error(kInvalidArgument, "split-K kernel: workspace too small");
+  if ((reinterpret_cast<uintptr_t>(g.workspace) & 15) != 0)
+    return Status::Error(kInvalidArgument, "split-K kernel: workspace must be 16-byte aligned");
+
+  CUtensorMap tmap_w, tmap_a;
+  st = MakeByteMatrixMap(&tmap_w, g.b, g.k, g.n, kTileN, kBK);            // W [k, n]: box 128(n) x 128(k)
+  if (!st.ok()) return st;
+  st = MakeByteMatrixMap(&tmap_a, g.a, g.m, g.k, kBK, uint32_t(g.m));     // A [m, k]: box 128(k) x m
+  if (!st.ok()) return st;
+
+  SkinnyArgs p{};
+  p.m = int32_t(g.m); p.n = g.n; p.k = g.k;
+  p.num_n_tiles = int32_t((g.n + kTileN - 1) / kTileN);
+  p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
+  p.total_units = int64_t(p.num_n_tiles) * p.num_k_blocks;
+  // D^T = W^T . A^T: the 128-row operand is W (MN-major), the N operand is A (K-major), N = m.
+  p.idesc = make_idesc(1u, g.b_dtype == kF8E5M2 ? 1u : 0u, g.a_dtype == kF8E5M2 ? 1u : 0u, true, false, 128,
+                       uint32_t(g.m));
+  p.a_scale = g.a_scale; p.b_scale = g.b_scale; p.alpha = g.alpha;
+  p.d = g.d; p.d_dtype = g.d_dtype;
+  p.flags = static_cast<uint32_t*>(g.workspace);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + kFlagBytes);
+  p.status = StatusWordPtr();
+
+  int64_t grid = DeviceSmCount();
+  if (grid > kMaxCtas) grid = kMaxCtas;
+  if (grid > p.total_units) grid = p.total_units;
+  cudaError_t e = cudaMemsetAsync(p.flags, 0, kFlagBytes, stream);
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(flags): ") + cudaGetErrorString(e));
+  skinny_gemm_kernel<<<int(grid), kThreads, kSkinnySmemBytes, stream>>>(tmap_w, tmap_a, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("skinny_gemm_kernel launch: ") + cudaGetErrorString(e));
+  if (stats) {
+    stats->kernel = kKernelSkinny;
+    stats->grid = int32_t(grid);
+    stats->launches = 1;
+  }
+  return Status::Ok();
+}
+
+}  // namespace b200sd

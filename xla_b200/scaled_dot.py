@@ -1,0 +1,302 @@
+"""Host-side front end of the scaled-dot custom calls.
+
+Mirrors, for this one path, what XLA does around `__cublas$lt$matmul$f8`:
+`GemmBackendConfig` (xla/service/gpu/backend_configs.proto:88-135) carries the per-op
+configuration, `ScaledDotCall` plays the part of the thunk for one call site (operands and
+results in the order fixed by xla/service/gpu/thunk_emitter.cc:776-862, driven through the FFI
+stages like xla/backends/gpu/runtime/custom_call_thunk.cc:451-560), and
+`cublas_lt_matmul_f8` is the one-shot convenience wrapper tests and benchmarks use.
+
+Everything goes through the C ABI of libb200_scaled_dot.so by way of XLA FFI call frames; torch
+tensors only supply device memory and the stream.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+import enum
+from typing import NamedTuple, Optional, Sequence
+
+from . import _native
+
+# XLA PrimitiveType / XLA_FFI_DataType numbers (xla/ffi/api/c_api.h:233-266).
+PRED, S8, S32, S64, F16, F32, F64, BF16, F8E5M2, F8E4M3FN = 1, 2, 4, 5, 10, 11, 12, 16, 19, 20
+
+TARGET_F8 = "b200$scaled_dot$f8"
+TARGET_S8 = "b200$dot$s8"
+XLA_WORKSPACE_BYTES = 32 * 1024 * 1024  # GemmConfig::kHopperWorkspace, xla/service/gpu/matmul_utils.h:103
+
+_STAGE_INSTANTIATE, _STAGE_PREPARE, _STAGE_INITIALIZE, _STAGE_EXECUTE = 0, 1, 2, 3
+
+
+class Epilogue(enum.IntEnum):
+    """GemmBackendConfig.Epilogue (backend_configs.proto:106-117)."""
+
+    DEFAULT = 1
+    BIAS = 2
+    RELU = 3
+    BIAS_RELU = 4
+    GELU = 5
+    GELU_AUX = 6
+    BIAS_GELU = 7
+    BIAS_GELU_AUX = 8
+
+    @property
+    def adds_vector_bias(self) -> bool:
+        return self in (Epilogue.BIAS, Epilogue.BIAS_RELU, Epilogue.BIAS_GELU, Epilogue.BIAS_GELU_AUX)
+
+
+@dataclasses.dataclass
+class GemmBackendConfig:
+    """The fields of xla.gpu.GemmBackendConfig this path reads."""
+
+    alpha_real: float = 1.0
+    alpha_imag: float = 0.0
+    beta: float = 0.0
+    lhs_contracting_dimensions: Sequence[int] = (1,)
+    rhs_contracting_dimensions: Sequence[int] = (0,)
+    epilogue: Epilogue = Epilogue.DEFAULT
+    damax_output: bool = False
+    selected_algorithm: int = 0  # 0 = automatic; 1 = dense kernel; 2 = split-K kernel
+
+
+class XlaFfiError(RuntimeError):
+    """A non-OK XLA_FFI_Error returned by a handler (code = absl::StatusCode number)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+INVALID_ARGUMENT, NOT_FOUND, UNIMPLEMENTED, INTERNAL = 3, 5, 12, 13
+
+
+class Buffer(NamedTuple):
+    """What an XLA_FFI_Buffer carries: element type, dims, device address (0 = not bound yet)."""
+
+    dtype: int
+    dims: Sequence[int]
+    data: int = 0
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    table = {
+        torch.float8_e4m3fn: F8E4M3FN, torch.float8_e5m2: F8E5M2, torch.int8: S8, torch.int32: S32,
+        torch.float16: F16, torch.float32: F32, torch.bfloat16: BF16,
+    }
+    return table[t]
+
+
+def as_buffer(x) -> Buffer:
+    if isinstance(x, Buffer):
+        return x
+    if not x.is_contiguous():
+        raise ValueError("custom-call operands are dense row-major buffers; got a non-contiguous tensor")
+    return Buffer(_dtype_code(x.dtype), tuple(x.shape), x.data_ptr())
+
+
+def _err_buf():
+    return C.create_string_buffer(1024)
+
+
+class FfiCall:
+    """One custom-call site bound to a target registered with the (mock) XLA FFI runtime."""
+
+    def __init__(self, target: str, operands: Sequence, results: Sequence, attrs: dict):
+        _native.ensure_registered()
+        self._h = _native.mock.mockffi_call_new(target.encode())
+        self.target = target
+        self._keep = []
+        for op in operands:
+            b = as_buffer(op)
+            dims = (C.c_int64 * max(1, len(b.dims)))(*b.dims)
+            _native.mock.mockffi_call_add_arg(self._h, b.dtype, b.data, len(b.dims), dims)
+        for r in results:
+            b = as_buffer(r)
+            dims = (C.c_int64 * max(1, len(b.dims)))(*b.dims)
+            _native.mock.mockffi_call_add_ret(self._h, b.dtype, b.data, len(b.dims), dims)
+        for name, value in attrs.items():
+            self._add_attr(name, value)
+
+    def _add_attr(self, name: str, value) -> None:
+        n = name.encode()
+        m = _native.mock
+        if isinstance(value, tuple) and len(value) == 2 and value[0] in ("i32", "f32", "i64", "f64"):
+            kind, v = value
+            {"i32": m.mockffi_call_attr_i32, "f32": m.mockffi_call_attr_f32,
+             "i64": m.mockffi_call_attr_i64, "f64": m.mockffi_call_attr_f64}[kind](self._h, n, v)
+        elif isinstance(value, bool):
+            m.mockffi_call_attr_bool(self._h, n, int(value))
+        elif isinstance(value, int):
+            m.mockffi_call_attr_i64(self._h, n, value)
+        elif isinstance(value, float):
+            m.mockffi_call_attr_f64(self._h, n, value)
+        elif isinstance(value, str):
+            m.mockffi_call_attr_str(self._h, n, value.encode())
+        elif isinstance(value, (list, tuple)):
+            arr = (C.c_int64 * max(1, len(value)))(*value)
+            m.mockffi_call_attr_i64_array(self._h, n, arr, len(value))
+        else:
+            raise TypeError(f"unsupported attribute type for {name}: {type(value)}")
+
+    def _check(self, rc: int, err) -> None:
+        if rc != 0:
+            raise XlaFfiError(rc, err.value.decode(errors="replace"))
+
+    def invoke_stage(self, stage: int, stream: int = 0, device: int = 0) -> None:
+        err = _err_buf()
+        self._check(_native.mock.mockffi_call_invoke(self._h, stage, stream, device, err, len(err)), err)
+
+    def instantiate(self) -> None:
+        self.invoke_stage(_STAGE_INSTANTIATE)
+
+    def run(self, stream: int = 0, device: int = 0) -> None:
+        """instantiate (first time) -> prepare -> initialize -> execute."""
+        err = _err_buf()
+        self._check(_native.mock.mockffi_call_run(self._h, stream, device, err, len(err)), err)
+
+    def execute(self, stream: int = 0, device: int = 0) -> None:
+        err = _err_buf()
+        self._check(_native.mock.mockffi_call_execute(self._h, stream, device, err, len(err)), err)
+
+    def set_operand(self, index: int, tensor) -> None:
+        _native.mock.mockffi_call_set_arg_data(self._h, index, tensor.data_ptr())
+
+    def set_result(self, index: int, tensor) -> None:
+        _native.mock.mockffi_call_set_ret_data(self._h, index, tensor.data_ptr())
+
+    def close(self) -> None:
+        if self._h:
+            _native.mock.mockffi_call_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _config_attrs(cfg: GemmBackendConfig) -> dict:
+    if len(cfg.lhs_contracting_dimensions) != 1 or len(cfg.rhs_contracting_dimensions) != 1:
+        raise XlaFfiError(INVALID_ARGUMENT, "exactly one contracting dimension per operand")
+    return {
+        "alpha_real": float(cfg.alpha_real),
+        "alpha_imag": float(cfg.alpha_imag),
+        "beta": float(cfg.beta),
+        "epilogue": ("i32", int(cfg.epilogue)),
+        "lhs_contracting_dim": int(cfg.lhs_contracting_dimensions[0]),
+        "rhs_contracting_dim": int(cfg.rhs_contracting_dimensions[0]),
+        "damax_output": bool(cfg.damax_output),
+        "selected_config": int(cfg.selected_algorithm),
+    }
+
+
+class ScaledDotCall(FfiCall):
+    """A `b200$scaled_dot$f8` call site.
+
+    operands: a, b, [c], a_scale, b_scale, [bias], [d_scale]; results: D, [amax], [workspace] --
+    the arrangement of `__cublas$lt$matmul$f8`.
+    """
+
+    def __init__(self, operands: Sequence, results: Sequence, config: GemmBackendConfig):
+        super().__init__(TARGET_F8, operands, results, _config_attrs(config))
+        self.config = config
+
+
+class Int8DotCall(FfiCall):
+    """A `b200$dot$s8` call site: operands a, b, [a_row_scale, b_col_scale]; results D, [acc s32],
+    [workspace]."""
+
+    def __init__(self, operands: Sequence, results: Sequence, *, lhs_contracting_dim=1, rhs_contracting_dim=0,
+                 emit_s32=False):
+        super().__init__(TARGET_S8, operands, results, {
+            "lhs_contracting_dim": int(lhs_contracting_dim),
+            "rhs_contracting_dim": int(rhs_contracting_dim),
+            "emit_s32": bool(emit_s32),
+        })
+
+
+def _current_stream_and_device(t):
+    torch = _torch()
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    return torch.cuda.current_stream(dev).cuda_stream, dev
+
+
+def cublas_lt_matmul_f8(a, b, a_scale, b_scale, *, c=None, bias=None, d_scale=None, out_dtype=None,
+                        config: Optional[GemmBackendConfig] = None, workspace=None, out=None, amax_out=None):
+    """Runs one scaled dot on the current CUDA stream and returns (D, amax or None).
+
+    a, b: torch float8 tensors; a_scale, b_scale, d_scale: f32 scalar tensors on the device.
+    """
+    torch = _torch()
+    cfg = config or GemmBackendConfig()
+    lc, rc = cfg.lhs_contracting_dimensions[0], cfg.rhs_contracting_dimensions[0]
+    m, n = a.shape[1 - lc], b.shape[1 - rc]
+    out_dtype = out_dtype or torch.bfloat16
+    d = out if out is not None else torch.empty((m, n), dtype=out_dtype, device=a.device)
+    operands = [a, b]
+    if cfg.beta != 0.0:
+        operands.append(c)
+    operands += [a_scale, b_scale]
+    if cfg.epilogue.adds_vector_bias:
+        operands.append(bias)
+    if d.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        operands.append(d_scale if d_scale is not None else torch.ones((), dtype=torch.float32, device=a.device))
+    results = [d]
+    amax = None
+    if cfg.damax_output:
+        amax = amax_out if amax_out is not None else torch.empty((), dtype=torch.float32, device=a.device)
+        results.append(amax)
+    if workspace is None:
+        workspace = torch.empty(XLA_WORKSPACE_BYTES, dtype=torch.int8, device=a.device)
+    results.append(workspace)
+    call = ScaledDotCall(operands, results, cfg)
+    stream, dev = _current_stream_and_device(a)
+    call.run(stream, dev)
+    call.close()
+    return d, amax
+
+
+def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=None, emit_s32=False,
+                        lhs_contracting_dim=1, rhs_contracting_dim=0):
+    """s8 x s8 dot; returns (D, acc or None)."""
+    torch = _torch()
+    m, n = a.shape[1 - lhs_contracting_dim], b.shape[1 - rhs_contracting_dim]
+    out_dtype = out_dtype or (torch.int32 if a_row_scale is None else torch.bfloat16)
+    d = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    operands = [a, b] + ([a_row_scale, b_col_scale] if a_row_scale is not None else [])
+    results = [d]
+    acc = None
+    if emit_s32:
+        acc = torch.empty((m, n), dtype=torch.int32, device=a.device)
+        results.append(acc)
+    call = Int8DotCall(operands, results, lhs_contracting_dim=lhs_contracting_dim,
+                       rhs_contracting_dim=rhs_contracting_dim, emit_s32=emit_s32)
+    stream, dev = _current_stream_and_device(a)
+    call.run(stream, dev)
+    call.close()
+    return d, acc
+
+
+def device_status() -> int:
+    """Synchronises the device and returns (and clears) the kernels' error bit mask."""
+    bits = C.c_uint32(0)
+    err = _err_buf()
+    rc = _native.product.b200sd_device_status(C.byref(bits), err, len(err))
+    if rc != 0:
+        raise XlaFfiError(rc, err.value.decode(errors="replace"))
+    return bits.value
+
+
+def launch_count() -> int:
+    return int(_native.product.b200sd_launch_count())
