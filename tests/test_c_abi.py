@@ -1,0 +1,172 @@
+"""Host-only tests of the drop-in boundary: the shared library loads, exports every symbol the
+public header declares, registers with an XLA FFI runtime, and validates call frames at the
+`instantiate` stage (no device access) the way xla/ffi/api/ffi_test.cc exercises handlers --
+by building call frames by hand."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+import xla_b200
+from xla_b200 import _native
+from xla_b200.scaled_dot import (BF16, F16, F32, F8E4M3FN, F8E5M2, S8, S32, Buffer, Epilogue, FfiCall,
+                                 GemmBackendConfig, Int8DotCall, ScaledDotCall, XlaFfiError)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_every_declared_symbol_is_exported():
+    header = open(os.path.join(ROOT, "include", "b200_scaled_dot.h")).read()
+    names = set(re.findall(r"\b(b200sd_[a-z0-9_]+)\s*\(", header))
+    assert len(names) >= 15
+    for n in sorted(names):
+        assert hasattr(_native.product, n), f"{n} is declared in the header but not exported"
+
+
+def test_struct_layouts_match_the_header():
+    """The ctypes mirrors must have the C structs' sizes (checked through struct_size validation)."""
+    err = C.create_string_buffer(256)
+    a = _native.ScaledDotF8Args()
+    a.struct_size = C.sizeof(a) - 8
+    assert _native.product.b200sd_check_scaled_dot_f8(C.byref(a), err, len(err)) == 3
+    assert b"struct_size" in err.value
+    s = _native.DotS8Args()
+    s.struct_size = 8
+    assert _native.product.b200sd_check_dot_s8(C.byref(s), err, len(err)) == 3
+
+
+def test_registration_and_metadata():
+    _native.ensure_registered()
+    traits, minor = C.c_uint32(0), C.c_int(0)
+    for target in (b"b200$scaled_dot$f8", b"b200$dot$s8"):
+        assert _native.mock.mockffi_find_handler(target, b"CUDA", C.byref(traits), C.byref(minor)) == 1
+        assert traits.value & 1           # XLA_FFI_HANDLER_TRAITS_COMMAND_BUFFER_COMPATIBLE
+        assert 1 <= minor.value <= 4      # API versions the XLA runtime accepts (ffi_registry.cc:47-65)
+    assert _native.mock.mockffi_find_handler(b"b200$scaled_dot$f8", b"Host", None, None) == 0
+    # Registering twice is refused, as XLA's registry does.
+    err = C.create_string_buffer(256)
+    assert _native.product.b200sd_ffi_register(_native.mock.mockffi_api(), err, len(err)) == 6   # ALREADY_EXISTS
+
+
+def _f8_frame(m=256, k=512, n=256, *, a=F8E4M3FN, b=F8E4M3FN, d=BF16, extra_ops=(), extra_res=(Buffer(S8, (1 << 20,)),),
+              lc=1, rc=0):
+    a_dims = (m, k) if lc == 1 else (k, m)
+    b_dims = (k, n) if rc == 0 else (n, k)
+    ops = [Buffer(a, a_dims), Buffer(b, b_dims), Buffer(F32, ()), Buffer(F32, ())] + list(extra_ops)
+    return ops, [Buffer(d, (m, n))] + list(extra_res)
+
+
+@pytest.mark.parametrize("case", [
+    # every operand/result arrangement FileCheck'd in gemm_rewriter_fp8_test.cc (lines in comments)
+    dict(),                                                                               # :501  a,b,as,bs -> D,ws
+    dict(cfg=dict(beta=1.0), ops_insert_c=True),                                           # :1370 matrix bias
+    dict(cfg=dict(epilogue=Epilogue.BIAS), extra_ops=[Buffer(BF16, (256,))]),              # :1167 vector bias
+    dict(cfg=dict(epilogue=Epilogue.BIAS_RELU), extra_ops=[Buffer(F16, (256,))]),          # :2031
+    dict(cfg=dict(epilogue=Epilogue.BIAS_GELU), extra_ops=[Buffer(BF16, (256,))]),         # :2166
+    dict(d=F8E4M3FN, extra_ops=[Buffer(F32, ())]),                                         # :1709 d_scale
+    dict(d=F8E4M3FN, extra_ops=[Buffer(F32, ())], cfg=dict(damax_output=True),
+         extra_res=[Buffer(F32, ()), Buffer(S8, (1 << 20,))]),                             # :2613 amax
+    dict(d=F8E4M3FN, cfg=dict(epilogue=Epilogue.BIAS), extra_ops=[Buffer(BF16, (256,)), Buffer(F32, ())]),   # :1971
+    dict(d=F8E4M3FN, cfg=dict(epilogue=Epilogue.BIAS_GELU, damax_output=True),
+         extra_ops=[Buffer(BF16, (256,)), Buffer(F32, ())],
+         extra_res=[Buffer(F32, ()), Buffer(S8, (1 << 20,))]),                             # BASELINE config 1
+    dict(extra_res=[]),                                                                    # no workspace result
+    dict(b=F8E5M2, d=F8E5M2, extra_ops=[Buffer(F32, ())]),
+    dict(lc=0, rc=1),
+])
+def test_accepted_arrangements_instantiate(case):
+    ops, res = _f8_frame(a=case.get("a", F8E4M3FN), b=case.get("b", F8E4M3FN), d=case.get("d", BF16),
+                         extra_ops=case.get("extra_ops", ()),
+                         extra_res=case.get("extra_res", (Buffer(S8, (1 << 20,)),)),
+                         lc=case.get("lc", 1), rc=case.get("rc", 0))
+    if case.get("ops_insert_c"):
+        ops.insert(2, Buffer(BF16, (256, 256)))
+    cfg = GemmBackendConfig(lhs_contracting_dimensions=(case.get("lc", 1),),
+                            rhs_contracting_dimensions=(case.get("rc", 0),), **case.get("cfg", {}))
+    ScaledDotCall(ops, res, cfg).instantiate()
+
+
+@pytest.mark.parametrize("mutate,code,needle", [
+    (lambda o, r, c: o.__setitem__(0, Buffer(F8E5M2, (256, 512))) or o.__setitem__(1, Buffer(F8E5M2, (512, 256))), 12, "F8E5M2 x F8E5M2"),
+    (lambda o, r, c: o.__setitem__(0, Buffer(BF16, (256, 512))), 3, "F8E4M3FN or F8E5M2"),
+    (lambda o, r, c: o.__setitem__(1, Buffer(F8E4M3FN, (500, 256))), 3, "contracting dimensions"),
+    (lambda o, r, c: r.__setitem__(0, Buffer(BF16, (256, 128))), 3, "result shape"),
+    (lambda o, r, c: r.__setitem__(0, Buffer(S32, (256, 256))), 3, "output type"),
+    (lambda o, r, c: o.__setitem__(2, Buffer(F32, (2,))), 3, "f32 scalars"),
+    (lambda o, r, c: o.__setitem__(3, Buffer(BF16, ())), 3, "f32 scalars"),
+    (lambda o, r, c: o.pop(), 3, "operands"),
+    (lambda o, r, c: o.append(Buffer(F32, ())), 3, "operands"),
+    (lambda o, r, c: setattr(c, "epilogue", Epilogue.BIAS), 3, "operands"),
+    (lambda o, r, c: setattr(c, "epilogue", Epilogue.GELU_AUX), 12, "auxiliary"),
+    (lambda o, r, c: setattr(c, "damax_output", True), 3, "amax result"),
+    (lambda o, r, c: setattr(c, "lhs_contracting_dimensions", (2,)), 3, "lhs_contracting_dim"),
+    (lambda o, r, c: o.__setitem__(0, Buffer(F8E4M3FN, (2, 256, 512))), 12, "rank-2"),
+    (lambda o, r, c: (o.__setitem__(0, Buffer(F8E4M3FN, (250, 512))), r.__setitem__(0, Buffer(BF16, (250, 256)))), 3, "multiples of 16"),
+    (lambda o, r, c: r.__setitem__(0, Buffer(F8E5M2, (256, 256))) or o.append(Buffer(F32, ())), 12, "type table"),
+])
+def test_rejected_call_frames(mutate, code, needle):
+    """Bad dtypes / dims / attrs surface as XLA_FFI_Error with the right code at instantiate time;
+    nothing is launched and nothing faults."""
+    ops, res = _f8_frame()
+    cfg = GemmBackendConfig()
+    mutate(ops, res, cfg)
+    with pytest.raises(XlaFfiError) as e:
+        ScaledDotCall(ops, res, cfg).instantiate()
+    assert e.value.code == code, e.value
+    assert needle in e.value.message, e.value.message
+
+
+def test_attribute_spellings():
+    """Integer attributes may arrive as i32 or i64, floats as f32 or f64 (the MLIR dictionary a
+    backend_config is parsed into keeps the written width: xla/service/gpu/custom_call_test.cc:554-577)."""
+    ops, res = _f8_frame()
+    for attrs in (
+        {"epilogue": ("i32", 1), "lhs_contracting_dim": ("i32", 1), "rhs_contracting_dim": ("i64", 0), "beta": ("f32", 0.0)},
+        {"epilogue": 1, "alpha_real": 1.0},
+        {},
+    ):
+        FfiCall("b200$scaled_dot$f8", ops, res, attrs).instantiate()
+    with pytest.raises(XlaFfiError):
+        FfiCall("b200$scaled_dot$f8", ops, res, {"alpha_imag": 1.0}).instantiate()
+
+
+def test_int8_frames():
+    Int8DotCall([Buffer(S8, (64, 128)), Buffer(S8, (128, 32))], [Buffer(S32, (64, 32))]).instantiate()
+    Int8DotCall([Buffer(S8, (64, 128)), Buffer(S8, (128, 32)), Buffer(F32, (64,)), Buffer(F32, (32,))],
+                [Buffer(BF16, (64, 32)), Buffer(S32, (64, 32))], emit_s32=True).instantiate()
+    for ops, res, kw, code in [
+        ([Buffer(S8, (64, 128)), Buffer(F8E4M3FN, (128, 32))], [Buffer(S32, (64, 32))], {}, 3),
+        ([Buffer(S8, (64, 128)), Buffer(S8, (128, 32)), Buffer(F32, (64,)), Buffer(F32, (32,))], [Buffer(S32, (64, 32))], {}, 3),
+        ([Buffer(S8, (64, 128)), Buffer(S8, (128, 32)), Buffer(F32, (63,)), Buffer(F32, (32,))], [Buffer(BF16, (64, 32))], {}, 3),
+        ([Buffer(S8, (64, 128)), Buffer(S8, (128, 32))], [Buffer(S8, (64, 32))], {}, 3),
+        ([Buffer(S8, (64, 128)), Buffer(S8, (128, 32))], [Buffer(S32, (64, 32))], {"emit_s32": True}, 3),
+    ]:
+        with pytest.raises(XlaFfiError) as e:
+            Int8DotCall(ops, res, **kw).instantiate()
+        assert e.value.code == code
+
+
+def test_unknown_target_and_wrong_stage():
+    with pytest.raises(XlaFfiError) as e:
+        FfiCall("__cublas$lt$matmul$f8", [], [], {}).instantiate()
+    assert e.value.code == 5          # NOT_FOUND: nothing is registered under the cuBLASLt name
+
+
+def test_kernel_selection_table():
+    """The static stand-in for the autotuner: decode shapes -> split-K (2), the rest -> dense (1)."""
+    sel = _native.product.b200sd_select_kernel
+    assert sel(8192, 8192, 8192) == 1
+    assert sel(256, 256, 512) == 1
+    for m in (16, 64, 128):
+        assert sel(m, 28672, 8192) == 2
+        need = _native.product.b200sd_workspace_bytes(m, 28672, 8192)
+        assert 0 < need <= 32 * 1024 * 1024       # fits the workspace XLA attaches (matmul_utils.h:103)
+    assert sel(16, 256, 256) == 1
+    assert _native.product.b200sd_workspace_bytes(8192, 8192, 8192) == 0
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    monkeypatch.setattr(_native, "PRODUCT_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError):
+        _native._load(_native.PRODUCT_LIB)

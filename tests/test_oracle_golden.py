@@ -1,0 +1,184 @@
+"""Pins the CPU oracle against the reference's own known-answer vectors (tests/golden/*.json,
+generated from the reference tree by tests/golden/make_golden.py) and checks the oracle's two
+implementations (NumPy and plain C) against each other."""
+import ctypes as C
+import json
+import math
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from oracle import scaled_dot_oracle as o
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def _val(s):
+    return {"nan": math.nan, "inf": math.inf, "-inf": -math.inf}.get(s, None) if s in ("nan", "inf", "-inf") else float.fromhex(s)
+
+
+@pytest.fixture(scope="module")
+def golden():
+    with open(os.path.join(HERE, "golden", "fp8_convert_roundtrip.json")) as f:
+        return json.load(f)
+
+
+@pytest.fixture(scope="module")
+def c_oracle():
+    subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle")], stdout=subprocess.DEVNULL)
+    lib = C.CDLL(os.path.join(ROOT, "oracle", "_build", "liboracle.so"))
+    lib.oracle_fp8_decode.restype = C.c_float
+    lib.oracle_fp8_decode.argtypes = [C.c_uint8, C.c_int]
+    lib.oracle_fp8_encode.restype = C.c_uint8
+    lib.oracle_fp8_encode.argtypes = [C.c_float, C.c_int]
+    lib.oracle_f32_to_bf16.restype = C.c_uint16
+    lib.oracle_f32_to_bf16.argtypes = [C.c_float]
+    lib.oracle_scaled_dot_f8.restype = C.c_float
+    lib.oracle_scaled_dot_f8.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int64,
+                                         C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_float, C.c_float, C.c_void_p,
+                                         C.c_void_p, C.c_int, C.c_void_p]
+    lib.oracle_dot_s8.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p]
+    return lib
+
+
+@pytest.mark.parametrize("table", ["ConvertF16F8e5m2Roundtrip", "ConvertF32F8e5m2Roundtrip",
+                                   "ConvertF16F8e4m3fnRoundtrip", "ConvertF32F8e4m3fnRoundtrip"])
+def test_reference_roundtrip_tables(golden, c_oracle, table):
+    """xla/tests/convert_test.cc: value -> FP8 -> value must give the listed result exactly."""
+    t = golden["tables"][table]
+    kind = t["fp8"]
+    assert len(t["cases"]) >= 20
+    for src, want in t["cases"]:
+        x, w = _val(src), _val(want)
+        xin = np.float32(np.float16(x)) if t["via"] == "f16" else np.float32(x)
+        got = float(o.fp8_decode(o.fp8_encode(np.array([xin], np.float32), kind), kind)[0])
+        got_c = c_oracle.oracle_fp8_decode(c_oracle.oracle_fp8_encode(float(xin), 0 if kind == "e4m3fn" else 1),
+                                           0 if kind == "e4m3fn" else 1)
+        for g in (got, got_c):
+            if math.isnan(w):
+                assert math.isnan(g), (table, src, g)
+            else:
+                assert g == w, (table, src, g, w)        # ErrorSpec(0.): value equality (-0 == 0)
+
+
+@pytest.mark.parametrize("kind", ["e4m3fn", "e5m2"])
+def test_exhaustive_roundtrips(c_oracle, kind):
+    """ConvertF8e4m3fnRoundtripExhaustive{,2,3} / the e5m2 twins: all 256 code points survive
+    FP8 -> f32 -> FP8, and FP8 -> bf16/f16 -> FP8 (every FP8 value is exact in those types)."""
+    codes = np.arange(256, dtype=np.uint8)
+    vals = o.fp8_decode(codes, kind)
+    back = o.fp8_encode(vals, kind)
+    nan = np.isnan(vals)
+    assert np.array_equal(back[~nan], codes[~nan])
+    assert np.isnan(o.fp8_decode(back[nan], kind)).all()
+    ck = 0 if kind == "e4m3fn" else 1
+    for c in range(256):
+        v = c_oracle.oracle_fp8_decode(c, ck)
+        assert (math.isnan(v) and nan[c]) or v == vals[c]
+        if not nan[c]:
+            assert c_oracle.oracle_fp8_encode(v, ck) == c
+    via_bf16 = o.bf16_bits_to_f32(o.f32_to_bf16_bits(vals[~nan]))
+    assert np.array_equal(via_bf16, vals[~nan])
+    assert np.array_equal(vals[~nan].astype(np.float16).astype(np.float32), vals[~nan])
+
+
+@pytest.mark.parametrize("kind", ["e4m3fn", "e5m2"])
+def test_all_f16_inputs_numpy_vs_c(c_oracle, kind):
+    """ConvertF8e4m3fnF16RoundtripExhaustive4: every f16 bit pattern -> FP8; the two oracle
+    implementations must agree everywhere (a sample keeps the ctypes loop short)."""
+    x = np.arange(0, 65536, 7, dtype=np.uint16).view(np.float16).astype(np.float32)
+    enc = o.fp8_encode(x, kind)
+    ck = 0 if kind == "e4m3fn" else 1
+    for xi, e in zip(x.tolist(), enc.tolist()):
+        g = c_oracle.oracle_fp8_encode(xi, ck)
+        if math.isnan(xi):
+            assert math.isnan(c_oracle.oracle_fp8_decode(g, ck))
+        else:
+            assert g == e, (xi, g, e)
+
+
+def test_optional_cross_check_with_ml_dtypes():
+    ml = pytest.importorskip("ml_dtypes")
+    for kind, t in (("e4m3fn", ml.float8_e4m3fn), ("e5m2", ml.float8_e5m2)):
+        rng = np.random.default_rng(0)
+        x = np.concatenate([rng.standard_normal(50000).astype(np.float32) * 200,
+                            rng.integers(0, 2 ** 32, 200000, dtype=np.uint64).astype(np.uint32).view(np.float32)])
+        with np.errstate(all="ignore"):
+            ref = x.astype(t).view(np.uint8)
+        mine = o.fp8_encode(x, kind)
+        ref_nan = np.isnan(ref.view(t).astype(np.float32))
+        assert np.array_equal(ref_nan, np.isnan(o.fp8_decode(mine, kind)))
+        assert np.array_equal(ref[~ref_nan], mine[~ref_nan])
+
+
+def test_bf16_rounding_numpy_vs_c(c_oracle):
+    x = np.random.default_rng(1).integers(0, 2 ** 32, 20000, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    bits = o.f32_to_bf16_bits(x)
+    for xi, b in zip(x.tolist(), bits.tolist()):
+        if not math.isnan(xi):
+            assert c_oracle.oracle_f32_to_bf16(xi) == b
+    # ties to even
+    assert o.f32_to_bf16_bits(np.array([1.00390625], np.float32))[0] == 0x3F80     # 1 + 2^-8 -> 1.0
+    assert o.f32_to_bf16_bits(np.array([1.01171875], np.float32))[0] == 0x3F82     # 1 + 3*2^-8 -> 1 + 2^-6
+
+
+def test_s8_known_answer():
+    """cuda_blas_lt_test.cc:48-156 on the oracle: 32^3 all ones -> 32 everywhere."""
+    with open(os.path.join(HERE, "golden", "s8_known_answer.json")) as f:
+        ka = json.load(f)
+    a = np.full((ka["m"], ka["k"]), ka["a_fill"], np.int8)
+    b = np.full((ka["k"], ka["n"]), ka["b_fill"], np.int8)
+    assert (o.dot_s8(a, b) == ka["expected_every_element"]).all()
+
+
+@pytest.mark.parametrize("lc,rc", [(1, 0), (0, 0), (1, 1), (0, 1)])
+def test_numpy_dot_matches_strict_c_interpreter_order(c_oracle, lc, rc):
+    """BLAS order (used for big shapes) vs the strict sequential-k C restatement: 1e-5 relative."""
+    m, k, n = 48, 160, 64
+    a, b, sa, sb = o.make_f8_operands(70, m, k, n)
+    a_st = a if lc == 1 else np.ascontiguousarray(a.T)
+    b_st = b if rc == 0 else np.ascontiguousarray(b.T)
+    bias = o.bf16_bits_to_f32(o.make_bias_bf16(70, n))
+    out = np.zeros((m, n), np.float32)
+    amax_c = c_oracle.oracle_scaled_dot_f8(a_st.ctypes.data, b_st.ctypes.data, float(sa), float(sb), 0, 0, m, n, k,
+                                           lc, rc, 1.0, 0.0, None, bias.ctypes.data, 7, out.ctypes.data)
+    exp, amax = o.scaled_dot_f8(a_st, b_st, sa, sb, lhs_contracting=lc, rhs_contracting=rc, bias=bias, epilogue=7,
+                                out_dtype=o.F32, want_amax=True)
+    np.testing.assert_allclose(exp, out, rtol=1e-5, atol=1e-6)
+    assert abs(amax - amax_c) <= 1e-5 * abs(amax_c)
+    strict, _ = o.scaled_dot_f8(a_st, b_st, sa, sb, lhs_contracting=lc, rhs_contracting=rc, bias=bias, epilogue=7,
+                                out_dtype=o.F32, strict=True)
+    np.testing.assert_allclose(strict, out, rtol=1e-5, atol=1e-6)
+
+
+def test_s8_dot_numpy_vs_c(c_oracle):
+    a, b, _, _ = o.make_s8_operands(3, 40, 96, 56)
+    out = np.zeros((40, 56), np.int32)
+    c_oracle.oracle_dot_s8(a.ctypes.data, b.ctypes.data, 40, 56, 96, 1, 0, out.ctypes.data)
+    assert np.array_equal(out, o.dot_s8(a, b))
+    assert np.array_equal(out, a.astype(np.int64) @ b.astype(np.int64))
+
+
+def test_nan_rules():
+    """maximum and clamp propagate NaN (hlo_evaluator_typed_visitor.h:594-613, 843-865)."""
+    a, b, sa, sb = o.make_f8_operands(71, 16, 32, 16)
+    a = a.copy()
+    a[3, 4] = 0x7F
+    d, amax = o.scaled_dot_f8(a, b, sa, sb, d_scale=1.0, out_dtype=o.F8E4M3FN, want_amax=True)
+    assert np.isnan(amax)
+    assert ((d[3] & 0x7F) == 0x7F).all() and ((d[2] & 0x7F) != 0x7F).all()
+    assert o.fp8_encode_saturating(np.array([1e9, -1e9, np.inf, 500.0], np.float32)).tolist() == [0x7E, 0xFE, 0x7E, 0x7E]
+
+
+def test_near_comparison_rule():
+    """literal_comparison.cc:528-535: mismatch needs BOTH bounds exceeded; NaN == NaN; inf must match."""
+    exp = np.array([1.0, 100.0, 0.0, np.nan, np.inf, 1.0], np.float32)
+    act = np.array([1.005, 100.5, 0.005, np.nan, np.inf, 1.02], np.float32)
+    bad, _, _ = o.near_mismatches(exp, act, 1e-2, 1e-2)
+    assert bad == 1          # only 1.0 vs 1.02 exceeds both
+    assert o.near_mismatches(np.array([np.inf]), np.array([1e30]), 1e-2, 1e-2)[0] == 1
+    assert o.near_mismatches(np.array([1.0]), np.array([np.nan]), 1e-2, 1e-2)[0] == 1
+    assert o.fp8_within_n_values(np.array([0x38, 0x38, 0x81], np.uint8), np.array([0x39, 0x3A, 0x01], np.uint8), 1) == 2

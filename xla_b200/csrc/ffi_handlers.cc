@@ -198,6 +198,8 @@ ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   a.d = (*d)->untyped_data();
   a.d_dtype = static_cast<int32_t>((*d)->element_type());
   if (operands.size() == 4) {
+    if ((*d)->element_type() == ffi::DataType::S32)
+      return MakeError(3, "dequantisation scales need a floating-point output type");
     auto rs = operands.get<ffi::AnyBuffer>(2);
     auto cs = operands.get<ffi::AnyBuffer>(3);
     if (!rs.has_value()) return rs.error();
