@@ -50,7 +50,13 @@ enum {
 };
 
 /* Kernel choice; plays the role of GemmBackendConfig.selected_algorithm. */
-enum { B200SD_KERNEL_AUTO = 0, B200SD_KERNEL_DENSE = 1, B200SD_KERNEL_SKINNY = 2 };
+enum {
+  B200SD_KERNEL_AUTO = 0,
+  B200SD_KERNEL_DENSE = 1,        /* dense kernel, pair or single-CTA instantiation chosen by shape */
+  B200SD_KERNEL_SKINNY = 2,       /* split-K kernel for decode shapes */
+  B200SD_KERNEL_DENSE_SINGLE = 3, /* one CTA per 128 x 256 tile */
+  B200SD_KERNEL_DENSE_PAIR = 4    /* two-CTA clusters on 256 x 256 tiles (tcgen05 cta_group::2) */
+};
 
 /* Arguments of one FP8 scaled dot.
  *
@@ -108,6 +114,7 @@ typedef struct B200SD_DotS8 {
   int32_t d_dtype;               /* S32, F32 or BF16 */
   int32_t lhs_contracting_dim;
   int32_t rhs_contracting_dim;
+  int32_t kernel;                /* B200SD_KERNEL_AUTO, _DENSE, _DENSE_SINGLE or _DENSE_PAIR */
 } B200SD_DotS8;
 
 /* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the

@@ -55,6 +55,7 @@ class DotS8Args(C.Structure):
         ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
         ("d_dtype", C.c_int32),
         ("lhs_contracting_dim", C.c_int32), ("rhs_contracting_dim", C.c_int32),
+        ("kernel", C.c_int32),
     ]
 
 

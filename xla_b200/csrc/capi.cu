@@ -137,6 +137,7 @@ Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointe
   if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16 (pad as the rewriter does)");
   if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
   if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
+  if (a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_PAIR) return Status::Error(kInvalidArgument, "unknown kernel selection " + std::to_string(a.kernel));
   bool has_bias = false;
   int32_t act = kActNone;
   switch (a.epilogue) {
@@ -183,6 +184,7 @@ Status ValidateS8(const B200SD_DotS8& a, GemmProblem* g, bool check_pointers = t
   if (a.m <= 0 || a.n <= 0 || a.k <= 0) return Status::Error(kInvalidArgument, "m, n and k must be positive");
   if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16");
   if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
+  if (a.kernel == B200SD_KERNEL_SKINNY || a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_PAIR) return Status::Error(kInvalidArgument, "integer dots run on the dense kernel only");
   if (a.k > 133144) return Status::Error(kInvalidArgument, "k too large for exact s32 accumulation of s8 products");
   if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
   g->m = a.m; g->n = a.n; g->k = a.k;
@@ -234,7 +236,7 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
   }
   LaunchStats stats;
   st = kernel == B200SD_KERNEL_SKINNY ? LaunchSkinny(g, static_cast<cudaStream_t>(cuda_stream), &stats)
-                                      : LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats);
+                                      : LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats, kernel);
   if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
   return CopyStatus(st, err, err_len);
 }
@@ -245,7 +247,7 @@ int b200sd_dot_s8(const B200SD_DotS8* args, void* cuda_stream, char* err, size_t
   Status st = ValidateS8(*args, &g);
   if (!st.ok()) return CopyStatus(st, err, err_len);
   LaunchStats stats;
-  st = LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats);
+  st = LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats, args->kernel == B200SD_KERNEL_AUTO ? B200SD_KERNEL_DENSE : args->kernel);
   if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
   return CopyStatus(st, err, err_len);
 }

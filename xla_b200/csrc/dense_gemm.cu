@@ -2,16 +2,18 @@
 // (FP8 e4m3fn / e5m2 operands, f32 accumulate) and the s8 x s8 -> s32 dot, with the whole epilogue
 // fused.  Replaces the library call at xla/stream_executor/cuda/cuda_blas_lt.cc:559-564.
 //
-// Structure (one persistent CTA per SM, 192 threads):
-//   warp 0      TMA producer: streams 128x128-byte A tiles and 256x128-byte B tiles into a
-//               4-stage ring of 128B-swizzled shared memory.
-//   warp 1      allocates all 512 TMEM columns, then one elected thread issues
-//               tcgen05.mma (M=128, N=256, K=32; four per stage) into one of two f32/s32
-//               accumulators and commits stage-free / accumulator-ready mbarriers.
-//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one row per thread), apply
-//               scale / beta*C / bias / ReLU or GELU / amax / d_scale / cast, store D.  The other
-//               accumulator is being filled by the next tile's main loop meanwhile.
-// Every wait is bounded; on expiry the kernel records a status bit and drains.
+// Two instantiations of one persistent, warp-specialised kernel (320 threads per CTA):
+//   pair   clusters of two CTAs work on 256 x 256 tiles with tcgen05.mma cta_group::2: each CTA
+//          streams its own 128 rows of A and its own 128 columns of B (32 KiB per 128-deep
+//          k-block, six stages), the leader CTA issues M=256, N=256, K=32 MMAs that read both
+//          CTAs' shared memory, and each CTA ends up with its 128 x 256 slice of the accumulator
+//          in its own TMEM.  Halving the B traffic per SM is what lets the shared-memory fill
+//          rate keep up with the tensor pipe.
+//   single one CTA per 128 x 256 tile (48 KiB per k-block, four stages); used when M <= 128.
+// Roles: warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, warps 2-9 = epilogue
+// (tcgen05.ld, scale / beta*C / bias / ReLU or GELU / amax / d_scale / cast, vector stores).
+// TMEM holds two 256-column accumulators so the epilogue of one tile overlaps the main loop of the
+// next.  Every wait is bounded; on expiry the kernel records a status bit and drains.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -22,34 +24,43 @@
 #include "ptx.cuh"
 
 namespace b200sd {
-
 namespace {
 
-constexpr int kBM = 128;          // rows of D per tile (= TMEM lanes)
+constexpr int kBM = 128;          // rows of D per CTA per tile (= TMEM lanes)
 constexpr int kBN = 256;          // columns of D per tile (= TMEM columns per accumulator)
 constexpr int kBK = 128;          // bytes (= 8-bit elements) of K per stage: one 128B swizzle row
 constexpr int kUmmaK = 32;        // K per tcgen05.mma for 8-bit operands
-constexpr int kStages = 4;
 constexpr int kAccBufs = 2;
 constexpr int kAStageBytes = kBM * kBK;          // 16 KiB
-constexpr int kBStageBytes = kBN * kBK;          // 32 KiB
-constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kColsPerEpilogueWarp = kBN / 2;    // warps 2-5 take columns 0-127, warps 6-9 columns 128-255
 constexpr int kTmemCols = 512;
 
+template <bool kPair>
+struct Shape {
+  static constexpr int kStages = kPair ? 6 : 4;
+  static constexpr int kBStageBytes = (kPair ? kBN / 2 : kBN) * kBK;   // 16 or 32 KiB
+  static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+  static constexpr int kTileRows = kPair ? 2 * kBM : kBM;
+};
+
+template <bool kPair>
 struct __align__(16) DenseAux {
-  uint64_t full_bar[kStages];
-  uint64_t empty_bar[kStages];
+  uint64_t full_bar[Shape<kPair>::kStages];
+  uint64_t empty_bar[Shape<kPair>::kStages];
   uint64_t acc_full_bar[kAccBufs];
   uint64_t acc_empty_bar[kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
-  float bias_s[4][kBN];      // one private copy per epilogue warp: no CTA-level barrier needed
-  float colscale_s[4][kBN];
+  float bias_s[kEpilogueWarps][kColsPerEpilogueWarp];      // private per-warp copies: no CTA-level barrier
+  float colscale_s[kEpilogueWarps][kColsPerEpilogueWarp];
 };
 
-constexpr size_t kDenseSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(DenseAux);
+template <bool kPair>
+constexpr size_t DenseSmemBytes() {
+  return 1024 /*alignment slack*/ + size_t(Shape<kPair>::kStages) * Shape<kPair>::kStageBytes + sizeof(DenseAux<kPair>);
+}
 
 struct DenseArgs {
   int64_t m, n, k;
@@ -84,12 +95,14 @@ __device__ __forceinline__ float load_as_f32(const void* base, int32_t dtype, in
   }
 }
 
-// tanh-form GELU, spelled like the HLO the rewriter matches
-// (xla/backends/gpu/transforms/gemm_rewriter.cc:924-971).
+// tanh-form GELU as matched by the rewriter (xla/backends/gpu/transforms/gemm_rewriter.cc:924-971):
+// 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3).  Evaluated through the identity
+// 0.5 (1 + tanh(u)) = 1 / (1 + exp(-2u)) with the hardware exponential and reciprocal
+// (relative error about 2^-21, far inside bf16 / e4m3 output resolution); the limits
+// exp -> inf and exp -> 0 give exactly 0 and x.
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float x3 = x * x * x;
-  const float inner = 0.797884583f * (x + 0.044715f * x3);
-  return x * (0.5f * (1.0f + tanhf(inner)));
+  const float u = 0.797884583f * (x + 0.044715f * (x * x * x));
+  return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
 
 __device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, int32_t* mt, int32_t* nt) {
@@ -122,36 +135,32 @@ __device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float 
       reinterpret_cast<uint4*>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
       reinterpret_cast<uint4*>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else {
-      for (int i = 0; i < ncols; ++i) out[i] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, fmt);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) out[i] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, fmt);
     }
   } else if (p.d_dtype == kBF16 || p.d_dtype == kF16) {
     uint16_t* out = static_cast<uint16_t*>(p.d) + off;
     const bool bf = p.d_dtype == kBF16;
-    if (ncols == 32 && p.vec_store_ok) {
-      uint32_t w[16];
+    uint32_t w[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        if (bf) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-          w[i] = *reinterpret_cast<const uint32_t*>(&h);
-        } else {
-          const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-          w[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
+    for (int i = 0; i < 16; ++i) {
+      if (bf) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
       }
+    }
+    if (ncols == 32 && p.vec_store_ok) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         reinterpret_cast<uint4*>(out)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
     } else {
-      for (int i = 0; i < ncols; ++i) {
-        if (bf) {
-          const __nv_bfloat16 h = __float2bfloat16_rn(v[i]);
-          out[i] = *reinterpret_cast<const uint16_t*>(&h);
-        } else {
-          const __half h = __float2half_rn(v[i]);
-          out[i] = *reinterpret_cast<const uint16_t*>(&h);
-        }
-      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) out[i] = static_cast<uint16_t>(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xFFFFu);
     }
   } else {  // kF32
     float* out = static_cast<float*>(p.d) + off;
@@ -160,25 +169,77 @@ __device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float 
       for (int i = 0; i < 8; ++i)
         reinterpret_cast<float4*>(out)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
     } else {
-      for (int i = 0; i < ncols; ++i) out[i] = v[i];
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncols) out[i] = v[i];
     }
   }
 }
 
+// Epilogue arithmetic and store for one 32-column chunk of one accumulator row.
 template <bool kInt8>
+__device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t (&r)[32], int64_t row, int64_t col0,
+                                             int32_t ncols, float scale, float d_scale, float row_scale,
+                                             const float* bias_c, const float* colscale_c, uint32_t* amax_bits) {
+  float v[32];
+  if (kInt8) {
+    if (p.d_s32) {
+      int32_t* out = p.d_s32 + row * p.n + col0;
+      if (ncols == 32 && p.vec_store_ok) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<uint4*>(out)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < ncols) out[i] = static_cast<int32_t>(r[i]);
+      }
+    }
+    if (p.d == nullptr) return;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float x = __int2float_rn(static_cast<int32_t>(r[i]));
+      if (p.a_row_scale) x = x * row_scale;
+      if (p.b_col_scale) x = x * colscale_c[i];
+      v[i] = x;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float x = __uint_as_float(r[i]) * scale;
+      if (p.c != nullptr && i < ncols) x += p.beta * load_as_f32(p.c, p.c_dtype, row * p.n + col0 + i);
+      if (p.bias) x += bias_c[i];
+      if (p.activation == kActRelu) {
+        x = (x != x) ? x : fmaxf(x, 0.0f);
+      } else if (p.activation == kActGelu) {
+        x = gelu_tanh(x);
+      }
+      if (p.amax != nullptr && i < ncols) *amax_bits = max(*amax_bits, __float_as_uint(fabsf(x)));
+      v[i] = x * d_scale;
+    }
+  }
+  store_row_chunk(p, v, row, col0, ncols);
+}
+
+template <bool kInt8, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const DenseArgs p) {
+  using S = Shape<kPair>;
+  constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kAStageBytes;
-  DenseAux* aux = reinterpret_cast<DenseAux*>(smem + kStages * kStageBytes);
+  DenseAux<kPair>* aux = reinterpret_cast<DenseAux<kPair>*>(smem + kStages * S::kStageBytes);
   volatile int* abort_flag = &aux->abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = kPair ? cluster_cta_rank() : 0u;        // 0 = leader of the pair
   const int32_t num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int32_t first_tile = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
+  const int32_t tile_step = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -187,7 +248,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&aux->acc_full_bar[b], 1);
-      mbar_init(&aux->acc_empty_bar[b], kEpilogueThreads);
+      mbar_init(&aux->acc_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
     aux->abort_flag = 0;
     fence_mbar_init();
@@ -196,11 +257,17 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(&aux->tmem_base, kTmemCols);
-    tmem_relinquish_alloc();
+    if (kPair) {
+      tmem_alloc_pair(&aux->tmem_base, kTmemCols);
+      tmem_relinquish_alloc_pair();
+    } else {
+      tmem_alloc(&aux->tmem_base, kTmemCols);
+      tmem_relinquish_alloc();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (kPair) cluster_sync_all();          // the peer's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = aux->tmem_base;
 
@@ -210,26 +277,44 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         int32_t mt, nt;
         tile_coords(tile, p, &mt, &nt);
+        const int32_t row0 = mt * S::kTileRows + int32_t(rank) * kBM;
+        const int32_t col0 = nt * kBN + (kPair ? int32_t(rank) * (kBN / 2) : 0);
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
           if (!ok) break;
-          uint64_t* full = &aux->full_bar[stage];
-          mbar_arrive_expect_tx(full, kStageBytes);
           uint8_t* sa = smem_a + stage * kAStageBytes;
-          uint8_t* sb = smem_b + stage * kBStageBytes;
-          if (p.a_mn_major) {
-            tma_load_2d(sa, &tmap_a, full, mt * kBM, kb * kBK);
+          uint8_t* sb = smem_b + stage * S::kBStageBytes;
+          if (kPair) {
+            // Both CTAs' loads count on the leader's barrier; the leader announces the bytes of both.
+            if (rank == 0) mbar_arrive_expect_tx(&aux->full_bar[stage], 2 * S::kStageBytes);
+            const uint32_t full = map_to_cta(&aux->full_bar[stage], 0);
+            if (p.a_mn_major) {
+              tma_load_2d_pair(sa, &tmap_a, full, row0, kb * kBK);
+            } else {
+              tma_load_2d_pair(sa, &tmap_a, full, kb * kBK, row0);
+            }
+            if (p.b_mn_major) {
+              tma_load_2d_pair(sb, &tmap_b, full, col0, kb * kBK);
+            } else {
+              tma_load_2d_pair(sb, &tmap_b, full, kb * kBK, col0);
+            }
           } else {
-            tma_load_2d(sa, &tmap_a, full, kb * kBK, mt * kBM);
-          }
-          if (p.b_mn_major) {
-            tma_load_2d(sb, &tmap_b, full, nt * kBN, kb * kBK);
-            tma_load_2d(sb + kBStageBytes / 2, &tmap_b, full, nt * kBN + 128, kb * kBK);
-          } else {
-            tma_load_2d(sb, &tmap_b, full, kb * kBK, nt * kBN);
+            uint64_t* full = &aux->full_bar[stage];
+            mbar_arrive_expect_tx(full, S::kStageBytes);
+            if (p.a_mn_major) {
+              tma_load_2d(sa, &tmap_a, full, row0, kb * kBK);
+            } else {
+              tma_load_2d(sa, &tmap_a, full, kb * kBK, row0);
+            }
+            if (p.b_mn_major) {
+              tma_load_2d(sb, &tmap_b, full, col0, kb * kBK);
+              tma_load_2d(sb + S::kBStageBytes / 2, &tmap_b, full, col0 + 128, kb * kBK);
+            } else {
+              tma_load_2d(sb, &tmap_b, full, kb * kBK, col0);
+            }
           }
           if (++stage == kStages) {
             stage = 0;
@@ -237,7 +322,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
         }
       }
-      if (!ok) {
+      if (!ok && !kPair) {
         // Abort path: let loads that were already issued land before the CTA's memory is released.
         for (int s = 0; s < kStages; ++s) {
           for (int i = 0; i < 100000 && !mbar_try_wait(&aux->full_bar[s], 0) && !mbar_try_wait(&aux->full_bar[s], 1); ++i) {
@@ -246,11 +331,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      const uint32_t a_lbo = 16384, b_lbo = 16384, sbo = 1024;
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), a_lbo, sbo);
-      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), b_lbo, sbo);
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t sbo = 1024, lbo = 16384;
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), lbo, sbo);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), lbo, sbo);
       // Encoded (>>4) advance of the start address per K=32 step: 32 bytes along a K-major row,
       // 32 rows of 128 bytes for an MN-major operand.
       const uint32_t a_kstep = p.a_mn_major ? (kUmmaK * 128) >> 4 : kUmmaK >> 4;
@@ -260,7 +345,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
         if (!ok) break;
         tc_fence_after_sync();
@@ -270,24 +355,38 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
-          const uint64_t b_desc = b_desc0 + uint64_t((stage * kBStageBytes) >> 4);
+          const uint64_t b_desc = b_desc0 + uint64_t((stage * S::kBStageBytes) >> 4);
 #pragma unroll
           for (int j = 0; j < kBK / kUmmaK; ++j) {
             const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
-            if (kInt8) {
-              umma_i8(d_tmem, a_desc + uint64_t(j * a_kstep), b_desc + uint64_t(j * b_kstep), p.idesc, accumulate);
+            const uint64_t ad = a_desc + uint64_t(j * a_kstep), bd = b_desc + uint64_t(j * b_kstep);
+            if (kPair) {
+              if (kInt8) umma_i8_pair(d_tmem, ad, bd, p.idesc, accumulate);
+              else umma_f8_pair(d_tmem, ad, bd, p.idesc, accumulate);
             } else {
-              umma_f8(d_tmem, a_desc + uint64_t(j * a_kstep), b_desc + uint64_t(j * b_kstep), p.idesc, accumulate);
+              if (kInt8) umma_i8(d_tmem, ad, bd, p.idesc, accumulate);
+              else umma_f8(d_tmem, ad, bd, p.idesc, accumulate);
             }
           }
-          umma_commit(&aux->empty_bar[stage]);   // stage reusable once these MMAs have read it
+          // The stage may be refilled once these MMAs have read it -- in both CTAs of a pair.
+          if (kPair) {
+            umma_commit_pair(map_to_cta(&aux->empty_bar[stage], 0));
+            umma_commit_pair(map_to_cta(&aux->empty_bar[stage], 1));
+          } else {
+            umma_commit(&aux->empty_bar[stage]);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&aux->acc_full_bar[acc]);    // accumulator complete
+        if (kPair) {                                   // accumulator complete (each CTA has its rows)
+          umma_commit_pair(map_to_cta(&aux->acc_full_bar[acc], 0));
+          umma_commit_pair(map_to_cta(&aux->acc_full_bar[acc], 1));
+        } else {
+          umma_commit(&aux->acc_full_bar[acc]);
+        }
         if (++acc == kAccBufs) {
           acc = 0;
           acc_phase ^= 1;
@@ -295,10 +394,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;                      // TMEM lane quarter this warp may access
-    float* bias_w = aux->bias_s[q];
-    float* colscale_w = aux->colscale_s[q];
+    const int ew = warp - 2;                     // 0..7
+    const int col_half = ew >> 2;                // which 128 columns of the tile
+    float* bias_w = aux->bias_s[ew];
+    float* colscale_w = aux->colscale_s[ew];
     float scale = p.alpha;
     float d_scale = 1.0f;
     if (!kInt8) {
@@ -310,13 +411,13 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (int32_t tile = first_tile; tile < num_tiles; tile += tile_step) {
       int32_t mt, nt;
       tile_coords(tile, p, &mt, &nt);
-      const int64_t col_base = int64_t(nt) * kBN;
-      // Stage the per-column vectors of this tile (each warp keeps its own copy).
+      const int64_t col_base = int64_t(nt) * kBN + col_half * kColsPerEpilogueWarp;
+      // Stage the per-column vectors of this warp's columns.
       __syncwarp();
-      for (int i = lane; i < kBN; i += 32) {
+      for (int i = lane; i < kColsPerEpilogueWarp; i += 32) {
         const int64_t col = col_base + i;
         if (p.bias) bias_w[i] = col < p.n ? load_as_f32(p.bias, p.bias_dtype, col) : 0.0f;
         if (kInt8 && p.b_col_scale) colscale_w[i] = col < p.n ? __ldg(p.b_col_scale + col) : 0.0f;
@@ -331,60 +432,36 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
       tc_fence_after_sync();
 
-      const int64_t row = int64_t(mt) * kBM + q * 32 + lane;
+      const int64_t row = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
       const bool row_ok = row < p.m;
       float row_scale = 1.0f;
       if (kInt8 && p.a_row_scale && row_ok) row_scale = __ldg(p.a_row_scale + row);
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN);
+      const uint32_t taddr =
+          tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN + col_half * kColsPerEpilogueWarp);
 
-#pragma unroll 1
-      for (int cchunk = 0; cchunk < kBN / 32; ++cchunk) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + cchunk * 32, r);
-        tmem_ld_wait();
+      // Four 32-column chunks; the load of the next chunk is in flight while one is processed.
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(taddr, r0);
+#pragma unroll
+      for (int cchunk = 0; cchunk < kColsPerEpilogueWarp / 32; ++cchunk) {
+        uint32_t(&cur)[32] = (cchunk & 1) ? r1 : r0;
+        uint32_t(&nxt)[32] = (cchunk & 1) ? r0 : r1;
+        tmem_ld_wait_for(cur);
+        if (cchunk + 1 < kColsPerEpilogueWarp / 32) tmem_ld_32x32(taddr + (cchunk + 1) * 32, nxt);
         const int64_t col0 = col_base + cchunk * 32;
-        if (col0 >= p.n) continue;
-        const int32_t ncols = static_cast<int32_t>(min(int64_t(32), p.n - col0));
-        if (!row_ok) continue;
-        float v[32];
-        if (kInt8) {
-          if (p.d_s32) {
-            int32_t* out = p.d_s32 + row * p.n + col0;
-            if (ncols == 32 && p.vec_store_ok) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                reinterpret_cast<uint4*>(out)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-            } else {
-              for (int i = 0; i < ncols; ++i) out[i] = static_cast<int32_t>(r[i]);
-            }
-          }
-          if (p.d == nullptr) continue;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __int2float_rn(static_cast<int32_t>(r[i]));
-            if (p.a_row_scale) x = x * row_scale;
-            if (p.b_col_scale) x = x * colscale_w[cchunk * 32 + i];
-            v[i] = x;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(r[i]) * scale;
-            if (p.c != nullptr && i < ncols) x += p.beta * load_as_f32(p.c, p.c_dtype, row * p.n + col0 + i);
-            if (p.bias) x += bias_w[cchunk * 32 + i];
-            if (p.activation == kActRelu) {
-              x = (x != x) ? x : fmaxf(x, 0.0f);
-            } else if (p.activation == kActGelu) {
-              x = gelu_tanh(x);
-            }
-            if (p.amax != nullptr && i < ncols) amax_bits = max(amax_bits, __float_as_uint(fabsf(x)));
-            v[i] = x * d_scale;
-          }
+        if (col0 < p.n && row_ok) {
+          const int32_t ncols = static_cast<int32_t>(min(int64_t(32), p.n - col0));
+          finish_chunk<kInt8>(p, cur, row, col0, ncols, scale, d_scale, row_scale, bias_w + cchunk * 32,
+                              colscale_w + cchunk * 32, &amax_bits);
         }
-        store_row_chunk(p, v, row, col0, ncols);
       }
+      // Hand the accumulator back to the MMA issuer (in the leader CTA): one arrival per warp.
       tc_fence_before_sync();
-      mbar_arrive(&aux->acc_empty_bar[acc]);
+      __syncwarp();
+      if (lane == 0) {
+        if (kPair && rank != 0) mbar_arrive_cluster(map_to_cta(&aux->acc_empty_bar[acc], 0));
+        else mbar_arrive(&aux->acc_empty_bar[acc]);
+      }
       if (++acc == kAccBufs) {
         acc = 0;
         acc_phase ^= 1;
@@ -400,9 +477,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
   tc_fence_before_sync();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // nobody leaves while the peer may still read this CTA's shared memory
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -422,6 +501,25 @@ EncodeTiledFn GetEncodeTiled() {
     return reinterpret_cast<EncodeTiledFn>(p);
   }();
   return fn;
+}
+
+int g_max_pair_clusters[64];   // co-resident 2-CTA clusters per device, filled by InitDenseKernels
+
+template <bool kInt8, bool kPair>
+cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const DenseArgs& p) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = DenseSmemBytes<kPair>();
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kPair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, dense_gemm_kernel<kInt8, kPair>, ta, tb, p);
 }
 
 }  // namespace
@@ -446,12 +544,36 @@ Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64
 }
 
 Status InitDenseKernels() {
-  cudaError_t e = cudaFuncSetAttribute(dense_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       int(kDenseSmemBytes));
-  if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(dense_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             int(kDenseSmemBytes));
+  int device = 0;
+  cudaGetDevice(&device);
+  cudaError_t e = cudaSuccess;
+  auto set = [&](const void* fn, size_t bytes) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
+  };
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, false>), DenseSmemBytes<false>());
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<true, false>), DenseSmemBytes<false>());
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true>), DenseSmemBytes<true>());
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<true, true>), DenseSmemBytes<true>());
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(dense): ") + cudaGetErrorString(e));
+  // How many CTA pairs fit on the device at once bounds the persistent grid of the pair kernel.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = DenseSmemBytes<true>();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&clusters, dense_gemm_kernel<false, true>, &cfg);
+  if (e != cudaSuccess || clusters <= 0) {
+    cudaGetLastError();
+    clusters = 0;             // the pair kernel is then never selected
+  }
+  if (device >= 0 && device < 64) g_max_pair_clusters[device] = clusters;
   return Status::Ok();
 }
 
@@ -460,11 +582,24 @@ uint32_t FormatCode(int32_t dtype) {
   return dtype == kF8E5M2 ? 1u : (dtype == kS8 ? 1u : 0u);
 }
 
-Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats) {
+int MaxPairClusters() {
+  int device = 0;
+  cudaGetDevice(&device);
+  return (device >= 0 && device < 64) ? g_max_pair_clusters[device] : 0;
+}
+
+Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats, int variant) {
   int device = 0;
   cudaGetDevice(&device);
   Status st = InitDevice(device);
   if (!st.ok()) return st;
+  const int max_pairs = MaxPairClusters();
+  bool pair = g.m > kBM && max_pairs > 0;           // a second CTA would only compute padding when M <= 128
+  if (variant == kKernelDenseSingle) pair = false;
+  if (variant == kKernelDensePair) {
+    if (max_pairs <= 0) return Status::Error(kFailedPrecondition, "this device cannot co-schedule CTA pairs for the pair kernel");
+    pair = true;
+  }
 
   CUtensorMap tmap_a, tmap_b;
   if (g.a_mn_major) {
@@ -474,21 +609,22 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   }
   if (!st.ok()) return st;
   if (g.b_mn_major) {
-    st = MakeByteMatrixMap(&tmap_b, g.b, g.k, g.n, 128, kBK);       // [k, n], box 128(n) x 128(k), two per stage
+    st = MakeByteMatrixMap(&tmap_b, g.b, g.k, g.n, 128, kBK);       // [k, n], box 128(n) x 128(k)
   } else {
-    st = MakeByteMatrixMap(&tmap_b, g.b, g.n, g.k, kBK, kBN);       // [n, k], box 128(k) x 256(n)
+    st = MakeByteMatrixMap(&tmap_b, g.b, g.n, g.k, kBK, pair ? kBN / 2 : kBN);   // [n, k], box 128(k) x 128|256(n)
   }
   if (!st.ok()) return st;
 
   DenseArgs p{};
   p.m = g.m; p.n = g.n; p.k = g.k;
-  p.num_m_tiles = int32_t((g.m + kBM - 1) / kBM);
+  const int tile_rows = pair ? 2 * kBM : kBM;
+  p.num_m_tiles = int32_t((g.m + tile_rows - 1) / tile_rows);
   p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
-  p.raster_group = 16;
+  p.raster_group = pair ? 8 : 16;
   p.a_mn_major = g.a_mn_major; p.b_mn_major = g.b_mn_major;
   p.idesc = make_idesc(g.int8 ? 2u : 1u, FormatCode(g.a_dtype), FormatCode(g.b_dtype), g.a_mn_major, g.b_mn_major,
-                       kBM, kBN);
+                       uint32_t(tile_rows), kBN);
   p.a_scale = g.a_scale; p.b_scale = g.b_scale; p.d_scale = g.d_scale;
   p.alpha = g.alpha; p.beta = g.beta;
   p.c = (g.beta != 0.0f) ? g.c : nullptr; p.c_dtype = g.c_dtype;
@@ -511,20 +647,25 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   p.status = StatusWordPtr();
 
   const int64_t tiles = int64_t(p.num_m_tiles) * p.num_n_tiles;
-  const int grid = int(tiles < DeviceSmCount() ? tiles : DeviceSmCount());
+  int grid;
+  if (pair) {
+    grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
+  } else {
+    grid = int(tiles < DeviceSmCount() ? tiles : DeviceSmCount());
+  }
   if (g.amax != nullptr) {
     cudaError_t e = cudaMemsetAsync(g.amax, 0, sizeof(float), stream);
     if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(amax): ") + cudaGetErrorString(e));
   }
-  if (g.int8) {
-    dense_gemm_kernel<true><<<grid, kThreads, kDenseSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  cudaError_t e;
+  if (pair) {
+    e = g.int8 ? LaunchOne<true, true>(grid, stream, tmap_a, tmap_b, p) : LaunchOne<false, true>(grid, stream, tmap_a, tmap_b, p);
   } else {
-    dense_gemm_kernel<false><<<grid, kThreads, kDenseSmemBytes, stream>>>(tmap_a, tmap_b, p);
+    e = g.int8 ? LaunchOne<true, false>(grid, stream, tmap_a, tmap_b, p) : LaunchOne<false, false>(grid, stream, tmap_a, tmap_b, p);
   }
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("dense_gemm_kernel launch: ") + cudaGetErrorString(e));
   if (stats) {
-    stats->kernel = kKernelDense;
+    stats->kernel = pair ? kKernelDensePair : kKernelDenseSingle;
     stats->grid = grid;
     stats->launches = 1;
   }

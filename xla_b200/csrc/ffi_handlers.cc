@@ -169,6 +169,7 @@ ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   a.struct_size = sizeof(a);
   a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(1));
   a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(0));
+  a.kernel = static_cast<int32_t>(GetInt(attrs, "selected_config").value_or(B200SD_KERNEL_AUTO));
   const bool emit_s32 = GetBool(attrs, "emit_s32", false);
   if (GetFloat(attrs, "alpha_real").value_or(1.0) != 1.0 || GetFloat(attrs, "beta").value_or(0.0) != 0.0)
     return MakeError(12, "alpha and beta are not fused into integer dots (the reference does not either)");

@@ -79,7 +79,7 @@ struct GemmProblem {
 };
 
 // Kernel selection (stands in for cuBLASLt's algorithm index).
-enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2 };
+enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2, kKernelDenseSingle = 3, kKernelDensePair = 4 };
 
 struct LaunchStats {
   int32_t kernel = 0;     // KernelKind actually used
@@ -91,7 +91,8 @@ struct LaunchStats {
 // be called for the first time while the stream is being captured.
 Status InitDevice(int device);
 
-Status LaunchDense(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats);
+// `variant`: kKernelDense picks between the CTA-pair and the single-CTA instantiation.
+Status LaunchDense(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats, int variant = kKernelDense);
 Status LaunchSkinny(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats);
 size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k);
 

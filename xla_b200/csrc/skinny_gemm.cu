@@ -4,17 +4,20 @@
 // where it is bound by memory bandwidth.
 //
 // The roles of the operands are swapped so that W fills the 128-row side of the tensor-core
-// instruction: each tile computes D^T[128 n, m] = W^T . A^T with W taken MN-major straight from
-// its row-major [k,n] storage and A as the (narrow) N operand.  Work is split stream-K style:
-// the (n-tile, k-block) units are dealt out evenly to one persistent CTA per SM, so every SM
-// streams the same number of W bytes.  A CTA whose range ends inside a tile computes that piece
+// instruction: D^T[128 n, m] = W^T . A^T, with W taken MN-major straight from its row-major [k,n]
+// storage and A as the (narrow) N operand.  A CTA works on a "strip" of `n_sub` adjacent 128-column
+// tiles at once (n_sub accumulators), so that every k-row it fetches is n_sub*128 contiguous
+// bytes of W -- long enough runs for the DRAM pages to be used well.  Work is split stream-K
+// style: the (strip, k-block) units are dealt out evenly to one persistent CTA per SM, so every SM
+// streams the same number of W bytes.  A CTA whose range ends inside a strip computes that piece
 // FIRST, writes the f32 partial to the caller's workspace and raises a flag; the CTA that owns
-// the tile's last k-block adds the partials of the (lower-numbered) CTAs before it and writes D.
+// the strip's last k-block adds the partials of the (lower-numbered) CTAs before it and writes D.
 // Waiting therefore only ever targets CTAs that were scheduled earlier and finished that piece
 // long ago; the wait is bounded all the same.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "kernels.h"
@@ -23,35 +26,36 @@
 namespace b200sd {
 namespace {
 
-constexpr int kTileN = 128;        // weight columns per tile (= TMEM lanes)
+constexpr int kTileN = 128;        // weight columns per accumulator (= TMEM lanes)
 constexpr int kBK = 128;           // k per stage
 constexpr int kUmmaK = 32;
-constexpr int kStages = 6;
-constexpr int kWStageBytes = kBK * kTileN;   // 16 KiB
-constexpr int kAStageBytes = 128 * kBK;      // up to 128 activation rows, 16 KiB
-constexpr int kStageBytes = kWStageBytes + kAStageBytes;
+constexpr int kMaxStages = 8;
+constexpr int kMaxSub = 4;
+constexpr int kWBoxBytes = kBK * kTileN;     // 16 KiB per 128-column tile per stage
 constexpr int kThreads = 192;
 constexpr int kAccBufs = 2;
-constexpr int kTmemCols = 256;     // two accumulators of up to 128 columns
-constexpr int kMaxCtas = 256;
+constexpr int kTmemCols = 512;
+constexpr int kMaxCtas = 160;
 constexpr size_t kFlagBytes = size_t(kMaxCtas) * 4 * sizeof(uint32_t);   // one flag per CTA per epilogue warp
+constexpr size_t kSmemBudget = 227 * 1024;
 
 struct __align__(16) SkinnyAux {
-  uint64_t full_bar[kStages];
-  uint64_t empty_bar[kStages];
+  uint64_t full_bar[kMaxStages];
+  uint64_t empty_bar[kMaxStages];
   uint64_t acc_full_bar[kAccBufs];
   uint64_t acc_empty_bar[kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-constexpr size_t kSkinnySmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(SkinnyAux);
-
 struct SkinnyArgs {
   int32_t m;                 // activation rows (multiple of 16, <= 128)
   int64_t n, k;
-  int32_t num_n_tiles, num_k_blocks;
-  int64_t total_units;       // num_n_tiles * num_k_blocks
+  int32_t n_sub;             // 128-column tiles per strip
+  int32_t stages;
+  int32_t a_stage_bytes;     // m * 128 rounded up to 1 KiB
+  int32_t num_strips, num_k_blocks;
+  int64_t total_units;       // num_strips * num_k_blocks
   uint32_t idesc;
   const float* a_scale;
   const float* b_scale;
@@ -59,7 +63,7 @@ struct SkinnyArgs {
   void* d;
   int32_t d_dtype;
   uint32_t* flags;           // [grid][4], zeroed before the launch
-  float* partials;           // [grid][m][128]
+  float* partials;           // [grid][n_sub][m][128]
   uint32_t* status;
 };
 
@@ -74,6 +78,13 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
 }
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
@@ -100,9 +111,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const SkinnyArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_w = smem;
-  uint8_t* smem_a = smem + kStages * kWStageBytes;
-  SkinnyAux* aux = reinterpret_cast<SkinnyAux*>(smem + kStages * kStageBytes);
+  const int w_stage_bytes = p.n_sub * kWBoxBytes;
+  const int stage_bytes = w_stage_bytes + p.a_stage_bytes;
+  SkinnyAux* aux = reinterpret_cast<SkinnyAux*>(smem + p.stages * stage_bytes);
   volatile int* abort_flag = &aux->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -110,16 +121,17 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int64_t cta = blockIdx.x, grid = gridDim.x;
   const int64_t u_begin = unit_begin(cta, p.total_units, grid);
   const int64_t u_end = unit_begin(cta + 1, p.total_units, grid);
-  const uint32_t stage_tx_bytes = kWStageBytes + uint32_t(p.m) * kBK;
+  const uint32_t stage_tx_bytes = uint32_t(w_stage_bytes) + uint32_t(p.m) * kBK;
+  const int acc_cols = p.n_sub * p.m;            // TMEM columns of one accumulator set
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < p.stages; ++s) {
       mbar_init(&aux->full_bar[s], 1);
       mbar_init(&aux->empty_bar[s], 1);
     }
     for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&aux->acc_full_bar[b], 1);
-      mbar_init(&aux->acc_empty_bar[b], 128);
+      mbar_init(&aux->acc_empty_bar[b], 4);
     }
     aux->abort_flag = 0;
     fence_mbar_init();
@@ -136,10 +148,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = aux->tmem_base;
 
-  // The CTA walks its unit range [u_begin, u_end) backwards, one tile-segment at a time:
-  //   segment = units of one tile, [max(u_begin, tile*KB), min(u_end, (tile+1)*KB)).
+  // The CTA walks its unit range [u_begin, u_end) backwards, one strip-segment at a time:
+  //   segment = units of one strip, [max(u_begin, strip*KB), min(u_end, (strip+1)*KB)).
   // All three roles derive the same segment sequence from these two numbers.
-  const int64_t kb_per_tile = p.num_k_blocks;
+  const int64_t kb_per_strip = p.num_k_blocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -149,17 +161,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       bool ok = true;
       int64_t seg_end = u_end;
       while (seg_end > u_begin && ok) {
-        const int64_t tile = (seg_end - 1) / kb_per_tile;
-        const int64_t seg_begin = max(u_begin, tile * kb_per_tile);
+        const int64_t strip = (seg_end - 1) / kb_per_strip;
+        const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
         for (int64_t u = seg_begin; u < seg_end; ++u) {
-          const int32_t kb = int32_t(u - tile * kb_per_tile);
+          const int32_t kb = int32_t(u - strip * kb_per_strip);
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
           if (!ok) break;
           uint64_t* full = &aux->full_bar[stage];
           mbar_arrive_expect_tx(full, stage_tx_bytes);
-          tma_load_2d(smem_w + stage * kWStageBytes, &tmap_w, full, int32_t(tile) * kTileN, kb * kBK);
-          tma_load_2d(smem_a + stage * kAStageBytes, &tmap_a, full, kb * kBK, 0);
-          if (++stage == kStages) {
+          uint8_t* sw = smem + stage * stage_bytes;
+          for (int s = 0; s < p.n_sub; ++s)
+            tma_load_2d(sw + s * kWBoxBytes, &tmap_w, full, (int32_t(strip) * p.n_sub + s) * kTileN, kb * kBK);
+          tma_load_2d(sw + w_stage_bytes, &tmap_a, full, kb * kBK, 0);
+          if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
           }
@@ -167,7 +181,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         seg_end = seg_begin;
       }
       if (!ok) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
           for (int i = 0; i < 100000 && !mbar_try_wait(&aux->full_bar[s], 0) && !mbar_try_wait(&aux->full_bar[s], 1); ++i) {
           }
         }
@@ -176,8 +190,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint64_t w_desc0 = make_smem_desc_sw128(smem_u32(smem_w), 16384, 1024);   // MN-major
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), 16, 1024);      // K-major
+      const uint64_t w_desc0 = make_smem_desc_sw128(smem_u32(smem), 16384, 1024);                    // MN-major
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem + w_stage_bytes), 16, 1024);       // K-major
       const uint32_t w_kstep = (kUmmaK * 128) >> 4;
       const uint32_t a_kstep = kUmmaK >> 4;
       int stage = 0;
@@ -187,25 +201,27 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       bool ok = true;
       int64_t seg_end = u_end;
       while (seg_end > u_begin && ok) {
-        const int64_t tile = (seg_end - 1) / kb_per_tile;
-        const int64_t seg_begin = max(u_begin, tile * kb_per_tile);
+        const int64_t strip = (seg_end - 1) / kb_per_strip;
+        const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
         ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * 128;
+        const uint32_t d_tmem = tmem_base + acc * acc_cols;
         for (int64_t u = seg_begin; u < seg_end; ++u) {
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint64_t w_desc = w_desc0 + uint64_t((stage * kWStageBytes) >> 4);
-          const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
+          const uint64_t stage_off = uint64_t((stage * stage_bytes) >> 4);
+          for (int s = 0; s < p.n_sub; ++s) {
+            const uint64_t w_desc = w_desc0 + stage_off + uint64_t((s * kWBoxBytes) >> 4);
 #pragma unroll
-          for (int j = 0; j < kBK / kUmmaK; ++j) {
-            umma_f8(d_tmem, w_desc + uint64_t(j * w_kstep), a_desc + uint64_t(j * a_kstep), p.idesc,
-                    (u > seg_begin || j > 0) ? 1u : 0u);
+            for (int j = 0; j < kBK / kUmmaK; ++j) {
+              umma_f8(d_tmem + s * p.m, w_desc + uint64_t(j * w_kstep), a_desc0 + stage_off + uint64_t(j * a_kstep),
+                      p.idesc, (u > seg_begin || j > 0) ? 1u : 0u);
+            }
           }
           umma_commit(&aux->empty_bar[stage]);
-          if (++stage == kStages) {
+          if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
           }
@@ -230,11 +246,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     bool ok = true;
     int64_t seg_end = u_end;
     while (seg_end > u_begin) {
-      const int64_t tile = (seg_end - 1) / kb_per_tile;
-      const int64_t tile_first = tile * kb_per_tile;
-      const int64_t seg_begin = max(u_begin, tile_first);
-      const bool owns_tail = seg_end == tile_first + kb_per_tile;   // holds the tile's last k-block
-      const bool owns_head = seg_begin == tile_first;
+      const int64_t strip = (seg_end - 1) / kb_per_strip;
+      const int64_t strip_first = strip * kb_per_strip;
+      const int64_t seg_begin = max(u_begin, strip_first);
+      const bool owns_tail = seg_end == strip_first + kb_per_strip;   // holds the strip's last k-block
+      const bool owns_head = seg_begin == strip_first;
 
       if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -242,30 +258,32 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);
       tc_fence_after_sync();
 
-      const int nl = q * 32 + lane;                          // lane of the accumulator = column of the tile
-      const int64_t col = tile * kTileN + nl;
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * 128);
+      const int nl = q * 32 + lane;                          // lane of the accumulator = column within a tile
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * acc_cols);
+      const int64_t slot_floats = int64_t(p.n_sub) * p.m * kTileN;
 
       if (!owns_tail) {
         // Partial piece: park it in this CTA's workspace slot and publish.
-        float* slot = p.partials + (cta * p.m) * kTileN;
+        float* slot = p.partials + cta * slot_floats;
+        for (int s = 0; s < p.n_sub; ++s) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < p.m; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld_32x16(taddr + c0, r);
-          tmem_ld_wait();
+          for (int c0 = 0; c0 < p.m; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + s * p.m + c0, r);
+            tmem_ld_wait_16(r);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) __stcg(slot + (c0 + i) * kTileN + nl, __uint_as_float(r[i]));
+            for (int i = 0; i < 16; ++i) __stcg(slot + (int64_t(s) * p.m + c0 + i) * kTileN + nl, __uint_as_float(r[i]));
+          }
         }
         __threadfence();
         __syncwarp();
         if (lane == 0) st_release_gpu(p.flags + cta * 4 + q, 1u);
       } else {
-        // Finishing piece.  Wait for the CTAs that hold the earlier k-blocks of this tile.
-        int64_t first_contrib = cta;   // lowest CTA index that contributed to this tile
+        // Finishing piece.  Wait for the CTAs that hold the earlier k-blocks of this strip.
+        int64_t first_contrib = cta;   // lowest CTA index that contributed to this strip
         if (!owns_head) {
           first_contrib = cta - 1;
-          while (unit_begin(first_contrib, p.total_units, grid) > tile_first) --first_contrib;
+          while (unit_begin(first_contrib, p.total_units, grid) > strip_first) --first_contrib;
           if (lane == 0) {
             for (int64_t c = cta - 1; c >= first_contrib && ok; --c) {
               const uint32_t* f = p.flags + c * 4 + q;
@@ -287,29 +305,34 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
+          __syncwarp();
           __threadfence();
         }
+        for (int s = 0; s < p.n_sub; ++s) {
+          const int64_t col = (strip * p.n_sub + s) * kTileN + nl;
 #pragma unroll 1
-        for (int c0 = 0; c0 < p.m; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld_32x16(taddr + c0, r);
-          tmem_ld_wait();
-          float v[16];
+          for (int c0 = 0; c0 < p.m; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + s * p.m + c0, r);
+            tmem_ld_wait_16(r);
+            float v[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-          for (int64_t c = first_contrib; c < cta; ++c) {
-            const float* slot = p.partials + (c * p.m) * kTileN;
+            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+            for (int64_t c = first_contrib; c < cta; ++c) {
+              const float* slot = p.partials + c * slot_floats;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] += __ldcg(slot + (c0 + i) * kTileN + nl);
-          }
-          if (col < p.n) {
+              for (int i = 0; i < 16; ++i) v[i] += __ldcg(slot + (int64_t(s) * p.m + c0 + i) * kTileN + nl);
+            }
+            if (col < p.n) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) store_out(p, int64_t(c0 + i) * p.n + col, v[i] * scale);
+              for (int i = 0; i < 16; ++i) store_out(p, int64_t(c0 + i) * p.n + col, v[i] * scale);
+            }
           }
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(&aux->acc_empty_bar[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&aux->acc_empty_bar[acc]);
       if (++acc == kAccBufs) {
         acc = 0;
         acc_phase ^= 1;
@@ -326,6 +349,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   }
 }
 
+// Strip width: as wide as the two accumulator sets allow (2 * n_sub * m <= 512 TMEM columns).
+int StripTiles(int64_t m) {
+  static const int forced = [] {
+    const char* e = std::getenv("B200SD_SKINNY_NSUB");   // tuning override: 1, 2 or 4
+    return e ? std::atoi(e) : 0;
+  }();
+  int n_sub = m <= 64 ? 4 : 2;
+  if (forced == 1 || forced == 2 || forced == 4) n_sub = forced;
+  while (2 * n_sub * m > kTmemCols) n_sub >>= 1;
+  return n_sub;
+}
+
 }  // namespace
 
 Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, uint32_t box_cols,
@@ -333,14 +368,14 @@ Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64
 
 Status InitSkinnyKernels() {
   cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       int(kSkinnySmemBytes));
+                                       int(kSmemBudget));
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(skinny): ") + cudaGetErrorString(e));
   return Status::Ok();
 }
 
 size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k) {
   if (m <= 0 || m > 128 || m % 16 != 0 || n <= 0 || k <= 0) return 0;
-  return kFlagBytes + size_t(kMaxCtas) * size_t(m) * kTileN * sizeof(float);
+  return kFlagBytes + size_t(kMaxCtas) * size_t(kMaxSub) * size_t(m <= 64 ? m : m / 2) * kTileN * sizeof(float);
 }
 
 Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats) {
@@ -364,9 +399,17 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
 
   SkinnyArgs p{};
   p.m = int32_t(g.m); p.n = g.n; p.k = g.k;
-  p.num_n_tiles = int32_t((g.n + kTileN - 1) / kTileN);
+  p.n_sub = StripTiles(g.m);
+  p.a_stage_bytes = int32_t((g.m * kBK + 1023) / 1024 * 1024);
+  const size_t stage_bytes = size_t(p.n_sub) * kWBoxBytes + p.a_stage_bytes;
+  int stages = int((kSmemBudget - 1024 - sizeof(SkinnyAux)) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return Status::Error(kInternal, "split-K kernel: not enough shared memory for two stages");
+  p.stages = stages;
+  const int64_t strip_cols = int64_t(p.n_sub) * kTileN;
+  p.num_strips = int32_t((g.n + strip_cols - 1) / strip_cols);
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
-  p.total_units = int64_t(p.num_n_tiles) * p.num_k_blocks;
+  p.total_units = int64_t(p.num_strips) * p.num_k_blocks;
   // D^T = W^T . A^T: the 128-row operand is W (MN-major), the N operand is A (K-major), N = m.
   p.idesc = make_idesc(1u, g.b_dtype == kF8E5M2 ? 1u : 0u, g.a_dtype == kF8E5M2 ? 1u : 0u, true, false, 128,
                        uint32_t(g.m));
@@ -379,9 +422,10 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   int64_t grid = DeviceSmCount();
   if (grid > kMaxCtas) grid = kMaxCtas;
   if (grid > p.total_units) grid = p.total_units;
+  const size_t smem_bytes = 1024 + size_t(stages) * stage_bytes + sizeof(SkinnyAux);
   cudaError_t e = cudaMemsetAsync(p.flags, 0, kFlagBytes, stream);
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(flags): ") + cudaGetErrorString(e));
-  skinny_gemm_kernel<<<int(grid), kThreads, kSkinnySmemBytes, stream>>>(tmap_w, tmap_a, p);
+  skinny_gemm_kernel<<<int(grid), kThreads, smem_bytes, stream>>>(tmap_w, tmap_a, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("skinny_gemm_kernel launch: ") + cudaGetErrorString(e));
   if (stats) {

@@ -58,7 +58,7 @@ class GemmBackendConfig:
     rhs_contracting_dimensions: Sequence[int] = (0,)
     epilogue: Epilogue = Epilogue.DEFAULT
     damax_output: bool = False
-    selected_algorithm: int = 0  # 0 = automatic; 1 = dense kernel; 2 = split-K kernel
+    selected_algorithm: int = 0  # 0 automatic; 1 dense; 2 split-K; 3 dense single-CTA; 4 dense CTA-pair
 
 
 class XlaFfiError(RuntimeError):
@@ -218,11 +218,12 @@ class Int8DotCall(FfiCall):
     [workspace]."""
 
     def __init__(self, operands: Sequence, results: Sequence, *, lhs_contracting_dim=1, rhs_contracting_dim=0,
-                 emit_s32=False):
+                 emit_s32=False, selected_algorithm=0):
         super().__init__(TARGET_S8, operands, results, {
             "lhs_contracting_dim": int(lhs_contracting_dim),
             "rhs_contracting_dim": int(rhs_contracting_dim),
             "emit_s32": bool(emit_s32),
+            "selected_config": int(selected_algorithm),
         })
 
 
@@ -268,7 +269,7 @@ def cublas_lt_matmul_f8(a, b, a_scale, b_scale, *, c=None, bias=None, d_scale=No
 
 
 def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=None, emit_s32=False,
-                        lhs_contracting_dim=1, rhs_contracting_dim=0):
+                        lhs_contracting_dim=1, rhs_contracting_dim=0, selected_algorithm=0):
     """s8 x s8 dot; returns (D, acc or None)."""
     torch = _torch()
     m, n = a.shape[1 - lhs_contracting_dim], b.shape[1 - rhs_contracting_dim]
@@ -281,7 +282,8 @@ def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=N
         acc = torch.empty((m, n), dtype=torch.int32, device=a.device)
         results.append(acc)
     call = Int8DotCall(operands, results, lhs_contracting_dim=lhs_contracting_dim,
-                       rhs_contracting_dim=rhs_contracting_dim, emit_s32=emit_s32)
+                       rhs_contracting_dim=rhs_contracting_dim, emit_s32=emit_s32,
+                       selected_algorithm=selected_algorithm)
     stream, dev = _current_stream_and_device(a)
     call.run(stream, dev)
     call.close()
