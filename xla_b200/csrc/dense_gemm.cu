@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "kernels.h"
@@ -84,7 +85,14 @@ struct DenseArgs {
   int32_t d_dtype;
   int32_t vec_store_ok;  // D rows start 16-byte aligned and N is a multiple of the vector width
   uint32_t* status;      // device status word (error bits)
+  unsigned long long* timing;   // optional per-CTA wait-time counters (tuning aid), else nullptr
 };
+
+// Tuning aid: per CTA, [0] cycles the MMA issuer waited for operands, [1] cycles it waited for a
+// free accumulator, [2] its total cycles, [3] cycles the producer waited for a free stage,
+// [4] the CTA's wall time in ns, [5]/[6] cycles epilogue warp 2 waited for / worked on accumulators.
+// Filled only when B200SD_TIMING=1 was set at load time.
+__device__ unsigned long long g_dense_timing[8 * 512];
 
 __device__ __forceinline__ float load_as_f32(const void* base, int32_t dtype, int64_t idx) {
   switch (dtype) {
@@ -117,105 +125,130 @@ __device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, in
   *nt = r / gsize;
 }
 
-// Converts and stores 32 consecutive columns of one row.
-__device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float (&v)[32], int64_t row, int64_t col0,
+constexpr int kChunk = 16;   // accumulator columns handled per epilogue step
+
+// Converts and stores kChunk consecutive columns of one row.
+__device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float (&v)[kChunk], int64_t row, int64_t col0,
                                                 int32_t ncols) {
   const int64_t off = row * p.n + col0;
+  const bool vec = ncols == kChunk && p.vec_store_ok;
   if (p.d_dtype == kF8E4M3FN || p.d_dtype == kF8E5M2) {
     const __nv_fp8_interpretation_t fmt = p.d_dtype == kF8E4M3FN ? __NV_E4M3 : __NV_E5M2;
     uint8_t* out = static_cast<uint8_t*>(p.d) + off;
-    if (ncols == 32 && p.vec_store_ok) {
-      uint32_t w[8];
+    uint32_t w[kChunk / 4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i], v[4 * i + 1]), __NV_SATFINITE, fmt);
-        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i + 2], v[4 * i + 3]), __NV_SATFINITE, fmt);
-        w[i] = lo | (hi << 16);
-      }
-      reinterpret_cast<uint4*>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      reinterpret_cast<uint4*>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    for (int i = 0; i < kChunk / 4; ++i) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i], v[4 * i + 1]), __NV_SATFINITE, fmt);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i + 2], v[4 * i + 3]), __NV_SATFINITE, fmt);
+      w[i] = lo | (hi << 16);
+    }
+    if (vec) {
+      *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
     } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < ncols) out[i] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, fmt);
+      for (int i = 0; i < kChunk; ++i)
+        if (i < ncols) out[i] = static_cast<uint8_t>(w[i >> 2] >> (8 * (i & 3)));
     }
   } else if (p.d_dtype == kBF16 || p.d_dtype == kF16) {
     uint16_t* out = static_cast<uint16_t*>(p.d) + off;
-    const bool bf = p.d_dtype == kBF16;
-    uint32_t w[16];
+    uint32_t w[kChunk / 2];
+    if (p.d_dtype == kBF16) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      if (bf) {
+      for (int i = 0; i < kChunk / 2; ++i) {
         const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
         w[i] = *reinterpret_cast<const uint32_t*>(&h);
-      } else {
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kChunk / 2; ++i) {
         const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
         w[i] = *reinterpret_cast<const uint32_t*>(&h);
       }
     }
-    if (ncols == 32 && p.vec_store_ok) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        reinterpret_cast<uint4*>(out)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    if (vec) {
+      reinterpret_cast<uint4*>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < ncols) out[i] = static_cast<uint16_t>(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xFFFFu);
+      for (int i = 0; i < kChunk; ++i)
+        if (i < ncols) out[i] = static_cast<uint16_t>(w[i >> 1] >> (16 * (i & 1)));
     }
   } else {  // kF32
     float* out = static_cast<float*>(p.d) + off;
-    if (ncols == 32 && p.vec_store_ok) {
+    if (vec) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < kChunk / 4; ++i)
         reinterpret_cast<float4*>(out)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
     } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < kChunk; ++i)
         if (i < ncols) out[i] = v[i];
     }
   }
 }
 
-// Epilogue arithmetic and store for one 32-column chunk of one accumulator row.
+// Epilogue arithmetic and store for kChunk columns of one accumulator row.  Every option is
+// tested once per chunk, outside the per-element loops, which keeps the unrolled code small
+// enough to stay resident in the instruction cache while eight warps run it.
 template <bool kInt8>
-__device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t (&r)[32], int64_t row, int64_t col0,
+__device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t (&r)[kChunk], int64_t row, int64_t col0,
                                              int32_t ncols, float scale, float d_scale, float row_scale,
                                              const float* bias_c, const float* colscale_c, uint32_t* amax_bits) {
-  float v[32];
+  float v[kChunk];
   if (kInt8) {
     if (p.d_s32) {
       int32_t* out = p.d_s32 + row * p.n + col0;
-      if (ncols == 32 && p.vec_store_ok) {
+      if (ncols == kChunk && p.vec_store_ok) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < kChunk / 4; ++i)
           reinterpret_cast<uint4*>(out)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < kChunk; ++i)
           if (i < ncols) out[i] = static_cast<int32_t>(r[i]);
       }
     }
     if (p.d == nullptr) return;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float x = __int2float_rn(static_cast<int32_t>(r[i]));
-      if (p.a_row_scale) x = x * row_scale;
-      if (p.b_col_scale) x = x * colscale_c[i];
-      v[i] = x;
+    for (int i = 0; i < kChunk; ++i) v[i] = __int2float_rn(static_cast<int32_t>(r[i]));
+    if (p.a_row_scale) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = v[i] * row_scale;
+    }
+    if (p.b_col_scale) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = v[i] * colscale_c[i];
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float x = __uint_as_float(r[i]) * scale;
-      if (p.c != nullptr && i < ncols) x += p.beta * load_as_f32(p.c, p.c_dtype, row * p.n + col0 + i);
-      if (p.bias) x += bias_c[i];
-      if (p.activation == kActRelu) {
-        x = (x != x) ? x : fmaxf(x, 0.0f);
-      } else if (p.activation == kActGelu) {
-        x = gelu_tanh(x);
-      }
-      if (p.amax != nullptr && i < ncols) *amax_bits = max(*amax_bits, __float_as_uint(fabsf(x)));
-      v[i] = x * d_scale;
+    for (int i = 0; i < kChunk; ++i) v[i] = __uint_as_float(r[i]) * scale;
+    if (p.c != nullptr) {
+      const int64_t off = row * p.n + col0;
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i)
+        if (i < ncols) v[i] += p.beta * load_as_f32(p.c, p.c_dtype, off + i);
+    }
+    if (p.bias) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] += bias_c[i];
+    }
+    if (p.activation == kActRelu) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = (v[i] != v[i]) ? v[i] : fmaxf(v[i], 0.0f);
+    } else if (p.activation == kActGelu) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = gelu_tanh(v[i]);
+    }
+    if (p.amax != nullptr) {
+      // Columns past N hold act(0 + 0) = 0 (zero-filled operands, zero-staged bias) and cannot raise the maximum.
+      uint32_t m = *amax_bits;
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) m = max(m, __float_as_uint(fabsf(v[i])));
+      *amax_bits = m;
+    }
+    if (d_scale != 1.0f) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] *= d_scale;
     }
   }
   store_row_chunk(p, v, row, col0, ncols);
@@ -283,7 +316,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int32_t row0 = mt * S::kTileRows + int32_t(rank) * kBM;
         const int32_t col0 = nt * kBN + (kPair ? int32_t(rank) * (kBN / 2) : 0);
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          const long long tw = p.timing ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          if (p.timing) p.timing[blockIdx.x * 8 + 3] += clock64() - tw;
           if (!ok) break;
           uint8_t* sa = smem_a + stage * kAStageBytes;
           uint8_t* sb = smem_b + stage * S::kBStageBytes;
@@ -333,6 +368,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && elect_one()) {
+      const long long t_begin = p.timing ? clock64() : 0;
+      const unsigned long long ns_begin = p.timing ? global_timer_ns() : 0;
+      long long wait_full = 0, wait_acc = 0;
       const uint32_t sbo = 1024, lbo = 16384;
       const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), lbo, sbo);
       const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), lbo, sbo);
@@ -346,12 +384,16 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+        const long long tw0 = p.timing ? clock64() : 0;
         ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+        if (p.timing) wait_acc += clock64() - tw0;
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          const long long tw1 = p.timing ? clock64() : 0;
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
+          if (p.timing) wait_full += clock64() - tw1;
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
@@ -392,6 +434,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           acc_phase ^= 1;
         }
       }
+      if (p.timing) {
+        p.timing[blockIdx.x * 8 + 0] = wait_full;
+        p.timing[blockIdx.x * 8 + 1] = wait_acc;
+        p.timing[blockIdx.x * 8 + 2] = clock64() - t_begin;
+        p.timing[blockIdx.x * 8 + 4] = global_timer_ns() - ns_begin;
+      }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
@@ -408,6 +456,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (p.d_scale) d_scale = __ldg(p.d_scale);
     }
     uint32_t amax_bits = 0;
+    long long ep_wait = 0, ep_busy = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -426,8 +475,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
       // Lane 0 does the bounded wait; the warp then agrees on the outcome so that the
       // warp-collective TMEM loads below never run with a partial warp.
+      const long long te0 = p.timing ? clock64() : 0;
       if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      const long long te1 = p.timing ? clock64() : 0;
+      ep_wait += te1 - te0;
       if (!ok) break;
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
       tc_fence_after_sync();
@@ -439,25 +491,33 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint32_t taddr =
           tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN + col_half * kColsPerEpilogueWarp);
 
-      // Four 32-column chunks; the load of the next chunk is in flight while one is processed.
-      uint32_t r0[32], r1[32];
-      tmem_ld_32x32(taddr, r0);
-#pragma unroll
-      for (int cchunk = 0; cchunk < kColsPerEpilogueWarp / 32; ++cchunk) {
-        uint32_t(&cur)[32] = (cchunk & 1) ? r1 : r0;
-        uint32_t(&nxt)[32] = (cchunk & 1) ? r0 : r1;
-        tmem_ld_wait_for(cur);
-        if (cchunk + 1 < kColsPerEpilogueWarp / 32) tmem_ld_32x32(taddr + (cchunk + 1) * 32, nxt);
-        const int64_t col0 = col_base + cchunk * 32;
+      // kChunk columns at a time, two chunks per loop trip: the load of one chunk is in flight
+      // while the other is processed.
+      uint32_t ra[kChunk], rb[kChunk];
+      tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kColsPerEpilogueWarp; c0 += 2 * kChunk) {
+        tmem_ld_wait_16(ra);
+        tmem_ld_32x16(taddr + c0 + kChunk, rb);
+        int64_t col0 = col_base + c0;
         if (col0 < p.n && row_ok) {
-          const int32_t ncols = static_cast<int32_t>(min(int64_t(32), p.n - col0));
-          finish_chunk<kInt8>(p, cur, row, col0, ncols, scale, d_scale, row_scale, bias_w + cchunk * 32,
-                              colscale_w + cchunk * 32, &amax_bits);
+          const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
+          finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
+                              &amax_bits);
+        }
+        tmem_ld_wait_16(rb);
+        if (c0 + 2 * kChunk < kColsPerEpilogueWarp) tmem_ld_32x16(taddr + c0 + 2 * kChunk, ra);
+        col0 += kChunk;
+        if (col0 < p.n && row_ok) {
+          const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
+          finish_chunk<kInt8>(p, rb, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0 + kChunk,
+                              colscale_w + c0 + kChunk, &amax_bits);
         }
       }
       // Hand the accumulator back to the MMA issuer (in the leader CTA): one arrival per warp.
       tc_fence_before_sync();
       __syncwarp();
+      if (p.timing) ep_busy += clock64() - te1;
       if (lane == 0) {
         if (kPair && rank != 0) mbar_arrive_cluster(map_to_cta(&aux->acc_empty_bar[acc], 0));
         else mbar_arrive(&aux->acc_empty_bar[acc]);
@@ -466,6 +526,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    if (p.timing && warp == 2 && lane == 0) {
+      p.timing[blockIdx.x * 8 + 5] = ep_wait;
+      p.timing[blockIdx.x * 8 + 6] = ep_busy;
     }
     if (!kInt8 && p.amax != nullptr) {
       // The bit pattern of a non-negative float orders like the float; NaN patterns sit above
@@ -582,6 +646,12 @@ uint32_t FormatCode(int32_t dtype) {
   return dtype == kF8E5M2 ? 1u : (dtype == kS8 ? 1u : 0u);
 }
 
+// Copies the tuning counters of the last dense launch on the current device (8 per CTA).
+extern "C" int b200sd_debug_read_timing(unsigned long long* out, int count) {
+  cudaDeviceSynchronize();
+  return int(cudaMemcpyFromSymbol(out, g_dense_timing, sizeof(unsigned long long) * size_t(count)));
+}
+
 int MaxPairClusters() {
   int device = 0;
   cudaGetDevice(&device);
@@ -645,6 +715,15 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   const int64_t d_elt = (g.d_dtype == kF8E4M3FN || g.d_dtype == kF8E5M2) ? 1 : (g.d_dtype == kF32 || g.d_dtype == kS32) ? 4 : 2;
   p.vec_store_ok = aligned(p.d, d_elt) && aligned(p.d_s32, 4);
   p.status = StatusWordPtr();
+  static const bool timing_on = [] {
+    const char* e = std::getenv("B200SD_TIMING");
+    return e != nullptr && e[0] == '1';
+  }();
+  p.timing = nullptr;
+  if (timing_on) {
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_dense_timing);
+    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
+  }
 
   const int64_t tiles = int64_t(p.num_m_tiles) * p.num_n_tiles;
   int grid;
