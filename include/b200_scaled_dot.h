@@ -154,6 +154,33 @@ int b200sd_device_status(uint32_t* bits, char* err, size_t err_len);
  * through the status word (value 16).  Lets a test watch a wait expire without faulting anything. */
 int b200sd_wait_probe(uint64_t limit_ns, void* cuda_stream, char* err, size_t err_len);
 
+/* Decode-shaped scaled dot that allocates nothing and needs no workspace from the caller.
+ * (No counterpart in the reference, whose cuBLASLt call always receives a workspace buffer.)
+ *
+ * For callers that cannot hand over scratch memory and are not allowed to create any: an XLA
+ * executable runs on a memory plan that was fixed when it was compiled, the runtime's allocator
+ * has usually taken nearly all of the GPU's memory already, and a handler that declares itself
+ * safe to record into a command buffer must not allocate while it runs -- so if the custom call
+ * was emitted without its trailing workspace result, the regular split-K kernel has nowhere to
+ * put its partial sums.  This variant keeps that scratch in a fixed array inside the library
+ * image: b200sd_noalloc_scratch_bytes() bytes (about 10 MiB) stay resident on every GPU that
+ * loads the library until the process exits.
+ *
+ * Same arguments as b200sd_scaled_dot_f8, of which it computes the plain case only: e4m3 A[m,k]
+ * and B[k,n] (row-major, contracting dims 1 and 0), per-tensor a_scale / b_scale, bf16 / f16 /
+ * f32 output, no c, bias, activation, amax or d_scale; `workspace` is not used and `kernel` has
+ * no effect.
+ * Limit: m <= 128; anything larger is refused with INVALID_ARGUMENT and a message naming the
+ * limit.  It calls no cudaMalloc / cudaFree nor any allocating library routine.
+ * The first call on a device looks up the array's device address (and does the one-time
+ * per-device set-up of b200sd_init_device); make that first call before capturing the stream.
+ * All calls on a device share the one array, which still holds the previous call's contents --
+ * the part that must start at zero is cleared on the stream at the start of every call -- so two
+ * calls that overlap on the same GPU (different streams) race; serialise them. */
+int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* args, void* cuda_stream, char* err,
+                                        size_t err_len);
+size_t b200sd_noalloc_scratch_bytes(void);
+
 /* ---- XLA FFI handlers (typed FFI, api_version = API_VERSION_TYPED_FFI) -----------------------
  * Signature: XLA_FFI_Error* (*)(XLA_FFI_CallFrame*), xla/ffi/api/c_api.h:517.  Declared with
  * void* here so that this header does not depend on XLA's.  Register them under the custom-call

@@ -1,0 +1,93 @@
+"""The decode entry point that allocates nothing (b200sd_scaled_dot_f8_decode_noalloc).
+
+Who needs it: a caller that has no scratch buffer to pass and may not create one.  Inside an XLA
+executable all device memory is laid out at compile time and the runtime's allocator already
+holds nearly the whole GPU, and a handler recorded into a command buffer must not allocate while
+it runs; if the custom call arrives without its workspace result, the regular split-K kernel
+cannot run.  This variant carries its scratch inside the library image instead.
+
+The test calls it through the C ABI exactly as the regular entry point is called, twice in a row
+(the second call finds the first call's partial sums and flags still in the shared array), and
+compares both results with the regular entry point's output under the tolerance the other parity
+tests use (abs 1e-2 AND rel 1e-2, the reference's own bound).  This file sorts last so that a run
+stopping at the first failure has already executed every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import scaled_dot_oracle as o
+import xla_b200
+from xla_b200 import _native
+
+pytestmark = pytest.mark.gpu
+
+
+def _args(a, b, sa, sb, d, m, n, k, workspace=None, kernel=0):
+    x = _native.ScaledDotF8Args()
+    x.struct_size = C.sizeof(x)
+    x.a, x.b = a.data_ptr(), b.data_ptr()
+    x.a_scale, x.b_scale = sa.data_ptr(), sb.data_ptr()
+    x.d = d.data_ptr()
+    if workspace is not None:
+        x.workspace, x.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    x.m, x.n, x.k = m, n, k
+    x.a_dtype = x.b_dtype = 20          # F8E4M3FN
+    x.d_dtype = 16                      # BF16
+    x.lhs_contracting_dim, x.rhs_contracting_dim = 1, 0
+    x.epilogue = 1                      # DEFAULT
+    x.alpha, x.beta = 1.0, 0.0
+    x.kernel = kernel
+    return x
+
+
+@pytest.mark.parametrize("m", [16, 128])
+def test_noalloc_decode_matches_regular_entry_point_twice(cuda_device, m):
+    dev = cuda_device
+    k, n = 4096, 3584 + 16              # uneven split over the CTAs: partial tiles and flags are in play
+    a_np, b_np, sa_np, sb_np = o.make_f8_operands(2, m, k, n)
+    a = torch.from_numpy(a_np).to(dev).view(torch.float8_e4m3fn)
+    b = torch.from_numpy(b_np).to(dev).view(torch.float8_e4m3fn)
+    sa, sb = torch.tensor(sa_np, device=dev), torch.tensor(sb_np, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    err = C.create_string_buffer(512)
+    lib = _native.product
+
+    # Reference result: the existing entry point with a caller-provided workspace.
+    d_ref = torch.zeros((m, n), dtype=torch.bfloat16, device=dev)
+    ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)
+    ref_args = _args(a, b, sa, sb, d_ref, m, n, k, workspace=ws, kernel=2)
+    assert lib.b200sd_scaled_dot_f8(C.byref(ref_args), stream, err, len(err)) == 0, err.value
+    torch.cuda.synchronize()
+    expected = d_ref.float().cpu().numpy()
+    oracle_bits, _ = o.scaled_dot_f8(a_np, b_np, sa_np, sb_np)
+    assert o.near_mismatches(o.bf16_bits_to_f32(oracle_bits), expected, 1e-2, 1e-2)[0] == 0
+
+    # Two calls in a row through the new entry point; no workspace is passed.
+    for attempt in range(2):
+        d = torch.zeros((m, n), dtype=torch.bfloat16, device=dev)
+        args = _args(a, b, sa, sb, d, m, n, k)
+        rc = lib.b200sd_scaled_dot_f8_decode_noalloc(C.byref(args), stream, err, len(err))
+        assert rc == 0, err.value
+        torch.cuda.synchronize()
+        assert xla_b200.device_status() == 0
+        got = d.float().cpu().numpy()
+        bad, max_abs, max_rel = o.near_mismatches(expected, got, 1e-2, 1e-2)
+        assert bad == 0, f"call {attempt}: {bad} mismatches (max abs {max_abs}, max rel {max_rel})"
+
+
+def test_noalloc_decode_refuses_what_its_scratch_cannot_hold(cuda_device):
+    dev = cuda_device
+    m, k, n = 256, 256, 256             # m above the 128-row limit of the built-in scratch
+    a = torch.zeros((m, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    b = torch.zeros((k, n), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    s = torch.ones((), device=dev)
+    d = torch.zeros((m, n), dtype=torch.bfloat16, device=dev)
+    err = C.create_string_buffer(512)
+    rc = _native.product.b200sd_scaled_dot_f8_decode_noalloc(C.byref(_args(a, b, s, s, d, m, n, k)),
+                                                           torch.cuda.current_stream().cuda_stream, err, len(err))
+    assert rc == 3
+    assert b"at most 128 rows" in err.value
+    assert 0 < _native.product.b200sd_noalloc_scratch_bytes() <= 16 << 20

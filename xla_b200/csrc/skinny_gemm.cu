@@ -18,8 +18,11 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
 #include <string>
 
+#include "../../include/b200_scaled_dot.h"
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -418,4 +421,123 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   return Status::Ok();
 }
 
+
+// ----------------------------------------------------------------------------- no-allocation variant
+// The split-K kernel needs scratch: per-CTA f32 partial tiles and the flags that publish them.
+// The regular entry point takes that scratch from the caller.  Some callers have none to give
+// and may not create any: an XLA executable runs on a memory plan fixed at compile time, its
+// allocator usually already owns almost all of HBM, and a handler that promises to be recordable
+// into a command buffer must not allocate while it executes.  When such a call site carries no
+// workspace result, the variant below still works: its scratch is a fixed array that is part of
+// the library image, so every GPU that loads the library holds these bytes until the process exits.
+// The array bounds what the variant accepts (m <= 128 with single-tile strips on at most
+// kMaxCtas CTAs).
+constexpr size_t kStaticPartialBytes = size_t(kMaxCtas) * 128 * kTileN * sizeof(float);   // 10 MiB
+constexpr size_t kStaticScratchBytes = kFlagBytes + kStaticPartialBytes;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+struct StaticScratchState {
+  std::once_flag once;
+  cudaError_t error = cudaSuccess;
+  unsigned char* device_ptr = nullptr;   // address of g_static_scratch on this device
+};
+StaticScratchState g_static_state[64];
+
+// `g_static_scratch` named in host code is only a handle for the runtime, not a device address;
+// the address on the current device has to be asked for, once per device.
+Status StaticScratchPtr(int device, unsigned char** ptr) {
+  if (device < 0 || device >= 64) return Status::Error(kInvalidArgument, "device ordinal out of range");
+  StaticScratchState& st = g_static_state[device];
+  std::call_once(st.once, [&] {
+    void* p = nullptr;
+    st.error = cudaGetSymbolAddress(&p, g_static_scratch);
+    st.device_ptr = static_cast<unsigned char*>(p);
+  });
+  if (st.error != cudaSuccess || st.device_ptr == nullptr)
+    return Status::Error(kInternal, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(st.error));
+  *ptr = st.device_ptr;
+  return Status::Ok();
+}
+
+}  // namespace
+
+Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointers);
+
 }  // namespace b200sd
+
+extern "C" size_t b200sd_noalloc_scratch_bytes(void) { return b200sd::kStaticScratchBytes; }
+
+extern "C" int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* args, void* cuda_stream, char* err,
+                                                   size_t err_len) {
+  using namespace b200sd;
+  auto fail = [&](int code, const std::string& msg) {
+    if (err != nullptr && err_len > 0) {
+      const size_t n = msg.size() < err_len - 1 ? msg.size() : err_len - 1;
+      std::memcpy(err, msg.data(), n);
+      err[n] = '\0';
+    }
+    return code;
+  };
+  if (args == nullptr) return fail(kInvalidArgument, "args is null");
+  GemmProblem g;
+  Status st = ValidateF8(*args, &g, /*check_pointers=*/true);
+  if (!st.ok()) return fail(st.code, st.message);
+  if (g.m > 128)
+    return fail(kInvalidArgument, "the no-allocation decode entry point accepts at most 128 rows of A (m = " +
+                                      std::to_string(g.m) + "): its built-in scratch holds one 128 x 128 f32 partial per CTA");
+  if (g.a_mn_major || !g.b_mn_major || g.a_dtype != kF8E4M3FN || g.b_dtype != kF8E4M3FN || g.c != nullptr ||
+      g.bias != nullptr || g.activation != kActNone || g.amax != nullptr || g.d_scale != nullptr ||
+      !(g.d_dtype == kBF16 || g.d_dtype == kF16 || g.d_dtype == kF32))
+    return fail(kInvalidArgument, "the no-allocation decode entry point computes the plain scaled dot only: e4m3 A[m,k] and "
+                                  "B[k,n] row-major, per-tensor scales, bf16/f16/f32 output, no bias, activation, amax or d_scale");
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail(kInternal, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  st = InitDevice(device);
+  if (!st.ok()) return fail(st.code, st.message);
+  unsigned char* scratch = nullptr;
+  st = StaticScratchPtr(device, &scratch);
+  if (!st.ok()) return fail(st.code, st.message);
+
+  CUtensorMap tmap_w, tmap_a;
+  st = MakeByteMatrixMap(&tmap_w, g.b, g.k, g.n, kTileN, kBK);
+  if (!st.ok()) return fail(st.code, st.message);
+  st = MakeByteMatrixMap(&tmap_a, g.a, g.m, g.k, kBK, uint32_t(g.m));
+  if (!st.ok()) return fail(st.code, st.message);
+
+  SkinnyArgs p{};
+  p.m = int32_t(g.m); p.n = g.n; p.k = g.k;
+  p.n_sub = 1;                                        // one 128-column tile per strip keeps a partial at m * 128 floats
+  p.a_stage_bytes = int32_t((g.m * kBK + 1023) / 1024 * 1024);
+  const size_t stage_bytes = size_t(kWBoxBytes) + p.a_stage_bytes;
+  int stages = int((kSmemBudget - 1024 - sizeof(SkinnyAux)) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  p.stages = stages;
+  p.num_strips = int32_t((g.n + kTileN - 1) / kTileN);
+  p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
+  p.total_units = int64_t(p.num_strips) * p.num_k_blocks;
+  p.idesc = make_idesc(1u, 0u, 0u, true, false, 128, uint32_t(g.m));
+  p.a_scale = g.a_scale; p.b_scale = g.b_scale; p.alpha = g.alpha;
+  p.d = g.d; p.d_dtype = g.d_dtype;
+  p.flags = reinterpret_cast<uint32_t*>(scratch);
+  p.partials = reinterpret_cast<float*>(scratch + kFlagBytes);
+  p.status = StatusWordPtr();
+
+  int64_t grid = DeviceSmCount();
+  if (grid > kMaxCtas) grid = kMaxCtas;
+  if (grid > p.total_units) grid = p.total_units;
+  if (size_t(grid) * size_t(g.m) * kTileN * sizeof(float) > kStaticPartialBytes)
+    return fail(kInvalidArgument, "problem does not fit the built-in scratch");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // The array still holds the previous call's flags; they must read zero before any CTA publishes.
+  e = cudaMemsetAsync(p.flags, 0, kFlagBytes, stream);
+  if (e != cudaSuccess) return fail(kInternal, std::string("cudaMemsetAsync(flags): ") + cudaGetErrorString(e));
+  const size_t smem_bytes = 1024 + size_t(stages) * stage_bytes + sizeof(SkinnyAux);
+  skinny_gemm_kernel<<<int(grid), kThreads, smem_bytes, stream>>>(tmap_w, tmap_a, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(kInternal, std::string("skinny_gemm_kernel launch: ") + cudaGetErrorString(e));
+  if (err != nullptr && err_len > 0) err[0] = '\0';
+  return kOk;
+}
