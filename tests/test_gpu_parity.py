@@ -164,7 +164,7 @@ def test_int8_dot_bit_exact_and_dequant(cuda_device, shape):
         assert np.array_equal(d3.cpu().numpy(), exp_acc)
 
 
-@pytest.mark.parametrize("m", [16, 64, 128])
+@pytest.mark.parametrize("m", [16, 48, 64, 128])
 def test_decode_shape_split_k_kernel(cuda_device, m):
     """BASELINE config 2's arrangement (M in {16,64,128}, K=8192) on a narrower weight matrix so
     that the oracle stays fast; uneven unit split across CTAs exercises the partial-tile fix-up."""

@@ -310,6 +310,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prod_wait = 0;
       for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         int32_t mt, nt;
         tile_coords(tile, p, &mt, &nt);
@@ -318,7 +319,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
           const long long tw = p.timing ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
-          if (p.timing) p.timing[blockIdx.x * 8 + 3] += clock64() - tw;
+          if (p.timing) prod_wait += clock64() - tw;
           if (!ok) break;
           uint8_t* sa = smem_a + stage * kAStageBytes;
           uint8_t* sb = smem_b + stage * S::kBStageBytes;
@@ -357,6 +358,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
         }
       }
+      if (p.timing) p.timing[blockIdx.x * 8 + 3] = prod_wait;
       if (!ok && !kPair) {
         // Abort path: let loads that were already issued land before the CTA's memory is released.
         for (int s = 0; s < kStages; ++s) {
@@ -591,7 +593,7 @@ cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, cons
 // A row-major [rows, cols] byte matrix viewed as a 2-D tensor with `cols` innermost; box =
 // box_cols x box_rows, 128-byte swizzle, out-of-range elements read as zero.
 Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, uint32_t box_cols,
-                         uint32_t box_rows) {
+                         uint32_t box_rows, int l2_promotion) {
   EncodeTiledFn encode = GetEncodeTiled();
   if (encode == nullptr) return Status::Error(kInternal, "cuTensorMapEncodeTiled is not available from this driver");
   if (cols % 16 != 0) return Status::Error(kInvalidArgument, "the minor dimension of an 8-bit operand must be a multiple of 16");
@@ -602,7 +604,11 @@ Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
                             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                            l2_promotion == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                            : l2_promotion == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                            : l2_promotion == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return Status::Error(kInternal, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
   return Status::Ok();
 }

@@ -6,6 +6,8 @@
 
 #include <string>
 
+struct CUtensorMap_st;   // CUtensorMap of <cuda.h>
+
 namespace b200sd {
 
 // xla::PrimitiveType numbers (mirrored by XLA_FFI_DataType, xla/ffi/api/c_api.h:233-266).
@@ -105,6 +107,11 @@ Status ReadDeviceStatus(uint32_t* bits);
 Status LaunchWaitProbe(uint64_t limit_ns, cudaStream_t stream);
 
 int DeviceSmCount();
+
+// Tensor map of a row-major [rows, cols] byte matrix, `cols` innermost; box = box_cols x box_rows bytes,
+// 128-byte swizzle, out-of-range elements read as zero.  `l2_promotion`: 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B.
+Status MakeByteMatrixMap(::CUtensorMap_st* map, const void* base, int64_t rows, int64_t cols, uint32_t box_cols,
+                         uint32_t box_rows, int l2_promotion = 3);
 
 // Device address of the current device's status word (valid after InitDevice).
 uint32_t* StatusWordPtr();

@@ -17,9 +17,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <random>
 #include <string>
 
 #include "../../include/b200_scaled_dot.h"
@@ -32,14 +34,14 @@ namespace {
 constexpr int kTileN = 128;        // weight columns per accumulator (= TMEM lanes)
 constexpr int kBK = 128;           // k per stage
 constexpr int kUmmaK = 32;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;
 constexpr int kMaxSub = 4;
 constexpr int kWBoxBytes = kBK * kTileN;     // 16 KiB per 128-column tile per stage
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;            // producer warp, MMA warp, eight epilogue warps
 constexpr int kAccBufs = 2;
 constexpr int kTmemCols = 512;
 constexpr int kMaxCtas = 160;
-constexpr size_t kFlagBytes = size_t(kMaxCtas) * 4 * sizeof(uint32_t);   // one flag per CTA per epilogue warp
+constexpr size_t kFlagBytes = size_t(kMaxCtas) * 8 * sizeof(uint64_t);   // one flag per CTA per epilogue warp
 constexpr size_t kSmemBudget = 227 * 1024;
 
 struct __align__(16) SkinnyAux {
@@ -54,7 +56,8 @@ struct __align__(16) SkinnyAux {
 struct SkinnyArgs {
   int32_t m;                 // activation rows (multiple of 16, <= 128)
   int64_t n, k;
-  int32_t n_sub;             // 128-column tiles per strip
+  int32_t n_sub;             // 128-column tiles per CTA per strip
+  int32_t group;             // CTAs that walk the same unit range side by side
   int32_t stages;
   int32_t a_stage_bytes;     // m * 128 rounded up to 1 KiB
   int32_t num_strips, num_k_blocks;
@@ -65,20 +68,27 @@ struct SkinnyArgs {
   float alpha;
   void* d;
   int32_t d_dtype;
-  uint32_t* flags;           // [grid][4], zeroed before the launch
+  uint64_t* flags;           // [grid][8]; a flag is raised by storing this launch's epoch
+  uint64_t epoch;            // unique per launch, so stale or foreign workspace contents never look raised
   float* partials;           // [grid][n_sub][m][128]
   uint32_t* status;
+  unsigned long long* timing;   // optional per-CTA wait counters (tuning aid), else nullptr
 };
+
+// Tuning aid, 8 counters per CTA: [0] cycles the MMA issuer waited for operands, [1] for a free
+// accumulator, [2] its total cycles, [3] cycles the producer waited for a free stage, [4] the CTA's
+// wall time in ns, [5] time the first operands landed, [6] cycles epilogue warp 2 was busy, [7] CTA exit time.  Filled only when B200SD_TIMING=1.
+__device__ unsigned long long g_skinny_timing[16 * 256];
 
 __device__ __forceinline__ int64_t unit_begin(int64_t cta, int64_t total, int64_t grid) { return cta * total / grid; }
 
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint64_t ld_acquire_gpu(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_release_gpu(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 __device__ __forceinline__ void store_out(const SkinnyArgs& p, int64_t idx, float x) {
@@ -103,35 +113,22 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int64_t cta = blockIdx.x, grid = gridDim.x;
-  const int64_t u_begin = unit_begin(cta, p.total_units, grid);
-  const int64_t u_end = unit_begin(cta + 1, p.total_units, grid);
+  // CTAs work in lock-step groups of `p.group`: the members of a group walk the same range of
+  // (strip, k-block) units, member j on the j-th tile set of each strip, so that at any moment they
+  // fetch neighbouring 128-byte pieces of the same rows of W (long contiguous runs for the DRAM).
+  const int64_t cta = blockIdx.x;                      // physical CTA: owns workspace slot and flags
+  const int64_t side = cta % p.group;                  // position inside the group
+  const int64_t member = cta / p.group;                // which unit range
+  const int64_t grid = gridDim.x / p.group;            // number of unit ranges
+  const int64_t u_begin = unit_begin(member, p.total_units, grid);
+  const int64_t u_end = unit_begin(member + 1, p.total_units, grid);
   const uint32_t stage_tx_bytes = uint32_t(w_stage_bytes) + uint32_t(p.m) * kBK;
   const int acc_cols = p.n_sub * p.m;            // TMEM columns of one accumulator set
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&aux->full_bar[s], 1);
-      mbar_init(&aux->empty_bar[s], 1);
-    }
-    for (int b = 0; b < kAccBufs; ++b) {
-      mbar_init(&aux->acc_full_bar[b], 1);
-      mbar_init(&aux->acc_empty_bar[b], 4);
-    }
-    aux->abort_flag = 0;
-    fence_mbar_init();
-    fence_proxy_async_smem();
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_a);
-  }
-  if (warp == 1) {
-    tmem_alloc(&aux->tmem_base, kTmemCols);
-    tmem_relinquish_alloc();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = aux->tmem_base;
+  // Eight epilogue warps split the m columns in two halves when that leaves whole 16-column
+  // chunks; otherwise four warps take all columns and the other four stay out of the way.
+  const int ep_halves = (p.m % 32 == 0) ? 2 : 1;
+  const int cols_per_warp = p.m / ep_halves;
+  if (p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 1] = global_timer_ns();
 
   // The CTA walks its unit range [u_begin, u_end) backwards, one strip-segment at a time:
   //   segment = units of one strip, [max(u_begin, strip*KB), min(u_end, (strip+1)*KB)).
@@ -140,24 +137,49 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // Starts streaming before the rest of the CTA has finished setting up: it only needs its
+    // own barriers, which it initialises itself.
+    if (lane == 0) {
+      for (int s = 0; s < p.stages; ++s) {
+        mbar_init(&aux->full_bar[s], 1);
+        mbar_init(&aux->empty_bar[s], 1);
+      }
+      for (int b = 0; b < kAccBufs; ++b) {
+        mbar_init(&aux->acc_full_bar[b], 1);
+        mbar_init(&aux->acc_empty_bar[b], 4 * ep_halves);
+      }
+      aux->abort_flag = 0;
+      fence_mbar_init();
+      fence_proxy_async_smem();
+    }
+    __syncwarp();
+    named_bar_arrive(1, kThreads);               // barriers are ready: release the other warps
     if (elect_one()) {
+      tma_prefetch_desc(&tmap_w);
+      tma_prefetch_desc(&tmap_a);
+      const uint64_t stream_once = l2_policy_evict_first();   // W passes through L2 exactly once
+      const uint64_t keep = l2_policy_evict_last();           // A is re-read by every CTA
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prod_wait = 0;
       int64_t seg_end = u_end;
       while (seg_end > u_begin && ok) {
         const int64_t strip = (seg_end - 1) / kb_per_strip;
         const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
         for (int64_t u = seg_begin; u < seg_end; ++u) {
           const int32_t kb = int32_t(u - strip * kb_per_strip);
+          const long long tw = p.timing ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          if (p.timing) prod_wait += clock64() - tw;
           if (!ok) break;
           uint64_t* full = &aux->full_bar[stage];
           mbar_arrive_expect_tx(full, stage_tx_bytes);
           uint8_t* sw = smem + stage * stage_bytes;
           for (int s = 0; s < p.n_sub; ++s)
-            tma_load_2d(sw + s * kWBoxBytes, &tmap_w, full, (int32_t(strip) * p.n_sub + s) * kTileN, kb * kBK);
-          tma_load_2d(sw + w_stage_bytes, &tmap_a, full, kb * kBK, 0);
+            tma_load_2d_hint(sw + s * kWBoxBytes, &tmap_w, full, int32_t((strip * p.group + side) * p.n_sub + s) * kTileN, kb * kBK,
+                             stream_once);
+          tma_load_2d_hint(sw + w_stage_bytes, &tmap_a, full, kb * kBK, 0, keep);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1;
@@ -165,6 +187,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         seg_end = seg_begin;
       }
+      if (p.timing) p.timing[blockIdx.x * 16 + 3] = prod_wait;
       if (!ok) {
         for (int s = 0; s < p.stages; ++s) {
           for (int i = 0; i < 100000 && !mbar_try_wait(&aux->full_bar[s], 0) && !mbar_try_wait(&aux->full_bar[s], 1); ++i) {
@@ -172,109 +195,140 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      const uint64_t w_desc0 = make_smem_desc_sw128(smem_u32(smem), 16384, 1024);                    // MN-major
-      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem + w_stage_bytes), 16, 1024);       // K-major
-      const uint32_t w_kstep = (kUmmaK * 128) >> 4;
-      const uint32_t a_kstep = kUmmaK >> 4;
-      int stage = 0;
-      uint32_t phase = 0;
+  } else {
+    if (warp == 1) {
+      tmem_alloc(&aux->tmem_base, kTmemCols);
+      tmem_relinquish_alloc();
+      tc_fence_before_sync();
+    }
+    named_bar_sync(1, kThreads);                 // barriers initialised (warp 0) and TMEM allocated (warp 1)
+    tc_fence_after_sync();
+    const uint32_t tmem_base = aux->tmem_base;
+
+    if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (elect_one()) {
+        const uint64_t w_desc0 = make_smem_desc_sw128(smem_u32(smem), 16384, 1024);                    // MN-major
+        const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem + w_stage_bytes), 16, 1024);       // K-major
+        const uint32_t w_kstep = (kUmmaK * 128) >> 4;
+        const uint32_t a_kstep = kUmmaK >> 4;
+        const long long t_begin = p.timing ? clock64() : 0;
+        const unsigned long long ns_begin = p.timing ? global_timer_ns() : 0;
+        long long wait_full = 0, wait_acc = 0;
+        unsigned long long first_data_ns = 0;
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        int64_t seg_end = u_end;
+        while (seg_end > u_begin && ok) {
+          const int64_t strip = (seg_end - 1) / kb_per_strip;
+          const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
+          const long long tw0 = p.timing ? clock64() : 0;
+          ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+          if (p.timing) wait_acc += clock64() - tw0;
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + acc * acc_cols;
+          for (int64_t u = seg_begin; u < seg_end; ++u) {
+            const long long tw1 = p.timing ? clock64() : 0;
+            ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
+            if (p.timing) {
+              wait_full += clock64() - tw1;
+              if (first_data_ns == 0) first_data_ns = global_timer_ns();   // first operands have landed
+            }
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint64_t stage_off = uint64_t((stage * stage_bytes) >> 4);
+            for (int s = 0; s < p.n_sub; ++s) {
+              const uint64_t w_desc = w_desc0 + stage_off + uint64_t((s * kWBoxBytes) >> 4);
+#pragma unroll
+              for (int j = 0; j < kBK / kUmmaK; ++j) {
+                umma_f8(d_tmem + s * p.m, w_desc + uint64_t(j * w_kstep), a_desc0 + stage_off + uint64_t(j * a_kstep),
+                        p.idesc, (u > seg_begin || j > 0) ? 1u : 0u);
+              }
+            }
+            umma_commit(&aux->empty_bar[stage]);
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (!ok) break;
+          umma_commit(&aux->acc_full_bar[acc]);
+          if (++acc == kAccBufs) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+          seg_end = seg_begin;
+        }
+        if (p.timing) {
+          p.timing[blockIdx.x * 16 + 0] = wait_full;
+          p.timing[blockIdx.x * 16 + 5] = first_data_ns;
+          p.timing[blockIdx.x * 16 + 8] = wait_acc;
+          p.timing[blockIdx.x * 16 + 2] = clock64() - t_begin;
+          p.timing[blockIdx.x * 16 + 4] = global_timer_ns() - ns_begin;
+        }
+      }
+    } else if ((warp - 2) / 4 < ep_halves) {
+      // ------------------------------------------------------------------ epilogue (warps 2..9)
+      const int q = warp & 3;                    // TMEM lane quarter
+      const int half = (warp - 2) >> 2;          // which half of the m columns
+      const int fq = half * 4 + q;               // flag / partial ownership index within a CTA
+      const int col_lo = half * cols_per_warp;
+      float scale = p.alpha;
+      if (p.a_scale) scale *= __ldg(p.a_scale);
+      if (p.b_scale) scale *= __ldg(p.b_scale);
+      const uint64_t keep = l2_policy_evict_last();            // partial tiles should still be in L2 when they are summed
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      long long ep_accwait = 0, ep_flagwait = 0, ep_busy = 0;
       int64_t seg_end = u_end;
-      while (seg_end > u_begin && ok) {
+      while (seg_end > u_begin) {
         const int64_t strip = (seg_end - 1) / kb_per_strip;
-        const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
-        ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * acc_cols;
-        for (int64_t u = seg_begin; u < seg_end; ++u) {
-          ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint64_t stage_off = uint64_t((stage * stage_bytes) >> 4);
-          for (int s = 0; s < p.n_sub; ++s) {
-            const uint64_t w_desc = w_desc0 + stage_off + uint64_t((s * kWBoxBytes) >> 4);
+        const int64_t strip_first = strip * kb_per_strip;
+        const int64_t seg_begin = max(u_begin, strip_first);
+        const bool owns_tail = seg_end == strip_first + kb_per_strip;   // holds the strip's last k-block
+        const bool owns_head = seg_begin == strip_first;
+
+        const int nl = q * 32 + lane;                          // lane of the accumulator = column within a tile
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * acc_cols);
+        const int64_t slot_floats = int64_t(p.n_sub) * p.m * kTileN;
+        const int chunks_per_sub = cols_per_warp / 16;
+        const int nchunks = p.n_sub * chunks_per_sub;
+        const bool finisher = owns_tail && !owns_head;       // must add other CTAs' partial sums
+        int64_t first_contrib = member;                      // lowest unit range that contributed to this strip
+        float pre0[16], pre1[16], pre2[16], pre3[16];        // other CTAs' partial sums, fetched four chunks ahead
+
+        // Sum of the lower-numbered CTAs' partials for chunk `ci` (requested early, consumed later).
+        auto load_partials = [&](int ci, float (&pre)[16]) {
+          const int s = ci / chunks_per_sub, c0 = col_lo + (ci % chunks_per_sub) * 16;
+          const float* slot =
+              p.partials + (first_contrib * p.group + side) * slot_floats + (int64_t(s) * p.m + c0) * kTileN + nl;
 #pragma unroll
-            for (int j = 0; j < kBK / kUmmaK; ++j) {
-              umma_f8(d_tmem + s * p.m, w_desc + uint64_t(j * w_kstep), a_desc0 + stage_off + uint64_t(j * a_kstep),
-                      p.idesc, (u > seg_begin || j > 0) ? 1u : 0u);
-            }
-          }
-          umma_commit(&aux->empty_bar[stage]);
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-        if (!ok) break;
-        umma_commit(&aux->acc_full_bar[acc]);
-        if (++acc == kAccBufs) {
-          acc = 0;
-          acc_phase ^= 1;
-        }
-        seg_end = seg_begin;
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;
-    float scale = p.alpha;
-    if (p.a_scale) scale *= __ldg(p.a_scale);
-    if (p.b_scale) scale *= __ldg(p.b_scale);
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    int64_t seg_end = u_end;
-    while (seg_end > u_begin) {
-      const int64_t strip = (seg_end - 1) / kb_per_strip;
-      const int64_t strip_first = strip * kb_per_strip;
-      const int64_t seg_begin = max(u_begin, strip_first);
-      const bool owns_tail = seg_end == strip_first + kb_per_strip;   // holds the strip's last k-block
-      const bool owns_head = seg_begin == strip_first;
-
-      if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);
-      tc_fence_after_sync();
-
-      const int nl = q * 32 + lane;                          // lane of the accumulator = column within a tile
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * acc_cols);
-      const int64_t slot_floats = int64_t(p.n_sub) * p.m * kTileN;
-
-      if (!owns_tail) {
-        // Partial piece: park it in this CTA's workspace slot and publish.
-        float* slot = p.partials + cta * slot_floats;
-        for (int s = 0; s < p.n_sub; ++s) {
-#pragma unroll 1
-          for (int c0 = 0; c0 < p.m; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld_32x16(taddr + s * p.m + c0, r);
-            tmem_ld_wait_16(r);
+          for (int i = 0; i < 16; ++i) pre[i] = __ldcg(slot + i * kTileN);
+          for (int64_t c = first_contrib + 1; c < member; ++c) {
+            slot += p.group * slot_floats;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) __stcg(slot + (int64_t(s) * p.m + c0 + i) * kTileN + nl, __uint_as_float(r[i]));
+            for (int i = 0; i < 16; ++i) pre[i] += __ldcg(slot + i * kTileN);
           }
-        }
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) st_release_gpu(p.flags + cta * 4 + q, 1u);
-      } else {
-        // Finishing piece.  Wait for the CTAs that hold the earlier k-blocks of this strip.
-        int64_t first_contrib = cta;   // lowest CTA index that contributed to this strip
-        if (!owns_head) {
-          first_contrib = cta - 1;
+        };
+
+        if (finisher) {
+          // The CTAs holding the earlier k-blocks of this strip finished their piece long ago (it was
+          // the first thing they did).  Their flags and partials are fetched now, while this CTA's own
+          // MMAs for the strip are still running, so that nothing but arithmetic is left for the end.
+          first_contrib = member - 1;
           while (unit_begin(first_contrib, p.total_units, grid) > strip_first) --first_contrib;
+          const long long tf0 = p.timing ? clock64() : 0;
           if (lane == 0) {
-            for (int64_t c = cta - 1; c >= first_contrib && ok; --c) {
-              const uint32_t* f = p.flags + c * 4 + q;
+            for (int64_t c = member - 1; c >= first_contrib && ok; --c) {
+              const uint64_t* f = p.flags + (c * p.group + side) * 8 + fq;
               uint64_t t0 = 0;
               uint32_t polls = 0;
-              while (ld_acquire_gpu(f) == 0u) {
+              while (ld_acquire_gpu(f) != p.epoch) {
                 if ((++polls & 1023u) == 0) {
                   const uint64_t now = global_timer_ns();
                   if (t0 == 0) t0 = now;
@@ -289,49 +343,122 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
           }
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (p.timing) ep_flagwait += clock64() - tf0;
           if (!ok) break;
-          __syncwarp();
-          __threadfence();
+          // Every lane acquires the (already raised) flags itself before it reads the partials.
+          for (int64_t c = member - 1; c >= first_contrib; --c)
+            (void)ld_acquire_gpu(p.flags + (c * p.group + side) * 8 + fq);
+          load_partials(0, pre0);
+          if (nchunks > 1) load_partials(1, pre1);
+          if (nchunks > 2) load_partials(2, pre2);
+          if (nchunks > 3) load_partials(3, pre3);
         }
-        for (int s = 0; s < p.n_sub; ++s) {
-          const int64_t col = (strip * p.n_sub + s) * kTileN + nl;
+
+        const long long te0 = p.timing ? clock64() : 0;
+        if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);
+        tc_fence_after_sync();
+        const long long te1 = p.timing ? clock64() : 0;
+        ep_accwait += te1 - te0;
+
+        if (!owns_tail) {
+          // Partial piece: park it in this CTA's workspace slot and publish.
+          float* slot = p.partials + cta * slot_floats;
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + col_lo, r);
 #pragma unroll 1
-          for (int c0 = 0; c0 < p.m; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld_32x16(taddr + s * p.m + c0, r);
+          for (int ci = 0; ci < nchunks; ++ci) {
+            const int s = ci / chunks_per_sub, c0 = col_lo + (ci % chunks_per_sub) * 16;
+            float* out = slot + (int64_t(s) * p.m + c0) * kTileN + nl;
             tmem_ld_wait_16(r);
             float v[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-            for (int64_t c = first_contrib; c < cta; ++c) {
-              const float* slot = p.partials + c * slot_floats;
+            if (ci + 1 < nchunks) {
+              const int s1 = (ci + 1) / chunks_per_sub, c1 = col_lo + ((ci + 1) % chunks_per_sub) * 16;
+              tmem_ld_32x16(taddr + s1 * p.m + c1, r);
+            }
 #pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] += __ldcg(slot + (int64_t(s) * p.m + c0 + i) * kTileN + nl);
+            for (int i = 0; i < 16; ++i) st_global_f32_hint(out + i * kTileN, v[i], keep);
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) st_release_gpu(p.flags + cta * 8 + fq, p.epoch);
+        } else {
+          // Finishing piece: accumulator (+ the other CTAs' partials) -> scale -> cast -> D.
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + col_lo, r);
+          auto finish_chunk = [&](int ci, float (&pre)[16]) {
+            const int s = ci / chunks_per_sub, c0 = col_lo + (ci % chunks_per_sub) * 16;
+            const int64_t col = ((strip * p.group + side) * p.n_sub + s) * kTileN + nl;
+            float v[16];
+            if (finisher) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = pre[i];
+              if (ci + 4 < nchunks) load_partials(ci + 4, pre);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+            }
+            tmem_ld_wait_16(r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = (v[i] + __uint_as_float(r[i])) * scale;
+            if (ci + 1 < nchunks) {
+              const int s1 = (ci + 1) / chunks_per_sub, c1 = col_lo + ((ci + 1) % chunks_per_sub) * 16;
+              tmem_ld_32x16(taddr + s1 * p.m + c1, r);
             }
             if (col < p.n) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) store_out(p, int64_t(c0 + i) * p.n + col, v[i] * scale);
+              for (int i = 0; i < 16; ++i) store_out(p, int64_t(c0 + i) * p.n + col, v[i]);
             }
+          };
+#pragma unroll 1
+          for (int ci = 0; ci < nchunks; ci += 4) {
+            finish_chunk(ci, pre0);
+            if (ci + 1 < nchunks) finish_chunk(ci + 1, pre1);
+            if (ci + 2 < nchunks) finish_chunk(ci + 2, pre2);
+            if (ci + 3 < nchunks) finish_chunk(ci + 3, pre3);
           }
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (p.timing) ep_busy += clock64() - te1;
+        if (lane == 0) mbar_arrive(&aux->acc_empty_bar[acc]);
+        if (++acc == kAccBufs) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        seg_end = seg_begin;
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&aux->acc_empty_bar[acc]);
-      if (++acc == kAccBufs) {
-        acc = 0;
-        acc_phase ^= 1;
+      if (p.timing && warp == 2 && lane == 0) {
+        p.timing[blockIdx.x * 16 + 6] = ep_busy;
+        p.timing[blockIdx.x * 16 + 9] = ep_flagwait;
+        p.timing[blockIdx.x * 16 + 10] = ep_accwait;
       }
-      seg_end = seg_begin;
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 7] = global_timer_ns();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(aux->tmem_base, kTmemCols);
   }
+}
+
+// A 64-bit value no earlier launch of this process has used and that arbitrary memory contents will
+// not equal by accident: a per-process random tag in the high half, a launch counter in the low half.
+uint64_t NextEpoch() {
+  static const uint64_t tag = [] {
+    std::random_device rd;
+    uint64_t t = (uint64_t(rd()) << 32) ^ uint64_t(rd());
+    return (t | (1ull << 63)) & 0xFFFFFFFF00000000ull;
+  }();
+  static std::atomic<uint64_t> counter{1};
+  return tag | (counter.fetch_add(1, std::memory_order_relaxed) & 0xFFFFFFFFull);
 }
 
 // Strip width: as wide as the two accumulator sets allow (2 * n_sub * m <= 512 TMEM columns).
@@ -340,7 +467,7 @@ int StripTiles(int64_t m) {
     const char* e = std::getenv("B200SD_SKINNY_NSUB");   // tuning override: 1, 2 or 4
     return e ? std::atoi(e) : 0;
   }();
-  int n_sub = m <= 64 ? 4 : 2;
+  int n_sub = 1;   // measured fastest: wider strips lengthen the exposed last epilogue more than they help DRAM
   if (forced == 1 || forced == 2 || forced == 4) n_sub = forced;
   while (2 * n_sub * m > kTmemCols) n_sub >>= 1;
   return n_sub;
@@ -348,14 +475,16 @@ int StripTiles(int64_t m) {
 
 }  // namespace
 
-Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, uint32_t box_cols,
-                         uint32_t box_rows);
-
 Status InitSkinnyKernels() {
   cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        int(kSmemBudget));
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(skinny): ") + cudaGetErrorString(e));
   return Status::Ok();
+}
+
+extern "C" int b200sd_debug_read_skinny_timing(unsigned long long* out, int count) {
+  cudaDeviceSynchronize();
+  return int(cudaMemcpyFromSymbol(out, g_skinny_timing, sizeof(unsigned long long) * size_t(count)));
 }
 
 size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k) {
@@ -376,8 +505,11 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   if ((reinterpret_cast<uintptr_t>(g.workspace) & 15) != 0)
     return Status::Error(kInvalidArgument, "split-K kernel: workspace must be 16-byte aligned");
 
+  static const int env_promo = [] { const char* e = std::getenv("B200SD_SKINNY_PROMO"); return e ? std::atoi(e) : 3; }();
+  static const int env_stages = [] { const char* e = std::getenv("B200SD_SKINNY_STAGES"); return e ? std::atoi(e) : 0; }();
+  static const bool timing_on = [] { const char* e = std::getenv("B200SD_TIMING"); return e != nullptr && e[0] == '1'; }();
   CUtensorMap tmap_w, tmap_a;
-  st = MakeByteMatrixMap(&tmap_w, g.b, g.k, g.n, kTileN, kBK);            // W [k, n]: box 128(n) x 128(k)
+  st = MakeByteMatrixMap(&tmap_w, g.b, g.k, g.n, kTileN, kBK, env_promo);  // W [k, n]: box 128(n) x 128(k)
   if (!st.ok()) return st;
   st = MakeByteMatrixMap(&tmap_a, g.a, g.m, g.k, kBK, uint32_t(g.m));     // A [m, k]: box 128(k) x m
   if (!st.ok()) return st;
@@ -389,9 +521,12 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   const size_t stage_bytes = size_t(p.n_sub) * kWBoxBytes + p.a_stage_bytes;
   int stages = int((kSmemBudget - 1024 - sizeof(SkinnyAux)) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
+  if (env_stages >= 2 && env_stages < stages) stages = env_stages;
   if (stages < 2) return Status::Error(kInternal, "split-K kernel: not enough shared memory for two stages");
   p.stages = stages;
-  const int64_t strip_cols = int64_t(p.n_sub) * kTileN;
+  static const int env_group = [] { const char* e = std::getenv("B200SD_SKINNY_GROUP"); return e ? std::atoi(e) : 2; }();
+  p.group = (env_group == 1 || env_group == 2 || env_group == 4) ? env_group : 2;
+  const int64_t strip_cols = int64_t(p.n_sub) * p.group * kTileN;
   p.num_strips = int32_t((g.n + strip_cols - 1) / strip_cols);
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
   p.total_units = int64_t(p.num_strips) * p.num_k_blocks;
@@ -400,18 +535,23 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
                        uint32_t(g.m));
   p.a_scale = g.a_scale; p.b_scale = g.b_scale; p.alpha = g.alpha;
   p.d = g.d; p.d_dtype = g.d_dtype;
-  p.flags = static_cast<uint32_t*>(g.workspace);
+  p.flags = static_cast<uint64_t*>(g.workspace);
+  p.epoch = NextEpoch();
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + kFlagBytes);
   p.status = StatusWordPtr();
+  p.timing = nullptr;
+  if (timing_on) {
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_skinny_timing);
+    cudaMemsetAsync(p.timing, 0, sizeof(g_skinny_timing), stream);
+  }
 
   int64_t grid = DeviceSmCount();
   if (grid > kMaxCtas) grid = kMaxCtas;
-  if (grid > p.total_units) grid = p.total_units;
+  if (grid > p.total_units * p.group) grid = p.total_units * p.group;
+  grid -= grid % p.group;
   const size_t smem_bytes = 1024 + size_t(stages) * stage_bytes + sizeof(SkinnyAux);
-  cudaError_t e = cudaMemsetAsync(p.flags, 0, kFlagBytes, stream);
-  if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(flags): ") + cudaGetErrorString(e));
   skinny_gemm_kernel<<<int(grid), kThreads, smem_bytes, stream>>>(tmap_w, tmap_a, p);
-  e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("skinny_gemm_kernel launch: ") + cudaGetErrorString(e));
   if (stats) {
     stats->kernel = kKernelSkinny;
@@ -510,6 +650,7 @@ extern "C" int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* arg
   SkinnyArgs p{};
   p.m = int32_t(g.m); p.n = g.n; p.k = g.k;
   p.n_sub = 1;                                        // one 128-column tile per strip keeps a partial at m * 128 floats
+  p.group = 1;
   p.a_stage_bytes = int32_t((g.m * kBK + 1023) / 1024 * 1024);
   const size_t stage_bytes = size_t(kWBoxBytes) + p.a_stage_bytes;
   int stages = int((kSmemBudget - 1024 - sizeof(SkinnyAux)) / stage_bytes);
@@ -521,7 +662,8 @@ extern "C" int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* arg
   p.idesc = make_idesc(1u, 0u, 0u, true, false, 128, uint32_t(g.m));
   p.a_scale = g.a_scale; p.b_scale = g.b_scale; p.alpha = g.alpha;
   p.d = g.d; p.d_dtype = g.d_dtype;
-  p.flags = reinterpret_cast<uint32_t*>(scratch);
+  p.flags = reinterpret_cast<uint64_t*>(scratch);
+  p.epoch = NextEpoch();
   p.partials = reinterpret_cast<float*>(scratch + kFlagBytes);
   p.status = StatusWordPtr();
 
