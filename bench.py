@@ -355,7 +355,11 @@ def gpu_arm(args):
                 "peak_source": f"2 x MEASURED_PEAKS bf16_tflops burst ({peaks['source']}); 8-bit tensor rate is twice bf16",
                 "frac_of_nominal_4500": flops / world / ms / 1e9 / 4500.0}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = None
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+    # (single GPU, default sizes only; bytes).
+    measured_traffic = {("c1", 8192, 8192, 8192): 396.0e6, ("c2", 64, 28672, 8192): 240.2e6,
+                        ("c3", 4096, 4096, 4096): 33.8e6}
+    roof["traffic"] = measured_traffic.get((kind, m, n, k)) if world == 1 else None
     roof["kernel"] = {"c2": "skinny_gemm_kernel", "c3": "dense_gemm_kernel<int8>"}.get(kind, "dense_gemm_kernel<fp8>")
     line = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,

@@ -697,7 +697,8 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   p.num_m_tiles = int32_t((g.m + tile_rows - 1) / tile_rows);
   p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
-  p.raster_group = pair ? 8 : 16;
+  static const int env_raster = [] { const char* e = std::getenv("B200SD_RASTER"); return e ? std::atoi(e) : 0; }();
+  p.raster_group = env_raster > 0 ? env_raster : 16;   // B200SD_RASTER: tuning override (16 measured best at 8192^3)
   p.a_mn_major = g.a_mn_major; p.b_mn_major = g.b_mn_major;
   p.idesc = make_idesc(g.int8 ? 2u : 1u, FormatCode(g.a_dtype), FormatCode(g.b_dtype), g.a_mn_major, g.b_mn_major,
                        uint32_t(tile_rows), kBN);
