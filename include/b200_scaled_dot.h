@@ -181,6 +181,18 @@ int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* args, void* cu
                                         size_t err_len);
 size_t b200sd_noalloc_scratch_bytes(void);
 
+/* Rewriter-lite: applies GemmRewriter's decisions for this path
+ * (xla/backends/gpu/transforms/gemm_rewriter.cc:190-336 MatchFp8Param, :1235-1591 CreateF8CustomCall,
+ * :1829-2249 bias / ReLU / GELU fusion, :1635-1794 FP8 output cast and amax, :2774-2892 workspace) to an
+ * HLO module given as text, over the subset of HLO the fixtures under tests/golden/hlo use, and emits
+ * the custom calls "b200$scaled_dot$f8" / "b200$dot$s8" where the reference would emit
+ * "__cublas$lt$matmul$f8" / "__cublas$lt$matmul".  `out_hlo` receives the rewritten module text,
+ * `plan_json` a description of the custom call (operand sources in terms of the module's parameters,
+ * results, attributes).  Returns 0 when the text was understood (plan_json says whether anything was
+ * rewritten and, if not, why), 3 for unparsable text, 8 when a buffer is too small. */
+int b200sd_rewrite_hlo(const char* hlo_text, char* out_hlo, size_t out_hlo_len, char* plan_json,
+                       size_t plan_json_len, char* err, size_t err_len);
+
 /* ---- XLA FFI handlers (typed FFI, api_version = API_VERSION_TYPED_FFI) -----------------------
  * Signature: XLA_FFI_Error* (*)(XLA_FFI_CallFrame*), xla/ffi/api/c_api.h:517.  Declared with
  * void* here so that this header does not depend on XLA's.  Register them under the custom-call

@@ -1,0 +1,97 @@
+"""The same HLO text drives the CPU interpreter and, through the rewriter-lite and the FFI
+boundary, the CUDA kernels; the results must agree under the reference's tolerances."""
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hlo_eval
+from oracle import scaled_dot_oracle as o
+from xla_b200 import hlo_runner
+
+pytestmark = pytest.mark.gpu
+HLO_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "hlo")
+_TORCH = {"f8e4m3fn": torch.float8_e4m3fn, "f8e5m2": torch.float8_e5m2, "bf16": torch.bfloat16}
+
+
+def load(name, shrink=None):
+    text = open(os.path.join(HLO_DIR, name + ".hlo")).read()
+    for old, new in (shrink or {}).items():
+        text = re.sub(rf"\b{old}\b", str(new), text)
+    return text
+
+
+def to_dev(v, kind, dev):
+    t = torch.from_numpy(np.ascontiguousarray(v)).to(dev)
+    if kind in ("f8e4m3fn", "f8e5m2"):
+        return t.view(_TORCH[kind])
+    if kind == "bf16":
+        return t.view(torch.int16).view(torch.bfloat16)
+    return t
+
+
+def back(t):
+    if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return t.view(torch.uint8).cpu().numpy()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def test_config0_module(cuda_device):
+    text = load("c0_scaled_dot_f8")
+    a, b, sa, sb = o.make_f8_operands(0, 256, 512, 256)
+    exp = hlo_eval.evaluate(text, [a, b, np.float32(sa), np.float32(sb)])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert o.near_mismatches(o.bf16_bits_to_f32(exp), o.bf16_bits_to_f32(back(got)), 1e-2, 1e-2)[0] == 0
+
+
+def test_config1_module_reduced(cuda_device):
+    text = load("c1_fp8_linear_gelu_amax", {"8192": 512})
+    a, b, sa, sb = o.make_f8_operands(1, 512, 512, 512)
+    bias = o.make_bias_bf16(1, 512)
+    out_scale = np.float32(0.5)
+    exp_d, exp_amax = hlo_eval.evaluate(text, [a, b, np.float32(sa), np.float32(sb), bias, out_scale])
+    d, amax = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                               torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device),
+                                               to_dev(bias, "bf16", cuda_device), torch.tensor(out_scale, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert o.fp8_within_n_values(exp_d, back(d), 1) == 0
+    assert float(amax.item()) == pytest.approx(float(exp_amax), rel=1e-3)
+
+
+def test_config3_module_reduced(cuda_device):
+    text = load("c3_int8_dequant", {"4096": 256})
+    a, b, rs, cs = o.make_s8_operands(3, 256, 256, 256)
+    exp = hlo_eval.evaluate(text, [a, b, rs, cs])
+    got = hlo_runner.run_hlo_module(text, [torch.from_numpy(x).to(cuda_device) for x in (a, b, rs, cs)])
+    torch.cuda.synchronize()
+    assert np.array_equal(back(got), exp)                      # integer path: bit-exact, also after the dequantisation
+
+
+def test_divide_scales_e5m2_bias_relu_and_matrix_bias_modules(cuda_device):
+    rng = np.random.default_rng(5)
+    text = load("scaled_ab_divide_bias_relu_e5m2")
+    a = o.fp8_encode(rng.standard_normal((64, 128), dtype=np.float32) * 8, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((96, 128), dtype=np.float32) * 8, "e5m2")
+    sa, sb = np.float32(4.0), np.float32(0.5)
+    bias = o.f32_to_bf16_bits(rng.standard_normal(96, dtype=np.float32))
+    exp = hlo_eval.evaluate(text, [a, b, sa, sb, bias])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e5m2", cuda_device),
+                                           torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device),
+                                           to_dev(bias, "bf16", cuda_device)])
+    torch.cuda.synchronize()
+    assert o.near_mismatches(o.bf16_bits_to_f32(exp), o.bf16_bits_to_f32(back(got)), 1e-2, 1e-2)[0] == 0
+    text = load("unscaled_matrix_bias_f32")
+    a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 80), dtype=np.float32), "e4m3fn")
+    c = rng.standard_normal((48, 80), dtype=np.float32)
+    exp = hlo_eval.evaluate(text, [a, b, c])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           torch.from_numpy(c).to(cuda_device)])
+    torch.cuda.synchronize()
+    assert o.near_mismatches(exp, back(got), 1e-2, 1e-2)[0] == 0

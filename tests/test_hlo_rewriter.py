@@ -1,0 +1,116 @@
+"""Rewriter-lite and the fixture HLO modules (host only).
+
+The assertions on the emitted custom call play the part of the FileCheck patterns in
+xla/backends/gpu/transforms/gemm_rewriter_fp8_test.cc (operands, result tuple, backend_config);
+the mini interpreter is checked against the scaled-dot oracle on the same modules.
+"""
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import hlo_eval
+from oracle import scaled_dot_oracle as o
+from xla_b200 import hlo_runner
+from xla_b200.scaled_dot import XlaFfiError
+
+HLO_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "hlo")
+
+
+def load(name, shrink=None):
+    text = open(os.path.join(HLO_DIR, name + ".hlo")).read()
+    for old, new in (shrink or {}).items():
+        text = re.sub(rf"\b{old}\b", str(new), text)
+    return text
+
+
+def roles(plan):
+    return [s["role"] for s in plan["operands"]]
+
+
+def test_config0_lowering():
+    hlo, plan = hlo_runner.rewrite(load("c0_scaled_dot_f8"))
+    assert plan["rewritten"] and plan["target"] == "b200$scaled_dot$f8"
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale"]
+    assert (plan["m"], plan["k"], plan["n"]) == (256, 512, 256)
+    assert plan["attrs"]["epilogue"] == 1 and plan["attrs"]["lhs_contracting_dim"] == 1 and plan["attrs"]["rhs_contracting_dim"] == 0
+    assert [r["role"] for r in plan["results"]] == ["d", "workspace"]
+    assert plan["results"][0]["dtype"] == 16
+    # No transposes on Blackwell (gemm_rewriter.cc:1535-1554): operands are the parameters themselves.
+    assert re.search(r"custom-call\(a, b, a_scale, b_scale\), custom_call_target=\"b200\$scaled_dot\$f8\"", hlo)
+    assert "(bf16[256,256], s8[33554432])" in hlo and "api_version=API_VERSION_TYPED_FFI" in hlo
+
+
+def test_config1_lowering_matches_the_expected_custom_call():
+    """bias + GELU + scaled e4m3 output + amax: operands a, b, a_scale, b_scale, bias, 1/out_scale;
+    results (f8e4m3fn, f32[], workspace); epilogue BIAS_GELU, damax_output (thunk_emitter.cc:776-862)."""
+    hlo, plan = hlo_runner.rewrite(load("c1_fp8_linear_gelu_amax"))
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias", "d_scale"]
+    d_scale = plan["operands"][-1]
+    assert d_scale["param"] == 5 and d_scale["reciprocal"]          # the HLO divides by out_scale
+    assert plan["operands"][4]["dtype"] == 16                        # the bf16 value feeding the convert
+    assert plan["attrs"]["epilogue"] == 7 and plan["attrs"]["damax_output"] is True
+    assert [r["role"] for r in plan["results"]] == ["d", "amax", "workspace"]
+    assert plan["results"][0]["dtype"] == 20 and plan["results"][0]["root_index"] == 0 and plan["results"][1]["root_index"] == 1
+    assert "(f8e4m3fn[8192,8192], f32[], s8[33554432]) custom-call(a, b, a_scale, b_scale, bias, d_scale_inv)" in hlo
+    assert "tanh" not in hlo and "clamp" not in hlo and "reduce" not in hlo     # everything was folded
+
+
+def test_int8_lowering_folds_the_dequantisation():
+    hlo, plan = hlo_runner.rewrite(load("c3_int8_dequant"))
+    assert plan["target"] == "b200$dot$s8"
+    assert roles(plan) == ["a", "b", "a_row_scale", "b_col_scale"]
+    assert plan["results"][0]["dtype"] == 16
+    assert "custom-call(a, b, a_scale, b_scale), custom_call_target=\"b200$dot$s8\"" in hlo
+
+
+def test_divide_scales_e5m2_bias_relu_and_matrix_bias():
+    _, plan = hlo_runner.rewrite(load("scaled_ab_divide_bias_relu_e5m2"))
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"]
+    assert plan["operands"][2]["reciprocal"] and plan["operands"][3]["reciprocal"]
+    assert plan["operands"][1]["dtype"] == 19 and plan["attrs"]["rhs_contracting_dim"] == 1
+    assert plan["attrs"]["epilogue"] == 4                            # BIAS_RELU
+    assert plan["results"][0]["dtype"] == 16                         # the final convert became the output type
+    _, plan = hlo_runner.rewrite(load("unscaled_matrix_bias_f32"))
+    assert roles(plan) == ["a", "b", "c", "a_scale", "b_scale"]      # c at operand index 2 (gemm_rewriter.cc:1829-1978)
+    assert plan["attrs"]["beta"] == 1.0
+    assert plan["operands"][3]["param"] == -1 and plan["operands"][3]["constant"] == 1.0
+
+
+def test_modules_that_must_be_left_alone():
+    hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
+    assert not plan["rewritten"] and "e5m2" in plan["reason"]
+    assert "custom-call" not in hlo
+    f32_dot = load("c0_scaled_dot_f8").replace("f8e4m3fn", "f32")
+    assert not hlo_runner.rewrite(f32_dot)[1]["rewritten"]
+    ragged = load("c0_scaled_dot_f8", {"256": 250})
+    assert "multiples of 16" in hlo_runner.rewrite(ragged)[1]["reason"]
+    # The GELU pre-activation has another user: would need the AUX epilogue, so GELU is not folded
+    # and the output then depends on a value the custom call does not produce.
+    aux = load("c1_fp8_linear_gelu_amax", {"8192": 64}).replace("tuple(d, amax)", "tuple(d, x)").replace(
+        "(f8e4m3fn[64,64], f32[]) tuple", "(f8e4m3fn[64,64], f32[64,64]) tuple")
+    assert not hlo_runner.rewrite(aux)[1]["rewritten"]
+    with pytest.raises(XlaFfiError) as e:
+        hlo_runner.rewrite("HloModule broken\nENTRY main {\n  x = oops\n}\n")
+    assert e.value.code == 3
+
+
+def test_interpreter_agrees_with_the_scaled_dot_oracle():
+    m = k = n = 64
+    text = load("c1_fp8_linear_gelu_amax", {"8192": 64})
+    a, b, sa, sb = o.make_f8_operands(1, m, k, n)
+    bias = o.make_bias_bf16(1, n)
+    d, amax = hlo_eval.evaluate(text, [a, b, np.float32(sa), np.float32(sb), bias, np.float32(2.0)])
+    exp, exp_amax = o.scaled_dot_f8(a, b, sa, sb, bias=o.bf16_bits_to_f32(bias), epilogue=o.EPI_BIAS_GELU, d_scale=0.5,
+                                    out_dtype=o.F8E4M3FN, want_amax=True)
+    assert o.fp8_within_n_values(exp, d, 1) == 0 and float((exp == d).mean()) > 0.99
+    assert float(amax) == pytest.approx(float(exp_amax), rel=1e-6)
+    a8, b8, rs, cs = o.make_s8_operands(3, 32, 48, 64)
+    text = load("c3_int8_dequant")
+    text = re.sub(r"s8\[4096,4096\] parameter\(0\)", "s8[32,48] parameter(0)", text)
+    text = re.sub(r"s8\[4096,4096\] parameter\(1\)", "s8[48,64] parameter(1)", text)
+    text = text.replace("f32[4096] parameter(2)", "f32[32] parameter(2)").replace("f32[4096] parameter(3)", "f32[64] parameter(3)")
+    text = text.replace("[4096,4096]", "[32,64]")
+    out = hlo_eval.evaluate(text, [a8, b8, rs, cs])
+    assert np.array_equal(out, o.dequant_s32_to_bf16(o.dot_s8(a8, b8), rs, cs))

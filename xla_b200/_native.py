@@ -77,6 +77,7 @@ product.b200sd_wait_probe.argtypes = [C.c_uint64, C.c_void_p, *_ERR]
 product.b200sd_ffi_register.argtypes = [C.c_void_p, *_ERR]
 product.b200sd_scaled_dot_f8_decode_noalloc.argtypes = [C.POINTER(ScaledDotF8Args), C.c_void_p, *_ERR]
 product.b200sd_noalloc_scratch_bytes.restype = C.c_size_t
+product.b200sd_rewrite_hlo.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t, *_ERR]
 
 mock.mockffi_api.restype = C.c_void_p
 mock.mockffi_load_library.argtypes = [C.c_char_p, C.c_char_p, *_ERR]

@@ -1,0 +1,70 @@
+"""Runs a fixture HLO module on the GPU the way XLA would after its GemmRewriter pass.
+
+The module text goes through `b200sd_rewrite_hlo` (the rewriter-lite in csrc/hlo_rewriter.cc, which
+restates xla/backends/gpu/transforms/gemm_rewriter.cc for this path); the resulting custom call is
+then executed through the FFI boundary exactly like any other call site.  The only work done
+outside the custom call is what the rewritten module itself still contains: the reciprocal of a
+scale the original HLO divided by, and scalar constants.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+from typing import Sequence
+
+from . import _native
+from .scaled_dot import FfiCall, XlaFfiError
+
+_TORCH_DTYPE = {}
+
+
+def _torch_dtype(code: int):
+    import torch
+
+    if not _TORCH_DTYPE:
+        _TORCH_DTYPE.update({2: torch.int8, 4: torch.int32, 10: torch.float16, 11: torch.float32, 16: torch.bfloat16,
+                             19: torch.float8_e5m2, 20: torch.float8_e4m3fn})
+    return _TORCH_DTYPE[code]
+
+
+def rewrite(hlo_text: str):
+    """Returns (rewritten module text, plan dict)."""
+    out = C.create_string_buffer(max(1 << 16, 4 * len(hlo_text)))
+    plan = C.create_string_buffer(1 << 15)
+    err = C.create_string_buffer(1024)
+    rc = _native.product.b200sd_rewrite_hlo(hlo_text.encode(), out, len(out), plan, len(plan), err, len(err))
+    if rc != 0:
+        raise XlaFfiError(rc, err.value.decode(errors="replace"))
+    return out.value.decode(), json.loads(plan.value.decode())
+
+
+def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
+    """Rewrites `hlo_text` and executes the custom call on `params` (torch CUDA tensors in parameter
+    order).  Returns the module's outputs in the order of its ROOT (a tensor, or a tuple)."""
+    import torch
+
+    _, plan = rewrite(hlo_text)
+    if not plan["rewritten"]:
+        raise XlaFfiError(12, "module was not rewritten onto a custom call: " + plan["reason"])
+    dev = params[0].device
+    operands = []
+    for src in plan["operands"]:
+        if src["param"] < 0:
+            operands.append(torch.full((), float(src["constant"]), dtype=torch.float32, device=dev))
+        elif src["reciprocal"]:
+            operands.append((1.0 / params[src["param"]].float()).reshape(()))
+        else:
+            operands.append(params[src["param"]])
+    results, outputs = [], {}
+    for res in plan["results"]:
+        t = torch.empty(tuple(res["dims"]), dtype=_torch_dtype(res["dtype"]), device=dev)
+        results.append(t)
+        if res["root_index"] >= -1:
+            outputs[res["root_index"]] = t
+    call = FfiCall(plan["target"], operands, results, dict(plan["attrs"]))
+    s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    call.run(s, dev.index or 0)
+    call.close()
+    if -1 in outputs:
+        return outputs[-1]
+    return tuple(outputs[i] for i in sorted(outputs))
