@@ -43,6 +43,10 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="c1", choices=["c1", "plain", "c2", "c3", "c4"])
+    p.add_argument("--overlap", type=int, default=1, help="c4, N>1: all-reduce finished row blocks while the dot still runs")
+    p.add_argument("--ar-rows", type=int, default=2048, help="c4 overlap: rows of D per all-reduce")
+    p.add_argument("--gemm-ctas", type=int, default=132, help="c4 overlap: SMs the dot may occupy")
+    p.add_argument("--nccl-ctas", type=int, default=16, help="c4 overlap: CTAs the collective may use (0 = NCCL's choice)")
     p.add_argument("--m", type=int, default=0)
     p.add_argument("--n", type=int, default=0)
     p.add_argument("--k", type=int, default=0)
@@ -256,8 +260,23 @@ def gpu_arm(args):
     torch.cuda.synchronize()
     assert xla_b200.device_status() == 0
 
+    overlapped = None
+    if kind == "c4" and world > 1 and args.overlap:
+        group = None
+        if args.nccl_ctas > 0:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = args.nccl_ctas
+            opts.config.min_ctas = min(args.nccl_ctas, 4)
+            group = dist.new_group(backend="nccl", pg_options=opts)
+        overlapped = [sharding.OverlappedRowParallelScaledDot(ops[0], ops[1], ops[2], ops[3], res[0], rows_per_block=args.ar_rows,
+                                                              gemm_ctas=args.gemm_ctas, group=group)
+                      for _, ops, res in sets]
+
     def step(i):
         call, ops, res = sets[i & 1]
+        if overlapped is not None:
+            overlapped[i & 1]()                                  # dot + row-block all-reduces on a second stream
+            return
         call.execute(stream, local_rank)
         if kind == "c4" and world > 1:
             dist.all_reduce(res[0], op=dist.ReduceOp.SUM)        # bf16 partials, one NCCL all-reduce
@@ -305,9 +324,12 @@ def gpu_arm(args):
         def e2e_step():
             for hbuf, o in zip(host_in, ops):
                 o.copy_(hbuf, non_blocking=True)
-            call.execute(stream, local_rank)
-            if kind == "c4" and world > 1:
-                dist.all_reduce(res[0], op=dist.ReduceOp.SUM)
+            if overlapped is not None:
+                overlapped[0]()
+            else:
+                call.execute(stream, local_rank)
+                if kind == "c4" and world > 1:
+                    dist.all_reduce(res[0], op=dist.ReduceOp.SUM)
             for hbuf, o in zip(host_out, outs):
                 hbuf.copy_(o, non_blocking=True)
 
@@ -372,7 +394,9 @@ def gpu_arm(args):
                                 "c4": "config 4: row-parallel FP8 dot + one NCCL all-reduce of bf16 partials"}[kind],
                    "m": m, "n": n, "k": k,
                    "parallelism": ("single GPU" if world == 1 else
-                                   (f"K-split x{world} + all-reduce" if kind == "c4" else f"N-split x{world}, no collective")),
+                                   (f"K-split x{world} + all-reduce" + (f" of {args.ar_rows}-row blocks overlapped with the dot "
+                                    f"({args.gemm_ctas} SMs dot, {args.nccl_ctas} CTAs NCCL)" if overlapped is not None else "")
+                                    if kind == "c4" else f"N-split x{world}, no collective")),
                    "l2": "two operand/result sets used alternately; together larger than the 126 MB L2"},
         "clocks": clocks, "gpu_launches": int(launches_t.item()), "roofline": roof,
     }

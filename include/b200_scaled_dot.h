@@ -154,6 +154,34 @@ int b200sd_device_status(uint32_t* bits, char* err, size_t err_len);
  * through the status word (value 16).  Lets a test watch a wait expire without faulting anything. */
 int b200sd_wait_probe(uint64_t limit_ns, void* cuda_stream, char* err, size_t err_len);
 
+/* Row-block progress of a dense scaled dot, for overlapping the all-reduce of a contracting-
+ * dimension split (xla/service/spmd/dot_handler.cc:2815-2951 emits dot -> all-reduce; XLA's own
+ * overlap of that pair is the async collective scheduling of
+ * xla/backends/gpu/runtime/all_reduce_thunk.cc:89-150, which cannot start before the dot ends).
+ * `counters[i]` (u32, device memory, caller-owned, at least `num_blocks` entries, zeroed once by
+ * the caller and never reset by the library) grows by `increment` per launch as rows
+ * [i*rows_per_block, (i+1)*rows_per_block) of D are stored (`last_increment` for the last, possibly
+ * shorter, block).  A consumer stream calls b200sd_stream_wait_counter() with the running total it
+ * expects and may then read those rows.  `max_ctas` > 0 caps the SMs the kernel occupies so the
+ * consumer's kernels can run beside it.  The three outputs are filled in by the call. */
+typedef struct B200SD_Progress {
+  size_t struct_size;
+  uint32_t* counters;
+  int32_t rows_per_block;   /* positive multiple of 256 */
+  int32_t max_ctas;         /* 0 = all SMs */
+  int32_t num_blocks;       /* out */
+  uint32_t increment;       /* out */
+  uint32_t last_increment;  /* out */
+} B200SD_Progress;
+
+/* b200sd_scaled_dot_f8 on the dense kernel, reporting progress as described above. */
+int b200sd_scaled_dot_f8_progress(const B200SD_ScaledDotF8* args, B200SD_Progress* progress, void* cuda_stream,
+                                  char* err, size_t err_len);
+
+/* Enqueues on `cuda_stream` a wait (a stream memory operation, no kernel) until
+ * (int32)(*counter - target) >= 0. */
+int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint32_t target, char* err, size_t err_len);
+
 /* Decode-shaped scaled dot that allocates nothing and needs no workspace from the caller.
  * (No counterpart in the reference, whose cuBLASLt call always receives a workspace buffer.)
  *

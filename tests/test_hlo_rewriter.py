@@ -114,3 +114,21 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
     text = text.replace("[4096,4096]", "[32,64]")
     out = hlo_eval.evaluate(text, [a8, b8, rs, cs])
     assert np.array_equal(out, o.dequant_s32_to_bf16(o.dot_s8(a8, b8), rs, cs))
+
+
+@pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
+                                  "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32"])
+def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
+    """The plan's operands, results and attributes must form a call frame the handler accepts at
+    instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""
+    import torch
+    from xla_b200.scaled_dot import FfiCall
+
+    _, plan = hlo_runner.rewrite(load(name))
+    assert plan["rewritten"], plan
+    assert isinstance(plan["attrs"]["beta"], float) and isinstance(plan["attrs"]["alpha_real"], float)
+    ops = [torch.empty(tuple(s["dims"]), dtype=hlo_runner._torch_dtype(s["dtype"]), device="meta") for s in plan["operands"]]
+    res = [torch.empty(tuple(r["dims"]), dtype=hlo_runner._torch_dtype(r["dtype"]), device="meta") for r in plan["results"]]
+    call = FfiCall(plan["target"], ops, res, dict(plan["attrs"]))
+    call.instantiate()
+    call.close()

@@ -59,6 +59,17 @@ class DotS8Args(C.Structure):
     ]
 
 
+class ProgressArgs(C.Structure):
+    """B200SD_Progress of include/b200_scaled_dot.h."""
+
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("counters", C.c_void_p),
+        ("rows_per_block", C.c_int32), ("max_ctas", C.c_int32),
+        ("num_blocks", C.c_int32), ("increment", C.c_uint32), ("last_increment", C.c_uint32),
+    ]
+
+
 product = _load(PRODUCT_LIB)
 mock = _load(MOCK_LIB)
 
@@ -77,6 +88,8 @@ product.b200sd_wait_probe.argtypes = [C.c_uint64, C.c_void_p, *_ERR]
 product.b200sd_ffi_register.argtypes = [C.c_void_p, *_ERR]
 product.b200sd_scaled_dot_f8_decode_noalloc.argtypes = [C.POINTER(ScaledDotF8Args), C.c_void_p, *_ERR]
 product.b200sd_noalloc_scratch_bytes.restype = C.c_size_t
+product.b200sd_scaled_dot_f8_progress.argtypes = [C.POINTER(ScaledDotF8Args), C.POINTER(ProgressArgs), C.c_void_p, *_ERR]
+product.b200sd_stream_wait_counter.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, *_ERR]
 product.b200sd_rewrite_hlo.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t, *_ERR]
 
 mock.mockffi_api.restype = C.c_void_p

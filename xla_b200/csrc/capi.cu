@@ -241,6 +241,46 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
   return CopyStatus(st, err, err_len);
 }
 
+int b200sd_scaled_dot_f8_progress(const B200SD_ScaledDotF8* args, B200SD_Progress* progress, void* cuda_stream, char* err,
+                                  size_t err_len) {
+  if (args == nullptr || progress == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args or progress is null"), err, err_len);
+  if (progress->struct_size < sizeof(B200SD_Progress)) return CopyStatus(Status::Error(kInvalidArgument, "B200SD_Progress.struct_size is smaller than this library's struct"), err, err_len);
+  GemmProblem g;
+  Status st = ValidateF8(*args, &g);
+  if (!st.ok()) return CopyStatus(st, err, err_len);
+  if (args->kernel != B200SD_KERNEL_AUTO && args->kernel != B200SD_KERNEL_DENSE) return CopyStatus(Status::Error(kInvalidArgument, "progress reporting exists for the dense kernel only (kernel AUTO or DENSE)"), err, err_len);
+  if (progress->counters == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "progress counters must not be null"), err, err_len);
+  if (progress->rows_per_block <= 0 || progress->rows_per_block % 256 != 0) return CopyStatus(Status::Error(kInvalidArgument, "rows_per_block must be a positive multiple of 256"), err, err_len);
+  if (progress->max_ctas < 0) return CopyStatus(Status::Error(kInvalidArgument, "max_ctas must not be negative"), err, err_len);
+  g.progress = progress->counters;
+  g.progress_rows = progress->rows_per_block;
+  g.max_ctas = progress->max_ctas;
+  progress->num_blocks = int32_t((g.m + g.progress_rows - 1) / g.progress_rows);
+  progress->increment = ProgressIncrement(g, 0);
+  progress->last_increment = ProgressIncrement(g, progress->num_blocks - 1);
+  LaunchStats stats;
+  st = LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats, B200SD_KERNEL_DENSE);
+  if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
+  return CopyStatus(st, err, err_len);
+}
+
+int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint32_t target, char* err, size_t err_len) {
+  // A stream memory operation, not a kernel: the waiting stream holds no SM while it waits and the
+  // producer never waits for it.
+  typedef CUresult (*WaitValueFn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+  static WaitValueFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return reinterpret_cast<WaitValueFn>(p);
+  }();
+  if (fn == nullptr) return CopyStatus(Status::Error(kInternal, "cuStreamWaitValue32 is not available from this driver"), err, err_len);
+  if (counter == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "counter is null"), err, err_len);
+  const CUresult r = fn(static_cast<CUstream>(cuda_stream), reinterpret_cast<CUdeviceptr>(counter), target, CU_STREAM_WAIT_VALUE_GEQ);
+  if (r != CUDA_SUCCESS) return CopyStatus(Status::Error(kInternal, "cuStreamWaitValue32 failed with CUresult " + std::to_string(int(r))), err, err_len);
+  return CopyStatus(Status::Ok(), err, err_len);
+}
+
 int b200sd_dot_s8(const B200SD_DotS8* args, void* cuda_stream, char* err, size_t err_len) {
   if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
   GemmProblem g;

@@ -18,6 +18,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <string>
 
@@ -85,6 +86,8 @@ struct DenseArgs {
   int32_t d_dtype;
   int32_t vec_store_ok;  // D rows start 16-byte aligned and N is a multiple of the vector width
   uint32_t* status;      // device status word (error bits)
+  uint32_t* progress;    // optional per-row-block completion counters, else nullptr
+  int32_t progress_tiles;   // row-tiles per progress counter
   unsigned long long* timing;   // optional per-CTA wait-time counters (tuning aid), else nullptr
 };
 
@@ -516,6 +519,13 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                               colscale_w + c0 + kChunk, &amax_bits);
         }
       }
+      if (p.progress != nullptr) {
+        // Publish this warp's part of the tile: each lane orders its own stores device-wide, the
+        // warp agrees, one lane counts.  A consumer that sees the full count sees the stores.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.progress + mt / p.progress_tiles, 1u);
+      }
       // Hand the accumulator back to the MMA issuer (in the leader CTA): one arrival per warp.
       tc_fence_before_sync();
       __syncwarp();
@@ -613,6 +623,8 @@ Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64
   return Status::Ok();
 }
 
+int MaxPairClusters();
+
 Status InitDenseKernels() {
   int device = 0;
   cudaGetDevice(&device);
@@ -658,6 +670,20 @@ extern "C" int b200sd_debug_read_timing(unsigned long long* out, int count) {
   return int(cudaMemcpyFromSymbol(out, g_dense_timing, sizeof(unsigned long long) * size_t(count)));
 }
 
+uint32_t ProgressIncrement(const GemmProblem& g, int32_t block) {
+  // Every epilogue warp of every CTA working on a tile counts once: 8 warps x (2 CTAs for the pair kernel).
+  if (g.progress_rows <= 0 || block < 0 || int64_t(block) * g.progress_rows >= g.m) return 0;
+  int device = 0;
+  cudaGetDevice(&device);
+  if (!InitDevice(device).ok()) return 0;
+  const bool pair = g.m > kBM && MaxPairClusters() > 0;
+  const int tile_rows = pair ? 2 * kBM : kBM;
+  const int64_t rows = std::min<int64_t>(g.progress_rows, g.m - int64_t(block) * g.progress_rows);
+  const int64_t row_tiles = (rows + tile_rows - 1) / tile_rows;
+  const int64_t col_tiles = (g.n + kBN - 1) / kBN;
+  return uint32_t(row_tiles * col_tiles * kEpilogueWarps * (pair ? 2 : 1));
+}
+
 int MaxPairClusters() {
   int device = 0;
   cudaGetDevice(&device);
@@ -699,6 +725,14 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
   static const int env_raster = [] { const char* e = std::getenv("B200SD_RASTER"); return e ? std::atoi(e) : 0; }();
   p.raster_group = env_raster > 0 ? env_raster : 16;   // B200SD_RASTER: tuning override (16 measured best at 8192^3)
+  p.progress = nullptr;
+  p.progress_tiles = 1;
+  if (g.progress != nullptr) {
+    if (g.progress_rows <= 0 || g.progress_rows % (2 * kBM) != 0) return Status::Error(kInvalidArgument, "progress_rows must be a positive multiple of 256");
+    p.progress = g.progress;
+    p.progress_tiles = g.progress_rows / tile_rows;
+    p.raster_group = p.progress_tiles;   // row blocks then finish one after the other, not all at the end
+  }
   p.a_mn_major = g.a_mn_major; p.b_mn_major = g.b_mn_major;
   p.idesc = make_idesc(g.int8 ? 2u : 1u, FormatCode(g.a_dtype), FormatCode(g.b_dtype), g.a_mn_major, g.b_mn_major,
                        uint32_t(tile_rows), kBN);
@@ -739,6 +773,7 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   } else {
     grid = int(tiles < DeviceSmCount() ? tiles : DeviceSmCount());
   }
+  if (g.max_ctas > 0 && grid > g.max_ctas) grid = pair ? (g.max_ctas >= 2 ? g.max_ctas & ~1 : 2) : g.max_ctas;
   if (g.amax != nullptr) {
     cudaError_t e = cudaMemsetAsync(g.amax, 0, sizeof(float), stream);
     if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(amax): ") + cudaGetErrorString(e));

@@ -588,6 +588,13 @@ std::string Num(double v) {
   return buf;
 }
 
+// A value that must stay floating point when parsed back (JSON readers turn "1" into an integer).
+std::string F64(double v) {
+  std::string s = Num(v);
+  if (s.find_first_of(".einf") == std::string::npos) s += ".0";
+  return s;
+}
+
 constexpr int64_t kWorkspaceBytes = 32ll * 1024 * 1024;   // GemmConfig::kHopperWorkspace, matmul_utils.h:103
 
 bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::string* json) {
@@ -633,7 +640,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   for (size_t i = 0; i < op_names.size(); ++i) o << (i ? ", " : "") << op_names[i];
   o << "), custom_call_target=\"" << plan->target << "\", api_version=API_VERSION_TYPED_FFI, backend_config={";
   if (f8) {
-    o << "alpha_real = " << Num(plan->alpha) << " : f64, beta = " << Num(plan->beta) << " : f64, epilogue = " << plan->epilogue
+    o << "alpha_real = " << F64(plan->alpha) << " : f64, beta = " << F64(plan->beta) << " : f64, epilogue = " << plan->epilogue
       << " : i32, lhs_contracting_dim = " << plan->lhs_contracting << " : i64, rhs_contracting_dim = " << plan->rhs_contracting
       << " : i64, damax_output = " << (plan->damax ? "true" : "false") << ", selected_config = 0 : i64}\n";
   } else {
@@ -665,7 +672,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
   if (plan->damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": [], \"root_index\": " << plan->amax_root_index << "}";
   if (f8) j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
-  j << "], \"attrs\": {\"alpha_real\": " << Num(plan->alpha) << ", \"beta\": " << Num(plan->beta) << ", \"epilogue\": " << plan->epilogue
+  j << "], \"attrs\": {\"alpha_real\": " << F64(plan->alpha) << ", \"beta\": " << F64(plan->beta) << ", \"epilogue\": " << plan->epilogue
     << ", \"lhs_contracting_dim\": " << plan->lhs_contracting << ", \"rhs_contracting_dim\": " << plan->rhs_contracting
     << ", \"damax_output\": " << (plan->damax ? "true" : "false") << "}}";
   *json = j.str();

@@ -78,7 +78,18 @@ struct GemmProblem {
 
   void* workspace = nullptr;         // caller-owned scratch for the split-K kernel
   size_t workspace_bytes = 0;
+
+  // Optional progress reporting of the dense kernel, for a consumer on another stream that wants
+  // to start on finished row blocks of D (the all-reduce of a K-split dot) before the kernel ends.
+  // counters[i] is incremented (never reset) as tiles of rows [i*progress_rows, (i+1)*progress_rows)
+  // are stored; ProgressIncrement() is what one launch adds to each counter.
+  uint32_t* progress = nullptr;
+  int32_t progress_rows = 0;         // multiple of 256
+  int32_t max_ctas = 0;              // > 0: use at most this many SMs, leaving the rest to the consumer
 };
+
+// What one dense launch adds to progress counter `block` (0 when the block is past the last row).
+uint32_t ProgressIncrement(const GemmProblem& g, int32_t block);
 
 // Kernel selection (stands in for cuBLASLt's algorithm index).
 enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2, kKernelDenseSingle = 3, kKernelDensePair = 4 };

@@ -61,7 +61,10 @@ def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
         results.append(t)
         if res["root_index"] >= -1:
             outputs[res["root_index"]] = t
-    call = FfiCall(plan["target"], operands, results, dict(plan["attrs"]))
+    attrs = dict(plan["attrs"])
+    for key in ("alpha_real", "beta"):                       # f64 attributes, whatever the JSON reader made of them
+        attrs[key] = float(attrs[key])
+    call = FfiCall(plan["target"], operands, results, attrs)
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
     call.run(s, dev.index or 0)
     call.close()

@@ -116,3 +116,82 @@ def gather_columns(shards: Sequence, axis: int = 1):
     import numpy as np
 
     return np.concatenate(list(shards), axis=axis)
+
+
+class OverlappedRowParallelScaledDot:
+    """K-split scaled dot whose all-reduce starts while the dot is still running.
+
+    The dense kernel counts finished row blocks of its bf16 partial (b200sd_scaled_dot_f8_progress);
+    a second stream waits on each counter with a stream memory operation and all-reduces that row
+    block, so all but the last block's reduction hides under the remaining tiles.  The kernel is
+    held to `gemm_ctas` SMs so the collective's kernels find room beside it.  The result is the
+    same sum of bf16 partials as the plain pattern: every element is reduced exactly once, by the
+    same collective.
+
+    XLA's counterpart is the async all-reduce start/done pair scheduled around the dot's thunk
+    (xla/backends/gpu/runtime/all_reduce_thunk.cc:89-150); it cannot begin before the dot ends.
+    """
+
+    def __init__(self, a_shard, b_shard, a_scale, b_scale, out, *, rows_per_block: int = 2048, gemm_ctas: int = 132,
+                 group=None, lhs_contracting_dim: int = 1, rhs_contracting_dim: int = 0):
+        import ctypes as C
+
+        import torch
+
+        from . import _native
+        from .scaled_dot import _dtype_code
+
+        self._torch, self._native, self._C = torch, _native, C
+        self.group = group
+        m = a_shard.shape[0] if lhs_contracting_dim == 1 else a_shard.shape[1]
+        k = a_shard.shape[1] if lhs_contracting_dim == 1 else a_shard.shape[0]
+        n = b_shard.shape[1] if rhs_contracting_dim == 0 else b_shard.shape[0]
+        if out.shape != (m, n) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise ValueError("out must be a contiguous bf16 [m, n] tensor")
+        self.keep = (a_shard, b_shard, a_scale, b_scale, out)
+        self.out = out
+        self.rows = rows_per_block
+        self.args = _native.ScaledDotF8Args(
+            struct_size=C.sizeof(_native.ScaledDotF8Args), a=a_shard.data_ptr(), b=b_shard.data_ptr(),
+            a_scale=a_scale.data_ptr(), b_scale=b_scale.data_ptr(), d=out.data_ptr(), m=m, n=n, k=k,
+            a_dtype=_dtype_code(a_shard.dtype), b_dtype=_dtype_code(b_shard.dtype),
+            d_dtype=_dtype_code(out.dtype), lhs_contracting_dim=lhs_contracting_dim,
+            rhs_contracting_dim=rhs_contracting_dim, epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+        blocks = (m + rows_per_block - 1) // rows_per_block
+        self.counters = torch.zeros(blocks, dtype=torch.int32, device=out.device)
+        self.totals = [0] * blocks
+        self.progress = _native.ProgressArgs(struct_size=C.sizeof(_native.ProgressArgs), counters=self.counters.data_ptr(),
+                                             rows_per_block=rows_per_block, max_ctas=gemm_ctas)
+        self.side = torch.cuda.Stream(device=out.device)
+        self.reduced = None          # event: the previous call's all-reduces are done with `out`
+        self._err = C.create_string_buffer(512)
+
+    def _check(self, rc):
+        if rc != 0:
+            from .scaled_dot import XlaFfiError
+
+            raise XlaFfiError(rc, self._err.value.decode(errors="replace"))
+
+    def __call__(self):
+        """Enqueues the dot on the current stream and the row-block all-reduces on the side stream;
+        the current stream then waits for the last of them.  Returns `out`."""
+        import torch.distributed as dist
+
+        torch, lib = self._torch, self._native.product
+        main = torch.cuda.current_stream(self.out.device)
+        start = torch.cuda.Event()
+        start.record(main)                       # the side stream may not run ahead of earlier users of `out`
+        self._check(lib.b200sd_scaled_dot_f8_progress(self.args, self.progress, main.cuda_stream, self._err, len(self._err)))
+        p = self.progress
+        self.side.wait_event(start)
+        with torch.cuda.stream(self.side):
+            for i in range(p.num_blocks):
+                inc = p.last_increment if i == p.num_blocks - 1 else p.increment
+                self.totals[i] = (self.totals[i] + inc) & 0xFFFFFFFF
+                addr = self.counters.data_ptr() + 4 * i
+                self._check(lib.b200sd_stream_wait_counter(self.side.cuda_stream, addr, self.totals[i], self._err, len(self._err)))
+                dist.all_reduce(self.out[i * self.rows:(i + 1) * self.rows], op=dist.ReduceOp.SUM, group=self.group)
+            done = torch.cuda.Event()
+            done.record(self.side)
+        main.wait_event(done)
+        return self.out
