@@ -182,6 +182,47 @@ int b200sd_scaled_dot_f8_progress(const B200SD_ScaledDotF8* args, B200SD_Progres
  * (int32)(*counter - target) >= 0. */
 int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint32_t target, char* err, size_t err_len);
 
+/* Contracting-dimension split over `world` GPUs of one box with the sum formed inside the dot's
+ * kernel, over peer memory, instead of by a separate all-reduce.  Replaces the pair
+ * dot -> all-reduce that xla/service/spmd/dot_handler.cc:2815-2951 emits and
+ * xla/backends/gpu/runtime/all_reduce_thunk.cc:89-150 /
+ * xla/backends/gpu/collectives/nccl_communicator.cc:557-592 execute.
+ *
+ * Every rank calls this with its own K-shard in `args` (a, b, scales; args->d = d[rank]; bf16
+ * result, no epilogue).  Rank r pushes the bf16 partial of the row blocks it does not own into the
+ * owner's `stage` buffer while its tensor cores work on the next tile, computes its own block
+ * (rows [r*m/world, (r+1)*m/world)) last, adds the partials the others pushed (in rank order, in
+ * f32, rounded once) and writes the finished rows into every rank's `d`.  When the kernel ends on
+ * a rank, that rank's `d` is complete.  m must be a multiple of 256*world.
+ *
+ * d[i], stage[i] (m*n*2 bytes) and flags[i] (b200sd_peer_reduce_flag_words() u32, zeroed once when
+ * allocated, never by the library) are rank i's buffers as mapped into THIS process (peer memory:
+ * symmetric-memory or IPC mappings); the same buffers must be passed on every call of a sequence
+ * and `epoch` must count the calls 1, 2, 3, ... identically on every rank.  Waits between ranks
+ * are bounded (2 s) and report through b200sd_device_status (bit 32).
+ *
+ * emulate_ranks == world makes ONE launch on ONE GPU play every rank (each with its own operands
+ * emu_a[i], emu_b[i] and 1/world of the SMs): the way to exercise the protocol without a second
+ * GPU.  It synchronises the stream once before the launch. */
+typedef struct B200SD_PeerReduce {
+  size_t struct_size;
+  int32_t world;
+  int32_t rank;
+  int32_t emulate_ranks;
+  uint32_t epoch;
+  void* d[8];
+  void* stage[8];
+  uint32_t* flags[8];
+  const void* emu_a[8];
+  const void* emu_b[8];
+} B200SD_PeerReduce;
+
+int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200SD_PeerReduce* peers, void* cuda_stream,
+                                     char* err, size_t err_len);
+
+/* Number of u32 flag words each rank must provide for the call above (0 if the shape is not supported). */
+size_t b200sd_peer_reduce_flag_words(int64_t m, int64_t n, int32_t world);
+
 /* Decode-shaped scaled dot that allocates nothing and needs no workspace from the caller.
  * (No counterpart in the reference, whose cuBLASLt call always receives a workspace buffer.)
  *

@@ -70,6 +70,17 @@ class ProgressArgs(C.Structure):
     ]
 
 
+class PeerReduceArgs(C.Structure):
+    """B200SD_PeerReduce of include/b200_scaled_dot.h."""
+
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("world", C.c_int32), ("rank", C.c_int32), ("emulate_ranks", C.c_int32), ("epoch", C.c_uint32),
+        ("d", C.c_void_p * 8), ("stage", C.c_void_p * 8), ("flags", C.c_void_p * 8),
+        ("emu_a", C.c_void_p * 8), ("emu_b", C.c_void_p * 8),
+    ]
+
+
 product = _load(PRODUCT_LIB)
 mock = _load(MOCK_LIB)
 
@@ -90,6 +101,9 @@ product.b200sd_scaled_dot_f8_decode_noalloc.argtypes = [C.POINTER(ScaledDotF8Arg
 product.b200sd_noalloc_scratch_bytes.restype = C.c_size_t
 product.b200sd_scaled_dot_f8_progress.argtypes = [C.POINTER(ScaledDotF8Args), C.POINTER(ProgressArgs), C.c_void_p, *_ERR]
 product.b200sd_stream_wait_counter.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, *_ERR]
+product.b200sd_scaled_dot_f8_peer_reduce.argtypes = [C.POINTER(ScaledDotF8Args), C.POINTER(PeerReduceArgs), C.c_void_p, *_ERR]
+product.b200sd_peer_reduce_flag_words.argtypes = [C.c_int64, C.c_int64, C.c_int32]
+product.b200sd_peer_reduce_flag_words.restype = C.c_size_t
 product.b200sd_rewrite_hlo.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t, *_ERR]
 
 mock.mockffi_api.restype = C.c_void_p

@@ -264,6 +264,33 @@ int b200sd_scaled_dot_f8_progress(const B200SD_ScaledDotF8* args, B200SD_Progres
   return CopyStatus(st, err, err_len);
 }
 
+int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200SD_PeerReduce* peers, void* cuda_stream, char* err,
+                                     size_t err_len) {
+  if (args == nullptr || peers == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args or peers is null"), err, err_len);
+  if (peers->struct_size < sizeof(B200SD_PeerReduce)) return CopyStatus(Status::Error(kInvalidArgument, "B200SD_PeerReduce.struct_size is smaller than this library's struct"), err, err_len);
+  GemmProblem g;
+  Status st = ValidateF8(*args, &g);
+  if (!st.ok()) return CopyStatus(st, err, err_len);
+  PeerReduceProblem r;
+  r.world = peers->world;
+  r.rank = peers->rank;
+  r.emulate = peers->emulate_ranks;
+  r.epoch = peers->epoch;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    r.d[i] = peers->d[i];
+    r.stage[i] = peers->stage[i];
+    r.flags[i] = peers->flags[i];
+    r.emu_a[i] = peers->emu_a[i];
+    r.emu_b[i] = peers->emu_b[i];
+  }
+  LaunchStats stats;
+  st = LaunchDenseReduce(g, r, static_cast<cudaStream_t>(cuda_stream), &stats);
+  if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
+  return CopyStatus(st, err, err_len);
+}
+
+size_t b200sd_peer_reduce_flag_words(int64_t m, int64_t n, int32_t world) { return PeerReduceFlagWords(m, n, world); }
+
 int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint32_t target, char* err, size_t err_len) {
   // A stream memory operation, not a kernel: the waiting stream holds no SM while it waits and the
   // producer never waits for it.

@@ -64,6 +64,19 @@ constexpr size_t DenseSmemBytes() {
   return 1024 /*alignment slack*/ + size_t(Shape<kPair>::kStages) * Shape<kPair>::kStageBytes + sizeof(DenseAux<kPair>);
 }
 
+// Peer-reduce mode (see PeerReduceProblem): what the kernel needs of it.
+struct ReduceArgs {
+  int32_t world, rank, emulate;
+  int32_t m_tiles_per_block;      // 256-row tiles in the row block each rank owns
+  uint32_t flag_target;           // value a (tile, warp) flag reaches when every other rank has pushed: epoch * (world - 1)
+  uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
+  int32_t done_index;             // index of that counter in the flag array
+  uint16_t* d[kMaxPeers];
+  uint16_t* stage[kMaxPeers];
+  uint32_t* flags[kMaxPeers];
+  const CUtensorMap* emu_maps;    // emulate: A and B maps of rank r at [2r], [2r+1]
+};
+
 struct DenseArgs {
   int64_t m, n, k;
   int32_t num_m_tiles, num_n_tiles, num_k_blocks, raster_group;
@@ -89,6 +102,7 @@ struct DenseArgs {
   uint32_t* progress;    // optional per-row-block completion counters, else nullptr
   int32_t progress_tiles;   // row-tiles per progress counter
   unsigned long long* timing;   // optional per-CTA wait-time counters (tuning aid), else nullptr
+  ReduceArgs red;               // read by the peer-reduce instantiation only
 };
 
 // Tuning aid: per CTA, [0] cycles the MMA issuer waited for operands, [1] cycles it waited for a
@@ -128,7 +142,84 @@ __device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, in
   *nt = r / gsize;
 }
 
+// Peer-reduce order: rank r walks the row blocks r+1, r+2, ..., r (its own last), so that what it
+// pushes first is what its neighbours need last, and by the time it reaches its own block the
+// others' partials of that block have long arrived.  `blk` is the owner of the tile's rows,
+// `slot` the tile's index inside that block (names its flags).
+__device__ __forceinline__ void tile_coords_reduce(int32_t tile, const DenseArgs& p, int32_t my_rank, int32_t* mt,
+                                                   int32_t* nt, int32_t* blk, int32_t* slot) {
+  const int32_t mtpb = p.red.m_tiles_per_block;
+  const int32_t per_block = mtpb * p.num_n_tiles;
+  const int32_t b = tile / per_block;
+  const int32_t local = tile - b * per_block;
+  int32_t owner = my_rank + 1 + b;
+  if (owner >= p.red.world) owner -= p.red.world;
+  const int32_t rg = min(p.raster_group, mtpb);
+  const int32_t per_group = rg * p.num_n_tiles;
+  const int32_t g = local / per_group;
+  const int32_t first_m = g * rg;
+  const int32_t gsize = min(rg, mtpb - first_m);
+  const int32_t r = local - g * per_group;
+  const int32_t mt_local = first_m + r % gsize;
+  *nt = r / gsize;
+  *mt = owner * mtpb + mt_local;
+  *blk = owner;
+  *slot = mt_local * p.num_n_tiles + *nt;
+}
+
 constexpr int kChunk = 16;   // accumulator columns handled per epilogue step
+
+// Peer-reduce epilogue for kChunk columns of one row.  The partial is rounded to bf16 (the dot's
+// result type).  For a row another rank owns it goes into that rank's staging buffer; for an own
+// row the bf16 partials of all ranks are added in rank order in f32, rounded once and written to
+// every rank's D.
+__device__ __forceinline__ void reduce_chunk(const DenseArgs& p, const uint32_t (&r)[kChunk], float scale, int32_t my_rank,
+                                             int32_t blk, int64_t row, int64_t row_in_block, int64_t rows_per_block,
+                                             int64_t col0) {
+  uint32_t w[kChunk / 2];
+#pragma unroll
+  for (int i = 0; i < kChunk / 2; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  if (blk != my_rank) {
+    uint4* dst = reinterpret_cast<uint4*>(p.red.stage[blk] + (int64_t(my_rank) * rows_per_block + row_in_block) * p.n + col0);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    return;
+  }
+  float acc[kChunk];
+#pragma unroll
+  for (int i = 0; i < kChunk; ++i) acc[i] = 0.0f;
+  for (int32_t s = 0; s < p.red.world; ++s) {
+    uint32_t x[kChunk / 2];
+    if (s == my_rank) {
+#pragma unroll
+      for (int i = 0; i < kChunk / 2; ++i) x[i] = w[i];
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(p.red.stage[my_rank] + (int64_t(s) * rows_per_block + row_in_block) * p.n + col0);
+      const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);      // written by another GPU: never through L1
+      x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+      x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    }
+#pragma unroll
+    for (int i = 0; i < kChunk / 2; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x[i]));
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kChunk / 2; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  for (int32_t j = 0; j < p.red.world; ++j) {
+    uint4* dst = reinterpret_cast<uint4*>(p.red.d[j] + row * p.n + col0);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
 
 // Converts and stores kChunk consecutive columns of one row.
 __device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float (&v)[kChunk], int64_t row, int64_t col0,
@@ -257,10 +348,11 @@ __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t 
   store_row_chunk(p, v, row, col0, ncols);
 }
 
-template <bool kInt8, bool kPair>
+template <bool kInt8, bool kPair, bool kReduce = false>
 __global__ void __launch_bounds__(kThreads, 1)
-dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid_constant__ CUtensorMap tmap_b_param,
                   const DenseArgs p) {
+  static_assert(!kReduce || (kPair && !kInt8), "peer-reduce mode exists for the FP8 pair kernel only");
   using S = Shape<kPair>;
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -274,8 +366,24 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int lane = threadIdx.x & 31;
   const uint32_t rank = kPair ? cluster_cta_rank() : 0u;        // 0 = leader of the pair
   const int32_t num_tiles = p.num_m_tiles * p.num_n_tiles;
-  const int32_t first_tile = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
-  const int32_t tile_step = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
+  int32_t first_tile = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
+  int32_t tile_step = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
+  // Which rank of a contracting-dimension split this CTA works for, and on whose operands.
+  int32_t my_rank = 0;
+  const CUtensorMap* tmap_a_ptr = &tmap_a_param;
+  const CUtensorMap* tmap_b_ptr = &tmap_b_param;
+  if constexpr (kReduce) {
+    my_rank = p.red.rank;
+    if (p.red.emulate) {
+      tile_step /= p.red.world;                   // clusters per emulated rank
+      my_rank = first_tile / tile_step;
+      first_tile -= my_rank * tile_step;
+      tmap_a_ptr = p.red.emu_maps + 2 * my_rank;
+      tmap_b_ptr = p.red.emu_maps + 2 * my_rank + 1;
+    }
+  }
+  const CUtensorMap& tmap_a = *tmap_a_ptr;
+  const CUtensorMap& tmap_b = *tmap_b_ptr;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -316,7 +424,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       long long prod_wait = 0;
       for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         int32_t mt, nt;
-        tile_coords(tile, p, &mt, &nt);
+        if constexpr (kReduce) {
+          int32_t blk, slot;
+          tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
+        } else {
+          tile_coords(tile, p, &mt, &nt);
+        }
         const int32_t row0 = mt * S::kTileRows + int32_t(rank) * kBM;
         const int32_t col0 = nt * kBN + (kPair ? int32_t(rank) * (kBN / 2) : 0);
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
@@ -460,6 +573,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (p.b_scale) scale *= __ldg(p.b_scale);
       if (p.d_scale) d_scale = __ldg(p.d_scale);
     }
+    const int64_t rows_per_block = kReduce ? int64_t(p.red.m_tiles_per_block) * S::kTileRows : 0;
     uint32_t amax_bits = 0;
     long long ep_wait = 0, ep_busy = 0;
     int acc = 0;
@@ -467,7 +581,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     bool ok = true;
     for (int32_t tile = first_tile; tile < num_tiles; tile += tile_step) {
       int32_t mt, nt;
-      tile_coords(tile, p, &mt, &nt);
+      int32_t blk = 0, slot = 0;
+      if constexpr (kReduce) tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
+      else tile_coords(tile, p, &mt, &nt);
       const int64_t col_base = int64_t(nt) * kBN + col_half * kColsPerEpilogueWarp;
       // Stage the per-column vectors of this warp's columns.
       __syncwarp();
@@ -488,6 +604,16 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!ok) break;
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
       tc_fence_after_sync();
+      // Flag of this warp's part of the tile: raised once by the same warp of every other rank.
+      uint32_t* const my_flag_base = kReduce ? p.red.flags[my_rank] : nullptr;
+      const int32_t flag_index = (slot * 2 + int32_t(rank)) * kEpilogueWarps + ew;
+      if constexpr (kReduce) {
+        if (blk == my_rank && p.red.world > 1) {
+          if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+        }
+      }
 
       const int64_t row = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
       const bool row_ok = row < p.m;
@@ -507,16 +633,27 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         int64_t col0 = col_base + c0;
         if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
-                              &amax_bits);
+          if constexpr (kReduce) reduce_chunk(p, ra, scale, my_rank, blk, row, row - int64_t(blk) * rows_per_block, rows_per_block, col0);
+          else finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
+                                   &amax_bits);
         }
         tmem_ld_wait_16(rb);
         if (c0 + 2 * kChunk < kColsPerEpilogueWarp) tmem_ld_32x16(taddr + c0 + 2 * kChunk, ra);
         col0 += kChunk;
         if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          finish_chunk<kInt8>(p, rb, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0 + kChunk,
-                              colscale_w + c0 + kChunk, &amax_bits);
+          if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, row, row - int64_t(blk) * rows_per_block, rows_per_block, col0);
+          else finish_chunk<kInt8>(p, rb, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0 + kChunk,
+                                   colscale_w + c0 + kChunk, &amax_bits);
+        }
+      }
+      if constexpr (kReduce) {
+        if (blk != my_rank) {
+          // The partial is in the owner's staging buffer: make it visible to that GPU, then raise
+          // the owner's flag for this warp's part of the tile.
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) red_release_sys_add_u32(p.red.flags[blk] + flag_index, 1u);
         }
       }
       if (p.progress != nullptr) {
@@ -538,6 +675,18 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    if constexpr (kReduce) {
+      // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
+      // warp of every rank has said the same, so that D is complete here when the kernel ends and
+      // nobody overwrites a staging buffer that is still being read.
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        for (int32_t j = 0; j < p.red.world; ++j) red_release_sys_add_u32(p.red.flags[j] + p.red.done_index, 1u);
+        (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout);
+      }
+      __syncwarp();
     }
     if (p.timing && warp == 2 && lane == 0) {
       p.timing[blockIdx.x * 8 + 5] = ep_wait;
@@ -581,7 +730,7 @@ EncodeTiledFn GetEncodeTiled() {
 
 int g_max_pair_clusters[64];   // co-resident 2-CTA clusters per device, filled by InitDenseKernels
 
-template <bool kInt8, bool kPair>
+template <bool kInt8, bool kPair, bool kReduce = false>
 cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const DenseArgs& p) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -595,7 +744,7 @@ cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, dense_gemm_kernel<kInt8, kPair>, ta, tb, p);
+  return cudaLaunchKernelEx(&cfg, dense_gemm_kernel<kInt8, kPair, kReduce>, ta, tb, p);
 }
 
 }  // namespace
@@ -636,6 +785,7 @@ Status InitDenseKernels() {
   set(reinterpret_cast<const void*>(dense_gemm_kernel<true, false>), DenseSmemBytes<false>());
   set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true>), DenseSmemBytes<true>());
   set(reinterpret_cast<const void*>(dense_gemm_kernel<true, true>), DenseSmemBytes<true>());
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true, true>), DenseSmemBytes<true>());
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(dense): ") + cudaGetErrorString(e));
   // How many CTA pairs fit on the device at once bounds the persistent grid of the pair kernel.
   cudaLaunchConfig_t cfg{};
@@ -787,6 +937,101 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("dense_gemm_kernel launch: ") + cudaGetErrorString(e));
   if (stats) {
     stats->kernel = pair ? kKernelDensePair : kKernelDenseSingle;
+    stats->grid = grid;
+    stats->launches = 1;
+  }
+  return Status::Ok();
+}
+
+// Tensor maps of the emulated ranks (single-GPU testing of the peer-reduce protocol).
+__device__ __align__(64) CUtensorMap g_emu_maps[2 * kMaxPeers];
+
+size_t PeerReduceFlagWords(int64_t m, int64_t n, int32_t world) {
+  if (world < 1 || m <= 0 || n <= 0 || m % (int64_t(world) * 2 * kBM) != 0) return 0;
+  const int64_t tiles_per_block = (m / world / (2 * kBM)) * ((n + kBN - 1) / kBN);
+  return size_t(tiles_per_block) * 2 * kEpilogueWarps + 64;   // one flag per (tile, CTA of the pair, warp); then the end-of-call counter
+}
+
+Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaStream_t stream, LaunchStats* stats) {
+  int device = 0;
+  cudaGetDevice(&device);
+  Status st = InitDevice(device);
+  if (!st.ok()) return st;
+  const int max_pairs = MaxPairClusters();
+  if (max_pairs <= 0) return Status::Error(kFailedPrecondition, "this device cannot co-schedule CTA pairs for the pair kernel");
+  if (r.world < 1 || r.world > kMaxPeers || r.rank < 0 || r.rank >= r.world) return Status::Error(kInvalidArgument, "world must be 1..8 and rank inside it");
+  if (g.int8 || g.d_dtype != kBF16 || g.c != nullptr || g.bias != nullptr || g.activation != kActNone || g.amax != nullptr || g.d_scale != nullptr)
+    return Status::Error(kInvalidArgument, "the peer-reduced dot is the plain FP8 scaled dot with a bf16 result");
+  if (g.m % (int64_t(r.world) * 2 * kBM) != 0) return Status::Error(kInvalidArgument, "m must be a multiple of 256 x world for the peer-reduced dot");
+  if (g.n % 16 != 0) return Status::Error(kInvalidArgument, "n must be a multiple of 16");
+  if (r.epoch == 0) return Status::Error(kInvalidArgument, "epoch counts calls from 1");
+  if (r.emulate && r.emulate != r.world) return Status::Error(kInvalidArgument, "emulate must be 0 or equal to world");
+  for (int i = 0; i < r.world; ++i) {
+    if (r.d[i] == nullptr || r.stage[i] == nullptr || r.flags[i] == nullptr) return Status::Error(kInvalidArgument, "d, stage and flags are needed for every rank");
+    if ((reinterpret_cast<uintptr_t>(r.d[i]) | reinterpret_cast<uintptr_t>(r.stage[i])) & 15) return Status::Error(kInvalidArgument, "d and stage must be 16-byte aligned");
+    if (r.emulate && (r.emu_a[i] == nullptr || r.emu_b[i] == nullptr)) return Status::Error(kInvalidArgument, "emulation needs every rank's operands");
+  }
+
+  DenseArgs p{};
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.num_m_tiles = int32_t(g.m / (2 * kBM));
+  p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
+  p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
+  p.raster_group = 16;
+  p.a_mn_major = g.a_mn_major; p.b_mn_major = g.b_mn_major;
+  p.idesc = make_idesc(1u, FormatCode(g.a_dtype), FormatCode(g.b_dtype), g.a_mn_major, g.b_mn_major, 2 * kBM, kBN);
+  p.a_scale = g.a_scale; p.b_scale = g.b_scale;
+  p.alpha = g.alpha;
+  p.d = r.d[r.rank]; p.d_dtype = kBF16;
+  p.vec_store_ok = 1;
+  p.status = StatusWordPtr();
+  p.progress_tiles = 1;
+
+  const int64_t tiles = int64_t(p.num_m_tiles) * p.num_n_tiles;
+  int clusters_per_rank = r.emulate ? max_pairs / r.world : max_pairs;
+  if (clusters_per_rank > tiles) clusters_per_rank = int(tiles);
+  if (clusters_per_rank < 1) return Status::Error(kFailedPrecondition, "not enough SMs to emulate this many ranks");
+  const int grid = 2 * clusters_per_rank * (r.emulate ? r.world : 1);
+
+  ReduceArgs& q = p.red;
+  q.world = r.world; q.rank = r.rank; q.emulate = r.emulate;
+  q.m_tiles_per_block = p.num_m_tiles / r.world;
+  q.flag_target = r.epoch * uint32_t(r.world - 1);
+  q.done_index = int32_t(PeerReduceFlagWords(g.m, g.n, r.world)) - 32;
+  q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps);
+  for (int i = 0; i < r.world; ++i) {
+    q.d[i] = static_cast<uint16_t*>(r.d[i]);
+    q.stage[i] = static_cast<uint16_t*>(r.stage[i]);
+    q.flags[i] = r.flags[i];
+  }
+  q.emu_maps = nullptr;
+
+  auto make_maps = [&](const void* a, const void* b, CUtensorMap* ta, CUtensorMap* tb) {
+    Status s = g.a_mn_major ? MakeByteMatrixMap(ta, a, g.k, g.m, 128, kBK) : MakeByteMatrixMap(ta, a, g.m, g.k, kBK, kBM);
+    if (!s.ok()) return s;
+    return g.b_mn_major ? MakeByteMatrixMap(tb, b, g.k, g.n, 128, kBK) : MakeByteMatrixMap(tb, b, g.n, g.k, kBK, kBN / 2);
+  };
+  CUtensorMap tmap_a, tmap_b;
+  if (r.emulate) {
+    CUtensorMap maps[2 * kMaxPeers];
+    for (int i = 0; i < r.world; ++i) {
+      st = make_maps(r.emu_a[i], r.emu_b[i], &maps[2 * i], &maps[2 * i + 1]);
+      if (!st.ok()) return st;
+    }
+    cudaError_t e = cudaMemcpyToSymbolAsync(g_emu_maps, maps, sizeof(CUtensorMap) * 2 * r.world, 0, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);   // `maps` lives on this stack frame
+    if (e != cudaSuccess) return Status::Error(kInternal, std::string("copying the emulated ranks' tensor maps: ") + cudaGetErrorString(e));
+    cudaGetSymbolAddress(reinterpret_cast<void**>(const_cast<CUtensorMap**>(&q.emu_maps)), g_emu_maps);
+    tmap_a = maps[0];
+    tmap_b = maps[1];
+  } else {
+    st = make_maps(g.a, g.b, &tmap_a, &tmap_b);
+    if (!st.ok()) return st;
+  }
+  cudaError_t e = LaunchOne<false, true, true>(grid, stream, tmap_a, tmap_b, p);
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("dense_gemm_kernel (peer reduce) launch: ") + cudaGetErrorString(e));
+  if (stats) {
+    stats->kernel = kKernelDensePair;
     stats->grid = grid;
     stats->launches = 1;
   }

@@ -88,6 +88,25 @@ struct GemmProblem {
   int32_t max_ctas = 0;              // > 0: use at most this many SMs, leaving the rest to the consumer
 };
 
+// A contracting-dimension split over `world` GPUs whose sum is formed inside the dense kernel:
+// every rank pushes its bf16 partial of the row blocks it does not own into the owner's staging
+// buffer over peer memory, computes its own block last, adds what the others pushed and writes
+// the finished rows into every rank's D.  All pointers are indexed by rank and peer-mapped.
+constexpr int kMaxPeers = 8;
+struct PeerReduceProblem {
+  int32_t world = 1, rank = 0;
+  int32_t emulate = 0;               // one launch on one GPU plays all ranks (single-GPU testing)
+  uint32_t epoch = 1;                // 1, 2, 3, ...; the same on every rank for the same call
+  void* d[kMaxPeers] = {};
+  void* stage[kMaxPeers] = {};       // m*n bf16 each
+  uint32_t* flags[kMaxPeers] = {};   // PeerReduceFlagWords() u32 each, zeroed once
+  const void* emu_a[kMaxPeers] = {};
+  const void* emu_b[kMaxPeers] = {};
+};
+size_t PeerReduceFlagWords(int64_t m, int64_t n, int32_t world);
+struct LaunchStats;
+Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaStream_t stream, LaunchStats* stats);
+
 // What one dense launch adds to progress counter `block` (0 when the block is past the last row).
 uint32_t ProgressIncrement(const GemmProblem& g, int32_t block);
 

@@ -17,6 +17,7 @@ enum DeviceStatusBits : uint32_t {
   kStatusEpilogueTimeout = 1u << 2,   // epilogue gave up waiting for an accumulator
   kStatusFixupTimeout = 1u << 3,      // split-K reducer gave up waiting for a partial tile
   kStatusProbeTimeout = 1u << 4,      // a wait made to expire on purpose (host-visible status test)
+  kStatusPeerTimeout = 1u << 5,       // gave up waiting for another rank's partial tile or end-of-call signal
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -83,6 +84,39 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 4095u) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > limit_ns) {
+        *abort_flag = 1;
+        atomicOr(status, status_bit);
+        return false;
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- flags between ranks
+// Counters in global memory that another GPU (or another CTA) increments after it has written
+// data for us: release-add on the writer's side, acquire-load on ours, both at system scope.
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until the counter has reached `target` (wrap-safe: counters only grow).  Same
+// abort / status protocol as mbar_wait.
+__device__ __forceinline__ bool counter_wait(const uint32_t* counter, uint32_t target, volatile int* abort_flag,
+                                             uint32_t* status, uint32_t status_bit, uint64_t limit_ns = kWaitLimitNs) {
+  uint64_t t0 = 0;
+  uint32_t polls = 0;
+  while (true) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(counter) - target) >= 0) return true;
+    if ((++polls & 255u) == 0) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
