@@ -1,0 +1,60 @@
+"""Two-process runs over real peer memory (skipped on a single-GPU machine): the peer-reduced
+K-split dot against the sum of the ranks' bf16 partials, and the NCCL pattern beside it."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, m, n, k):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    try:
+        from xla_b200 import device_status, sharding
+        from xla_b200.scaled_dot import cublas_lt_matmul_f8
+
+        fused = sharding.PeerReducedRowParallelScaledDot(m, n, device=dev)
+        ks = sharding.row_parallel_slices(k, world, rank)
+        for call in range(3):
+            gen = torch.Generator(device=dev).manual_seed(50 + call)       # same full operands on every rank
+            a = torch.randn((m, k), device=dev, generator=gen).to(torch.float8_e4m3fn)
+            b = torch.randn((k, n), device=dev, generator=gen).to(torch.float8_e4m3fn)
+            sa, sb = torch.tensor(0.25, device=dev), torch.tensor(0.5, device=dev)
+            a_shard, b_shard = a[:, ks].contiguous(), b[ks, :].contiguous()
+            out = fused(a_shard, b_shard, sa, sb)
+            partial = cublas_lt_matmul_f8(a_shard, b_shard, sa, sb)[0]
+            parts = [torch.empty_like(partial) for _ in range(world)]
+            dist.all_gather(parts, partial)
+            acc = torch.zeros((m, n), dtype=torch.float32, device=dev)
+            for p in parts:
+                acc = acc + p.float()
+            torch.cuda.synchronize()
+            assert device_status() == 0
+            assert torch.equal(out, acc.bfloat16()), f"rank {rank} call {call}"
+            # and close to the unsplit dot: each bf16 partial and the sum carry one rounding of 2^-9
+            full = cublas_lt_matmul_f8(a, b, sa, sb, out_dtype=torch.float32)[0]
+            bound = 2.0 ** -8 * (sum(p.float().abs() for p in parts) + full.abs()) + 1e-6
+            assert bool(((out.float() - full).abs() <= bound).all())
+            dist.barrier()                   # the next call's operands are regenerated; keep the ranks in step
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_reduced_dot_on_two_gpus():
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), 1024, 768, 512), nprocs=world, join=True)

@@ -55,7 +55,7 @@ struct __align__(16) DenseAux {
   uint64_t acc_empty_bar[kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
-  float bias_s[kEpilogueWarps][kColsPerEpilogueWarp];      // private per-warp copies: no CTA-level barrier
+  alignas(16) float bias_s[kEpilogueWarps][kColsPerEpilogueWarp];   // private per-warp copies: no CTA-level barrier
   float colscale_s[kEpilogueWarps][kColsPerEpilogueWarp];
 };
 
@@ -76,6 +76,13 @@ struct ReduceArgs {
   uint32_t* flags[kMaxPeers];
   const CUtensorMap* emu_maps;    // emulate: A and B maps of rank r at [2r], [2r+1]
 };
+
+// Peer-reduce mode stages 32 rows x 64 bf16 columns per epilogue warp in shared memory so that
+// every store that crosses NVLink is a full 128-byte line.  Warps 0 and 1 use the (otherwise idle)
+// bias and column-scale arrays, the other six the bytes behind the aux block.
+constexpr int kStoreStageBytes = 32 * 128;
+constexpr size_t kReduceExtraSmem = size_t(kEpilogueWarps - 2) * kStoreStageBytes;
+static_assert(sizeof(float) * kColsPerEpilogueWarp * kEpilogueWarps == kStoreStageBytes, "bias_s holds one warp's store stage");
 
 struct DenseArgs {
   int64_t m, n, k;
@@ -170,55 +177,71 @@ __device__ __forceinline__ void tile_coords_reduce(int32_t tile, const DenseArgs
 constexpr int kChunk = 16;   // accumulator columns handled per epilogue step
 
 // Peer-reduce epilogue for kChunk columns of one row.  The partial is rounded to bf16 (the dot's
-// result type).  For a row another rank owns it goes into that rank's staging buffer; for an own
-// row the bf16 partials of all ranks are added in rank order in f32, rounded once and written to
-// every rank's D.
+// result type).  For a row this rank owns, the bf16 partials of all ranks are added in rank order
+// in f32 and rounded once.  Either way the 16 values go into the warp's store stage (row = lane,
+// 16-byte units XOR-swizzled by the row to spread the banks); flush_store_stage writes them out.
 __device__ __forceinline__ void reduce_chunk(const DenseArgs& p, const uint32_t (&r)[kChunk], float scale, int32_t my_rank,
-                                             int32_t blk, int64_t row, int64_t row_in_block, int64_t rows_per_block,
-                                             int64_t col0) {
+                                             int32_t blk, int64_t row_in_block, int64_t rows_per_block, int64_t col0,
+                                             uint4* stage_row, int unit0, int lane) {
   uint32_t w[kChunk / 2];
 #pragma unroll
   for (int i = 0; i < kChunk / 2; ++i) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale);
     w[i] = *reinterpret_cast<const uint32_t*>(&h);
   }
-  if (blk != my_rank) {
-    uint4* dst = reinterpret_cast<uint4*>(p.red.stage[blk] + (int64_t(my_rank) * rows_per_block + row_in_block) * p.n + col0);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    return;
-  }
-  float acc[kChunk];
+  if (blk == my_rank && p.red.world > 1) {
+    float acc[kChunk];
 #pragma unroll
-  for (int i = 0; i < kChunk; ++i) acc[i] = 0.0f;
-  for (int32_t s = 0; s < p.red.world; ++s) {
-    uint32_t x[kChunk / 2];
-    if (s == my_rank) {
+    for (int i = 0; i < kChunk; ++i) acc[i] = 0.0f;
+    for (int32_t s = 0; s < p.red.world; ++s) {
+      uint32_t x[kChunk / 2];
+      if (s == my_rank) {
 #pragma unroll
-      for (int i = 0; i < kChunk / 2; ++i) x[i] = w[i];
-    } else {
-      const uint4* src = reinterpret_cast<const uint4*>(p.red.stage[my_rank] + (int64_t(s) * rows_per_block + row_in_block) * p.n + col0);
-      const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);      // written by another GPU: never through L1
-      x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
-      x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+        for (int i = 0; i < kChunk / 2; ++i) x[i] = w[i];
+      } else {
+        const uint4* src = reinterpret_cast<const uint4*>(p.red.stage[my_rank] + (int64_t(s) * rows_per_block + row_in_block) * p.n + col0);
+        const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);      // written by another GPU: never through L1
+        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+      }
+#pragma unroll
+      for (int i = 0; i < kChunk / 2; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x[i]));
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
     }
 #pragma unroll
     for (int i = 0; i < kChunk / 2; ++i) {
-      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x[i]));
-      acc[2 * i] += f.x;
-      acc[2 * i + 1] += f.y;
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
   }
+  stage_row[(unit0) ^ (lane & 7)] = make_uint4(w[0], w[1], w[2], w[3]);
+  stage_row[(unit0 + 1) ^ (lane & 7)] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// Writes the warp's 32 x 64 staged values: four full 128-byte rows per store instruction.  Rows
+// another rank owns go to that rank's staging buffer, own rows to every rank's D.
+__device__ __forceinline__ void flush_store_stage(const DenseArgs& p, const uint4* stage, int32_t my_rank, int32_t blk,
+                                                  int64_t row0, int64_t row0_in_block, int64_t rows_per_block, int64_t col0,
+                                                  int lane) {
+  __syncwarp();
+  const int unit = lane & 7;
+  const int64_t col = col0 + unit * 8;
+  if (col < p.n) {
 #pragma unroll
-  for (int i = 0; i < kChunk / 2; ++i) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    for (int it = 0; it < 8; ++it) {
+      const int rrow = it * 4 + (lane >> 3);
+      const uint4 v = stage[rrow * 8 + (unit ^ (rrow & 7))];
+      if (blk != my_rank) {
+        *reinterpret_cast<uint4*>(p.red.stage[blk] + (int64_t(my_rank) * rows_per_block + row0_in_block + rrow) * p.n + col) = v;
+      } else {
+        for (int32_t j = 0; j < p.red.world; ++j) *reinterpret_cast<uint4*>(p.red.d[j] + (row0 + rrow) * p.n + col) = v;
+      }
+    }
   }
-  for (int32_t j = 0; j < p.red.world; ++j) {
-    uint4* dst = reinterpret_cast<uint4*>(p.red.d[j] + row * p.n + col0);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  }
+  __syncwarp();
 }
 
 // Converts and stores kChunk consecutive columns of one row.
@@ -574,6 +597,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if (p.d_scale) d_scale = __ldg(p.d_scale);
     }
     const int64_t rows_per_block = kReduce ? int64_t(p.red.m_tiles_per_block) * S::kTileRows : 0;
+    uint4* const store_stage = reinterpret_cast<uint4*>(
+        ew == 0 ? reinterpret_cast<uint8_t*>(aux->bias_s)
+                : ew == 1 ? reinterpret_cast<uint8_t*>(aux->colscale_s)
+                          : reinterpret_cast<uint8_t*>(aux) + sizeof(DenseAux<kPair>) + (ew - 2) * kStoreStageBytes);
     uint32_t amax_bits = 0;
     long long ep_wait = 0, ep_busy = 0;
     int acc = 0;
@@ -633,7 +660,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         int64_t col0 = col_base + c0;
         if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          if constexpr (kReduce) reduce_chunk(p, ra, scale, my_rank, blk, row, row - int64_t(blk) * rows_per_block, rows_per_block, col0);
+          if constexpr (kReduce) reduce_chunk(p, ra, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
+                                              store_stage + lane * 8, (c0 >> 3) & 7, lane);
           else finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
                                    &amax_bits);
         }
@@ -642,9 +670,17 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         col0 += kChunk;
         if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, row, row - int64_t(blk) * rows_per_block, rows_per_block, col0);
+          if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
+                                              store_stage + lane * 8, ((c0 >> 3) & 7) + 2, lane);
           else finish_chunk<kInt8>(p, rb, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0 + kChunk,
                                    colscale_w + c0 + kChunk, &amax_bits);
+        }
+        if constexpr (kReduce) {
+          if ((c0 & 32) != 0) {            // 64 columns staged: write them out as full lines
+            const int64_t warp_row0 = row - lane;
+            flush_store_stage(p, store_stage, my_rank, blk, warp_row0, warp_row0 - int64_t(blk) * rows_per_block, rows_per_block,
+                              col_base + c0 - 32, lane);
+          }
         }
       }
       if constexpr (kReduce) {
@@ -735,7 +771,7 @@ cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, cons
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = DenseSmemBytes<kPair>();
+  cfg.dynamicSmemBytes = DenseSmemBytes<kPair>() + (kReduce ? kReduceExtraSmem : 0);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -785,7 +821,7 @@ Status InitDenseKernels() {
   set(reinterpret_cast<const void*>(dense_gemm_kernel<true, false>), DenseSmemBytes<false>());
   set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true>), DenseSmemBytes<true>());
   set(reinterpret_cast<const void*>(dense_gemm_kernel<true, true>), DenseSmemBytes<true>());
-  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true, true>), DenseSmemBytes<true>());
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true, true>), DenseSmemBytes<true>() + kReduceExtraSmem);
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(dense): ") + cudaGetErrorString(e));
   // How many CTA pairs fit on the device at once bounds the persistent grid of the pair kernel.
   cudaLaunchConfig_t cfg{};

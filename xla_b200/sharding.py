@@ -195,3 +195,68 @@ class OverlappedRowParallelScaledDot:
             done.record(self.side)
         main.wait_event(done)
         return self.out
+
+
+class PeerReducedRowParallelScaledDot:
+    """K-split scaled dot whose sum is formed inside the dot's kernel over peer memory
+    (b200sd_scaled_dot_f8_peer_reduce): no collective launch at all.  Replaces the dot -> all-reduce
+    pair of xla/service/spmd/dot_handler.cc:2815-2951.
+
+    The output, staging and flag buffers live in symmetric memory (torch.distributed's
+    `_symmetric_memory`, used purely as the allocator / address exchange) so that every rank holds
+    a mapping of every other rank's buffers.  All ranks must call the object the same number of
+    times: the call count is the protocol's epoch.
+    """
+
+    def __init__(self, m: int, n: int, group=None, device=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _native
+
+        self._torch, self._native, self._C = torch, _native, C
+        group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.m, self.n = m, n
+        words = _native.product.b200sd_peer_reduce_flag_words(m, n, self.world)
+        if words == 0:
+            raise ValueError(f"m = {m} must be a multiple of 256 x world ({self.world}) for the peer-reduced dot")
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        self.out = symm.empty((m, n), dtype=torch.bfloat16, device=device)
+        self.stage = symm.empty((m, n), dtype=torch.bfloat16, device=device)
+        self.flags = symm.empty((words,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self._handles = [symm.rendezvous(t, group) for t in (self.out, self.stage, self.flags)]
+        self._handles[2].barrier()                 # every rank's flags are zero before anyone counts on them
+        self.peers = _native.PeerReduceArgs(struct_size=C.sizeof(_native.PeerReduceArgs), world=self.world, rank=self.rank,
+                                            emulate_ranks=0, epoch=0)
+        for r in range(self.world):
+            self.peers.d[r] = self._handles[0].buffer_ptrs[r]
+            self.peers.stage[r] = self._handles[1].buffer_ptrs[r]
+            self.peers.flags[r] = self._handles[2].buffer_ptrs[r]
+        self._err = C.create_string_buffer(512)
+
+    def __call__(self, a_shard, b_shard, a_scale, b_scale, *, lhs_contracting_dim: int = 1, rhs_contracting_dim: int = 0):
+        """Enqueues this rank's part on the current stream; returns the [m,n] bf16 sum (complete on
+        this rank when the stream reaches the end of the kernel)."""
+        from .scaled_dot import XlaFfiError, _dtype_code
+
+        torch, C, native = self._torch, self._C, self._native
+        k = a_shard.shape[1] if lhs_contracting_dim == 1 else a_shard.shape[0]
+        args = native.ScaledDotF8Args(
+            struct_size=C.sizeof(native.ScaledDotF8Args), a=a_shard.data_ptr(), b=b_shard.data_ptr(),
+            a_scale=a_scale.data_ptr(), b_scale=b_scale.data_ptr(), d=self.out.data_ptr(), m=self.m, n=self.n, k=k,
+            a_dtype=_dtype_code(a_shard.dtype), b_dtype=_dtype_code(b_shard.dtype), d_dtype=_dtype_code(self.out.dtype),
+            lhs_contracting_dim=lhs_contracting_dim, rhs_contracting_dim=rhs_contracting_dim, epilogue=1, alpha=1.0,
+            beta=0.0, kernel=0)
+        self.peers.epoch += 1
+        stream = torch.cuda.current_stream(self.out.device).cuda_stream
+        rc = native.product.b200sd_scaled_dot_f8_peer_reduce(args, self.peers, stream, self._err, len(self._err))
+        if rc != 0:
+            self.peers.epoch -= 1
+            raise XlaFfiError(rc, self._err.value.decode(errors="replace"))
+        return self.out
