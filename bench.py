@@ -239,7 +239,8 @@ def gpu_arm(args):
             rs = torch.rand(lm, device=dev, generator=g) * 0.019 + 0.001
             cs = torch.rand(ln, device=dev, generator=g) * 0.019 + 0.001
             d = torch.empty((lm, ln), dtype=torch.bfloat16, device=dev)
-            ops, res = [a, b, rs, cs], [d]
+            ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)   # the s8[] scratch XLA appends to the call
+            ops, res = [a, b, rs, cs], [d, ws]
             call = Int8DotCall(ops, res)
         else:
             a, sa = f8_operand((lm, lk), 1000 * i + 1)           # A replicated (same seed on every rank) unless K-split
@@ -321,7 +322,7 @@ def gpu_arm(args):
         host_in = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in ops]
         for hbuf, o in zip(host_in, ops):
             hbuf.copy_(o)
-        outs = res[:-1] if (kind != "c3") else res                # the workspace is scratch, not a result
+        outs = res[:-1]                                           # the workspace is scratch, not a result
         host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
         h2d = sum(hb.numel() * hb.element_size() for hb in host_in)
         d2h = sum(hb.numel() * hb.element_size() for hb in host_out)

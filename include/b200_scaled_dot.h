@@ -55,7 +55,9 @@ enum {
   B200SD_KERNEL_DENSE = 1,        /* dense kernel, pair or single-CTA instantiation chosen by shape */
   B200SD_KERNEL_SKINNY = 2,       /* split-K kernel for decode shapes */
   B200SD_KERNEL_DENSE_SINGLE = 3, /* one CTA per 128 x 256 tile */
-  B200SD_KERNEL_DENSE_PAIR = 4    /* two-CTA clusters on 256 x 256 tiles (tcgen05 cta_group::2) */
+  B200SD_KERNEL_DENSE_PAIR = 4,   /* two-CTA clusters on 256 x 256 tiles (tcgen05 cta_group::2) */
+  B200SD_KERNEL_DENSE_STREAMK = 5 /* DENSE_PAIR whose tiles past the last full wave are cut along K, one equal share per
+                                     cluster (needs the workspace; plain DENSE_PAIR when the shape has no such tail) */
 };
 
 /* Arguments of one FP8 scaled dot.
@@ -115,6 +117,9 @@ typedef struct B200SD_DotS8 {
   int32_t lhs_contracting_dim;
   int32_t rhs_contracting_dim;
   int32_t kernel;                /* B200SD_KERNEL_AUTO, _DENSE, _DENSE_SINGLE or _DENSE_PAIR */
+  /* Fields below were added later: a caller whose struct_size stops before them gets NULL / 0. */
+  void* workspace;               /* optional scratch (the custom call's s8[] result); lets the kernel balance its last wave */
+  size_t workspace_bytes;
 } B200SD_DotS8;
 
 /* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the

@@ -56,6 +56,7 @@ class DotS8Args(C.Structure):
         ("d_dtype", C.c_int32),
         ("lhs_contracting_dim", C.c_int32), ("rhs_contracting_dim", C.c_int32),
         ("kernel", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 

@@ -2,6 +2,7 @@
 // spreads over GemmRewriter::CreateF8CustomCall, TypesAreSupportedByCublasLt and
 // cuda::BlasLt::GetMatmulPlan), kernel selection (instead of the cuBLASLt autotuner) and launch.
 #include <atomic>
+#include <cstddef>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -137,7 +138,7 @@ Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointe
   if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16 (pad as the rewriter does)");
   if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
   if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
-  if (a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_PAIR) return Status::Error(kInvalidArgument, "unknown kernel selection " + std::to_string(a.kernel));
+  if (a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_STREAMK) return Status::Error(kInvalidArgument, "unknown kernel selection " + std::to_string(a.kernel));
   bool has_bias = false;
   int32_t act = kActNone;
   switch (a.epilogue) {
@@ -176,15 +177,18 @@ Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointe
   return Status::Ok();
 }
 
-Status ValidateS8(const B200SD_DotS8& a, GemmProblem* g, bool check_pointers = true) {
-  if (a.struct_size < sizeof(B200SD_DotS8)) return Status::Error(kInvalidArgument, "B200SD_DotS8.struct_size is smaller than this library's struct");
+Status ValidateS8(const B200SD_DotS8& in, GemmProblem* g, bool check_pointers = true) {
+  // The struct grew by the workspace fields; older callers pass the shorter size and get none.
+  if (in.struct_size < offsetof(B200SD_DotS8, workspace)) return Status::Error(kInvalidArgument, "B200SD_DotS8.struct_size is smaller than this library's struct");
+  B200SD_DotS8 a{};
+  memcpy(&a, &in, in.struct_size < sizeof(a) ? in.struct_size : sizeof(a));
   if (check_pointers && (a.a == nullptr || a.b == nullptr || a.d == nullptr)) return Status::Error(kInvalidArgument, "a, b and d must not be null");
   if (!(a.d_dtype == kS32 || a.d_dtype == kF32 || a.d_dtype == kBF16)) return Status::Error(kInvalidArgument, "output type must be S32, F32 or BF16");
   if (a.d_dtype == kS32 && (a.a_row_scale || a.b_col_scale)) return Status::Error(kInvalidArgument, "dequantisation scales need a floating-point output type");
   if (a.m <= 0 || a.n <= 0 || a.k <= 0) return Status::Error(kInvalidArgument, "m, n and k must be positive");
   if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16");
   if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
-  if (a.kernel == B200SD_KERNEL_SKINNY || a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_PAIR) return Status::Error(kInvalidArgument, "integer dots run on the dense kernel only");
+  if (a.kernel == B200SD_KERNEL_SKINNY || a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_STREAMK) return Status::Error(kInvalidArgument, "integer dots run on the dense kernel only");
   if (a.k > 133144) return Status::Error(kInvalidArgument, "k too large for exact s32 accumulation of s8 products");
   if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
   g->m = a.m; g->n = a.n; g->k = a.k;
@@ -196,6 +200,7 @@ Status ValidateS8(const B200SD_DotS8& a, GemmProblem* g, bool check_pointers = t
   g->a_row_scale = a.a_row_scale; g->b_col_scale = a.b_col_scale;
   g->d_s32 = a.acc_out;
   g->d = a.d; g->d_dtype = a.d_dtype;
+  g->workspace = a.workspace; g->workspace_bytes = a.workspace_bytes;
   return Status::Ok();
 }
 

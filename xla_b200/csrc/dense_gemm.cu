@@ -19,6 +19,8 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <atomic>
+#include <random>
 #include <cstdlib>
 #include <string>
 
@@ -53,6 +55,8 @@ struct __align__(16) DenseAux {
   uint64_t empty_bar[Shape<kPair>::kStages];
   uint64_t acc_full_bar[kAccBufs];
   uint64_t acc_empty_bar[kAccBufs];
+  uint64_t preload_bar;      // stream-K: the finishing share's accumulator holds the earlier shares' sum
+  uint64_t pad_;
   uint32_t tmem_base;
   int abort_flag;
   alignas(16) float bias_s[kEpilogueWarps][kColsPerEpilogueWarp];   // private per-warp copies: no CTA-level barrier
@@ -110,7 +114,17 @@ struct DenseArgs {
   int32_t progress_tiles;   // row-tiles per progress counter
   unsigned long long* timing;   // optional per-CTA wait-time counters (tuning aid), else nullptr
   ReduceArgs red;               // read by the peer-reduce instantiation only
+  // Stream-K tail (pair kernel): the tiles past the last full wave are cut along K into equal
+  // shares, one per cluster.  dp_tiles tiles are worked one per cluster per round; sk_tiles follow.
+  int32_t dp_tiles, sk_tiles;
+  unsigned long long sk_epoch;          // value that marks a partial of THIS launch as written
+  unsigned long long* sk_flags;         // [clusters][2 CTAs][8 warps]
+  uint4* sk_partials;                   // [clusters] raw accumulator tiles, 256 KiB each
 };
+
+constexpr size_t kSkFlagBytes = 16384;                                 // up to 128 clusters x 16 flags x 8 B
+constexpr size_t kSkPartialBytes = size_t(2 * kBM) * kBN * 4;          // one 256 x 256 accumulator tile
+
 
 // Tuning aid: per CTA, [0] cycles the MMA issuer waited for operands, [1] cycles it waited for a
 // free accumulator, [2] its total cycles, [3] cycles the producer waited for a free stage,
@@ -147,6 +161,87 @@ __device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, in
   const int32_t r = tile - g * per_group;
   *mt = first_m + r % gsize;
   *nt = r / gsize;
+}
+
+// What one cluster does, in order: its share of the stream-K tail that does NOT finish a tile
+// (accumulator dumped to the workspace), its whole tiles, then the share that finishes a tile
+// (earlier shares of that tile, dumped by lower-numbered clusters as the first thing they did,
+// are added before the epilogue).  Finishers therefore never wait for work that has not started.
+struct WorkItem {
+  int32_t tile, kb0, kb1;
+  int32_t mode;            // 0 whole tile, 1 dump a partial, 2 finish a tile others contributed to
+};
+struct WorkList {
+  int32_t n_items, dp_count, first_tile, tile_step;
+  int32_t nf_tile, nf_kb0, nf_kb1;     // share that does not finish its tile (nf_tile < 0: none)
+  int32_t fin_tile, fin_kb0;           // share that finishes its tile (fin_tile < 0: none)
+};
+
+__device__ __forceinline__ int64_t sk_bound(const DenseArgs& p, int32_t cluster, int32_t clusters) {
+  return int64_t(cluster) * (int64_t(p.sk_tiles) * p.num_k_blocks) / clusters;
+}
+
+__device__ __forceinline__ WorkList make_work_list(const DenseArgs& p, int32_t cluster, int32_t clusters, int32_t first_tile,
+                                                   int32_t tile_step) {
+  WorkList w;
+  w.first_tile = first_tile;
+  w.tile_step = tile_step;
+  w.dp_count = first_tile < p.dp_tiles ? (p.dp_tiles - first_tile + tile_step - 1) / tile_step : 0;
+  w.nf_tile = -1;
+  w.fin_tile = -1;
+  w.nf_kb0 = w.nf_kb1 = w.fin_kb0 = 0;
+  if (p.sk_tiles > 0) {
+    const int64_t u0 = sk_bound(p, cluster, clusters), u1 = sk_bound(p, cluster + 1, clusters);
+    if (u1 > u0) {
+      const int32_t kb = p.num_k_blocks;
+      const int32_t t_lo = int32_t(u0 / kb), t_hi = int32_t((u1 - 1) / kb);
+      if (t_lo == t_hi) {
+        const int32_t k0 = int32_t(u0 - int64_t(t_lo) * kb), k1 = int32_t(u1 - int64_t(t_lo) * kb);
+        if (k1 == kb) {
+          w.fin_tile = p.dp_tiles + t_lo;
+          w.fin_kb0 = k0;
+        } else {
+          w.nf_tile = p.dp_tiles + t_lo;
+          w.nf_kb0 = k0;
+          w.nf_kb1 = k1;
+        }
+      } else {
+        w.fin_tile = p.dp_tiles + t_lo;
+        w.fin_kb0 = int32_t(u0 - int64_t(t_lo) * kb);
+        w.nf_tile = p.dp_tiles + t_hi;
+        w.nf_kb0 = 0;
+        w.nf_kb1 = int32_t(u1 - int64_t(t_hi) * kb);
+      }
+    }
+  }
+  w.n_items = w.dp_count + (w.nf_tile >= 0 ? 1 : 0) + (w.fin_tile >= 0 ? 1 : 0);
+  return w;
+}
+
+__device__ __forceinline__ WorkItem get_item(const WorkList& w, const DenseArgs& p, int32_t it) {
+  WorkItem x;
+  if (w.nf_tile >= 0) {
+    if (it == 0) {
+      x.tile = w.nf_tile; x.kb0 = w.nf_kb0; x.kb1 = w.nf_kb1; x.mode = 1;
+      return x;
+    }
+    --it;
+  }
+  if (it < w.dp_count) {
+    x.tile = w.first_tile + it * w.tile_step; x.kb0 = 0; x.kb1 = p.num_k_blocks; x.mode = 0;
+    return x;
+  }
+  x.tile = w.fin_tile; x.kb0 = w.fin_kb0; x.kb1 = p.num_k_blocks; x.mode = w.fin_kb0 > 0 ? 2 : 0;
+  return x;
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 // Peer-reduce order: rank r walks the row blocks r+1, r+2, ..., r (its own last), so that what it
@@ -388,7 +483,6 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = kPair ? cluster_cta_rank() : 0u;        // 0 = leader of the pair
-  const int32_t num_tiles = p.num_m_tiles * p.num_n_tiles;
   int32_t first_tile = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
   int32_t tile_step = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
   // Which rank of a contracting-dimension split this CTA works for, and on whose operands.
@@ -407,6 +501,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   }
   const CUtensorMap& tmap_a = *tmap_a_ptr;
   const CUtensorMap& tmap_b = *tmap_b_ptr;
+  const int32_t cluster_id = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
+  const WorkList work = make_work_list(p, cluster_id, kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x), first_tile, tile_step);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -417,6 +513,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       mbar_init(&aux->acc_full_bar[b], 1);
       mbar_init(&aux->acc_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
+    mbar_init(&aux->preload_bar, kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     aux->abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -445,7 +542,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       uint32_t phase = 0;
       bool ok = true;
       long long prod_wait = 0;
-      for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      for (int32_t it = 0; it < work.n_items && ok; ++it) {
+        const WorkItem item = get_item(work, p, it);
+        const int32_t tile = item.tile;
         int32_t mt, nt;
         if constexpr (kReduce) {
           int32_t blk, slot;
@@ -455,7 +554,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         }
         const int32_t row0 = mt * S::kTileRows + int32_t(rank) * kBM;
         const int32_t col0 = nt * kBN + (kPair ? int32_t(rank) * (kBN / 2) : 0);
-        for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+        for (int32_t kb = item.kb0; kb < item.kb1; ++kb) {
           const long long tw = p.timing ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
           if (p.timing) prod_wait += clock64() - tw;
@@ -524,14 +623,22 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int32_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+      for (int32_t it = 0; it < work.n_items && ok; ++it) {
+        const WorkItem item = get_item(work, p, it);
         const long long tw0 = p.timing ? clock64() : 0;
         ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
         if (p.timing) wait_acc += clock64() - tw0;
         if (!ok) break;
+        if (item.mode == 2) {       // the epilogue warps have put the earlier shares' sum into this accumulator
+          const long long tp0 = p.timing ? clock64() : 0;
+          ok = mbar_wait(&aux->preload_bar, 0, abort_flag, p.status, kStatusMmaTimeout);
+          if (p.timing) p.timing[blockIdx.x * 8 + 7] = clock64() - tp0;
+          if (!ok) break;
+        }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+        const bool preloaded = item.mode == 2;
+        for (int32_t kb = item.kb0; kb < item.kb1; ++kb) {
           const long long tw1 = p.timing ? clock64() : 0;
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
           if (p.timing) wait_full += clock64() - tw1;
@@ -541,7 +648,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           const uint64_t b_desc = b_desc0 + uint64_t((stage * S::kBStageBytes) >> 4);
 #pragma unroll
           for (int j = 0; j < kBK / kUmmaK; ++j) {
-            const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+            const uint32_t accumulate = (preloaded || kb > item.kb0 || j > 0) ? 1u : 0u;
             const uint64_t ad = a_desc + uint64_t(j * a_kstep), bd = b_desc + uint64_t(j * b_kstep);
             if (kPair) {
               if (kInt8) umma_i8_pair(d_tmem, ad, bd, p.idesc, accumulate);
@@ -606,7 +713,80 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int32_t tile = first_tile; tile < num_tiles; tile += tile_step) {
+    // Stream-K: index of the item that finishes a tile other clusters worked on (-1: none).
+    const int32_t fin_it = (!kReduce && work.fin_tile >= 0 && work.fin_kb0 > 0) ? work.n_items - 1 : -1;
+    for (int32_t it = 0; it < work.n_items; ++it) {
+      if (!kReduce && fin_it > 0 && it == fin_it - 1) {
+        // The accumulator the finishing share will use is free (this warp has read item it-1's
+        // values out of its part).  Fill this warp's part with the sum of the shares that
+        // lower-numbered clusters dumped when they started, so that the MMAs continue from it and
+        // nothing is left to add at the end.  Runs under the main loop of item `it`.
+        constexpr int kWarpPartU4 = kColsPerEpilogueWarp * 32 / 4;
+        constexpr size_t kSlotU4 = kSkPartialBytes / sizeof(uint4);
+        const int warp_part = int(rank) * kEpilogueWarps + ew;
+        const int32_t clusters = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
+        const int64_t tile_start = int64_t(work.fin_tile - p.dp_tiles) * p.num_k_blocks;
+        int32_t first_contrib = cluster_id;
+        while (first_contrib > 0 && sk_bound(p, first_contrib, clusters) > tile_start) --first_contrib;
+        if (lane == 0) {
+          for (int32_t c = cluster_id - 1; c >= first_contrib && ok; --c) {
+            const unsigned long long* f = p.sk_flags + c * 2 * kEpilogueWarps + warp_part;
+            uint64_t t0 = 0;
+            uint32_t polls = 0;
+            while (ld_acquire_gpu_u64(f) != p.sk_epoch) {
+              if ((++polls & 1023u) == 0) {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (*abort_flag || now - t0 > kWaitLimitNs) {
+                  *abort_flag = 1;
+                  atomicOr(p.status, kStatusFixupTimeout);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        for (int32_t c = cluster_id - 1; c >= first_contrib; --c)    // every lane acquires before it reads the partials
+          (void)ld_acquire_gpu_u64(p.sk_flags + c * 2 * kEpilogueWarps + warp_part);
+        const uint32_t taddr_fin =
+            tmem_base + (uint32_t(q * 32) << 16) + uint32_t((fin_it & 1) * kBN + col_half * kColsPerEpilogueWarp);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kColsPerEpilogueWarp; c0 += kChunk) {
+          uint32_t r[kChunk];
+#pragma unroll
+          for (int i = 0; i < kChunk; ++i) r[i] = 0u;
+          for (int32_t c = first_contrib; c < cluster_id; ++c) {
+            const uint4* src = p.sk_partials + size_t(c) * kSlotU4 + warp_part * kWarpPartU4 + (c0 / kChunk) * 128 + lane;
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __ldcg(src + j * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (kInt8) {
+                r[4 * j] += v[j].x; r[4 * j + 1] += v[j].y; r[4 * j + 2] += v[j].z; r[4 * j + 3] += v[j].w;
+              } else {
+                r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(v[j].x));
+                r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(v[j].y));
+                r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(v[j].z));
+                r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(v[j].w));
+              }
+            }
+          }
+          tmem_st_32x16(taddr_fin + c0, r);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (kPair && rank != 0) mbar_arrive_cluster(map_to_cta(&aux->preload_bar, 0));
+          else mbar_arrive(&aux->preload_bar);
+        }
+      }
+      const WorkItem item = get_item(work, p, it);
+      const int32_t tile = item.tile;
       int32_t mt, nt;
       int32_t blk = 0, slot = 0;
       if constexpr (kReduce) tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
@@ -642,6 +822,17 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         }
       }
 
+      // Stream-K: where this warp's part of a dumped accumulator lives (same lane mapping for the
+      // writer and the reader, 512 contiguous bytes per store instruction), and who contributed.
+      constexpr int kWarpPartU4 = kColsPerEpilogueWarp * 32 / 4;                     // uint4 per warp part
+      constexpr size_t kSlotU4 = kSkPartialBytes / sizeof(uint4);
+      const int warp_part = int(rank) * kEpilogueWarps + ew;
+      auto sk_dump = [&](const uint32_t (&r)[kChunk], int c0) {
+        uint4* dst = p.sk_partials + size_t(cluster_id) * kSlotU4 + warp_part * kWarpPartU4 + (c0 / kChunk) * 128 + lane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[j * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+      };
+
       const int64_t row = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
       const bool row_ok = row < p.m;
       float row_scale = 1.0f;
@@ -658,7 +849,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         tmem_ld_wait_16(ra);
         tmem_ld_32x16(taddr + c0 + kChunk, rb);
         int64_t col0 = col_base + c0;
-        if (col0 < p.n && row_ok) {
+        if (!kReduce && item.mode == 1) {
+          sk_dump(ra, c0);
+        } else if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
           if constexpr (kReduce) reduce_chunk(p, ra, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
                                               store_stage + lane * 8, (c0 >> 3) & 7, lane);
@@ -668,7 +861,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         tmem_ld_wait_16(rb);
         if (c0 + 2 * kChunk < kColsPerEpilogueWarp) tmem_ld_32x16(taddr + c0 + 2 * kChunk, ra);
         col0 += kChunk;
-        if (col0 < p.n && row_ok) {
+        if (!kReduce && item.mode == 1) {
+          sk_dump(rb, c0 + kChunk);
+        } else if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
           if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
                                               store_stage + lane * 8, ((c0 >> 3) & 7) + 2, lane);
@@ -691,6 +886,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           __syncwarp();
           if (lane == 0) red_release_sys_add_u32(p.red.flags[blk] + flag_index, 1u);
         }
+      }
+      if (!kReduce && item.mode == 1) {
+        // The dumped part is complete: publish it to the cluster that finishes this tile.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu_u64(p.sk_flags + cluster_id * 2 * kEpilogueWarps + warp_part, p.sk_epoch);
       }
       if (p.progress != nullptr) {
         // Publish this warp's part of the tile: each lane orders its own stores device-wide, the
@@ -856,6 +1057,18 @@ extern "C" int b200sd_debug_read_timing(unsigned long long* out, int count) {
   return int(cudaMemcpyFromSymbol(out, g_dense_timing, sizeof(unsigned long long) * size_t(count)));
 }
 
+// A 64-bit value no earlier launch of this process has used and that stale workspace contents will
+// not equal by accident: a per-process random tag in the high half, a launch counter in the low half.
+unsigned long long NextDenseEpoch() {
+  static const uint64_t tag = [] {
+    std::random_device rd;
+    const uint64_t t = (uint64_t(rd()) << 32) ^ uint64_t(rd());
+    return (t | (1ull << 62)) & 0xFFFFFFFF00000000ull;
+  }();
+  static std::atomic<uint64_t> counter{1};
+  return tag | (counter.fetch_add(1, std::memory_order_relaxed) & 0xFFFFFFFFull);
+}
+
 uint32_t ProgressIncrement(const GemmProblem& g, int32_t block) {
   // Every epilogue warp of every CTA working on a tile counts once: 8 warps x (2 CTAs for the pair kernel).
   if (g.progress_rows <= 0 || block < 0 || int64_t(block) * g.progress_rows >= g.m) return 0;
@@ -884,7 +1097,7 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   const int max_pairs = MaxPairClusters();
   bool pair = g.m > kBM && max_pairs > 0;           // a second CTA would only compute padding when M <= 128
   if (variant == kKernelDenseSingle) pair = false;
-  if (variant == kKernelDensePair) {
+  if (variant == kKernelDensePair || variant == kKernelDenseStreamK) {
     if (max_pairs <= 0) return Status::Error(kFailedPrecondition, "this device cannot co-schedule CTA pairs for the pair kernel");
     pair = true;
   }
@@ -960,6 +1173,28 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
     grid = int(tiles < DeviceSmCount() ? tiles : DeviceSmCount());
   }
   if (g.max_ctas > 0 && grid > g.max_ctas) grid = pair ? (g.max_ctas >= 2 ? g.max_ctas & ~1 : 2) : g.max_ctas;
+  // Stream-K tail: when the tiles do not fill the last wave, cut the leftover tiles along K so
+  // that every cluster gets the same number of k-blocks.  Needs the caller's workspace for the
+  // partial accumulators and at least one full wave (or a long K) to be worth the extra traffic.
+  p.dp_tiles = int32_t(tiles);
+  p.sk_tiles = 0;
+  // Opt-in (kernel variant DENSE_STREAMK): measured on B200 it does not pay under the 1 kW power cap,
+  // where SMs idling in the last wave let the others clock higher (8192 x 1024 x 8192: 64 us against
+  // 62 us without; 4096^3: 73 against 62).
+  if (pair && variant == kKernelDenseStreamK && g.progress == nullptr && g.workspace != nullptr) {
+    const int clusters = grid / 2;
+    const int64_t rem = tiles % clusters;
+    const int64_t share = rem * p.num_k_blocks / clusters;              // k-blocks per cluster in the tail
+    const size_t need = kSkFlagBytes + size_t(clusters) * kSkPartialBytes;
+    if (tiles > clusters && rem != 0 && share >= 8 && g.workspace_bytes >= need && clusters <= 128 &&
+        (reinterpret_cast<uintptr_t>(g.workspace) & 15) == 0) {
+      p.sk_tiles = int32_t(rem);
+      p.dp_tiles = int32_t(tiles - rem);
+      p.sk_epoch = NextDenseEpoch();
+      p.sk_flags = static_cast<unsigned long long*>(g.workspace);
+      p.sk_partials = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.workspace) + kSkFlagBytes);
+    }
+  }
   if (g.amax != nullptr) {
     cudaError_t e = cudaMemsetAsync(g.amax, 0, sizeof(float), stream);
     if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(amax): ") + cudaGetErrorString(e));
@@ -1024,6 +1259,8 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   p.progress_tiles = 1;
 
   const int64_t tiles = int64_t(p.num_m_tiles) * p.num_n_tiles;
+  p.dp_tiles = int32_t(tiles);
+  p.sk_tiles = 0;
   int clusters_per_rank = r.emulate ? max_pairs / r.world : max_pairs;
   if (clusters_per_rank > tiles) clusters_per_rank = int(tiles);
   if (clusters_per_rank < 1) return Status::Error(kFailedPrecondition, "not enough SMs to emulate this many ranks");

@@ -219,6 +219,12 @@ ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
       return MakeError(3, "the emit_s32 result must be s32[m, n]");
     a.acc_out = static_cast<int32_t*>((*acc)->untyped_data());
   }
+  if (results.size() == want_results + 1) {       // trailing s8[workspace], as GemmWorkspaceRewriteVisitor appends
+    auto ws = results.get<ffi::AnyBuffer>(want_results);
+    if (!ws.has_value()) return ws.error();
+    a.workspace = (*ws)->untyped_data();
+    a.workspace_bytes = (*ws)->size_bytes();
+  }
   *out = a;
   return ffi::Error::Success();
 }

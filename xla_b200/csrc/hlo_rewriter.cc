@@ -634,7 +634,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   const bool f8 = plan->target == "b200$scaled_dot$f8";
   std::string tuple_shape = "(" + plan->d_shape.ToString();
   if (plan->damax) tuple_shape += ", f32[]";
-  if (f8) tuple_shape += ", s8[" + std::to_string(kWorkspaceBytes) + "]";
+  tuple_shape += ", s8[" + std::to_string(kWorkspaceBytes) + "]";   // appended to every cuBLASLt matmul, FP8 or not
   tuple_shape += ")";
   o << "  cc = " << tuple_shape << " custom-call(";
   for (size_t i = 0; i < op_names.size(); ++i) o << (i ? ", " : "") << op_names[i];
@@ -671,7 +671,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   j << "], \"results\": [{\"role\": \"d\", \"dtype\": " << TypeCode(plan->d_shape.type) << ", \"dims\": " << Dims(plan->d_shape)
     << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
   if (plan->damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": [], \"root_index\": " << plan->amax_root_index << "}";
-  if (f8) j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
+  j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
   j << "], \"attrs\": {\"alpha_real\": " << F64(plan->alpha) << ", \"beta\": " << F64(plan->beta) << ", \"epilogue\": " << plan->epilogue
     << ", \"lhs_contracting_dim\": " << plan->lhs_contracting << ", \"rhs_contracting_dim\": " << plan->rhs_contracting
     << ", \"damax_output\": " << (plan->damax ? "true" : "false") << "}}";

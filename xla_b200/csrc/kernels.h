@@ -111,7 +111,8 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
 uint32_t ProgressIncrement(const GemmProblem& g, int32_t block);
 
 // Kernel selection (stands in for cuBLASLt's algorithm index).
-enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2, kKernelDenseSingle = 3, kKernelDensePair = 4 };
+enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2, kKernelDenseSingle = 3, kKernelDensePair = 4,
+                            kKernelDenseStreamK = 5 };
 
 struct LaunchStats {
   int32_t kernel = 0;     // KernelKind actually used

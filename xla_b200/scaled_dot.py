@@ -269,8 +269,9 @@ def cublas_lt_matmul_f8(a, b, a_scale, b_scale, *, c=None, bias=None, d_scale=No
 
 
 def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=None, emit_s32=False,
-                        lhs_contracting_dim=1, rhs_contracting_dim=0, selected_algorithm=0):
-    """s8 x s8 dot; returns (D, acc or None)."""
+                        lhs_contracting_dim=1, rhs_contracting_dim=0, selected_algorithm=0, workspace=None):
+    """s8 x s8 dot; returns (D, acc or None).  `workspace` (an int8 tensor) becomes the trailing
+    scratch result of the call site, as in XLA."""
     torch = _torch()
     m, n = a.shape[1 - lhs_contracting_dim], b.shape[1 - rhs_contracting_dim]
     out_dtype = out_dtype or (torch.int32 if a_row_scale is None else torch.bfloat16)
@@ -281,6 +282,8 @@ def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=N
     if emit_s32:
         acc = torch.empty((m, n), dtype=torch.int32, device=a.device)
         results.append(acc)
+    if workspace is not None:
+        results.append(workspace)
     call = Int8DotCall(operands, results, lhs_contracting_dim=lhs_contracting_dim,
                        rhs_contracting_dim=rhs_contracting_dim, emit_s32=emit_s32,
                        selected_algorithm=selected_algorithm)
