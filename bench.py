@@ -382,7 +382,8 @@ def gpu_arm(args):
         fp8_peak = 2.0 * peaks["bf16_tflops"]
         roof = {"bound": "tensor", "achieved": flops / world / ms / 1e9, "peak": fp8_peak, "unit": "TFLOP/s",
                 "peak_source": f"2 x MEASURED_PEAKS bf16_tflops burst ({peaks['source']}); 8-bit tensor rate is twice bf16",
-                "frac_of_nominal_4500": flops / world / ms / 1e9 / 4500.0}
+                "frac_of_nominal_4500": flops / world / ms / 1e9 / 4500.0,
+                "frac_of_sustained": flops / world / ms / 1e9 / (2.0 * peaks["bf16_tflops_sustained"])}
     roof["frac"] = roof["achieved"] / roof["peak"]
     # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
     # (single GPU, default sizes only; bytes).
