@@ -45,6 +45,7 @@ def parse_args():
     p.add_argument("--workload", default="c1", choices=["c1", "plain", "c2", "c3", "c4"])
     p.add_argument("--overlap", type=int, default=2, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory (default), 1 = NCCL all-reduce of finished "
                    "row blocks on a second stream, 0 = dot then one NCCL all-reduce")
+    p.add_argument("--multicast", type=int, default=1, help="c4 fused: write finished rows through the NVSwitch multicast mapping")
     p.add_argument("--ar-rows", type=int, default=2048, help="c4 overlap: rows of D per all-reduce")
     p.add_argument("--gemm-ctas", type=int, default=132, help="c4 overlap: SMs the dot may occupy")
     p.add_argument("--nccl-ctas", type=int, default=16, help="c4 overlap: CTAs the collective may use (0 = NCCL's choice)")
@@ -264,7 +265,7 @@ def gpu_arm(args):
 
     overlapped = None
     if kind == "c4" and world > 1 and args.overlap == 2:
-        fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=dev) for _ in sets]
+        fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=dev, multicast=bool(args.multicast)) for _ in sets]
         overlapped = [(lambda f=f, ops=ops: f(ops[0], ops[1], ops[2], ops[3])) for f, (_, ops, _) in zip(fused, sets)]
         for i, f in enumerate(fused):                            # results now land in the symmetric buffers
             sets[i] = (sets[i][0], sets[i][1], [f.out] + list(sets[i][2][1:]))
@@ -402,7 +403,8 @@ def gpu_arm(args):
                                 "c4": "config 4: row-parallel FP8 dot + one NCCL all-reduce of bf16 partials"}[kind],
                    "m": m, "n": n, "k": k,
                    "parallelism": ("single GPU" if world == 1 else
-                                   (f"K-split x{world} + all-reduce" + ({2: " formed inside the dot's kernel over peer memory (no collective launch)",
+                                   (f"K-split x{world} + all-reduce" + ({2: " formed inside the dot's kernel over peer memory (no collective launch" +
+                                        (", finished rows via NVSwitch multicast)" if args.multicast else ")"),
                                      1: f" of {args.ar_rows}-row blocks overlapped with the dot ({args.gemm_ctas} SMs dot, "
                                         f"{args.nccl_ctas} CTAs NCCL)"}.get(args.overlap, "") if overlapped is not None else "")
                                     if kind == "c4" else f"N-split x{world}, no collective")),

@@ -220,6 +220,8 @@ typedef struct B200SD_PeerReduce {
   uint32_t* flags[8];
   const void* emu_a[8];
   const void* emu_b[8];
+  void* d_multicast;   /* optional: an NVSwitch multicast address bound to every rank's d (same offset);
+                          finished rows then leave this GPU once and the switch replicates them */
 } B200SD_PeerReduce;
 
 int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200SD_PeerReduce* peers, void* cuda_stream,

@@ -95,3 +95,18 @@ def test_divide_scales_e5m2_bias_relu_and_matrix_bias_modules(cuda_device):
                                            torch.from_numpy(c).to(cuda_device)])
     torch.cuda.synchronize()
     assert o.near_mismatches(exp, back(got), 1e-2, 1e-2)[0] == 0
+
+
+def test_ragged_module_is_padded_and_sliced(cuda_device):
+    text = load("c1_fp8_linear_gelu_amax", {"8192": 200})            # 200 is not a multiple of 16
+    a, b, sa, sb = o.make_f8_operands(7, 200, 200, 200)
+    bias = o.make_bias_bf16(7, 200)
+    out_scale = np.float32(2.0)
+    exp_d, exp_amax = hlo_eval.evaluate(text, [a, b, np.float32(sa), np.float32(sb), bias, out_scale])
+    d, amax = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                               torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device),
+                                               to_dev(bias, "bf16", cuda_device), torch.tensor(out_scale, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert tuple(d.shape) == (200, 200)
+    assert o.fp8_within_n_values(exp_d, back(d.contiguous()), 1) == 0
+    assert float(amax.item()) == pytest.approx(float(exp_amax), rel=1e-3)

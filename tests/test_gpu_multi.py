@@ -17,7 +17,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, m, n, k):
+def _worker(rank, world, port, m, n, k, multicast):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -27,7 +27,7 @@ def _worker(rank, world, port, m, n, k):
         from xla_b200 import device_status, sharding
         from xla_b200.scaled_dot import cublas_lt_matmul_f8
 
-        fused = sharding.PeerReducedRowParallelScaledDot(m, n, device=dev)
+        fused = sharding.PeerReducedRowParallelScaledDot(m, n, device=dev, multicast=multicast)
         ks = sharding.row_parallel_slices(k, world, rank)
         for call in range(3):
             gen = torch.Generator(device=dev).manual_seed(50 + call)       # same full operands on every rank
@@ -55,6 +55,7 @@ def _worker(rank, world, port, m, n, k):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_reduced_dot_on_two_gpus():
+@pytest.mark.parametrize("multicast", [False, True])
+def test_peer_reduced_dot_on_two_gpus(multicast):
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), 1024, 768, 512), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), 1024, 768, 512, multicast), nprocs=world, join=True)

@@ -78,14 +78,27 @@ def test_divide_scales_e5m2_bias_relu_and_matrix_bias():
     assert plan["operands"][3]["param"] == -1 and plan["operands"][3]["constant"] == 1.0
 
 
+def test_ragged_shapes_are_padded_to_16_and_sliced():
+    """PadOperandToMultipleOf16 / the slice of the result (gemm_rewriter.cc:1556-1580; FileCheck'd in
+    gemm_rewriter_fp8_test.cc:521-577)."""
+    hlo, plan = hlo_runner.rewrite(load("c0_scaled_dot_f8", {"256": 250, "512": 500}))
+    assert plan["rewritten"] and (plan["m"], plan["k"], plan["n"]) == (250, 500, 250)
+    assert plan["operands"][0]["dims"] == [250, 500] and plan["operands"][0]["padded_dims"] == [256, 512]
+    assert plan["operands"][2]["padded_dims"] == []                  # scalars are left alone
+    assert plan["results"][0]["dims"] == [250, 250] and plan["results"][0]["padded_dims"] == [256, 256]
+    assert "a_pad = f8e4m3fn[256,512] pad(a, zero" in hlo and "padding=0_6x0_12" in hlo
+    assert "(bf16[256,256], s8[33554432]) custom-call(a_pad, b_pad, a_scale, b_scale)" in hlo
+    assert "d = bf16[250,250] slice(d_full), slice={[0:250], [0:250]}" in hlo
+    _, plan = hlo_runner.rewrite(load("c0_scaled_dot_f8"))
+    assert plan["operands"][0]["padded_dims"] == plan["operands"][0]["dims"]
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
     assert "custom-call" not in hlo
     f32_dot = load("c0_scaled_dot_f8").replace("f8e4m3fn", "f32")
     assert not hlo_runner.rewrite(f32_dot)[1]["rewritten"]
-    ragged = load("c0_scaled_dot_f8", {"256": 250})
-    assert "multiples of 16" in hlo_runner.rewrite(ragged)[1]["reason"]
     # The GELU pre-activation has another user: would need the AUX epilogue, so GELU is not folded
     # and the output then depends on a value the custom call does not produce.
     aux = load("c1_fp8_linear_gelu_amax", {"8192": 64}).replace("tuple(d, amax)", "tuple(d, x)").replace(

@@ -79,6 +79,7 @@ class PeerReduceArgs(C.Structure):
         ("world", C.c_int32), ("rank", C.c_int32), ("emulate_ranks", C.c_int32), ("epoch", C.c_uint32),
         ("d", C.c_void_p * 8), ("stage", C.c_void_p * 8), ("flags", C.c_void_p * 8),
         ("emu_a", C.c_void_p * 8), ("emu_b", C.c_void_p * 8),
+        ("d_multicast", C.c_void_p),
     ]
 
 

@@ -281,6 +281,7 @@ int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200S
   r.rank = peers->rank;
   r.emulate = peers->emulate_ranks;
   r.epoch = peers->epoch;
+  r.d_multicast = peers->d_multicast;
   for (int i = 0; i < kMaxPeers; ++i) {
     r.d[i] = peers->d[i];
     r.stage[i] = peers->stage[i];

@@ -59,14 +59,27 @@ struct __align__(16) DenseAux {
   uint64_t pad_;
   uint32_t tmem_base;
   int abort_flag;
-  alignas(16) float bias_s[kEpilogueWarps][kColsPerEpilogueWarp];   // private per-warp copies: no CTA-level barrier
+};
+
+// Per-column vectors staged per epilogue warp (private copies: no CTA-level barrier).  Not present
+// in the peer-reduce instantiation, which has no bias and spends the space on its store stages.
+struct __align__(16) EpilogueVectors {
+  float bias_s[kEpilogueWarps][kColsPerEpilogueWarp];
   float colscale_s[kEpilogueWarps][kColsPerEpilogueWarp];
 };
 
-template <bool kPair>
+// Peer-reduce mode stages 32 rows x 64 bf16 columns per epilogue warp in shared memory, in the
+// 128-byte-swizzled layout a TMA store reads, so that what crosses NVLink are bulk stores of
+// full lines issued by one lane instead of 16-byte stores from every lane.
+constexpr int kStoreStageBytes = 32 * 128;
+
+// Layout: [pipeline stages][peer-reduce: eight 4 KiB store stages][aux][others: epilogue vectors].
+template <bool kPair, bool kReduce = false>
 constexpr size_t DenseSmemBytes() {
-  return 1024 /*alignment slack*/ + size_t(Shape<kPair>::kStages) * Shape<kPair>::kStageBytes + sizeof(DenseAux<kPair>);
+  return 1024 /*alignment slack*/ + size_t(Shape<kPair>::kStages) * Shape<kPair>::kStageBytes + sizeof(DenseAux<kPair>) +
+         (kReduce ? size_t(kEpilogueWarps) * kStoreStageBytes : sizeof(EpilogueVectors));
 }
+static_assert(DenseSmemBytes<true, true>() <= 232448 && DenseSmemBytes<true, false>() <= 232448, "shared memory budget");
 
 // Peer-reduce mode (see PeerReduceProblem): what the kernel needs of it.
 struct ReduceArgs {
@@ -76,17 +89,18 @@ struct ReduceArgs {
   uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
   int32_t done_index;             // index of that counter in the flag array
   uint16_t* d[kMaxPeers];
+  uint16_t* d_multicast;          // optional: NVSwitch multicast address covering every rank's D
   uint16_t* stage[kMaxPeers];
   uint32_t* flags[kMaxPeers];
   const CUtensorMap* emu_maps;    // emulate: A and B maps of rank r at [2r], [2r+1]
 };
 
-// Peer-reduce mode stages 32 rows x 64 bf16 columns per epilogue warp in shared memory so that
-// every store that crosses NVLink is a full 128-byte line.  Warps 0 and 1 use the (otherwise idle)
-// bias and column-scale arrays, the other six the bytes behind the aux block.
-constexpr int kStoreStageBytes = 32 * 128;
-constexpr size_t kReduceExtraSmem = size_t(kEpilogueWarps - 2) * kStoreStageBytes;
-static_assert(sizeof(float) * kColsPerEpilogueWarp * kEpilogueWarps == kStoreStageBytes, "bias_s holds one warp's store stage");
+// Peer-reduce mode: byte-matrix maps ([m, 2n] bytes, 128 B x 32 row boxes, 128-byte swizzle) of
+// every rank's staging buffer and output, for the epilogue's bulk stores.
+struct ReduceMaps {
+  CUtensorMap stage[kMaxPeers];
+  CUtensorMap d[kMaxPeers];
+};
 
 struct DenseArgs {
   int64_t m, n, k;
@@ -285,25 +299,39 @@ __device__ __forceinline__ void reduce_chunk(const DenseArgs& p, const uint32_t 
     w[i] = *reinterpret_cast<const uint32_t*>(&h);
   }
   if (blk == my_rank && p.red.world > 1) {
+    // The other ranks' partials are requested four ranks at a time before any is used: one memory
+    // latency per group instead of one per rank.
     float acc[kChunk];
 #pragma unroll
     for (int i = 0; i < kChunk; ++i) acc[i] = 0.0f;
-    for (int32_t s = 0; s < p.red.world; ++s) {
-      uint32_t x[kChunk / 2];
-      if (s == my_rank) {
+    const uint16_t* const mine = p.red.stage[my_rank] + row_in_block * p.n + col0;
+    const int64_t slot_stride = rows_per_block * p.n;
+#pragma unroll 1
+    for (int32_t s0 = 0; s0 < p.red.world; s0 += 4) {
+      uint4 lo[4], hi[4];
 #pragma unroll
-        for (int i = 0; i < kChunk / 2; ++i) x[i] = w[i];
-      } else {
-        const uint4* src = reinterpret_cast<const uint4*>(p.red.stage[my_rank] + (int64_t(s) * rows_per_block + row_in_block) * p.n + col0);
-        const uint4 lo = __ldcg(src), hi = __ldcg(src + 1);      // written by another GPU: never through L1
-        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
-        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+      for (int j = 0; j < 4; ++j) {
+        const int32_t s = s0 + j;
+        if (s < p.red.world && s != my_rank) {
+          const uint4* src = reinterpret_cast<const uint4*>(mine + s * slot_stride);
+          lo[j] = __ldcg(src);           // written by another GPU: never through L1
+          hi[j] = __ldcg(src + 1);
+        } else {                         // this rank's own partial takes its place in the rank order
+          lo[j] = make_uint4(w[0], w[1], w[2], w[3]);
+          hi[j] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
       }
 #pragma unroll
-      for (int i = 0; i < kChunk / 2; ++i) {
-        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x[i]));
-        acc[2 * i] += f.x;
-        acc[2 * i + 1] += f.y;
+      for (int j = 0; j < 4; ++j) {
+        if (s0 + j < p.red.world) {
+          const uint32_t x[kChunk / 2] = {lo[j].x, lo[j].y, lo[j].z, lo[j].w, hi[j].x, hi[j].y, hi[j].z, hi[j].w};
+#pragma unroll
+          for (int i = 0; i < kChunk / 2; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x[i]));
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
+          }
+        }
       }
     }
 #pragma unroll
@@ -316,27 +344,37 @@ __device__ __forceinline__ void reduce_chunk(const DenseArgs& p, const uint32_t 
   stage_row[(unit0 + 1) ^ (lane & 7)] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-// Writes the warp's 32 x 64 staged values: four full 128-byte rows per store instruction.  Rows
-// another rank owns go to that rank's staging buffer, own rows to every rank's D.
-__device__ __forceinline__ void flush_store_stage(const DenseArgs& p, const uint4* stage, int32_t my_rank, int32_t blk,
-                                                  int64_t row0, int64_t row0_in_block, int64_t rows_per_block, int64_t col0,
-                                                  int lane) {
-  __syncwarp();
-  const int unit = lane & 7;
-  const int64_t col = col0 + unit * 8;
-  if (col < p.n) {
+// Sends the warp's 32 x 64 staged values on their way.  Rows another rank owns go to that rank's
+// staging buffer, own rows to every rank's D: one bulk tensor store per destination, issued by
+// lane 0 (or, with an NVSwitch multicast mapping of D, multimem stores from every lane).
+// `byte_col` / `row` are the coordinates of the stage's first element in the destination matrix.
+__device__ __forceinline__ void flush_store_stage(const DenseArgs& p, const ReduceMaps& maps, const uint4* stage,
+                                                  int32_t my_rank, int32_t blk, int64_t row0, int64_t row0_in_block,
+                                                  int64_t rows_per_block, int64_t col0, int lane) {
+  if (blk == my_rank && p.red.d_multicast != nullptr) {
+    __syncwarp();
+    const int unit = lane & 7;
+    const int64_t col = col0 + unit * 8;
+    if (col < p.n) {
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int rrow = it * 4 + (lane >> 3);
-      const uint4 v = stage[rrow * 8 + (unit ^ (rrow & 7))];
-      if (blk != my_rank) {
-        *reinterpret_cast<uint4*>(p.red.stage[blk] + (int64_t(my_rank) * rows_per_block + row0_in_block + rrow) * p.n + col) = v;
-      } else {
-        for (int32_t j = 0; j < p.red.world; ++j) *reinterpret_cast<uint4*>(p.red.d[j] + (row0 + rrow) * p.n + col) = v;
+      for (int it = 0; it < 8; ++it) {
+        const int rrow = it * 4 + (lane >> 3);
+        multimem_st_v4(p.red.d_multicast + (row0 + rrow) * p.n + col, stage[rrow * 8 + (unit ^ (rrow & 7))]);
       }
     }
+    __syncwarp();
+    return;
   }
+  fence_proxy_async_smem();        // this lane's writes to the stage become visible to the bulk-copy engine
   __syncwarp();
+  if (lane == 0 && col0 < p.n) {
+    if (blk != my_rank) {
+      tma_store_2d(&maps.stage[blk], stage, int32_t(col0 * 2), int32_t(int64_t(my_rank) * rows_per_block + row0_in_block));
+    } else {
+      for (int32_t j = 0; j < p.red.world; ++j) tma_store_2d(&maps.d[j], stage, int32_t(col0 * 2), int32_t(row0));
+    }
+    tma_store_commit();
+  }
 }
 
 // Converts and stores kChunk consecutive columns of one row.
@@ -469,7 +507,7 @@ __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t 
 template <bool kInt8, bool kPair, bool kReduce = false>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid_constant__ CUtensorMap tmap_b_param,
-                  const DenseArgs p) {
+                  const DenseArgs p, const __grid_constant__ ReduceMaps rmaps) {
   static_assert(!kReduce || (kPair && !kInt8), "peer-reduce mode exists for the FP8 pair kernel only");
   using S = Shape<kPair>;
   constexpr int kStages = S::kStages;
@@ -477,7 +515,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kAStageBytes;
-  DenseAux<kPair>* aux = reinterpret_cast<DenseAux<kPair>*>(smem + kStages * S::kStageBytes);
+  uint8_t* const after_stages = smem + kStages * S::kStageBytes;                  // 1024-byte aligned
+  DenseAux<kPair>* aux = reinterpret_cast<DenseAux<kPair>*>(after_stages + (kReduce ? kEpilogueWarps * kStoreStageBytes : 0));
   volatile int* abort_flag = &aux->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -694,8 +733,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
     const int q = warp & 3;                      // TMEM lane quarter this warp may access
     const int ew = warp - 2;                     // 0..7
     const int col_half = ew >> 2;                // which 128 columns of the tile
-    float* bias_w = aux->bias_s[ew];
-    float* colscale_w = aux->colscale_s[ew];
+    EpilogueVectors* const vecs = reinterpret_cast<EpilogueVectors*>(aux + 1);        // absent in peer-reduce mode
+    float* bias_w = kReduce ? nullptr : vecs->bias_s[ew];
+    float* colscale_w = kReduce ? nullptr : vecs->colscale_s[ew];
     float scale = p.alpha;
     float d_scale = 1.0f;
     if (!kInt8) {
@@ -704,10 +744,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if (p.d_scale) d_scale = __ldg(p.d_scale);
     }
     const int64_t rows_per_block = kReduce ? int64_t(p.red.m_tiles_per_block) * S::kTileRows : 0;
-    uint4* const store_stage = reinterpret_cast<uint4*>(
-        ew == 0 ? reinterpret_cast<uint8_t*>(aux->bias_s)
-                : ew == 1 ? reinterpret_cast<uint8_t*>(aux->colscale_s)
-                          : reinterpret_cast<uint8_t*>(aux) + sizeof(DenseAux<kPair>) + (ew - 2) * kStoreStageBytes);
+    uint4* const store_stage = reinterpret_cast<uint4*>(after_stages + ew * kStoreStageBytes);   // 1024-byte aligned
     uint32_t amax_bits = 0;
     long long ep_wait = 0, ep_busy = 0;
     int acc = 0;
@@ -801,6 +838,25 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
       __syncwarp();
 
+      // Flag of this warp's part of the tile: raised once by the same warp of every other rank.
+      uint32_t* const my_flag_base = kReduce ? p.red.flags[my_rank] : nullptr;
+      const int32_t flag_index = (slot * 2 + int32_t(rank)) * kEpilogueWarps + ew;
+      if constexpr (kReduce) {
+        if (blk == my_rank && p.red.world > 1) {
+          // An own tile: the other ranks pushed their partials long ago.  Confirm that, and pull
+          // them towards the L2 while the tensor cores are still busy with this tile.
+          if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          const int64_t prow = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane - int64_t(blk) * rows_per_block;
+          for (int32_t s = 0; s < p.red.world; ++s) {
+            if (s == my_rank) continue;
+            const uint16_t* line = p.red.stage[my_rank] + (int64_t(s) * rows_per_block + prow) * p.n + col_base;
+            if (col_base < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+            if (col_base + 64 < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(line + 64));
+          }
+        }
+      }
       // Lane 0 does the bounded wait; the warp then agrees on the outcome so that the
       // warp-collective TMEM loads below never run with a partial warp.
       const long long te0 = p.timing ? clock64() : 0;
@@ -811,16 +867,6 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if (!ok) break;
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
       tc_fence_after_sync();
-      // Flag of this warp's part of the tile: raised once by the same warp of every other rank.
-      uint32_t* const my_flag_base = kReduce ? p.red.flags[my_rank] : nullptr;
-      const int32_t flag_index = (slot * 2 + int32_t(rank)) * kEpilogueWarps + ew;
-      if constexpr (kReduce) {
-        if (blk == my_rank && p.red.world > 1) {
-          if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout);
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-          if (!ok) break;
-        }
-      }
 
       // Stream-K: where this warp's part of a dumped accumulator lives (same lane mapping for the
       // writer and the reader, 512 contiguous bytes per store instruction), and who contributed.
@@ -853,8 +899,14 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           sk_dump(ra, c0);
         } else if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          if constexpr (kReduce) reduce_chunk(p, ra, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
-                                              store_stage + lane * 8, (c0 >> 3) & 7, lane);
+          if constexpr (kReduce) {
+            if ((c0 & 32) == 0) {          // a new 64-column group: the bulk store of the previous one must have read the stage
+              if (lane == 0) tma_store_wait_read<0>();
+              __syncwarp();
+            }
+            reduce_chunk(p, ra, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
+                         store_stage + lane * 8, (c0 >> 3) & 7, lane);
+          }
           else finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
                                    &amax_bits);
         }
@@ -873,15 +925,18 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         if constexpr (kReduce) {
           if ((c0 & 32) != 0) {            // 64 columns staged: write them out as full lines
             const int64_t warp_row0 = row - lane;
-            flush_store_stage(p, store_stage, my_rank, blk, warp_row0, warp_row0 - int64_t(blk) * rows_per_block, rows_per_block,
-                              col_base + c0 - 32, lane);
+            flush_store_stage(p, rmaps, store_stage, my_rank, blk, warp_row0, warp_row0 - int64_t(blk) * rows_per_block,
+                              rows_per_block, col_base + c0 - 32, lane);
           }
         }
       }
       if constexpr (kReduce) {
+        if (lane == 0) tma_store_wait_all<0>();     // this warp's bulk stores of the tile have been performed
+        __syncwarp();
         if (blk != my_rank) {
           // The partial is in the owner's staging buffer: make it visible to that GPU, then raise
           // the owner's flag for this warp's part of the tile.
+          asm volatile("fence.proxy.async.global;" ::: "memory");
           __threadfence_system();
           __syncwarp();
           if (lane == 0) red_release_sys_add_u32(p.red.flags[blk] + flag_index, 1u);
@@ -914,6 +969,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
     }
     if constexpr (kReduce) {
+      asm volatile("fence.proxy.async.global;" ::: "memory");
       // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
       // warp of every rank has said the same, so that D is complete here when the kernel ends and
       // nobody overwrites a staging buffer that is still being read.
@@ -968,11 +1024,13 @@ EncodeTiledFn GetEncodeTiled() {
 int g_max_pair_clusters[64];   // co-resident 2-CTA clusters per device, filled by InitDenseKernels
 
 template <bool kInt8, bool kPair, bool kReduce = false>
-cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const DenseArgs& p) {
+cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const DenseArgs& p,
+                      const ReduceMaps* rmaps = nullptr) {
+  static const ReduceMaps no_maps{};
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = DenseSmemBytes<kPair>() + (kReduce ? kReduceExtraSmem : 0);
+  cfg.dynamicSmemBytes = DenseSmemBytes<kPair, kReduce>();
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -981,7 +1039,7 @@ cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, dense_gemm_kernel<kInt8, kPair, kReduce>, ta, tb, p);
+  return cudaLaunchKernelEx(&cfg, dense_gemm_kernel<kInt8, kPair, kReduce>, ta, tb, p, rmaps ? *rmaps : no_maps);
 }
 
 }  // namespace
@@ -1022,7 +1080,7 @@ Status InitDenseKernels() {
   set(reinterpret_cast<const void*>(dense_gemm_kernel<true, false>), DenseSmemBytes<false>());
   set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true>), DenseSmemBytes<true>());
   set(reinterpret_cast<const void*>(dense_gemm_kernel<true, true>), DenseSmemBytes<true>());
-  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true, true>), DenseSmemBytes<true>() + kReduceExtraSmem);
+  set(reinterpret_cast<const void*>(dense_gemm_kernel<false, true, true>), (DenseSmemBytes<true, true>()));
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(dense): ") + cudaGetErrorString(e));
   // How many CTA pairs fit on the device at once bounds the persistent grid of the pair kernel.
   cudaLaunchConfig_t cfg{};
@@ -1277,7 +1335,16 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
     q.stage[i] = static_cast<uint16_t*>(r.stage[i]);
     q.flags[i] = r.flags[i];
   }
+  static const bool timing_on = [] {
+    const char* e = std::getenv("B200SD_TIMING");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (timing_on) {
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_dense_timing);
+    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
+  }
   q.emu_maps = nullptr;
+  q.d_multicast = r.emulate ? nullptr : static_cast<uint16_t*>(r.d_multicast);
 
   auto make_maps = [&](const void* a, const void* b, CUtensorMap* ta, CUtensorMap* tb) {
     Status s = g.a_mn_major ? MakeByteMatrixMap(ta, a, g.k, g.m, 128, kBK) : MakeByteMatrixMap(ta, a, g.m, g.k, kBK, kBM);
@@ -1301,7 +1368,14 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
     st = make_maps(g.a, g.b, &tmap_a, &tmap_b);
     if (!st.ok()) return st;
   }
-  cudaError_t e = LaunchOne<false, true, true>(grid, stream, tmap_a, tmap_b, p);
+  // Maps for the epilogue's bulk stores: each rank's staging buffer and output as [m, 2n]-byte matrices.
+  ReduceMaps rmaps{};
+  for (int i = 0; i < r.world; ++i) {
+    st = MakeByteMatrixMap(&rmaps.stage[i], r.stage[i], g.m, 2 * g.n, 128, 32);
+    if (st.ok()) st = MakeByteMatrixMap(&rmaps.d[i], r.d[i], g.m, 2 * g.n, 128, 32);
+    if (!st.ok()) return st;
+  }
+  cudaError_t e = LaunchOne<false, true, true>(grid, stream, tmap_a, tmap_b, p, &rmaps);
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("dense_gemm_kernel (peer reduce) launch: ") + cudaGetErrorString(e));
   if (stats) {
     stats->kernel = kKernelDensePair;

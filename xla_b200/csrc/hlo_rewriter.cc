@@ -308,6 +308,7 @@ struct Source {
   bool reciprocal = false;   // operand = 1 / parameter (the HLO divided by the scale)
   double constant = 1.0;     // value when param < 0
   Shape shape;
+  Shape padded;              // shape the custom call receives (dimensions rounded up to 16)
   std::string instr;         // name of the instruction in the original module
 };
 
@@ -355,7 +356,7 @@ struct Plan {
   double alpha = 1.0, beta = 0.0;
   bool damax = false, emit_s32 = false;
   std::vector<Source> operands;
-  Shape d_shape;
+  Shape d_shape, d_padded;
   int d_root_index = -1, amax_root_index = -1;   // position in the ROOT tuple (-1: ROOT itself / absent)
   std::string d_instr, amax_instr;     // instructions of the original module the results replace
 };
@@ -499,7 +500,6 @@ Plan Decide(const Graph& g) {
   plan.k = lhs->shape.dims[lc];
   plan.m = lhs->shape.dims[1 - lc];
   plan.n = rhs->shape.dims[1 - rc];
-  if (plan.m % 16 || plan.n % 16 || plan.k % 16) { plan.reason = "dimensions are not multiples of 16 (padding is not implemented)"; return plan; }
 
   if (lhs->shape.type == "s8" && rhs->shape.type == "s8" && dot->shape.type == "s32") {
     // Integer dot; optionally convert(f32) * broadcast(row scale) * broadcast(col scale) -> convert(bf16).
@@ -631,8 +631,29 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
       op_names.push_back(s.instr);
     }
   }
+  // Operands whose dimensions are not multiples of 16 are zero-padded and the result is sliced back
+  // (PadOperandToMultipleOf16 / PadShapeToMultipleOf16, gemm_rewriter.cc:1556-1580).  Zero rows and
+  // columns add nothing to the dot, a zero bias entry keeps act(0) = 0 out of amax.
+  auto round16 = [](int64_t v) { return (v + 15) / 16 * 16; };
+  bool padded = false;
+  for (size_t i = 0; i < plan->operands.size(); ++i) {
+    Source& s = plan->operands[i];
+    s.padded = s.shape;
+    for (int64_t& d : s.padded.dims) d = round16(d);
+    if (s.padded.dims == s.shape.dims) continue;
+    padded = true;
+    const std::string z = "zero" + std::to_string(tmp++), n = s.role + "_pad";
+    o << "  " << z << " = " << s.shape.type << "[] constant(0)\n";
+    o << "  " << n << " = " << s.padded.ToString() << " pad(" << op_names[i] << ", " << z << "), padding=";
+    for (size_t d = 0; d < s.shape.dims.size(); ++d) o << (d ? "x" : "") << "0_" << (s.padded.dims[d] - s.shape.dims[d]);
+    o << "\n";
+    op_names[i] = n;
+  }
+  plan->d_padded = plan->d_shape;
+  for (int64_t& d : plan->d_padded.dims) d = round16(d);
+  const Shape d_logical = plan->d_shape;
   const bool f8 = plan->target == "b200$scaled_dot$f8";
-  std::string tuple_shape = "(" + plan->d_shape.ToString();
+  std::string tuple_shape = "(" + plan->d_padded.ToString();
   if (plan->damax) tuple_shape += ", f32[]";
   tuple_shape += ", s8[" + std::to_string(kWorkspaceBytes) + "]";   // appended to every cuBLASLt matmul, FP8 or not
   tuple_shape += ")";
@@ -647,7 +668,14 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     o << "lhs_contracting_dim = " << plan->lhs_contracting << " : i64, rhs_contracting_dim = " << plan->rhs_contracting
       << " : i64, emit_s32 = false}\n";
   }
-  o << "  d = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
+  if (padded || plan->d_padded.dims != d_logical.dims) {
+    o << "  d_full = " << plan->d_padded.ToString() << " get-tuple-element(cc), index=0\n";
+    o << "  d = " << d_logical.ToString() << " slice(d_full), slice={";
+    for (size_t d = 0; d < d_logical.dims.size(); ++d) o << (d ? ", " : "") << "[0:" << d_logical.dims[d] << "]";
+    o << "}\n";
+  } else {
+    o << "  d = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
+  }
   if (plan->damax) o << "  amax = f32[] get-tuple-element(cc), index=1\n";
   if (root->opcode == "tuple") {
     o << "  ROOT out = " << root->shape.ToString() << " tuple(";
@@ -666,10 +694,10 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     const Source& s = plan->operands[i];
     j << (i ? ", " : "") << "{\"role\": " << JsonStr(s.role) << ", \"param\": " << s.param << ", \"reciprocal\": "
       << (s.reciprocal ? "true" : "false") << ", \"constant\": " << Num(s.constant) << ", \"dtype\": " << TypeCode(s.shape.type)
-      << ", \"dims\": " << Dims(s.shape) << "}";
+      << ", \"dims\": " << Dims(s.shape) << ", \"padded_dims\": " << Dims(s.padded) << "}";
   }
   j << "], \"results\": [{\"role\": \"d\", \"dtype\": " << TypeCode(plan->d_shape.type) << ", \"dims\": " << Dims(plan->d_shape)
-    << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
+    << ", \"padded_dims\": " << Dims(plan->d_padded) << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
   if (plan->damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": [], \"root_index\": " << plan->amax_root_index << "}";
   j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
   j << "], \"attrs\": {\"alpha_real\": " << F64(plan->alpha) << ", \"beta\": " << F64(plan->beta) << ", \"epilogue\": " << plan->epilogue

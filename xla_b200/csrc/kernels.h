@@ -98,6 +98,7 @@ struct PeerReduceProblem {
   int32_t emulate = 0;               // one launch on one GPU plays all ranks (single-GPU testing)
   uint32_t epoch = 1;                // 1, 2, 3, ...; the same on every rank for the same call
   void* d[kMaxPeers] = {};
+  void* d_multicast = nullptr;       // optional NVSwitch multicast mapping of all the d[i]
   void* stage[kMaxPeers] = {};       // m*n bf16 each
   uint32_t* flags[kMaxPeers] = {};   // PeerReduceFlagWords() u32 each, zeroed once
   const void* emu_a[kMaxPeers] = {};

@@ -108,6 +108,13 @@ __device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v)
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// One 16-byte store that NVSwitch replicates into every GPU bound to the multicast address.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // Bounded wait until the counter has reached `target` (wrap-safe: counters only grow).  Same
 // abort / status protocol as mbar_wait.
 __device__ __forceinline__ bool counter_wait(const uint32_t* counter, uint32_t target, volatile int* abort_flag,

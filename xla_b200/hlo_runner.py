@@ -55,12 +55,21 @@ def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
             operands.append((1.0 / params[src["param"]].float()).reshape(()))
         else:
             operands.append(params[src["param"]])
+        if src.get("padded_dims", src["dims"]) != src["dims"]:
+            # the `pad` instructions of the rewritten module: zero-fill up to multiples of 16
+            t = operands[-1]
+            full = torch.zeros(tuple(src["padded_dims"]), dtype=torch.uint8 if t.element_size() == 1 else t.dtype, device=dev)
+            view = t.view(torch.uint8) if t.element_size() == 1 else t
+            full[tuple(slice(0, d) for d in src["dims"])] = view
+            operands[-1] = full.view(t.dtype) if t.element_size() == 1 else full
     results, outputs = [], {}
     for res in plan["results"]:
-        t = torch.empty(tuple(res["dims"]), dtype=_torch_dtype(res["dtype"]), device=dev)
+        alloc = res.get("padded_dims", res["dims"])
+        t = torch.empty(tuple(alloc), dtype=_torch_dtype(res["dtype"]), device=dev)
         results.append(t)
         if res["root_index"] >= -1:
-            outputs[res["root_index"]] = t
+            # the `slice` instruction of the rewritten module
+            outputs[res["root_index"]] = t[tuple(slice(0, d) for d in res["dims"])] if alloc != res["dims"] else t
     attrs = dict(plan["attrs"])
     for key in ("alpha_real", "beta"):                       # f64 attributes, whatever the JSON reader made of them
         attrs[key] = float(attrs[key])

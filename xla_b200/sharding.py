@@ -208,7 +208,7 @@ class PeerReducedRowParallelScaledDot:
     times: the call count is the protocol's epoch.
     """
 
-    def __init__(self, m: int, n: int, group=None, device=None):
+    def __init__(self, m: int, n: int, group=None, device=None, multicast: bool = True):
         import ctypes as C
 
         import torch
@@ -238,6 +238,10 @@ class PeerReducedRowParallelScaledDot:
             self.peers.d[r] = self._handles[0].buffer_ptrs[r]
             self.peers.stage[r] = self._handles[1].buffer_ptrs[r]
             self.peers.flags[r] = self._handles[2].buffer_ptrs[r]
+        # With NVSwitch multicast the finished rows leave this GPU once instead of world-1 times.
+        mc = getattr(self._handles[0], "multicast_ptr", 0) if (multicast and self.world > 1) else 0
+        self.peers.d_multicast = mc or None
+        self.multicast = bool(mc)
         self._err = C.create_string_buffer(512)
 
     def __call__(self, a_shard, b_shard, a_scale, b_scale, *, lhs_contracting_dim: int = 1, rhs_contracting_dim: int = 0):
