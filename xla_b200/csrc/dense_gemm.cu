@@ -367,13 +367,15 @@ __device__ __forceinline__ void flush_store_stage(const DenseArgs& p, const Redu
   }
   fence_proxy_async_smem();        // this lane's writes to the stage become visible to the bulk-copy engine
   __syncwarp();
-  if (lane == 0 && col0 < p.n) {
-    if (blk != my_rank) {
-      tma_store_2d(&maps.stage[blk], stage, int32_t(col0 * 2), int32_t(int64_t(my_rank) * rows_per_block + row0_in_block));
-    } else {
-      for (int32_t j = 0; j < p.red.world; ++j) tma_store_2d(&maps.d[j], stage, int32_t(col0 * 2), int32_t(row0));
+  if (lane == 0) {
+    if (col0 < p.n) {
+      if (blk != my_rank) {
+        tma_store_2d(&maps.stage[blk], stage, int32_t(col0 * 2), int32_t(int64_t(my_rank) * rows_per_block + row0_in_block));
+      } else {
+        for (int32_t j = 0; j < p.red.world; ++j) tma_store_2d(&maps.d[j], stage, int32_t(col0 * 2), int32_t(row0));
+      }
     }
-    tma_store_commit();
+    tma_store_commit();          // also when empty: every tile adds exactly two groups
   }
 }
 
@@ -744,6 +746,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if (p.d_scale) d_scale = __ldg(p.d_scale);
     }
     const int64_t rows_per_block = kReduce ? int64_t(p.red.m_tiles_per_block) * S::kTileRows : 0;
+    uint32_t* pending_flag = nullptr;     // peer-reduce, lane 0: flag of the pushed tile whose stores are still in flight
     uint4* const store_stage = reinterpret_cast<uint4*>(after_stages + ew * kStoreStageBytes);   // 1024-byte aligned
     uint32_t amax_bits = 0;
     long long ep_wait = 0, ep_busy = 0;
@@ -844,7 +847,15 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if constexpr (kReduce) {
         if (blk == my_rank && p.red.world > 1) {
           // An own tile: the other ranks pushed their partials long ago.  Confirm that, and pull
-          // them towards the L2 while the tensor cores are still busy with this tile.
+          // them towards the L2 while the tensor cores are still busy with this tile.  A flag this
+          // warp still owes another rank goes out first: no rank may wait for a peer while it
+          // holds back something a peer waits for.
+          if (lane == 0 && pending_flag != nullptr) {
+            tma_store_wait_all<0>();
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            red_release_sys_add_u32(pending_flag, 1u);
+            pending_flag = nullptr;
+          }
           if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout);
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
@@ -931,15 +942,18 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         }
       }
       if constexpr (kReduce) {
-        if (lane == 0) tma_store_wait_all<0>();     // this warp's bulk stores of the tile have been performed
-        __syncwarp();
-        if (blk != my_rank) {
-          // The partial is in the owner's staging buffer: make it visible to that GPU, then raise
-          // the owner's flag for this warp's part of the tile.
-          asm volatile("fence.proxy.async.global;" ::: "memory");
-          __threadfence_system();
-          __syncwarp();
-          if (lane == 0) red_release_sys_add_u32(p.red.flags[blk] + flag_index, 1u);
+        // Lane 0 issued this tile's bulk stores (two groups).  Waiting for them here would put an
+        // NVLink round trip into every tile, so the owner's flag for a pushed tile is raised one
+        // tile later, when its stores have long been performed.
+        if (lane == 0) {
+          if (pending_flag != nullptr) {
+            if (blk == my_rank && p.red.d_multicast != nullptr) tma_store_wait_all<0>();   // this tile added no groups
+            else tma_store_wait_all<2>();                                                  // all but this tile's two
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            red_release_sys_add_u32(pending_flag, 1u);
+            pending_flag = nullptr;
+          }
+          if (blk != my_rank) pending_flag = p.red.flags[blk] + flag_index;
         }
       }
       if (!kReduce && item.mode == 1) {
@@ -969,7 +983,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
     }
     if constexpr (kReduce) {
-      asm volatile("fence.proxy.async.global;" ::: "memory");
+      if (lane == 0) {
+        tma_store_wait_all<0>();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        if (pending_flag != nullptr) red_release_sys_add_u32(pending_flag, 1u);
+      }
       // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
       // warp of every rank has said the same, so that D is complete here when the kernel ends and
       // nobody overwrites a staging buffer that is still being read.
