@@ -43,9 +43,9 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="c1", choices=["c1", "plain", "c2", "c3", "c4"])
-    p.add_argument("--overlap", type=int, default=2, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory (default), 1 = NCCL all-reduce of finished "
-                   "row blocks on a second stream, 0 = dot then one NCCL all-reduce")
-    p.add_argument("--multicast", type=int, default=1, help="c4 fused: write finished rows through the NVSwitch multicast mapping")
+    p.add_argument("--overlap", type=int, default=-1, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory, 1 = NCCL all-reduce of finished row blocks "
+                   "on a second stream, 0 = dot then one NCCL all-reduce; default: 2 up to 4 GPUs, 0 beyond (measured faster)")
+    p.add_argument("--multicast", type=int, default=0, help="c4 fused: write finished rows through the NVSwitch multicast mapping")
     p.add_argument("--ar-rows", type=int, default=2048, help="c4 overlap: rows of D per all-reduce")
     p.add_argument("--gemm-ctas", type=int, default=132, help="c4 overlap: SMs the dot may occupy")
     p.add_argument("--nccl-ctas", type=int, default=16, help="c4 overlap: CTAs the collective may use (0 = NCCL's choice)")
@@ -264,6 +264,8 @@ def gpu_arm(args):
     assert xla_b200.device_status() == 0
 
     overlapped = None
+    if args.overlap < 0:
+        args.overlap = 2 if world <= 4 else 0
     if kind == "c4" and world > 1 and args.overlap == 2:
         fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=dev, multicast=bool(args.multicast)) for _ in sets]
         overlapped = [(lambda f=f, ops=ops: f(ops[0], ops[1], ops[2], ops[3])) for f, (_, ops, _) in zip(fused, sets)]

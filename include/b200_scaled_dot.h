@@ -94,6 +94,10 @@ typedef struct B200SD_ScaledDotF8 {
   int32_t epilogue;              /* B200SD_EPILOGUE_* */
   float alpha, beta;
   int32_t kernel;                /* B200SD_KERNEL_* */
+  /* Added later: a caller whose struct_size stops before it gets batch_count = 1. */
+  int32_t batch_count;           /* > 1: A, B, C and D carry this leading batch dimension ([batch, m, k] ...,
+                                    dense row-major, lhs/rhs_batch_dims = {0} as in gemm_rewriter_fp8_test.cc:941-991);
+                                    the bias vector, the scales and amax are shared by all batches */
 } B200SD_ScaledDotF8;
 
 /* Arguments of one s8 x s8 dot with s32 accumulation, optionally followed by the dequantising
@@ -120,6 +124,7 @@ typedef struct B200SD_DotS8 {
   /* Fields below were added later: a caller whose struct_size stops before them gets NULL / 0. */
   void* workspace;               /* optional scratch (the custom call's s8[] result); lets the kernel balance its last wave */
   size_t workspace_bytes;
+  int64_t batch_count;           /* > 1: leading batch dimension of A, B, D and acc_out; the scale vectors are shared */
 } B200SD_DotS8;
 
 /* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the

@@ -87,6 +87,26 @@ def test_accepted_arrangements_instantiate(case):
     ScaledDotCall(ops, res, cfg).instantiate()
 
 
+def test_batched_frame_instantiates_and_mismatches_are_rejected():
+    """gemm_rewriter_fp8_test.cc:941-991: rank-3 operands with one leading batch dimension."""
+    cfg = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,), lhs_batch_dimensions=(0,),
+                            rhs_batch_dimensions=(0,))
+    ops = [Buffer(F8E4M3FN, (10, 16, 32)), Buffer(F8E4M3FN, (10, 32, 16)), Buffer(F32, ()), Buffer(F32, ())]
+    ScaledDotCall(ops, [Buffer(F32, (10, 16, 16)), Buffer(S8, (1 << 20,))], cfg).instantiate()
+    with pytest.raises(XlaFfiError) as e:
+        ScaledDotCall(ops, [Buffer(F32, (9, 16, 16)), Buffer(S8, (1 << 20,))], cfg).instantiate()
+    assert e.value.code == 3 and "batch" in e.value.message
+    with pytest.raises(XlaFfiError) as e:                                   # batch attributes on rank-2 operands
+        ScaledDotCall([Buffer(F8E4M3FN, (16, 32)), Buffer(F8E4M3FN, (32, 16)), Buffer(F32, ()), Buffer(F32, ())],
+                      [Buffer(F32, (16, 16))], GemmBackendConfig(lhs_batch_dimensions=(0,), rhs_batch_dimensions=(0,))).instantiate()
+    assert e.value.code == 3
+    cfg2 = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,), lhs_batch_dimensions=(1,),
+                             rhs_batch_dimensions=(0,))
+    with pytest.raises(XlaFfiError) as e:                                   # only a LEADING batch dimension is implemented
+        ScaledDotCall(ops, [Buffer(F32, (10, 16, 16))], cfg2).instantiate()
+    assert e.value.code == 12
+
+
 @pytest.mark.parametrize("mutate,code,needle", [
     (lambda o, r, c: o.__setitem__(0, Buffer(F8E5M2, (256, 512))) or o.__setitem__(1, Buffer(F8E5M2, (512, 256))), 12, "F8E5M2 x F8E5M2"),
     (lambda o, r, c: o.__setitem__(0, Buffer(BF16, (256, 512))), 3, "F8E4M3FN or F8E5M2"),
@@ -101,7 +121,7 @@ def test_accepted_arrangements_instantiate(case):
     (lambda o, r, c: setattr(c, "epilogue", Epilogue.GELU_AUX), 12, "auxiliary"),
     (lambda o, r, c: setattr(c, "damax_output", True), 3, "amax result"),
     (lambda o, r, c: setattr(c, "lhs_contracting_dimensions", (2,)), 3, "lhs_contracting_dim"),
-    (lambda o, r, c: o.__setitem__(0, Buffer(F8E4M3FN, (2, 256, 512))), 12, "rank-2"),
+    (lambda o, r, c: o.__setitem__(0, Buffer(F8E4M3FN, (2, 256, 512))), 12, "rank 2"),
     (lambda o, r, c: (o.__setitem__(0, Buffer(F8E4M3FN, (250, 512))), r.__setitem__(0, Buffer(BF16, (250, 256)))), 3, "multiples of 16"),
     (lambda o, r, c: r.__setitem__(0, Buffer(F8E5M2, (256, 256))) or o.append(Buffer(F32, ())), 12, "type table"),
 ])

@@ -1,0 +1,97 @@
+"""Batched scaled dots: one leading batch dimension on a, b, c and D, lhs/rhs_batch_dims = {0} --
+the form of gemm_rewriter_fp8_test.cc:941-991 (BatchedScaledABUnscaledDF8)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import scaled_dot_oracle as o
+from xla_b200 import device_status
+from xla_b200.scaled_dot import Epilogue, GemmBackendConfig, XlaFfiError, cublas_lt_matmul_f8
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(x, dev, dt):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dev).view(dt)
+
+
+@pytest.mark.parametrize("batch,m,k,n,rc", [(10, 16, 32, 16, 1), (3, 272, 256, 528, 1), (4, 128, 192, 256, 2), (2, 400, 128, 144, 1)])
+def test_batched_scaled_dot_f32_out(cuda_device, batch, m, k, n, rc):
+    """rc is the rhs contracting dimension in the rank-3 index space: 1 -> b is [batch, k, n], 2 -> [batch, n, k]."""
+    rng = np.random.default_rng(batch * 1000 + m)
+    a = o.fp8_encode(rng.standard_normal((batch, m, k), dtype=np.float32) * 4, "e4m3fn")
+    bshape = (batch, k, n) if rc == 1 else (batch, n, k)
+    b = o.fp8_encode(rng.standard_normal(bshape, dtype=np.float32) * 4, "e4m3fn")
+    sa, sb = np.float32(0.5), np.float32(0.25)
+    cfg = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(rc,), lhs_batch_dimensions=(0,),
+                            rhs_batch_dimensions=(0,))
+    d, _ = cublas_lt_matmul_f8(_dev(a, cuda_device, torch.float8_e4m3fn), _dev(b, cuda_device, torch.float8_e4m3fn),
+                               torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device),
+                               out_dtype=torch.float32, config=cfg)
+    torch.cuda.synchronize()
+    assert tuple(d.shape) == (batch, m, n)
+    got = d.cpu().numpy()
+    for i in range(batch):
+        exp = o.scaled_dot_f8(a[i], b[i], sa, sb, rhs_contracting=rc - 1, out_dtype=o.F32)[0]
+        assert o.near_mismatches(exp, got[i], 1e-3, 1e-4)[0] == 0, f"batch {i}"
+    assert device_status() == 0
+
+
+def test_batched_with_bias_gelu_fp8_out_and_amax(cuda_device):
+    batch, m, k, n = 3, 256, 384, 512
+    rng = np.random.default_rng(77)
+    a = o.fp8_encode(rng.standard_normal((batch, m, k), dtype=np.float32) * 2, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((batch, k, n), dtype=np.float32) * 2, "e4m3fn")
+    bias = o.make_bias_bf16(5, n)
+    sa, sb = np.float32(0.05), np.float32(0.04)
+    cfg = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,), lhs_batch_dimensions=(0,),
+                            rhs_batch_dimensions=(0,), epilogue=Epilogue.BIAS_GELU, damax_output=True)
+    d, amax = cublas_lt_matmul_f8(_dev(a, cuda_device, torch.float8_e4m3fn), _dev(b, cuda_device, torch.float8_e4m3fn),
+                                  torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device),
+                                  bias=_dev(bias, cuda_device, torch.int16).view(torch.bfloat16),
+                                  d_scale=torch.tensor(2.0, device=cuda_device), out_dtype=torch.float8_e4m3fn, config=cfg)
+    torch.cuda.synchronize()
+    got = d.view(torch.uint8).cpu().numpy()
+    top = 0.0
+    for i in range(batch):
+        exp, am = o.scaled_dot_f8(a[i], b[i], sa, sb, bias=o.bf16_bits_to_f32(bias), epilogue=o.EPI_BIAS_GELU, d_scale=2.0,
+                                  out_dtype=o.F8E4M3FN, want_amax=True)
+        assert o.fp8_within_n_values(exp, got[i], 1) == 0, f"batch {i}"
+        top = max(top, float(am))
+    assert float(amax.item()) == pytest.approx(top, rel=1e-4)      # one amax over all batches
+    assert device_status() == 0
+
+
+def test_batched_matrix_bias(cuda_device):
+    batch, m, k, n = 2, 128, 128, 256
+    rng = np.random.default_rng(78)
+    a = o.fp8_encode(rng.standard_normal((batch, m, k), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((batch, k, n), dtype=np.float32), "e4m3fn")
+    c = rng.standard_normal((batch, m, n), dtype=np.float32)
+    one = torch.ones((), device=cuda_device)
+    cfg = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,), lhs_batch_dimensions=(0,),
+                            rhs_batch_dimensions=(0,), beta=1.0)
+    d, _ = cublas_lt_matmul_f8(_dev(a, cuda_device, torch.float8_e4m3fn), _dev(b, cuda_device, torch.float8_e4m3fn), one, one,
+                               c=torch.from_numpy(c).to(cuda_device), out_dtype=torch.float32, config=cfg)
+    torch.cuda.synchronize()
+    for i in range(batch):
+        exp = o.scaled_dot_f8(a[i], b[i], 1.0, 1.0, c=c[i], beta=1.0, out_dtype=o.F32)[0]
+        assert o.near_mismatches(exp, d[i].cpu().numpy(), 1e-3, 1e-4)[0] == 0
+
+
+def test_batched_frames_that_must_be_rejected(cuda_device):
+    a = torch.zeros((2, 64, 64), device=cuda_device).to(torch.float8_e4m3fn)
+    b3 = torch.zeros((3, 64, 64), device=cuda_device).to(torch.float8_e4m3fn)
+    one = torch.ones((), device=cuda_device)
+    cfg = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,), lhs_batch_dimensions=(0,),
+                            rhs_batch_dimensions=(0,))
+    with pytest.raises(XlaFfiError) as e:
+        cublas_lt_matmul_f8(a, b3, one, one, config=cfg)
+    assert e.value.code == 3 and "batch" in e.value.message
+    with pytest.raises(XlaFfiError) as e:                         # rank-3 operands without batch attributes
+        cublas_lt_matmul_f8(a, a, one, one, config=GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,)),
+                            out=torch.zeros((2, 64, 64), dtype=torch.bfloat16, device=cuda_device))
+    assert e.value.code == 12
+    cfg.selected_algorithm = 2
+    with pytest.raises(XlaFfiError):                              # the split-K kernel does not take batches
+        cublas_lt_matmul_f8(a, a, one, one, config=cfg)

@@ -126,8 +126,13 @@ int SelectKernel(int64_t m, int64_t n, int64_t k) {
   return kKernelDense;
 }
 
-Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointers = true) {
-  if (a.struct_size < sizeof(B200SD_ScaledDotF8)) return Status::Error(kInvalidArgument, "B200SD_ScaledDotF8.struct_size is smaller than this library's struct");
+Status ValidateF8(const B200SD_ScaledDotF8& in, GemmProblem* g, bool check_pointers = true) {
+  // The struct grew by batch_count; older callers pass the shorter size and get a plain matrix product.
+  if (in.struct_size < offsetof(B200SD_ScaledDotF8, batch_count)) return Status::Error(kInvalidArgument, "B200SD_ScaledDotF8.struct_size is smaller than this library's struct");
+  B200SD_ScaledDotF8 a{};
+  memcpy(&a, &in, in.struct_size < sizeof(a) ? in.struct_size : sizeof(a));
+  if (a.batch_count == 0) a.batch_count = 1;
+  if (a.batch_count < 0 || a.batch_count > (1 << 20)) return Status::Error(kInvalidArgument, "batch_count out of range");
   if (check_pointers && (a.a == nullptr || a.b == nullptr || a.d == nullptr)) return Status::Error(kInvalidArgument, "a, b and d must not be null");
   if (!IsF8(a.a_dtype) || !IsF8(a.b_dtype)) return Status::Error(kInvalidArgument, "operands must be F8E4M3FN or F8E5M2");
   if (a.a_dtype == kF8E5M2 && a.b_dtype == kF8E5M2) return Status::Error(kUnimplemented, "F8E5M2 x F8E5M2 is not a supported FP8 dot (one operand must be F8E4M3FN)");
@@ -174,6 +179,7 @@ Status ValidateF8(const B200SD_ScaledDotF8& a, GemmProblem* g, bool check_pointe
   g->amax = a.amax;
   g->d = a.d; g->d_dtype = a.d_dtype;
   g->workspace = a.workspace; g->workspace_bytes = a.workspace_bytes;
+  g->batch = a.batch_count;
   return Status::Ok();
 }
 
@@ -201,6 +207,8 @@ Status ValidateS8(const B200SD_DotS8& in, GemmProblem* g, bool check_pointers = 
   g->d_s32 = a.acc_out;
   g->d = a.d; g->d_dtype = a.d_dtype;
   g->workspace = a.workspace; g->workspace_bytes = a.workspace_bytes;
+  g->batch = a.batch_count > 0 ? a.batch_count : 1;
+  if (a.batch_count < 0 || a.batch_count > (1 << 20)) return Status::Error(kInvalidArgument, "batch_count out of range");
   return Status::Ok();
 }
 
@@ -223,7 +231,8 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
   Status st = ValidateF8(*args, &g);
   if (!st.ok()) return CopyStatus(st, err, err_len);
   int kernel = args->kernel;
-  if (kernel == B200SD_KERNEL_AUTO) kernel = SelectKernel(g.m, g.n, g.k);
+  if (kernel == B200SD_KERNEL_AUTO) kernel = g.batch > 1 ? B200SD_KERNEL_DENSE : SelectKernel(g.m, g.n, g.k);
+  if (kernel == B200SD_KERNEL_SKINNY && g.batch > 1) return CopyStatus(Status::Error(kInvalidArgument, "the split-K kernel does not take batched dots"), err, err_len);
   if (kernel == B200SD_KERNEL_SKINNY) {
     // The split-K kernel covers the plain scaled dot only; fall back to the dense kernel for the rest
     // or when the caller's workspace is too small.

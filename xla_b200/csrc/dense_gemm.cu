@@ -104,6 +104,7 @@ struct ReduceMaps {
 
 struct DenseArgs {
   int64_t m, n, k;
+  int32_t batch;                 // leading batch dimension of A, B, C and D (1 = plain matrices)
   int32_t num_m_tiles, num_n_tiles, num_k_blocks, raster_group;
   int32_t a_mn_major, b_mn_major;
   uint32_t idesc;
@@ -165,9 +166,13 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
 
-__device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, int32_t* mt, int32_t* nt) {
-  // Groups of `raster_group` row-tiles are swept column by column so that the CTAs running at the
-  // same time share A row-panels and B column-panels in L2.
+__device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, int32_t* mt, int32_t* nt, int32_t* batch) {
+  // Batches one after the other; inside a batch, groups of `raster_group` row-tiles are swept
+  // column by column so that the CTAs running at the same time share A row-panels and B
+  // column-panels in L2.
+  const int32_t per_batch = p.num_m_tiles * p.num_n_tiles;
+  *batch = tile / per_batch;
+  tile -= *batch * per_batch;
   const int32_t per_group = p.raster_group * p.num_n_tiles;
   const int32_t g = tile / per_group;
   const int32_t first_m = g * p.raster_group;
@@ -586,12 +591,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       for (int32_t it = 0; it < work.n_items && ok; ++it) {
         const WorkItem item = get_item(work, p, it);
         const int32_t tile = item.tile;
-        int32_t mt, nt;
+        int32_t mt, nt, bt = 0;
         if constexpr (kReduce) {
           int32_t blk, slot;
           tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
         } else {
-          tile_coords(tile, p, &mt, &nt);
+          tile_coords(tile, p, &mt, &nt, &bt);
         }
         const int32_t row0 = mt * S::kTileRows + int32_t(rank) * kBM;
         const int32_t col0 = nt * kBN + (kPair ? int32_t(rank) * (kBN / 2) : 0);
@@ -607,28 +612,28 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
             if (rank == 0) mbar_arrive_expect_tx(&aux->full_bar[stage], 2 * S::kStageBytes);
             const uint32_t full = map_to_cta(&aux->full_bar[stage], 0);
             if (p.a_mn_major) {
-              tma_load_2d_pair(sa, &tmap_a, full, row0, kb * kBK);
+              tma_load_3d_pair(sa, &tmap_a, full, row0, kb * kBK, bt);
             } else {
-              tma_load_2d_pair(sa, &tmap_a, full, kb * kBK, row0);
+              tma_load_3d_pair(sa, &tmap_a, full, kb * kBK, row0, bt);
             }
             if (p.b_mn_major) {
-              tma_load_2d_pair(sb, &tmap_b, full, col0, kb * kBK);
+              tma_load_3d_pair(sb, &tmap_b, full, col0, kb * kBK, bt);
             } else {
-              tma_load_2d_pair(sb, &tmap_b, full, kb * kBK, col0);
+              tma_load_3d_pair(sb, &tmap_b, full, kb * kBK, col0, bt);
             }
           } else {
             uint64_t* full = &aux->full_bar[stage];
             mbar_arrive_expect_tx(full, S::kStageBytes);
             if (p.a_mn_major) {
-              tma_load_2d(sa, &tmap_a, full, row0, kb * kBK);
+              tma_load_3d(sa, &tmap_a, full, row0, kb * kBK, bt);
             } else {
-              tma_load_2d(sa, &tmap_a, full, kb * kBK, row0);
+              tma_load_3d(sa, &tmap_a, full, kb * kBK, row0, bt);
             }
             if (p.b_mn_major) {
-              tma_load_2d(sb, &tmap_b, full, col0, kb * kBK);
-              tma_load_2d(sb + S::kBStageBytes / 2, &tmap_b, full, col0 + 128, kb * kBK);
+              tma_load_3d(sb, &tmap_b, full, col0, kb * kBK, bt);
+              tma_load_3d(sb + S::kBStageBytes / 2, &tmap_b, full, col0 + 128, kb * kBK, bt);
             } else {
-              tma_load_2d(sb, &tmap_b, full, kb * kBK, col0);
+              tma_load_3d(sb, &tmap_b, full, kb * kBK, col0, bt);
             }
           }
           if (++stage == kStages) {
@@ -827,10 +832,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
       const WorkItem item = get_item(work, p, it);
       const int32_t tile = item.tile;
-      int32_t mt, nt;
+      int32_t mt, nt, bt = 0;
       int32_t blk = 0, slot = 0;
       if constexpr (kReduce) tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
-      else tile_coords(tile, p, &mt, &nt);
+      else tile_coords(tile, p, &mt, &nt, &bt);
       const int64_t col_base = int64_t(nt) * kBN + col_half * kColsPerEpilogueWarp;
       // Stage the per-column vectors of this warp's columns.
       __syncwarp();
@@ -890,10 +895,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         for (int j = 0; j < 4; ++j) dst[j * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
       };
 
-      const int64_t row = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
-      const bool row_ok = row < p.m;
+      const int64_t row_in_batch = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
+      const bool row_ok = row_in_batch < p.m;
       float row_scale = 1.0f;
-      if (kInt8 && p.a_row_scale && row_ok) row_scale = __ldg(p.a_row_scale + row);
+      if (kInt8 && p.a_row_scale && row_ok) row_scale = __ldg(p.a_row_scale + row_in_batch);
+      const int64_t row = int64_t(bt) * p.m + row_in_batch;        // row of the [batch * m, n] view of C and D
       const uint32_t taddr =
           tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN + col_half * kColsPerEpilogueWarp);
 
@@ -1087,6 +1093,26 @@ Status MakeByteMatrixMap(CUtensorMap* map, const void* base, int64_t rows, int64
 
 int MaxPairClusters();
 
+// `batch` row-major [rows, cols] byte matrices stored one after the other, as a 3-D tensor
+// (cols innermost); box = box_cols x box_rows x 1, 128-byte swizzle, out-of-range elements read
+// as zero -- also past the last row of a batch, so tiles never see the next batch's data.
+Status MakeBatchedByteMatrixMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
+                                uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn encode = GetEncodeTiled();
+  if (encode == nullptr) return Status::Error(kInternal, "cuTensorMapEncodeTiled is not available from this driver");
+  if (cols % 16 != 0) return Status::Error(kInvalidArgument, "the minor dimension of an 8-bit operand must be a multiple of 16");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return Status::Error(kInvalidArgument, "operand base address must be 16-byte aligned");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows) * static_cast<cuuint64_t>(cols)};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Status::Error(kInternal, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
+  return Status::Ok();
+}
+
 Status InitDenseKernels() {
   int device = 0;
   cudaGetDevice(&device);
@@ -1178,22 +1204,26 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
     pair = true;
   }
 
+  const int64_t batch = g.batch > 0 ? g.batch : 1;
+  if (batch > 1 && g.progress != nullptr) return Status::Error(kInvalidArgument, "progress reporting is not available for batched dots");
+  if (batch * ((g.m + kBM - 1) / kBM) * ((g.n + kBN - 1) / kBN) > (1ll << 30)) return Status::Error(kInvalidArgument, "too many tiles");
   CUtensorMap tmap_a, tmap_b;
   if (g.a_mn_major) {
-    st = MakeByteMatrixMap(&tmap_a, g.a, g.k, g.m, 128, kBK);       // [k, m], box 128(m) x 128(k)
+    st = MakeBatchedByteMatrixMap(&tmap_a, g.a, batch, g.k, g.m, 128, kBK);       // [k, m], box 128(m) x 128(k)
   } else {
-    st = MakeByteMatrixMap(&tmap_a, g.a, g.m, g.k, kBK, kBM);       // [m, k], box 128(k) x 128(m)
+    st = MakeBatchedByteMatrixMap(&tmap_a, g.a, batch, g.m, g.k, kBK, kBM);       // [m, k], box 128(k) x 128(m)
   }
   if (!st.ok()) return st;
   if (g.b_mn_major) {
-    st = MakeByteMatrixMap(&tmap_b, g.b, g.k, g.n, 128, kBK);       // [k, n], box 128(n) x 128(k)
+    st = MakeBatchedByteMatrixMap(&tmap_b, g.b, batch, g.k, g.n, 128, kBK);       // [k, n], box 128(n) x 128(k)
   } else {
-    st = MakeByteMatrixMap(&tmap_b, g.b, g.n, g.k, kBK, pair ? kBN / 2 : kBN);   // [n, k], box 128(k) x 128|256(n)
+    st = MakeBatchedByteMatrixMap(&tmap_b, g.b, batch, g.n, g.k, kBK, pair ? kBN / 2 : kBN);   // [n, k], box 128(k) x 128|256(n)
   }
   if (!st.ok()) return st;
 
   DenseArgs p{};
   p.m = g.m; p.n = g.n; p.k = g.k;
+  p.batch = int32_t(batch);
   const int tile_rows = pair ? 2 * kBM : kBM;
   p.num_m_tiles = int32_t((g.m + tile_rows - 1) / tile_rows);
   p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
@@ -1241,7 +1271,7 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
     cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
   }
 
-  const int64_t tiles = int64_t(p.num_m_tiles) * p.num_n_tiles;
+  const int64_t tiles = batch * p.num_m_tiles * p.num_n_tiles;
   int grid;
   if (pair) {
     grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
@@ -1307,6 +1337,7 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   const int max_pairs = MaxPairClusters();
   if (max_pairs <= 0) return Status::Error(kFailedPrecondition, "this device cannot co-schedule CTA pairs for the pair kernel");
   if (r.world < 1 || r.world > kMaxPeers || r.rank < 0 || r.rank >= r.world) return Status::Error(kInvalidArgument, "world must be 1..8 and rank inside it");
+  if (g.batch > 1) return Status::Error(kInvalidArgument, "the peer-reduced dot does not take batched dots");
   if (g.int8 || g.d_dtype != kBF16 || g.c != nullptr || g.bias != nullptr || g.activation != kActNone || g.amax != nullptr || g.d_scale != nullptr)
     return Status::Error(kInvalidArgument, "the peer-reduced dot is the plain FP8 scaled dot with a bf16 result");
   if (g.m % (int64_t(r.world) * 2 * kBM) != 0) return Status::Error(kInvalidArgument, "m must be a multiple of 256 x world for the peer-reduced dot");
@@ -1321,6 +1352,7 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
 
   DenseArgs p{};
   p.m = g.m; p.n = g.n; p.k = g.k;
+  p.batch = 1;
   p.num_m_tiles = int32_t(g.m / (2 * kBM));
   p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
@@ -1365,9 +1397,9 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   q.d_multicast = r.emulate ? nullptr : static_cast<uint16_t*>(r.d_multicast);
 
   auto make_maps = [&](const void* a, const void* b, CUtensorMap* ta, CUtensorMap* tb) {
-    Status s = g.a_mn_major ? MakeByteMatrixMap(ta, a, g.k, g.m, 128, kBK) : MakeByteMatrixMap(ta, a, g.m, g.k, kBK, kBM);
+    Status s = g.a_mn_major ? MakeBatchedByteMatrixMap(ta, a, 1, g.k, g.m, 128, kBK) : MakeBatchedByteMatrixMap(ta, a, 1, g.m, g.k, kBK, kBM);
     if (!s.ok()) return s;
-    return g.b_mn_major ? MakeByteMatrixMap(tb, b, g.k, g.n, 128, kBK) : MakeByteMatrixMap(tb, b, g.n, g.k, kBK, kBN / 2);
+    return g.b_mn_major ? MakeBatchedByteMatrixMap(tb, b, 1, g.k, g.n, 128, kBK) : MakeBatchedByteMatrixMap(tb, b, 1, g.n, g.k, kBK, kBN / 2);
   };
   CUtensorMap tmap_a, tmap_b;
   if (r.emulate) {

@@ -27,6 +27,8 @@
 
 #define B200SD_NO_FFI_DECLS 1
 #include "../../include/b200_scaled_dot.h"
+#include <vector>
+
 #include "xla/ffi/api/ffi.h"
 
 namespace ffi = xla::ffi;
@@ -47,6 +49,11 @@ std::optional<double> GetFloat(const ffi::Dictionary& attrs, std::string_view na
   if (attrs.contains<double>(name)) return *attrs.get<double>(name);
   if (attrs.contains<float>(name)) return static_cast<double>(*attrs.get<float>(name));
   return std::nullopt;
+}
+std::optional<std::vector<int64_t>> GetIntArray(const ffi::Dictionary& attrs, std::string_view name) {
+  auto span = attrs.get<ffi::Span<const int64_t>>(name);     // absent (or not an i64 array): no value
+  if (!span.has_value()) return std::nullopt;
+  return std::vector<int64_t>(span->begin(), span->end());
 }
 bool GetBool(const ffi::Dictionary& attrs, std::string_view name, bool dflt) {
   if (attrs.contains<bool>(name)) return *attrs.get<bool>(name);
@@ -98,15 +105,34 @@ ffi::Error DecodeF8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   auto rhs = operands.get<ffi::AnyBuffer>(idx++);
   if (!lhs.has_value()) return lhs.error();
   if (!rhs.has_value()) return rhs.error();
-  if (lhs->dimensions().size() != 2 || rhs->dimensions().size() != 2 || (*d)->dimensions().size() != 2)
-    return MakeError(12, "only rank-2 operands are implemented (batched dots are not)");
-  if (a.lhs_contracting_dim != 0 && a.lhs_contracting_dim != 1) return MakeError(3, "lhs_contracting_dim must be 0 or 1");
-  if (a.rhs_contracting_dim != 0 && a.rhs_contracting_dim != 1) return MakeError(3, "rhs_contracting_dim must be 0 or 1");
-  a.k = lhs->dimensions()[a.lhs_contracting_dim];
-  a.m = lhs->dimensions()[1 - a.lhs_contracting_dim];
-  a.n = rhs->dimensions()[1 - a.rhs_contracting_dim];
-  if (rhs->dimensions()[a.rhs_contracting_dim] != a.k) return MakeError(3, "contracting dimensions of a and b differ");
-  if ((*d)->dimensions()[0] != a.m || (*d)->dimensions()[1] != a.n) return MakeError(3, "result shape is not [m, n]");
+  // Rank 2, or rank 3 with ONE leading batch dimension on a, b and D (lhs_batch_dims = rhs_batch_dims = {0},
+  // the canonical form the rewriter produces, gemm_rewriter_fp8_test.cc:941-991).  Contracting
+  // dimensions are given in the operand's own index space, as DotDimensionNumbers does.
+  const size_t rank = lhs->dimensions().size();
+  if ((rank != 2 && rank != 3) || rhs->dimensions().size() != rank || (*d)->dimensions().size() != rank)
+    return MakeError(12, "operands and result must all have rank 2, or rank 3 with one leading batch dimension");
+  const int64_t bo = rank == 3 ? 1 : 0;                  // offset of the matrix dimensions
+  {
+    auto lb = GetIntArray(attrs, "lhs_batch_dims"), rb = GetIntArray(attrs, "rhs_batch_dims");
+    const bool want = rank == 3;
+    auto ok = [&](const std::optional<std::vector<int64_t>>& v) {
+      if (!v.has_value()) return !want;
+      return want ? (v->size() == 1 && (*v)[0] == 0) : v->empty();
+    };
+    if (!ok(lb) || !ok(rb)) return MakeError(want ? 12 : 3, "lhs_batch_dims and rhs_batch_dims must be {0} for rank-3 operands and empty for rank-2");
+  }
+  a.batch_count = rank == 3 ? static_cast<int32_t>(lhs->dimensions()[0]) : 1;
+  if (rank == 3 && (rhs->dimensions()[0] != lhs->dimensions()[0] || (*d)->dimensions()[0] != lhs->dimensions()[0]))
+    return MakeError(3, "batch dimensions of a, b and the result differ");
+  a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(bo + 1) - bo);
+  a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(bo) - bo);
+  if (a.lhs_contracting_dim != 0 && a.lhs_contracting_dim != 1) return MakeError(3, "lhs_contracting_dim must be one of the two matrix dimensions");
+  if (a.rhs_contracting_dim != 0 && a.rhs_contracting_dim != 1) return MakeError(3, "rhs_contracting_dim must be one of the two matrix dimensions");
+  a.k = lhs->dimensions()[bo + a.lhs_contracting_dim];
+  a.m = lhs->dimensions()[bo + 1 - a.lhs_contracting_dim];
+  a.n = rhs->dimensions()[bo + 1 - a.rhs_contracting_dim];
+  if (rhs->dimensions()[bo + a.rhs_contracting_dim] != a.k) return MakeError(3, "contracting dimensions of a and b differ");
+  if ((*d)->dimensions()[bo] != a.m || (*d)->dimensions()[bo + 1] != a.n) return MakeError(3, "result shape is not [m, n]");
   a.a = lhs->untyped_data();
   a.b = rhs->untyped_data();
   a.a_dtype = static_cast<int32_t>(lhs->element_type());
@@ -117,8 +143,9 @@ ffi::Error DecodeF8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   if (has_c) {
     auto c = operands.get<ffi::AnyBuffer>(idx++);
     if (!c.has_value()) return c.error();
-    if (c->dimensions().size() != 2 || c->dimensions()[0] != a.m || c->dimensions()[1] != a.n)
-      return MakeError(3, "matrix bias c must have shape [m, n]");
+    if (c->dimensions().size() != rank || c->dimensions()[bo] != a.m || c->dimensions()[bo + 1] != a.n ||
+        (rank == 3 && c->dimensions()[0] != a.batch_count))
+      return MakeError(3, "matrix bias c must have the result's shape");
     a.c = c->untyped_data();
     a.c_dtype = static_cast<int32_t>(c->element_type());
   }

@@ -50,6 +50,7 @@ struct Status {
 // `b_mn_major` that B is stored [k,n] (contracting dimension 0).
 struct GemmProblem {
   int64_t m = 0, n = 0, k = 0;
+  int64_t batch = 1;                 // leading batch dimension shared by A, B, C and D (dense kernel only)
   bool int8 = false;                 // s8 x s8 -> s32 accumulate, else FP8 -> f32 accumulate
   int32_t a_dtype = kF8E4M3FN, b_dtype = kF8E4M3FN;
   bool a_mn_major = false, b_mn_major = true;

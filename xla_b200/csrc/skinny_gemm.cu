@@ -624,6 +624,7 @@ extern "C" int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* arg
   GemmProblem g;
   Status st = ValidateF8(*args, &g, /*check_pointers=*/true);
   if (!st.ok()) return fail(st.code, st.message);
+  if (g.batch > 1) return fail(kInvalidArgument, "the no-allocation decode entry point does not take batched dots");
   if (g.m > 128)
     return fail(kInvalidArgument, "the no-allocation decode entry point accepts at most 128 rows of A (m = " +
                                       std::to_string(g.m) + "): its built-in scratch holds one 128 x 128 f32 partial per CTA");

@@ -56,6 +56,8 @@ class GemmBackendConfig:
     beta: float = 0.0
     lhs_contracting_dimensions: Sequence[int] = (1,)
     rhs_contracting_dimensions: Sequence[int] = (0,)
+    lhs_batch_dimensions: Sequence[int] = ()      # () or (0,): one leading batch dimension on a, b, c and D
+    rhs_batch_dimensions: Sequence[int] = ()
     epilogue: Epilogue = Epilogue.DEFAULT
     damax_output: bool = False
     selected_algorithm: int = 0  # 0 automatic; 1 dense; 2 split-K; 3 dense single-CTA; 4 dense CTA-pair
@@ -189,7 +191,11 @@ class FfiCall:
 def _config_attrs(cfg: GemmBackendConfig) -> dict:
     if len(cfg.lhs_contracting_dimensions) != 1 or len(cfg.rhs_contracting_dimensions) != 1:
         raise XlaFfiError(INVALID_ARGUMENT, "exactly one contracting dimension per operand")
+    batch = {}
+    if tuple(cfg.lhs_batch_dimensions) or tuple(cfg.rhs_batch_dimensions):
+        batch = {"lhs_batch_dims": list(cfg.lhs_batch_dimensions), "rhs_batch_dims": list(cfg.rhs_batch_dimensions)}
     return {
+        **batch,
         "alpha_real": float(cfg.alpha_real),
         "alpha_imag": float(cfg.alpha_imag),
         "beta": float(cfg.beta),
@@ -242,9 +248,10 @@ def cublas_lt_matmul_f8(a, b, a_scale, b_scale, *, c=None, bias=None, d_scale=No
     torch = _torch()
     cfg = config or GemmBackendConfig()
     lc, rc = cfg.lhs_contracting_dimensions[0], cfg.rhs_contracting_dimensions[0]
-    m, n = a.shape[1 - lc], b.shape[1 - rc]
+    bo = 1 if tuple(cfg.lhs_batch_dimensions) else 0          # contracting dimensions index the rank-3 operand then
+    m, n = a.shape[bo + 1 - (lc - bo)], b.shape[bo + 1 - (rc - bo)]
     out_dtype = out_dtype or torch.bfloat16
-    d = out if out is not None else torch.empty((m, n), dtype=out_dtype, device=a.device)
+    d = out if out is not None else torch.empty(tuple(a.shape[:bo]) + (m, n), dtype=out_dtype, device=a.device)
     operands = [a, b]
     if cfg.beta != 0.0:
         operands.append(c)
