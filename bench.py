@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized scaled-dot hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|cublaslt] [--workload c1|...]
 
 A "step" is one pass of the hot path over one batch of synthetic input: one custom call through
 the XLA FFI boundary of libb200_scaled_dot.so.  Default workload `c1` is BASELINE config 1:
@@ -41,7 +41,7 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=100)
     p.add_argument("--warmup", type=int, default=5)
-    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--impl", default="ours", choices=["ours", "reference", "cublaslt"])
     p.add_argument("--workload", default="c1", choices=["c1", "plain", "c2", "c3", "c4"])
     p.add_argument("--overlap", type=int, default=-1, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory, 1 = NCCL all-reduce of finished row blocks "
                    "on a second stream, 0 = dot then one NCCL all-reduce; default: 2 up to 4 GPUs, 0 beyond (measured faster)")
@@ -448,9 +448,62 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def cublaslt_arm(args):
+    """The library the reference's GPU path calls (cuBLASLt, reached here through torch._scaled_mm /
+    torch._int_mm), timed on one GPU on the same shapes for a side-by-side note.  It is not the
+    product and not the reference arm: it has no GELU, no amax and no fused dequantisation, so
+    config 1 runs as dot + bias -> bf16 and config 3 as the bare s8 dot -> s32."""
+    import torch
+
+    kind = args.workload
+    m, n, k = workload_dims(args)
+    dev = torch.device("cuda", 0)
+    steps, warmup = args.steps, max(3, args.warmup)
+    sets = []
+    for i in range(2):
+        g = torch.Generator(device=dev).manual_seed(1000 * i + 1)
+        if kind == "c3":
+            sets.append((torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev, generator=g),
+                         torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev, generator=g), None))
+        else:
+            a = torch.randn((m, k), device=dev, generator=g).to(torch.float8_e4m3fn)
+            bt = torch.randn((n, k), device=dev, generator=g).to(torch.float8_e4m3fn)     # column-major B, as cuBLASLt wants it
+            sets.append((a, bt, (torch.randn(n, device=dev, generator=g) * 0.02).bfloat16() if kind == "c1" else None))
+    one = torch.ones((), device=dev)
+
+    def step(i):
+        a, b, bias = sets[i & 1]
+        if kind == "c3":
+            torch._int_mm(a, b)
+        else:
+            torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, bias=bias, out_dtype=torch.bfloat16, use_fast_accum=True)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if kind == "c2":
+        value, unit = (k * n + m * k + 2 * m * n) / ms / 1e6, "GB/s"
+    else:
+        value, unit = 2.0 * m * n * k / ms / 1e9, "TFLOP/s"
+    print(json.dumps({"impl": "cublaslt", "metric": METRIC, "value": value, "unit": unit, "n_gpus": 1, "steps": steps,
+                      "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+                      "config": {"workload": kind, "m": m, "n": n, "k": k,
+                                 "note": "torch._scaled_mm / torch._int_mm (cuBLASLt); no GELU, amax or dequantisation fused"}}),
+          flush=True)
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.impl == "cublaslt":
+        cublaslt_arm(a)
+    elif a.impl == "reference":
         reference_arm(a)
     else:
         gpu_arm(a)
