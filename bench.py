@@ -52,7 +52,7 @@ def parse_args():
     p.add_argument("--m", type=int, default=0)
     p.add_argument("--n", type=int, default=0)
     p.add_argument("--k", type=int, default=0)
-    p.add_argument("--kernel", type=int, default=0, help="0 auto, 1 dense, 2 split-K")
+    p.add_argument("--kernel", type=int, default=0, help="0 auto, 1 dense, 2 split-K, 3 dense single-CTA, 4 dense CTA pair, 5 CTA pair with a stream-K tail")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
     return p.parse_args()
@@ -242,7 +242,7 @@ def gpu_arm(args):
             d = torch.empty((lm, ln), dtype=torch.bfloat16, device=dev)
             ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)   # the s8[] scratch XLA appends to the call
             ops, res = [a, b, rs, cs], [d, ws]
-            call = Int8DotCall(ops, res)
+            call = Int8DotCall(ops, res, selected_algorithm=args.kernel)
         else:
             a, sa = f8_operand((lm, lk), 1000 * i + 1)           # A replicated (same seed on every rank) unless K-split
             b, sb = f8_operand((lk, ln), 1000 * i + 2 + 17 * rank)
