@@ -15,11 +15,13 @@ Timing: W (>=3) untimed warm-up steps, then exactly K steps between two CUDA eve
 launching stream, bracketed by barrier + synchronize; max over ranks.  Two operand/result sets
 are used alternately and together exceed the 126 MB L2, so no step finds its inputs in cache.
 The JSON line also carries: `e2e` (same call with HOST buffers: pinned host -> device copies of
-every input and device -> host copies of every result inside the timed region), `roofline` for the
+every input and device -> host copies of every result inside the timed region, the upload, the
+call and the download of consecutive steps overlapped on three streams), `roofline` for the
 dominant kernel, `cpu_baseline` (the CPU oracle timed on a bounded sample), SM clocks sampled
 through NVML during the timed region, and the number of kernels launched.
 
-`--impl reference` times the reference arithmetic on the host cores instead (XLA's own CPU
+`--impl cublaslt` times the library the reference's GPU path calls on the same shapes (one GPU),
+for the side-by-side note under profiles/.  `--impl reference` times the reference arithmetic on the host cores instead (XLA's own CPU
 backend cannot be built offline, so this is the NumPy/BLAS port in oracle/), on a bounded sample of
 the same workload, and prints the same line with "impl": "reference".
 """
@@ -321,36 +323,62 @@ def gpu_arm(args):
     # ---- end to end with host buffers ----------------------------------------------------------
     e2e = None
     if not args.no_e2e:
-        call, ops, res = sets[0]
-        host_in = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in ops]
-        for hbuf, o in zip(host_in, ops):
+        # Host buffers in pinned memory; every step copies ALL inputs to the device, runs the call through the
+        # FFI boundary and copies ALL results back.  The three legs run on three streams and the two device
+        # operand/result sets alternate, so step i+1's upload and step i-1's download overlap step i's kernel
+        # (PCIe is full duplex); every byte still moves inside the timed region.
+        host_in = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in sets[0][1]]
+        for hbuf, o in zip(host_in, sets[0][1]):
             hbuf.copy_(o)
-        outs = res[:-1]                                           # the workspace is scratch, not a result
-        host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in sets[0][2][:-1]]   # the workspace is scratch, not a result
         h2d = sum(hb.numel() * hb.element_size() for hb in host_in)
         d2h = sum(hb.numel() * hb.element_size() for hb in host_out)
-        e2e_steps = max(3, min(steps, 20))
+        e2e_steps = max(4, min(steps, 20))
+        s_in, s_cmp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        computed = [torch.cuda.Event() for _ in range(2)]
+        downloaded = [torch.cuda.Event() for _ in range(2)]
 
-        def e2e_step():
-            for hbuf, o in zip(host_in, ops):
-                o.copy_(hbuf, non_blocking=True)
-            if overlapped is not None:
-                overlapped[0]()
-            else:
-                call.execute(stream, local_rank)
-                if kind == "c4" and world > 1:
-                    dist.all_reduce(res[0], op=dist.ReduceOp.SUM)
-            for hbuf, o in zip(host_out, outs):
-                hbuf.copy_(o, non_blocking=True)
+        def e2e_step(i):
+            j = i & 1
+            call, ops, res = sets[j]
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(computed[j])                 # set j's operands were last read by step i-2
+                for hbuf, o in zip(host_in, ops):
+                    o.copy_(hbuf, non_blocking=True)
+                in_ready[j].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(in_ready[j])
+                if i >= 2:
+                    s_cmp.wait_event(downloaded[j])              # set j's results were last read by step i-2's download
+                if overlapped is not None:
+                    overlapped[j]()
+                else:
+                    call.execute(s_cmp.cuda_stream, local_rank)
+                    if kind == "c4" and world > 1:
+                        dist.all_reduce(res[0], op=dist.ReduceOp.SUM)
+                computed[j].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(computed[j])
+                for hbuf, o in zip(host_out, res[:-1]):
+                    hbuf.copy_(o, non_blocking=True)
+                downloaded[j].record(s_out)
 
-        for _ in range(2):
-            e2e_step()
+        def e2e_run(n):
+            for st in (s_in, s_cmp, s_out):
+                st.wait_stream(torch.cuda.current_stream(dev))
+            for i in range(n):
+                e2e_step(i)
+            for st in (s_in, s_cmp, s_out):
+                torch.cuda.current_stream(dev).wait_stream(st)
+
+        e2e_run(2)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         e0.record()
-        for _ in range(e2e_steps):
-            e2e_step()
+        e2e_run(e2e_steps)
         e1.record()
         torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
