@@ -177,7 +177,13 @@ def evaluate(text, params):
             lc = _attr_dims(ins["attrs"], "lhs_contracting_dims")[0]
             rc = _attr_dims(ins["attrs"], "rhs_contracting_dims")[0]
             (lt, lv), (rt, rv) = a
-            if lt == "s8":
+            if "lhs_batch_dims" in ins["attrs"]:
+                # one leading batch dimension on both operands: independent dots, stacked
+                assert _attr_dims(ins["attrs"], "lhs_batch_dims") == (0,) and _attr_dims(ins["attrs"], "rhs_batch_dims") == (0,)
+                fl, fr = _to_f32(lt, lv), _to_f32(rt, rv)
+                parts = [o.dot_f32(fl[i], fr[i], lc - 1, rc - 1) for i in range(fl.shape[0])]
+                val = (t, _from_f32(t, np.stack(parts)))
+            elif lt == "s8":
                 val = (t, o.dot_s8(lv, rv, lc, rc))
             else:
                 val = (t, _from_f32(t, o.dot_f32(_to_f32(lt, lv), _to_f32(rt, rv), lc, rc)))

@@ -110,3 +110,18 @@ def test_ragged_module_is_padded_and_sliced(cuda_device):
     assert tuple(d.shape) == (200, 200)
     assert o.fp8_within_n_values(exp_d, back(d.contiguous()), 1) == 0
     assert float(amax.item()) == pytest.approx(float(exp_amax), rel=1e-3)
+
+
+def test_batched_module(cuda_device):
+    rng = np.random.default_rng(9)
+    for shrink, (bt, m, k, n) in [(None, (10, 16, 32, 16)), ({"10": 3, "16": 272, "32": 192}, (3, 272, 192, 272))]:
+        text = load("batched_scaled_ab_f32", shrink)
+        a = o.fp8_encode(rng.standard_normal((bt, m, k), dtype=np.float32) * 2, "e4m3fn")
+        b = o.fp8_encode(rng.standard_normal((bt, k, n), dtype=np.float32) * 2, "e4m3fn")
+        sa, sb = np.float32(0.25), np.float32(0.5)
+        exp = hlo_eval.evaluate(text, [a, b, sa, sb])
+        got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                               torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device)])
+        torch.cuda.synchronize()
+        assert tuple(got.shape) == (bt, m, n)
+        assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0

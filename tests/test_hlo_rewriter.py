@@ -93,6 +93,29 @@ def test_ragged_shapes_are_padded_to_16_and_sliced():
     assert plan["operands"][0]["padded_dims"] == plan["operands"][0]["dims"]
 
 
+def test_batched_dot_lowering_and_interpreter():
+    """BatchedScaledABUnscaledDF8 (gemm_rewriter_fp8_test.cc:941-991): batch dimension 0 stays on the operands, the
+    dimension numbers are kept in the rank-3 index space; no transposes on Blackwell."""
+    text = load("batched_scaled_ab_f32")
+    hlo, plan = hlo_runner.rewrite(text)
+    assert plan["rewritten"] and plan["batch"] == 10 and (plan["m"], plan["k"], plan["n"]) == (16, 32, 16)
+    assert plan["attrs"]["lhs_contracting_dim"] == 2 and plan["attrs"]["rhs_contracting_dim"] == 1
+    assert plan["attrs"]["lhs_batch_dims"] == [0] and plan["attrs"]["rhs_batch_dims"] == [0]
+    assert "(f32[10,16,16], s8[33554432]) custom-call(a, b, a_scale, b_scale)" in hlo
+    # ragged matrix dimensions are padded, the batch dimension is not
+    _, plan = hlo_runner.rewrite(load("batched_scaled_ab_f32", {"10": 7, "16": 20}))
+    assert plan["operands"][0]["padded_dims"] == [7, 32, 32] and plan["results"][0]["padded_dims"] == [7, 32, 32]
+    rng = np.random.default_rng(3)
+    a = o.fp8_encode(rng.standard_normal((10, 16, 32), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((10, 32, 16), dtype=np.float32), "e4m3fn")
+    out = hlo_eval.evaluate(text, [a, b, np.float32(0.5), np.float32(2.0)])
+    for i in range(10):
+        exp = o.scaled_dot_f8(a[i], b[i], 0.5, 2.0, out_dtype=o.F32)[0]
+        np.testing.assert_allclose(out[i], exp, rtol=1e-6, atol=1e-6)
+    mixed = text.replace("rhs_batch_dims={0}", "rhs_batch_dims={2}")
+    assert not hlo_runner.rewrite(mixed)[1]["rewritten"]
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -130,7 +153,8 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 
 
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
-                                  "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32"])
+                                  "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
+                                  "batched_scaled_ab_f32"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""

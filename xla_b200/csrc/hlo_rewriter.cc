@@ -355,6 +355,7 @@ struct Plan {
   int epilogue = 1;                    // GemmBackendConfig.Epilogue number
   double alpha = 1.0, beta = 0.0;
   bool damax = false, emit_s32 = false;
+  int64_t batch = 0;                   // > 0: leading batch dimension of a, b, c and D
   std::vector<Source> operands;
   Shape d_shape, d_padded;
   int d_root_index = -1, amax_root_index = -1;   // position in the ROOT tuple (-1: ROOT itself / absent)
@@ -384,7 +385,7 @@ void MatchF8Epilogue(const Graph& g, Instr* dot, Plan* plan) {
     Instr* other = OtherOperand(g, u, "add", cur);
     if (other == nullptr) continue;
     int pnum;
-    if (other->opcode == "broadcast" && AttrDim(other->attrs, "dimensions", -1) == 1) {
+    if (other->opcode == "broadcast" && AttrDim(other->attrs, "dimensions", -1) == int64_t(cur->shape.dims.size()) - 1) {
       Instr* v = g.Operand(other, 0);
       if (v != nullptr && v->opcode == "convert") v = g.Operand(v, 0);      // f32 bias must be convert(bf16/f16)
       if (v != nullptr && AsParameter(v, &pnum) && v->shape.dims.size() == 1 && v->shape.dims[0] == plan->n &&
@@ -490,18 +491,27 @@ Plan Decide(const Graph& g) {
   Instr* lhs = g.Operand(dot, 0);
   Instr* rhs = g.Operand(dot, 1);
   const int64_t lc = AttrDim(dot->attrs, "lhs_contracting_dims", -2), rc = AttrDim(dot->attrs, "rhs_contracting_dims", -2);
-  if (lhs == nullptr || rhs == nullptr || lc < 0 || rc < 0 || lhs->shape.dims.size() != 2 || rhs->shape.dims.size() != 2 ||
-      dot->attrs.find("batch_dims") != std::string::npos) {
-    plan.reason = "only rank-2 dots with one contracting dimension per operand are handled";
+  // Rank 2, or rank 3 with one leading batch dimension on both operands (the canonical batched form,
+  // gemm_rewriter_fp8_test.cc:941-991).
+  const bool has_batch = dot->attrs.find("batch_dims") != std::string::npos;
+  const size_t rank = lhs ? lhs->shape.dims.size() : 0;
+  const int64_t bo = has_batch ? 1 : 0;
+  if (lhs == nullptr || rhs == nullptr || lc < bo || rc < bo || rank != size_t(2 + bo) || rhs->shape.dims.size() != rank ||
+      lc > bo + 1 || rc > bo + 1 ||
+      (has_batch && (AttrDim(dot->attrs, "lhs_batch_dims", -2) != 0 || AttrDim(dot->attrs, "rhs_batch_dims", -2) != 0 ||
+                     lhs->shape.dims[0] != rhs->shape.dims[0]))) {
+    plan.reason = "only dots of rank 2, or rank 3 with batch dimension 0 on both operands, with one contracting dimension each are handled";
     return plan;
   }
   plan.lhs_contracting = int(lc);
   plan.rhs_contracting = int(rc);
+  plan.batch = has_batch ? lhs->shape.dims[0] : 0;
   plan.k = lhs->shape.dims[lc];
-  plan.m = lhs->shape.dims[1 - lc];
-  plan.n = rhs->shape.dims[1 - rc];
+  plan.m = lhs->shape.dims[bo + (bo + 1 - lc)];
+  plan.n = rhs->shape.dims[bo + (bo + 1 - rc)];
 
   if (lhs->shape.type == "s8" && rhs->shape.type == "s8" && dot->shape.type == "s32") {
+    if (has_batch) { plan.reason = "batched integer dots are not handled"; return plan; }
     // Integer dot; optionally convert(f32) * broadcast(row scale) * broadcast(col scale) -> convert(bf16).
     int pa, pb;
     if (!AsParameter(lhs, &pa) || !AsParameter(rhs, &pb)) { plan.reason = "s8 operands must be parameters"; return plan; }
@@ -639,7 +649,10 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   for (size_t i = 0; i < plan->operands.size(); ++i) {
     Source& s = plan->operands[i];
     s.padded = s.shape;
-    for (int64_t& d : s.padded.dims) d = round16(d);
+    {
+      const size_t first = (plan->batch > 0 && s.padded.dims.size() == 3) ? 1 : 0;      // the batch dimension stays
+      for (size_t d = first; d < s.padded.dims.size(); ++d) s.padded.dims[d] = round16(s.padded.dims[d]);
+    }
     if (s.padded.dims == s.shape.dims) continue;
     padded = true;
     const std::string z = "zero" + std::to_string(tmp++), n = s.role + "_pad";
@@ -650,7 +663,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     op_names[i] = n;
   }
   plan->d_padded = plan->d_shape;
-  for (int64_t& d : plan->d_padded.dims) d = round16(d);
+  for (size_t d = plan->batch > 0 ? 1 : 0; d < plan->d_padded.dims.size(); ++d) plan->d_padded.dims[d] = round16(plan->d_padded.dims[d]);
   const Shape d_logical = plan->d_shape;
   const bool f8 = plan->target == "b200$scaled_dot$f8";
   std::string tuple_shape = "(" + plan->d_padded.ToString();
@@ -663,7 +676,8 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   if (f8) {
     o << "alpha_real = " << F64(plan->alpha) << " : f64, beta = " << F64(plan->beta) << " : f64, epilogue = " << plan->epilogue
       << " : i32, lhs_contracting_dim = " << plan->lhs_contracting << " : i64, rhs_contracting_dim = " << plan->rhs_contracting
-      << " : i64, damax_output = " << (plan->damax ? "true" : "false") << ", selected_config = 0 : i64}\n";
+      << " : i64, damax_output = " << (plan->damax ? "true" : "false")
+      << (plan->batch > 0 ? ", lhs_batch_dims = array<i64: 0>, rhs_batch_dims = array<i64: 0>" : "") << ", selected_config = 0 : i64}\n";
   } else {
     o << "lhs_contracting_dim = " << plan->lhs_contracting << " : i64, rhs_contracting_dim = " << plan->rhs_contracting
       << " : i64, emit_s32 = false}\n";
@@ -702,7 +716,8 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
   j << "], \"attrs\": {\"alpha_real\": " << F64(plan->alpha) << ", \"beta\": " << F64(plan->beta) << ", \"epilogue\": " << plan->epilogue
     << ", \"lhs_contracting_dim\": " << plan->lhs_contracting << ", \"rhs_contracting_dim\": " << plan->rhs_contracting
-    << ", \"damax_output\": " << (plan->damax ? "true" : "false") << "}}";
+    << ", \"damax_output\": " << (plan->damax ? "true" : "false")
+    << (plan->batch > 0 ? ", \"lhs_batch_dims\": [0], \"rhs_batch_dims\": [0]" : "") << "}, \"batch\": " << plan->batch << "}";
   *json = j.str();
   return true;
 }
