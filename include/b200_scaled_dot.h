@@ -152,6 +152,15 @@ size_t b200sd_workspace_bytes(int64_t m, int64_t n, int64_t k);
  * (xla/backends/gpu/autotuner/cublaslt.cc:84-189). */
 int b200sd_select_kernel(int64_t m, int64_t n, int64_t k);
 
+/* Replaces the tuned kernel choices of this process with those in a text file, one per line:
+ *     f8|s8  m  n  k  kernel          (kernel = B200SD_KERNEL_* 1..5; `#` starts a comment)
+ * B200SD_KERNEL_AUTO then uses an entry whose (type, m, n, k) matches exactly and the static rule
+ * otherwise.  The file is what a persisted autotuning result is to the reference
+ * (docs/persisted_autotuning.md; the cuBLASLt backend of the autotuner,
+ * xla/backends/gpu/autotuner/cublaslt.cc:84-189, times the algorithms and keeps the best);
+ * `python -m xla_b200.autotune` writes one.  A malformed file is rejected as a whole. */
+int b200sd_load_config_table(const char* path, int32_t* entries, char* err, size_t err_len);
+
 /* Number of kernels this library has launched in the calling process (for benchmarks). */
 uint64_t b200sd_launch_count(void);
 

@@ -190,3 +190,30 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setattr(_native, "PRODUCT_LIB", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         _native._load(_native.PRODUCT_LIB)
+
+
+def test_config_table_overrides_the_static_choice(tmp_path):
+    """The persisted-tuning stand-in: exact (type, m, n, k) matches win over the static rule; a bad file changes nothing."""
+    import xla_b200
+
+    assert xla_b200.select_kernel(64, 28672, 8192) == 2 and xla_b200.select_kernel(8192, 8192, 8192) == 1
+    good = tmp_path / "table.txt"
+    good.write_text("# comment\nf8 64 28672 8192 3   # dense single-CTA here\n\ns8 4096 4096 4096 5\nf8 8192 8192 8192 4\n")
+    assert xla_b200.load_config_table(good) == 3
+    assert xla_b200.select_kernel(64, 28672, 8192) == 3 and xla_b200.select_kernel(8192, 8192, 8192) == 4
+    assert xla_b200.select_kernel(128, 28672, 8192) == 2              # no entry: static rule
+    bad = tmp_path / "bad.txt"
+    bad.write_text("f8 64 28672 8192 9\n")
+    with pytest.raises(XlaFfiError) as e:
+        xla_b200.load_config_table(bad)
+    assert e.value.code == 3 and "bad.txt:1" in e.value.message
+    assert xla_b200.select_kernel(64, 28672, 8192) == 3               # still the good table
+    with pytest.raises(XlaFfiError):
+        xla_b200.load_config_table(tmp_path / "missing.txt")
+    with pytest.raises(XlaFfiError):
+        (tmp_path / "s8skinny.txt").write_text("s8 64 4096 4096 2\n")
+        xla_b200.load_config_table(tmp_path / "s8skinny.txt")
+    empty = tmp_path / "empty.txt"
+    empty.write_text("# nothing\n")
+    assert xla_b200.load_config_table(empty) == 0                     # and back to the static rule for later tests
+    assert xla_b200.select_kernel(64, 28672, 8192) == 2

@@ -18,4 +18,6 @@ from .scaled_dot import (  # noqa: F401
     cublas_lt_matmul_s8,
     device_status,
     launch_count,
+    load_config_table,
+    select_kernel,
 )

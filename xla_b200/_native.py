@@ -95,6 +95,7 @@ product.b200sd_check_dot_s8.argtypes = [C.POINTER(DotS8Args), *_ERR]
 product.b200sd_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
 product.b200sd_workspace_bytes.restype = C.c_size_t
 product.b200sd_select_kernel.argtypes = [C.c_int64, C.c_int64, C.c_int64]
+product.b200sd_load_config_table.argtypes = [C.c_char_p, C.POINTER(C.c_int32), *_ERR]
 product.b200sd_launch_count.restype = C.c_uint64
 product.b200sd_device_status.argtypes = [C.POINTER(C.c_uint32), *_ERR]
 product.b200sd_wait_probe.argtypes = [C.c_uint64, C.c_void_p, *_ERR]

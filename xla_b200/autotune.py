@@ -1,0 +1,106 @@
+"""Times the kernel variants on given shapes and writes the table `b200sd_load_config_table` reads.
+
+    python -m xla_b200.autotune --out table.txt [--shape f8:8192x8192x8192 ...] [--iters 20]
+
+The offline counterpart of the reference's cuBLASLt autotuner backend
+(xla/backends/gpu/autotuner/cublaslt.cc:84-189: enumerate the algorithms of a GEMM, time each, keep the
+best) and of its persisted result (docs/persisted_autotuning.md).  Shapes are `f8:MxNxK` or `s8:MxNxK`
+(A is [M,K], B is [K,N], row-major).  Point B200SD_CONFIG_TABLE at the file, or load it with
+`xla_b200.load_config_table(path)`, and B200SD_KERNEL_AUTO / selected_config = 0 follows it.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import sys
+
+from . import _native
+
+# Configs of the benchmark plus their per-GPU shards.
+DEFAULT_SHAPES = ["f8:8192x8192x8192", "f8:8192x4096x8192", "f8:8192x2048x8192", "f8:8192x1024x8192", "f8:4096x4096x4096",
+                  "f8:16x28672x8192", "f8:64x28672x8192", "f8:128x28672x8192", "f8:8192x8192x14336", "f8:8192x8192x7168",
+                  "s8:4096x4096x4096"]
+KERNEL_NAMES = {1: "dense", 2: "split-K", 3: "dense single-CTA", 4: "dense CTA pair", 5: "CTA pair + stream-K tail"}
+
+
+def candidates(kind: str, m: int, n: int, k: int):
+    out = [3, 4, 5] if m > 128 else [3]
+    if kind == "f8" and m <= 128 and _native.product.b200sd_workspace_bytes(m, n, k) > 0:
+        out.append(2)
+    return out
+
+
+def time_variant(kind: str, m: int, n: int, k: int, kernel: int, iters: int):
+    import torch
+
+    from .scaled_dot import GemmBackendConfig, Int8DotCall, ScaledDotCall
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    calls = []
+    for i in range(2):                                   # two operand sets, so a launch never finds its inputs in L2
+        ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)
+        if kind == "s8":
+            a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+            b = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev)
+            d = torch.empty((m, n), dtype=torch.int32, device=dev)
+            calls.append((Int8DotCall([a, b], [d, ws], selected_algorithm=kernel), (a, b, d, ws)))
+        else:
+            a = torch.randn((m, k), device=dev).to(torch.float8_e4m3fn)
+            b = torch.randn((k, n), device=dev).to(torch.float8_e4m3fn)
+            one = torch.ones((), device=dev)
+            d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            calls.append((ScaledDotCall([a, b, one, one], [d, ws], GemmBackendConfig(selected_algorithm=kernel)), (a, b, d, ws, one)))
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ordinal = dev.index or 0
+    for c, _ in calls:
+        c.run(stream, ordinal)
+    for i in range(3):
+        calls[i & 1][0].execute(stream, ordinal)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        calls[i & 1][0].execute(stream, ordinal)
+    e1.record()
+    torch.cuda.synchronize()
+    for c, _ in calls:
+        c.close()
+    return e0.elapsed_time(e1) / iters
+
+
+def parse_shape(text: str):
+    kind, dims = text.split(":")
+    m, n, k = (int(x) for x in dims.lower().split("x"))
+    if kind not in ("f8", "s8"):
+        raise ValueError(f"shape {text}: type must be f8 or s8")
+    return kind, m, n, k
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--shape", action="append", default=None, help="f8:MxNxK or s8:MxNxK; may repeat")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args(argv)
+    lines = ["# type m n k kernel   (written by python -m xla_b200.autotune; times in ms per launch)"]
+    for text in args.shape or DEFAULT_SHAPES:
+        kind, m, n, k = parse_shape(text)
+        timings = {kern: time_variant(kind, m, n, k, kern, args.iters) for kern in candidates(kind, m, n, k)}
+        best = min(timings, key=timings.get)
+        detail = ", ".join(f"{KERNEL_NAMES[kk]} {t:.4f}" for kk, t in sorted(timings.items()))
+        lines.append(f"{kind} {m} {n} {k} {best}   # {detail}")
+        print(lines[-1], flush=True)
+    with open(args.out, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    err = C.create_string_buffer(512)
+    n_entries = C.c_int32(0)
+    rc = _native.product.b200sd_load_config_table(args.out.encode(), C.byref(n_entries), err, len(err))
+    if rc != 0:
+        print(f"the written table does not load: {err.value.decode()}", file=sys.stderr)
+        return 1
+    print(f"{args.out}: {n_entries.value} entries")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

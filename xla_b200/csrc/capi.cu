@@ -2,6 +2,11 @@
 // spreads over GemmRewriter::CreateF8CustomCall, TypesAreSupportedByCublasLt and
 // cuda::BlasLt::GetMatmulPlan), kernel selection (instead of the cuBLASLt autotuner) and launch.
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <shared_mutex>
+#include <tuple>
 #include <cstddef>
 #include <cstring>
 #include <mutex>
@@ -56,6 +61,8 @@ __global__ void wait_probe_kernel(uint64_t limit_ns, uint32_t* status) {
 
 }  // namespace
 
+extern "C" int b200sd_load_config_table(const char* path, int32_t* entries, char* err, size_t err_len);
+
 Status InitDevice(int device) {
   if (device < 0 || device >= 64) return Status::Error(kInvalidArgument, "device ordinal out of range");
   DeviceState& st = g_state[device];
@@ -80,6 +87,16 @@ Status InitDevice(int device) {
     }
     st.init_status = InitDenseKernels();
     if (st.init_status.ok()) st.init_status = InitSkinnyKernels();
+    // A persisted tuning result named by the environment is loaded with the first device (a file
+    // that cannot be read or parsed makes the first call fail loudly instead of being ignored).
+    static std::once_flag table_once;
+    std::call_once(table_once, [&] {
+      const char* path = std::getenv("B200SD_CONFIG_TABLE");
+      if (path == nullptr || path[0] == 0 || !st.init_status.ok()) return;
+      char msg[512] = {0};
+      const int rc = b200sd_load_config_table(path, nullptr, msg, sizeof msg);
+      if (rc != 0) st.init_status = Status::Error(rc, std::string("B200SD_CONFIG_TABLE: ") + msg);
+    });
   });
   return st.init_status;
 }
@@ -119,12 +136,31 @@ Status LaunchWaitProbe(uint64_t limit_ns, cudaStream_t stream) {
   return Status::Ok();
 }
 
-// Static kernel choice.  Decode-shaped problems (few rows of A, a weight matrix that has to be
-// streamed once from HBM) go to the split-K kernel, everything else to the dense kernel.
-int SelectKernel(int64_t m, int64_t n, int64_t k) {
-  if (m <= 128 && n >= 1024 && k >= 1024 && SkinnyWorkspaceBytes(m, n, k) > 0) return kKernelSkinny;
+// Tuned kernel choices keyed by (integer?, m, n, k): what `selected_algorithm` of a persisted
+// autotuning result is to the reference (xla/backends/gpu/autotuner/cublaslt.cc:84-189 picks an
+// algorithm by timing, docs/persisted_autotuning.md stores it).  Filled by b200sd_load_config_table;
+// read-mostly, so lookups take a shared lock only.
+struct ConfigKey {
+  int32_t int8;
+  int64_t m, n, k;
+  bool operator<(const ConfigKey& o) const { return std::tie(int8, m, n, k) < std::tie(o.int8, o.m, o.n, o.k); }
+};
+std::shared_mutex g_config_mutex;
+std::map<ConfigKey, int32_t> g_config_table;
+
+// Kernel choice for B200SD_KERNEL_AUTO: the tuned table first, then the static rule -- decode-shaped
+// problems (few rows of A, a weight matrix that has to be streamed once from HBM) go to the split-K
+// kernel, everything else to the dense kernel.
+int SelectKernelFor(bool int8, int64_t m, int64_t n, int64_t k) {
+  {
+    std::shared_lock<std::shared_mutex> lock(g_config_mutex);
+    auto it = g_config_table.find(ConfigKey{int8 ? 1 : 0, m, n, k});
+    if (it != g_config_table.end()) return it->second;
+  }
+  if (!int8 && m <= 128 && n >= 1024 && k >= 1024 && SkinnyWorkspaceBytes(m, n, k) > 0) return kKernelSkinny;
   return kKernelDense;
 }
+int SelectKernel(int64_t m, int64_t n, int64_t k) { return SelectKernelFor(false, m, n, k); }
 
 Status ValidateF8(const B200SD_ScaledDotF8& in, GemmProblem* g, bool check_pointers = true) {
   // The struct grew by batch_count; older callers pass the shorter size and get a plain matrix product.
@@ -329,7 +365,12 @@ int b200sd_dot_s8(const B200SD_DotS8* args, void* cuda_stream, char* err, size_t
   Status st = ValidateS8(*args, &g);
   if (!st.ok()) return CopyStatus(st, err, err_len);
   LaunchStats stats;
-  st = LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats, args->kernel == B200SD_KERNEL_AUTO ? B200SD_KERNEL_DENSE : args->kernel);
+  int kernel = args->kernel;
+  if (kernel == B200SD_KERNEL_AUTO) {
+    kernel = g.batch > 1 ? B200SD_KERNEL_DENSE : SelectKernelFor(true, g.m, g.n, g.k);
+    if (kernel == B200SD_KERNEL_SKINNY) kernel = B200SD_KERNEL_DENSE;       // a table entry cannot send an integer dot there
+  }
+  st = LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats, kernel);
   if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
   return CopyStatus(st, err, err_len);
 }
@@ -351,6 +392,41 @@ size_t b200sd_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 }
 
 int b200sd_select_kernel(int64_t m, int64_t n, int64_t k) { return SelectKernel(m, n, k); }
+
+int b200sd_load_config_table(const char* path, int32_t* entries, char* err, size_t err_len) {
+  if (entries != nullptr) *entries = 0;
+  if (path == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "path is null"), err, err_len);
+  FILE* f = std::fopen(path, "r");
+  if (f == nullptr) return CopyStatus(Status::Error(kInvalidArgument, std::string("cannot open ") + path), err, err_len);
+  std::map<ConfigKey, int32_t> table;
+  char line[256];
+  int lineno = 0;
+  Status st = Status::Ok();
+  while (std::fgets(line, sizeof line, f) != nullptr) {
+    ++lineno;
+    char* p = line;
+    while (*p == ' ' || *p == '\t') ++p;
+    if (*p == '#' || *p == '\n' || *p == '\r' || *p == 0) continue;
+    char type[8];
+    long long m, n, k;
+    int kernel;
+    if (std::sscanf(p, "%7s %lld %lld %lld %d", type, &m, &n, &k, &kernel) != 5 || (std::strcmp(type, "f8") != 0 && std::strcmp(type, "s8") != 0) ||
+        m <= 0 || n <= 0 || k <= 0 || kernel < B200SD_KERNEL_DENSE || kernel > B200SD_KERNEL_DENSE_STREAMK ||
+        (type[0] == 's' && kernel == B200SD_KERNEL_SKINNY)) {
+      st = Status::Error(kInvalidArgument, std::string(path) + ":" + std::to_string(lineno) + ": expected `f8|s8 m n k kernel` with kernel 1..5");
+      break;
+    }
+    table[ConfigKey{type[0] == 's' ? 1 : 0, m, n, k}] = kernel;
+  }
+  std::fclose(f);
+  if (!st.ok()) return CopyStatus(st, err, err_len);          // a bad file changes nothing
+  {
+    std::unique_lock<std::shared_mutex> lock(g_config_mutex);
+    g_config_table.swap(table);
+    if (entries != nullptr) *entries = int32_t(g_config_table.size());
+  }
+  return CopyStatus(Status::Ok(), err, err_len);
+}
 
 uint64_t b200sd_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -312,3 +312,18 @@ def device_status() -> int:
 
 def launch_count() -> int:
     return int(_native.product.b200sd_launch_count())
+
+
+def load_config_table(path: str) -> int:
+    """Loads a tuned kernel-choice table (see `python -m xla_b200.autotune`); returns the number of entries."""
+    n = C.c_int32(0)
+    err = _err_buf()
+    rc = _native.product.b200sd_load_config_table(str(path).encode(), C.byref(n), err, len(err))
+    if rc != 0:
+        raise XlaFfiError(rc, err.value.decode(errors="replace"))
+    return n.value
+
+
+def select_kernel(m: int, n: int, k: int) -> int:
+    """What selected_config = 0 resolves to for an FP8 dot of this shape."""
+    return int(_native.product.b200sd_select_kernel(m, n, k))
