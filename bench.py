@@ -421,7 +421,11 @@ def gpu_arm(args):
     measured_traffic = {("c1", 8192, 8192, 8192): 396.0e6, ("c2", 64, 28672, 8192): 240.2e6,
                         ("c3", 4096, 4096, 4096): 33.8e6}
     roof["traffic"] = measured_traffic.get((kind, m, n, k)) if world == 1 else None
-    roof["kernel"] = {"c2": "skinny_gemm_kernel", "c3": "dense_gemm_kernel<int8>"}.get(kind, "dense_gemm_kernel<fp8>")
+    c2_kernel = args.kernel or xla_b200.select_kernel(lm, ln, lk)
+    roof["kernel"] = {"c2": "skinny_gemm_kernel" if c2_kernel == 2 else "dense_gemm_kernel<fp8, single>",
+                      "c3": "dense_gemm_kernel<int8>"}.get(kind, "dense_gemm_kernel<fp8>")
+    if kind == "c2" and c2_kernel != 2:
+        roof["traffic"] = None      # the captured figure under profiles/ is the split-K kernel's
     line = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

@@ -174,14 +174,18 @@ def test_unknown_target_and_wrong_stage():
 
 
 def test_kernel_selection_table():
-    """The static stand-in for the autotuner: decode shapes -> split-K (2), the rest -> dense (1)."""
+    """The static stand-in for the autotuner: decode shapes whose 256-column strips leave SMs idle -> split-K (2);
+    decode shapes with about one strip per SM, and everything else -> dense (1)."""
     sel = _native.product.b200sd_select_kernel
     assert sel(8192, 8192, 8192) == 1
     assert sel(256, 256, 512) == 1
     for m in (16, 64, 128):
-        assert sel(m, 28672, 8192) == 2
-        need = _native.product.b200sd_workspace_bytes(m, 28672, 8192)
-        assert 0 < need <= 32 * 1024 * 1024       # fits the workspace XLA attaches (matmul_utils.h:103)
+        assert sel(m, 28672, 8192) == 1           # 112 strips on 148 SMs: one CTA per strip streams all of K
+        for shard in (14336, 7168, 3584):         # the per-GPU shards of an N-split: too few strips, split K
+            assert sel(m, shard, 8192) == 2
+            need = _native.product.b200sd_workspace_bytes(m, shard, 8192)
+            assert 0 < need <= 32 * 1024 * 1024   # fits the workspace XLA attaches (matmul_utils.h:103)
+        assert sel(m, 256 * 150, 8192) == 2       # 150 strips: a second wave of two
     assert sel(16, 256, 256) == 1
     assert _native.product.b200sd_workspace_bytes(8192, 8192, 8192) == 0
 
@@ -196,18 +200,18 @@ def test_config_table_overrides_the_static_choice(tmp_path):
     """The persisted-tuning stand-in: exact (type, m, n, k) matches win over the static rule; a bad file changes nothing."""
     import xla_b200
 
-    assert xla_b200.select_kernel(64, 28672, 8192) == 2 and xla_b200.select_kernel(8192, 8192, 8192) == 1
+    assert xla_b200.select_kernel(64, 14336, 8192) == 2 and xla_b200.select_kernel(8192, 8192, 8192) == 1
     good = tmp_path / "table.txt"
-    good.write_text("# comment\nf8 64 28672 8192 3   # dense single-CTA here\n\ns8 4096 4096 4096 5\nf8 8192 8192 8192 4\n")
+    good.write_text("# comment\nf8 64 14336 8192 3   # dense single-CTA here\n\ns8 4096 4096 4096 5\nf8 8192 8192 8192 4\n")
     assert xla_b200.load_config_table(good) == 3
-    assert xla_b200.select_kernel(64, 28672, 8192) == 3 and xla_b200.select_kernel(8192, 8192, 8192) == 4
-    assert xla_b200.select_kernel(128, 28672, 8192) == 2              # no entry: static rule
+    assert xla_b200.select_kernel(64, 14336, 8192) == 3 and xla_b200.select_kernel(8192, 8192, 8192) == 4
+    assert xla_b200.select_kernel(128, 14336, 8192) == 2              # no entry: static rule
     bad = tmp_path / "bad.txt"
-    bad.write_text("f8 64 28672 8192 9\n")
+    bad.write_text("f8 64 14336 8192 9\n")
     with pytest.raises(XlaFfiError) as e:
         xla_b200.load_config_table(bad)
     assert e.value.code == 3 and "bad.txt:1" in e.value.message
-    assert xla_b200.select_kernel(64, 28672, 8192) == 3               # still the good table
+    assert xla_b200.select_kernel(64, 14336, 8192) == 3               # still the good table
     with pytest.raises(XlaFfiError):
         xla_b200.load_config_table(tmp_path / "missing.txt")
     with pytest.raises(XlaFfiError):
@@ -216,4 +220,4 @@ def test_config_table_overrides_the_static_choice(tmp_path):
     empty = tmp_path / "empty.txt"
     empty.write_text("# nothing\n")
     assert xla_b200.load_config_table(empty) == 0                     # and back to the static rule for later tests
-    assert xla_b200.select_kernel(64, 28672, 8192) == 2
+    assert xla_b200.select_kernel(64, 14336, 8192) == 2

@@ -183,10 +183,12 @@ def test_decode_full_width_linearity(cuda_device):
     agree, and scaling a_scale by 2 scales the bf16 output exactly by 2."""
     m, k, n = 64, 8192, 28672
     a, b, sa, sb = o.make_f8_operands(2, m, k, n)
-    got, _ = h.run_scaled_dot(cuda_device, a, b, sa, sb)
+    got, _ = h.run_scaled_dot(cuda_device, a, b, sa, sb, kernel=2)
     got_dense, _ = h.run_scaled_dot(cuda_device, a, b, sa, sb, kernel=1)
     h.check_close(got_dense, got, o.BF16, abs_tol=1e-3, rel_tol=1e-2)
-    got2, _ = h.run_scaled_dot(cuda_device, a, b, 2 * sa, sb)
+    got_auto, _ = h.run_scaled_dot(cuda_device, a, b, sa, sb)       # 112 strips: the automatic choice is the dense kernel
+    assert np.array_equal(got_auto, got_dense)
+    got2, _ = h.run_scaled_dot(cuda_device, a, b, 2 * sa, sb, kernel=2)
     assert np.array_equal(o.bf16_bits_to_f32(got2), 2 * o.bf16_bits_to_f32(got))
     cols = np.random.default_rng(0).choice(n, 64, replace=False)
     exp, _ = o.scaled_dot_f8(a, np.ascontiguousarray(b[:, cols]), sa, sb)

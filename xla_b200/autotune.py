@@ -30,42 +30,51 @@ def candidates(kind: str, m: int, n: int, k: int):
     return out
 
 
-def time_variant(kind: str, m: int, n: int, k: int, kernel: int, iters: int):
+def time_variants(kind: str, m: int, n: int, k: int, kernels, iters: int, rounds: int = 5):
+    """Returns {kernel: ms per launch}.  The variants are timed in turn, `rounds` times over, and the
+    best round of each is kept, so that clock and temperature drift hits all of them alike."""
     import torch
 
     from .scaled_dot import GemmBackendConfig, Int8DotCall, ScaledDotCall
 
     dev = torch.device("cuda", torch.cuda.current_device())
-    calls = []
+    operand_sets = []
     for i in range(2):                                   # two operand sets, so a launch never finds its inputs in L2
         ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)
         if kind == "s8":
             a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
             b = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev)
-            d = torch.empty((m, n), dtype=torch.int32, device=dev)
-            calls.append((Int8DotCall([a, b], [d, ws], selected_algorithm=kernel), (a, b, d, ws)))
+            operand_sets.append(([a, b], [torch.empty((m, n), dtype=torch.int32, device=dev), ws]))
         else:
             a = torch.randn((m, k), device=dev).to(torch.float8_e4m3fn)
             b = torch.randn((k, n), device=dev).to(torch.float8_e4m3fn)
             one = torch.ones((), device=dev)
-            d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-            calls.append((ScaledDotCall([a, b, one, one], [d, ws], GemmBackendConfig(selected_algorithm=kernel)), (a, b, d, ws, one)))
+            operand_sets.append(([a, b, one, one], [torch.empty((m, n), dtype=torch.bfloat16, device=dev), ws]))
     stream = torch.cuda.current_stream(dev).cuda_stream
     ordinal = dev.index or 0
-    for c, _ in calls:
-        c.run(stream, ordinal)
-    for i in range(3):
-        calls[i & 1][0].execute(stream, ordinal)
-    torch.cuda.synchronize()
+    calls = {}
+    for kern in kernels:
+        if kind == "s8":
+            calls[kern] = [Int8DotCall(ops, res, selected_algorithm=kern) for ops, res in operand_sets]
+        else:
+            calls[kern] = [ScaledDotCall(ops, res, GemmBackendConfig(selected_algorithm=kern)) for ops, res in operand_sets]
+        for c in calls[kern]:
+            c.run(stream, ordinal)
+    best = {kern: float("inf") for kern in kernels}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        calls[i & 1][0].execute(stream, ordinal)
-    e1.record()
-    torch.cuda.synchronize()
-    for c, _ in calls:
-        c.close()
-    return e0.elapsed_time(e1) / iters
+    for r in range(rounds + 1):                          # round 0 warms up and is not counted
+        for kern in kernels:
+            e0.record()
+            for i in range(iters):
+                calls[kern][i & 1].execute(stream, ordinal)
+            e1.record()
+            torch.cuda.synchronize()
+            if r > 0:
+                best[kern] = min(best[kern], e0.elapsed_time(e1) / iters)
+    for kern in kernels:
+        for c in calls[kern]:
+            c.close()
+    return best
 
 
 def parse_shape(text: str):
@@ -80,12 +89,12 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--out", required=True)
     ap.add_argument("--shape", action="append", default=None, help="f8:MxNxK or s8:MxNxK; may repeat")
-    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=30)
     args = ap.parse_args(argv)
     lines = ["# type m n k kernel   (written by python -m xla_b200.autotune; times in ms per launch)"]
     for text in args.shape or DEFAULT_SHAPES:
         kind, m, n, k = parse_shape(text)
-        timings = {kern: time_variant(kind, m, n, k, kern, args.iters) for kern in candidates(kind, m, n, k)}
+        timings = time_variants(kind, m, n, k, candidates(kind, m, n, k), args.iters)
         best = min(timings, key=timings.get)
         detail = ", ".join(f"{KERNEL_NAMES[kk]} {t:.4f}" for kk, t in sorted(timings.items()))
         lines.append(f"{kind} {m} {n} {k} {best}   # {detail}")

@@ -157,7 +157,18 @@ int SelectKernelFor(bool int8, int64_t m, int64_t n, int64_t k) {
     auto it = g_config_table.find(ConfigKey{int8 ? 1 : 0, m, n, k});
     if (it != g_config_table.end()) return it->second;
   }
-  if (!int8 && m <= 128 && n >= 1024 && k >= 1024 && SkinnyWorkspaceBytes(m, n, k) > 0) return kKernelSkinny;
+  if (!int8 && m <= 128 && n >= 1024 && k >= 1024 && SkinnyWorkspaceBytes(m, n, k) > 0) {
+    // Decode shapes are bound by streaming the weights.  When the 256-column strips of the dense
+    // single-CTA kernel fill one wave of the 148 SMs well (or many waves), each CTA streams its own
+    // strip over all of K with nothing to combine afterwards, which measures faster than splitting K
+    // (8192 x 28672, 112 strips: 5.56 / 5.47 / 5.32 TB/s against 5.35 / 5.46 / 4.89 at M = 16 / 64 / 128).
+    // Few strips (the per-GPU shards of an N-split) leave SMs without work: split K then.
+    constexpr int64_t kSms = 148;
+    const int64_t strips = (n + 255) / 256;
+    const int64_t last_wave = strips % kSms == 0 ? kSms : strips % kSms;
+    if (strips >= 4 * kSms || (strips >= (kSms * 7) / 10 && last_wave >= (kSms * 7) / 10)) return kKernelDense;
+    return kKernelSkinny;
+  }
   return kKernelDense;
 }
 int SelectKernel(int64_t m, int64_t n, int64_t k) { return SelectKernelFor(false, m, n, k); }
