@@ -424,8 +424,8 @@ def gpu_arm(args):
     c2_kernel = args.kernel or xla_b200.select_kernel(lm, ln, lk)
     roof["kernel"] = {"c2": "skinny_gemm_kernel" if c2_kernel == 2 else "dense_gemm_kernel<fp8, single>",
                       "c3": "dense_gemm_kernel<int8>"}.get(kind, "dense_gemm_kernel<fp8>")
-    if kind == "c2" and c2_kernel != 2:
-        roof["traffic"] = None      # the captured figure under profiles/ is the split-K kernel's
+    if kind == "c2" and c2_kernel != 2:   # the dense single-CTA kernel's capture (profiles/dense_gemm_single_fp8_c2_m64.md)
+        roof["traffic"] = 240.06e6 if (world == 1 and (m, n, k) == (64, 28672, 8192)) else None
     line = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
