@@ -94,8 +94,7 @@ typedef struct B200SD_ScaledDotF8 {
   int32_t epilogue;              /* B200SD_EPILOGUE_* */
   float alpha, beta;
   int32_t kernel;                /* B200SD_KERNEL_* */
-  /* Added later: a caller whose struct_size stops before it gets batch_count = 1. */
-  int32_t batch_count;           /* > 1: A, B, C and D carry this leading batch dimension ([batch, m, k] ...,
+  int32_t batch_count;           /* 0 or 1: plain matrices.  > 1: A, B, C and D carry this leading batch dimension ([batch, m, k] ...,
                                     dense row-major, lhs/rhs_batch_dims = {0} as in gemm_rewriter_fp8_test.cc:941-991);
                                     the bias vector, the scales and amax are shared by all batches */
 } B200SD_ScaledDotF8;

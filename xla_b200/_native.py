@@ -41,6 +41,7 @@ class ScaledDotF8Args(C.Structure):
         ("epilogue", C.c_int32),
         ("alpha", C.c_float), ("beta", C.c_float),
         ("kernel", C.c_int32),
+        ("batch_count", C.c_int32),
     ]
 
 
@@ -57,6 +58,7 @@ class DotS8Args(C.Structure):
         ("lhs_contracting_dim", C.c_int32), ("rhs_contracting_dim", C.c_int32),
         ("kernel", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("batch_count", C.c_int64),
     ]
 
 
