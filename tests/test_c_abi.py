@@ -221,3 +221,30 @@ def test_config_table_overrides_the_static_choice(tmp_path):
     empty.write_text("# nothing\n")
     assert xla_b200.load_config_table(empty) == 0                     # and back to the static rule for later tests
     assert xla_b200.select_kernel(64, 14336, 8192) == 2
+
+
+def test_ctypes_mirrors_match_the_header_as_a_c_compiler_sees_it(tmp_path):
+    """include/b200_scaled_dot.h compiles as plain C, and every struct has the size and the field offsets of its ctypes mirror."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    pairs = [("B200SD_ScaledDotF8", _native.ScaledDotF8Args), ("B200SD_DotS8", _native.DotS8Args),
+             ("B200SD_Progress", _native.ProgressArgs), ("B200SD_PeerReduce", _native.PeerReduceArgs)]
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "b200_scaled_dot.h"', "int main(void) {"]
+    for cname, mirror in pairs:
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{cname}.{field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "abi.c"
+    src.write_text("\n".join(lines) + "\n")
+    exe = tmp_path / "abi"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    seen = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, mirror in pairs:
+        assert int(seen[cname]) == C.sizeof(mirror), cname
+        for field, _ in mirror._fields_:
+            assert int(seen[f"{cname}.{field}"]) == getattr(mirror, field).offset, f"{cname}.{field}"
