@@ -95,3 +95,48 @@ def test_batched_frames_that_must_be_rejected(cuda_device):
     cfg.selected_algorithm = 2
     with pytest.raises(XlaFfiError):                              # the split-K kernel does not take batches
         cublas_lt_matmul_f8(a, a, one, one, config=cfg)
+
+
+@pytest.mark.parametrize("kernel", [3, 4, 5])
+def test_batched_kernel_variants_agree(cuda_device, kernel):
+    batch, m, k, n = 5, 512, 1024, 768                  # 5 x 2 x 3 = 30 pair tiles
+    rng = np.random.default_rng(21)
+    a = _dev(o.fp8_encode(rng.standard_normal((batch, m, k), dtype=np.float32) * 3, "e4m3fn"), cuda_device, torch.float8_e4m3fn)
+    b = _dev(o.fp8_encode(rng.standard_normal((batch, k, n), dtype=np.float32) * 3, "e4m3fn"), cuda_device, torch.float8_e4m3fn)
+    one = torch.ones((), device=cuda_device)
+
+    def run(alg):
+        cfg = GemmBackendConfig(lhs_contracting_dimensions=(2,), rhs_contracting_dimensions=(1,), lhs_batch_dimensions=(0,),
+                                rhs_batch_dimensions=(0,), selected_algorithm=alg)
+        return cublas_lt_matmul_f8(a, b, one, one, out_dtype=torch.bfloat16, config=cfg)[0]
+
+    ref = run(1)
+    got = run(kernel)
+    torch.cuda.synchronize()
+    if kernel == 3:       # M=128 instead of M=256 MMAs: the same sums up to the f32 order inside the tensor core
+        assert o.near_mismatches(ref.float().cpu().numpy(), got.float().cpu().numpy(), 1e-2, 1e-2)[0] == 0
+    else:                 # the CTA-pair kernel, with or without a stream-K tail (30 tiles: there is none)
+        assert torch.equal(ref, got)
+    assert device_status() == 0
+
+
+def test_batched_int8_through_the_plain_c_entry_point(cuda_device):
+    import ctypes as C
+
+    from xla_b200 import _native
+
+    batch, m, k, n = 3, 144, 256, 272
+    rng = np.random.default_rng(22)
+    a8 = rng.integers(-127, 128, (batch, m, k), dtype=np.int8)
+    b8 = rng.integers(-127, 128, (batch, k, n), dtype=np.int8)
+    a, b = torch.from_numpy(a8).to(cuda_device), torch.from_numpy(b8).to(cuda_device)
+    d = torch.zeros((batch, m, n), dtype=torch.int32, device=cuda_device)
+    args = _native.DotS8Args(struct_size=C.sizeof(_native.DotS8Args), a=a.data_ptr(), b=b.data_ptr(), d=d.data_ptr(), m=m, n=n, k=k,
+                             d_dtype=4, lhs_contracting_dim=1, rhs_contracting_dim=0, kernel=0, batch_count=batch)
+    err = C.create_string_buffer(512)
+    assert _native.product.b200sd_dot_s8(args, torch.cuda.current_stream(cuda_device).cuda_stream, err, len(err)) == 0, err.value
+    torch.cuda.synchronize()
+    got = d.cpu().numpy()
+    for i in range(batch):
+        assert np.array_equal(got[i], o.dot_s8(a8[i], b8[i])), f"batch {i}"
+    assert device_status() == 0
