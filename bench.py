@@ -416,6 +416,16 @@ def gpu_arm(args):
                 "frac_of_nominal_4500": flops / world / ms / 1e9 / 4500.0,
                 "frac_of_sustained": flops / world / ms / 1e9 / (2.0 * peaks["bf16_tflops_sustained"])}
     roof["frac"] = roof["achieved"] / roof["peak"]
+    if kind == "c4" and world > 1:
+        # A dot followed by its sum across the ranks: the target time is the slower of the dot at the measured
+        # tensor peak and the bytes every rank must send (reduce-scatter + all-gather of the bf16 [m, n] result)
+        # at the measured peer-copy rate of this pool, 770 GB/s per direction.
+        t_tensor_ms = flops / world / (fp8_peak * 1e9)
+        link_bytes = 2.0 * (world - 1) / world * m * n * 2
+        t_link_ms = link_bytes / 770e9 * 1e3
+        roof["fused"] = {"bound": "tensor" if t_tensor_ms >= t_link_ms else "nvlink", "tensor_ms": t_tensor_ms, "nvlink_ms": t_link_ms,
+                         "nvlink_bytes_per_rank": link_bytes, "target_ms": max(t_tensor_ms, t_link_ms),
+                         "frac": max(t_tensor_ms, t_link_ms) / ms}
     # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
     # (single GPU, default sizes only; bytes).
     measured_traffic = {("c1", 8192, 8192, 8192): 396.0e6, ("c2", 64, 28672, 8192): 240.2e6,
