@@ -207,11 +207,11 @@ int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint3
  * xla/backends/gpu/collectives/nccl_communicator.cc:557-592 execute.
  *
  * Every rank calls this with its own K-shard in `args` (a, b, scales; args->d = d[rank]; bf16
- * result, no epilogue).  Rank r pushes the bf16 partial of the row blocks it does not own into the
- * owner's `stage` buffer while its tensor cores work on the next tile, computes its own block
- * (rows [r*m/world, (r+1)*m/world)) last, adds the partials the others pushed (in rank order, in
- * f32, rounded once) and writes the finished rows into every rank's `d`.  When the kernel ends on
- * a rank, that rank's `d` is complete.  m must be a multiple of 256*world.
+ * result, no epilogue).  The rows are dealt out to the ranks in sub-blocks.  Rank r pushes the bf16
+ * partial of the sub-blocks it does not own into the owner's `stage` buffer while its tensor cores
+ * work on the next tile; for a sub-block it owns it adds the partials the others pushed (in rank
+ * order, in f32, rounded once) and writes the finished rows into every rank's `d`.  When the
+ * kernel ends on a rank, that rank's `d` is complete.  m must be a multiple of 256*world.
  *
  * d[i], stage[i] (m*n*2 bytes) and flags[i] (b200sd_peer_reduce_flag_words() u32, zeroed once when
  * allocated, never by the library) are rank i's buffers as mapped into THIS process (peer memory:

@@ -84,7 +84,8 @@ static_assert(DenseSmemBytes<true, true>() <= 232448 && DenseSmemBytes<true, fal
 // Peer-reduce mode (see PeerReduceProblem): what the kernel needs of it.
 struct ReduceArgs {
   int32_t world, rank, emulate;
-  int32_t m_tiles_per_block;      // 256-row tiles in the row block each rank owns
+  int32_t m_tiles_per_block;      // 256-row tiles each rank owns in all (its rows of the staging buffers)
+  int32_t stages;                 // the rows are dealt out in `stages` rounds of world sub-blocks (see tile_coords_reduce)
   uint32_t flag_target;           // value a (tile, warp) flag reaches when every other rank has pushed: epoch * (world - 1)
   uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
   int32_t done_index;             // index of that counter in the flag array
@@ -263,29 +264,35 @@ __device__ __forceinline__ void st_release_gpu_u64(unsigned long long* p, unsign
   asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// Peer-reduce order: rank r walks the row blocks r+1, r+2, ..., r (its own last), so that what it
-// pushes first is what its neighbours need last, and by the time it reaches its own block the
-// others' partials of that block have long arrived.  `blk` is the owner of the tile's rows,
-// `slot` the tile's index inside that block (names its flags).
+// Peer-reduce order.  The rows are cut into stages x world sub-blocks; sub-block s*world + j belongs to
+// rank j.  In every stage rank r walks the sub-blocks of ranks r+1, r+2, ..., r (its own last): what it
+// pushes first is what its neighbours need last, and when it reaches its own sub-block the others'
+// partials of it have arrived.  Several stages spread the broadcasts of finished rows over the
+// kernel instead of leaving them all for its end.  `blk` is the owner of the tile's rows, `own_mt`
+// the tile's row-tile index within the owner's rows (staging buffer, flags), `slot` names its flags.
 __device__ __forceinline__ void tile_coords_reduce(int32_t tile, const DenseArgs& p, int32_t my_rank, int32_t* mt,
-                                                   int32_t* nt, int32_t* blk, int32_t* slot) {
-  const int32_t mtpb = p.red.m_tiles_per_block;
-  const int32_t per_block = mtpb * p.num_n_tiles;
-  const int32_t b = tile / per_block;
-  const int32_t local = tile - b * per_block;
+                                                   int32_t* nt, int32_t* blk, int32_t* slot, int32_t* own_mt) {
+  const int32_t mtps = p.red.m_tiles_per_block / p.red.stages;       // row tiles per sub-block
+  const int32_t per_sub = mtps * p.num_n_tiles;
+  const int32_t per_stage = per_sub * p.red.world;
+  const int32_t st = tile / per_stage;
+  const int32_t within = tile - st * per_stage;
+  const int32_t b = within / per_sub;
+  const int32_t local = within - b * per_sub;
   int32_t owner = my_rank + 1 + b;
   if (owner >= p.red.world) owner -= p.red.world;
-  const int32_t rg = min(p.raster_group, mtpb);
+  const int32_t rg = min(p.raster_group, mtps);
   const int32_t per_group = rg * p.num_n_tiles;
   const int32_t g = local / per_group;
   const int32_t first_m = g * rg;
-  const int32_t gsize = min(rg, mtpb - first_m);
+  const int32_t gsize = min(rg, mtps - first_m);
   const int32_t r = local - g * per_group;
   const int32_t mt_local = first_m + r % gsize;
   *nt = r / gsize;
-  *mt = owner * mtpb + mt_local;
+  *mt = (st * p.red.world + owner) * mtps + mt_local;
   *blk = owner;
-  *slot = mt_local * p.num_n_tiles + *nt;
+  *own_mt = st * mtps + mt_local;
+  *slot = *own_mt * p.num_n_tiles + *nt;
 }
 
 constexpr int kChunk = 16;   // accumulator columns handled per epilogue step
@@ -593,8 +600,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         const int32_t tile = item.tile;
         int32_t mt, nt, bt = 0;
         if constexpr (kReduce) {
-          int32_t blk, slot;
-          tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
+          int32_t blk, slot, own_mt;
+          tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot, &own_mt);
         } else {
           tile_coords(tile, p, &mt, &nt, &bt);
         }
@@ -833,8 +840,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       const WorkItem item = get_item(work, p, it);
       const int32_t tile = item.tile;
       int32_t mt, nt, bt = 0;
-      int32_t blk = 0, slot = 0;
-      if constexpr (kReduce) tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot);
+      int32_t blk = 0, slot = 0, own_mt = 0;
+      if constexpr (kReduce) tile_coords_reduce(tile, p, my_rank, &mt, &nt, &blk, &slot, &own_mt);
       else tile_coords(tile, p, &mt, &nt, &bt);
       const int64_t col_base = int64_t(nt) * kBN + col_half * kColsPerEpilogueWarp;
       // Stage the per-column vectors of this warp's columns.
@@ -864,7 +871,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout);
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
-          const int64_t prow = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane - int64_t(blk) * rows_per_block;
+          const int64_t prow = int64_t(own_mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
           for (int32_t s = 0; s < p.red.world; ++s) {
             if (s == my_rank) continue;
             const uint16_t* line = p.red.stage[my_rank] + (int64_t(s) * rows_per_block + prow) * p.n + col_base;
@@ -900,6 +907,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       float row_scale = 1.0f;
       if (kInt8 && p.a_row_scale && row_ok) row_scale = __ldg(p.a_row_scale + row_in_batch);
       const int64_t row = int64_t(bt) * p.m + row_in_batch;        // row of the [batch * m, n] view of C and D
+      const int64_t own_row = int64_t(own_mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;   // peer reduce: row within the owner's rows
       const uint32_t taddr =
           tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN + col_half * kColsPerEpilogueWarp);
 
@@ -921,7 +929,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
               if (lane == 0) tma_store_wait_read<0>();
               __syncwarp();
             }
-            reduce_chunk(p, ra, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
+            reduce_chunk(p, ra, scale, my_rank, blk, own_row, rows_per_block, col0,
                          store_stage + lane * 8, (c0 >> 3) & 7, lane);
           }
           else finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
@@ -934,7 +942,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           sk_dump(rb, c0 + kChunk);
         } else if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, row - int64_t(blk) * rows_per_block, rows_per_block, col0,
+          if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, own_row, rows_per_block, col0,
                                               store_stage + lane * 8, ((c0 >> 3) & 7) + 2, lane);
           else finish_chunk<kInt8>(p, rb, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0 + kChunk,
                                    colscale_w + c0 + kChunk, &amax_bits);
@@ -942,8 +950,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         if constexpr (kReduce) {
           if ((c0 & 32) != 0) {            // 64 columns staged: write them out as full lines
             const int64_t warp_row0 = row - lane;
-            flush_store_stage(p, rmaps, store_stage, my_rank, blk, warp_row0, warp_row0 - int64_t(blk) * rows_per_block,
-                              rows_per_block, col_base + c0 - 32, lane);
+            flush_store_stage(p, rmaps, store_stage, my_rank, blk, warp_row0, own_row - lane, rows_per_block,
+                              col_base + c0 - 32, lane);
           }
         }
       }
@@ -1377,6 +1385,12 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   ReduceArgs& q = p.red;
   q.world = r.world; q.rank = r.rank; q.emulate = r.emulate;
   q.m_tiles_per_block = p.num_m_tiles / r.world;
+  // Rounds in which the rows are dealt out: two when each rank's row tiles divide (measured at 4 GPUs on
+  // 8192 x 28672 x 8192: 0.515 / 0.487 / 0.520 / 0.580 ms for 1 / 2 / 4 / 8 rounds -- more rounds spread the
+  // broadcasts but add a rendezvous each).  B200SD_REDUCE_STAGES overrides, for tuning.
+  static const int env_stages = [] { const char* e = std::getenv("B200SD_REDUCE_STAGES"); return e ? std::atoi(e) : 0; }();
+  q.stages = q.m_tiles_per_block % 2 == 0 ? 2 : 1;
+  if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
   q.flag_target = r.epoch * uint32_t(r.world - 1);
   q.done_index = int32_t(PeerReduceFlagWords(g.m, g.n, r.world)) - 32;
   q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps);
