@@ -125,3 +125,25 @@ def test_batched_module(cuda_device):
         torch.cuda.synchronize()
         assert tuple(got.shape) == (bt, m, n)
         assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0
+
+
+def test_alpha_and_output_scale_modules(cuda_device):
+    rng = np.random.default_rng(12)
+    text = load("scaled_ab_alpha_f32")
+    a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32) * 2, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32) * 2, "e4m3fn")
+    sa, sb = np.float32(0.5), np.float32(0.125)
+    exp = hlo_eval.evaluate(text, [a, b, sa, sb])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0
+    text = load("unscaled_ab_scaled_f32_d")
+    a = o.fp8_encode(rng.standard_normal((32, 64), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 48), dtype=np.float32), "e4m3fn")
+    s = np.float32(0.75)
+    exp = hlo_eval.evaluate(text, [a, b, s])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           torch.tensor(s, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0

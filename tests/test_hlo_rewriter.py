@@ -116,6 +116,37 @@ def test_batched_dot_lowering_and_interpreter():
     assert not hlo_runner.rewrite(mixed)[1]["rewritten"]
 
 
+def test_alpha_and_output_scale_without_an_fp8_cast():
+    """ScaledABAlphaDF8 (gemm_rewriter_fp8_test.cc:993-1047): a constant factor behind the dot becomes alpha_real.
+    UnscaledABScaledF32DF8 (:1514-1561, F8ScaleD gemm_rewriter.cc:1593-1633): a scalar factor on a non-FP8 result
+    travels as a_scale -- only while a_scale is still the constant 1."""
+    text = load("scaled_ab_alpha_f32")
+    hlo, plan = hlo_runner.rewrite(text)
+    assert plan["attrs"]["alpha_real"] == 3.0 and roles(plan) == ["a", "b", "a_scale", "b_scale"]
+    assert "alpha_real = 3.0 : f64" in hlo and "ROOT out = f32[48,32] copy(d)" in hlo
+    rng = np.random.default_rng(11)
+    a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32), "e4m3fn")
+    out = hlo_eval.evaluate(text, [a, b, np.float32(0.5), np.float32(0.25)])
+    np.testing.assert_allclose(out, o.scaled_dot_f8(a, b, 0.5, 0.25, alpha=3.0, out_dtype=o.F32)[0], rtol=1e-6, atol=1e-6)
+
+    text = load("unscaled_ab_scaled_f32_d")
+    _, plan = hlo_runner.rewrite(text)
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale"]
+    assert plan["operands"][2]["param"] == 2 and not plan["operands"][2]["reciprocal"]       # out_scale took a_scale's place
+    assert plan["operands"][3]["param"] == -1 and plan["operands"][3]["constant"] == 1.0
+    assert plan["results"][0]["dtype"] == 11
+    _, plan = hlo_runner.rewrite(text.replace("multiply(dot0, s_b)", "divide(dot0, s_b)"))
+    assert plan["operands"][2]["param"] == 2 and plan["operands"][2]["reciprocal"]
+    # with scaled operands the factor cannot be forwarded: the multiply stays outside, and since the module's
+    # output is then not the custom call's result the module is left alone
+    scaled = load("c0_scaled_dot_f8").replace("ROOT out = bf16[256,256] dot(", "dot0 = f32[256,256] dot(")
+    head, _, _ = scaled.rpartition("}")
+    scaled = head + "  s = f32[] parameter(4)\n  s_b = f32[256,256] broadcast(s), dimensions={}\n  ROOT out = f32[256,256] multiply(dot0, s_b)\n}\n"
+    assert "multiply(dot0, s_b)" in scaled and "dot0 = f32[256,256] dot(" in scaled
+    assert not hlo_runner.rewrite(scaled)[1]["rewritten"]
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -154,7 +185,7 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
-                                  "batched_scaled_ab_f32"])
+                                  "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""

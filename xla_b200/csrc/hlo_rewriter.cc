@@ -379,6 +379,17 @@ bool ScaleSource(const Graph& g, Instr* scale, bool divide, const char* role, So
 void MatchF8Epilogue(const Graph& g, Instr* dot, Plan* plan) {
   Instr* cur = dot;
   bool relu = false, gelu = false, vector_bias = false;
+  // -- alpha: multiply(dot, broadcast(constant)) right behind the dot (HandleMultiply, gemm_rewriter.cc:888-921;
+  //    gemm_rewriter_fp8_test.cc:993-1047)
+  if (g.Users(cur).size() == 1 && g.Users(cur)[0]->opcode == "multiply") {
+    Instr* mul = g.Users(cur)[0];
+    Instr* other = OtherOperand(g, mul, "multiply", cur);
+    double c;
+    if (other != nullptr && ScalarConstant(g, BroadcastedScalar(g, other), &c)) {
+      plan->alpha = c;
+      cur = mul;
+    }
+  }
   // -- bias (vector along the minor dimension, or a full matrix with beta = 1)
   for (Instr* u : g.Users(cur)) {
     if (u->opcode != "add") continue;
@@ -469,6 +480,23 @@ void MatchF8Epilogue(const Graph& g, Instr* dot, Plan* plan) {
     plan->operands.push_back(s);
     d = conv;
     break;
+  }
+  if (!IsF8(d->shape.type) && !gelu && !vector_bias && plan->beta == 0.0 && g.Users(cur).size() == 1 &&
+      plan->operands.size() >= 4 && plan->operands[2].param < 0 && plan->operands[2].constant == 1.0 && !plan->operands[2].reciprocal) {
+    // F8ScaleD (gemm_rewriter.cc:1593-1633): the output is scaled by a scalar but NOT cast to FP8.  The factor is
+    // forwarded as a_scale -- only when no input scale was fused there (a_scale is still the constant 1), the
+    // epilogue is DEFAULT or RELU and no matrix bias was fused.
+    Instr* u = g.Users(cur)[0];
+    if (u->opcode == "multiply" || (u->opcode == "divide" && g.Operand(u, 0) == cur)) {
+      Instr* scale = BroadcastedScalar(g, OtherOperand(g, u, u->opcode.c_str(), cur));
+      Source sd;
+      std::string why;
+      if (scale != nullptr && ScaleSource(g, scale, u->opcode == "divide", "a_scale", &sd, &why)) {
+        plan->operands[2] = sd;
+        cur = u;
+        d = u;
+      }
+    }
   }
   if (!IsF8(d->shape.type)) {
     amax = nullptr;   // amax is only produced together with an FP8 output (the delayed-scaling pattern)
