@@ -71,6 +71,7 @@ def _f8_frame(m=256, k=512, n=256, *, a=F8E4M3FN, b=F8E4M3FN, d=BF16, extra_ops=
     dict(d=F8E4M3FN, cfg=dict(epilogue=Epilogue.BIAS_GELU, damax_output=True),
          extra_ops=[Buffer(BF16, (256,)), Buffer(F32, ())],
          extra_res=[Buffer(F32, ()), Buffer(S8, (1 << 20,))]),                             # BASELINE config 1
+    dict(d=F8E4M3FN),                                                                      # :313  FP8 result, b_scale doubles as d_scale
     dict(extra_res=[]),                                                                    # no workspace result
     dict(b=F8E5M2, d=F8E5M2, extra_ops=[Buffer(F32, ())]),
     dict(lc=0, rc=1),

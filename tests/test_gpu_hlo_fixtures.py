@@ -147,3 +147,14 @@ def test_alpha_and_output_scale_modules(cuda_device):
                                            torch.tensor(s, device=cuda_device)])
     torch.cuda.synchronize()
     assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0
+
+
+def test_bare_fp8_dot_module(cuda_device):
+    text = load("bare_fp8_dot")
+    rng = np.random.default_rng(13)
+    a = o.fp8_encode(rng.standard_normal((32, 64), dtype=np.float32) * 0.5, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 48), dtype=np.float32) * 0.5, "e4m3fn")
+    exp = hlo_eval.evaluate(text, [a, b])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device)])
+    torch.cuda.synchronize()
+    assert o.fp8_within_n_values(exp, back(got), 1) == 0

@@ -147,6 +147,15 @@ def test_alpha_and_output_scale_without_an_fp8_cast():
     assert not hlo_runner.rewrite(scaled)[1]["rewritten"]
 
 
+def test_bare_fp8_dot():
+    """UnscaledABUnscaledDF8 (gemm_rewriter_fp8_test.cc:313-350): custom-call(a, b, 1, 1) with an FP8 result and no
+    d_scale operand of its own -- the emitter then reads the last operand as d_scale (thunk_emitter.cc:812-818)."""
+    hlo, plan = hlo_runner.rewrite(load("bare_fp8_dot"))
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale"] and plan["results"][0]["dtype"] == 20
+    assert all(s["param"] == -1 and s["constant"] == 1.0 for s in plan["operands"][2:])
+    assert "(f8e4m3fn[32,48], s8[33554432]) custom-call(a, b, a_scale_const0, b_scale_const1)" in hlo
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -185,7 +194,7 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
-                                  "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d"])
+                                  "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""

@@ -327,6 +327,10 @@ struct Fp8Operand {
 // MatchFp8Param (gemm_rewriter.cc:190-336) for the shapes the fixtures use.
 bool MatchFp8Operand(const Graph& g, Instr* x, Fp8Operand* out) {
   if (x == nullptr) return false;
+  if (IsF8(x->shape.type)) {        // an FP8 value fed to the dot as it is (gemm_rewriter_fp8_test.cc:313-350)
+    out->f8 = x;
+    return true;
+  }
   Instr* conv = x;
   if (x->opcode == "multiply" || x->opcode == "divide") {
     Instr* l = g.Operand(x, 0);
