@@ -6,11 +6,13 @@
 // Call-frame contract (operand order of ThunkEmitter::EmitCublasLtMatmulF8,
 // xla/service/gpu/thunk_emitter.cc:776-862):
 //   operands  a, b, [c iff beta != 0], a_scale, b_scale, [bias iff the epilogue adds one],
-//             [d_scale iff D is F8E4M3FN / F8E5M2]
+//             [d_scale iff D is F8E4M3FN / F8E5M2; may be left out when there is no bias, b_scale then
+//             doubles as d_scale]
 //   results   D, [amax f32[] iff damax_output], [workspace s8[n]]
 //   attrs     GemmBackendConfig fields (xla/service/gpu/backend_configs.proto:88-135) as a flat
 //             dictionary: alpha_real, beta (f64 or f32), epilogue (i32/i64, enum number),
 //             lhs_contracting_dim, rhs_contracting_dim (i64/i32), damax_output (bool),
+//             lhs_batch_dims, rhs_batch_dims (i64 arrays, {0} for rank-3 operands),
 //             selected_config (i64, optional; 0 = automatic kernel choice).
 // XLA_FFI_Buffer carries no layout (xla/ffi/api/c_api.h:273-281): every buffer is row-major and
 // transposition is expressed by the contracting dimensions alone.
