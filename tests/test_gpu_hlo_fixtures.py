@@ -158,3 +158,30 @@ def test_bare_fp8_dot_module(cuda_device):
     got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device)])
     torch.cuda.synchronize()
     assert o.fp8_within_n_values(exp, back(got), 1) == 0
+
+
+def test_combined_epilogue_modules(cuda_device):
+    rng = np.random.default_rng(15)
+    dev = cuda_device
+    text = load("matrix_bias_scaled_d_amax")
+    a = o.fp8_encode(rng.standard_normal((64, 128), dtype=np.float32) * 4, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((128, 96), dtype=np.float32) * 4, "e4m3fn")
+    c = rng.standard_normal((64, 96), dtype=np.float32)
+    sa, sb, ds = np.float32(0.5), np.float32(0.25), np.float32(0.5)
+    exp_d, exp_amax = hlo_eval.evaluate(text, [a, b, c, sa, sb, ds])
+    d, amax = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", dev), to_dev(b, "f8e4m3fn", dev), torch.from_numpy(c).to(dev),
+                                               torch.tensor(sa, device=dev), torch.tensor(sb, device=dev), torch.tensor(ds, device=dev)])
+    torch.cuda.synchronize()
+    assert o.fp8_within_n_values(exp_d, back(d), 1) == 0
+    assert float(amax.item()) == pytest.approx(float(exp_amax), rel=1e-4)
+
+    text = load("relu_amax_e5m2_out")
+    a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32) * 4, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 80), dtype=np.float32) * 4, "e5m2")
+    sa, sb, dm = np.float32(0.5), np.float32(0.5), np.float32(1.5)
+    exp_d, exp_amax = hlo_eval.evaluate(text, [a, b, sa, sb, dm])
+    d, amax = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", dev), to_dev(b, "f8e5m2", dev), torch.tensor(sa, device=dev),
+                                               torch.tensor(sb, device=dev), torch.tensor(dm, device=dev)])
+    torch.cuda.synchronize()
+    assert o.fp8_within_n_values(exp_d, back(d), 1) == 0
+    assert float(amax.item()) == pytest.approx(float(exp_amax), rel=1e-4)

@@ -156,6 +156,33 @@ def test_bare_fp8_dot():
     assert "(f8e4m3fn[32,48], s8[33554432]) custom-call(a, b, a_scale_const0, b_scale_const1)" in hlo
 
 
+def test_combined_epilogues():
+    """ScaledABScaledDMatrixBiasWithDAmaxF8 (gemm_rewriter_fp8_test.cc:1839-1917): a, b, c, a_scale, b_scale, d_scale ->
+    (FP8, amax).  ScaledABScaledDReluActivationF8 with amax (:2715-2790): after ReLU the amax reduce needs no abs."""
+    text = load("matrix_bias_scaled_d_amax")
+    _, plan = hlo_runner.rewrite(text)
+    assert roles(plan) == ["a", "b", "c", "a_scale", "b_scale", "d_scale"] and plan["operands"][5]["reciprocal"]
+    assert plan["attrs"]["beta"] == 1.0 and plan["attrs"]["damax_output"] is True and plan["attrs"]["epilogue"] == 1
+    rng = np.random.default_rng(14)
+    a = o.fp8_encode(rng.standard_normal((64, 128), dtype=np.float32) * 4, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((128, 96), dtype=np.float32) * 4, "e4m3fn")
+    c = rng.standard_normal((64, 96), dtype=np.float32)
+    d, amax = hlo_eval.evaluate(text, [a, b, c, np.float32(0.5), np.float32(0.25), np.float32(0.5)])
+    exp, exp_amax = o.scaled_dot_f8(a, b, 0.5, 0.25, c=c, beta=1.0, d_scale=2.0, out_dtype=o.F8E4M3FN, want_amax=True)
+    assert o.fp8_within_n_values(exp, d, 1) == 0 and float(amax) == pytest.approx(float(exp_amax), rel=1e-6)
+
+    text = load("relu_amax_e5m2_out")
+    _, plan = hlo_runner.rewrite(text)
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale", "d_scale"] and not plan["operands"][4]["reciprocal"]
+    assert plan["attrs"]["epilogue"] == 3 and plan["attrs"]["damax_output"] is True
+    assert plan["operands"][1]["dtype"] == 19 and plan["results"][0]["dtype"] == 19
+    a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32) * 4, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 80), dtype=np.float32) * 4, "e5m2")
+    d, amax = hlo_eval.evaluate(text, [a, b, np.float32(0.5), np.float32(0.5), np.float32(1.5)])
+    exp, exp_amax = o.scaled_dot_f8(a, b, 0.5, 0.5, b_kind="e5m2", epilogue=o.EPI_RELU, d_scale=1.5, out_dtype=o.F8E5M2, want_amax=True)
+    assert o.fp8_within_n_values(exp, d, 1) == 0 and float(amax) == pytest.approx(float(exp_amax), rel=1e-6)
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -194,7 +221,8 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
-                                  "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot"])
+                                  "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
+                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""
