@@ -77,3 +77,38 @@ def test_progress_rejects_bad_requests(cuda_device):
     assert _native.product.b200sd_scaled_dot_f8_progress(args, prog, None, err, len(err)) == 3
     torch.cuda.synchronize()
     assert counters.item() == 0
+
+
+def test_amax_with_and_without_a_workspace(cuda_device):
+    """With the call site's workspace the kernel clears amax itself (two words at the workspace's end);
+    without one the host puts a memset node in front.  Same amax either way, also when the result
+    buffer starts out holding something larger, and on the second call with the same buffers."""
+    from xla_b200.scaled_dot import Epilogue, GemmBackendConfig
+
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(3)
+    a = torch.randn((512, 256), device=dev, generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn((256, 768), device=dev, generator=g).to(torch.float8_e4m3fn)
+    one = torch.ones((), device=dev)
+    d = torch.zeros((512, 768), dtype=torch.float8_e4m3fn, device=dev)
+    amax = torch.full((), 1e30, dtype=torch.float32, device=dev)
+    ws = torch.empty(1 << 20, dtype=torch.int8, device=dev).random_(-128, 127)
+    err = C.create_string_buffer(512)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def call(workspace):
+        args = _native.ScaledDotF8Args(struct_size=C.sizeof(_native.ScaledDotF8Args), a=a.data_ptr(), b=b.data_ptr(),
+                                       a_scale=one.data_ptr(), b_scale=one.data_ptr(), d_scale=one.data_ptr(), d=d.data_ptr(),
+                                       amax=amax.data_ptr(), workspace=workspace.data_ptr() if workspace is not None else None,
+                                       workspace_bytes=workspace.numel() if workspace is not None else 0, m=512, n=768, k=256,
+                                       a_dtype=20, b_dtype=20, d_dtype=20, lhs_contracting_dim=1, rhs_contracting_dim=0,
+                                       epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+        assert _native.product.b200sd_scaled_dot_f8(args, stream, err, len(err)) == 0, err.value
+        torch.cuda.synchronize()
+        return float(amax.item())
+
+    expect = float((a.float() @ b.float()).abs().max().item())
+    for workspace in (None, ws, ws, None):
+        amax.fill_(1e30)
+        assert call(workspace) == pytest.approx(expect, rel=1e-5)
+    assert device_status() == 0

@@ -136,6 +136,11 @@ struct DenseArgs {
   unsigned long long sk_epoch;          // value that marks a partial of THIS launch as written
   unsigned long long* sk_flags;         // [clusters][2 CTAs][8 warps]
   uint4* sk_partials;                   // [clusters] raw accumulator tiles, 256 KiB each
+  // amax without a memset in front of the launch: two words in the caller's workspace.  The first warp
+  // of THIS launch to finish (it swaps the launch's epoch into word 0 and finds another value there)
+  // stores 0 to amax and then publishes the epoch in word 1; every other warp waits for word 1.
+  unsigned long long* amax_sync;        // nullptr: the host cleared amax with a memset node
+  unsigned long long amax_epoch;
 };
 
 constexpr size_t kSkFlagBytes = 16384;                                 // up to 128 clusters x 16 flags x 8 B
@@ -1021,7 +1026,30 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       // The bit pattern of a non-negative float orders like the float; NaN patterns sit above
       // +inf, so an integer max propagates NaN the way XLA's `maximum` does.
       amax_bits = __reduce_max_sync(0xffffffffu, amax_bits);
-      if (lane == 0) atomicMax(reinterpret_cast<unsigned int*>(p.amax), amax_bits);
+      if (lane == 0) {
+        if (p.amax_sync != nullptr) {
+          const unsigned long long old = atomicExch(p.amax_sync, p.amax_epoch);
+          if (old != p.amax_epoch) {
+            *reinterpret_cast<volatile unsigned int*>(p.amax) = 0u;
+            __threadfence();
+            st_release_gpu_u64(p.amax_sync + 1, p.amax_epoch);
+          } else {
+            uint64_t t0 = 0;
+            uint32_t polls = 0;
+            while (ld_acquire_gpu_u64(p.amax_sync + 1) != p.amax_epoch) {
+              if ((++polls & 1023u) == 0) {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > kWaitLimitNs) {
+                  atomicOr(p.status, kStatusEpilogueTimeout);
+                  break;
+                }
+              }
+            }
+          }
+        }
+        atomicMax(reinterpret_cast<unsigned int*>(p.amax), amax_bits);
+      }
     }
   }
 
@@ -1309,9 +1337,19 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
       p.sk_partials = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.workspace) + kSkFlagBytes);
     }
   }
+  p.amax_sync = nullptr;
   if (g.amax != nullptr) {
-    cudaError_t e = cudaMemsetAsync(g.amax, 0, sizeof(float), stream);
-    if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(amax): ") + cudaGetErrorString(e));
+    // The last 64 bytes of the caller's workspace hold the two words that let the kernel clear amax
+    // itself (the stream-K scratch, when used, sits at the front); without a workspace a memset node does it.
+    const size_t front = p.sk_tiles > 0 ? kSkFlagBytes + size_t(grid / 2) * kSkPartialBytes : 0;
+    if (g.workspace != nullptr && g.workspace_bytes >= front + 128) {
+      uintptr_t end = (reinterpret_cast<uintptr_t>(g.workspace) + g.workspace_bytes) & ~uintptr_t(63);
+      p.amax_sync = reinterpret_cast<unsigned long long*>(end - 64);
+      p.amax_epoch = NextDenseEpoch();
+    } else {
+      cudaError_t e = cudaMemsetAsync(g.amax, 0, sizeof(float), stream);
+      if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(amax): ") + cudaGetErrorString(e));
+    }
   }
   cudaError_t e;
   if (pair) {
