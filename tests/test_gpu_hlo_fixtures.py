@@ -185,3 +185,32 @@ def test_combined_epilogue_modules(cuda_device):
     torch.cuda.synchronize()
     assert o.fp8_within_n_values(exp_d, back(d), 1) == 0
     assert float(amax.item()) == pytest.approx(float(exp_amax), rel=1e-4)
+
+
+def test_all_32_layout_combinations_run(cuda_device):
+    """ScaledABUnscaledDF8Parameterized (gemm_rewriter_fp8_test.cc:2825-2890) end to end: column-major operands are
+    handed over as the row-major matrices they are, a column-major result comes back as D^T."""
+    from test_hlo_rewriter import layout_cases, layout_module
+
+    rng = np.random.default_rng(16)
+    dev = cuda_device
+    sa, sb = np.float32(0.5), np.float32(0.25)
+    for d_col, a_col, b_col, lc, rc in layout_cases():
+        text = layout_module(d_col, a_col, b_col, lc, rc)
+        a_shape = (64, 32) if lc == 1 else (32, 64)
+        b_shape = (32, 16) if rc == 0 else (16, 32)
+        a = o.fp8_encode(rng.standard_normal(a_shape, dtype=np.float32) * 2, "e4m3fn")
+        b = o.fp8_encode(rng.standard_normal(b_shape, dtype=np.float32) * 2, "e4m3fn")
+        exp = hlo_eval.evaluate(text, [a, b, sa, sb])                       # layouts do not change what is computed
+
+        def device_param(x, col):      # logical tensor whose memory is column-major when the module says so
+            t = to_dev(np.ascontiguousarray(x.T) if col else x, "f8e4m3fn", dev)
+            return t.t() if col else t
+
+        got = hlo_runner.run_hlo_module(text, [device_param(a, a_col), device_param(b, b_col), torch.tensor(sa, device=dev),
+                                               torch.tensor(sb, device=dev)])
+        torch.cuda.synchronize()
+        assert tuple(got.shape) == (64, 16)
+        assert got.t().is_contiguous() if d_col else got.is_contiguous()
+        case = f"d_col={d_col} a_col={a_col} b_col={b_col} lc={lc} rc={rc}"
+        assert o.near_mismatches(exp, got.contiguous().cpu().numpy(), 1e-3, 1e-4)[0] == 0, case

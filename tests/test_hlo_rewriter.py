@@ -183,6 +183,59 @@ def test_combined_epilogues():
     assert o.fp8_within_n_values(exp, d, 1) == 0 and float(amax) == pytest.approx(float(exp_amax), rel=1e-6)
 
 
+LAYOUT_TEMPLATE = """HloModule layouts
+ENTRY main {
+  x = f8e4m3fn<<A>><<AL>> parameter(0)
+  x_f32 = f32<<A>><<AL>> convert(x)
+  x_scale = f32[] parameter(2)
+  x_sb = f32<<A>> broadcast(x_scale), dimensions={}
+  x_dq = f32<<A>> multiply(x_f32, x_sb)
+  y = f8e4m3fn<<B>><<BL>> parameter(1)
+  y_f32 = f32<<B>><<BL>> convert(y)
+  y_scale = f32[] parameter(3)
+  y_sb = f32<<B>> broadcast(y_scale), dimensions={}
+  y_dq = f32<<B>> multiply(y_f32, y_sb)
+  ROOT out = f32[64,16]<<OL>> dot(x_dq, y_dq), lhs_contracting_dims={<<LC>>}, rhs_contracting_dims={<<RC>>}
+}
+"""
+
+
+def layout_cases():
+    for d_col in (False, True):
+        for a_col in (False, True):
+            for b_col in (False, True):
+                for lc in (0, 1):
+                    for rc in (0, 1):
+                        yield d_col, a_col, b_col, lc, rc
+
+
+def layout_module(d_col, a_col, b_col, lc, rc):
+    rep = {"<<A>>": "[64,32]" if lc == 1 else "[32,64]", "<<B>>": "[32,16]" if rc == 0 else "[16,32]",
+           "<<AL>>": "{0,1}" if a_col else "{1,0}", "<<BL>>": "{0,1}" if b_col else "{1,0}", "<<OL>>": "{0,1}" if d_col else "{1,0}",
+           "<<LC>>": str(lc), "<<RC>>": str(rc)}
+    text = LAYOUT_TEMPLATE
+    for key, val in rep.items():
+        text = text.replace(key, val)
+    return text
+
+
+@pytest.mark.parametrize("d_col,a_col,b_col,lc,rc", list(layout_cases()))
+def test_all_32_layout_combinations_are_rewritten(d_col, a_col, b_col, lc, rc):
+    """ScaledABUnscaledDF8Parameterized (gemm_rewriter_fp8_test.cc:2825-2890): row / column-major A, B and D with either
+    contracting dimension.  The call takes row-major buffers only, so the plan must describe the same product."""
+    _, plan = hlo_runner.rewrite(layout_module(d_col, a_col, b_col, lc, rc))
+    assert plan["rewritten"], plan
+    a, b = plan["operands"][0], plan["operands"][1]
+    L, R = plan["attrs"]["lhs_contracting_dim"], plan["attrs"]["rhs_contracting_dim"]
+    assert a["dims"][L] == 32 and b["dims"][R] == 32                           # both contract over k = 32
+    want = (16, 64) if d_col else (64, 16)                                      # D^T when the result is column-major
+    assert (a["dims"][1 - L], b["dims"][1 - R]) == want and tuple(plan["results"][0]["dims"]) == want
+    assert plan["results"][0]["transposed"] == d_col
+    first, second = (b_col, a_col) if d_col else (a_col, b_col)                 # the operands swap places for D^T
+    assert a["transposed"] == first and b["transposed"] == second
+    assert a["param"] == (1 if d_col else 0) and plan["operands"][2]["param"] == (3 if d_col else 2)
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]

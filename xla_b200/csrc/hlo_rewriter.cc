@@ -38,6 +38,8 @@ struct Shape {
   std::string type;                 // "f32", "f8e4m3fn", ... or "tuple"
   std::vector<int64_t> dims;
   std::vector<Shape> elements;      // for tuples
+  std::vector<int64_t> layout;      // minor_to_major as written ({1,0} row-major); empty = default (row-major)
+  bool IsColumnMajor2D() const { return dims.size() == 2 && layout.size() == 2 && layout[0] == 0 && layout[1] == 1; }
   std::string ToString() const {
     if (type == "tuple") {
       std::string s = "(";
@@ -46,7 +48,13 @@ struct Shape {
     }
     std::string s = type + "[";
     for (size_t i = 0; i < dims.size(); ++i) s += (i ? "," : "") + std::to_string(dims[i]);
-    return s + "]";
+    s += "]";
+    if (!layout.empty()) {
+      s += "{";
+      for (size_t i = 0; i < layout.size(); ++i) s += (i ? "," : "") + std::to_string(layout[i]);
+      s += "}";
+    }
+    return s;
   }
   bool IsScalar() const { return type != "tuple" && dims.empty(); }
 };
@@ -108,8 +116,15 @@ bool ParseShape(const std::string& text, size_t* pos, Shape* out) {
   if (p >= text.size()) return false;
   if (!num.empty()) out->dims.push_back(std::stoll(num));
   ++p;
-  if (p < text.size() && text[p] == '{') {                // layout suffix {1,0}: skipped
-    while (p < text.size() && text[p] != '}') ++p;
+  if (p < text.size() && text[p] == '{') {                // layout suffix: minor_to_major, e.g. {1,0}
+    ++p;
+    std::string v;
+    while (p < text.size() && text[p] != '}') {
+      if (text[p] == ',') { if (!v.empty()) out->layout.push_back(std::stoll(v)); v.clear(); }
+      else if (isdigit(static_cast<unsigned char>(text[p]))) v += text[p];
+      ++p;
+    }
+    if (!v.empty()) out->layout.push_back(std::stoll(v));
     if (p < text.size()) ++p;
   }
   *pos = p;
@@ -309,6 +324,7 @@ struct Source {
   double constant = 1.0;     // value when param < 0
   Shape shape;
   Shape padded;              // shape the custom call receives (dimensions rounded up to 16)
+  bool transposed = false;   // the parameter is column-major: its buffer IS the row-major matrix with the dimensions swapped
   std::string instr;         // name of the instruction in the original module
 };
 
@@ -360,6 +376,7 @@ struct Plan {
   double alpha = 1.0, beta = 0.0;
   bool damax = false, emit_s32 = false;
   int64_t batch = 0;                   // > 0: leading batch dimension of a, b, c and D
+  bool d_transposed = false;           // the result is column-major: the call computes D^T = B^T A^T into a row-major [n, m] buffer
   std::vector<Source> operands;
   Shape d_shape, d_padded;
   int d_root_index = -1, amax_root_index = -1;   // position in the ROOT tuple (-1: ROOT itself / absent)
@@ -605,6 +622,42 @@ Plan Decide(const Graph& g) {
   const std::string& dt = plan.d_shape.type;
   if (!(dt == "bf16" || dt == "f16" || dt == "f32" || IsF8(dt))) { plan.rewritten = false; plan.reason = "unsupported output type " + dt; return plan; }
   if (dt == "f8e5m2" && a.shape.type == "f8e4m3fn" && b.shape.type == "f8e4m3fn") { plan.reason = "e4m3 x e4m3 -> e5m2 is not in the supported type table"; return plan; }
+
+  // Layouts (gemm_rewriter_fp8_test.cc:2825-2890 runs all 32 combinations).  The custom call takes row-major
+  // buffers only: a column-major [r, c] operand IS the row-major [c, r] matrix, so it is passed as that with its
+  // contracting dimension renumbered; a column-major result is D^T, obtained by swapping the operands
+  // (MakeOutputColumnMajor's identity, xla/stream_executor/gpu/gpu_blas_lt.cc:271-287).
+  if (plan.batch == 0) {
+    auto as_row_major = [](Source* src, int* contracting) {
+      std::swap(src->shape.dims[0], src->shape.dims[1]);
+      src->shape.layout.clear();
+      src->transposed = true;
+      *contracting = 1 - *contracting;
+    };
+    if (plan.operands[0].shape.IsColumnMajor2D()) as_row_major(&plan.operands[0], &plan.lhs_contracting);
+    if (plan.operands[1].shape.IsColumnMajor2D()) as_row_major(&plan.operands[1], &plan.rhs_contracting);
+    if (plan.d_shape.IsColumnMajor2D()) {
+      if (plan.epilogue != 1 || plan.beta != 0.0 || plan.damax || plan.operands.size() != 4) {
+        plan.reason = "a column-major result is handled for the plain scaled dot only";
+        return plan;
+      }
+      std::swap(plan.operands[0], plan.operands[1]);
+      std::swap(plan.operands[2], plan.operands[3]);
+      plan.operands[0].role = "a"; plan.operands[1].role = "b";
+      plan.operands[2].role = "a_scale"; plan.operands[3].role = "b_scale";
+      std::swap(plan.lhs_contracting, plan.rhs_contracting);
+      std::swap(plan.m, plan.n);
+      std::swap(plan.d_shape.dims[0], plan.d_shape.dims[1]);
+      plan.d_shape.layout.clear();
+      plan.d_transposed = true;
+    }
+  } else if (plan.operands[0].shape.IsColumnMajor2D() || !plan.d_shape.layout.empty() || !plan.operands[0].shape.layout.empty() ||
+             !plan.operands[1].shape.layout.empty()) {
+    bool default_layouts = true;
+    for (const Shape* sh : {&plan.operands[0].shape, &plan.operands[1].shape, &plan.d_shape})
+      for (size_t i = 0; i < sh->layout.size(); ++i) default_layouts = default_layouts && sh->layout[i] == int64_t(sh->layout.size() - 1 - i);
+    if (!default_layouts) { plan.reason = "batched dots are handled in the default (row-major) layout only"; return plan; }
+  }
   plan.rewritten = true;
   return plan;
 }
@@ -669,6 +722,10 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
       o << "  " << one << " = f32[] constant(1)\n";
       o << "  " << n << " = f32[] divide(" << one << ", " << s.instr << ")\n";
       op_names.push_back(n);
+    } else if (s.transposed) {
+      const std::string n = s.role + "_rm";          // the same bytes, read as the row-major matrix they are
+      o << "  " << n << " = " << s.shape.ToString() << "{1,0} bitcast(" << s.instr << ")\n";
+      op_names.push_back(n);
     } else {
       op_names.push_back(s.instr);
     }
@@ -719,6 +776,12 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     o << "  d = " << d_logical.ToString() << " slice(d_full), slice={";
     for (size_t d = 0; d < d_logical.dims.size(); ++d) o << (d ? ", " : "") << "[0:" << d_logical.dims[d] << "]";
     o << "}\n";
+  } else if (plan->d_transposed) {
+    Shape logical = plan->d_shape;
+    std::swap(logical.dims[0], logical.dims[1]);
+    logical.layout = {0, 1};
+    o << "  d_t = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
+    o << "  d = " << logical.ToString() << " bitcast(d_t)\n";
   } else {
     o << "  d = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
   }
@@ -728,7 +791,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     for (size_t i = 0; i < root_elems.size(); ++i) o << (i ? ", " : "") << (int(i) == plan->d_root_index ? "d" : "amax");
     o << ")\n";
   } else {
-    o << "  ROOT out = " << plan->d_shape.ToString() << " copy(d)\n";
+    o << "  ROOT out = " << root->shape.ToString() << " copy(d)\n";
   }
   o << "}\n";
   *hlo = o.str();
@@ -740,10 +803,12 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     const Source& s = plan->operands[i];
     j << (i ? ", " : "") << "{\"role\": " << JsonStr(s.role) << ", \"param\": " << s.param << ", \"reciprocal\": "
       << (s.reciprocal ? "true" : "false") << ", \"constant\": " << Num(s.constant) << ", \"dtype\": " << TypeCode(s.shape.type)
-      << ", \"dims\": " << Dims(s.shape) << ", \"padded_dims\": " << Dims(s.padded) << "}";
+      << ", \"dims\": " << Dims(s.shape) << ", \"padded_dims\": " << Dims(s.padded) << ", \"transposed\": "
+      << (s.transposed ? "true" : "false") << "}";
   }
   j << "], \"results\": [{\"role\": \"d\", \"dtype\": " << TypeCode(plan->d_shape.type) << ", \"dims\": " << Dims(plan->d_shape)
-    << ", \"padded_dims\": " << Dims(plan->d_padded) << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
+    << ", \"padded_dims\": " << Dims(plan->d_padded) << ", \"transposed\": " << (plan->d_transposed ? "true" : "false")
+    << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
   if (plan->damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": [], \"root_index\": " << plan->amax_root_index << "}";
   j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
   j << "], \"attrs\": {\"alpha_real\": " << F64(plan->alpha) << ", \"beta\": " << F64(plan->beta) << ", \"epilogue\": " << plan->epilogue

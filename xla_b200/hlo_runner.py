@@ -55,6 +55,12 @@ def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
             operands.append((1.0 / params[src["param"]].float()).reshape(()))
         else:
             operands.append(params[src["param"]])
+        if src.get("transposed"):
+            # a column-major parameter: the same bytes are the row-major matrix with the dimensions swapped
+            phys = operands[-1].t()
+            if not phys.is_contiguous():
+                raise ValueError(f"parameter {src['param']} is declared column-major; pass a tensor whose .t() is contiguous")
+            operands[-1] = phys
         if src.get("padded_dims", src["dims"]) != src["dims"]:
             # the `pad` instructions of the rewritten module: zero-fill up to multiples of 16
             t = operands[-1]
@@ -69,7 +75,8 @@ def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
         results.append(t)
         if res["root_index"] >= -1:
             # the `slice` instruction of the rewritten module
-            outputs[res["root_index"]] = t[tuple(slice(0, d) for d in res["dims"])] if alloc != res["dims"] else t
+            out = t[tuple(slice(0, d) for d in res["dims"])] if alloc != res["dims"] else t
+            outputs[res["root_index"]] = out.t() if res.get("transposed") else out     # a column-major result: D^T was computed
     attrs = dict(plan["attrs"])
     for key in ("alpha_real", "beta"):                       # f64 attributes, whatever the JSON reader made of them
         attrs[key] = float(attrs[key])
