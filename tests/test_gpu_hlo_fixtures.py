@@ -214,3 +214,21 @@ def test_all_32_layout_combinations_run(cuda_device):
         assert got.t().is_contiguous() if d_col else got.is_contiguous()
         case = f"d_col={d_col} a_col={a_col} b_col={b_col} lc={lc} rc={rc}"
         assert o.near_mismatches(exp, got.contiguous().cpu().numpy(), 1e-3, 1e-4)[0] == 0, case
+
+
+def test_precision_module_meets_the_highest_precision_bound(cuda_device):
+    """UnscaledABUnscaledDPrecisionF8 (gemm_rewriter_fp8_test.cc:2793-2823): 1600 x 3200 x 1600, f32 result within
+    ErrorSpec{1e-3, 1e-3} of the interpreter at default precision and {1e-4, 1e-4} at `highest`.  The kernel has one
+    accumulation mode (full f32 in TMEM), so it has to meet the tighter bound."""
+    text = load("precision_1600x3200x1600")
+    rng = np.random.default_rng(17)
+    a = o.fp8_encode(rng.standard_normal((1600, 3200), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((3200, 1600), dtype=np.float32), "e4m3fn")
+    sa, sb = np.float32(1.0), np.float32(1.0)
+    exp = hlo_eval.evaluate(text, [a, b, sa, sb])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device)])
+    torch.cuda.synchronize()
+    got = back(got)
+    assert o.near_mismatches(exp, got, 1e-3, 1e-3)[0] == 0
+    assert o.near_mismatches(exp, got, 1e-4, 1e-4)[0] == 0

@@ -275,7 +275,7 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
                                   "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
-                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out"])
+                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""
