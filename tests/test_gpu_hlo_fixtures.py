@@ -232,3 +232,14 @@ def test_precision_module_meets_the_highest_precision_bound(cuda_device):
     got = back(got)
     assert o.near_mismatches(exp, got, 1e-3, 1e-3)[0] == 0
     assert o.near_mismatches(exp, got, 1e-4, 1e-4)[0] == 0
+
+
+def test_tiny_int8_module(cuda_device):
+    text = load("int8_12x4x8")
+    rng = np.random.default_rng(19)
+    a = rng.integers(-127, 128, (12, 4), dtype=np.int8)
+    b = rng.integers(-127, 128, (4, 8), dtype=np.int8)
+    got = hlo_runner.run_hlo_module(text, [torch.from_numpy(a).to(cuda_device), torch.from_numpy(b).to(cuda_device)])
+    torch.cuda.synchronize()
+    assert tuple(got.shape) == (12, 8)
+    assert np.array_equal(got.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32))     # bit-exact

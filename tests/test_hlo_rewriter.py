@@ -236,6 +236,20 @@ def test_all_32_layout_combinations_are_rewritten(d_col, a_col, b_col, lc, rc):
     assert a["param"] == (1 if d_col else 0) and plan["operands"][2]["param"] == (3 if d_col else 2)
 
 
+def test_tiny_int8_dot_is_padded_and_sliced():
+    """Int8Gemm / Int8GemmNotMultipleOfFour (gemm_rewriter_test.cc:3182-3209, 3324-3368): the reference pads s8 operands
+    (CublasPadForGemms, to multiples of 4) and slices the s32 result; this library's unit is 16."""
+    text = load("int8_12x4x8")
+    hlo, plan = hlo_runner.rewrite(text)
+    assert plan["target"] == "b200$dot$s8" and plan["results"][0]["dtype"] == 4
+    assert [s["padded_dims"] for s in plan["operands"]] == [[16, 16], [16, 16]] and plan["results"][0]["padded_dims"] == [16, 16]
+    assert "slice={[0:12], [0:8]}" in hlo
+    rng = np.random.default_rng(18)
+    a = rng.integers(-127, 128, (12, 4), dtype=np.int8)
+    b = rng.integers(-127, 128, (4, 8), dtype=np.int8)
+    assert np.array_equal(hlo_eval.evaluate(text, [a, b]), a.astype(np.int32) @ b.astype(np.int32))
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -275,7 +289,7 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
                                   "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
-                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600"])
+                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""
@@ -285,8 +299,11 @@ def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     _, plan = hlo_runner.rewrite(load(name))
     assert plan["rewritten"], plan
     assert isinstance(plan["attrs"]["beta"], float) and isinstance(plan["attrs"]["alpha_real"], float)
-    ops = [torch.empty(tuple(s["dims"]), dtype=hlo_runner._torch_dtype(s["dtype"]), device="meta") for s in plan["operands"]]
-    res = [torch.empty(tuple(r["dims"]), dtype=hlo_runner._torch_dtype(r["dtype"]), device="meta") for r in plan["results"]]
+    # the call receives the padded shapes (the pad / slice instructions stay outside it)
+    ops = [torch.empty(tuple(s.get("padded_dims", s["dims"])), dtype=hlo_runner._torch_dtype(s["dtype"]), device="meta")
+           for s in plan["operands"]]
+    res = [torch.empty(tuple(r.get("padded_dims", r["dims"])), dtype=hlo_runner._torch_dtype(r["dtype"]), device="meta")
+           for r in plan["results"]]
     call = FfiCall(plan["target"], ops, res, dict(plan["attrs"]))
     call.instantiate()
     call.close()
