@@ -2,7 +2,7 @@
 
 Evaluates the small subset of HLO text the fixtures under tests/golden/hlo use (parameter,
 constant, convert, broadcast, multiply, divide, add, dot, tanh, maximum, abs, reduce with a max
-computation, clamp, copy, tuple, get-tuple-element) with the interpreter's rules
+computation, clamp, copy, bitcast, reshape, tuple, get-tuple-element) with the interpreter's rules
 (xla/hlo/evaluator/hlo_evaluator_typed_visitor.h: element-wise ops in the operand type, dot with
 f32 accumulation :1271-1340, maximum / clamp propagating NaN :594-613, :843-865), using the
 conversions of scaled_dot_oracle.py.  It lets the SAME module text drive both the expected values
@@ -139,6 +139,8 @@ def evaluate(text, params):
                 val = (t, _from_f32(t, _to_f32(st, sv)))
         elif op in ("copy",):
             val = a[0]
+        elif op in ("bitcast", "reshape"):            # default layouts only: a row-major reinterpretation of the shape
+            val = (t, np.asarray(a[0][1]).reshape(dims))
         elif op == "broadcast":
             bd = _attr_dims(ins["attrs"], "dimensions") or ()
             st, sv = a[0]

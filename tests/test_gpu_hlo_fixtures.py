@@ -243,3 +243,17 @@ def test_tiny_int8_module(cuda_device):
     torch.cuda.synchronize()
     assert tuple(got.shape) == (12, 8)
     assert np.array_equal(got.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32))     # bit-exact
+
+
+def test_bitcast_operand_module(cuda_device):
+    text = load("bitcast_operand")
+    rng = np.random.default_rng(21)
+    a = o.fp8_encode(rng.standard_normal((2, 24, 64), dtype=np.float32) * 2, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32) * 2, "e4m3fn")
+    sa, sb = np.float32(0.5), np.float32(0.25)
+    exp = hlo_eval.evaluate(text, [a, b, sa, sb])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           torch.tensor(sa, device=cuda_device), torch.tensor(sb, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert tuple(got.shape) == (48, 32)
+    assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0

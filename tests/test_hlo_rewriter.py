@@ -250,6 +250,20 @@ def test_tiny_int8_dot_is_padded_and_sliced():
     assert np.array_equal(hlo_eval.evaluate(text, [a, b]), a.astype(np.int32) @ b.astype(np.int32))
 
 
+def test_bitcast_between_dequantisation_and_dot():
+    """ScaledABUnscaledDBitcastF8 (gemm_rewriter_fp8_test.cc:579-612)."""
+    text = load("bitcast_operand")
+    hlo, plan = hlo_runner.rewrite(text)
+    assert plan["rewritten"] and (plan["m"], plan["k"], plan["n"]) == (48, 64, 32)
+    assert plan["operands"][0]["dims"] == [48, 64] and plan["operands"][0]["reshaped"] and not plan["operands"][1]["reshaped"]
+    assert "a_view = f8e4m3fn[48,64] bitcast(a)" in hlo and "custom-call(a_view, b, a_scale, b_scale)" in hlo
+    rng = np.random.default_rng(20)
+    a = o.fp8_encode(rng.standard_normal((2, 24, 64), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32), "e4m3fn")
+    out = hlo_eval.evaluate(text, [a, b, np.float32(0.5), np.float32(2.0)])
+    np.testing.assert_allclose(out, o.scaled_dot_f8(a.reshape(48, 64), b, 0.5, 2.0, out_dtype=o.F32)[0], rtol=1e-6, atol=1e-6)
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -289,7 +303,7 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
                                   "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
-                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8"])
+                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8", "bitcast_operand"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""

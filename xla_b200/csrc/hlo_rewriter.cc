@@ -324,6 +324,7 @@ struct Source {
   double constant = 1.0;     // value when param < 0
   Shape shape;
   Shape padded;              // shape the custom call receives (dimensions rounded up to 16)
+  bool reshaped = false;     // the parameter is viewed in another shape (a bitcast of the same row-major bytes)
   bool transposed = false;   // the parameter is column-major: its buffer IS the row-major matrix with the dimensions swapped
   std::string instr;         // name of the instruction in the original module
 };
@@ -338,11 +339,21 @@ struct Fp8Operand {
   Instr* f8 = nullptr;       // the FP8 value (must be a parameter in the lite version)
   Instr* scale = nullptr;    // scalar the dequantised value was multiplied / divided by, or nullptr
   bool divide = false;
+  bool reshaped = false;     // a bitcast / reshape sat between the dequantisation and the dot
+  Shape view;                // ... and gave the operand this shape (same bytes, row-major)
 };
 
 // MatchFp8Param (gemm_rewriter.cc:190-336) for the shapes the fixtures use.
 bool MatchFp8Operand(const Graph& g, Instr* x, Fp8Operand* out) {
   if (x == nullptr) return false;
+  // A bitcast / reshape of the dequantised value commutes with the dequantisation (FindF8SubgraphRecursive walks
+  // through it, gemm_rewriter.cc:248-336; gemm_rewriter_fp8_test.cc:579-612): the FP8 buffer is viewed in the new shape.
+  while (x->opcode == "bitcast" || x->opcode == "reshape") {
+    if (!x->shape.layout.empty() && !std::is_sorted(x->shape.layout.rbegin(), x->shape.layout.rend())) return false;
+    if (!out->reshaped) { out->reshaped = true; out->view = x->shape; }
+    x = g.Operand(x, 0);
+    if (x == nullptr) return false;
+  }
   if (IsF8(x->shape.type)) {        // an FP8 value fed to the dot as it is (gemm_rewriter_fp8_test.cc:313-350)
     out->f8 = x;
     return true;
@@ -612,6 +623,16 @@ Plan Decide(const Graph& g) {
   plan.target = "b200$scaled_dot$f8";
   Source a; a.role = "a"; a.param = pa; a.shape = fa.f8->shape; a.instr = fa.f8->name;
   Source b; b.role = "b"; b.param = pb; b.shape = fb.f8->shape; b.instr = fb.f8->name;
+  for (auto pr : {std::make_pair(&a, &fa), std::make_pair(&b, &fb)}) {
+    if (!pr.second->reshaped) continue;
+    if (!pr.first->shape.layout.empty() && !std::is_sorted(pr.first->shape.layout.rbegin(), pr.first->shape.layout.rend())) {
+      plan.reason = "a reshaped operand must be in the default layout";
+      return plan;
+    }
+    pr.first->shape.dims = pr.second->view.dims;
+    pr.first->shape.layout.clear();
+    pr.first->reshaped = true;
+  }
   Source as, bs;
   if (!ScaleSource(g, fa.scale, fa.divide, "a_scale", &as, &plan.reason)) return plan;
   if (!ScaleSource(g, fb.scale, fb.divide, "b_scale", &bs, &plan.reason)) return plan;
@@ -722,6 +743,10 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
       o << "  " << one << " = f32[] constant(1)\n";
       o << "  " << n << " = f32[] divide(" << one << ", " << s.instr << ")\n";
       op_names.push_back(n);
+    } else if (s.reshaped && !s.transposed) {
+      const std::string n = s.role + "_view";
+      o << "  " << n << " = " << s.shape.ToString() << " bitcast(" << s.instr << ")\n";
+      op_names.push_back(n);
     } else if (s.transposed) {
       const std::string n = s.role + "_rm";          // the same bytes, read as the row-major matrix they are
       o << "  " << n << " = " << s.shape.ToString() << "{1,0} bitcast(" << s.instr << ")\n";
@@ -804,7 +829,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     j << (i ? ", " : "") << "{\"role\": " << JsonStr(s.role) << ", \"param\": " << s.param << ", \"reciprocal\": "
       << (s.reciprocal ? "true" : "false") << ", \"constant\": " << Num(s.constant) << ", \"dtype\": " << TypeCode(s.shape.type)
       << ", \"dims\": " << Dims(s.shape) << ", \"padded_dims\": " << Dims(s.padded) << ", \"transposed\": "
-      << (s.transposed ? "true" : "false") << "}";
+      << (s.transposed ? "true" : "false") << ", \"reshaped\": " << (s.reshaped ? "true" : "false") << "}";
   }
   j << "], \"results\": [{\"role\": \"d\", \"dtype\": " << TypeCode(plan->d_shape.type) << ", \"dims\": " << Dims(plan->d_shape)
     << ", \"padded_dims\": " << Dims(plan->d_padded) << ", \"transposed\": " << (plan->d_transposed ? "true" : "false")

@@ -55,6 +55,11 @@ def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
             operands.append((1.0 / params[src["param"]].float()).reshape(()))
         else:
             operands.append(params[src["param"]])
+        if src.get("reshaped"):
+            # a bitcast between the dequantisation and the dot: the same row-major bytes in the shape the dot saw
+            if not operands[-1].is_contiguous():
+                raise ValueError(f"parameter {src['param']} is viewed in another shape and must be contiguous")
+            operands[-1] = operands[-1].reshape(tuple(src["dims"]))
         if src.get("transposed"):
             # a column-major parameter: the same bytes are the row-major matrix with the dimensions swapped
             phys = operands[-1].t()
