@@ -257,3 +257,19 @@ def test_bitcast_operand_module(cuda_device):
     torch.cuda.synchronize()
     assert tuple(got.shape) == (48, 32)
     assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0
+
+
+def test_rank3_vector_bias_module(cuda_device):
+    text = load("rank3_vector_bias")
+    rng = np.random.default_rng(23)
+    a = o.fp8_encode(rng.standard_normal((4, 16, 64), dtype=np.float32) * 2, "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32) * 2, "e4m3fn")
+    bias = o.make_bias_bf16(23, 32)
+    sa, sb = np.float32(0.5), np.float32(0.25)
+    exp = hlo_eval.evaluate(text, [a, b, bias, sa, sb])
+    got = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                           to_dev(bias, "bf16", cuda_device), torch.tensor(sa, device=cuda_device),
+                                           torch.tensor(sb, device=cuda_device)])
+    torch.cuda.synchronize()
+    assert tuple(got.shape) == (4, 16, 32)
+    assert o.near_mismatches(exp, back(got), 1e-3, 1e-4)[0] == 0

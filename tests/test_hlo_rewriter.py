@@ -264,6 +264,24 @@ def test_bitcast_between_dequantisation_and_dot():
     np.testing.assert_allclose(out, o.scaled_dot_f8(a.reshape(48, 64), b, 0.5, 2.0, out_dtype=o.F32)[0], rtol=1e-6, atol=1e-6)
 
 
+def test_rank3_activation_with_vector_bias_on_the_view():
+    """Rank3ScaledABUnscaledDVectorBiasF8 (gemm_rewriter_fp8_test.cc:2112-2186): bitcast in, matrix product, bitcast out,
+    bias added on the rank-3 view -- one custom call producing the [m, n] matrix, viewed as [4, 16, 32]."""
+    text = load("rank3_vector_bias")
+    hlo, plan = hlo_runner.rewrite(text)
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"] and plan["attrs"]["epilogue"] == 2
+    assert plan["operands"][0]["dims"] == [64, 64] and plan["operands"][0]["reshaped"]
+    assert plan["results"][0]["dims"] == [64, 32] and plan["results"][0]["view_dims"] == [4, 16, 32]
+    assert "d = f32[4,16,32] bitcast(d_mat)" in hlo
+    rng = np.random.default_rng(22)
+    a = o.fp8_encode(rng.standard_normal((4, 16, 64), dtype=np.float32), "e4m3fn")
+    b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32), "e4m3fn")
+    bias = o.make_bias_bf16(22, 32)
+    out = hlo_eval.evaluate(text, [a, b, bias, np.float32(0.5), np.float32(2.0)])
+    exp = o.scaled_dot_f8(a.reshape(64, 64), b, 0.5, 2.0, bias=o.bf16_bits_to_f32(bias), epilogue=o.EPI_BIAS, out_dtype=o.F32)[0]
+    np.testing.assert_allclose(out.reshape(64, 32), exp, rtol=1e-6, atol=1e-6)
+
+
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
     assert not plan["rewritten"] and "e5m2" in plan["reason"]
@@ -303,7 +321,7 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
 @pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
                                   "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
                                   "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
-                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8", "bitcast_operand"])
+                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8", "bitcast_operand", "rank3_vector_bias"])
 def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     """The plan's operands, results and attributes must form a call frame the handler accepts at
     instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""

@@ -387,6 +387,8 @@ struct Plan {
   double alpha = 1.0, beta = 0.0;
   bool damax = false, emit_s32 = false;
   int64_t batch = 0;                   // > 0: leading batch dimension of a, b, c and D
+  bool d_viewed = false;               // a bitcast / reshape sits behind the dot: the [m, n] result is viewed as d_view
+  Shape d_view;
   bool d_transposed = false;           // the result is column-major: the call computes D^T = B^T A^T into a row-major [n, m] buffer
   std::vector<Source> operands;
   Shape d_shape, d_padded;
@@ -420,6 +422,16 @@ void MatchF8Epilogue(const Graph& g, Instr* dot, Plan* plan) {
     if (other != nullptr && ScalarConstant(g, BroadcastedScalar(g, other), &c)) {
       plan->alpha = c;
       cur = mul;
+    }
+  }
+  // -- a bitcast / reshape of the dot's result that keeps the minor dimension (a rank-3 x rank-2 dot written as a
+  //    matrix product, gemm_rewriter_fp8_test.cc:2112-2186, 2274-2344): the epilogue continues on the view
+  if (g.Users(cur).size() == 1 && (g.Users(cur)[0]->opcode == "bitcast" || g.Users(cur)[0]->opcode == "reshape")) {
+    Instr* v = g.Users(cur)[0];
+    const bool row_major = v->shape.layout.empty() || std::is_sorted(v->shape.layout.rbegin(), v->shape.layout.rend());
+    if (row_major && !v->shape.dims.empty() && v->shape.dims.back() == plan->n) {
+      plan->d_viewed = true;
+      cur = v;
     }
   }
   // -- bias (vector along the minor dimension, or a full matrix with beta = 1)
@@ -640,6 +652,21 @@ Plan Decide(const Graph& g) {
   plan.d_instr = dot->name;
   plan.d_shape = dot->shape;
   MatchF8Epilogue(g, dot, &plan);
+  if (plan.d_viewed) {
+    // The call produces the [m, n] matrix; the module sees it in the shape of the view.  A matrix bias given in that
+    // shape is the same bytes as an [m, n] matrix.
+    plan.d_view = plan.d_shape;
+    plan.d_view.layout.clear();
+    plan.d_shape.dims = {plan.m, plan.n};
+    plan.d_shape.layout.clear();
+    for (Source& src : plan.operands) {
+      if (src.role == "c" && src.shape.dims.size() != 2) {
+        src.shape.dims = {plan.m, plan.n};
+        src.shape.layout.clear();
+        src.reshaped = true;
+      }
+    }
+  }
   const std::string& dt = plan.d_shape.type;
   if (!(dt == "bf16" || dt == "f16" || dt == "f32" || IsF8(dt))) { plan.rewritten = false; plan.reason = "unsupported output type " + dt; return plan; }
   if (dt == "f8e5m2" && a.shape.type == "f8e4m3fn" && b.shape.type == "f8e4m3fn") { plan.reason = "e4m3 x e4m3 -> e5m2 is not in the supported type table"; return plan; }
@@ -796,9 +823,10 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     o << "lhs_contracting_dim = " << plan->lhs_contracting << " : i64, rhs_contracting_dim = " << plan->rhs_contracting
       << " : i64, emit_s32 = false}\n";
   }
+  const std::string dn = plan->d_viewed ? "d_mat" : "d";      // the [m, n] result; `d` is what the module sees
   if (padded || plan->d_padded.dims != d_logical.dims) {
     o << "  d_full = " << plan->d_padded.ToString() << " get-tuple-element(cc), index=0\n";
-    o << "  d = " << d_logical.ToString() << " slice(d_full), slice={";
+    o << "  " << dn << " = " << d_logical.ToString() << " slice(d_full), slice={";
     for (size_t d = 0; d < d_logical.dims.size(); ++d) o << (d ? ", " : "") << "[0:" << d_logical.dims[d] << "]";
     o << "}\n";
   } else if (plan->d_transposed) {
@@ -806,10 +834,11 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
     std::swap(logical.dims[0], logical.dims[1]);
     logical.layout = {0, 1};
     o << "  d_t = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
-    o << "  d = " << logical.ToString() << " bitcast(d_t)\n";
+    o << "  " << dn << " = " << logical.ToString() << " bitcast(d_t)\n";
   } else {
-    o << "  d = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
+    o << "  " << dn << " = " << plan->d_shape.ToString() << " get-tuple-element(cc), index=0\n";
   }
+  if (plan->d_viewed) o << "  d = " << plan->d_view.ToString() << " bitcast(d_mat)\n";
   if (plan->damax) o << "  amax = f32[] get-tuple-element(cc), index=1\n";
   if (root->opcode == "tuple") {
     o << "  ROOT out = " << root->shape.ToString() << " tuple(";
@@ -833,7 +862,7 @@ bool Emit(const Module& m, const Graph& g, Plan* plan, std::string* hlo, std::st
   }
   j << "], \"results\": [{\"role\": \"d\", \"dtype\": " << TypeCode(plan->d_shape.type) << ", \"dims\": " << Dims(plan->d_shape)
     << ", \"padded_dims\": " << Dims(plan->d_padded) << ", \"transposed\": " << (plan->d_transposed ? "true" : "false")
-    << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
+    << ", \"view_dims\": " << (plan->d_viewed ? Dims(plan->d_view) : std::string("null")) << ", \"root_index\": " << (root->opcode == "tuple" ? plan->d_root_index : -1) << "}";
   if (plan->damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": [], \"root_index\": " << plan->amax_root_index << "}";
   j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "], \"root_index\": -2}";
   j << "], \"attrs\": {\"alpha_real\": " << F64(plan->alpha) << ", \"beta\": " << F64(plan->beta) << ", \"epilogue\": " << plan->epilogue

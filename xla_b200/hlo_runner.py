@@ -81,7 +81,11 @@ def run_hlo_module(hlo_text: str, params: Sequence, stream=None):
         if res["root_index"] >= -1:
             # the `slice` instruction of the rewritten module
             out = t[tuple(slice(0, d) for d in res["dims"])] if alloc != res["dims"] else t
-            outputs[res["root_index"]] = out.t() if res.get("transposed") else out     # a column-major result: D^T was computed
+            if res.get("transposed"):
+                out = out.t()                                   # a column-major result: D^T was computed
+            if res.get("view_dims"):
+                out = out.reshape(tuple(res["view_dims"]))      # the bitcast behind the dot
+            outputs[res["root_index"]] = out
     attrs = dict(plan["attrs"])
     for key in ("alpha_real", "beta"):                       # f64 attributes, whatever the JSON reader made of them
         attrs[key] = float(attrs[key])
