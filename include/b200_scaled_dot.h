@@ -37,16 +37,20 @@ enum {
   B200SD_F8E4M3FN = 20
 };
 
-/* GemmBackendConfig.Epilogue (xla/service/gpu/backend_configs.proto:106-117). */
+/* GemmBackendConfig.Epilogue, with the enum's own (0-based) numbers
+ * (xla/service/gpu/backend_configs.proto:106-117), so that a backend_config written by
+ * GemmRewriter is understood as it stands. */
 enum {
-  B200SD_EPILOGUE_DEFAULT = 1,
-  B200SD_EPILOGUE_BIAS = 2,
-  B200SD_EPILOGUE_RELU = 3,
-  B200SD_EPILOGUE_BIAS_RELU = 4,
-  B200SD_EPILOGUE_GELU = 5,
-  B200SD_EPILOGUE_GELU_AUX = 6,       /* not implemented: returns UNIMPLEMENTED */
-  B200SD_EPILOGUE_BIAS_GELU = 7,
-  B200SD_EPILOGUE_BIAS_GELU_AUX = 8   /* not implemented: returns UNIMPLEMENTED */
+  B200SD_EPILOGUE_DEFAULT = 0,
+  B200SD_EPILOGUE_BIAS = 1,
+  B200SD_EPILOGUE_RELU = 2,
+  B200SD_EPILOGUE_BIAS_RELU = 3,
+  B200SD_EPILOGUE_GELU = 4,
+  B200SD_EPILOGUE_GELU_AUX = 5,       /* not implemented: returns UNIMPLEMENTED (as thunk_emitter.cc:842 for FP8) */
+  B200SD_EPILOGUE_BIAS_GELU = 6,
+  B200SD_EPILOGUE_BIAS_GELU_AUX = 7,  /* not implemented: returns UNIMPLEMENTED */
+  B200SD_EPILOGUE_SILU = 8,           /* not implemented: returns UNIMPLEMENTED (as cuda_blas_lt.cc:142-146) */
+  B200SD_EPILOGUE_BIAS_SILU = 9       /* not implemented: returns UNIMPLEMENTED */
 };
 
 /* Kernel choice; plays the role of GemmBackendConfig.selected_algorithm. */

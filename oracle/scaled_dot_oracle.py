@@ -45,8 +45,8 @@ import numpy as np
 S8, S32, F16, F32, BF16, F8E5M2, F8E4M3FN = 2, 4, 10, 11, 16, 19, 20
 
 # GemmBackendConfig.Epilogue values (xla/service/gpu/backend_configs.proto:106-117).
-EPI_DEFAULT, EPI_BIAS, EPI_RELU, EPI_BIAS_RELU = 1, 2, 3, 4
-EPI_GELU, EPI_GELU_AUX, EPI_BIAS_GELU, EPI_BIAS_GELU_AUX = 5, 6, 7, 8
+EPI_DEFAULT, EPI_BIAS, EPI_RELU, EPI_BIAS_RELU = 0, 1, 2, 3
+EPI_GELU, EPI_GELU_AUX, EPI_BIAS_GELU, EPI_BIAS_GELU_AUX = 4, 5, 6, 7
 
 _FP8 = {
     # name: (exponent bits, mantissa bits, bias, finite-only "fn" flavour)

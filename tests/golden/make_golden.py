@@ -11,6 +11,9 @@ Sources, read as text:
     literals, `nan`, `inf`).
   * xla/stream_executor/cuda/cuda_blas_lt_test.cc -- the S8S8S32 / S8S8F32
     known answer: m = n = k = 32, all-ones operands, every output == k.
+  * xla/service/gpu/backend_configs.proto -- `enum Epilogue { ... }` of GemmBackendConfig, and
+    xla/ffi/api/c_api.h -- `XLA_FFI_DataType`, `XLA_FFI_Error_Code`: the numbers the boundary
+    (include/b200_scaled_dot.h) must use (interface_enums.json).
 """
 import json
 import math
@@ -53,6 +56,37 @@ def enc(v: float):
     return v.hex()
 
 
+def c_enum(src: str, start_marker: str, prefix: str):
+    """`NAME = number` pairs of the C / proto enum that starts at `start_marker`."""
+    begin = src.index(start_marker)
+    end = src.index("}", begin)
+    line = src[:begin].count("\n") + 1
+    vals = {}
+    for m in re.finditer(r"\b" + prefix + r"([A-Z0-9_a-z]+)\s*=\s*(\d+)\s*[,;]", src[begin:end]):
+        vals[m.group(1)] = int(m.group(2))
+    return line, src[:end].count("\n") + 1, vals
+
+
+def write_interface_enums():
+    proto = open(os.path.join(ROOT, "xla/service/gpu/backend_configs.proto")).read()
+    gemm = proto.index("message GemmBackendConfig")
+    l0, l1, epilogue = c_enum(proto[gemm:], "enum Epilogue {", "")
+    base = proto[:gemm].count("\n")
+    capi = open(os.path.join(ROOT, "xla/ffi/api/c_api.h")).read()
+    d0, d1, dtypes = c_enum(capi, "  XLA_FFI_DataType_INVALID = 0", "XLA_FFI_DataType_")
+    e0, e1, codes = c_enum(capi, "  XLA_FFI_Error_Code_OK = 0", "XLA_FFI_Error_Code_")
+    scale_mode = re.search(r"int32 scale_mode = (\d+);", proto)
+    assert epilogue["DEFAULT"] == 0 and len(epilogue) == 10 and dtypes["F8E4M3FN"] == 20 and codes["UNIMPLEMENTED"] == 12
+    out = {
+        "epilogue": {"source": f"xla/service/gpu/backend_configs.proto:{base + l0}-{base + l1}", "values": epilogue},
+        "data_type": {"source": f"xla/ffi/api/c_api.h:{d0}-{d1}", "values": dtypes},
+        "error_code": {"source": f"xla/ffi/api/c_api.h:{e0}-{e1}", "values": codes},
+        "scale_mode_field_number": int(scale_mode.group(1)),
+    }
+    with open(os.path.join(HERE, "interface_enums.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
 def main():
     src = open(os.path.join(ROOT, "xla/tests/convert_test.cc")).read()
     out = {"source": "xla/tests/convert_test.cc", "tables": {}}
@@ -86,6 +120,7 @@ def main():
     }
     with open(os.path.join(HERE, "s8_known_answer.json"), "w") as f:
         json.dump(known, f, indent=1)
+    write_interface_enums()
     print("wrote", sorted(os.listdir(HERE)))
 
 

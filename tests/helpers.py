@@ -28,7 +28,7 @@ def result_to_oracle_repr(d: torch.Tensor, out_dtype: int) -> np.ndarray:
     return d.cpu().numpy()
 
 
-def run_scaled_dot(dev, a, b, sa, sb, *, a_kind="e4m3fn", b_kind="e4m3fn", lc=1, rc=0, epilogue=1, bias_bits=None,
+def run_scaled_dot(dev, a, b, sa, sb, *, a_kind="e4m3fn", b_kind="e4m3fn", lc=1, rc=0, epilogue=o.EPI_DEFAULT, bias_bits=None,
                    c_f32=None, beta=0.0, alpha=1.0, d_scale=None, out_dtype=o.BF16, want_amax=False, kernel=0):
     """a, b: FP8 code points in their STORAGE layout.  Returns (D in oracle representation, amax)."""
     cfg = GemmBackendConfig(alpha_real=alpha, beta=beta, lhs_contracting_dimensions=(lc,),

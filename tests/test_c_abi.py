@@ -24,6 +24,55 @@ def test_every_declared_symbol_is_exported():
         assert hasattr(_native.product, n), f"{n} is declared in the header but not exported"
 
 
+def test_interface_numbers_are_the_reference_s():
+    """Every enum the boundary shares with XLA carries XLA's own numbers: GemmBackendConfig.Epilogue
+    (backend_configs.proto:106-117), XLA_FFI_DataType and XLA_FFI_Error_Code (xla/ffi/api/c_api.h),
+    as extracted from the reference tree into tests/golden/interface_enums.json."""
+    import json
+
+    from oracle import scaled_dot_oracle as o
+
+    golden = json.load(open(os.path.join(ROOT, "tests", "golden", "interface_enums.json")))
+    header = open(os.path.join(ROOT, "include", "b200_scaled_dot.h")).read()
+    in_header = {k: int(v) for k, v in re.findall(r"\bB200SD_EPILOGUE_([A-Z_]+)\s*=\s*(\d+)", header)}
+    assert in_header == golden["epilogue"]["values"]            # all ten, DEFAULT = 0 ... BIAS_SILU = 9
+    assert {e.name: int(e) for e in Epilogue} == golden["epilogue"]["values"]
+    for name in ("DEFAULT", "BIAS", "RELU", "BIAS_RELU", "GELU", "GELU_AUX", "BIAS_GELU", "BIAS_GELU_AUX"):
+        assert getattr(o, "EPI_" + name) == golden["epilogue"]["values"][name]
+    types_in_header = {k: int(v) for k, v in re.findall(r"\bB200SD_(S8|S32|F16|F32|BF16|F8E5M2|F8E4M3FN|F8E8M0FNU)\s*=\s*(\d+)", header)}
+    assert len(types_in_header) >= 7
+    for name, number in types_in_header.items():
+        assert golden["data_type"]["values"][name] == number
+    for name, number in dict(S8=S8, S32=S32, F16=F16, F32=F32, BF16=BF16, F8E5M2=F8E5M2, F8E4M3FN=F8E4M3FN).items():
+        assert golden["data_type"]["values"][name] == number
+    kernels_h = open(os.path.join(ROOT, "xla_b200", "csrc", "kernels.h")).read()
+    for cname, gname in (("kInvalidArgument", "INVALID_ARGUMENT"), ("kUnimplemented", "UNIMPLEMENTED"), ("kInternal", "INTERNAL"),
+                         ("kFailedPrecondition", "FAILED_PRECONDITION"), ("kResourceExhausted", "RESOURCE_EXHAUSTED"),
+                         ("kDeadlineExceeded", "DEADLINE_EXCEEDED")):
+        assert int(re.search(cname + r"\s*=\s*(\d+)", kernels_h).group(1)) == golden["error_code"]["values"][gname]
+
+
+def test_reference_epilogue_numbers_decode_as_the_reference_means_them():
+    """A call frame carrying the reference's own numbers: 0 (DEFAULT) is accepted without a bias operand,
+    6 (BIAS_GELU) wants the bias, 5 / 7 (the AUX forms) and 8 / 9 (SILU) are UNIMPLEMENTED, 10 is unknown."""
+    ops, res = _f8_frame()
+    FfiCall("b200$scaled_dot$f8", ops, res, {"epilogue": ("i32", 0)}).instantiate()
+    FfiCall("b200$scaled_dot$f8", ops, res, {}).instantiate()                      # absent = DEFAULT
+    with pytest.raises(XlaFfiError) as e:
+        FfiCall("b200$scaled_dot$f8", ops, res, {"epilogue": ("i32", 6)}).instantiate()
+    assert e.value.code == 3 and "operands" in str(e.value)
+    FfiCall("b200$scaled_dot$f8", ops + [Buffer(BF16, (256,))], res, {"epilogue": ("i32", 6)}).instantiate()
+    FfiCall("b200$scaled_dot$f8", ops + [Buffer(BF16, (256,))], res, {"epilogue": ("i32", 1)}).instantiate()
+    for number, with_bias in ((5, False), (7, True), (8, False), (9, False)):
+        with pytest.raises(XlaFfiError) as e:
+            FfiCall("b200$scaled_dot$f8", ops + ([Buffer(BF16, (256,))] if with_bias else []), res,
+                    {"epilogue": ("i32", number)}).instantiate()
+        assert e.value.code == 12, (number, str(e.value))
+    with pytest.raises(XlaFfiError) as e:
+        FfiCall("b200$scaled_dot$f8", ops, res, {"epilogue": ("i32", 10)}).instantiate()
+    assert e.value.code == 3
+
+
 def test_struct_layouts_match_the_header():
     """The ctypes mirrors must have the C structs' sizes (checked through struct_size validation)."""
     err = C.create_string_buffer(256)
@@ -143,8 +192,8 @@ def test_attribute_spellings():
     backend_config is parsed into keeps the written width: xla/service/gpu/custom_call_test.cc:554-577)."""
     ops, res = _f8_frame()
     for attrs in (
-        {"epilogue": ("i32", 1), "lhs_contracting_dim": ("i32", 1), "rhs_contracting_dim": ("i64", 0), "beta": ("f32", 0.0)},
-        {"epilogue": 1, "alpha_real": 1.0},
+        {"epilogue": ("i32", 0), "lhs_contracting_dim": ("i32", 1), "rhs_contracting_dim": ("i64", 0), "beta": ("f32", 0.0)},
+        {"epilogue": 0, "alpha_real": 1.0},
         {},
     ):
         FfiCall("b200$scaled_dot$f8", ops, res, attrs).instantiate()

@@ -48,11 +48,11 @@ def test_all_contracting_dim_combinations(cuda_device, lc, rc, kernel):
 
 
 @pytest.mark.parametrize("out_dtype", [o.BF16, o.F16, o.F32])
-@pytest.mark.parametrize("epilogue", [1, 2, 3, 4, 5, 7])
+@pytest.mark.parametrize("epilogue", [o.EPI_DEFAULT, o.EPI_BIAS, o.EPI_RELU, o.EPI_BIAS_RELU, o.EPI_GELU, o.EPI_BIAS_GELU])
 def test_epilogues(cuda_device, epilogue, out_dtype):
     m, k, n = 272, 528, 304   # ragged against the 256 x 256 x 128 tile of the pair kernel
     a, b, sa, sb = o.make_f8_operands(20 + epilogue, m, k, n)
-    bias = o.make_bias_bf16(20, n) if epilogue in (2, 4, 7) else None
+    bias = o.make_bias_bf16(20, n) if epilogue in (o.EPI_BIAS, o.EPI_BIAS_RELU, o.EPI_BIAS_GELU) else None
     got, _ = h.run_scaled_dot(cuda_device, a, b, sa, sb, epilogue=epilogue, bias_bits=bias, out_dtype=out_dtype)
     exp, _ = o.scaled_dot_f8(a, b, sa, sb, epilogue=epilogue,
                              bias=o.bf16_bits_to_f32(bias) if bias is not None else None, out_dtype=out_dtype)
@@ -84,9 +84,9 @@ def test_config1_shape_fp8_linear_gelu_amax_reduced(cuda_device):
     m = k = n = 1024
     a, b, sa, sb = o.make_f8_operands(1, m, k, n)
     bias = o.make_bias_bf16(1, n)
-    got, amax = h.run_scaled_dot(cuda_device, a, b, sa, sb, epilogue=7, bias_bits=bias, d_scale=1.0,
+    got, amax = h.run_scaled_dot(cuda_device, a, b, sa, sb, epilogue=o.EPI_BIAS_GELU, bias_bits=bias, d_scale=1.0,
                                  out_dtype=o.F8E4M3FN, want_amax=True)
-    exp, exp_amax = o.scaled_dot_f8(a, b, sa, sb, epilogue=7, bias=o.bf16_bits_to_f32(bias), d_scale=1.0,
+    exp, exp_amax = o.scaled_dot_f8(a, b, sa, sb, epilogue=o.EPI_BIAS_GELU, bias=o.bf16_bits_to_f32(bias), d_scale=1.0,
                                     out_dtype=o.F8E4M3FN, want_amax=True)
     assert o.fp8_within_n_values(exp, got, 1) == 0          # within one e4m3 ulp
     assert float((exp == got).mean()) > 0.98
@@ -201,10 +201,10 @@ def test_full_size_dense_properties(cuda_device):
     m = k = n = 8192
     a, b, sa, sb = o.make_f8_operands(1, m, k, n)
     bias = o.make_bias_bf16(1, n)
-    got, amax = h.run_scaled_dot(cuda_device, a, b, sa, sb, epilogue=7, bias_bits=bias, d_scale=1.0,
+    got, amax = h.run_scaled_dot(cuda_device, a, b, sa, sb, epilogue=o.EPI_BIAS_GELU, bias_bits=bias, d_scale=1.0,
                                  out_dtype=o.F8E4M3FN, want_amax=True)
     rows = np.random.default_rng(1).choice(m, 48, replace=False)
-    exp, exp_amax_rows = o.scaled_dot_f8(np.ascontiguousarray(a[rows]), b, sa, sb, epilogue=7,
+    exp, exp_amax_rows = o.scaled_dot_f8(np.ascontiguousarray(a[rows]), b, sa, sb, epilogue=o.EPI_BIAS_GELU,
                                          bias=o.bf16_bits_to_f32(bias), d_scale=1.0, out_dtype=o.F8E4M3FN,
                                          want_amax=True)
     assert o.fp8_within_n_values(exp, got[rows], 1) == 0

@@ -43,7 +43,7 @@ def test_emulated_ranks_match_sum_of_bf16_partials(cuda_device, world, m, n, k_p
         args = _native.ScaledDotF8Args(struct_size=C.sizeof(_native.ScaledDotF8Args), a=a[0].data_ptr(), b=b[0].data_ptr(),
                                        a_scale=sa.data_ptr(), b_scale=sb.data_ptr(), d=d[0].data_ptr(), m=m, n=n, k=k_per_rank,
                                        a_dtype=20, b_dtype=20, d_dtype=16, lhs_contracting_dim=1, rhs_contracting_dim=0,
-                                       epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+                                       epilogue=0, alpha=1.0, beta=0.0, kernel=0)
         peers = _native.PeerReduceArgs(struct_size=C.sizeof(_native.PeerReduceArgs), world=world, rank=0, emulate_ranks=world,
                                        epoch=epoch)
         for r in range(world):
@@ -71,7 +71,7 @@ def test_peer_reduce_rejects_what_it_cannot_do(cuda_device):
         args = _native.ScaledDotF8Args(struct_size=C.sizeof(_native.ScaledDotF8Args), a=a.data_ptr(), b=a.data_ptr(),
                                        a_scale=s.data_ptr(), b_scale=s.data_ptr(), d=d.data_ptr(), m=m, n=256, k=256,
                                        a_dtype=20, b_dtype=20, d_dtype=d_dtype, lhs_contracting_dim=1, rhs_contracting_dim=1,
-                                       epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+                                       epilogue=0, alpha=1.0, beta=0.0, kernel=0)
         peers = _native.PeerReduceArgs(struct_size=C.sizeof(_native.PeerReduceArgs), world=world, rank=0, emulate_ranks=world, epoch=epoch)
         for r in range(min(world, 8)):
             peers.d[r], peers.stage[r], peers.flags[r] = d.data_ptr(), stage_ptr, f.data_ptr()

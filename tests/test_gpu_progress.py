@@ -18,7 +18,7 @@ def _args(a, b, sa, sb, d):
     return _native.ScaledDotF8Args(struct_size=C.sizeof(_native.ScaledDotF8Args), a=a.data_ptr(), b=b.data_ptr(),
                                    a_scale=sa.data_ptr(), b_scale=sb.data_ptr(), d=d.data_ptr(), m=m, n=n, k=k,
                                    a_dtype=20, b_dtype=20, d_dtype=16, lhs_contracting_dim=1, rhs_contracting_dim=0,
-                                   epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+                                   epilogue=0, alpha=1.0, beta=0.0, kernel=0)
 
 
 def test_progress_counters_and_stream_wait(cuda_device):
@@ -102,7 +102,7 @@ def test_amax_with_and_without_a_workspace(cuda_device):
                                        amax=amax.data_ptr(), workspace=workspace.data_ptr() if workspace is not None else None,
                                        workspace_bytes=workspace.numel() if workspace is not None else 0, m=512, n=768, k=256,
                                        a_dtype=20, b_dtype=20, d_dtype=20, lhs_contracting_dim=1, rhs_contracting_dim=0,
-                                       epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+                                       epilogue=0, alpha=1.0, beta=0.0, kernel=0)
         assert _native.product.b200sd_scaled_dot_f8(args, stream, err, len(err)) == 0, err.value
         torch.cuda.synchronize()
         return float(amax.item())

@@ -34,7 +34,7 @@ def test_config0_lowering():
     assert plan["rewritten"] and plan["target"] == "b200$scaled_dot$f8"
     assert roles(plan) == ["a", "b", "a_scale", "b_scale"]
     assert (plan["m"], plan["k"], plan["n"]) == (256, 512, 256)
-    assert plan["attrs"]["epilogue"] == 1 and plan["attrs"]["lhs_contracting_dim"] == 1 and plan["attrs"]["rhs_contracting_dim"] == 0
+    assert plan["attrs"]["epilogue"] == o.EPI_DEFAULT and plan["attrs"]["lhs_contracting_dim"] == 1 and plan["attrs"]["rhs_contracting_dim"] == 0
     assert [r["role"] for r in plan["results"]] == ["d", "workspace"]
     assert plan["results"][0]["dtype"] == 16
     # No transposes on Blackwell (gemm_rewriter.cc:1535-1554): operands are the parameters themselves.
@@ -50,7 +50,7 @@ def test_config1_lowering_matches_the_expected_custom_call():
     d_scale = plan["operands"][-1]
     assert d_scale["param"] == 5 and d_scale["reciprocal"]          # the HLO divides by out_scale
     assert plan["operands"][4]["dtype"] == 16                        # the bf16 value feeding the convert
-    assert plan["attrs"]["epilogue"] == 7 and plan["attrs"]["damax_output"] is True
+    assert plan["attrs"]["epilogue"] == o.EPI_BIAS_GELU and plan["attrs"]["damax_output"] is True
     assert [r["role"] for r in plan["results"]] == ["d", "amax", "workspace"]
     assert plan["results"][0]["dtype"] == 20 and plan["results"][0]["root_index"] == 0 and plan["results"][1]["root_index"] == 1
     assert "(f8e4m3fn[8192,8192], f32[], s8[33554432]) custom-call(a, b, a_scale, b_scale, bias, d_scale_inv)" in hlo
@@ -70,7 +70,7 @@ def test_divide_scales_e5m2_bias_relu_and_matrix_bias():
     assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"]
     assert plan["operands"][2]["reciprocal"] and plan["operands"][3]["reciprocal"]
     assert plan["operands"][1]["dtype"] == 19 and plan["attrs"]["rhs_contracting_dim"] == 1
-    assert plan["attrs"]["epilogue"] == 4                            # BIAS_RELU
+    assert plan["attrs"]["epilogue"] == o.EPI_BIAS_RELU                            # BIAS_RELU
     assert plan["results"][0]["dtype"] == 16                         # the final convert became the output type
     _, plan = hlo_runner.rewrite(load("unscaled_matrix_bias_f32"))
     assert roles(plan) == ["a", "b", "c", "a_scale", "b_scale"]      # c at operand index 2 (gemm_rewriter.cc:1829-1978)
@@ -162,7 +162,7 @@ def test_combined_epilogues():
     text = load("matrix_bias_scaled_d_amax")
     _, plan = hlo_runner.rewrite(text)
     assert roles(plan) == ["a", "b", "c", "a_scale", "b_scale", "d_scale"] and plan["operands"][5]["reciprocal"]
-    assert plan["attrs"]["beta"] == 1.0 and plan["attrs"]["damax_output"] is True and plan["attrs"]["epilogue"] == 1
+    assert plan["attrs"]["beta"] == 1.0 and plan["attrs"]["damax_output"] is True and plan["attrs"]["epilogue"] == o.EPI_DEFAULT
     rng = np.random.default_rng(14)
     a = o.fp8_encode(rng.standard_normal((64, 128), dtype=np.float32) * 4, "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((128, 96), dtype=np.float32) * 4, "e4m3fn")
@@ -174,7 +174,7 @@ def test_combined_epilogues():
     text = load("relu_amax_e5m2_out")
     _, plan = hlo_runner.rewrite(text)
     assert roles(plan) == ["a", "b", "a_scale", "b_scale", "d_scale"] and not plan["operands"][4]["reciprocal"]
-    assert plan["attrs"]["epilogue"] == 3 and plan["attrs"]["damax_output"] is True
+    assert plan["attrs"]["epilogue"] == o.EPI_RELU and plan["attrs"]["damax_output"] is True
     assert plan["operands"][1]["dtype"] == 19 and plan["results"][0]["dtype"] == 19
     a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32) * 4, "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((64, 80), dtype=np.float32) * 4, "e5m2")
@@ -269,7 +269,7 @@ def test_rank3_activation_with_vector_bias_on_the_view():
     bias added on the rank-3 view -- one custom call producing the [m, n] matrix, viewed as [4, 16, 32]."""
     text = load("rank3_vector_bias")
     hlo, plan = hlo_runner.rewrite(text)
-    assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"] and plan["attrs"]["epilogue"] == 2
+    assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"] and plan["attrs"]["epilogue"] == o.EPI_BIAS
     assert plan["operands"][0]["dims"] == [64, 64] and plan["operands"][0]["reshaped"]
     assert plan["results"][0]["dims"] == [64, 32] and plan["results"][0]["view_dims"] == [4, 16, 32]
     assert "d = f32[4,16,32] bitcast(d_mat)" in hlo

@@ -145,11 +145,11 @@ def test_numpy_dot_matches_strict_c_interpreter_order(c_oracle, lc, rc):
     out = np.zeros((m, n), np.float32)
     amax_c = c_oracle.oracle_scaled_dot_f8(a_st.ctypes.data, b_st.ctypes.data, float(sa), float(sb), 0, 0, m, n, k,
                                            lc, rc, 1.0, 0.0, None, bias.ctypes.data, 7, out.ctypes.data)
-    exp, amax = o.scaled_dot_f8(a_st, b_st, sa, sb, lhs_contracting=lc, rhs_contracting=rc, bias=bias, epilogue=7,
+    exp, amax = o.scaled_dot_f8(a_st, b_st, sa, sb, lhs_contracting=lc, rhs_contracting=rc, bias=bias, epilogue=o.EPI_BIAS_GELU,
                                 out_dtype=o.F32, want_amax=True)
     np.testing.assert_allclose(exp, out, rtol=1e-5, atol=1e-6)
     assert abs(amax - amax_c) <= 1e-5 * abs(amax_c)
-    strict, _ = o.scaled_dot_f8(a_st, b_st, sa, sb, lhs_contracting=lc, rhs_contracting=rc, bias=bias, epilogue=7,
+    strict, _ = o.scaled_dot_f8(a_st, b_st, sa, sb, lhs_contracting=lc, rhs_contracting=rc, bias=bias, epilogue=o.EPI_BIAS_GELU,
                                 out_dtype=o.F32, strict=True)
     np.testing.assert_allclose(strict, out, rtol=1e-5, atol=1e-6)
 

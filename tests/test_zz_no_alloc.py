@@ -37,7 +37,7 @@ def _args(a, b, sa, sb, d, m, n, k, workspace=None, kernel=0):
     x.a_dtype = x.b_dtype = 20          # F8E4M3FN
     x.d_dtype = 16                      # BF16
     x.lhs_contracting_dim, x.rhs_contracting_dim = 1, 0
-    x.epilogue = 1                      # DEFAULT
+    x.epilogue = 0                      # DEFAULT
     x.alpha, x.beta = 1.0, 0.0
     x.kernel = kernel
     return x

@@ -202,6 +202,8 @@ Status ValidateF8(const B200SD_ScaledDotF8& in, GemmProblem* g, bool check_point
     case B200SD_EPILOGUE_BIAS_GELU: has_bias = true; act = kActGelu; break;
     case B200SD_EPILOGUE_GELU_AUX:
     case B200SD_EPILOGUE_BIAS_GELU_AUX: return Status::Error(kUnimplemented, "epilogues with an auxiliary output are not implemented");
+    case B200SD_EPILOGUE_SILU:
+    case B200SD_EPILOGUE_BIAS_SILU: return Status::Error(kUnimplemented, "SILU epilogues are not supported");
     default: return Status::Error(kInvalidArgument, "unknown epilogue " + std::to_string(a.epilogue));
   }
   if (has_bias) {

@@ -383,7 +383,7 @@ struct Plan {
   std::string target;
   int64_t m = 0, n = 0, k = 0;
   int lhs_contracting = 1, rhs_contracting = 0;
-  int epilogue = 1;                    // GemmBackendConfig.Epilogue number
+  int epilogue = 0;                    // GemmBackendConfig.Epilogue number (backend_configs.proto:106-117; DEFAULT = 0)
   double alpha = 1.0, beta = 0.0;
   bool damax = false, emit_s32 = false;
   int64_t batch = 0;                   // > 0: leading batch dimension of a, b, c and D
@@ -482,7 +482,8 @@ void MatchF8Epilogue(const Graph& g, Instr* dot, Plan* plan) {
     // reference needs the GELU_AUX epilogue, gemm_rewriter.cc:2190-2192).
     if (out != nullptr && g.Users(x).size() == 4) { gelu = true; cur = out; }
   }
-  plan->epilogue = gelu ? (vector_bias ? 7 : 5) : relu ? (vector_bias ? 4 : 3) : (vector_bias ? 2 : 1);
+  // DEFAULT 0, BIAS 1, RELU 2, BIAS_RELU 3, GELU 4, BIAS_GELU 6 (backend_configs.proto:106-117)
+  plan->epilogue = gelu ? (vector_bias ? 6 : 4) : relu ? (vector_bias ? 3 : 2) : (vector_bias ? 1 : 0);
 
   // -- amax = reduce-max(abs(x)) (abs optional after ReLU), F8AddDAmax
   Instr* amax = nullptr;
@@ -685,7 +686,7 @@ Plan Decide(const Graph& g) {
     if (plan.operands[0].shape.IsColumnMajor2D()) as_row_major(&plan.operands[0], &plan.lhs_contracting);
     if (plan.operands[1].shape.IsColumnMajor2D()) as_row_major(&plan.operands[1], &plan.rhs_contracting);
     if (plan.d_shape.IsColumnMajor2D()) {
-      if (plan.epilogue != 1 || plan.beta != 0.0 || plan.damax || plan.operands.size() != 4) {
+      if (plan.epilogue != 0 || plan.beta != 0.0 || plan.damax || plan.operands.size() != 4) {
         plan.reason = "a column-major result is handled for the plain scaled dot only";
         return plan;
       }

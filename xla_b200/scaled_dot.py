@@ -33,14 +33,16 @@ _STAGE_INSTANTIATE, _STAGE_PREPARE, _STAGE_INITIALIZE, _STAGE_EXECUTE = 0, 1, 2,
 class Epilogue(enum.IntEnum):
     """GemmBackendConfig.Epilogue (backend_configs.proto:106-117)."""
 
-    DEFAULT = 1
-    BIAS = 2
-    RELU = 3
-    BIAS_RELU = 4
-    GELU = 5
-    GELU_AUX = 6
-    BIAS_GELU = 7
-    BIAS_GELU_AUX = 8
+    DEFAULT = 0
+    BIAS = 1
+    RELU = 2
+    BIAS_RELU = 3
+    GELU = 4
+    GELU_AUX = 5
+    BIAS_GELU = 6
+    BIAS_GELU_AUX = 7
+    SILU = 8
+    BIAS_SILU = 9
 
     @property
     def adds_vector_bias(self) -> bool:

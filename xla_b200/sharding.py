@@ -20,6 +20,8 @@ from __future__ import annotations
 
 from typing import Callable, Optional, Sequence, Tuple
 
+from .scaled_dot import Epilogue
+
 
 def shard_bounds(extent: int, world: int, rank: int, multiple: int = 16) -> Tuple[int, int]:
     """[begin, end) of `rank`'s slice of a dimension, in units of `multiple` (the rewriter keeps
@@ -156,7 +158,7 @@ class OverlappedRowParallelScaledDot:
             a_scale=a_scale.data_ptr(), b_scale=b_scale.data_ptr(), d=out.data_ptr(), m=m, n=n, k=k,
             a_dtype=_dtype_code(a_shard.dtype), b_dtype=_dtype_code(b_shard.dtype),
             d_dtype=_dtype_code(out.dtype), lhs_contracting_dim=lhs_contracting_dim,
-            rhs_contracting_dim=rhs_contracting_dim, epilogue=1, alpha=1.0, beta=0.0, kernel=0)
+            rhs_contracting_dim=rhs_contracting_dim, epilogue=int(Epilogue.DEFAULT), alpha=1.0, beta=0.0, kernel=0)
         blocks = (m + rows_per_block - 1) // rows_per_block
         self.counters = torch.zeros(blocks, dtype=torch.int32, device=out.device)
         self.totals = [0] * blocks
@@ -255,7 +257,7 @@ class PeerReducedRowParallelScaledDot:
             struct_size=C.sizeof(native.ScaledDotF8Args), a=a_shard.data_ptr(), b=b_shard.data_ptr(),
             a_scale=a_scale.data_ptr(), b_scale=b_scale.data_ptr(), d=self.out.data_ptr(), m=self.m, n=self.n, k=k,
             a_dtype=_dtype_code(a_shard.dtype), b_dtype=_dtype_code(b_shard.dtype), d_dtype=_dtype_code(self.out.dtype),
-            lhs_contracting_dim=lhs_contracting_dim, rhs_contracting_dim=rhs_contracting_dim, epilogue=1, alpha=1.0,
+            lhs_contracting_dim=lhs_contracting_dim, rhs_contracting_dim=rhs_contracting_dim, epilogue=int(Epilogue.DEFAULT), alpha=1.0,
             beta=0.0, kernel=0)
         self.peers.epoch += 1
         stream = torch.cuda.current_stream(self.out.device).cuda_stream
