@@ -220,8 +220,18 @@ int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint3
  * d[i], stage[i] (m*n*2 bytes) and flags[i] (b200sd_peer_reduce_flag_words() u32, zeroed once when
  * allocated, never by the library) are rank i's buffers as mapped into THIS process (peer memory:
  * symmetric-memory or IPC mappings); the same buffers must be passed on every call of a sequence
- * and `epoch` must count the calls 1, 2, 3, ... identically on every rank.  Waits between ranks
- * are bounded (2 s) and report through b200sd_device_status (bit 32).
+ * and `epoch` must count the calls 1, 2, 3, ... identically on every rank.
+ *
+ * Failure and recovery.  Waits between ranks are bounded: `peer_wait_ms` milliseconds (0 = 10 s,
+ * long enough for the launch skew of separate processes and the lazy loading of a first call).  A
+ * wait that gives up sets bit 32 of the status word and the kernel drains; the call has still
+ * returned 0 when it was enqueued, and D then holds incomplete sums.  So a caller MUST read
+ * b200sd_device_status() after a call (or a step of calls) before it trusts D.  The flag counters
+ * only grow and their targets are multiples of `epoch`, so after one such failure every later
+ * call would miss its targets too: re-arm before going on -- every rank synchronises its device,
+ * zeroes its own flags buffer, all ranks meet in a barrier (any host-side one), and the epoch
+ * restarts at 1.  Because the epoch is an argument fixed at enqueue time, this call is not meant to
+ * be recorded into a CUDA graph.
  *
  * emulate_ranks == world makes ONE launch on ONE GPU play every rank (each with its own operands
  * emu_a[i], emu_b[i] and 1/world of the SMs): the way to exercise the protocol without a second
@@ -239,6 +249,8 @@ typedef struct B200SD_PeerReduce {
   const void* emu_b[8];
   void* d_multicast;   /* optional: an NVSwitch multicast address bound to every rank's d (same offset);
                           finished rows then leave this GPU once and the switch replicates them */
+  /* Added later: a caller whose struct_size stops before this field gets the default. */
+  uint32_t peer_wait_ms; /* limit of every wait for another rank, milliseconds; 0 = 10000 */
 } B200SD_PeerReduce;
 
 int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200SD_PeerReduce* peers, void* cuda_stream,

@@ -92,3 +92,39 @@ def test_batched_and_int8_launches_stay_inside_their_buffers(cuda_device):
         assert ws.intact()
         assert torch.equal(d32, (a8.double() @ b8.double()).to(torch.int32))
     assert device_status() == 0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_decode_shape_with_fp8_result_takes_the_dense_kernel(cuda_device, out_dtype):
+    """A decode-shaped call (m <= 128, n, k >= 1024, a workspace) whose result is FP8: the split-K kernel stores
+    bf16 / f16 / f32 only, so automatic selection must send the call to the dense kernel, and naming the
+    split-K kernel explicitly must be refused -- with D, one byte per element, inside guard bands."""
+    from oracle import scaled_dot_oracle as o
+    from xla_b200.scaled_dot import XlaFfiError
+
+    dev = cuda_device
+    m, n, k = 64, 1024, 1024
+    assert _native.product.b200sd_select_kernel(m, n, k) == 2          # a shape the split-K kernel is chosen for
+    b_kind = "e5m2" if out_dtype == torch.float8_e5m2 else "e4m3fn"     # e4m3 x e4m3 -> e5m2 is not in the type table
+    a, b, sa, sb = o.make_f8_operands(77, m, k, n)
+    if b_kind == "e5m2":
+        b = o.fp8_encode(o.fp8_decode(b, "e4m3fn"), "e5m2")
+    ta = torch.from_numpy(a).to(dev).view(torch.float8_e4m3fn)
+    tb = torch.from_numpy(b).to(dev).view(out_dtype if b_kind == "e5m2" else torch.float8_e4m3fn)
+    scales = [torch.tensor(np.float32(v), device=dev) for v in (sa, sb, 3.0)]
+    d = Guarded((m, n), out_dtype, dev)
+    ws = Guarded((16 << 20,), torch.int8, dev)
+    cublas_lt_matmul_f8(ta, tb, scales[0], scales[1], d_scale=scales[2], out_dtype=out_dtype,
+                        config=GemmBackendConfig(), workspace=ws.tensor, out=d.tensor)
+    torch.cuda.synchronize()
+    assert d.intact() and ws.intact()
+    out_code = o.F8E5M2 if out_dtype == torch.float8_e5m2 else o.F8E4M3FN
+    exp, _ = o.scaled_dot_f8(a, b, sa, sb, b_kind=b_kind, d_scale=3.0, out_dtype=out_code)
+    got = d.tensor.view(torch.uint8).cpu().numpy()
+    assert o.fp8_within_n_values(exp, got, 1) == 0            # finite values only: the cast saturates
+    with pytest.raises(XlaFfiError) as e:
+        cublas_lt_matmul_f8(ta, tb, scales[0], scales[1], d_scale=scales[2], out_dtype=out_dtype,
+                            config=GemmBackendConfig(selected_algorithm=2), workspace=ws.tensor, out=d.tensor)
+    assert e.value.code == 3
+    torch.cuda.synchronize()
+    assert d.intact() and device_status() == 0

@@ -82,6 +82,7 @@ class PeerReduceArgs(C.Structure):
         ("d", C.c_void_p * 8), ("stage", C.c_void_p * 8), ("flags", C.c_void_p * 8),
         ("emu_a", C.c_void_p * 8), ("emu_b", C.c_void_p * 8),
         ("d_multicast", C.c_void_p),
+        ("peer_wait_ms", C.c_uint32),
     ]
 
 

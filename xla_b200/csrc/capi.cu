@@ -285,14 +285,17 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
   if (kernel == B200SD_KERNEL_SKINNY) {
     // The split-K kernel covers the plain scaled dot only; fall back to the dense kernel for the rest
     // or when the caller's workspace is too small.
+    // ... with a bf16 / f16 / f32 result: its store path knows no FP8 cast and no d_scale.
     const bool plain = g.c == nullptr && g.bias == nullptr && g.activation == kActNone && g.amax == nullptr &&
+                       g.d_scale == nullptr && (g.d_dtype == kBF16 || g.d_dtype == kF16 || g.d_dtype == kF32) &&
                        !g.a_mn_major && g.b_mn_major && g.m <= 128 && g.a_dtype == kF8E4M3FN &&
                        g.b_dtype == kF8E4M3FN;
     const size_t need = SkinnyWorkspaceBytes(g.m, g.n, g.k);
     if (!plain || need == 0 || g.workspace == nullptr || g.workspace_bytes < need) {
       if (args->kernel == B200SD_KERNEL_SKINNY)
         return CopyStatus(Status::Error(kInvalidArgument, "the split-K kernel needs m <= 128, row-major A[m,k] and B[k,n], e4m3 operands, "
-                                                          "no bias/activation/amax and a workspace of b200sd_workspace_bytes()"),
+                                                          "a bf16/f16/f32 result, no bias/activation/amax/d_scale and a workspace of "
+                                                          "b200sd_workspace_bytes()"),
                           err, err_len);
       kernel = B200SD_KERNEL_DENSE;
     }
@@ -330,7 +333,7 @@ int b200sd_scaled_dot_f8_progress(const B200SD_ScaledDotF8* args, B200SD_Progres
 int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200SD_PeerReduce* peers, void* cuda_stream, char* err,
                                      size_t err_len) {
   if (args == nullptr || peers == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args or peers is null"), err, err_len);
-  if (peers->struct_size < sizeof(B200SD_PeerReduce)) return CopyStatus(Status::Error(kInvalidArgument, "B200SD_PeerReduce.struct_size is smaller than this library's struct"), err, err_len);
+  if (peers->struct_size < offsetof(B200SD_PeerReduce, peer_wait_ms)) return CopyStatus(Status::Error(kInvalidArgument, "B200SD_PeerReduce.struct_size is smaller than this library's struct"), err, err_len);
   GemmProblem g;
   Status st = ValidateF8(*args, &g);
   if (!st.ok()) return CopyStatus(st, err, err_len);
@@ -340,6 +343,8 @@ int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200S
   r.emulate = peers->emulate_ranks;
   r.epoch = peers->epoch;
   r.d_multicast = peers->d_multicast;
+  r.peer_wait_ms = peers->struct_size >= sizeof(B200SD_PeerReduce) ? peers->peer_wait_ms : 0;
+  if (r.peer_wait_ms > 600000u) return CopyStatus(Status::Error(kInvalidArgument, "peer_wait_ms above ten minutes"), err, err_len);
   for (int i = 0; i < kMaxPeers; ++i) {
     r.d[i] = peers->d[i];
     r.stage[i] = peers->stage[i];

@@ -89,6 +89,7 @@ struct ReduceArgs {
   uint32_t flag_target;           // value a (tile, warp) flag reaches when every other rank has pushed: epoch * (world - 1)
   uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
   int32_t done_index;             // index of that counter in the flag array
+  uint64_t peer_wait_ns;          // limit of a wait for another rank
   uint16_t* d[kMaxPeers];
   uint16_t* d_multicast;          // optional: NVSwitch multicast address covering every rank's D
   uint16_t* stage[kMaxPeers];
@@ -873,7 +874,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
             red_release_sys_add_u32(pending_flag, 1u);
             pending_flag = nullptr;
           }
-          if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout);
+          if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
           const int64_t prow = int64_t(own_mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
@@ -1014,7 +1015,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       __syncwarp();
       if (lane == 0) {
         for (int32_t j = 0; j < p.red.world; ++j) red_release_sys_add_u32(p.red.flags[j] + p.red.done_index, 1u);
-        (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout);
+        (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
       }
       __syncwarp();
     }
@@ -1320,6 +1321,7 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   // partial accumulators and at least one full wave (or a long K) to be worth the extra traffic.
   p.dp_tiles = int32_t(tiles);
   p.sk_tiles = 0;
+  const bool capturing = StreamIsCapturing(stream);
   // Opt-in (kernel variant DENSE_STREAMK): measured on B200 it does not pay under the 1 kW power cap,
   // where SMs idling in the last wave let the others clock higher (8192 x 1024 x 8192: 64 us against
   // 62 us without; 4096^3: 73 against 62).
@@ -1335,14 +1337,19 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
       p.sk_epoch = NextDenseEpoch();
       p.sk_flags = static_cast<unsigned long long*>(g.workspace);
       p.sk_partials = reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.workspace) + kSkFlagBytes);
+      if (capturing) {   // replays repeat sk_epoch: the previous replay's flags must be cleared by a node of the graph
+        cudaError_t me = cudaMemsetAsync(p.sk_flags, 0, kSkFlagBytes, stream);
+        if (me != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(stream-K flags): ") + cudaGetErrorString(me));
+      }
     }
   }
   p.amax_sync = nullptr;
   if (g.amax != nullptr) {
     // The last 64 bytes of the caller's workspace hold the two words that let the kernel clear amax
-    // itself (the stream-K scratch, when used, sits at the front); without a workspace a memset node does it.
+    // itself (the stream-K scratch, when used, sits at the front); without a workspace, or while the stream is
+    // being captured (every replay would carry the same epoch), a memset node does it.
     const size_t front = p.sk_tiles > 0 ? kSkFlagBytes + size_t(grid / 2) * kSkPartialBytes : 0;
-    if (g.workspace != nullptr && g.workspace_bytes >= front + 128) {
+    if (!capturing && g.workspace != nullptr && g.workspace_bytes >= front + 128) {
       uintptr_t end = (reinterpret_cast<uintptr_t>(g.workspace) + g.workspace_bytes) & ~uintptr_t(63);
       p.amax_sync = reinterpret_cast<unsigned long long*>(end - 64);
       p.amax_epoch = NextDenseEpoch();
@@ -1432,6 +1439,7 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   q.flag_target = r.epoch * uint32_t(r.world - 1);
   q.done_index = int32_t(PeerReduceFlagWords(g.m, g.n, r.world)) - 32;
   q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps);
+  q.peer_wait_ns = uint64_t(r.peer_wait_ms ? r.peer_wait_ms : kDefaultPeerWaitMs) * 1000000ull;
   for (int i = 0; i < r.world; ++i) {
     q.d[i] = static_cast<uint16_t*>(r.d[i]);
     q.stage[i] = static_cast<uint16_t*>(r.stage[i]);

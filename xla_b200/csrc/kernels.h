@@ -94,10 +94,12 @@ struct GemmProblem {
 // buffer over peer memory, computes its own block last, adds what the others pushed and writes
 // the finished rows into every rank's D.  All pointers are indexed by rank and peer-mapped.
 constexpr int kMaxPeers = 8;
+constexpr uint32_t kDefaultPeerWaitMs = 10000;   // covers launch skew between processes and a first call's lazy loading
 struct PeerReduceProblem {
   int32_t world = 1, rank = 0;
   int32_t emulate = 0;               // one launch on one GPU plays all ranks (single-GPU testing)
   uint32_t epoch = 1;                // 1, 2, 3, ...; the same on every rank for the same call
+  uint32_t peer_wait_ms = 0;         // limit of a wait for another rank; 0 = kDefaultPeerWaitMs
   void* d[kMaxPeers] = {};
   void* d_multicast = nullptr;       // optional NVSwitch multicast mapping of all the d[i]
   void* stage[kMaxPeers] = {};       // m*n bf16 each
@@ -140,6 +142,19 @@ Status ReadDeviceStatus(uint32_t* bits);
 Status LaunchWaitProbe(uint64_t limit_ns, cudaStream_t stream);
 
 int DeviceSmCount();
+
+// True while `stream` is being captured into a CUDA graph (an XLA command buffer records a custom
+// call this way).  A recorded launch replays with the SAME kernel arguments, so the per-launch epoch
+// values that normally stand in for clearing flags and amax cannot tell one replay from the next;
+// launches made during capture therefore put a memset node in front of the kernel instead.
+inline bool StreamIsCapturing(cudaStream_t stream) {
+  cudaStreamCaptureStatus s = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &s) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return s != cudaStreamCaptureStatusNone;
+}
 
 // Tensor map of a row-major [rows, cols] byte matrix, `cols` innermost; box = box_cols x box_rows bytes,
 // 128-byte swizzle, out-of-range elements read as zero.  `l2_promotion`: 0 none, 1 = 64 B, 2 = 128 B, 3 = 256 B.

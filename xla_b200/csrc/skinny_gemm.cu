@@ -499,6 +499,11 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   if (!st.ok()) return st;
   if (g.int8 || g.a_mn_major || !g.b_mn_major || g.m > 128 || g.m % 16 != 0)
     return Status::Error(kInvalidArgument, "split-K kernel: unsupported operand arrangement");
+  // store_out() writes bf16, f16 or f32 and applies no output scale: anything else would be
+  // stored with the wrong element size.
+  if (!(g.d_dtype == kBF16 || g.d_dtype == kF16 || g.d_dtype == kF32) || g.d_scale != nullptr || g.c != nullptr ||
+      g.bias != nullptr || g.activation != kActNone || g.amax != nullptr)
+    return Status::Error(kInvalidArgument, "split-K kernel: computes the plain scaled dot with a bf16, f16 or f32 result only");
   const size_t need = SkinnyWorkspaceBytes(g.m, g.n, g.k);
   if (g.workspace == nullptr || g.workspace_bytes < need)
     return Status::Error(kInvalidArgument, "split-K kernel: workspace too small");
@@ -549,6 +554,12 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   if (grid > kMaxCtas) grid = kMaxCtas;
   if (grid > p.total_units * p.group) grid = p.total_units * p.group;
   grid -= grid % p.group;
+  if (StreamIsCapturing(stream)) {
+    // Every replay of the recorded launch carries this same epoch: the flags the previous replay
+    // raised must read "not raised" again, so a memset node goes in front of the kernel.
+    cudaError_t me = cudaMemsetAsync(p.flags, 0, kFlagBytes, stream);
+    if (me != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(split-K flags): ") + cudaGetErrorString(me));
+  }
   const size_t smem_bytes = 1024 + size_t(stages) * stage_bytes + sizeof(SkinnyAux);
   skinny_gemm_kernel<<<int(grid), kThreads, smem_bytes, stream>>>(tmap_w, tmap_a, p);
   cudaError_t e = cudaGetLastError();

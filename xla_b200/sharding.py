@@ -208,9 +208,14 @@ class PeerReducedRowParallelScaledDot:
     `_symmetric_memory`, used purely as the allocator / address exchange) so that every rank holds
     a mapping of every other rank's buffers.  All ranks must call the object the same number of
     times: the call count is the protocol's epoch.
+
+    A rank that is late by more than `peer_wait_ms` makes its peers' waits give up: the kernels
+    drain, the device status word gets bit 32 and the result is incomplete.  `check()` reads the
+    status word; when it reports a failure on any rank, `rearm()` (a collective: every rank must
+    call it) puts the protocol back to its initial state.
     """
 
-    def __init__(self, m: int, n: int, group=None, device=None, multicast: bool = True):
+    def __init__(self, m: int, n: int, group=None, device=None, multicast: bool = True, peer_wait_ms: int = 0):
         import ctypes as C
 
         import torch
@@ -235,7 +240,8 @@ class PeerReducedRowParallelScaledDot:
         self._handles = [symm.rendezvous(t, group) for t in (self.out, self.stage, self.flags)]
         self._handles[2].barrier()                 # every rank's flags are zero before anyone counts on them
         self.peers = _native.PeerReduceArgs(struct_size=C.sizeof(_native.PeerReduceArgs), world=self.world, rank=self.rank,
-                                            emulate_ranks=0, epoch=0)
+                                            emulate_ranks=0, epoch=0, peer_wait_ms=int(peer_wait_ms))
+        self.group = group
         for r in range(self.world):
             self.peers.d[r] = self._handles[0].buffer_ptrs[r]
             self.peers.stage[r] = self._handles[1].buffer_ptrs[r]
@@ -266,3 +272,21 @@ class PeerReducedRowParallelScaledDot:
             self.peers.epoch -= 1
             raise XlaFfiError(rc, self._err.value.decode(errors="replace"))
         return self.out
+
+    def check(self) -> int:
+        """Synchronises this rank's device and returns (and clears) its status word: 0 when every wait
+        of the calls so far was satisfied, bit 32 set when a wait for a peer gave up."""
+        from .scaled_dot import device_status
+
+        return device_status()
+
+    def rearm(self) -> None:
+        """Collective.  Back to the state of a fresh object after a failed call: each rank waits for its
+        own kernels, zeroes its flag counters, the ranks meet, and the epoch restarts."""
+        torch = self._torch
+        torch.cuda.synchronize(self.out.device)
+        self._handles[2].barrier()          # nobody still adds to a peer's counters
+        self.flags.zero_()
+        torch.cuda.synchronize(self.out.device)
+        self._handles[2].barrier()          # every rank's counters are zero before anyone counts on them
+        self.peers.epoch = 0
