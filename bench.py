@@ -8,25 +8,36 @@ the XLA FFI boundary of libb200_scaled_dot.so.  Default workload `c1` is BASELIN
 M=N=K=8192 e4m3fn operands (values from N(0,1) scaled to amax 448), per-tensor f32 scales, bf16
 bias ~N(0,0.02), GELU, scaled e4m3fn output (out_scale 1.0) and an f32 amax.  On N>1 GPUs B, bias
 and D are N-split column-parallel (A replicated) with no collective: total work is fixed, so
-scaling is "strong".  Other workloads (plain, c2 decode, c3 int8, c4 row-parallel + all-reduce)
-exist for the profiles and the design notes; `--m/--n/--k` shrink a workload for ncu captures.
+scaling is "strong".
 
 Timing: W (>=3) untimed warm-up steps, then exactly K steps between two CUDA events on the
 launching stream, bracketed by barrier + synchronize; max over ranks.  Two operand/result sets
 are used alternately and together exceed the 126 MB L2, so no step finds its inputs in cache.
-The JSON line also carries: `e2e` (same call with HOST buffers: pinned host -> device copies of
-every input and device -> host copies of every result inside the timed region, the upload, the
-call and the download of consecutive steps overlapped on three streams), `roofline` for the
-dominant kernel, `cpu_baseline` (the CPU oracle timed on a bounded sample), SM clocks sampled
-through NVML during the timed region, and the number of kernels launched.
 
-`--impl cublaslt` times the library the reference's GPU path calls on the same shapes (one GPU),
-for the side-by-side note under profiles/.  `--impl reference` times the reference arithmetic on the host cores instead (XLA's own CPU
-backend cannot be built offline, so this is the NumPy/BLAS port in oracle/), on a bounded sample of
-the same workload, and prints the same line with "impl": "reference".
+The one JSON line carries, besides the contract's keys:
+  e2e          the same call with HOST buffers: pinned host -> device copies of every input and
+               device -> host copies of every result inside the timed region (upload, call and
+               download of consecutive steps overlapped on three streams)
+  roofline     for the dominant kernel of the headline workload
+  sustained    the headline workload launched back to back for at least two seconds with the
+               clock sampler running: TFLOP/s, median SM MHz, fraction of the tensor rate at
+               that clock and of twice the sustained bf16 figure
+  secondary    the other BASELINE configurations, a few hundred launches each: config 2 (decode,
+               GB/s at M = 16 / 64 / 128, and N-split at N > 1), config 3 (int8, TOP/s and the
+               number of s32 mismatches against the oracle on a block of rows), and at N > 1
+               config 4 (K-split dot + sum across ranks, ms, max over ranks)
+  cpu_baseline the CPU oracle timed on a bounded sample, all host threads
+  clocks, gpu_launches
+
+`--impl cublaslt` times the library the reference's GPU path calls on the same shapes (one GPU).
+`--impl reference` times the reference arithmetic on the host cores (XLA's own CPU backend cannot
+be built offline, so this is the NumPy/BLAS port in oracle/), on a bounded sample of the same
+workload, and prints the same line with "impl": "reference".  `--workload`, `--m/--n/--k` and
+`--kernel` select other workloads / sizes / kernel variants for profiler captures.
 """
 import argparse
 import json
+import math
 import os
 import sys
 import threading
@@ -36,6 +47,20 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "FP8 scaled-dot TFLOP/s at 8192^3 per B200 and at 2/4/8 GPUs; % of FP8 dense peak"
+WORKLOAD_NAME = {
+    "c1": "config 1: dense FP8 linear 8192^3, bias + GELU + scaled e4m3 output + amax",
+    "plain": "scaled dot, bf16 output, no epilogue",
+    "c2": "config 2: decode-shape FP8 dot, bf16 output",
+    "c3": "config 3: int8 dot + per-row x per-column dequant to bf16",
+    "c4": "config 4: row-parallel FP8 dot + sum of the bf16 partials across ranks",
+}
+DEFAULT_DIMS = {"c1": (8192, 8192, 8192), "plain": (8192, 8192, 8192), "c2": (64, 28672, 8192),
+                "c3": (4096, 4096, 4096), "c4": (8192, 8192, 28672)}
+FLOP_PER_CLK_PER_SM = 16384.0      # dense 8-bit tensor rate of one SM: 8192 multiply-adds per clock
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, each from one ncu capture of that kernel at
+# that size on one GPU (bytes).
+NCU_DRAM_BYTES_PER_LAUNCH = {("c1", 8192, 8192, 8192): 396.0e6, ("c2", 64, 28672, 8192): 240.06e6,
+                             ("c3", 4096, 4096, 4096): 33.8e6}
 
 
 def parse_args():
@@ -44,7 +69,7 @@ def parse_args():
     p.add_argument("--steps", type=int, default=100)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "cublaslt"])
-    p.add_argument("--workload", default="c1", choices=["c1", "plain", "c2", "c3", "c4"])
+    p.add_argument("--workload", default="c1", choices=sorted(WORKLOAD_NAME))
     p.add_argument("--overlap", type=int, default=-1, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory, 1 = NCCL all-reduce of finished row blocks "
                    "on a second stream, 0 = dot then one NCCL all-reduce; default: 2 up to 4 GPUs, 0 beyond (measured faster)")
     p.add_argument("--multicast", type=int, default=0, help="c4 fused: write finished rows through the NVSwitch multicast mapping")
@@ -57,13 +82,22 @@ def parse_args():
     p.add_argument("--kernel", type=int, default=0, help="0 auto, 1 dense, 2 split-K, 3 dense single-CTA, 4 dense CTA pair, 5 CTA pair with a stream-K tail")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler captures)")
+    p.add_argument("--no-sustained", action="store_true")
+    p.add_argument("--sustained-seconds", type=float, default=2.2)
+    p.add_argument("--counters", action="store_true", help="print the kernels' own wait counters of the last launch "
+                   "(needs the tuning build: B200SD_LIBRARY=xla_b200/lib/libb200_scaled_dot_tuning.so B200SD_TIMING=1)")
     return p.parse_args()
 
 
 def workload_dims(args):
-    dflt = {"c1": (8192, 8192, 8192), "plain": (8192, 8192, 8192), "c2": (64, 28672, 8192),
-            "c3": (4096, 4096, 4096), "c4": (8192, 8192, 28672)}[args.workload]
+    dflt = DEFAULT_DIMS[args.workload]
     return (args.m or dflt[0], args.n or dflt[1], args.k or dflt[2])
+
+
+def config_block(kind, m, n, k, parallelism):
+    return {"workload": WORKLOAD_NAME[kind], "m": m, "n": n, "k": k, "parallelism": parallelism,
+            "l2": "two operand/result sets used alternately; together larger than the 126 MB L2"}
 
 
 def measured_peaks():
@@ -76,12 +110,42 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def algorithmic_bytes(kind, m, n, k):
+    if kind == "c2":
+        return k * n + m * k + 2 * m * n
+    if kind == "c3":
+        return m * k + k * n + 2 * m * n + 4 * (m + n)
+    if kind == "c1":
+        return m * k + k * n + m * n + 2 * n    # e4m3 in, e4m3 out, bf16 bias
+    return m * k + k * n + 2 * m * n            # bf16 out
+
+
 # --------------------------------------------------------------------------------------------- CPU arm
-def cpu_sample_step(wl, m_rows, n_cols, seed=0):
-    """One pass of the oracle over an [m_rows, K] x [K, n_cols] sample of the workload.  Returns
-    (seconds, algorithmic units) where units are flops (c1/plain/c3/c4) or bytes (c2)."""
-    import numpy as np
+def host_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_block(kind, a, b, extra):
+    """The oracle on one block of rows: dequantise + dot + epilogue, exactly the workload's arithmetic."""
     from oracle import scaled_dot_oracle as o
+
+    if kind == "c3":
+        rs, cs = extra
+        return o.dequant_s32_to_bf16(o.dot_s8(a, b), rs, cs)
+    if kind == "c1":
+        return o.scaled_dot_f8(a, b, 0.01, 0.01, bias=extra, epilogue=o.EPI_BIAS_GELU, d_scale=1.0, out_dtype=o.F8E4M3FN,
+                               want_amax=True)
+    return o.scaled_dot_f8(a, b, 0.01, 0.01, out_dtype=o.BF16)
+
+
+def cpu_sample_step(wl, m_rows, n_cols, pool, threads, seed=0):
+    """One pass of the oracle over an [m_rows, K] x [K, n_cols] sample of the workload, the work dealt out to
+    `threads` workers by columns (NumPy releases the interpreter lock inside its loops and in BLAS, whose own
+    threading is switched off meanwhile).  Returns (seconds, algorithmic units): flops, or bytes for c2."""
+    import numpy as np
 
     kind, (m, n, k) = wl
     rng = np.random.default_rng(seed)
@@ -90,18 +154,21 @@ def cpu_sample_step(wl, m_rows, n_cols, seed=0):
         b = rng.integers(-127, 128, size=(k, n_cols), dtype=np.int8)
         rs = rng.uniform(0.001, 0.02, size=m_rows).astype(np.float32)
         cs = rng.uniform(0.001, 0.02, size=n_cols).astype(np.float32)
-        t0 = time.perf_counter()
-        o.dequant_s32_to_bf16(o.dot_s8(a, b), rs, cs)
-        return time.perf_counter() - t0, 2.0 * m_rows * n_cols * k
-    a = rng.integers(0, 0x7F, size=(m_rows, k), dtype=np.uint8)       # finite e4m3 code points
-    b = rng.integers(0, 0x7F, size=(k, n_cols), dtype=np.uint8)
-    bias = rng.standard_normal(n_cols).astype(np.float32) * np.float32(0.02)
-    t0 = time.perf_counter()
-    if kind == "c1":
-        o.scaled_dot_f8(a, b, 0.01, 0.01, bias=bias, epilogue=o.EPI_BIAS_GELU, d_scale=1.0, out_dtype=o.F8E4M3FN,
-                        want_amax=True)
     else:
-        o.scaled_dot_f8(a, b, 0.01, 0.01, out_dtype=o.BF16)
+        a = rng.integers(0, 0x7F, size=(m_rows, k), dtype=np.uint8)       # finite e4m3 code points
+        b = rng.integers(0, 0x7F, size=(k, n_cols), dtype=np.uint8)
+        bias = rng.standard_normal(n_cols).astype(np.float32) * np.float32(0.02)
+    # Column blocks: every worker dequantises its own columns of B once and the (few) rows of A.
+    parts = max(1, min(threads, n_cols // 64))
+    bounds = [n_cols * i // parts for i in range(parts + 1)]
+    t0 = time.perf_counter()
+    futures = []
+    for i in range(parts):
+        cols = slice(bounds[i], bounds[i + 1])
+        extra = (rs, cs[cols]) if kind == "c3" else (bias[cols] if kind == "c1" else None)
+        futures.append(pool.submit(cpu_block, kind, a, np.ascontiguousarray(b[:, cols]), extra))
+    for f in futures:
+        f.result()
     dt = time.perf_counter() - t0
     units = (k * n_cols + m_rows * k + 2 * m_rows * n_cols) if kind == "c2" else 2.0 * m_rows * n_cols * k
     return dt, units
@@ -109,32 +176,43 @@ def cpu_sample_step(wl, m_rows, n_cols, seed=0):
 
 def cpu_arm(wl, budget_s, steps, warmup):
     """Times `steps` oracle passes on a sample sized so that everything fits in `budget_s`."""
-    import torch
+    from concurrent.futures import ThreadPoolExecutor
 
     kind, (m, n, k) = wl
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    m_rows, n_cols = min(m, 64), min(n, 1024)
-    dt, _ = cpu_sample_step(wl, m_rows, n_cols)           # calibration (also warms the BLAS threads)
-    per_step_budget = budget_s / max(1, steps + warmup)
-    while dt * 3.0 < per_step_budget and (m_rows < m or n_cols < n):
-        if n_cols < n:
-            n_cols = min(n, n_cols * 2)
-        else:
-            m_rows = min(m, m_rows * 2)
-        dt, _ = cpu_sample_step(wl, m_rows, n_cols)
-    for _ in range(min(warmup, 2)):
-        cpu_sample_step(wl, m_rows, n_cols)
-    total_t, total_u = 0.0, 0.0
-    for i in range(steps):
-        t, u = cpu_sample_step(wl, m_rows, n_cols, seed=i)
-        total_t += t
-        total_u += u
+    threads = host_threads()
+    try:
+        from threadpoolctl import threadpool_limits
+        blas_guard = threadpool_limits(limits=1)          # one BLAS thread per worker: the workers are the parallelism
+    except Exception:
+        blas_guard = None
+    pool = ThreadPoolExecutor(max_workers=threads)
+    try:
+        m_rows, n_cols = min(m, max(64, 16 * threads)), min(n, 1024)
+        dt, _ = cpu_sample_step(wl, m_rows, n_cols, pool, threads)           # calibration (also starts the workers)
+        per_step_budget = budget_s / max(1, steps + warmup)
+        while dt * 3.0 < per_step_budget and (m_rows < m or n_cols < n):
+            if n_cols < n:
+                n_cols = min(n, n_cols * 2)
+            else:
+                m_rows = min(m, m_rows * 2)
+            dt, _ = cpu_sample_step(wl, m_rows, n_cols, pool, threads)
+        for _ in range(warmup):
+            cpu_sample_step(wl, m_rows, n_cols, pool, threads)
+        total_t, total_u = 0.0, 0.0
+        for i in range(steps):
+            t, u = cpu_sample_step(wl, m_rows, n_cols, pool, threads, seed=i)
+            total_t += t
+            total_u += u
+    finally:
+        pool.shutdown()
+        if blas_guard is not None:
+            blas_guard.restore_original_limits()
     scale = 1e-9 if kind == "c2" else 1e-12
-    return {"value": total_u / total_t * scale, "unit": "GB/s" if kind == "c2" else "TFLOP/s", "cores": cores,
+    return {"value": total_u / total_t * scale, "unit": "GB/s" if kind == "c2" else "TFLOP/s", "cores": threads,
             "kind": "port", "ms_per_step": 1e3 * total_t / steps,
             "sample": f"{steps} passes of the NumPy/BLAS oracle over A[{m_rows},{k}] x B[{k},{n_cols}] "
-                      f"(a {m_rows}x{n_cols} block of the {m}x{n} output), dequantise + dot + epilogue"}
+                      f"(a {m_rows}x{n_cols} block of the {m}x{n} output), dequantise + dot + epilogue, columns dealt out to "
+                      f"{threads} worker threads"}
 
 
 # --------------------------------------------------------------------------------------------- clocks
@@ -199,134 +277,171 @@ class ClockSampler(threading.Thread):
 
 
 # --------------------------------------------------------------------------------------------- GPU arm
-def gpu_arm(args):
-    import torch
-    import torch.distributed as dist
+class Bench:
+    """Per-process state of the GPU arm: device, rank, and the timing loop shared by every workload."""
 
-    import xla_b200
-    from xla_b200 import sharding
-    from xla_b200.scaled_dot import Epilogue, GemmBackendConfig, Int8DotCall, ScaledDotCall
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    kind = args.workload
-    m, n, k = workload_dims(args)
-    steps, warmup = args.steps, max(3, args.warmup)
-    stream = torch.cuda.current_stream().cuda_stream
+        import xla_b200
 
-    # ---- this rank's shard of the problem ---------------------------------------------------
-    if kind == "c4":
-        ks = sharding.row_parallel_slices(k, world, rank)
-        lm, ln, lk = m, n, ks.stop - ks.start
-    else:
-        cols = sharding.column_parallel_slices(n, world, rank)
-        lm, ln, lk = m, cols.stop - cols.start, k
+        self.torch, self.dist, self.lib, self.args = torch, dist, xla_b200, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.stream = torch.cuda.current_stream().cuda_stream
 
-    def f8_operand(shape, seed):
-        g = torch.Generator(device=dev).manual_seed(seed)
-        v = torch.randn(shape, device=dev, generator=g)
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, x):
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def time_steps(self, step, steps, warmup, sample_clocks=False):
+        """`warmup` untimed steps, then exactly `steps` between two events; ms per step, max over ranks."""
+        torch = self.torch
+        for i in range(warmup):
+            step(i)
+        self.barrier()
+        launches0 = self.lib.launch_count()
+        sampler = ClockSampler(self.local_rank) if sample_clocks else None
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.finish() if sampler else None
+        self.barrier()
+        launches = self.lib.launch_count() - launches0
+        ms = self.max_over_ranks(e0.elapsed_time(e1) / steps)
+        status = self.lib.device_status()
+        assert status == 0, f"device status word {status:#x}"
+        return ms, clocks, launches
+
+    # ---- problems ---------------------------------------------------------------------------
+    def shard(self, kind, m, n, k):
+        from xla_b200 import sharding
+
+        if kind == "c4":
+            ks = sharding.row_parallel_slices(k, self.world, self.rank)
+            return m, n, ks.stop - ks.start
+        cols = sharding.column_parallel_slices(n, self.world, self.rank)
+        return m, cols.stop - cols.start, k
+
+    def f8_operand(self, shape, seed):
+        torch = self.torch
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        v = torch.randn(shape, device=self.dev, generator=g)
         s = (v.abs().max() / 448.0).reshape(()).float()
         return (v / s).to(torch.float8_e4m3fn), s
 
-    sets, host_sets = [], []
-    for i in range(2):                                           # two rotating operand/result sets
-        if kind == "c3":
-            g = torch.Generator(device=dev).manual_seed(3000 + i)
-            a = torch.randint(-127, 128, (lm, lk), dtype=torch.int8, device=dev, generator=g)
-            b = torch.randint(-127, 128, (lk, ln), dtype=torch.int8, device=dev, generator=g)
-            rs = torch.rand(lm, device=dev, generator=g) * 0.019 + 0.001
-            cs = torch.rand(ln, device=dev, generator=g) * 0.019 + 0.001
-            d = torch.empty((lm, ln), dtype=torch.bfloat16, device=dev)
-            ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)   # the s8[] scratch XLA appends to the call
-            ops, res = [a, b, rs, cs], [d, ws]
-            call = Int8DotCall(ops, res, selected_algorithm=args.kernel)
-        else:
-            a, sa = f8_operand((lm, lk), 1000 * i + 1)           # A replicated (same seed on every rank) unless K-split
-            b, sb = f8_operand((lk, ln), 1000 * i + 2 + 17 * rank)
-            ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)
-            if kind == "c1":
-                bias = (torch.randn(ln, device=dev) * 0.02).bfloat16()
-                d = torch.empty((lm, ln), dtype=torch.float8_e4m3fn, device=dev)
-                amax = torch.zeros((), dtype=torch.float32, device=dev)
-                ops, res = [a, b, sa, sb, bias, torch.ones((), device=dev)], [d, amax, ws]
-                cfg = GemmBackendConfig(epilogue=Epilogue.BIAS_GELU, damax_output=True, selected_algorithm=args.kernel)
-            else:
+    def make_sets(self, kind, lm, ln, lk, kernel=0, emit_s32=False):
+        """Two rotating operand/result sets of one workload, each bound to its own call site."""
+        torch = self.torch
+        from xla_b200.scaled_dot import Epilogue, GemmBackendConfig, Int8DotCall, ScaledDotCall
+
+        dev, sets = self.dev, []
+        for i in range(2):
+            ws = torch.empty(32 << 20, dtype=torch.int8, device=dev)       # the s8[] scratch XLA appends to the call
+            if kind == "c3":
+                g = torch.Generator(device=dev).manual_seed(3000 + i)
+                a = torch.randint(-127, 128, (lm, lk), dtype=torch.int8, device=dev, generator=g)
+                b = torch.randint(-127, 128, (lk, ln), dtype=torch.int8, device=dev, generator=g)
+                rs = torch.rand(lm, device=dev, generator=g) * 0.019 + 0.001
+                cs = torch.rand(ln, device=dev, generator=g) * 0.019 + 0.001
                 d = torch.empty((lm, ln), dtype=torch.bfloat16, device=dev)
-                ops, res = [a, b, sa, sb], [d, ws]
-                cfg = GemmBackendConfig(selected_algorithm=args.kernel)
-            call = ScaledDotCall(ops, res, cfg)
-        call.run(stream, local_rank)                             # instantiate + initialize + first execute
-        sets.append((call, ops, res))
-    torch.cuda.synchronize()
-    assert xla_b200.device_status() == 0
+                ops, res = [a, b, rs, cs], [d, ws]
+                if emit_s32:
+                    res = [d, torch.empty((lm, ln), dtype=torch.int32, device=dev), ws]
+                call = Int8DotCall(ops, res, selected_algorithm=kernel, emit_s32=emit_s32)
+            else:
+                a, sa = self.f8_operand((lm, lk), 1000 * i + 1)           # A replicated (same seed on every rank) unless K-split
+                b, sb = self.f8_operand((lk, ln), 1000 * i + 2 + 17 * self.rank)
+                if kind == "c1":
+                    bias = (torch.randn(ln, device=dev) * 0.02).bfloat16()
+                    d = torch.empty((lm, ln), dtype=torch.float8_e4m3fn, device=dev)
+                    amax = torch.zeros((), dtype=torch.float32, device=dev)
+                    ops, res = [a, b, sa, sb, bias, torch.ones((), device=dev)], [d, amax, ws]
+                    cfg = GemmBackendConfig(epilogue=Epilogue.BIAS_GELU, damax_output=True, selected_algorithm=kernel)
+                else:
+                    d = torch.empty((lm, ln), dtype=torch.bfloat16, device=dev)
+                    ops, res = [a, b, sa, sb], [d, ws]
+                    cfg = GemmBackendConfig(selected_algorithm=kernel)
+                call = ScaledDotCall(ops, res, cfg)
+            call.run(self.stream, self.local_rank)                        # instantiate + initialize + first execute
+            sets.append((call, ops, res))
+        torch.cuda.synchronize()
+        assert self.lib.device_status() == 0
+        return sets
 
-    overlapped = None
-    if args.overlap < 0:
-        args.overlap = 2 if world <= 4 else 0
-    if kind == "c4" and world > 1 and args.overlap == 2:
-        fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=dev, multicast=bool(args.multicast)) for _ in sets]
-        overlapped = [(lambda f=f, ops=ops: f(ops[0], ops[1], ops[2], ops[3])) for f, (_, ops, _) in zip(fused, sets)]
-        for i, f in enumerate(fused):                            # results now land in the symmetric buffers
-            sets[i] = (sets[i][0], sets[i][1], [f.out] + list(sets[i][2][1:]))
-    elif kind == "c4" and world > 1 and args.overlap == 1:
-        group = None
-        if args.nccl_ctas > 0:
-            opts = dist.ProcessGroupNCCL.Options()
-            opts.config.max_ctas = args.nccl_ctas
-            opts.config.min_ctas = min(args.nccl_ctas, 4)
-            group = dist.new_group(backend="nccl", pg_options=opts)
-        overlapped = [sharding.OverlappedRowParallelScaledDot(ops[0], ops[1], ops[2], ops[3], res[0], rows_per_block=args.ar_rows,
-                                                              gemm_ctas=args.gemm_ctas, group=group)
-                      for _, ops, res in sets]
+    def c4_runner(self, sets, lm, ln, overlap, multicast=False):
+        """How the K-split dot and its sum run on N > 1 ranks.  Returns (per-set callables or None, description)."""
+        from xla_b200 import sharding
 
-    def step(i):
-        call, ops, res = sets[i & 1]
-        if overlapped is not None:
-            overlapped[i & 1]()                                  # dot + row-block all-reduces on a second stream
-            return
-        call.execute(stream, local_rank)
-        if kind == "c4" and world > 1:
-            dist.all_reduce(res[0], op=dist.ReduceOp.SUM)        # bf16 partials, one NCCL all-reduce
+        args, dist = self.args, self.dist
+        if overlap < 0:
+            overlap = 2 if self.world <= 4 else 0
+        if overlap == 2:
+            fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=self.dev, multicast=bool(multicast)) for _ in sets]
+            runners = [(lambda f=f, ops=ops: f(ops[0], ops[1], ops[2], ops[3])) for f, (_, ops, _) in zip(fused, sets)]
+            for i, f in enumerate(fused):                            # results now land in the symmetric buffers
+                sets[i] = (sets[i][0], sets[i][1], [f.out] + list(sets[i][2][1:]))
+            return runners, "formed inside the dot's kernel over peer memory (no collective launch" + \
+                (", finished rows via NVSwitch multicast)" if multicast else ")")
+        if overlap == 1:
+            group = None
+            if args.nccl_ctas > 0:
+                opts = dist.ProcessGroupNCCL.Options()
+                opts.config.max_ctas = args.nccl_ctas
+                opts.config.min_ctas = min(args.nccl_ctas, 4)
+                group = dist.new_group(backend="nccl", pg_options=opts)
+            runners = [sharding.OverlappedRowParallelScaledDot(ops[0], ops[1], ops[2], ops[3], res[0], rows_per_block=args.ar_rows,
+                                                               gemm_ctas=args.gemm_ctas, group=group)
+                       for _, ops, res in sets]
+            return runners, (f"of {args.ar_rows}-row blocks overlapped with the dot ({args.gemm_ctas} SMs dot, "
+                             f"{args.nccl_ctas} CTAs NCCL)")
+        return None, "by one NCCL all-reduce behind the dot"
 
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    launches0 = xla_b200.launch_count()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.finish()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    launches = xla_b200.launch_count() - launches0
-    ms = e0.elapsed_time(e1) / steps
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    assert xla_b200.device_status() == 0
+    def make_step(self, kind, sets, runners, stream=None):
+        dist, world = self.dist, self.world
 
-    # ---- end to end with host buffers ----------------------------------------------------------
-    e2e = None
-    if not args.no_e2e:
-        # Host buffers in pinned memory; every step copies ALL inputs to the device, runs the call through the
-        # FFI boundary and copies ALL results back.  The three legs run on three streams and the two device
-        # operand/result sets alternate, so step i+1's upload and step i-1's download overlap step i's kernel
-        # (PCIe is full duplex); every byte still moves inside the timed region.
+        def step(i):
+            call, ops, res = sets[i & 1]
+            if runners is not None:
+                runners[i & 1]()
+                return
+            call.execute(stream if stream is not None else self.stream, self.local_rank)
+            if kind == "c4" and world > 1:
+                dist.all_reduce(res[0], op=dist.ReduceOp.SUM)        # bf16 partials, one NCCL all-reduce
+        return step
+
+    # ---- end to end with host buffers ---------------------------------------------------------
+    def e2e(self, kind, sets, runners, steps):
+        """Host buffers in pinned memory; every step copies ALL inputs to the device, runs the call through the
+        FFI boundary and copies ALL results back.  The three legs run on three streams and the two device
+        operand/result sets alternate, so step i+1's upload and step i-1's download overlap step i's kernel
+        (PCIe is full duplex); every byte still moves inside the timed region."""
+        torch, dev, dist, world = self.torch, self.dev, self.dist, self.world
         host_in = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in sets[0][1]]
         for hbuf, o in zip(host_in, sets[0][1]):
             hbuf.copy_(o)
@@ -352,10 +467,10 @@ def gpu_arm(args):
                 s_cmp.wait_event(in_ready[j])
                 if i >= 2:
                     s_cmp.wait_event(downloaded[j])              # set j's results were last read by step i-2's download
-                if overlapped is not None:
-                    overlapped[j]()
+                if runners is not None:
+                    runners[j]()
                 else:
-                    call.execute(s_cmp.cuda_stream, local_rank)
+                    call.execute(s_cmp.cuda_stream, self.local_rank)
                     if kind == "c4" and world > 1:
                         dist.all_reduce(res[0], op=dist.ReduceOp.SUM)
                 computed[j].record(s_cmp)
@@ -374,39 +489,155 @@ def gpu_arm(args):
                 torch.cuda.current_stream(dev).wait_stream(st)
 
         e2e_run(2)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         e2e_run(e2e_steps)
         e1.record()
         torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-        hd = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(hd, op=dist.ReduceOp.SUM)
-        e2e = {"ms_per_step": e2e_ms, "h2d_bytes_per_step": int(hd[0].item()), "d2h_bytes_per_step": int(hd[1].item()),
-               "steps": e2e_steps}
+        ms = self.max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+        return {"ms_per_step": ms, "h2d_bytes_per_step": int(self.sum_over_ranks(h2d)),
+                "d2h_bytes_per_step": int(self.sum_over_ranks(d2h)), "steps": e2e_steps}
 
-    launches_t = torch.tensor([launches], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(launches_t, op=dist.ReduceOp.SUM)
+    # ---- the other BASELINE configurations --------------------------------------------------
+    def secondary(self, peaks):
+        """Configs 2, 3 and (N > 1) 4 in the line the driver parses.  Each is timed like the headline: >= 3
+        warm-up launches, two rotating operand sets larger than L2 together (config 3's are 2 x 67 MB),
+        events on the launching stream, max over ranks."""
+        import numpy as np
+
+        torch, world = self.torch, self.world
+        out = {}
+        steps, warmup = 200, 5
+        # config 2: decode shapes, W N-split over the ranks
+        k, n = 8192, 28672
+        c2 = {}
+        for m in (16, 64, 128):
+            lm, ln, lk = self.shard("c2", m, n, k)
+            sets = self.make_sets("c2", lm, ln, lk)
+            ms, _, launches = self.time_steps(self.make_step("c2", sets, None), steps, warmup)
+            by = algorithmic_bytes("c2", m, n, k)
+            sel = self.lib.select_kernel(lm, ln, lk)
+            c2[f"m{m}"] = {"ms": ms, "value": by / ms / 1e6, "unit": "GB/s", "frac": by / world / ms / 1e6 / peaks["hbm_gbs"],
+                           "frac_of_nominal_8000": by / world / ms / 1e6 / 8000.0,
+                           "kernel": "skinny_gemm_kernel" if sel == 2 else "dense_gemm_kernel<fp8, single>",
+                           "launches": int(self.sum_over_ranks(launches))}
+            del sets
+            torch.cuda.empty_cache()
+        out["c2"] = {"workload": WORKLOAD_NAME["c2"], "n": n, "k": k, "n_gpus": world,
+                     "parallelism": "single GPU" if world == 1 else f"N-split x{world}, no collective",
+                     "peak": peaks["hbm_gbs"], "peak_source": f"MEASURED_PEAKS hbm_gbs ({peaks['source']})", **c2}
+        # config 3: int8 + dequant (one GPU's worth of work per rank; reported for rank 0's device)
+        m = n3 = k3 = 4096
+        sets = self.make_sets("c3", m, n3, k3)
+        ms, _, launches = self.time_steps(self.make_step("c3", sets, None), steps, warmup)
+        check = self.make_sets("c3", m, n3, k3, emit_s32=True)
+        call, ops, res = check[0]
+        call.execute(self.stream, self.local_rank)
+        torch.cuda.synchronize()
+        from oracle import scaled_dot_oracle as o        # the checker: s32 block of rows against the CPU restatement
+        rows = np.arange(0, m, 32)
+        exp = o.dot_s8(ops[0][rows].cpu().numpy(), ops[1].cpu().numpy())
+        got = res[1][rows].cpu().numpy()
+        exp_bf16 = o.dequant_s32_to_bf16(exp, ops[2][rows].cpu().numpy(), ops[3].cpu().numpy())
+        got_bf16 = res[0][rows].view(torch.int16).cpu().numpy().view(np.uint16)
+        ops3 = 2.0 * m * n3 * k3
+        out["c3"] = {"workload": WORKLOAD_NAME["c3"], "m": m, "n": n3, "k": k3, "ms": ms, "value": ops3 / ms / 1e9, "unit": "TOP/s",
+                     "frac": ops3 / ms / 1e9 / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": ops3 / ms / 1e9 / 4500.0,
+                     "s32_mismatches": int((exp != got).sum()), "bf16_mismatches": int((exp_bf16 != got_bf16).sum()),
+                     "checked": f"{len(rows)} rows x {n3} columns of the s32 accumulator and of the bf16 result against the CPU oracle",
+                     "kernel": "dense_gemm_kernel<int8, pair>", "launches": int(launches), "n_gpus": 1}
+        del sets, check
+        torch.cuda.empty_cache()
+        # config 4: K-split + sum across ranks
+        if world > 1:
+            m4, n4, k4 = DEFAULT_DIMS["c4"]
+            lm, ln, lk = self.shard("c4", m4, n4, k4)
+            sets = self.make_sets("c4", lm, ln, lk)
+            runners, how = self.c4_runner(sets, lm, ln, self.args.overlap, self.args.multicast)
+            ms, _, launches = self.time_steps(self.make_step("c4", sets, runners), 50, 5)
+            flops = 2.0 * m4 * n4 * k4
+            fp8_peak = 2.0 * peaks["bf16_tflops"]
+            t_tensor = flops / world / (fp8_peak * 1e9)
+            link_bytes = 2.0 * (world - 1) / world * m4 * n4 * 2
+            t_link = link_bytes / 770e9 * 1e3
+            out["c4"] = {"workload": WORKLOAD_NAME["c4"], "m": m4, "n": n4, "k": k4, "n_gpus": world, "ms": ms,
+                         "value": flops / ms / 1e9, "unit": "TFLOP/s", "sum": how,
+                         "roofline": {"bound": "tensor" if t_tensor >= t_link else "nvlink", "tensor_ms": t_tensor, "nvlink_ms": t_link,
+                                      "nvlink_bytes_per_rank": link_bytes, "target_ms": max(t_tensor, t_link),
+                                      "frac": max(t_tensor, t_link) / ms,
+                                      "peak_source": "2 x bf16_tflops burst; 770 GB/s measured peer copy per direction"},
+                         "launches": int(self.sum_over_ranks(launches))}
+            del sets, runners
+            torch.cuda.empty_cache()
+        return out
+
+    def counters(self, grid_ctas):
+        """The kernels' own wait counters of the last dense launch (tuning build only)."""
+        import ctypes as C
+
+        from xla_b200 import _native
+
+        fn = getattr(_native.product, "b200sd_debug_read_timing", None)
+        if fn is None:
+            return {"unavailable": "the loaded library is the product build; load the tuning build through B200SD_LIBRARY"}
+        n = 8 * grid_ctas
+        buf = (C.c_ulonglong * n)()
+        fn(buf, n)
+        rows = [buf[8 * i:8 * i + 8] for i in range(grid_ctas)]
+        leaders = [r for r in rows if r[2] > 0]
+        if not leaders:
+            return {"unavailable": "no counters were written: set B200SD_TIMING=1"}
+        mean = lambda j, src: sum(r[j] for r in src) / len(src)     # noqa: E731
+        total = mean(2, leaders)
+        return {"ctas_with_issuer": len(leaders), "issuer_cycles": total, "issuer_wait_operands_frac": mean(0, leaders) / total,
+                "issuer_wait_accumulator_frac": mean(1, leaders) / total, "producer_wait_stage_frac": mean(3, rows) / total,
+                "epilogue_wait_frac": mean(5, rows) / total, "epilogue_busy_frac": mean(6, rows) / total,
+                "kernel_ns": mean(4, leaders), "sm_mhz_in_kernel": 1e3 * total / mean(4, leaders)}
+
+
+def gpu_arm(args):
+    B = Bench(args)
+    torch, world, rank = B.torch, B.world, B.rank
+    kind = args.workload
+    m, n, k = workload_dims(args)
+    steps, warmup = args.steps, max(3, args.warmup)
+    lm, ln, lk = B.shard(kind, m, n, k)
+    sets = B.make_sets(kind, lm, ln, lk, kernel=args.kernel)
+    runners, c4_how = (B.c4_runner(sets, lm, ln, args.overlap, args.multicast) if (kind == "c4" and world > 1) else (None, ""))
+    step = B.make_step(kind, sets, runners)
+    ms, clocks, launches = B.time_steps(step, steps, warmup, sample_clocks=True)
+    launches_total = int(B.sum_over_ranks(launches))
+    counters = B.counters(2 * 74 if lm > 128 else 148) if args.counters else None
+
+    e2e = None if args.no_e2e else B.e2e(kind, sets, runners, steps)
+
+    flops = 2.0 * m * n * k
+    sustained = None
+    if not args.no_sustained and kind in ("c1", "plain", "c3"):
+        n_steps = max(steps, int(math.ceil(args.sustained_seconds * 1e3 / ms)))
+        s_ms, s_clocks, _ = B.time_steps(step, n_steps, 3, sample_clocks=True)
+        rate = flops / world / s_ms / 1e9
+        sustained = {"steps": n_steps, "seconds": n_steps * s_ms / 1e3, "ms_per_step": s_ms, "value": flops / s_ms / 1e9,
+                     "unit": "TFLOP/s" if kind != "c3" else "TOP/s", "clocks": s_clocks}
+        if s_clocks and s_clocks.get("sm_mhz"):
+            sustained["frac_of_tensor_rate_at_median_clock"] = rate * 1e12 / (148 * FLOP_PER_CLK_PER_SM * s_clocks["sm_mhz"] * 1e6)
+    peaks = measured_peaks()
+    if sustained is not None:
+        sustained["frac_of_2x_bf16_sustained"] = flops / world / sustained["ms_per_step"] / 1e9 / (2.0 * peaks["bf16_tflops_sustained"])
+    del sets, runners, step
+    torch.cuda.empty_cache()
+    secondary = None if (args.no_secondary or kind != "c1" or (args.m or args.n or args.k)) else B.secondary(peaks)
     if rank != 0:
         if world > 1:
-            dist.destroy_process_group()
+            B.dist.destroy_process_group()
         return
 
     # ---- report ------------------------------------------------------------------------------
-    peaks = measured_peaks()
-    flops = 2.0 * m * n * k
     if kind == "c2":
-        algo_bytes = k * n + m * k + 2 * m * n
+        algo_bytes = algorithmic_bytes("c2", m, n, k)
         value, unit = algo_bytes / ms / 1e6, "GB/s"
-        per_launch = algo_bytes / world
-        roof = {"bound": "hbm", "achieved": per_launch / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        roof = {"bound": "hbm", "achieved": algo_bytes / world / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "peak_source": f"MEASURED_PEAKS hbm_gbs ({peaks['source']})"}
     else:
         value, unit = flops / ms / 1e9, "TFLOP/s"
@@ -414,7 +645,10 @@ def gpu_arm(args):
         roof = {"bound": "tensor", "achieved": flops / world / ms / 1e9, "peak": fp8_peak, "unit": "TFLOP/s",
                 "peak_source": f"2 x MEASURED_PEAKS bf16_tflops burst ({peaks['source']}); 8-bit tensor rate is twice bf16",
                 "frac_of_nominal_4500": flops / world / ms / 1e9 / 4500.0,
-                "frac_of_sustained": flops / world / ms / 1e9 / (2.0 * peaks["bf16_tflops_sustained"])}
+                "frac_of_sustained": flops / world / ms / 1e9 / (2.0 * peaks["bf16_tflops_sustained"]),
+                "algorithmic_bytes": algorithmic_bytes(kind, m, n, k) / world}
+        if clocks and clocks.get("sm_mhz"):
+            roof["frac_of_tensor_rate_at_median_clock"] = flops / world / ms * 1e3 / (148 * FLOP_PER_CLK_PER_SM * clocks["sm_mhz"] * 1e6)
     roof["frac"] = roof["achieved"] / roof["peak"]
     if kind == "c4" and world > 1:
         # A dot followed by its sum across the ranks: the target time is the slower of the dot at the measured
@@ -426,62 +660,59 @@ def gpu_arm(args):
         roof["fused"] = {"bound": "tensor" if t_tensor_ms >= t_link_ms else "nvlink", "tensor_ms": t_tensor_ms, "nvlink_ms": t_link_ms,
                          "nvlink_bytes_per_rank": link_bytes, "target_ms": max(t_tensor_ms, t_link_ms),
                          "frac": max(t_tensor_ms, t_link_ms) / ms}
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-    # (single GPU, default sizes only; bytes).
-    measured_traffic = {("c1", 8192, 8192, 8192): 396.0e6, ("c2", 64, 28672, 8192): 240.2e6,
-                        ("c3", 4096, 4096, 4096): 33.8e6}
-    roof["traffic"] = measured_traffic.get((kind, m, n, k)) if world == 1 else None
-    c2_kernel = args.kernel or xla_b200.select_kernel(lm, ln, lk)
+    roof["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get((kind, m, n, k)) if world == 1 else None
+    c2_kernel = args.kernel or B.lib.select_kernel(lm, ln, lk)
     roof["kernel"] = {"c2": "skinny_gemm_kernel" if c2_kernel == 2 else "dense_gemm_kernel<fp8, single>",
-                      "c3": "dense_gemm_kernel<int8>"}.get(kind, "dense_gemm_kernel<fp8>")
-    if kind == "c2" and c2_kernel != 2:   # the dense single-CTA kernel's capture (profiles/dense_gemm_single_fp8_c2_m64.md)
-        roof["traffic"] = 240.06e6 if (world == 1 and (m, n, k) == (64, 28672, 8192)) else None
+                      "c3": "dense_gemm_kernel<int8, pair>"}.get(kind, "dense_gemm_kernel<fp8, pair>")
+    parallelism = ("single GPU" if world == 1 else
+                   (f"K-split x{world}, sum {c4_how}" if kind == "c4" else f"N-split x{world}, no collective"))
     line = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "s8" if kind == "c3" else "f8e4m3fn", "data": "synthetic",
-        "config": {"workload": {"c1": "config 1: dense FP8 linear 8192^3, bias + GELU + scaled e4m3 output + amax",
-                                "plain": "scaled dot, bf16 output, no epilogue",
-                                "c2": "config 2: decode-shape FP8 dot, bf16 output",
-                                "c3": "config 3: int8 dot + per-row x per-column dequant to bf16",
-                                "c4": "config 4: row-parallel FP8 dot + one NCCL all-reduce of bf16 partials"}[kind],
-                   "m": m, "n": n, "k": k,
-                   "parallelism": ("single GPU" if world == 1 else
-                                   (f"K-split x{world} + all-reduce" + ({2: " formed inside the dot's kernel over peer memory (no collective launch" +
-                                        (", finished rows via NVSwitch multicast)" if args.multicast else ")"),
-                                     1: f" of {args.ar_rows}-row blocks overlapped with the dot ({args.gemm_ctas} SMs dot, "
-                                        f"{args.nccl_ctas} CTAs NCCL)"}.get(args.overlap, "") if overlapped is not None else "")
-                                    if kind == "c4" else f"N-split x{world}, no collective")),
-                   "l2": "two operand/result sets used alternately; together larger than the 126 MB L2"},
-        "clocks": clocks, "gpu_launches": int(launches_t.item()), "roofline": roof,
+        "config": config_block(kind, m, n, k, parallelism),
+        "clocks": clocks, "gpu_launches": launches_total, "roofline": roof,
     }
     if e2e is not None:
-        units = (k * n + m * k + 2 * m * n) / 1e6 if kind == "c2" else flops / 1e9
+        units = algorithmic_bytes("c2", m, n, k) / 1e6 if kind == "c2" else flops / 1e9
         line["e2e"] = {"value": units / e2e["ms_per_step"], "unit": unit, "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                        "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "ms_per_step": e2e["ms_per_step"],
                        "steps": e2e["steps"]}
+    if sustained is not None:
+        line["sustained"] = sustained
+    if secondary is not None:
+        line["secondary"] = secondary
+    if counters is not None:
+        line["counters"] = counters
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_arm((kind, (m, n, k)), budget_s=20.0, steps=3, warmup=1)
     print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        B.dist.destroy_process_group()
 
 
 def reference_arm(args):
+    """The reference arithmetic on the host cores, same workload, same line.  Under torchrun only rank 0 works;
+    the thread count is set here (torchrun exports OMP_NUM_THREADS=1, which would otherwise serialise BLAS)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     kind = args.workload
     m, n, k = workload_dims(args)
-    steps, warmup = args.steps, max(1, min(args.warmup, 3))
+    steps, warmup = args.steps, max(3, args.warmup)
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     res = cpu_arm((kind, (m, n, k)), budget_s=120.0, steps=steps, warmup=warmup)
+    parallelism = ("single GPU" if world == 1 else
+                   (f"K-split x{world}" if kind == "c4" else f"N-split x{world}, no collective"))
+    cfg = config_block(kind, m, n, k, parallelism)
+    cfg["note"] = ("reference arm: XLA's CPU backend is not buildable offline; the oracle port of the same HLO runs on the "
+                   "host cores of rank 0, each step over the bounded sample named in cpu_baseline.sample")
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": res["unit"],
-        "n_gpus": int(os.environ.get("WORLD_SIZE", str(args.gpus))), "steps": steps, "warmup": warmup,
+        "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "s8" if kind == "c3" else "f8e4m3fn", "data": "synthetic",
-        "config": {"workload": kind, "m": m, "n": n, "k": k,
-                   "note": "XLA's CPU backend is not buildable offline; this is the oracle port of the same HLO on host cores"},
+        "config": cfg,
         "cpu_baseline": {"value": res["value"], "unit": res["unit"], "cores": res["cores"], "kind": "port",
                          "sample": res["sample"]},
         "e2e": {"value": res["value"], "unit": res["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -520,29 +751,40 @@ def cublaslt_arm(args):
         else:
             torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, bias=bias, out_dtype=torch.bfloat16, use_fast_accum=True)
 
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
+    def timed(n_steps):
+        for i in range(warmup):
+            step(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_steps):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n_steps
+
+    ms = timed(steps)
     if kind == "c2":
-        value, unit = (k * n + m * k + 2 * m * n) / ms / 1e6, "GB/s"
+        value, unit, per_ms = algorithmic_bytes("c2", m, n, k) / ms / 1e6, "GB/s", algorithmic_bytes("c2", m, n, k) / 1e6
     else:
-        value, unit = 2.0 * m * n * k / ms / 1e9, "TFLOP/s"
-    print(json.dumps({"impl": "cublaslt", "metric": METRIC, "value": value, "unit": unit, "n_gpus": 1, "steps": steps,
-                      "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
-                      "config": {"workload": kind, "m": m, "n": n, "k": k,
-                                 "note": "torch._scaled_mm / torch._int_mm (cuBLASLt); no GELU, amax or dequantisation fused"}}),
-          flush=True)
+        value, unit, per_ms = 2.0 * m * n * k / ms / 1e9, "TFLOP/s", 2.0 * m * n * k / 1e9
+    line = {"impl": "cublaslt", "metric": METRIC, "value": value, "unit": unit, "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "config": {"workload": kind, "m": m, "n": n, "k": k,
+                       "note": "torch._scaled_mm / torch._int_mm (cuBLASLt); no GELU, amax or dequantisation fused"}}
+    if not args.no_sustained and kind != "c2":
+        n_steps = max(steps, int(math.ceil(args.sustained_seconds * 1e3 / ms)))
+        s_ms = timed(n_steps)
+        line["sustained"] = {"steps": n_steps, "ms_per_step": s_ms, "value": per_ms / s_ms, "unit": unit}
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
     a = parse_args()
+    if a.impl == "reference":
+        # All host threads, whatever the launcher exported: set before NumPy / BLAS are loaded.
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = str(host_threads())
     if a.impl == "cublaslt":
         cublaslt_arm(a)
     elif a.impl == "reference":

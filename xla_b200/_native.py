@@ -7,7 +7,8 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_DIR = os.path.join(_HERE, "lib")
-PRODUCT_LIB = os.path.join(LIB_DIR, "libb200_scaled_dot.so")
+# B200SD_LIBRARY names another build of the same library (the tuning build with its wait counters).
+PRODUCT_LIB = os.environ.get("B200SD_LIBRARY") or os.path.join(LIB_DIR, "libb200_scaled_dot.so")
 MOCK_LIB = os.path.join(LIB_DIR, "libb200_mock_ffi.so")
 
 

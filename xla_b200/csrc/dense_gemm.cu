@@ -151,8 +151,10 @@ constexpr size_t kSkPartialBytes = size_t(2 * kBM) * kBN * 4;          // one 25
 // Tuning aid: per CTA, [0] cycles the MMA issuer waited for operands, [1] cycles it waited for a
 // free accumulator, [2] its total cycles, [3] cycles the producer waited for a free stage,
 // [4] the CTA's wall time in ns, [5]/[6] cycles epilogue warp 2 waited for / worked on accumulators.
-// Filled only when B200SD_TIMING=1 was set at load time.
+// Tuning builds only; filled when B200SD_TIMING=1 was set at load time.
+#if B200SD_TUNING
 __device__ unsigned long long g_dense_timing[8 * 512];
+#endif
 
 __device__ __forceinline__ float load_as_f32(const void* base, int32_t dtype, int64_t idx) {
   switch (dtype) {
@@ -614,9 +616,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         const int32_t row0 = mt * S::kTileRows + int32_t(rank) * kBM;
         const int32_t col0 = nt * kBN + (kPair ? int32_t(rank) * (kBN / 2) : 0);
         for (int32_t kb = item.kb0; kb < item.kb1; ++kb) {
-          const long long tw = p.timing ? clock64() : 0;
+          const long long tw = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
-          if (p.timing) prod_wait += clock64() - tw;
+          if (kTiming && p.timing) prod_wait += clock64() - tw;
           if (!ok) break;
           uint8_t* sa = smem_a + stage * kAStageBytes;
           uint8_t* sb = smem_b + stage * S::kBStageBytes;
@@ -655,7 +657,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           }
         }
       }
-      if (p.timing) p.timing[blockIdx.x * 8 + 3] = prod_wait;
+      if (kTiming && p.timing) p.timing[blockIdx.x * 8 + 3] = prod_wait;
       if (!ok && !kPair) {
         // Abort path: let loads that were already issued land before the CTA's memory is released.
         for (int s = 0; s < kStages; ++s) {
@@ -667,8 +669,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (rank == 0 && elect_one()) {
-      const long long t_begin = p.timing ? clock64() : 0;
-      const unsigned long long ns_begin = p.timing ? global_timer_ns() : 0;
+      const long long t_begin = (kTiming && p.timing) ? clock64() : 0;
+      const unsigned long long ns_begin = (kTiming && p.timing) ? global_timer_ns() : 0;
       long long wait_full = 0, wait_acc = 0;
       const uint32_t sbo = 1024, lbo = 16384;
       const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), lbo, sbo);
@@ -684,23 +686,23 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       bool ok = true;
       for (int32_t it = 0; it < work.n_items && ok; ++it) {
         const WorkItem item = get_item(work, p, it);
-        const long long tw0 = p.timing ? clock64() : 0;
+        const long long tw0 = (kTiming && p.timing) ? clock64() : 0;
         ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
-        if (p.timing) wait_acc += clock64() - tw0;
+        if (kTiming && p.timing) wait_acc += clock64() - tw0;
         if (!ok) break;
         if (item.mode == 2) {       // the epilogue warps have put the earlier shares' sum into this accumulator
-          const long long tp0 = p.timing ? clock64() : 0;
+          const long long tp0 = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->preload_bar, 0, abort_flag, p.status, kStatusMmaTimeout);
-          if (p.timing) p.timing[blockIdx.x * 8 + 7] = clock64() - tp0;
+          if (kTiming && p.timing) p.timing[blockIdx.x * 8 + 7] = clock64() - tp0;
           if (!ok) break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         const bool preloaded = item.mode == 2;
         for (int32_t kb = item.kb0; kb < item.kb1; ++kb) {
-          const long long tw1 = p.timing ? clock64() : 0;
+          const long long tw1 = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
-          if (p.timing) wait_full += clock64() - tw1;
+          if (kTiming && p.timing) wait_full += clock64() - tw1;
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
@@ -741,7 +743,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           acc_phase ^= 1;
         }
       }
-      if (p.timing) {
+      if (kTiming && p.timing) {
         p.timing[blockIdx.x * 8 + 0] = wait_full;
         p.timing[blockIdx.x * 8 + 1] = wait_acc;
         p.timing[blockIdx.x * 8 + 2] = clock64() - t_begin;
@@ -888,10 +890,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
       // Lane 0 does the bounded wait; the warp then agrees on the outcome so that the
       // warp-collective TMEM loads below never run with a partial warp.
-      const long long te0 = p.timing ? clock64() : 0;
+      const long long te0 = (kTiming && p.timing) ? clock64() : 0;
       if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      const long long te1 = p.timing ? clock64() : 0;
+      const long long te1 = (kTiming && p.timing) ? clock64() : 0;
       ep_wait += te1 - te0;
       if (!ok) break;
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
@@ -992,7 +994,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       // Hand the accumulator back to the MMA issuer (in the leader CTA): one arrival per warp.
       tc_fence_before_sync();
       __syncwarp();
-      if (p.timing) ep_busy += clock64() - te1;
+      if (kTiming && p.timing) ep_busy += clock64() - te1;
       if (lane == 0) {
         if (kPair && rank != 0) mbar_arrive_cluster(map_to_cta(&aux->acc_empty_bar[acc], 0));
         else mbar_arrive(&aux->acc_empty_bar[acc]);
@@ -1019,7 +1021,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
       __syncwarp();
     }
-    if (p.timing && warp == 2 && lane == 0) {
+    if (kTiming && p.timing && warp == 2 && lane == 0) {
       p.timing[blockIdx.x * 8 + 5] = ep_wait;
       p.timing[blockIdx.x * 8 + 6] = ep_busy;
     }
@@ -1190,11 +1192,13 @@ uint32_t FormatCode(int32_t dtype) {
   return dtype == kF8E5M2 ? 1u : (dtype == kS8 ? 1u : 0u);
 }
 
+#if B200SD_TUNING
 // Copies the tuning counters of the last dense launch on the current device (8 per CTA).
 extern "C" int b200sd_debug_read_timing(unsigned long long* out, int count) {
   cudaDeviceSynchronize();
   return int(cudaMemcpyFromSymbol(out, g_dense_timing, sizeof(unsigned long long) * size_t(count)));
 }
+#endif
 
 // A 64-bit value no earlier launch of this process has used and that stale workspace contents will
 // not equal by accident: a per-process random tag in the high half, a launch counter in the low half.
@@ -1265,8 +1269,8 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   p.num_m_tiles = int32_t((g.m + tile_rows - 1) / tile_rows);
   p.num_n_tiles = int32_t((g.n + kBN - 1) / kBN);
   p.num_k_blocks = int32_t((g.k + kBK - 1) / kBK);
-  static const int env_raster = [] { const char* e = std::getenv("B200SD_RASTER"); return e ? std::atoi(e) : 0; }();
-  p.raster_group = env_raster > 0 ? env_raster : 16;   // B200SD_RASTER: tuning override (16 measured best at 8192^3)
+  static const int env_raster = TuningEnvInt("B200SD_RASTER", 0);
+  p.raster_group = env_raster > 0 ? env_raster : 16;   // 16 measured best at 8192^3
   p.progress = nullptr;
   p.progress_tiles = 1;
   if (g.progress != nullptr) {
@@ -1298,15 +1302,14 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   const int64_t d_elt = (g.d_dtype == kF8E4M3FN || g.d_dtype == kF8E5M2) ? 1 : (g.d_dtype == kF32 || g.d_dtype == kS32) ? 4 : 2;
   p.vec_store_ok = aligned(p.d, d_elt) && aligned(p.d_s32, 4);
   p.status = StatusWordPtr();
-  static const bool timing_on = [] {
-    const char* e = std::getenv("B200SD_TIMING");
-    return e != nullptr && e[0] == '1';
-  }();
   p.timing = nullptr;
+#if B200SD_TUNING
+  static const bool timing_on = TuningEnvInt("B200SD_TIMING", 0) == 1;
   if (timing_on) {
     cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_dense_timing);
     cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
   }
+#endif
 
   const int64_t tiles = batch * p.num_m_tiles * p.num_n_tiles;
   int grid;
@@ -1432,8 +1435,8 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   q.m_tiles_per_block = p.num_m_tiles / r.world;
   // Rounds in which the rows are dealt out: two when each rank's row tiles divide (measured at 4 GPUs on
   // 8192 x 28672 x 8192: 0.515 / 0.487 / 0.520 / 0.580 ms for 1 / 2 / 4 / 8 rounds -- more rounds spread the
-  // broadcasts but add a rendezvous each).  B200SD_REDUCE_STAGES overrides, for tuning.
-  static const int env_stages = [] { const char* e = std::getenv("B200SD_REDUCE_STAGES"); return e ? std::atoi(e) : 0; }();
+  // broadcasts but add a rendezvous each).
+  static const int env_stages = TuningEnvInt("B200SD_REDUCE_STAGES", 0);
   q.stages = q.m_tiles_per_block % 2 == 0 ? 2 : 1;
   if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
   q.flag_target = r.epoch * uint32_t(r.world - 1);
@@ -1445,14 +1448,13 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
     q.stage[i] = static_cast<uint16_t*>(r.stage[i]);
     q.flags[i] = r.flags[i];
   }
-  static const bool timing_on = [] {
-    const char* e = std::getenv("B200SD_TIMING");
-    return e != nullptr && e[0] == '1';
-  }();
+#if B200SD_TUNING
+  static const bool timing_on = TuningEnvInt("B200SD_TIMING", 0) == 1;
   if (timing_on) {
     cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_dense_timing);
     cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
   }
+#endif
   q.emu_maps = nullptr;
   q.d_multicast = r.emulate ? nullptr : static_cast<uint16_t*>(r.d_multicast);
 

@@ -4,11 +4,33 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
 #include <string>
 
 struct CUtensorMap_st;   // CUtensorMap of <cuda.h>
 
+// B200SD_TUNING=1 (make TUNING=1 -> libb200_scaled_dot_tuning.so) compiles in what the product
+// library leaves out: the per-CTA wait counters the kernels' roles keep (read back with
+// b200sd_debug_read_timing / b200sd_debug_read_skinny_timing, switched on by B200SD_TIMING=1) and the
+// environment overrides of tile order and pipeline depths.  The product build carries neither.
+#ifndef B200SD_TUNING
+#define B200SD_TUNING 0
+#endif
+
 namespace b200sd {
+
+constexpr bool kTiming = B200SD_TUNING != 0;
+
+// An integer tuning knob: read from the environment in a tuning build, `dflt` in the product build.
+inline int TuningEnvInt(const char* name, int dflt) {
+#if B200SD_TUNING
+  const char* e = std::getenv(name);
+  return e != nullptr ? std::atoi(e) : dflt;
+#else
+  (void)name;
+  return dflt;
+#endif
+}
 
 // xla::PrimitiveType numbers (mirrored by XLA_FFI_DataType, xla/ffi/api/c_api.h:233-266).
 enum PrimitiveType : int32_t {

@@ -77,8 +77,11 @@ struct SkinnyArgs {
 
 // Tuning aid, 8 counters per CTA: [0] cycles the MMA issuer waited for operands, [1] for a free
 // accumulator, [2] its total cycles, [3] cycles the producer waited for a free stage, [4] the CTA's
-// wall time in ns, [5] time the first operands landed, [6] cycles epilogue warp 2 was busy, [7] CTA exit time.  Filled only when B200SD_TIMING=1.
+// wall time in ns, [5] time the first operands landed, [6] cycles epilogue warp 2 was busy, [7] CTA exit time.
+// Tuning builds only; filled when B200SD_TIMING=1.
+#if B200SD_TUNING
 __device__ unsigned long long g_skinny_timing[16 * 256];
+#endif
 
 __device__ __forceinline__ int64_t unit_begin(int64_t cta, int64_t total, int64_t grid) { return cta * total / grid; }
 
@@ -128,7 +131,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   // chunks; otherwise four warps take all columns and the other four stay out of the way.
   const int ep_halves = (p.m % 32 == 0) ? 2 : 1;
   const int cols_per_warp = p.m / ep_halves;
-  if (p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 1] = global_timer_ns();
+  if (kTiming && p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 1] = global_timer_ns();
 
   // The CTA walks its unit range [u_begin, u_end) backwards, one strip-segment at a time:
   //   segment = units of one strip, [max(u_begin, strip*KB), min(u_end, (strip+1)*KB)).
@@ -169,9 +172,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
         for (int64_t u = seg_begin; u < seg_end; ++u) {
           const int32_t kb = int32_t(u - strip * kb_per_strip);
-          const long long tw = p.timing ? clock64() : 0;
+          const long long tw = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
-          if (p.timing) prod_wait += clock64() - tw;
+          if (kTiming && p.timing) prod_wait += clock64() - tw;
           if (!ok) break;
           uint64_t* full = &aux->full_bar[stage];
           mbar_arrive_expect_tx(full, stage_tx_bytes);
@@ -187,7 +190,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         seg_end = seg_begin;
       }
-      if (p.timing) p.timing[blockIdx.x * 16 + 3] = prod_wait;
+      if (kTiming && p.timing) p.timing[blockIdx.x * 16 + 3] = prod_wait;
       if (!ok) {
         for (int s = 0; s < p.stages; ++s) {
           for (int i = 0; i < 100000 && !mbar_try_wait(&aux->full_bar[s], 0) && !mbar_try_wait(&aux->full_bar[s], 1); ++i) {
@@ -212,8 +215,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem + w_stage_bytes), 16, 1024);       // K-major
         const uint32_t w_kstep = (kUmmaK * 128) >> 4;
         const uint32_t a_kstep = kUmmaK >> 4;
-        const long long t_begin = p.timing ? clock64() : 0;
-        const unsigned long long ns_begin = p.timing ? global_timer_ns() : 0;
+        const long long t_begin = (kTiming && p.timing) ? clock64() : 0;
+        const unsigned long long ns_begin = (kTiming && p.timing) ? global_timer_ns() : 0;
         long long wait_full = 0, wait_acc = 0;
         unsigned long long first_data_ns = 0;
         int stage = 0;
@@ -225,16 +228,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         while (seg_end > u_begin && ok) {
           const int64_t strip = (seg_end - 1) / kb_per_strip;
           const int64_t seg_begin = max(u_begin, strip * kb_per_strip);
-          const long long tw0 = p.timing ? clock64() : 0;
+          const long long tw0 = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
-          if (p.timing) wait_acc += clock64() - tw0;
+          if (kTiming && p.timing) wait_acc += clock64() - tw0;
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * acc_cols;
           for (int64_t u = seg_begin; u < seg_end; ++u) {
-            const long long tw1 = p.timing ? clock64() : 0;
+            const long long tw1 = (kTiming && p.timing) ? clock64() : 0;
             ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
-            if (p.timing) {
+            if (kTiming && p.timing) {
               wait_full += clock64() - tw1;
               if (first_data_ns == 0) first_data_ns = global_timer_ns();   // first operands have landed
             }
@@ -263,7 +266,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           seg_end = seg_begin;
         }
-        if (p.timing) {
+        if (kTiming && p.timing) {
           p.timing[blockIdx.x * 16 + 0] = wait_full;
           p.timing[blockIdx.x * 16 + 5] = first_data_ns;
           p.timing[blockIdx.x * 16 + 8] = wait_acc;
@@ -322,7 +325,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           // MMAs for the strip are still running, so that nothing but arithmetic is left for the end.
           first_contrib = member - 1;
           while (unit_begin(first_contrib, p.total_units, grid) > strip_first) --first_contrib;
-          const long long tf0 = p.timing ? clock64() : 0;
+          const long long tf0 = (kTiming && p.timing) ? clock64() : 0;
           if (lane == 0) {
             for (int64_t c = member - 1; c >= first_contrib && ok; --c) {
               const uint64_t* f = p.flags + (c * p.group + side) * 8 + fq;
@@ -343,7 +346,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             }
           }
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-          if (p.timing) ep_flagwait += clock64() - tf0;
+          if (kTiming && p.timing) ep_flagwait += clock64() - tf0;
           if (!ok) break;
           // Every lane acquires the (already raised) flags itself before it reads the partials.
           for (int64_t c = member - 1; c >= first_contrib; --c)
@@ -354,13 +357,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           if (nchunks > 3) load_partials(3, pre3);
         }
 
-        const long long te0 = p.timing ? clock64() : 0;
+        const long long te0 = (kTiming && p.timing) ? clock64() : 0;
         if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);
         tc_fence_after_sync();
-        const long long te1 = p.timing ? clock64() : 0;
+        const long long te1 = (kTiming && p.timing) ? clock64() : 0;
         ep_accwait += te1 - te0;
 
         if (!owns_tail) {
@@ -424,7 +427,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (p.timing) ep_busy += clock64() - te1;
+        if (kTiming && p.timing) ep_busy += clock64() - te1;
         if (lane == 0) mbar_arrive(&aux->acc_empty_bar[acc]);
         if (++acc == kAccBufs) {
           acc = 0;
@@ -432,7 +435,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
         seg_end = seg_begin;
       }
-      if (p.timing && warp == 2 && lane == 0) {
+      if (kTiming && p.timing && warp == 2 && lane == 0) {
         p.timing[blockIdx.x * 16 + 6] = ep_busy;
         p.timing[blockIdx.x * 16 + 9] = ep_flagwait;
         p.timing[blockIdx.x * 16 + 10] = ep_accwait;
@@ -442,7 +445,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
   tc_fence_before_sync();
   __syncthreads();
-  if (p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 7] = global_timer_ns();
+  if (kTiming && p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 7] = global_timer_ns();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(aux->tmem_base, kTmemCols);
@@ -463,10 +466,7 @@ uint64_t NextEpoch() {
 
 // Strip width: as wide as the two accumulator sets allow (2 * n_sub * m <= 512 TMEM columns).
 int StripTiles(int64_t m) {
-  static const int forced = [] {
-    const char* e = std::getenv("B200SD_SKINNY_NSUB");   // tuning override: 1, 2 or 4
-    return e ? std::atoi(e) : 0;
-  }();
+  static const int forced = TuningEnvInt("B200SD_SKINNY_NSUB", 0);   // 1, 2 or 4
   int n_sub = 1;   // measured fastest: wider strips lengthen the exposed last epilogue more than they help DRAM
   if (forced == 1 || forced == 2 || forced == 4) n_sub = forced;
   while (2 * n_sub * m > kTmemCols) n_sub >>= 1;
@@ -482,10 +482,12 @@ Status InitSkinnyKernels() {
   return Status::Ok();
 }
 
+#if B200SD_TUNING
 extern "C" int b200sd_debug_read_skinny_timing(unsigned long long* out, int count) {
   cudaDeviceSynchronize();
   return int(cudaMemcpyFromSymbol(out, g_skinny_timing, sizeof(unsigned long long) * size_t(count)));
 }
+#endif
 
 size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k) {
   if (m <= 0 || m > 128 || m % 16 != 0 || n <= 0 || k <= 0) return 0;
@@ -510,9 +512,8 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   if ((reinterpret_cast<uintptr_t>(g.workspace) & 15) != 0)
     return Status::Error(kInvalidArgument, "split-K kernel: workspace must be 16-byte aligned");
 
-  static const int env_promo = [] { const char* e = std::getenv("B200SD_SKINNY_PROMO"); return e ? std::atoi(e) : 3; }();
-  static const int env_stages = [] { const char* e = std::getenv("B200SD_SKINNY_STAGES"); return e ? std::atoi(e) : 0; }();
-  static const bool timing_on = [] { const char* e = std::getenv("B200SD_TIMING"); return e != nullptr && e[0] == '1'; }();
+  static const int env_promo = TuningEnvInt("B200SD_SKINNY_PROMO", 3);
+  static const int env_stages = TuningEnvInt("B200SD_SKINNY_STAGES", 0);
   CUtensorMap tmap_w, tmap_a;
   st = MakeByteMatrixMap(&tmap_w, g.b, g.k, g.n, kTileN, kBK, env_promo);  // W [k, n]: box 128(n) x 128(k)
   if (!st.ok()) return st;
@@ -529,7 +530,7 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   if (env_stages >= 2 && env_stages < stages) stages = env_stages;
   if (stages < 2) return Status::Error(kInternal, "split-K kernel: not enough shared memory for two stages");
   p.stages = stages;
-  static const int env_group = [] { const char* e = std::getenv("B200SD_SKINNY_GROUP"); return e ? std::atoi(e) : 2; }();
+  static const int env_group = TuningEnvInt("B200SD_SKINNY_GROUP", 2);
   p.group = (env_group == 1 || env_group == 2 || env_group == 4) ? env_group : 2;
   const int64_t strip_cols = int64_t(p.n_sub) * p.group * kTileN;
   p.num_strips = int32_t((g.n + strip_cols - 1) / strip_cols);
@@ -545,10 +546,13 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
   p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + kFlagBytes);
   p.status = StatusWordPtr();
   p.timing = nullptr;
+#if B200SD_TUNING
+  static const bool timing_on = TuningEnvInt("B200SD_TIMING", 0) == 1;
   if (timing_on) {
     cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_skinny_timing);
     cudaMemsetAsync(p.timing, 0, sizeof(g_skinny_timing), stream);
   }
+#endif
 
   int64_t grid = DeviceSmCount();
   if (grid > kMaxCtas) grid = kMaxCtas;
