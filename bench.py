@@ -581,19 +581,30 @@ class Bench:
         fn = getattr(_native.product, "b200sd_debug_read_timing", None)
         if fn is None:
             return {"unavailable": "the loaded library is the product build; load the tuning build through B200SD_LIBRARY"}
-        n = 8 * grid_ctas
+        slots = 16
+        n = slots * grid_ctas
         buf = (C.c_ulonglong * n)()
         fn(buf, n)
-        rows = [buf[8 * i:8 * i + 8] for i in range(grid_ctas)]
+        rows = [buf[slots * i:slots * i + slots] for i in range(grid_ctas)]
+        rows = [r for r in rows if r[8] > 0]
         leaders = [r for r in rows if r[2] > 0]
         if not leaders:
             return {"unavailable": "no counters were written: set B200SD_TIMING=1"}
         mean = lambda j, src: sum(r[j] for r in src) / len(src)     # noqa: E731
         total = mean(2, leaders)
-        return {"ctas_with_issuer": len(leaders), "issuer_cycles": total, "issuer_wait_operands_frac": mean(0, leaders) / total,
-                "issuer_wait_accumulator_frac": mean(1, leaders) / total, "producer_wait_stage_frac": mean(3, rows) / total,
+        t0 = min(r[8] for r in rows)
+        rel = lambda j, src, f: (f(r[j] for r in src if r[j] > 0) - t0) / 1e3     # noqa: E731  (us after the first CTA's entry)
+        return {"ctas": len(rows), "ctas_with_issuer": len(leaders), "issuer_cycles": total,
+                "issuer_wait_operands_frac": mean(0, leaders) / total,
+                "issuer_wait_accumulator_frac": mean(1, leaders) / total, "issuer_wait_preload_frac": mean(7, leaders) / total,
+                "producer_wait_stage_frac": mean(3, rows) / total,
                 "epilogue_wait_frac": mean(5, rows) / total, "epilogue_busy_frac": mean(6, rows) / total,
-                "kernel_ns": mean(4, leaders), "sm_mhz_in_kernel": 1e3 * total / mean(4, leaders)}
+                "issuer_ns_min_mean_max": [min(r[4] for r in leaders), mean(4, leaders), max(r[4] for r in leaders)],
+                "sm_mhz_in_kernel": 1e3 * total / mean(4, leaders),
+                "timeline_us": {"last_cta_entry": rel(8, rows, max), "setup_done_max": rel(9, rows, max),
+                                "first_operands_min": rel(10, leaders, min), "first_operands_max": rel(10, leaders, max),
+                                "issuer_done_min": rel(11, leaders, min), "issuer_done_max": rel(11, leaders, max),
+                                "epilogue_done_max": rel(12, rows, max), "cta_exit_max": rel(13, rows, max)}}
 
 
 def gpu_arm(args):

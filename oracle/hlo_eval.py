@@ -1,16 +1,19 @@
-"""Mini HLO interpreter for the fixture modules.  TEST INFRASTRUCTURE ONLY.
+"""Mini HLO interpreter for test modules.  TEST INFRASTRUCTURE ONLY.
 
-Evaluates the small subset of HLO text the fixtures under tests/golden/hlo use (parameter,
-constant, convert, broadcast, multiply, divide, add, dot, tanh, maximum, abs, reduce with a max
-computation, clamp, copy, bitcast, reshape, tuple, get-tuple-element) with the interpreter's rules
-(xla/hlo/evaluator/hlo_evaluator_typed_visitor.h: element-wise ops in the operand type, dot with
-f32 accumulation :1271-1340, maximum / clamp propagating NaN :594-613, :843-865), using the
-conversions of scaled_dot_oracle.py.  It lets the SAME module text drive both the expected values
-and, through the rewriter, the CUDA path.  Parity status: as for scaled_dot_oracle.py (conversions
-pinned by the reference's tables; the dot itself not pinned by stored outputs).
+Evaluates the subset of HLO text that the fixtures under tests/golden/hlo and the modules of the
+reference's own GemmRewriter tests (tests/golden/ref_rewrites.json) use -- parameter, constant,
+convert, broadcast, the element-wise arithmetic, compare, select, clamp, dot, reduce (max / add), pad,
+slice, dynamic-slice, concatenate, reshape, bitcast, transpose, copy, tuple, get-tuple-element --
+with the interpreter's rules (xla/hlo/evaluator/hlo_evaluator_typed_visitor.h: element-wise ops
+computed in f32 and rounded to the instruction's type, dot with f32 accumulation and one final
+rounding :1271-1340, maximum / clamp propagating NaN :594-613, :843-865), using the conversions of
+scaled_dot_oracle.py.  It lets the SAME module text drive both the expected values and, through
+the rewriter, the CUDA path.  Parity status: as for scaled_dot_oracle.py (conversions pinned by the
+reference's tables; the dot itself not pinned by stored outputs).
 
 Values are kept as (type, array): FP8 as uint8 code points, bf16 / f16 as uint16 bit patterns,
-f32 as float32, s8 / s32 as integers -- the same representation the parity tests compare in.
+f32 as float32, s8 / s32 as integers, pred as bool -- the representation the parity tests compare in.
+Arrays hold the LOGICAL value; the layout an instruction declares matters only to `bitcast`.
 """
 from __future__ import annotations
 
@@ -21,6 +24,7 @@ import numpy as np
 from . import scaled_dot_oracle as o
 
 _KIND = {"f8e4m3fn": "e4m3fn", "f8e5m2": "e5m2"}
+_INT = {"s8": np.int8, "s32": np.int32, "s64": np.int64, "u8": np.uint8, "u32": np.uint32}
 
 
 def _to_f32(t, v):
@@ -43,46 +47,11 @@ def _from_f32(t, x):
         return o.f32_to_f16_bits(x)
     if t == "f32":
         return x
-    if t == "s32":
-        return x.astype(np.int32)
+    if t in _INT:
+        return x.astype(_INT[t])
+    if t == "pred":
+        return x != 0
     raise ValueError(f"convert to {t}")
-
-
-def _parse(text):
-    comps, cur = {}, None
-    entry = None
-    for line in text.splitlines():
-        t = line.strip()
-        if not t or t.startswith("//") or t.startswith("HloModule"):
-            continue
-        if cur is None:
-            assert t.endswith("{"), t
-            head = t[:-1].strip()
-            is_entry = head.startswith("ENTRY ")
-            name = re.split(r"[ (]", head[6:].strip() if is_entry else head)[0].lstrip("%")
-            cur = comps.setdefault(name, [])
-            if is_entry:
-                entry = name
-            continue
-        if t == "}":
-            cur = None
-            continue
-        root = t.startswith("ROOT ")
-        if root:
-            t = t[5:].strip()
-        name, rest = t.split(" = ", 1)
-        m = re.match(r"(\(.*?\)|[a-z0-9]+\[[0-9, ]*\](?:\{[0-9,]*\})?)\s+([a-z\-]+)\((.*)$", rest)
-        assert m, rest
-        shape, opcode, tail = m.group(1), m.group(2), m.group(3)
-        depth, i = 1, 0
-        while depth:
-            depth += {"(": 1, ")": -1}.get(tail[i], 0)
-            i += 1
-        args, attrs = tail[: i - 1], tail[i:].lstrip(", ")
-        operands = [a.strip().split(" ")[-1].lstrip("%") for a in _split(args)] if opcode not in ("constant", "parameter") else []
-        cur.append(dict(name=name.strip().lstrip("%"), shape=shape, opcode=opcode, operands=operands, literal=args.strip(),
-                        attrs=attrs, root=root))
-    return comps, entry
 
 
 def _split(s):
@@ -101,9 +70,65 @@ def _split(s):
 
 
 def _shape(s):
-    m = re.match(r"([a-z0-9]+)\[([0-9, ]*)\]", s)
+    """"f32[2,3]{0,1}" -> ("f32", (2, 3), (0, 1) or None)."""
+    m = re.match(r"\s*([a-z0-9]+)\[([0-9, ]*)\](?:\{([0-9, ]*)[^}]*\})?", s)
     dims = tuple(int(x) for x in m.group(2).split(",") if x.strip())
-    return m.group(1), dims
+    layout = tuple(int(x) for x in m.group(3).split(",") if x.strip()) if m.group(3) else None
+    if layout is not None and len(layout) != len(dims):
+        layout = None
+    return m.group(1), dims, layout
+
+
+def _parse(text):
+    lines = []
+    for raw in text.splitlines():
+        t = raw.split("//")[0].strip()
+        if not t:
+            continue
+        eq, paren = t.find(" = "), t.find("(")
+        starts = eq >= 0 and (paren < 0 or eq < paren)
+        if t.startswith("HloModule") or t == "}" or starts or (t.endswith("{") and not starts) or not lines:
+            lines.append(t)
+        else:
+            lines[-1] += " " + t          # an instruction written over several lines
+    comps, cur, entry, last = {}, None, None, None
+    for t in lines:
+        if t.startswith("HloModule"):
+            continue
+        if cur is None:
+            assert t.endswith("{"), t
+            head = t[:-1].strip()
+            is_entry = head.startswith("ENTRY ")
+            name = re.split(r"[ (]", head[6:].strip() if is_entry else head)[0].lstrip("%")
+            cur = comps.setdefault(name, [])
+            last = name
+            if is_entry:
+                entry = name
+            continue
+        if t == "}":
+            cur = None
+            continue
+        closes = t.endswith("}") and t.count("{") < t.count("}")
+        if closes:
+            t = t[:-1].strip()
+        root = t.startswith("ROOT ")
+        if root:
+            t = t[5:].strip()
+        name, rest = t.split(" = ", 1)
+        m = re.match(r"(\(.*?\)\s|[a-z0-9]+\[[0-9, ]*\](?:\{[^}]*\})?\s)?\s*([a-z\-]+)\((.*)$", rest)
+        assert m, rest
+        shape, opcode, tail = m.group(1), m.group(2), m.group(3)
+        depth, i = 1, 0
+        while depth:
+            depth += {"(": 1, ")": -1}.get(tail[i], 0)
+            i += 1
+        args, attrs = tail[: i - 1], tail[i:].lstrip(", ")
+        operands = [a.strip().split(" ")[-1].lstrip("%") for a in _split(args)] if opcode not in ("constant", "parameter") else []
+        cur.append(dict(name=name.strip().lstrip("%"), shape=shape.strip() if shape else None, opcode=opcode, operands=operands,
+                        literal=args.strip(), attrs=attrs, root=root))
+        if closes:
+            cur = None
+    return comps, entry or last
 
 
 def _attr_dims(attrs, key):
@@ -111,59 +136,143 @@ def _attr_dims(attrs, key):
     return tuple(int(x) for x in m.group(1).split(",") if x.strip()) if m else None
 
 
+def _physical(dims, layout):
+    return tuple(reversed(layout)) if layout is not None else tuple(range(len(dims)))
+
+
+def _bitcast(v, src, dst):
+    """The bytes of `v` as they lie in memory under `src`'s layout, read under `dst`'s (same element size)."""
+    _, sdims, slayout = src
+    _, ddims, dlayout = dst
+    sp, dp = _physical(sdims, slayout), _physical(ddims, dlayout)
+    flat = np.ascontiguousarray(np.transpose(np.asarray(v).reshape(sdims), sp)).reshape(-1)
+    phys = flat.reshape(tuple(ddims[d] for d in dp))
+    inverse = [dp.index(i) for i in range(len(dp))]
+    return np.ascontiguousarray(np.transpose(phys, inverse))
+
+
+def _dot(lhs, rhs, lc, rc, lb, rb):
+    """f32 values; batch dims lb / rb; one contracting dim each.  Result dims: batch..., lhs free, rhs free."""
+    if lb:
+        lperm = list(lb) + [d for d in range(lhs.ndim) if d not in lb]
+        rperm = list(rb) + [d for d in range(rhs.ndim) if d not in rb]
+        l2, r2 = np.transpose(lhs, lperm), np.transpose(rhs, rperm)
+        nb = len(lb)
+        lc2, rc2 = lperm.index(lc) - nb, rperm.index(rc) - nb
+        bshape = l2.shape[:nb]
+        l3, r3 = l2.reshape((-1,) + l2.shape[nb:]), r2.reshape((-1,) + r2.shape[nb:])
+        parts = [o.dot_f32(np.ascontiguousarray(l3[i]), np.ascontiguousarray(r3[i]), lc2, rc2) for i in range(l3.shape[0])]
+        out = np.stack(parts)
+        return out.reshape(bshape + out.shape[1:])
+    return o.dot_f32(lhs, rhs, lc, rc)
+
+
 def evaluate(text, params):
     """Runs the ENTRY computation on `params` (list, in parameter order, in the representation
     described in the module docstring).  Returns the root value, or a tuple of values."""
     comps, entry = _parse(text)
-    env = {}
+    env, shapes = {}, {}
     result = None
     for ins in comps[entry]:
-        op, name = ins["opcode"], ins["name"]
-        if ins["shape"].startswith("("):
-            t, dims = "tuple", ()
+        op, name, attrs = ins["opcode"], ins["name"], ins["attrs"]
+        shape_text = ins["shape"]
+        if shape_text is None:
+            shp = shapes[ins["operands"][0]]                  # a shape left out is the first operand's
+        elif shape_text.startswith("("):
+            shp = ("tuple", (), None)
         else:
-            t, dims = _shape(ins["shape"])
+            shp = _shape(shape_text)
+        t, dims = shp[0], shp[1]
         a = [env[x] for x in ins["operands"]]
+        a_shapes = [shapes[x] for x in ins["operands"]]
         if op == "parameter":
             val = (t, np.asarray(params[int(ins["literal"])]).reshape(dims))
         elif op == "constant":
             lit = ins["literal"]
-            v = {"inf": np.inf, "-inf": -np.inf, "nan": np.nan}.get(lit)
+            v = {"inf": np.inf, "-inf": -np.inf, "nan": np.nan, "true": 1.0, "false": 0.0}.get(lit)
             v = float(lit) if v is None else v
-            val = (t, _from_f32(t, np.full(dims, v, np.float32)) if t != "s32" else np.full(dims, int(v), np.int32))
+            val = (t, _from_f32(t, np.full(dims, v, np.float32)) if t not in _INT else np.full(dims, int(v), _INT[t]))
         elif op == "convert":
             st, sv = a[0]
-            if st in ("s32", "s8") and t == "f32":
-                val = (t, sv.astype(np.float32))
+            if st in _INT and t == "f32":
+                val = (t, np.asarray(sv).astype(np.float32))
+            elif st == "pred":
+                val = (t, _from_f32(t, np.asarray(sv).astype(np.float32)))
             else:
                 val = (t, _from_f32(t, _to_f32(st, sv)))
-        elif op in ("copy",):
+        elif op == "copy":
             val = a[0]
-        elif op in ("bitcast", "reshape"):            # default layouts only: a row-major reinterpretation of the shape
+        elif op == "reshape":
             val = (t, np.asarray(a[0][1]).reshape(dims))
+        elif op == "bitcast":
+            val = (t, _bitcast(a[0][1], a_shapes[0], shp))
+        elif op == "transpose":
+            val = (t, np.ascontiguousarray(np.transpose(np.asarray(a[0][1]), _attr_dims(attrs, "dimensions"))))
         elif op == "broadcast":
-            bd = _attr_dims(ins["attrs"], "dimensions") or ()
+            bd = _attr_dims(attrs, "dimensions") or ()
             st, sv = a[0]
-            shape = [1] * len(dims)
+            view = [1] * len(dims)
             for i, d in enumerate(bd):
-                shape[d] = dims[d]
-            val = (t, np.broadcast_to(np.asarray(sv).reshape(shape), dims).copy())
-        elif op in ("multiply", "divide", "add", "maximum"):
+                view[d] = dims[d]
+            val = (t, np.broadcast_to(np.asarray(sv).reshape(view), dims).copy())
+        elif op == "slice":
+            spec = re.search(r"slice=\{(.*?)\}", attrs).group(1)
+            idx = []
+            for part in re.findall(r"\[([0-9:]+)\]", spec):
+                nums = [int(x) for x in part.split(":")]
+                idx.append(slice(nums[0], nums[1], nums[2] if len(nums) > 2 else 1))
+            val = (t, np.ascontiguousarray(np.asarray(a[0][1])[tuple(idx)]))
+        elif op == "dynamic-slice":
+            sizes = _attr_dims(attrs, "dynamic_slice_sizes")
+            src = np.asarray(a[0][1])
+            starts = [int(np.asarray(s[1]).reshape(())) for s in a[1:]]
+            starts = [min(max(s, 0), src.shape[i] - sizes[i]) for i, s in enumerate(starts)]     # clamped, as XLA does
+            val = (t, np.ascontiguousarray(src[tuple(slice(s, s + n) for s, n in zip(starts, sizes))]))
+        elif op == "pad":
+            cfg = re.search(r"padding=([0-9_x\-]+)", attrs).group(1)
+            lo_hi = [tuple(int(v) for v in part.split("_")) for part in cfg.split("x")]
+            assert all(len(p) == 2 or p[2] == 0 for p in lo_hi), "interior padding"
+            src = np.asarray(a[0][1])
+            out = np.empty(dims, src.dtype)
+            out[...] = np.asarray(a[1][1]).reshape(())
+            out[tuple(slice(lo, lo + n) for n, (lo, *_rest) in zip(src.shape, lo_hi))] = src
+            val = (t, out)
+        elif op == "concatenate":
+            val = (t, np.concatenate([np.asarray(x[1]) for x in a], axis=_attr_dims(attrs, "dimensions")[0]))
+        elif op == "select":
+            val = (t, np.where(np.asarray(a[0][1]).astype(bool), np.asarray(a[1][1]), np.asarray(a[2][1])))
+        elif op == "compare":
+            direction = re.search(r"direction=([A-Z]+)", attrs).group(1)
             x, y = _to_f32(*a[0]), _to_f32(*a[1])
+            fn = {"EQ": np.equal, "NE": np.not_equal, "LT": np.less, "LE": np.less_equal, "GT": np.greater, "GE": np.greater_equal}[direction]
+            val = ("pred", fn(x, y))
+        elif op in ("multiply", "divide", "add", "subtract", "maximum", "minimum"):
+            if a[0][0] in _INT:
+                x, y = np.asarray(a[0][1]), np.asarray(a[1][1])
+                r = {"multiply": x * y, "add": x + y, "subtract": x - y, "maximum": np.maximum(x, y), "minimum": np.minimum(x, y),
+                     "divide": None}[op]
+                val = (t, r.astype(_INT[t]))
+            else:
+                x, y = _to_f32(*a[0]), _to_f32(*a[1])
+                with np.errstate(all="ignore"):
+                    if op == "multiply":
+                        r = x * y
+                    elif op == "divide":
+                        r = x / y
+                    elif op == "add":
+                        r = x + y
+                    elif op == "subtract":
+                        r = x - y
+                    else:
+                        pick = np.maximum if op == "maximum" else np.minimum
+                        r = np.where(np.isnan(x) | np.isnan(y), np.float32(np.nan), pick(x, y))
+                val = (t, _from_f32(t, r.astype(np.float32)))
+        elif op in ("tanh", "abs", "negate", "exponential", "sqrt", "rsqrt", "logistic"):
+            x = _to_f32(*a[0])
             with np.errstate(all="ignore"):
-                if op == "multiply":
-                    r = x * y
-                elif op == "divide":
-                    r = x / y
-                elif op == "add":
-                    r = x + y
-                else:
-                    r = np.where(np.isnan(x) | np.isnan(y), np.float32(np.nan), np.maximum(x, y))
-            val = (t, _from_f32(t, r.astype(np.float32)))
-        elif op == "tanh":
-            val = (t, _from_f32(t, np.tanh(_to_f32(*a[0])).astype(np.float32)))
-        elif op == "abs":
-            val = (t, _from_f32(t, np.abs(_to_f32(*a[0]))))
+                r = {"tanh": np.tanh, "abs": np.abs, "negate": np.negative, "exponential": np.exp, "sqrt": np.sqrt,
+                     "rsqrt": lambda v: 1.0 / np.sqrt(v), "logistic": lambda v: 1.0 / (1.0 + np.exp(-v))}[op](x)
+            val = (t, _from_f32(t, np.asarray(r, np.float32)))
         elif op == "clamp":
             lo, x, hi = (_to_f32(*v) for v in a)
             with np.errstate(invalid="ignore"):
@@ -171,34 +280,54 @@ def evaluate(text, params):
             val = (t, _from_f32(t, r))
         elif op == "reduce":
             x, init = _to_f32(*a[0]), _to_f32(*a[1])
-            body = comps[re.search(r"to_apply=%?([A-Za-z0-9_.]+)", ins["attrs"]).group(1)]
-            assert any(i["opcode"] == "maximum" for i in body), "only max reductions are supported"
-            r = np.float32(np.nan) if np.isnan(x).any() else np.maximum(np.float32(init), x.max() if x.size else init)
+            body = comps[re.search(r"to_apply=%?([A-Za-z0-9_.\-]+)", attrs).group(1)]
+            kind = next((i["opcode"] for i in body if i["root"]), body[-1]["opcode"])
+            rd = _attr_dims(attrs, "dimensions")
+            axes = tuple(rd) if rd else None
+            if kind == "maximum":
+                with np.errstate(invalid="ignore"):
+                    r = np.maximum(np.float32(init), x.max(axis=axes) if x.size else init)
+                r = np.where(np.isnan(x).any(axis=axes), np.float32(np.nan), r)
+            elif kind == "add":
+                r = x.sum(axis=axes, dtype=np.float32) + np.float32(init)
+            else:
+                raise NotImplementedError(f"reduce with {kind}")
             val = (t, _from_f32(t, np.asarray(r, np.float32).reshape(dims)))
         elif op == "dot":
-            lc = _attr_dims(ins["attrs"], "lhs_contracting_dims")[0]
-            rc = _attr_dims(ins["attrs"], "rhs_contracting_dims")[0]
+            lc = _attr_dims(attrs, "lhs_contracting_dims")[0]
+            rc = _attr_dims(attrs, "rhs_contracting_dims")[0]
+            lb, rb = _attr_dims(attrs, "lhs_batch_dims") or (), _attr_dims(attrs, "rhs_batch_dims") or ()
             (lt, lv), (rt, rv) = a
-            if "lhs_batch_dims" in ins["attrs"]:
-                # one leading batch dimension on both operands: independent dots, stacked
-                assert _attr_dims(ins["attrs"], "lhs_batch_dims") == (0,) and _attr_dims(ins["attrs"], "rhs_batch_dims") == (0,)
-                fl, fr = _to_f32(lt, lv), _to_f32(rt, rv)
-                parts = [o.dot_f32(fl[i], fr[i], lc - 1, rc - 1) for i in range(fl.shape[0])]
-                val = (t, _from_f32(t, np.stack(parts)))
-            elif lt == "s8":
+            if lt == "s8" and not lb and np.asarray(lv).ndim == 2 and np.asarray(rv).ndim == 2:
                 val = (t, o.dot_s8(lv, rv, lc, rc))
+            elif lt in _INT and not lb:        # several free dimensions: exact integer contraction
+                val = (t, np.tensordot(np.asarray(lv, np.int64), np.asarray(rv, np.int64), axes=([lc], [rc])).astype(_INT[t]))
+            elif lt in _INT:
+                val = (t, _dot(np.asarray(lv, np.float64).astype(np.float32), np.asarray(rv, np.float64).astype(np.float32), lc, rc, lb, rb).astype(_INT[t]))
             else:
-                val = (t, _from_f32(t, o.dot_f32(_to_f32(lt, lv), _to_f32(rt, rv), lc, rc)))
+                val = (t, _from_f32(t, _dot(_to_f32(lt, lv), _to_f32(rt, rv), lc, rc, lb, rb)))
         elif op == "tuple":
             val = ("tuple", tuple(v for _, v in a))
         elif op == "get-tuple-element":
-            idx = int(re.search(r"index=(\d+)", ins["attrs"]).group(1))
+            idx = int(re.search(r"index=(\d+)", attrs).group(1))
             val = ("?", a[0][1][idx])
         else:
             raise NotImplementedError(op)
-        env[name] = val
+        env[name], shapes[name] = val, shp
         if ins["root"]:
             result = val
     if result is None:
         result = env[comps[entry][-1]["name"]]
     return result[1]
+
+
+def root_types(text):
+    """Element types of the module's result: a list (one entry per tuple element)."""
+    comps, entry = _parse(text)
+    ins = next((i for i in comps[entry] if i["root"]), comps[entry][-1])
+    s = ins["shape"]
+    if s is None:
+        return None
+    if s.startswith("("):
+        return [_shape(p)[0] for p in _split(s[1:-1])]
+    return [_shape(s)[0]]

@@ -29,17 +29,23 @@ def roles(plan):
     return [s["role"] for s in plan["operands"]]
 
 
+def call_line(hlo):
+    """The custom-call instruction of a rewritten module (the first one)."""
+    return next(line.strip() for line in hlo.splitlines() if " custom-call(" in line)
+
+
 def test_config0_lowering():
     hlo, plan = hlo_runner.rewrite(load("c0_scaled_dot_f8"))
-    assert plan["rewritten"] and plan["target"] == "b200$scaled_dot$f8"
+    assert plan["rewritten"] and plan["target"] == "b200$scaled_dot$f8" and len(plan["calls"]) == 1
     assert roles(plan) == ["a", "b", "a_scale", "b_scale"]
     assert (plan["m"], plan["k"], plan["n"]) == (256, 512, 256)
     assert plan["attrs"]["epilogue"] == o.EPI_DEFAULT and plan["attrs"]["lhs_contracting_dim"] == 1 and plan["attrs"]["rhs_contracting_dim"] == 0
     assert [r["role"] for r in plan["results"]] == ["d", "workspace"]
     assert plan["results"][0]["dtype"] == 16
     # No transposes on Blackwell (gemm_rewriter.cc:1535-1554): operands are the parameters themselves.
-    assert re.search(r"custom-call\(a, b, a_scale, b_scale\), custom_call_target=\"b200\$scaled_dot\$f8\"", hlo)
-    assert "(bf16[256,256], s8[33554432])" in hlo and "api_version=API_VERSION_TYPED_FFI" in hlo
+    assert [s["param"] for s in plan["operands"]] == [0, 1, 2, 3] and all(s["chain"] == [] for s in plan["operands"])
+    assert re.search(r"= \(bf16\[256,256\], s8\[33554432\]\) custom-call\(a, b, a_scale, b_scale\), custom_call_target=\"b200\$scaled_dot\$f8\"", hlo)
+    assert "api_version=API_VERSION_TYPED_FFI" in hlo and "transpose" not in hlo
 
 
 def test_config1_lowering_matches_the_expected_custom_call():
@@ -49,20 +55,31 @@ def test_config1_lowering_matches_the_expected_custom_call():
     assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias", "d_scale"]
     d_scale = plan["operands"][-1]
     assert d_scale["param"] == 5 and d_scale["reciprocal"]          # the HLO divides by out_scale
-    assert plan["operands"][4]["dtype"] == 16                        # the bf16 value feeding the convert
+    assert plan["operands"][4]["dtype"] == 16 and plan["operands"][4]["param"] == 4     # the bf16 value feeding the convert
     assert plan["attrs"]["epilogue"] == o.EPI_BIAS_GELU and plan["attrs"]["damax_output"] is True
     assert [r["role"] for r in plan["results"]] == ["d", "amax", "workspace"]
-    assert plan["results"][0]["dtype"] == 20 and plan["results"][0]["root_index"] == 0 and plan["results"][1]["root_index"] == 1
+    assert plan["results"][0]["dtype"] == 20
     assert "(f8e4m3fn[8192,8192], f32[], s8[33554432]) custom-call(a, b, a_scale, b_scale, bias, d_scale_inv)" in hlo
     assert "tanh" not in hlo and "clamp" not in hlo and "reduce" not in hlo     # everything was folded
+    assert re.search(r"ROOT \S+ = \(f8e4m3fn\[8192,8192\], f32\[\]\) tuple\(gemm, amax", hlo)
 
 
 def test_int8_lowering_folds_the_dequantisation():
     hlo, plan = hlo_runner.rewrite(load("c3_int8_dequant"))
     assert plan["target"] == "b200$dot$s8"
     assert roles(plan) == ["a", "b", "a_row_scale", "b_col_scale"]
-    assert plan["results"][0]["dtype"] == 16
+    assert plan["results"][0]["dtype"] == 16 and plan["attrs"]["emit_s32"] is False
     assert "custom-call(a, b, a_scale, b_scale), custom_call_target=\"b200$dot$s8\"" in hlo
+    assert "multiply" not in hlo and "convert" not in hlo
+    # when the raw accumulator is an output of the module as well, the call returns both
+    both = load("c3_int8_dequant", {"4096": 64})
+    both = both.replace("ROOT ", "").rstrip().rstrip("}")
+    root = re.findall(r"^\s*(\S+) = bf16\[64,64\] convert", both, flags=re.M)[-1]
+    acc = re.findall(r"^\s*(\S+) = s32\[64,64\] dot", both, flags=re.M)[-1]
+    both += f"  ROOT both = (bf16[64,64], s32[64,64]) tuple({root}, {acc})\n}}\n"
+    hlo, plan = hlo_runner.rewrite(both)
+    assert plan["attrs"]["emit_s32"] is True and [r["role"] for r in plan["results"]] == ["d", "acc", "workspace"]
+    assert "(bf16[64,64], s32[64,64], s8[33554432]) custom-call(" in hlo
 
 
 def test_divide_scales_e5m2_bias_relu_and_matrix_bias():
@@ -70,7 +87,7 @@ def test_divide_scales_e5m2_bias_relu_and_matrix_bias():
     assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"]
     assert plan["operands"][2]["reciprocal"] and plan["operands"][3]["reciprocal"]
     assert plan["operands"][1]["dtype"] == 19 and plan["attrs"]["rhs_contracting_dim"] == 1
-    assert plan["attrs"]["epilogue"] == o.EPI_BIAS_RELU                            # BIAS_RELU
+    assert plan["attrs"]["epilogue"] == o.EPI_BIAS_RELU
     assert plan["results"][0]["dtype"] == 16                         # the final convert became the output type
     _, plan = hlo_runner.rewrite(load("unscaled_matrix_bias_f32"))
     assert roles(plan) == ["a", "b", "c", "a_scale", "b_scale"]      # c at operand index 2 (gemm_rewriter.cc:1829-1978)
@@ -83,14 +100,14 @@ def test_ragged_shapes_are_padded_to_16_and_sliced():
     gemm_rewriter_fp8_test.cc:521-577)."""
     hlo, plan = hlo_runner.rewrite(load("c0_scaled_dot_f8", {"256": 250, "512": 500}))
     assert plan["rewritten"] and (plan["m"], plan["k"], plan["n"]) == (250, 500, 250)
-    assert plan["operands"][0]["dims"] == [250, 500] and plan["operands"][0]["padded_dims"] == [256, 512]
-    assert plan["operands"][2]["padded_dims"] == []                  # scalars are left alone
-    assert plan["results"][0]["dims"] == [250, 250] and plan["results"][0]["padded_dims"] == [256, 256]
+    assert plan["operands"][0]["source_dims"] == [250, 500] and plan["operands"][0]["dims"] == [256, 512]
+    assert plan["operands"][0]["chain"] == ["pad"] and plan["operands"][2]["dims"] == []      # scalars are left alone
+    assert plan["results"][0]["dims"] == [256, 256]
     assert "a_pad = f8e4m3fn[256,512] pad(a, zero" in hlo and "padding=0_6x0_12" in hlo
     assert "(bf16[256,256], s8[33554432]) custom-call(a_pad, b_pad, a_scale, b_scale)" in hlo
-    assert "d = bf16[250,250] slice(d_full), slice={[0:250], [0:250]}" in hlo
+    assert re.search(r"= bf16\[250,250\] slice\(gemm\), slice=\{\[0:250\], \[0:250\]\}", hlo)
     _, plan = hlo_runner.rewrite(load("c0_scaled_dot_f8"))
-    assert plan["operands"][0]["padded_dims"] == plan["operands"][0]["dims"]
+    assert plan["operands"][0]["chain"] == []
 
 
 def test_batched_dot_lowering_and_interpreter():
@@ -104,7 +121,7 @@ def test_batched_dot_lowering_and_interpreter():
     assert "(f32[10,16,16], s8[33554432]) custom-call(a, b, a_scale, b_scale)" in hlo
     # ragged matrix dimensions are padded, the batch dimension is not
     _, plan = hlo_runner.rewrite(load("batched_scaled_ab_f32", {"10": 7, "16": 20}))
-    assert plan["operands"][0]["padded_dims"] == [7, 32, 32] and plan["results"][0]["padded_dims"] == [7, 32, 32]
+    assert plan["operands"][0]["dims"] == [7, 32, 32] and plan["results"][0]["dims"] == [7, 32, 32]
     rng = np.random.default_rng(3)
     a = o.fp8_encode(rng.standard_normal((10, 16, 32), dtype=np.float32), "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((10, 32, 16), dtype=np.float32), "e4m3fn")
@@ -112,8 +129,11 @@ def test_batched_dot_lowering_and_interpreter():
     for i in range(10):
         exp = o.scaled_dot_f8(a[i], b[i], 0.5, 2.0, out_dtype=o.F32)[0]
         np.testing.assert_allclose(out[i], exp, rtol=1e-6, atol=1e-6)
-    mixed = text.replace("rhs_batch_dims={0}", "rhs_batch_dims={2}")
-    assert not hlo_runner.rewrite(mixed)[1]["rewritten"]
+    # a batch dimension that is not the major-most one of its buffer: still one call, behind a transpose
+    mixed = text.replace("rhs_batch_dims={0}", "rhs_batch_dims={2}").replace("rhs_contracting_dims={1}", "rhs_contracting_dims={0}")
+    mixed = re.sub(r"\[10,32,16\]", "[32,16,10]", mixed)
+    hlo, plan = hlo_runner.rewrite(mixed)
+    assert plan["rewritten"] and "transpose" in plan["operands"][1]["chain"] and plan["batch"] == 10
 
 
 def test_alpha_and_output_scale_without_an_fp8_cast():
@@ -123,7 +143,7 @@ def test_alpha_and_output_scale_without_an_fp8_cast():
     text = load("scaled_ab_alpha_f32")
     hlo, plan = hlo_runner.rewrite(text)
     assert plan["attrs"]["alpha_real"] == 3.0 and roles(plan) == ["a", "b", "a_scale", "b_scale"]
-    assert "alpha_real = 3.0 : f64" in hlo and "ROOT out = f32[48,32] copy(d)" in hlo
+    assert "alpha_real = 3.0 : f64" in hlo and "multiply" not in hlo
     rng = np.random.default_rng(11)
     a = o.fp8_encode(rng.standard_normal((48, 64), dtype=np.float32), "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32), "e4m3fn")
@@ -138,13 +158,14 @@ def test_alpha_and_output_scale_without_an_fp8_cast():
     assert plan["results"][0]["dtype"] == 11
     _, plan = hlo_runner.rewrite(text.replace("multiply(dot0, s_b)", "divide(dot0, s_b)"))
     assert plan["operands"][2]["param"] == 2 and plan["operands"][2]["reciprocal"]
-    # with scaled operands the factor cannot be forwarded: the multiply stays outside, and since the module's
-    # output is then not the custom call's result the module is left alone
+    # with scaled operands the factor cannot be forwarded: the dot still becomes a call, the multiply stays behind it
     scaled = load("c0_scaled_dot_f8").replace("ROOT out = bf16[256,256] dot(", "dot0 = f32[256,256] dot(")
     head, _, _ = scaled.rpartition("}")
     scaled = head + "  s = f32[] parameter(4)\n  s_b = f32[256,256] broadcast(s), dimensions={}\n  ROOT out = f32[256,256] multiply(dot0, s_b)\n}\n"
     assert "multiply(dot0, s_b)" in scaled and "dot0 = f32[256,256] dot(" in scaled
-    assert not hlo_runner.rewrite(scaled)[1]["rewritten"]
+    hlo, plan = hlo_runner.rewrite(scaled)
+    assert plan["rewritten"] and [s["param"] for s in plan["operands"]] == [0, 1, 2, 3]
+    assert re.search(r"ROOT out = f32\[256,256\] multiply\(gemm, s_b\)", hlo)
 
 
 def test_bare_fp8_dot():
@@ -153,7 +174,7 @@ def test_bare_fp8_dot():
     hlo, plan = hlo_runner.rewrite(load("bare_fp8_dot"))
     assert roles(plan) == ["a", "b", "a_scale", "b_scale"] and plan["results"][0]["dtype"] == 20
     assert all(s["param"] == -1 and s["constant"] == 1.0 for s in plan["operands"][2:])
-    assert "(f8e4m3fn[32,48], s8[33554432]) custom-call(a, b, a_scale_const0, b_scale_const1)" in hlo
+    assert "(f8e4m3fn[32,48], s8[33554432]) custom-call(a, b, a_scale_one, b_scale_one)" in hlo
 
 
 def test_combined_epilogues():
@@ -166,10 +187,16 @@ def test_combined_epilogues():
     rng = np.random.default_rng(14)
     a = o.fp8_encode(rng.standard_normal((64, 128), dtype=np.float32) * 4, "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((128, 96), dtype=np.float32) * 4, "e4m3fn")
-    c = rng.standard_normal((64, 96), dtype=np.float32)
-    d, amax = hlo_eval.evaluate(text, [a, b, c, np.float32(0.5), np.float32(0.25), np.float32(0.5)])
-    exp, exp_amax = o.scaled_dot_f8(a, b, 0.5, 0.25, c=c, beta=1.0, d_scale=2.0, out_dtype=o.F8E4M3FN, want_amax=True)
-    assert o.fp8_within_n_values(exp, d, 1) == 0 and float(amax) == pytest.approx(float(exp_amax), rel=1e-6)
+    c = o.f32_to_bf16_bits(rng.standard_normal((64, 96), dtype=np.float32))
+    half, quarter = (o.f32_to_bf16_bits(np.float32(v)) for v in (0.5, 0.25))
+    d, amax = hlo_eval.evaluate(text, [a, b, c, half, quarter, half])
+    exp, exp_amax = o.scaled_dot_f8(a, b, 0.5, 0.25, c=o.bf16_bits_to_f32(c), beta=1.0, d_scale=2.0, out_dtype=o.F8E4M3FN, want_amax=True)
+    # the module computes in bf16, the oracle call in f32: an element may sit one e4m3 step away, or -- where the
+    # sum cancels -- within the ErrorSpec{0.1, 0.1} the reference's own test of this pattern uses (gemm_rewriter_fp8_test.cc:1882)
+    fe, fd = o.fp8_decode(exp, "e4m3fn"), o.fp8_decode(d, "e4m3fn")
+    far = np.abs(o.fp8_ordinal(exp).astype(np.int64) - o.fp8_ordinal(d).astype(np.int64)) > 1
+    assert int((far & (np.abs(fe - fd) > 0.1) & (np.abs(fe - fd) > 0.1 * np.abs(fe))).sum()) == 0
+    assert float(o.bf16_bits_to_f32(amax)) == pytest.approx(float(exp_amax), rel=1e-2)
 
     text = load("relu_amax_e5m2_out")
     _, plan = hlo_runner.rewrite(text)
@@ -223,17 +250,18 @@ def layout_module(d_col, a_col, b_col, lc, rc):
 def test_all_32_layout_combinations_are_rewritten(d_col, a_col, b_col, lc, rc):
     """ScaledABUnscaledDF8Parameterized (gemm_rewriter_fp8_test.cc:2825-2890): row / column-major A, B and D with either
     contracting dimension.  The call takes row-major buffers only, so the plan must describe the same product."""
-    _, plan = hlo_runner.rewrite(layout_module(d_col, a_col, b_col, lc, rc))
+    hlo, plan = hlo_runner.rewrite(layout_module(d_col, a_col, b_col, lc, rc))
     assert plan["rewritten"], plan
     a, b = plan["operands"][0], plan["operands"][1]
     L, R = plan["attrs"]["lhs_contracting_dim"], plan["attrs"]["rhs_contracting_dim"]
     assert a["dims"][L] == 32 and b["dims"][R] == 32                           # both contract over k = 32
     want = (16, 64) if d_col else (64, 16)                                      # D^T when the result is column-major
     assert (a["dims"][1 - L], b["dims"][1 - R]) == want and tuple(plan["results"][0]["dims"]) == want
-    assert plan["results"][0]["transposed"] == d_col
+    assert plan["swapped"] == d_col
     first, second = (b_col, a_col) if d_col else (a_col, b_col)                 # the operands swap places for D^T
-    assert a["transposed"] == first and b["transposed"] == second
+    assert ("bitcast" in a["chain"]) == first and ("bitcast" in b["chain"]) == second     # a column-major buffer read as the row-major matrix it is
     assert a["param"] == (1 if d_col else 0) and plan["operands"][2]["param"] == (3 if d_col else 2)
+    assert "transpose" not in hlo and " copy(" not in hlo
 
 
 def test_tiny_int8_dot_is_padded_and_sliced():
@@ -242,7 +270,7 @@ def test_tiny_int8_dot_is_padded_and_sliced():
     text = load("int8_12x4x8")
     hlo, plan = hlo_runner.rewrite(text)
     assert plan["target"] == "b200$dot$s8" and plan["results"][0]["dtype"] == 4
-    assert [s["padded_dims"] for s in plan["operands"]] == [[16, 16], [16, 16]] and plan["results"][0]["padded_dims"] == [16, 16]
+    assert [s["dims"] for s in plan["operands"]] == [[16, 16], [16, 16]] and plan["results"][0]["dims"] == [16, 16]
     assert "slice={[0:12], [0:8]}" in hlo
     rng = np.random.default_rng(18)
     a = rng.integers(-127, 128, (12, 4), dtype=np.int8)
@@ -255,8 +283,9 @@ def test_bitcast_between_dequantisation_and_dot():
     text = load("bitcast_operand")
     hlo, plan = hlo_runner.rewrite(text)
     assert plan["rewritten"] and (plan["m"], plan["k"], plan["n"]) == (48, 64, 32)
-    assert plan["operands"][0]["dims"] == [48, 64] and plan["operands"][0]["reshaped"] and not plan["operands"][1]["reshaped"]
-    assert "a_view = f8e4m3fn[48,64] bitcast(a)" in hlo and "custom-call(a_view, b, a_scale, b_scale)" in hlo
+    assert plan["operands"][0]["dims"] == [48, 64] and plan["operands"][0]["source_dims"] == [2, 24, 64]
+    assert plan["operands"][0]["chain"] == ["bitcast"] and plan["operands"][1]["chain"] == []
+    assert re.search(r"(\S+) = f8e4m3fn\[48,64\] bitcast\(a\)", hlo)
     rng = np.random.default_rng(20)
     a = o.fp8_encode(rng.standard_normal((2, 24, 64), dtype=np.float32), "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32), "e4m3fn")
@@ -270,9 +299,9 @@ def test_rank3_activation_with_vector_bias_on_the_view():
     text = load("rank3_vector_bias")
     hlo, plan = hlo_runner.rewrite(text)
     assert roles(plan) == ["a", "b", "a_scale", "b_scale", "bias"] and plan["attrs"]["epilogue"] == o.EPI_BIAS
-    assert plan["operands"][0]["dims"] == [64, 64] and plan["operands"][0]["reshaped"]
-    assert plan["results"][0]["dims"] == [64, 32] and plan["results"][0]["view_dims"] == [4, 16, 32]
-    assert "d = f32[4,16,32] bitcast(d_mat)" in hlo
+    assert plan["operands"][0]["dims"] == [64, 64] and plan["operands"][0]["chain"] == ["bitcast"]
+    assert plan["results"][0]["dims"] == [64, 32]
+    assert re.search(r"ROOT \S+ = f32\[4,16,32\] bitcast\(gemm\)", hlo) and " add(" not in hlo
     rng = np.random.default_rng(22)
     a = o.fp8_encode(rng.standard_normal((4, 16, 64), dtype=np.float32), "e4m3fn")
     b = o.fp8_encode(rng.standard_normal((64, 32), dtype=np.float32), "e4m3fn")
@@ -284,18 +313,33 @@ def test_rank3_activation_with_vector_bias_on_the_view():
 
 def test_modules_that_must_be_left_alone():
     hlo, plan = hlo_runner.rewrite(load("not_rewritten_both_e5m2"))
-    assert not plan["rewritten"] and "e5m2" in plan["reason"]
+    assert not plan["rewritten"] and "e5m2" in plan["reason"] and plan["not_rewritten"][0]["dot"]
     assert "custom-call" not in hlo
     f32_dot = load("c0_scaled_dot_f8").replace("f8e4m3fn", "f32")
     assert not hlo_runner.rewrite(f32_dot)[1]["rewritten"]
-    # The GELU pre-activation has another user: would need the AUX epilogue, so GELU is not folded
-    # and the output then depends on a value the custom call does not produce.
+    # The GELU pre-activation has another user: that would need the AUX epilogue, which this library does not
+    # produce, so the bias is folded and the GELU arithmetic stays behind the call.
     aux = load("c1_fp8_linear_gelu_amax", {"8192": 64}).replace("tuple(d, amax)", "tuple(d, x)").replace(
         "(f8e4m3fn[64,64], f32[]) tuple", "(f8e4m3fn[64,64], f32[64,64]) tuple")
-    assert not hlo_runner.rewrite(aux)[1]["rewritten"]
+    hlo, plan = hlo_runner.rewrite(aux)
+    assert plan["rewritten"] and plan["attrs"]["epilogue"] == o.EPI_BIAS and "tanh" in hlo and plan["results"][0]["dtype"] == 11
     with pytest.raises(XlaFfiError) as e:
         hlo_runner.rewrite("HloModule broken\nENTRY main {\n  x = oops\n}\n")
     assert e.value.code == 3
+
+
+def test_two_dots_in_one_module_become_two_calls():
+    """GemmRewriterVisitor rewrites every dot it visits (gemm_rewriter.cc:657-779): a two-layer MLP -- FP8 linear +
+    GELU + scaled FP8 cast feeding a second FP8 linear -- lowers onto two calls, the second taking the first's
+    FP8 result as its A operand."""
+    text = load("two_layer_mlp")
+    hlo, plan = hlo_runner.rewrite(text)
+    assert plan["rewritten"] and len(plan["calls"]) == 2 and plan["not_rewritten"] == []
+    first, second = plan["calls"]
+    assert first["attrs"]["epilogue"] == o.EPI_BIAS_GELU and first["results"][0]["dtype"] == 20
+    assert [s["role"] for s in second["operands"]] == ["a", "b", "a_scale", "b_scale"] and second["results"][0]["dtype"] == 16
+    assert second["operands"][0]["source"] == first["name"]           # the FP8 activation never leaves FP8
+    assert hlo.count(" custom-call(") == 2 and " dot(" not in hlo and "tanh" not in hlo
 
 
 def test_interpreter_agrees_with_the_scaled_dot_oracle():
@@ -318,24 +362,34 @@ def test_interpreter_agrees_with_the_scaled_dot_oracle():
     assert np.array_equal(out, o.dequant_s32_to_bf16(o.dot_s8(a8, b8), rs, cs))
 
 
-@pytest.mark.parametrize("name", ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
-                                  "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
-                                  "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
-                                  "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8", "bitcast_operand", "rank3_vector_bias"])
-def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
-    """The plan's operands, results and attributes must form a call frame the handler accepts at
-    instantiate time (buffer data is null there, as in custom_call_thunk.cc:179-240)."""
-    import torch
-    from xla_b200.scaled_dot import FfiCall
+FIXTURES = ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_int8_dequant",
+            "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
+            "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
+            "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8", "bitcast_operand",
+            "rank3_vector_bias", "two_layer_mlp"]
 
-    _, plan = hlo_runner.rewrite(load(name))
+
+@pytest.mark.parametrize("name", FIXTURES)
+def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
+    """Every custom call of the rewritten module -- operands, result tuple, backend_config, as the text spells
+    them -- must form a call frame the handler accepts at instantiate time (buffer data is null there, as in
+    custom_call_thunk.cc:179-240)."""
+    from xla_b200.scaled_dot import Buffer, FfiCall
+
+    hlo, plan = hlo_runner.rewrite(load(name))
     assert plan["rewritten"], plan
-    assert isinstance(plan["attrs"]["beta"], float) and isinstance(plan["attrs"]["alpha_real"], float)
-    # the call receives the padded shapes (the pad / slice instructions stay outside it)
-    ops = [torch.empty(tuple(s.get("padded_dims", s["dims"])), dtype=hlo_runner._torch_dtype(s["dtype"]), device="meta")
-           for s in plan["operands"]]
-    res = [torch.empty(tuple(r.get("padded_dims", r["dims"])), dtype=hlo_runner._torch_dtype(r["dtype"]), device="meta")
-           for r in plan["results"]]
-    call = FfiCall(plan["target"], ops, res, dict(plan["attrs"]))
-    call.instantiate()
-    call.close()
+    comps, entry = hlo_runner.parse_module(hlo)
+    shapes = {i["name"]: i["shape"] for i in comps[entry]}
+    code = {"pred": 1, "s8": 2, "s32": 4, "f16": 10, "f32": 11, "bf16": 16, "f8e5m2": 19, "f8e4m3fn": 20}
+    n = 0
+    for ins in comps[entry]:
+        if ins["opcode"] != "custom-call":
+            continue
+        ops = [Buffer(code[shapes[o_][0]], tuple(shapes[o_][1])) for o_ in ins["operands"]]
+        res = [Buffer(code[s[0]], tuple(s[1])) for s in ins["shape"][1]]
+        target = re.search(r'custom_call_target="([^"]+)"', ins["attrs"]).group(1)
+        call = FfiCall(target, ops, res, hlo_runner._backend_config(ins["attrs"]))
+        call.instantiate()
+        call.close()
+        n += 1
+    assert n == len(plan["calls"])

@@ -150,10 +150,14 @@ constexpr size_t kSkPartialBytes = size_t(2 * kBM) * kBN * 4;          // one 25
 
 // Tuning aid: per CTA, [0] cycles the MMA issuer waited for operands, [1] cycles it waited for a
 // free accumulator, [2] its total cycles, [3] cycles the producer waited for a free stage,
-// [4] the CTA's wall time in ns, [5]/[6] cycles epilogue warp 2 waited for / worked on accumulators.
+// [4] the issuer's wall time in ns, [5]/[6] cycles epilogue warp 2 waited for / worked on accumulators,
+// [7] cycles the issuer waited for the stream-K preload; then absolute %globaltimer values (ns):
+// [8] CTA entry, [9] set-up done (after the cluster barrier), [10] first operands landed, [11] issuer done,
+// [12] epilogue warp 2 done, [13] CTA exit.
+constexpr int kTimingSlots = 16;
 // Tuning builds only; filled when B200SD_TIMING=1 was set at load time.
 #if B200SD_TUNING
-__device__ unsigned long long g_dense_timing[8 * 512];
+__device__ unsigned long long g_dense_timing[kTimingSlots * 512];
 #endif
 
 __device__ __forceinline__ float load_as_f32(const void* base, int32_t dtype, int64_t idx) {
@@ -543,6 +547,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (kTiming && p.timing && threadIdx.x == 0) p.timing[blockIdx.x * kTimingSlots + 8] = global_timer_ns();
   const uint32_t rank = kPair ? cluster_cta_rank() : 0u;        // 0 = leader of the pair
   int32_t first_tile = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
   int32_t tile_step = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
@@ -595,6 +600,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   if (kPair) cluster_sync_all();          // the peer's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = aux->tmem_base;
+  if (kTiming && p.timing && threadIdx.x == 0) p.timing[blockIdx.x * kTimingSlots + 9] = global_timer_ns();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -657,7 +663,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           }
         }
       }
-      if (kTiming && p.timing) p.timing[blockIdx.x * 8 + 3] = prod_wait;
+      if (kTiming && p.timing) p.timing[blockIdx.x * kTimingSlots + 3] = prod_wait;
       if (!ok && !kPair) {
         // Abort path: let loads that were already issued land before the CTA's memory is released.
         for (int s = 0; s < kStages; ++s) {
@@ -672,6 +678,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       const long long t_begin = (kTiming && p.timing) ? clock64() : 0;
       const unsigned long long ns_begin = (kTiming && p.timing) ? global_timer_ns() : 0;
       long long wait_full = 0, wait_acc = 0;
+      unsigned long long first_data_ns = 0;
       const uint32_t sbo = 1024, lbo = 16384;
       const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), lbo, sbo);
       const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), lbo, sbo);
@@ -693,7 +700,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         if (item.mode == 2) {       // the epilogue warps have put the earlier shares' sum into this accumulator
           const long long tp0 = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->preload_bar, 0, abort_flag, p.status, kStatusMmaTimeout);
-          if (kTiming && p.timing) p.timing[blockIdx.x * 8 + 7] = clock64() - tp0;
+          if (kTiming && p.timing) p.timing[blockIdx.x * kTimingSlots + 7] = clock64() - tp0;
           if (!ok) break;
         }
         tc_fence_after_sync();
@@ -702,7 +709,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         for (int32_t kb = item.kb0; kb < item.kb1; ++kb) {
           const long long tw1 = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
-          if (kTiming && p.timing) wait_full += clock64() - tw1;
+          if (kTiming && p.timing) {
+            wait_full += clock64() - tw1;
+            if (first_data_ns == 0) first_data_ns = global_timer_ns();
+          }
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t a_desc = a_desc0 + uint64_t((stage * kAStageBytes) >> 4);
@@ -744,10 +754,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         }
       }
       if (kTiming && p.timing) {
-        p.timing[blockIdx.x * 8 + 0] = wait_full;
-        p.timing[blockIdx.x * 8 + 1] = wait_acc;
-        p.timing[blockIdx.x * 8 + 2] = clock64() - t_begin;
-        p.timing[blockIdx.x * 8 + 4] = global_timer_ns() - ns_begin;
+        p.timing[blockIdx.x * kTimingSlots + 0] = wait_full;
+        p.timing[blockIdx.x * kTimingSlots + 1] = wait_acc;
+        p.timing[blockIdx.x * kTimingSlots + 2] = clock64() - t_begin;
+        p.timing[blockIdx.x * kTimingSlots + 4] = global_timer_ns() - ns_begin;
+        p.timing[blockIdx.x * kTimingSlots + 10] = first_data_ns;
+        p.timing[blockIdx.x * kTimingSlots + 11] = global_timer_ns();
       }
     }
   } else {
@@ -1022,8 +1034,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       __syncwarp();
     }
     if (kTiming && p.timing && warp == 2 && lane == 0) {
-      p.timing[blockIdx.x * 8 + 5] = ep_wait;
-      p.timing[blockIdx.x * 8 + 6] = ep_busy;
+      p.timing[blockIdx.x * kTimingSlots + 5] = ep_wait;
+      p.timing[blockIdx.x * kTimingSlots + 6] = ep_busy;
+      p.timing[blockIdx.x * kTimingSlots + 12] = global_timer_ns();
     }
     if (!kInt8 && p.amax != nullptr) {
       // The bit pattern of a non-negative float orders like the float; NaN patterns sit above
@@ -1059,6 +1072,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   tc_fence_before_sync();
   __syncthreads();
   if (kPair) cluster_sync_all();   // nobody leaves while the peer may still read this CTA's shared memory
+  if (kTiming && p.timing && threadIdx.x == 0) p.timing[blockIdx.x * kTimingSlots + 13] = global_timer_ns();
   if (warp == 1) {
     tc_fence_after_sync();
     if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
@@ -1307,7 +1321,7 @@ Status LaunchDense(const GemmProblem& g, cudaStream_t stream, LaunchStats* stats
   static const bool timing_on = TuningEnvInt("B200SD_TIMING", 0) == 1;
   if (timing_on) {
     cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_dense_timing);
-    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
+    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * kTimingSlots * 512, stream);
   }
 #endif
 
@@ -1452,7 +1466,7 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   static const bool timing_on = TuningEnvInt("B200SD_TIMING", 0) == 1;
   if (timing_on) {
     cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_dense_timing);
-    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * 8 * 512, stream);
+    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * kTimingSlots * 512, stream);
   }
 #endif
   q.emu_maps = nullptr;
