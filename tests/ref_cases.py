@@ -34,13 +34,14 @@ def parameters(hlo: str):
 
 def make_inputs(hlo: str, seed: int):
     """Seeded inputs in the oracle's representation (FP8 code points, bf16 / f16 bit patterns ...).  Values are kept
-    moderate (|x| <= 2, scales in [0.5, 2]) so that sums over the short contracting dimensions of these modules
-    stay far from the limits of f16 and of the FP8 output types."""
+    small (|x| <= 0.25, scales in [0.5, 1]) so that results over the short contracting dimensions of these modules
+    stay of order one or below: several of the reference's bounds are absolute (ErrorSpec{2e-3, 0}), and its tests
+    draw their random arguments from a small range too."""
     rng = np.random.default_rng(seed)
     out = []
     for _, t, dims in parameters(hlo):
         if t in ("f8e4m3fn", "f8e5m2"):
-            v = rng.uniform(-2.0, 2.0, size=dims).astype(np.float32)
+            v = rng.uniform(-0.25, 0.25, size=dims).astype(np.float32)
             out.append(o.fp8_encode(v, "e4m3fn" if t == "f8e4m3fn" else "e5m2"))
         elif t == "s8":
             out.append(rng.integers(-127, 128, size=dims, dtype=np.int8))
@@ -49,7 +50,7 @@ def make_inputs(hlo: str, seed: int):
         elif t in ("s32", "s64"):
             out.append(np.zeros(dims, np.int32))
         else:
-            v = (rng.uniform(0.5, 2.0, size=dims) if len(dims) == 0 else rng.uniform(-1.0, 1.0, size=dims)).astype(np.float32)
+            v = (rng.uniform(0.5, 1.0, size=dims) if len(dims) == 0 else rng.uniform(-0.25, 0.25, size=dims)).astype(np.float32)
             out.append({"f32": lambda x: x, "bf16": o.f32_to_bf16_bits, "f16": o.f32_to_f16_bits}[t](v))
     return out
 

@@ -274,19 +274,22 @@ class _Evaluator:
             direction = re.search(r"direction=([A-Z]+)", attrs).group(1)
             fn = {"EQ": torch.eq, "NE": torch.ne, "LT": torch.lt, "LE": torch.le, "GT": torch.gt, "GE": torch.ge}[direction]
             return fn(a[0], a[1])
-        if op in ("add", "subtract", "multiply", "divide", "maximum", "minimum"):
-            x, y = a
-            if op == "maximum" or op == "minimum":          # NaN propagates, as XLA's maximum / minimum do
-                r = (torch.maximum if op == "maximum" else torch.minimum)(x, y)
-                return r
-            return {"add": torch.add, "subtract": torch.sub, "multiply": torch.mul, "divide": torch.div}[op](x, y)
-        if op in ("tanh", "abs", "negate", "exponential", "sqrt", "rsqrt", "logistic"):
-            fn = {"tanh": torch.tanh, "abs": torch.abs, "negate": torch.neg, "exponential": torch.exp, "sqrt": torch.sqrt,
-                  "rsqrt": torch.rsqrt, "logistic": torch.sigmoid}[op]
-            return fn(a[0])
-        if op == "clamp":
-            lo, x, hi = a
-            return torch.minimum(torch.maximum(x, lo), hi)        # NaN in x stays NaN
+        if op in ("add", "subtract", "multiply", "divide", "maximum", "minimum", "tanh", "abs", "negate", "exponential", "sqrt",
+                  "rsqrt", "logistic", "clamp"):
+            # Floating-point element-wise ops are computed in f32 and rounded once to the instruction's type
+            # (FP8 tensors have no arithmetic of their own in torch); integers stay integers.
+            floating = a[0].dtype.is_floating_point
+            v = [x.float() for x in a] if floating else list(a)
+            if op in ("maximum", "minimum"):                   # NaN propagates, as XLA's maximum / minimum do
+                r = (torch.maximum if op == "maximum" else torch.minimum)(v[0], v[1])
+            elif op == "clamp":
+                r = torch.minimum(torch.maximum(v[1], v[0]), v[2])      # NaN in x stays NaN
+            elif len(v) == 2:
+                r = {"add": torch.add, "subtract": torch.sub, "multiply": torch.mul, "divide": torch.div}[op](v[0], v[1])
+            else:
+                r = {"tanh": torch.tanh, "abs": torch.abs, "negate": torch.neg, "exponential": torch.exp, "sqrt": torch.sqrt,
+                     "rsqrt": torch.rsqrt, "logistic": torch.sigmoid}[op](v[0])
+            return r.to(_dtype(t)) if floating else r
         if op == "reduce":
             body = self.comps[re.search(r"to_apply=%?([A-Za-z0-9_.\-]+)", attrs).group(1)]
             kind = next(i["opcode"] for i in body if i["root"] or i is body[-1])
