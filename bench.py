@@ -581,7 +581,7 @@ class Bench:
         fn = getattr(_native.product, "b200sd_debug_read_timing", None)
         if fn is None:
             return {"unavailable": "the loaded library is the product build; load the tuning build through B200SD_LIBRARY"}
-        slots = 16
+        slots = 24
         n = slots * grid_ctas
         buf = (C.c_ulonglong * n)()
         fn(buf, n)
@@ -599,11 +599,14 @@ class Bench:
                 "issuer_wait_accumulator_frac": mean(1, leaders) / total, "issuer_wait_preload_frac": mean(7, leaders) / total,
                 "producer_wait_stage_frac": mean(3, rows) / total,
                 "epilogue_wait_frac": mean(5, rows) / total, "epilogue_busy_frac": mean(6, rows) / total,
+                "epilogue_busy_split": {"tmem_load_wait": mean(16, rows) / max(1.0, mean(6, rows)), "arithmetic": mean(17, rows) / max(1.0, mean(6, rows)),
+                                        "stage_flush": mean(18, rows) / max(1.0, mean(6, rows))},
                 "issuer_ns_min_mean_max": [min(r[4] for r in leaders), mean(4, leaders), max(r[4] for r in leaders)],
                 "sm_mhz_in_kernel": 1e3 * total / mean(4, leaders),
                 "timeline_us": {"last_cta_entry": rel(8, rows, max), "setup_done_max": rel(9, rows, max),
                                 "first_operands_min": rel(10, leaders, min), "first_operands_max": rel(10, leaders, max),
                                 "issuer_done_min": rel(11, leaders, min), "issuer_done_max": rel(11, leaders, max),
+                                "last_accumulator_complete_max": rel(14, rows, max), "last_tile_stored_max": rel(15, rows, max),
                                 "epilogue_done_max": rel(12, rows, max), "cta_exit_max": rel(13, rows, max)}}
 
 

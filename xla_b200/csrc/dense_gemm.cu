@@ -73,11 +73,17 @@ struct __align__(16) EpilogueVectors {
 // full lines issued by one lane instead of 16-byte stores from every lane.
 constexpr int kStoreStageBytes = 32 * 128;
 
-// Layout: [pipeline stages][peer-reduce: eight 4 KiB store stages][aux][others: epilogue vectors].
+// Every other instantiation stages 32 rows x 64 bytes of converted output per epilogue warp, so that what
+// goes to global memory are 64-byte row segments from four neighbouring lanes instead of one 16-byte
+// piece per lane and row (a warp-wide store then touches 8 lines instead of 32).
+constexpr int kOutStageRowBytes = 64;
+constexpr int kOutStageBytes = 32 * kOutStageRowBytes;
+
+// Layout: [pipeline stages][peer-reduce: eight 4 KiB store stages][aux][others: epilogue vectors, eight 2 KiB output stages].
 template <bool kPair, bool kReduce = false>
 constexpr size_t DenseSmemBytes() {
   return 1024 /*alignment slack*/ + size_t(Shape<kPair>::kStages) * Shape<kPair>::kStageBytes + sizeof(DenseAux<kPair>) +
-         (kReduce ? size_t(kEpilogueWarps) * kStoreStageBytes : sizeof(EpilogueVectors));
+         (kReduce ? size_t(kEpilogueWarps) * kStoreStageBytes : sizeof(EpilogueVectors) + size_t(kEpilogueWarps) * kOutStageBytes);
 }
 static_assert(DenseSmemBytes<true, true>() <= 232448 && DenseSmemBytes<true, false>() <= 232448, "shared memory budget");
 
@@ -153,8 +159,10 @@ constexpr size_t kSkPartialBytes = size_t(2 * kBM) * kBN * 4;          // one 25
 // [4] the issuer's wall time in ns, [5]/[6] cycles epilogue warp 2 waited for / worked on accumulators,
 // [7] cycles the issuer waited for the stream-K preload; then absolute %globaltimer values (ns):
 // [8] CTA entry, [9] set-up done (after the cluster barrier), [10] first operands landed, [11] issuer done,
-// [12] epilogue warp 2 done, [13] CTA exit.
-constexpr int kTimingSlots = 16;
+// [12] epilogue warp 2 done, [13] CTA exit, [14] last accumulator complete (seen by epilogue warp 2), [15] that warp's
+// last tile stored (before the amax hand-shake), [16] cycles epilogue warp 2 spent waiting for its TMEM loads, [17] in the
+// arithmetic and conversion of chunks, [18] in the flushes of its output stage.
+constexpr int kTimingSlots = 24;
 // Tuning builds only; filled when B200SD_TIMING=1 was set at load time.
 #if B200SD_TUNING
 __device__ unsigned long long g_dense_timing[kTimingSlots * 512];
@@ -403,14 +411,14 @@ __device__ __forceinline__ void flush_store_stage(const DenseArgs& p, const Redu
   }
 }
 
-// Converts and stores kChunk consecutive columns of one row.
-__device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float (&v)[kChunk], int64_t row, int64_t col0,
-                                                int32_t ncols) {
-  const int64_t off = row * p.n + col0;
-  const bool vec = ncols == kChunk && p.vec_store_ok;
-  if (p.d_dtype == kF8E4M3FN || p.d_dtype == kF8E5M2) {
-    const __nv_fp8_interpretation_t fmt = p.d_dtype == kF8E4M3FN ? __NV_E4M3 : __NV_E5M2;
-    uint8_t* out = static_cast<uint8_t*>(p.d) + off;
+// Converts and stores kChunk consecutive columns of one row straight from the lane's registers.  The path
+// for outputs whose rows are not 16-byte aligned; kept out of line so that it does not widen the epilogue loop.
+__device__ __noinline__ void store_row_chunk(void* d, int32_t d_dtype, bool vec_ok, const float (&v)[kChunk], int64_t off,
+                                             int32_t ncols) {
+  const bool vec = ncols == kChunk && vec_ok;
+  if (d_dtype == kF8E4M3FN || d_dtype == kF8E5M2) {
+    const __nv_fp8_interpretation_t fmt = d_dtype == kF8E4M3FN ? __NV_E4M3 : __NV_E5M2;
+    uint8_t* out = static_cast<uint8_t*>(d) + off;
     uint32_t w[kChunk / 4];
 #pragma unroll
     for (int i = 0; i < kChunk / 4; ++i) {
@@ -425,10 +433,10 @@ __device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float 
       for (int i = 0; i < kChunk; ++i)
         if (i < ncols) out[i] = static_cast<uint8_t>(w[i >> 2] >> (8 * (i & 3)));
     }
-  } else if (p.d_dtype == kBF16 || p.d_dtype == kF16) {
-    uint16_t* out = static_cast<uint16_t*>(p.d) + off;
+  } else if (d_dtype == kBF16 || d_dtype == kF16) {
+    uint16_t* out = static_cast<uint16_t*>(d) + off;
     uint32_t w[kChunk / 2];
-    if (p.d_dtype == kBF16) {
+    if (d_dtype == kBF16) {
 #pragma unroll
       for (int i = 0; i < kChunk / 2; ++i) {
         const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
@@ -450,7 +458,7 @@ __device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float 
         if (i < ncols) out[i] = static_cast<uint16_t>(w[i >> 1] >> (16 * (i & 1)));
     }
   } else {  // kF32
-    float* out = static_cast<float*>(p.d) + off;
+    float* out = static_cast<float*>(d) + off;
     if (vec) {
 #pragma unroll
       for (int i = 0; i < kChunk / 4; ++i)
@@ -463,13 +471,85 @@ __device__ __forceinline__ void store_row_chunk(const DenseArgs& p, const float 
   }
 }
 
+// v += beta * C for kChunk columns of one row.  Out of line: a matrix bias is the rare case and its three
+// element types would otherwise triple this code inside the epilogue loop.
+__device__ __noinline__ void add_matrix_bias(const void* c, int32_t c_dtype, float beta, int64_t off, int32_t ncols, float (&v)[kChunk]) {
+#pragma unroll
+  for (int i = 0; i < kChunk; ++i)
+    if (i < ncols) v[i] += beta * load_as_f32(c, c_dtype, off + i);
+}
+
+// The warp's output stage: 32 rows (one per lane) x four 16-byte pieces, the piece index XOR-swizzled
+// by the row pair so that neither the row-per-lane writes nor the piece-per-lane reads collide on banks.
+__device__ __forceinline__ void stage_put(uint4* stage, int lane, int piece, uint4 v) {
+  stage[lane * 4 + (piece ^ ((lane >> 1) & 3))] = v;
+}
+
+// Converts kChunk values of this lane's row to the output type and puts them into the stage at
+// piece `piece0` (1, 2 or 4 pieces for 1-, 2- and 4-byte output elements).
+__device__ __forceinline__ void stage_row_chunk(const DenseArgs& p, const float (&v)[kChunk], uint4* stage, int lane, int piece0) {
+  if (p.d_dtype == kF8E4M3FN || p.d_dtype == kF8E5M2) {
+    const __nv_fp8_interpretation_t fmt = p.d_dtype == kF8E4M3FN ? __NV_E4M3 : __NV_E5M2;
+    uint32_t w[kChunk / 4];
+#pragma unroll
+    for (int i = 0; i < kChunk / 4; ++i) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i], v[4 * i + 1]), __NV_SATFINITE, fmt);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i + 2], v[4 * i + 3]), __NV_SATFINITE, fmt);
+      w[i] = lo | (hi << 16);
+    }
+    stage_put(stage, lane, piece0, make_uint4(w[0], w[1], w[2], w[3]));
+  } else if (p.d_dtype == kBF16 || p.d_dtype == kF16) {
+    uint32_t w[kChunk / 2];
+    if (p.d_dtype == kBF16) {
+#pragma unroll
+      for (int i = 0; i < kChunk / 2; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kChunk / 2; ++i) {
+        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    stage_put(stage, lane, piece0, make_uint4(w[0], w[1], w[2], w[3]));
+    stage_put(stage, lane, piece0 + 1, make_uint4(w[4], w[5], w[6], w[7]));
+  } else {  // kF32
+#pragma unroll
+    for (int i = 0; i < kChunk / 4; ++i)
+      stage_put(stage, lane, piece0 + i, make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]),
+                                                      __float_as_uint(v[4 * i + 2]), __float_as_uint(v[4 * i + 3])));
+  }
+}
+
+// Writes the warp's staged 32 x 64-byte block out: four store instructions, each covering 8 rows x 64
+// contiguous bytes.  `row0` is the warp's first row in the [batch * m, n] view of D, `rows_valid` how many
+// of its rows exist, `byte_col0` the block's first byte within a row, `row_bytes` the row pitch.
+__device__ __forceinline__ void stage_flush(const DenseArgs& p, const uint4* stage, int lane, int64_t row0, int32_t rows_valid,
+                                            int64_t byte_col0, int64_t row_bytes) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int q = i * 32 + lane;
+    const int r = q >> 2, piece = q & 3;
+    const uint4 v = stage[r * 4 + (piece ^ ((r >> 1) & 3))];
+    const int64_t bc = byte_col0 + piece * 16;
+    if (r < rows_valid && bc < row_bytes) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.d) + (row0 + r) * row_bytes + bc) = v;
+  }
+  __syncwarp();
+}
+
 // Epilogue arithmetic and store for kChunk columns of one accumulator row.  Every option is
 // tested once per chunk, outside the per-element loops, which keeps the unrolled code small
 // enough to stay resident in the instruction cache while eight warps run it.
+// With `stage` the converted values go to the warp's output stage (piece `piece0`) for a coalesced flush by
+// the caller; without it they are stored directly (unaligned or ragged outputs).
 template <bool kInt8>
 __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t (&r)[kChunk], int64_t row, int64_t col0,
                                              int32_t ncols, float scale, float d_scale, float row_scale,
-                                             const float* bias_c, const float* colscale_c, uint32_t* amax_bits) {
+                                             const float* bias_c, const float* colscale_c, uint32_t* amax_bits,
+                                             uint4* stage, int lane, int piece0) {
   float v[kChunk];
   if (kInt8) {
     if (p.d_s32) {
@@ -499,10 +579,13 @@ __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t 
 #pragma unroll
     for (int i = 0; i < kChunk; ++i) v[i] = __uint_as_float(r[i]) * scale;
     if (p.c != nullptr) {
-      const int64_t off = row * p.n + col0;
+      // through a copy: an array handed to an out-of-line function lives in local memory, and `v` must not
+      float t[kChunk];
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i)
-        if (i < ncols) v[i] += p.beta * load_as_f32(p.c, p.c_dtype, off + i);
+      for (int i = 0; i < kChunk; ++i) t[i] = v[i];
+      add_matrix_bias(p.c, p.c_dtype, p.beta, row * p.n + col0, ncols, t);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = t[i];
     }
     if (p.bias) {
 #pragma unroll
@@ -527,7 +610,14 @@ __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t 
       for (int i = 0; i < kChunk; ++i) v[i] *= d_scale;
     }
   }
-  store_row_chunk(p, v, row, col0, ncols);
+  if (stage != nullptr) {
+    stage_row_chunk(p, v, stage, lane, piece0);
+  } else {
+    float t[kChunk];                 // see add_matrix_bias above
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) t[i] = v[i];
+    store_row_chunk(p.d, p.d_dtype, p.vec_store_ok != 0, t, row * p.n + col0, ncols);
+  }
 }
 
 template <bool kInt8, bool kPair, bool kReduce = false>
@@ -547,7 +637,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (kTiming && p.timing && threadIdx.x == 0) p.timing[blockIdx.x * kTimingSlots + 8] = global_timer_ns();
+  const unsigned long long t_entry = (kTiming && p.timing) ? global_timer_ns() : 0;
+  // The kernel behind this one in the stream may be scheduled as this one's CTAs retire (it sets itself up
+  // and then waits for this grid to complete before it touches global memory).
+  if (threadIdx.x == 0) griddep_launch_dependents();
   const uint32_t rank = kPair ? cluster_cta_rank() : 0u;        // 0 = leader of the pair
   int32_t first_tile = kPair ? int32_t(blockIdx.x >> 1) : int32_t(blockIdx.x);
   int32_t tile_step = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
@@ -600,7 +693,13 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
   if (kPair) cluster_sync_all();          // the peer's barriers exist before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = aux->tmem_base;
-  if (kTiming && p.timing && threadIdx.x == 0) p.timing[blockIdx.x * kTimingSlots + 9] = global_timer_ns();
+  // Everything above touched only this CTA's shared memory, TMEM and the kernel parameters.  From here on
+  // global memory is read and written: the kernel in front of this one must have completed.
+  griddep_wait();
+  if (kTiming && p.timing && threadIdx.x == 0) {
+    p.timing[blockIdx.x * kTimingSlots + 9] = global_timer_ns();
+    p.timing[blockIdx.x * kTimingSlots + 8] = t_entry;
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -781,7 +880,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
     uint32_t* pending_flag = nullptr;     // peer-reduce, lane 0: flag of the pushed tile whose stores are still in flight
     uint4* const store_stage = reinterpret_cast<uint4*>(after_stages + ew * kStoreStageBytes);   // 1024-byte aligned
     uint32_t amax_bits = 0;
-    long long ep_wait = 0, ep_busy = 0;
+    long long ep_wait = 0, ep_busy = 0, ep_ld = 0, ep_math = 0, ep_flush = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -907,6 +1006,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       const long long te1 = (kTiming && p.timing) ? clock64() : 0;
       ep_wait += te1 - te0;
+      if (kTiming && p.timing && warp == 2 && lane == 0) p.timing[blockIdx.x * kTimingSlots + 14] = global_timer_ns();   // last accumulator complete
       if (!ok) break;
       (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);   // every lane observes the completed phase
       tc_fence_after_sync();
@@ -931,49 +1031,64 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       const uint32_t taddr =
           tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kBN + col_half * kColsPerEpilogueWarp);
 
-      // kChunk columns at a time, two chunks per loop trip: the load of one chunk is in flight
-      // while the other is processed.
-      uint32_t ra[kChunk], rb[kChunk];
-      tmem_ld_32x16(taddr, ra);
+      // Converted output goes through the warp's 32 x 64-byte stage and leaves in 64-byte row segments (direct
+      // 16-byte stores per lane only when D's rows are not 16-byte aligned).  One stage holds `group` chunks.
+      const int out_elt = (p.d_dtype == kF8E4M3FN || p.d_dtype == kF8E5M2) ? 1 : (p.d_dtype == kF32 ? 4 : 2);
+      uint4* const out_stage = (!kReduce && p.vec_store_ok && p.d != nullptr && item.mode != 1)
+                                   ? reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(vecs + 1) + ew * kOutStageBytes) : nullptr;
+      const int group = 4 / out_elt;
+      const int64_t warp_row0 = row - lane, out_row_bytes = p.n * out_elt;
+      const int32_t rows_valid = int32_t(max(int64_t(0), min(int64_t(32), p.m - (row_in_batch - lane))));
+      auto flush_group = [&](int ci) {         // after chunk ci: the group it completes, if any, goes out
+        if (out_stage == nullptr || ((ci + 1) % group) != 0) return;
+        const int64_t gcol0 = col_base + int64_t(ci + 1 - group) * kChunk;
+        if (gcol0 < p.n) stage_flush(p, out_stage, lane, warp_row0, rows_valid, gcol0 * out_elt, out_row_bytes);
+      };
+
+      // kChunk columns at a time; the load of the next chunk is in flight while this one is processed.  One copy of
+      // the loop body (the chunk just loaded is moved into `cur`) keeps the epilogue's code small: eight warps run
+      // it and it has to stay in the instruction cache.
+      constexpr int kChunks = kColsPerEpilogueWarp / kChunk;
+      uint32_t cur[kChunk], nxt[kChunk];
+      tmem_ld_32x16(taddr, nxt);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kColsPerEpilogueWarp; c0 += 2 * kChunk) {
-        tmem_ld_wait_16(ra);
-        tmem_ld_32x16(taddr + c0 + kChunk, rb);
-        int64_t col0 = col_base + c0;
+      for (int ci = 0; ci < kChunks; ++ci) {
+        const int c0 = ci * kChunk;
+        const long long tl0 = (kTiming && p.timing) ? clock64() : 0;
+        tmem_ld_wait_16(nxt);
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) cur[i] = nxt[i];
+        if (ci + 1 < kChunks) tmem_ld_32x16(taddr + c0 + kChunk, nxt);
+        const long long tl1 = (kTiming && p.timing) ? clock64() : 0;
+        ep_ld += tl1 - tl0;
+        const int64_t col0 = col_base + c0;
         if (!kReduce && item.mode == 1) {
-          sk_dump(ra, c0);
+          sk_dump(cur, c0);
         } else if (col0 < p.n && row_ok) {
           const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
           if constexpr (kReduce) {
-            if ((c0 & 32) == 0) {          // a new 64-column group: the bulk store of the previous one must have read the stage
+            if ((ci & 3) == 0) {           // a new 64-column group: the bulk store of the previous one must have read the stage
               if (lane == 0) tma_store_wait_read<0>();
               __syncwarp();
             }
-            reduce_chunk(p, ra, scale, my_rank, blk, own_row, rows_per_block, col0,
-                         store_stage + lane * 8, (c0 >> 3) & 7, lane);
+            reduce_chunk(p, cur, scale, my_rank, blk, own_row, rows_per_block, col0, store_stage + lane * 8, (ci * 2) & 7, lane);
+          } else {
+            finish_chunk<kInt8>(p, cur, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0, &amax_bits,
+                                out_stage, lane, (ci % group) * out_elt);
           }
-          else finish_chunk<kInt8>(p, ra, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0, colscale_w + c0,
-                                   &amax_bits);
         }
-        tmem_ld_wait_16(rb);
-        if (c0 + 2 * kChunk < kColsPerEpilogueWarp) tmem_ld_32x16(taddr + c0 + 2 * kChunk, ra);
-        col0 += kChunk;
-        if (!kReduce && item.mode == 1) {
-          sk_dump(rb, c0 + kChunk);
-        } else if (col0 < p.n && row_ok) {
-          const int32_t ncols = static_cast<int32_t>(min(int64_t(kChunk), p.n - col0));
-          if constexpr (kReduce) reduce_chunk(p, rb, scale, my_rank, blk, own_row, rows_per_block, col0,
-                                              store_stage + lane * 8, ((c0 >> 3) & 7) + 2, lane);
-          else finish_chunk<kInt8>(p, rb, row, col0, ncols, scale, d_scale, row_scale, bias_w + c0 + kChunk,
-                                   colscale_w + c0 + kChunk, &amax_bits);
-        }
+        const long long tl2 = (kTiming && p.timing) ? clock64() : 0;
+        ep_math += tl2 - tl1;
         if constexpr (kReduce) {
-          if ((c0 & 32) != 0) {            // 64 columns staged: write them out as full lines
-            const int64_t warp_row0 = row - lane;
-            flush_store_stage(p, rmaps, store_stage, my_rank, blk, warp_row0, own_row - lane, rows_per_block,
-                              col_base + c0 - 32, lane);
+          if ((ci & 3) == 3) {             // 64 columns staged: write them out as full lines
+            const int64_t warp_row0r = row - lane;
+            flush_store_stage(p, rmaps, store_stage, my_rank, blk, warp_row0r, own_row - lane, rows_per_block,
+                              col_base + c0 - 3 * kChunk, lane);
           }
+        } else {
+          flush_group(ci);
         }
+        if (kTiming && p.timing) ep_flush += clock64() - tl2;
       }
       if constexpr (kReduce) {
         // Lane 0 issued this tile's bulk stores (two groups).  Waiting for them here would put an
@@ -1034,9 +1149,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       __syncwarp();
     }
     if (kTiming && p.timing && warp == 2 && lane == 0) {
+      p.timing[blockIdx.x * kTimingSlots + 15] = global_timer_ns();        // column loops done, before the amax hand-shake
       p.timing[blockIdx.x * kTimingSlots + 5] = ep_wait;
       p.timing[blockIdx.x * kTimingSlots + 6] = ep_busy;
-      p.timing[blockIdx.x * kTimingSlots + 12] = global_timer_ns();
+      p.timing[blockIdx.x * kTimingSlots + 16] = ep_ld;
+      p.timing[blockIdx.x * kTimingSlots + 17] = ep_math;
+      p.timing[blockIdx.x * kTimingSlots + 18] = ep_flush;
     }
     if (!kInt8 && p.amax != nullptr) {
       // The bit pattern of a non-negative float orders like the float; NaN patterns sit above
@@ -1067,6 +1185,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         atomicMax(reinterpret_cast<unsigned int*>(p.amax), amax_bits);
       }
     }
+    if (kTiming && p.timing && warp == 2 && lane == 0) p.timing[blockIdx.x * kTimingSlots + 12] = global_timer_ns();
   }
 
   tc_fence_before_sync();
@@ -1109,13 +1228,17 @@ cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, cons
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = DenseSmemBytes<kPair, kReduce>();
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kPair ? 2 : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // Programmatic dependent launch: this kernel's set-up (barriers, TMEM, descriptor prefetch) overlaps the tail
+  // of the kernel in front of it; its griddep_wait() orders every global access behind that kernel's end.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = kReduce ? 1 : 2;       // the peer-reduce form waits on other GPUs: it keeps plain stream order
   return cudaLaunchKernelEx(&cfg, dense_gemm_kernel<kInt8, kPair, kReduce>, ta, tb, p, rmaps ? *rmaps : no_maps);
 }
 

@@ -268,6 +268,14 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* smem_ptr, uint32_t ra
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(smem_ptr)), "r"(rank));
   return a;
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start (set itself up) before the kernel in front of it in the stream has finished;
+// griddep_wait() then blocks until that kernel has completed and its memory operations are visible,
+// so it must come before the first access to global memory another kernel may have written.
+// griddep_launch_dependents() lets the kernel BEHIND this one be scheduled as this one's CTAs retire.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
