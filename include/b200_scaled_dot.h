@@ -34,7 +34,8 @@ enum {
   B200SD_F32 = 11,
   B200SD_BF16 = 16,
   B200SD_F8E5M2 = 19,
-  B200SD_F8E4M3FN = 20
+  B200SD_F8E4M3FN = 20,
+  B200SD_F8E8M0FNU = 33          /* the scale type of MX block-scaled operands */
 };
 
 /* GemmBackendConfig.Epilogue, with the enum's own (0-based) numbers
@@ -130,6 +131,34 @@ typedef struct B200SD_DotS8 {
   int64_t batch_count;           /* > 1: leading batch dimension of A, B, D and acc_out; the scale vectors are shared */
 } B200SD_DotS8;
 
+/* Arguments of one MX block-scaled dot (`scale_mode = BLOCK_SCALING` of GemmBackendConfig):
+ *
+ *   D[b,m,n] = alpha * sum_k  A[b,m,k] * 2^(SA[b,m,k/32] - 127)  *  B[b,n,k] * 2^(SB[b,n,k/32] - 127)
+ *
+ * The operand list is that of `ThunkEmitter::EmitCublasLtMatmulMx`
+ * (xla/service/gpu/thunk_emitter.cc:939-988): a, b, a_scale, b_scale and one result (plus the
+ * workspace XLA appends, which this kernel does not need); no bias, no matrix C, no d_scale, no
+ * amax.  Layout is the one `__op$block_scaled_dot` fixes
+ * (xla/backends/gpu/transforms/block_scaling_rewriter.h:30-77): the contracting dimension is
+ * the minor one of BOTH operands (A is [m,k], B is [n,k]), an optional batch dimension is the
+ * major one, and each scale tensor is row-major [rows, k/32] of f8e8m0fnu -- the plain HLO
+ * operand, not a library-specific swizzled form.  k must be a multiple of 32; m and n are free.
+ */
+typedef struct B200SD_BlockScaledDotMx {
+  size_t struct_size;            /* sizeof(B200SD_BlockScaledDotMx) */
+  const void* a;                 /* [batch, m, k] FP8 */
+  const void* b;                 /* [batch, n, k] FP8 */
+  const void* a_scale;           /* [batch, m, k/32] f8e8m0fnu */
+  const void* b_scale;           /* [batch, n, k/32] f8e8m0fnu */
+  void* d;                       /* [batch, m, n] */
+  int64_t m, n, k;
+  int32_t a_dtype, b_dtype;      /* B200SD_F8E4M3FN or B200SD_F8E5M2 */
+  int32_t scale_dtype;           /* B200SD_F8E8M0FNU */
+  int32_t d_dtype;               /* F32, BF16 or F16 */
+  float alpha;                   /* GemmBackendConfig.alpha_real; XLA writes 1 */
+  int32_t batch_count;           /* 0 or 1: plain matrices */
+} B200SD_BlockScaledDotMx;
+
 /* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the
  * first launch on a device; call it yourself before capturing a stream into a CUDA graph. */
 int b200sd_init_device(char* err, size_t err_len);
@@ -139,6 +168,11 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
 
 /* Replaces the same call for s8 x s8 -> s32 (type table at cuda_blas_lt.cc:444-445). */
 int b200sd_dot_s8(const B200SD_DotS8* args, void* cuda_stream, char* err, size_t err_len);
+
+/* Replaces the library call behind `__cublas$lt$matmul$mx` (CublasLtMatmulThunk built by
+ * xla/service/gpu/thunk_emitter.cc:939-988 with GemmConfig::scale_mode == BLOCK_SCALING). */
+int b200sd_block_scaled_dot_mx(const B200SD_BlockScaledDotMx* args, void* cuda_stream, char* err, size_t err_len);
+int b200sd_check_block_scaled_dot_mx(const B200SD_BlockScaledDotMx* args, char* err, size_t err_len);
 
 /* Validate everything about a call except the pointer values (which may be NULL): types, shapes,
  * epilogue, the supported type table (`TypesAreSupportedByCublasLt`,
@@ -301,7 +335,7 @@ int b200sd_rewrite_hlo(const char* hlo_text, char* out_hlo, size_t out_hlo_len, 
 /* ---- XLA FFI handlers (typed FFI, api_version = API_VERSION_TYPED_FFI) -----------------------
  * Signature: XLA_FFI_Error* (*)(XLA_FFI_CallFrame*), xla/ffi/api/c_api.h:517.  Declared with
  * void* here so that this header does not depend on XLA's.  Register them under the custom-call
- * targets "b200$scaled_dot$f8" and "b200$dot$s8" (platform "CUDA"); they accept the operand and
+ * targets "b200$scaled_dot$f8", "b200$dot$s8" and "b200$block_scaled_dot$mx" (platform "CUDA"); the first two accept the operand and
  * result arrangements of `__cublas$lt$matmul$f8` (xla/service/gpu/thunk_emitter.cc:776-862).
  * The *_instantiate / *_initialize symbols are the optional stages of the handler bundle
  * (c_api.h:520-526). */
@@ -312,9 +346,14 @@ void* b200sd_ffi_scaled_dot_f8_initialize(void* call_frame);
 void* b200sd_ffi_dot_s8(void* call_frame);
 void* b200sd_ffi_dot_s8_instantiate(void* call_frame);
 void* b200sd_ffi_dot_s8_initialize(void* call_frame);
+/* Target "b200$block_scaled_dot$mx": operands (a, b, a_scale, b_scale), results (D, [workspace]) -- the
+ * arrangement of `__cublas$lt$matmul$mx` (xla/service/gpu/thunk_emitter.cc:939-988). */
+void* b200sd_ffi_block_scaled_dot_mx(void* call_frame);
+void* b200sd_ffi_block_scaled_dot_mx_instantiate(void* call_frame);
+void* b200sd_ffi_block_scaled_dot_mx_initialize(void* call_frame);
 #endif
 
-/* Registers both bundles with the given `const XLA_FFI_Api*` (what XLA_FFI_REGISTER_HANDLER does,
+/* Registers the three bundles with the given `const XLA_FFI_Api*` (what XLA_FFI_REGISTER_HANDLER does,
  * xla/ffi/api/api.h:2881-2893).  Returns 0 or an error code. */
 int b200sd_ffi_register(const void* xla_ffi_api, char* err, size_t err_len);
 

@@ -43,6 +43,7 @@ import numpy as np
 # XLA PrimitiveType numbering (xla/ffi/api/c_api.h:233-266 mirrors it).
 # ----------------------------------------------------------------------------
 S8, S32, F16, F32, BF16, F8E5M2, F8E4M3FN = 2, 4, 10, 11, 16, 19, 20
+F8E8M0FNU = 33
 
 # GemmBackendConfig.Epilogue values (xla/service/gpu/backend_configs.proto:106-117).
 EPI_DEFAULT, EPI_BIAS, EPI_RELU, EPI_BIAS_RELU = 0, 1, 2, 3
@@ -134,6 +135,100 @@ def fp8_encode(x: np.ndarray, kind: str = "e4m3fn") -> np.ndarray:
         code = np.where(over | inf, inf_code, code)
         code = np.where(nan, inf_code | (1 << (mbits - 1)), code)  # quiet NaN 0x7e
     return (code.astype(np.uint8) | sign).astype(np.uint8)
+
+
+# ----------------------------------------------------------------------------
+# f8e8m0fnu: the scale type of MX block-scaled operands.  Eight exponent bits and nothing else:
+# code c is 2^(c-127), 0xff is NaN; no zero, no sign, no infinity.
+# Pinned by xla/tests/convert_test.cc:2114-2152 (ConvertF32F8e8m0fnuRoundtrip).
+# ----------------------------------------------------------------------------
+def e8m0_decode(codes: np.ndarray) -> np.ndarray:
+    """uint8 code points -> f32 values (exact; code 0 is the f32 denormal 2^-127)."""
+    c = np.asarray(codes, dtype=np.uint8).astype(np.int64)
+    v = np.ldexp(np.float64(1.0), np.minimum(c, 254) - 127).astype(np.float32)
+    return np.where(c == 255, np.float32(np.nan), v).astype(np.float32)
+
+
+def e8m0_encode(x: np.ndarray) -> np.ndarray:
+    """f32 -> f8e8m0fnu code points.  Zero, negative values, infinities and NaN become NaN (0xff);
+    a positive value rounds to the nearest power of two (a mantissa of exactly 1.5 rounds up, there
+    being no even neighbour to prefer); anything that rounds above 2^127 is NaN.  Below 2^-126 the
+    destination has one step of 2^-126: the value rounds, ties to even, to 2^-126 (code 1) or to
+    code 0."""
+    x = np.asarray(x, dtype=np.float32)
+    a = x.astype(np.float64)
+    bad = ~np.isfinite(a) | (a <= 0)
+    a = np.where(bad, 1.0, a)
+    m, e = np.frexp(a)                       # a = m * 2^e, m in [0.5, 1)
+    e = e - 1                                # a = (2m) * 2^e, 2m in [1, 2)
+    e = np.where(2.0 * m >= 1.5, e + 1, e)
+    tiny = a < 2.0 ** -126
+    q = np.rint(a / 2.0 ** -126)             # 0 or 1, ties to even
+    code = np.where(tiny, q, e + 127)
+    code = np.where(bad | (code > 254), 255, code)
+    return code.astype(np.uint8)
+
+
+MX_BLOCK = 32
+
+
+def mx_dequantize(codes: np.ndarray, scale_codes: np.ndarray, kind: str = "e4m3fn",
+                  out_dtype=np.float32) -> np.ndarray:
+    """One operand of a block-scaled dot as the reference expands it
+    (xla/backends/gpu/transforms/block_scaling_rewriter.cc:194-220, BuildDequantize): the input
+    and the scale are each converted to the result type, the scale is broadcast over its block
+    along the minor (contracting) dimension, and the two are multiplied.  `codes` is
+    [..., rows, k] FP8 code points, `scale_codes` is [..., rows, k / block] f8e8m0fnu code points;
+    the block size is the ratio of the two minor extents (32 for MX)."""
+    codes = np.asarray(codes, dtype=np.uint8)
+    scale_codes = np.asarray(scale_codes, dtype=np.uint8)
+    k, kb = codes.shape[-1], scale_codes.shape[-1]
+    assert codes.shape[:-1] == scale_codes.shape[:-1] and kb > 0 and k % kb == 0, (codes.shape, scale_codes.shape)
+    block = k // kb
+    v = fp8_decode(codes, kind).astype(out_dtype)
+    s = np.repeat(e8m0_decode(scale_codes).astype(out_dtype), block, axis=-1)
+    with np.errstate(over="ignore", invalid="ignore", under="ignore"):
+        return (v * s).astype(out_dtype)
+
+
+def block_scaled_dot(a, b, a_scale, b_scale, *, a_kind="e4m3fn", b_kind="e4m3fn", out_dtype=F32,
+                     alpha=1.0):
+    """`__op$block_scaled_dot` / `__cublas$lt$matmul$mx`
+    (xla/backends/gpu/transforms/block_scaling_rewriter.h:30-77, xla/service/gpu/thunk_emitter.cc:939-988):
+
+        D[b, m, n] = sum_k dequant(a)[b, m, k] * dequant(b)[b, n, k]
+
+    with both operands stored contracting-dimension-minor and an optional leading batch dimension.
+    The reference's expansion (block_scaling_rewriter.cc:222-262) dequantizes into the RESULT type
+    and then takes an ordinary dot, whose products the interpreter accumulates in f32
+    (hlo_evaluator_typed_visitor.h:1271-1340).  Returns D in the spelling of cast_output()."""
+    a = np.asarray(a, dtype=np.uint8)
+    b = np.asarray(b, dtype=np.uint8)
+    np_type = {F32: np.float32, F16: np.float16, BF16: None}[out_dtype]
+    if np_type is None:      # bf16: dequantized values rounded to bf16, then widened for the dot
+        a_dq = bf16_bits_to_f32(f32_to_bf16_bits(mx_dequantize(a, a_scale, a_kind)))
+        b_dq = bf16_bits_to_f32(f32_to_bf16_bits(mx_dequantize(b, b_scale, b_kind)))
+    else:
+        a_dq = mx_dequantize(a, a_scale, a_kind, np_type).astype(np.float32)
+        b_dq = mx_dequantize(b, b_scale, b_kind, np_type).astype(np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        x = np.matmul(a_dq, np.swapaxes(b_dq, -1, -2), dtype=np.float32)
+        if alpha != 1.0:
+            x = (x * np.float32(alpha)).astype(np.float32)
+    return cast_output(x, out_dtype)
+
+
+def make_mx_operands(seed: int, m: int, n: int, k: int, batch: int = 0, kind_a="e4m3fn", kind_b="e4m3fn",
+                     scale_lo: int = 119, scale_hi: int = 135):
+    """Seeded MX operands: FP8 codes of N(0,1) values scaled into the format's range and one
+    f8e8m0fnu exponent per 32 values drawn uniformly from [scale_lo, scale_hi] (2^-8 .. 2^8)."""
+    rng = np.random.default_rng(seed)
+    lead = (batch,) if batch > 0 else ()
+    a = fp8_encode(np.clip(rng.standard_normal(lead + (m, k), dtype=np.float32) * 4, -400, 400), kind_a)
+    b = fp8_encode(np.clip(rng.standard_normal(lead + (n, k), dtype=np.float32) * 4, -400, 400), kind_b)
+    sa = rng.integers(scale_lo, scale_hi + 1, size=lead + (m, k // MX_BLOCK), dtype=np.uint8)
+    sb = rng.integers(scale_lo, scale_hi + 1, size=lead + (n, k // MX_BLOCK), dtype=np.uint8)
+    return a, b, sa, sb
 
 
 def fp8_encode_saturating(x: np.ndarray, kind: str = "e4m3fn") -> np.ndarray:

@@ -7,8 +7,9 @@ never needs the reference tree at run time.
 Sources, read as text:
   * xla/tests/convert_test.cc -- the `{input, expected_roundtrip}` tables of
     ConvertF16F8e5m2Roundtrip, ConvertF32F8e5m2Roundtrip,
-    ConvertF16F8e4m3fnRoundtrip and ConvertF32F8e4m3fnRoundtrip (C hex-float
-    literals, `nan`, `inf`).
+    ConvertF16F8e4m3fnRoundtrip, ConvertF32F8e4m3fnRoundtrip and
+    ConvertF32F8e8m0fnuRoundtrip (the block-scale type) (C hex-float literals,
+    `nan`, `inf`).
   * xla/stream_executor/cuda/cuda_blas_lt_test.cc -- the S8S8S32 / S8S8F32
     known answer: m = n = k = 32, all-ones operands, every output == k.
   * xla/service/gpu/backend_configs.proto -- `enum Epilogue { ... }` of GemmBackendConfig, and
@@ -95,9 +96,10 @@ def main():
         ("ConvertF32F8e5m2Roundtrip", "e5m2", "f32"),
         ("ConvertF16F8e4m3fnRoundtrip", "e4m3fn", "f16"),
         ("ConvertF32F8e4m3fnRoundtrip", "e4m3fn", "f32"),
+        ("ConvertF32F8e8m0fnuRoundtrip", "e8m0fnu", "f32"),
     ]:
         rows = table_of(src, name)
-        assert len(rows) >= 15, (name, len(rows))
+        assert len(rows) >= 14, (name, len(rows))
         out["tables"][name] = {
             "fp8": kind,
             "via": via,

@@ -88,7 +88,7 @@ def test_struct_layouts_match_the_header():
 def test_registration_and_metadata():
     _native.ensure_registered()
     traits, minor = C.c_uint32(0), C.c_int(0)
-    for target in (b"b200$scaled_dot$f8", b"b200$dot$s8"):
+    for target in (b"b200$scaled_dot$f8", b"b200$dot$s8", b"b200$block_scaled_dot$mx"):
         assert _native.mock.mockffi_find_handler(target, b"CUDA", C.byref(traits), C.byref(minor)) == 1
         assert traits.value & 1           # XLA_FFI_HANDLER_TRAITS_COMMAND_BUFFER_COMPATIBLE
         assert 1 <= minor.value <= 4      # API versions the XLA runtime accepts (ffi_registry.cc:47-65)
@@ -217,6 +217,39 @@ def test_int8_frames():
         assert e.value.code == code
 
 
+def test_block_scaled_frames():
+    """`b200$block_scaled_dot$mx` takes what ThunkEmitter::EmitCublasLtMatmulMx takes
+    (xla/service/gpu/thunk_emitter.cc:939-988): exactly a, b, a_scale, b_scale and (D, [workspace]); shapes as
+    `__op$block_scaled_dot` fixes them (block_scaling_rewriter.h:30-77)."""
+    from xla_b200.scaled_dot import BlockScaledDotCall, F8E8M0FNU
+    E8 = F8E8M0FNU
+    ok = [
+        ([Buffer(F8E4M3FN, (8, 128)), Buffer(F8E4M3FN, (16, 128)), Buffer(E8, (8, 4)), Buffer(E8, (16, 4))], [Buffer(F32, (8, 16))]),
+        ([Buffer(F8E4M3FN, (4, 16, 256)), Buffer(F8E5M2, (4, 16, 256)), Buffer(E8, (4, 16, 8)), Buffer(E8, (4, 16, 8))],
+         [Buffer(BF16, (4, 16, 16)), Buffer(S8, (1 << 20,))]),
+        ([Buffer(F8E5M2, (200, 96)), Buffer(F8E4M3FN, (77, 96)), Buffer(E8, (200, 3)), Buffer(E8, (77, 3))], [Buffer(F16, (200, 77))]),
+    ]
+    for ops, res in ok:
+        BlockScaledDotCall(ops, res).instantiate()
+    a, b = Buffer(F8E4M3FN, (8, 128)), Buffer(F8E4M3FN, (16, 128))
+    sa, sb, d = Buffer(E8, (8, 4)), Buffer(E8, (16, 4)), Buffer(F32, (8, 16))
+    for ops, res, code in [
+        ([a, b, sa], [d], 3),                                                     # operand count
+        ([a, b, sa, sb, Buffer(F32, ())], [d], 3),                                # a global scale is not part of the $mx call
+        ([a, b, sa, sb], [d, Buffer(F32, ()), Buffer(S8, (16,))], 3),             # no amax result
+        ([a, b, Buffer(E8, (8, 8)), Buffer(E8, (16, 8))], [d], 3),                # block size 16
+        ([a, Buffer(F8E4M3FN, (16, 256)), sa, Buffer(E8, (16, 8))], [d], 3),      # K differs
+        ([a, b, Buffer(F8E4M3FN, (8, 4)), Buffer(F8E4M3FN, (16, 4))], [d], 12),   # e4m3 scales (NVFP4-style) not implemented
+        ([Buffer(S8, (8, 128)), b, sa, sb], [d], 12),                             # element type
+        ([a, b, sa, sb], [Buffer(F8E4M3FN, (8, 16))], 3),                         # result type
+        ([a, b, sa, sb], [Buffer(F32, (8, 8))], 3),                               # result shape
+        ([Buffer(F8E4M3FN, (8, 100)), Buffer(F8E4M3FN, (16, 100)), Buffer(E8, (8, 3)), Buffer(E8, (16, 3))], [d], 3),   # K % 32
+    ]:
+        with pytest.raises(XlaFfiError) as e:
+            BlockScaledDotCall(ops, res).instantiate()
+        assert e.value.code == code, (ops, e.value)
+
+
 def test_unknown_target_and_wrong_stage():
     with pytest.raises(XlaFfiError) as e:
         FfiCall("__cublas$lt$matmul$f8", [], [], {}).instantiate()
@@ -282,7 +315,8 @@ def test_ctypes_mirrors_match_the_header_as_a_c_compiler_sees_it(tmp_path):
     if gcc is None:
         pytest.skip("no C compiler")
     pairs = [("B200SD_ScaledDotF8", _native.ScaledDotF8Args), ("B200SD_DotS8", _native.DotS8Args),
-             ("B200SD_Progress", _native.ProgressArgs), ("B200SD_PeerReduce", _native.PeerReduceArgs)]
+             ("B200SD_Progress", _native.ProgressArgs), ("B200SD_PeerReduce", _native.PeerReduceArgs),
+             ("B200SD_BlockScaledDotMx", _native.BlockScaledDotMxArgs)]
     lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "b200_scaled_dot.h"', "int main(void) {"]
     for cname, mirror in pairs:
         lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')

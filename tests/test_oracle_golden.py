@@ -64,6 +64,41 @@ def test_reference_roundtrip_tables(golden, c_oracle, table):
                 assert g == w, (table, src, g, w)        # ErrorSpec(0.): value equality (-0 == 0)
 
 
+def test_e8m0_roundtrip_table(golden):
+    """xla/tests/convert_test.cc:2114-2152 (ConvertF32F8e8m0fnuRoundtrip): the block-scale type."""
+    t = golden["tables"]["ConvertF32F8e8m0fnuRoundtrip"]
+    assert t["fp8"] == "e8m0fnu" and len(t["cases"]) >= 14
+    for src, want in t["cases"]:
+        x, w = np.float32(_val(src)), _val(want)
+        g = float(o.e8m0_decode(o.e8m0_encode(np.array([x], np.float32)))[0])
+        assert (math.isnan(w) and math.isnan(g)) or g == w, (src, g, w)
+    # ConvertF8e8m0fnuRoundtripExhaustive (:2154-2172): every code point survives f8 -> f32 -> f8.
+    codes = np.arange(256, dtype=np.uint8)
+    assert (o.e8m0_encode(o.e8m0_decode(codes)) == codes).all()
+    assert o.e8m0_decode(np.array([0, 127, 254], np.uint8)).tolist() == [2.0 ** -127, 1.0, 2.0 ** 127]
+
+
+def test_block_scaled_dot_is_the_expanded_hlo():
+    """block_scaling_rewriter.cc:194-262: dequantize(a) . dequantize(b)^T with the scale broadcast over
+    blocks of 32 along K; checked against a literal loop on a small case and against hand values."""
+    a, b, sa, sb = o.make_mx_operands(9, 5, 3, 64, batch=2)
+    got = o.block_scaled_dot(a, b, sa, sb)
+    av, bv = o.fp8_decode(a).astype(np.float64), o.fp8_decode(b).astype(np.float64)
+    for bt in range(2):
+        for i in range(5):
+            for j in range(3):
+                acc = 0.0
+                for kk in range(64):
+                    acc += av[bt, i, kk] * 2.0 ** (int(sa[bt, i, kk // 32]) - 127) * bv[bt, j, kk] * 2.0 ** (int(sb[bt, j, kk // 32]) - 127)
+                assert abs(got[bt, i, j] - acc) <= 1e-5 * max(1.0, abs(acc))
+    one = o.fp8_encode(np.array([1.0], np.float32))[0]
+    d = o.block_scaled_dot(np.full((1, 64), one, np.uint8), np.full((1, 64), one, np.uint8),
+                           np.array([[128, 126]], np.uint8), np.array([[127, 130]], np.uint8))
+    assert d.tolist() == [[32 * 2.0 + 32 * 0.5 * 8.0]]
+    assert np.isnan(o.block_scaled_dot(np.full((1, 32), one, np.uint8), np.full((1, 32), one, np.uint8),
+                                       np.array([[255]], np.uint8), np.array([[127]], np.uint8))).all()
+
+
 @pytest.mark.parametrize("kind", ["e4m3fn", "e5m2"])
 def test_exhaustive_roundtrips(c_oracle, kind):
     """ConvertF8e4m3fnRoundtripExhaustive{,2,3} / the e5m2 twins: all 256 code points survive

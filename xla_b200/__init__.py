@@ -15,8 +15,10 @@ from .scaled_dot import (  # noqa: F401
     GemmBackendConfig,
     ScaledDotCall,
     Int8DotCall,
+    BlockScaledDotCall,
     cublas_lt_matmul_f8,
     cublas_lt_matmul_s8,
+    cublas_lt_matmul_mx,
     device_status,
     launch_count,
     load_config_table,

@@ -63,6 +63,20 @@ class DotS8Args(C.Structure):
     ]
 
 
+class BlockScaledDotMxArgs(C.Structure):
+    """B200SD_BlockScaledDotMx of include/b200_scaled_dot.h."""
+
+    _fields_ = [
+        ("struct_size", C.c_size_t),
+        ("a", C.c_void_p), ("b", C.c_void_p), ("a_scale", C.c_void_p), ("b_scale", C.c_void_p),
+        ("d", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("a_dtype", C.c_int32), ("b_dtype", C.c_int32), ("scale_dtype", C.c_int32), ("d_dtype", C.c_int32),
+        ("alpha", C.c_float),
+        ("batch_count", C.c_int32),
+    ]
+
+
 class ProgressArgs(C.Structure):
     """B200SD_Progress of include/b200_scaled_dot.h."""
 
@@ -96,6 +110,8 @@ product.b200sd_scaled_dot_f8.argtypes = [C.POINTER(ScaledDotF8Args), C.c_void_p,
 product.b200sd_dot_s8.argtypes = [C.POINTER(DotS8Args), C.c_void_p, *_ERR]
 product.b200sd_check_scaled_dot_f8.argtypes = [C.POINTER(ScaledDotF8Args), *_ERR]
 product.b200sd_check_dot_s8.argtypes = [C.POINTER(DotS8Args), *_ERR]
+product.b200sd_block_scaled_dot_mx.argtypes = [C.POINTER(BlockScaledDotMxArgs), C.c_void_p, *_ERR]
+product.b200sd_check_block_scaled_dot_mx.argtypes = [C.POINTER(BlockScaledDotMxArgs), *_ERR]
 product.b200sd_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
 product.b200sd_workspace_bytes.restype = C.c_size_t
 product.b200sd_select_kernel.argtypes = [C.c_int64, C.c_int64, C.c_int64]

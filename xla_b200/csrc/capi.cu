@@ -24,6 +24,7 @@ __device__ uint32_t g_device_status;
 
 Status InitDenseKernels();
 Status InitSkinnyKernels();
+Status InitMxKernels();
 
 namespace {
 
@@ -87,6 +88,7 @@ Status InitDevice(int device) {
     }
     st.init_status = InitDenseKernels();
     if (st.init_status.ok()) st.init_status = InitSkinnyKernels();
+    if (st.init_status.ok()) st.init_status = InitMxKernels();
     // A persisted tuning result named by the environment is loaded with the first device (a file
     // that cannot be read or parsed makes the first call fail loudly instead of being ignored).
     static std::once_flag table_once;
@@ -303,6 +305,39 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
   LaunchStats stats;
   st = kernel == B200SD_KERNEL_SKINNY ? LaunchSkinny(g, static_cast<cudaStream_t>(cuda_stream), &stats)
                                       : LaunchDense(g, static_cast<cudaStream_t>(cuda_stream), &stats, kernel);
+  if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
+  return CopyStatus(st, err, err_len);
+}
+
+namespace {
+Status ConvertMx(const B200SD_BlockScaledDotMx& a, MxProblem* g) {
+  if (a.struct_size < sizeof(B200SD_BlockScaledDotMx)) return Status::Error(kInvalidArgument, "B200SD_BlockScaledDotMx.struct_size is smaller than this library's struct");
+  g->m = a.m; g->n = a.n; g->k = a.k;
+  g->batch = a.batch_count > 1 ? a.batch_count : 1;
+  g->a_dtype = a.a_dtype; g->b_dtype = a.b_dtype;
+  g->scale_dtype = a.scale_dtype;
+  g->a = a.a; g->b = a.b;
+  g->a_scale = a.a_scale; g->b_scale = a.b_scale;
+  g->alpha = a.alpha;
+  g->d = a.d; g->d_dtype = a.d_dtype;
+  if (a.batch_count < 0) return Status::Error(kInvalidArgument, "batch_count must not be negative");
+  return ValidateMx(*g);
+}
+}  // namespace
+
+int b200sd_check_block_scaled_dot_mx(const B200SD_BlockScaledDotMx* args, char* err, size_t err_len) {
+  if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
+  MxProblem g;
+  return CopyStatus(ConvertMx(*args, &g), err, err_len);
+}
+
+int b200sd_block_scaled_dot_mx(const B200SD_BlockScaledDotMx* args, void* cuda_stream, char* err, size_t err_len) {
+  if (args == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "args is null"), err, err_len);
+  MxProblem g;
+  Status st = ConvertMx(*args, &g);
+  if (!st.ok()) return CopyStatus(st, err, err_len);
+  LaunchStats stats;
+  st = LaunchMx(g, static_cast<cudaStream_t>(cuda_stream), &stats);
   if (st.ok()) g_launches.fetch_add(stats.launches, std::memory_order_relaxed);
   return CopyStatus(st, err, err_len);
 }

@@ -1289,6 +1289,24 @@ Status MakeBatchedByteMatrixMap(CUtensorMap* map, const void* base, int64_t batc
   return Status::Ok();
 }
 
+// The same 3-D view without a shared-memory swizzle: the box lands row after row, box_cols bytes each.
+Status MakeBatchedPlainByteMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
+                               uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn encode = GetEncodeTiled();
+  if (encode == nullptr) return Status::Error(kInternal, "cuTensorMapEncodeTiled is not available from this driver");
+  if (cols % 16 != 0 || box_cols % 16 != 0) return Status::Error(kInvalidArgument, "the minor dimension and the box width must be multiples of 16 bytes");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return Status::Error(kInvalidArgument, "base address must be 16-byte aligned");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows) * static_cast<cuuint64_t>(cols)};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Status::Error(kInternal, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
+  return Status::Ok();
+}
+
 Status InitDenseKernels() {
   int device = 0;
   cudaGetDevice(&device);

@@ -307,7 +307,88 @@ ffi::Error DotS8Execute(cudaStream_t stream, ffi::RemainingArgs operands, ffi::R
   return FromCode(b200sd_dot_s8(&a, stream, msg, sizeof(msg)), msg);
 }
 
+// ---- b200$block_scaled_dot$mx --------------------------------------------------------------
+// Operands (a, b, a_scale, b_scale), results (D, [workspace]): the call ThunkEmitter::EmitCublasLtMatmulMx
+// accepts (xla/service/gpu/thunk_emitter.cc:939-988).  Shapes are those of `__op$block_scaled_dot`
+// (xla/backends/gpu/transforms/block_scaling_rewriter.h:30-77): a [b, m, k], b [b, n, k], scales
+// [b, rows, k / 32], D [b, m, n], the batch dimension optional.  Attribute `alpha_real` is optional.
+ffi::Error DecodeMx(ffi::RemainingArgs operands, ffi::RemainingRets results, ffi::Dictionary attrs,
+                    B200SD_BlockScaledDotMx* out) {
+  B200SD_BlockScaledDotMx a{};
+  a.struct_size = sizeof(a);
+  a.alpha = static_cast<float>(GetFloat(attrs, "alpha_real").value_or(1.0));
+  if (operands.size() != 4) return MakeError(3, "expected operands (a, b, a_scale, b_scale), got " + std::to_string(operands.size()));
+  if (results.size() < 1 || results.size() > 2) return MakeError(3, "expected results (D, [workspace]), got " + std::to_string(results.size()));
+  auto lhs = operands.get<ffi::AnyBuffer>(0);
+  auto rhs = operands.get<ffi::AnyBuffer>(1);
+  auto ls = operands.get<ffi::AnyBuffer>(2);
+  auto rs = operands.get<ffi::AnyBuffer>(3);
+  auto d = results.get<ffi::AnyBuffer>(0);
+  if (!lhs.has_value()) return lhs.error();
+  if (!rhs.has_value()) return rhs.error();
+  if (!ls.has_value()) return ls.error();
+  if (!rs.has_value()) return rs.error();
+  if (!d.has_value()) return d.error();
+  const size_t rank = lhs->dimensions().size();
+  if (rank != 2 && rank != 3) return MakeError(12, "operands must have rank 2, or rank 3 with a leading batch dimension");
+  if (rhs->dimensions().size() != rank || ls->dimensions().size() != rank || rs->dimensions().size() != rank ||
+      (*d)->dimensions().size() != rank)
+    return MakeError(3, "operands, scales and result must all have the same rank");
+  const size_t o = rank - 2;
+  const int64_t batch = rank == 3 ? lhs->dimensions()[0] : 1;
+  a.m = lhs->dimensions()[o];
+  a.k = lhs->dimensions()[o + 1];
+  a.n = rhs->dimensions()[o];
+  if (rhs->dimensions()[o + 1] != a.k) return MakeError(3, "contracting (minor) dimensions of a and b differ");
+  if (a.k % 32 != 0 || ls->dimensions()[o] != a.m || ls->dimensions()[o + 1] != a.k / 32 || rs->dimensions()[o] != a.n ||
+      rs->dimensions()[o + 1] != a.k / 32)
+    return MakeError(3, "scales must be [rows, k / 32]: one scale per block of 32 along the contracting dimension");
+  if ((*d)->dimensions()[o] != a.m || (*d)->dimensions()[o + 1] != a.n) return MakeError(3, "result shape is not [m, n]");
+  if (rank == 3 && (rhs->dimensions()[0] != batch || ls->dimensions()[0] != batch || rs->dimensions()[0] != batch ||
+                    (*d)->dimensions()[0] != batch))
+    return MakeError(3, "batch dimensions differ");
+  if (ls->element_type() != rs->element_type()) return MakeError(3, "a_scale and b_scale must have the same type");
+  a.batch_count = static_cast<int32_t>(batch);
+  a.a_dtype = static_cast<int32_t>(lhs->element_type());
+  a.b_dtype = static_cast<int32_t>(rhs->element_type());
+  a.scale_dtype = static_cast<int32_t>(ls->element_type());
+  a.d_dtype = static_cast<int32_t>((*d)->element_type());
+  a.a = lhs->untyped_data();
+  a.b = rhs->untyped_data();
+  a.a_scale = ls->untyped_data();
+  a.b_scale = rs->untyped_data();
+  a.d = (*d)->untyped_data();
+  *out = a;
+  return ffi::Error::Success();
+}
+ffi::Error BlockScaledDotMxInstantiate(ffi::RemainingArgs operands, ffi::RemainingRets results, ffi::Dictionary attrs) {
+  B200SD_BlockScaledDotMx a;
+  ffi::Error e = DecodeMx(operands, results, attrs, &a);
+  if (e.failure()) return e;
+  char msg[512];
+  return FromCode(b200sd_check_block_scaled_dot_mx(&a, msg, sizeof(msg)), msg);
+}
+ffi::Error BlockScaledDotMxExecute(cudaStream_t stream, ffi::RemainingArgs operands, ffi::RemainingRets results,
+                                   ffi::Dictionary attrs) {
+  B200SD_BlockScaledDotMx a;
+  ffi::Error e = DecodeMx(operands, results, attrs, &a);
+  if (e.failure()) return e;
+  char msg[512];
+  return FromCode(b200sd_block_scaled_dot_mx(&a, stream, msg, sizeof(msg)), msg);
+}
+
 }  // namespace
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_block_scaled_dot_mx_instantiate, BlockScaledDotMxInstantiate,
+                              ffi::Ffi::BindInstantiate().RemainingArgs().RemainingRets().Attrs());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_block_scaled_dot_mx_initialize, InitializeDevice, ffi::Ffi::BindInitialize());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_block_scaled_dot_mx, BlockScaledDotMxExecute,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .RemainingArgs()
+                                  .RemainingRets()
+                                  .Attrs(),
+                              {ffi::Traits::kCmdBufferCompatible});
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(b200sd_ffi_scaled_dot_f8_instantiate, ScaledDotF8Instantiate,
                               ffi::Ffi::BindInstantiate().RemainingArgs().RemainingRets().Attrs());
@@ -344,6 +425,9 @@ extern "C" int b200sd_ffi_register(const void* xla_ffi_api, char* err, size_t er
       {"b200$scaled_dot$f8",
        {b200sd_ffi_scaled_dot_f8_instantiate, nullptr, b200sd_ffi_scaled_dot_f8_initialize, b200sd_ffi_scaled_dot_f8}},
       {"b200$dot$s8", {b200sd_ffi_dot_s8_instantiate, nullptr, b200sd_ffi_dot_s8_initialize, b200sd_ffi_dot_s8}},
+      {"b200$block_scaled_dot$mx",
+       {b200sd_ffi_block_scaled_dot_mx_instantiate, nullptr, b200sd_ffi_block_scaled_dot_mx_initialize,
+        b200sd_ffi_block_scaled_dot_mx}},
   };
   for (const Target& t : targets) {
     XLA_FFI_Error* e = ffi::Ffi::RegisterStaticHandler(api, t.name, "CUDA", t.bundle,

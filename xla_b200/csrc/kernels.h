@@ -42,6 +42,7 @@ enum PrimitiveType : int32_t {
   kBF16 = 16,
   kF8E5M2 = 19,
   kF8E4M3FN = 20,
+  kF8E8M0FNU = 33,
 };
 
 // Activation applied after the optional bias.
@@ -138,7 +139,7 @@ uint32_t ProgressIncrement(const GemmProblem& g, int32_t block);
 
 // Kernel selection (stands in for cuBLASLt's algorithm index).
 enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2, kKernelDenseSingle = 3, kKernelDensePair = 4,
-                            kKernelDenseStreamK = 5 };
+                            kKernelDenseStreamK = 5, kKernelMxPair = 6 };
 
 struct LaunchStats {
   int32_t kernel = 0;     // KernelKind actually used
@@ -154,6 +155,24 @@ Status InitDevice(int device);
 Status LaunchDense(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats, int variant = kKernelDense);
 Status LaunchSkinny(const GemmProblem& p, cudaStream_t stream, LaunchStats* stats);
 size_t SkinnyWorkspaceBytes(int64_t m, int64_t n, int64_t k);
+
+// An MX block-scaled dot: D[b,m,n] = alpha * sum_k A[b,m,k] * 2^(SA[b,m,k/32]-127) * B[b,n,k] * 2^(SB[b,n,k/32]-127).
+// Both operands are stored contracting-dimension-minor, the scales row-major [rows, k/32].
+struct MxProblem {
+  int64_t m = 0, n = 0, k = 0;
+  int64_t batch = 1;
+  int32_t a_dtype = kF8E4M3FN, b_dtype = kF8E4M3FN;
+  int32_t scale_dtype = kF8E8M0FNU;
+  const void* a = nullptr;
+  const void* b = nullptr;
+  const void* a_scale = nullptr;
+  const void* b_scale = nullptr;
+  float alpha = 1.0f;
+  void* d = nullptr;
+  int32_t d_dtype = kF32;
+};
+Status ValidateMx(const MxProblem& g);      // everything but the pointers
+Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats);
 
 // Reads (and clears) the device status word the kernels OR their error bits into.  Synchronises
 // the device.

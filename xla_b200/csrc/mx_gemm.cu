@@ -1,0 +1,583 @@
+// MX block-scaled dot for sm_100a: the kernel behind XLA's `__cublas$lt$matmul$mx` custom call
+// (operand meaning: ThunkEmitter::EmitCublasLtMatmulMx, xla/service/gpu/thunk_emitter.cc:939-988; the
+// arithmetic: `__op$block_scaled_dot`, xla/backends/gpu/transforms/block_scaling_rewriter.h:30-77):
+//
+//     D[b, m, n] = alpha * sum_k  A[b, m, k] * 2^(SA[b, m, k/32] - 127)  *  B[b, n, k] * 2^(SB[b, n, k/32] - 127)
+//
+// A and B are FP8 (e4m3fn / e5m2), stored with the contracting dimension minor; SA and SB are
+// f8e8m0fnu, one per 32 values along K, stored row-major exactly as the HLO operand is -- no
+// pre-swizzled scale layout is asked of the caller.
+//
+// One persistent, warp-specialised kernel run by clusters of two CTAs on 256 x 256 tiles
+// (tcgen05.mma cta_group::2, kind::mxf8f6f4.block_scale), 384 threads per CTA:
+//   warp 0      TMA producer: per 128-deep k-block its CTA's 128 rows of A and 128 rows of B.
+//   warp 1      TMEM allocator; in the leader CTA the MMA issuer: per k-block three tcgen05.cp that
+//               move the block's scales from shared memory into TMEM, then four K=32 MMAs, each
+//               naming the byte of the scale columns that belongs to its 32 values.
+//   warp 2      scale loader: 4-byte asynchronous copies (cp.async) that gather the four scale bytes a
+//               row needs for one k-block straight into the layout tcgen05.cp wants: per 128 rows a
+//               block of 32 x 16 bytes, byte (r % 32) * 16 + (r / 32) * 4 + j holding the scale of row r
+//               and k-sub-block j.  Each CTA loads the scales of its own 128 rows of A and of all 256
+//               rows of B (every CTA of the pair multiplies by every column's scale).
+//   warps 4-11  epilogue: the whole 128 x 256 accumulator slice is pulled into registers (128 per
+//               thread), TMEM is handed back to the issuer at once, and only then are the values
+//               scaled, converted and stored.
+// TMEM holds ONE 256-column accumulator: with the scale columns there is no room for a second, so
+// what the epilogue keeps the tensor pipe waiting for is the register read-out, not the stores.
+// Every wait is bounded; on expiry the kernel records a status bit and drains.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <string>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b200sd {
+
+Status MakeBatchedByteMatrixMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
+                                uint32_t box_cols, uint32_t box_rows);
+Status MakeBatchedPlainByteMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
+                               uint32_t box_cols, uint32_t box_rows);
+int MaxPairClusters();
+
+namespace {
+
+constexpr int kMxBM = 128;                 // rows of D per CTA per tile (= TMEM lanes)
+constexpr int kMxTileM = 2 * kMxBM;        // rows of D per pair per tile
+constexpr int kMxBN = 256;                 // columns of D per tile
+constexpr int kMxBK = 128;                 // values of K per stage: one 128-byte swizzle row
+constexpr int kMxUmmaK = 32;               // K per MMA = one scale block
+constexpr int kMxStages = 6;
+constexpr int kMxAStageBytes = kMxBM * kMxBK;            // 16 KiB
+constexpr int kMxBStageBytes = (kMxBN / 2) * kMxBK;      // 16 KiB: this CTA's half of the tile's B rows
+constexpr int kMxSfBlockBytes = 512;                     // scales of 128 rows x 4 sub-blocks
+constexpr int kMxSfaStageBytes = kMxSfBlockBytes;        // this CTA's 128 rows of A
+constexpr int kMxSfbStageBytes = 2 * kMxSfBlockBytes;    // all 256 rows of B
+constexpr int kMxSfStageBytes = kMxSfaStageBytes + kMxSfbStageBytes;
+constexpr int kMxEpilogueWarps = 8;
+constexpr int kMxFirstEpilogueWarp = 4;
+constexpr int kMxThreads = 32 * (kMxFirstEpilogueWarp + kMxEpilogueWarps);
+constexpr int kMxTmemCols = 512;
+// TMEM columns: accumulator 0-255; scale columns in two alternating sets so that the copy for one
+// k-block never lands on columns the MMAs of the block before may still be reading.
+constexpr int kMxTmemSfa = 256;            // + 16 * set: 4 columns
+constexpr int kMxTmemSfb = 288;            // + 16 * set: 8 columns
+constexpr int kMxSfLookahead = 3;          // k-blocks of scale copies in flight per CTA (< kMxStages)
+// Bulk scale path: one TMA box brings the scales of four k-blocks (16 bytes per row) at a time.
+constexpr int kMxRawSlots = 3;
+constexpr int kMxRawSfaBytes = kMxBM * 16;               // 2 KiB: 128 rows of A
+constexpr int kMxRawSfbBytes = kMxBN * 16;               // 4 KiB: 256 rows of B
+constexpr int kMxRawSlotBytes = kMxRawSfaBytes + kMxRawSfbBytes;
+
+struct MxAux {
+  uint64_t full_bar[kMxStages];    // leader's: operands (both CTAs' TMA bytes) and both CTAs' scales have landed
+  uint64_t empty_bar[kMxStages];   // each CTA's: the MMAs that read the stage have completed
+  uint64_t acc_full_bar;           // each CTA's: the tile's accumulator is complete
+  uint64_t acc_empty_bar;          // leader's: all 16 epilogue warps of the pair have read the accumulator out
+  uint64_t raw_full_bar[kMxRawSlots];   // each CTA's: a four-k-block box of scales has landed
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t MxSmemBytes() {
+  return 1024 + size_t(kMxStages) * (kMxAStageBytes + kMxBStageBytes + kMxSfStageBytes) + kMxRawSlots * kMxRawSlotBytes +
+         sizeof(MxAux);
+}
+
+struct MxArgs {
+  int64_t m, n, k;
+  int64_t scale_cols;              // k / 32: bytes per row of SA and SB
+  int32_t batch;
+  int32_t num_m_tiles, num_n_tiles, num_k_blocks;
+  int32_t raster_group;
+  uint32_t idesc;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int32_t sf_words_ok;             // rows of SA / SB start on 4-byte boundaries and hold whole 4-byte groups
+  int32_t sf_bulk_ok;              // ... on 16-byte boundaries: the scales come by TMA, four k-blocks per box
+  float alpha;
+  void* d;
+  int32_t d_dtype;
+  int32_t vec_store_ok;
+  uint32_t* status;
+};
+
+// Tile order: groups of `raster_group` row tiles are swept column by column, so the clusters that run at
+// the same time share a few row panels of A and a few column panels of B in L2.
+__device__ __forceinline__ void mx_tile_coords(int32_t tile, const MxArgs& p, int32_t* mt, int32_t* nt, int32_t* bt) {
+  const int32_t per_batch = p.num_m_tiles * p.num_n_tiles;
+  *bt = tile / per_batch;
+  const int32_t t = tile - *bt * per_batch;
+  const int32_t group_tiles = p.raster_group * p.num_n_tiles;
+  const int32_t g = t / group_tiles;
+  const int32_t r = t - g * group_tiles;
+  const int32_t rows = min(p.raster_group, p.num_m_tiles - g * p.raster_group);
+  *mt = g * p.raster_group + r % rows;
+  *nt = r / rows;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Stores 32 consecutive f32 values of one row of D, columns [col, col + 32), as `dtype`.
+__device__ __forceinline__ void mx_store_chunk(const MxArgs& p, int64_t row_off, int32_t col, const uint32_t (&r)[32]) {
+  const float alpha = p.alpha;
+  if (p.vec_store_ok && col + 32 <= p.n) {
+    if (p.d_dtype == kF32) {
+      float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.d) + row_off + col);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dst[i] = make_float4(__uint_as_float(r[4 * i]) * alpha, __uint_as_float(r[4 * i + 1]) * alpha,
+                             __uint_as_float(r[4 * i + 2]) * alpha, __uint_as_float(r[4 * i + 3]) * alpha);
+      }
+    } else {
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) + row_off + col);
+      const bool bf = p.d_dtype == kBF16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __uint_as_float(r[8 * i + 2 * j]) * alpha, hi = __uint_as_float(r[8 * i + 2 * j + 1]) * alpha;
+          w[j] = bf ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+        }
+        dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    if (col + i < p.n) {
+      const float v = __uint_as_float(r[i]) * alpha;
+      if (p.d_dtype == kF32) static_cast<float*>(p.d)[row_off + col + i] = v;
+      else if (p.d_dtype == kBF16) static_cast<__nv_bfloat16*>(p.d)[row_off + col + i] = __float2bfloat16_rn(v);
+      else static_cast<__half*>(p.d)[row_off + col + i] = __float2half_rn(v);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const MxArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem_a + kMxStages * kMxAStageBytes;
+  uint8_t* smem_sf = smem_b + kMxStages * kMxBStageBytes;
+  uint8_t* smem_raw_sf = smem_sf + kMxStages * kMxSfStageBytes;
+  MxAux* aux = reinterpret_cast<MxAux*>(smem_raw_sf + kMxRawSlots * kMxRawSlotBytes);
+  volatile int* abort_flag = &aux->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();                 // 0 = leader of the pair
+  const int32_t cluster_id = int32_t(blockIdx.x >> 1);
+  const int32_t num_clusters = int32_t(gridDim.x >> 1);
+  const int32_t num_tiles = p.batch * p.num_m_tiles * p.num_n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMxStages; ++s) {
+      mbar_init(&aux->full_bar[s], 3);        // the leader's producer (with the byte count) + one scale loader per CTA
+      mbar_init(&aux->empty_bar[s], 1);
+    }
+    mbar_init(&aux->acc_full_bar, 1);
+    mbar_init(&aux->acc_empty_bar, 2 * kMxEpilogueWarps);
+    for (int s = 0; s < kMxRawSlots; ++s) mbar_init(&aux->raw_full_bar[s], 1);
+    aux->abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&aux->tmem_base, kMxTmemCols);
+    tmem_relinquish_alloc_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                         // the peer's barriers exist before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = aux->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int32_t mt, nt, bt;
+        mx_tile_coords(tile, p, &mt, &nt, &bt);
+        const int32_t row0 = mt * kMxTileM + int32_t(rank) * kMxBM;
+        const int32_t col0 = nt * kMxBN + int32_t(rank) * (kMxBN / 2);
+        for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          if (!ok) break;
+          // Both CTAs' loads count on the leader's barrier; the leader announces the bytes of both.
+          if (rank == 0) mbar_arrive_expect_tx(&aux->full_bar[stage], 2 * (kMxAStageBytes + kMxBStageBytes));
+          const uint32_t full = map_to_cta(&aux->full_bar[stage], 0);
+          tma_load_3d_pair(smem_a + stage * kMxAStageBytes, &tmap_a, full, kb * kMxBK, row0, bt);
+          tma_load_3d_pair(smem_b + stage * kMxBStageBytes, &tmap_b, full, kb * kMxBK, col0, bt);
+          if (++stage == kMxStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0 && elect_one()) {
+      const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem_a), 16384, 1024);
+      const uint64_t b_desc0 = make_smem_desc_sw128(smem_u32(smem_b), 16384, 1024);
+      const uint64_t sf_desc0 = make_smem_desc_noswizzle(smem_u32(smem_sf), 128);
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0, set = 0;
+      bool ok = true;
+      for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        ok = mbar_wait(&aux->acc_empty_bar, acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t a_desc = a_desc0 + uint64_t((stage * kMxAStageBytes) >> 4);
+          const uint64_t b_desc = b_desc0 + uint64_t((stage * kMxBStageBytes) >> 4);
+          const uint64_t sf_desc = sf_desc0 + uint64_t((stage * kMxSfStageBytes) >> 4);
+          const uint32_t sfa_t = tmem_base + kMxTmemSfa + 16 * set;
+          const uint32_t sfb_t = tmem_base + kMxTmemSfb + 16 * set;
+          tmem_cp_32x128b_pair(sfa_t, sf_desc);                                             // A rows of this CTA
+          tmem_cp_32x128b_pair(sfb_t, sf_desc + uint64_t(kMxSfaStageBytes >> 4));           // B rows 0-127
+          tmem_cp_32x128b_pair(sfb_t + 4, sf_desc + uint64_t((kMxSfaStageBytes + kMxSfBlockBytes) >> 4));   // B rows 128-255
+#pragma unroll
+          for (int j = 0; j < kMxBK / kMxUmmaK; ++j) {
+            const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+            umma_mxf8_pair(tmem_base, a_desc + uint64_t((j * kMxUmmaK) >> 4), b_desc + uint64_t((j * kMxUmmaK) >> 4),
+                           idesc_mx_with_scale_byte(p.idesc, uint32_t(j)), sfa_t, sfb_t, accumulate);
+          }
+          // The stage may be refilled once these copies and MMAs have read it -- in both CTAs.
+          umma_commit_pair(map_to_cta(&aux->empty_bar[stage], 0));
+          umma_commit_pair(map_to_cta(&aux->empty_bar[stage], 1));
+          set ^= 1;
+          if (++stage == kMxStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(map_to_cta(&aux->acc_full_bar, 0));     // accumulator complete (each CTA has its rows)
+        umma_commit_pair(map_to_cta(&aux->acc_full_bar, 1));
+        acc_phase ^= 1;
+      }
+    }
+  } else if (warp == 2 && p.sf_bulk_ok) {
+    // ------------------------------------------------------------------ scale loader, bulk path
+    // Lane 0 keeps up to kMxRawSlots boxes in flight (16 scale bytes = four k-blocks of every row of
+    // this CTA's A rows and of the tile's B rows).  When a box has landed, every lane reads the 16
+    // bytes of its twelve rows into registers once and then, k-block by k-block, writes the three
+    // 16-byte pieces that make up its part of the layout tcgen05.cp reads.
+    const int32_t groups_per_tile = (p.num_k_blocks + 3) / 4;
+    int32_t issue_tile = cluster_id, issue_group = 0;      // next box to ask for
+    uint32_t issued = 0, consumed = 0;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_sfa);
+      tma_prefetch_desc(&tmap_sfb);
+    }
+    for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int32_t grp = 0; grp < groups_per_tile && ok; ++grp) {
+        if (lane == 0) {
+          while (issue_tile < num_tiles && issued - consumed < uint32_t(kMxRawSlots)) {
+            int32_t mt, nt, bt;
+            mx_tile_coords(issue_tile, p, &mt, &nt, &bt);
+            const uint32_t slot = issued % kMxRawSlots;
+            uint8_t* raw = smem_raw_sf + slot * kMxRawSlotBytes;
+            mbar_arrive_expect_tx(&aux->raw_full_bar[slot], kMxRawSlotBytes);
+            tma_load_3d(raw, &tmap_sfa, &aux->raw_full_bar[slot], issue_group * 16, mt * kMxTileM + int32_t(rank) * kMxBM, bt);
+            tma_load_3d(raw + kMxRawSfaBytes, &tmap_sfb, &aux->raw_full_bar[slot], issue_group * 16, nt * kMxBN, bt);
+            ++issued;
+            if (++issue_group == groups_per_tile) {
+              issue_group = 0;
+              issue_tile += num_clusters;
+            }
+          }
+          ok = mbar_wait(&aux->raw_full_bar[consumed % kMxRawSlots], (consumed / kMxRawSlots) & 1, abort_flag, p.status,
+                         kStatusProducerTimeout);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        (void)mbar_try_wait(&aux->raw_full_bar[consumed % kMxRawSlots], (consumed / kMxRawSlots) & 1);   // every lane observes the phase
+        const uint32_t raw = smem_u32(smem_raw_sf) + (consumed % kMxRawSlots) * kMxRawSlotBytes + uint32_t(lane) * 16;
+        uint32_t w[12][4];
+#pragma unroll
+        for (int g = 0; g < 12; ++g) {      // row lane + 32 g of the box: g 0-3 rows of A, g 4-11 rows of B
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(w[g][0]), "=r"(w[g][1]), "=r"(w[g][2]), "=r"(w[g][3])
+                       : "r"(raw + uint32_t(g) * 512));
+        }
+        // The slot may be refilled: order this warp's reads before the next box's write.
+        fence_proxy_async_smem();
+        __syncwarp();
+        ++consumed;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (grp * 4 + j < p.num_k_blocks && ok) {
+            if (lane == 0) ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok) {
+              const uint32_t dst = smem_u32(smem_sf) + uint32_t(stage) * kMxSfStageBytes + uint32_t(lane) * 16;
+#pragma unroll
+              for (int blk = 0; blk < 3; ++blk) {
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + uint32_t(blk) * kMxSfBlockBytes),
+                             "r"(w[4 * blk][j]), "r"(w[4 * blk + 1][j]), "r"(w[4 * blk + 2][j]), "r"(w[4 * blk + 3][j])
+                             : "memory");
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(map_to_cta(&aux->full_bar[stage], 0));
+              if (++stage == kMxStages) {
+                stage = 0;
+                phase ^= 1;
+              }
+            }
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      // Abort path: let boxes that were already requested land before the CTA's memory is released.
+      for (; consumed < issued; ++consumed) {
+        for (int i = 0; i < 100000 && !mbar_try_wait(&aux->raw_full_bar[consumed % kMxRawSlots], (consumed / kMxRawSlots) & 1); ++i) {
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scale loader, gather path
+    const uint32_t sf_smem0 = smem_u32(smem_sf) + uint32_t(lane) * 16;
+    const int lookahead = p.sf_words_ok ? kMxSfLookahead : 0;
+    int stage = 0, sig_stage = 0, issued = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    auto signal_oldest = [&]() {
+      // The copies of the oldest outstanding k-block are complete for this lane; make them visible to
+      // the tensor core's reads of shared memory, then tell the leader.
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&aux->full_bar[sig_stage], 0));
+      if (++sig_stage == kMxStages) sig_stage = 0;
+      --issued;
+    };
+    for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int32_t mt, nt, bt;
+      mx_tile_coords(tile, p, &mt, &nt, &bt);
+      const int64_t a_row0 = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + lane;      // + 32 g
+      const int64_t b_row0 = int64_t(nt) * kMxBN + lane;                                  // + 32 g
+      const uint8_t* sfa_b = p.sfa + int64_t(bt) * p.m * p.scale_cols;
+      const uint8_t* sfb_b = p.sfb + int64_t(bt) * p.n * p.scale_cols;
+      for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+        if (lane == 0) ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        const uint32_t dst = sf_smem0 + uint32_t(stage) * kMxSfStageBytes;
+        const int64_t kcol = int64_t(kb) * 4;
+#pragma unroll
+        for (int g = 0; g < 12; ++g) {
+          // g 0-3: rows of A (block 0); g 4-11: rows of B (blocks 1 and 2).  Within a block, row group
+          // g % 4 goes to bytes 4 * (g % 4) .. + 3 of every lane's 16.
+          const bool is_a = g < 4;
+          const int64_t row = is_a ? a_row0 + 32 * g : b_row0 + 32 * (g - 4);
+          const bool valid = row < (is_a ? p.m : p.n);
+          const uint8_t* src = (is_a ? sfa_b : sfb_b) + (valid ? row * p.scale_cols + kcol : 0);
+          const uint32_t d = dst + uint32_t(g / 4) * kMxSfBlockBytes + uint32_t(g % 4) * 4;
+          if (p.sf_words_ok) {
+            cp_async_4(d, src, valid ? 4u : 0u);
+          } else {
+            uint32_t w = 0;
+            if (valid) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (kcol + j < p.scale_cols) w |= uint32_t(__ldg(src + j)) << (8 * j);
+              }
+            }
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(d), "r"(w) : "memory");
+          }
+        }
+        cp_async_commit();
+        ++issued;
+        if (issued > lookahead) {
+          cp_async_wait<kMxSfLookahead>();
+          signal_oldest();
+        }
+        if (++stage == kMxStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    cp_async_wait<0>();
+    while (issued > 0) signal_oldest();
+  } else if (warp >= kMxFirstEpilogueWarp) {
+    // ------------------------------------------------------------------ epilogue (warps 4..11)
+    const int q = warp & 3;                               // TMEM lane quarter this warp may access
+    const int col_half = (warp - kMxFirstEpilogueWarp) >> 2;
+    const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(col_half * 128);
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int32_t tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+      int32_t mt, nt, bt;
+      mx_tile_coords(tile, p, &mt, &nt, &bt);
+      if (lane == 0) ok = mbar_wait(&aux->acc_full_bar, acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      (void)mbar_try_wait(&aux->acc_full_bar, acc_phase);     // every lane observes the completed phase
+      tc_fence_after_sync();
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld_32x32(t_addr, r0);
+      tmem_ld_32x32(t_addr + 32, r1);
+      tmem_ld_32x32(t_addr + 64, r2);
+      tmem_ld_32x32(t_addr + 96, r3);
+      tmem_ld_wait_for(r0);
+      tmem_ld_wait_for(r1);
+      tmem_ld_wait_for(r2);
+      tmem_ld_wait_for(r3);
+      // The accumulator is in registers: the issuer may start the next tile.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank != 0) mbar_arrive_cluster(map_to_cta(&aux->acc_empty_bar, 0));
+        else mbar_arrive(&aux->acc_empty_bar);
+      }
+      acc_phase ^= 1;
+      const int64_t row = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + q * 32 + lane;
+      if (row < p.m) {
+        const int64_t row_off = (int64_t(bt) * p.m + row) * p.n;
+        const int32_t col = nt * kMxBN + col_half * 128;
+        mx_store_chunk(p, row_off, col, r0);
+        mx_store_chunk(p, row_off, col + 32, r1);
+        mx_store_chunk(p, row_off, col + 64, r2);
+        mx_store_chunk(p, row_off, col + 96, r3);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();      // nobody leaves while the peer may still read this CTA's shared memory
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kMxTmemCols);
+  }
+}
+
+}  // namespace
+
+// ----------------------------------------------------------------------------- host side
+Status InitMxKernels() {
+  const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(mx_gemm_kernel),
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(MxSmemBytes()));
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(mx): ") + cudaGetErrorString(e));
+  return Status::Ok();
+}
+
+Status ValidateMx(const MxProblem& g) {
+  auto f8 = [](int32_t t) { return t == kF8E4M3FN || t == kF8E5M2; };
+  if (!f8(g.a_dtype) || !f8(g.b_dtype)) {
+    return Status::Error(kUnimplemented, "block-scaled dot: operands must be f8e4m3fn or f8e5m2 (4- and 6-bit MX element types are not implemented)");
+  }
+  if (g.scale_dtype != kF8E8M0FNU) return Status::Error(kUnimplemented, "block-scaled dot: scales must be f8e8m0fnu (block size 32)");
+  if (g.d_dtype != kF32 && g.d_dtype != kBF16 && g.d_dtype != kF16) {
+    return Status::Error(kInvalidArgument, "block-scaled dot: the result must be f32, bf16 or f16");
+  }
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch < 0) return Status::Error(kInvalidArgument, "block-scaled dot: empty or negative dimension");
+  if (g.k % 32 != 0) return Status::Error(kInvalidArgument, "block-scaled dot: the contracting dimension must be a multiple of the block size 32");
+  if (g.m >= (1ll << 31) || g.n >= (1ll << 31) || g.k >= (1ll << 31)) return Status::Error(kInvalidArgument, "block-scaled dot: dimension too large");
+  return Status::Ok();
+}
+
+Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
+  Status st = ValidateMx(g);
+  if (!st.ok()) return st;
+  int device = 0;
+  cudaGetDevice(&device);
+  st = InitDevice(device);
+  if (!st.ok()) return st;
+  const int max_pairs = MaxPairClusters();
+  if (max_pairs <= 0) return Status::Error(kFailedPrecondition, "this device cannot co-schedule the CTA pairs the block-scaled kernel runs as");
+  if (g.a == nullptr || g.b == nullptr || g.a_scale == nullptr || g.b_scale == nullptr || g.d == nullptr) {
+    return Status::Error(kInvalidArgument, "block-scaled dot: null operand, scale or result pointer");
+  }
+  const int64_t batch = g.batch > 0 ? g.batch : 1;
+  CUtensorMap tmap_a, tmap_b;
+  st = MakeBatchedByteMatrixMap(&tmap_a, g.a, batch, g.m, g.k, kMxBK, kMxBM);          // [m, k], box 128(k) x 128(m)
+  if (!st.ok()) return st;
+  st = MakeBatchedByteMatrixMap(&tmap_b, g.b, batch, g.n, g.k, kMxBK, kMxBN / 2);      // [n, k], box 128(k) x 128(n)
+  if (!st.ok()) return st;
+
+  MxArgs p{};
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.scale_cols = g.k / 32;
+  // Scale rows that start on 16-byte boundaries can be fetched as TMA boxes of 16 bytes x 128 / 256 rows.
+  p.sf_bulk_ok = (p.scale_cols % 16 == 0 && (reinterpret_cast<uintptr_t>(g.a_scale) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(g.b_scale) & 15) == 0) ? 1 : 0;
+  CUtensorMap tmap_sfa = tmap_a, tmap_sfb = tmap_b;       // placeholders the gather path never touches
+  if (p.sf_bulk_ok) {
+    st = MakeBatchedPlainByteMap(&tmap_sfa, g.a_scale, batch, g.m, p.scale_cols, 16, kMxBM);
+    if (!st.ok()) return st;
+    st = MakeBatchedPlainByteMap(&tmap_sfb, g.b_scale, batch, g.n, p.scale_cols, 16, kMxBN);
+    if (!st.ok()) return st;
+  }
+  p.batch = int32_t(batch);
+  p.num_m_tiles = int32_t((g.m + kMxTileM - 1) / kMxTileM);
+  p.num_n_tiles = int32_t((g.n + kMxBN - 1) / kMxBN);
+  p.num_k_blocks = int32_t((g.k + kMxBK - 1) / kMxBK);
+  const int64_t tiles = batch * p.num_m_tiles * p.num_n_tiles;
+  if (tiles > (1ll << 30)) return Status::Error(kInvalidArgument, "block-scaled dot: too many tiles");
+  p.raster_group = 16;
+  p.idesc = make_idesc_mx(g.a_dtype == kF8E5M2 ? 1u : 0u, g.b_dtype == kF8E5M2 ? 1u : 0u, kMxTileM, kMxBN);
+  p.sfa = static_cast<const uint8_t*>(g.a_scale);
+  p.sfb = static_cast<const uint8_t*>(g.b_scale);
+  p.sf_words_ok = (p.scale_cols % 4 == 0 && (reinterpret_cast<uintptr_t>(g.a_scale) & 3) == 0 &&
+                   (reinterpret_cast<uintptr_t>(g.b_scale) & 3) == 0) ? 1 : 0;
+  p.alpha = g.alpha;
+  p.d = g.d;
+  p.d_dtype = g.d_dtype;
+  const int64_t d_elt = g.d_dtype == kF32 ? 4 : 2;
+  p.vec_store_ok = ((reinterpret_cast<uintptr_t>(g.d) & 15) == 0 && (g.n * d_elt) % 16 == 0) ? 1 : 0;
+  p.status = StatusWordPtr();
+
+  const int grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kMxThreads, 1, 1);
+  cfg.dynamicSmemBytes = MxSmemBytes();
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, mx_gemm_kernel, tmap_a, tmap_b, tmap_sfa, tmap_sfb, p);
+  if (e != cudaSuccess) return Status::Error(kInternal, std::string("mx_gemm_kernel launch: ") + cudaGetErrorString(e));
+  if (stats) {
+    stats->kernel = kKernelMxPair;
+    stats->grid = grid;
+    stats->launches = 1;
+  }
+  return Status::Ok();
+}
+
+}  // namespace b200sd

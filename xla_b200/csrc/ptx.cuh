@@ -425,4 +425,57 @@ __host__ __device__ inline uint32_t make_idesc(uint32_t c_format, uint32_t a_for
          (static_cast<uint32_t>(b_mn_major) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// ----------------------------------------------------------------------------- MX block-scaled MMA
+// 4-byte asynchronous copy global -> shared; bytes past `src_bytes` (0..4) are written as zero.
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+// Shared-memory descriptor of an un-swizzled K-major block of 8-row x 16-byte core matrices that
+// follow one another every `sbo_bytes` (the source operand of tcgen05.cp for scale factors).
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+
+// Copies 32 rows x 16 bytes of shared memory into 4 TMEM columns, the same data into each of the
+// four 32-lane quarters, in both CTAs of a pair (each from its own shared memory at the same offset).
+// One thread issues it; it is ordered with the tcgen05.mma instructions that thread issues afterwards
+// and completes towards tcgen05.commit like they do.
+__device__ __forceinline__ void tmem_cp_32x128b_pair(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// Block-scaled 256-row MMA across the pair: every 32 values along K of an A row (B row) are
+// multiplied by the e8m0 scale found in TMEM at `sfa_tmem` (`sfb_tmem`); which of the four bytes of
+// a scale column applies is part of `idesc` (make_idesc_mx).
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Instruction descriptor of kind::mxf8f6f4.block_scale with e8m0 scales (f32 accumulation implied):
+//   bits 4-5 byte of the B scale column    bits 7-9 / 10-12 A / B element format (0 e4m3, 1 e5m2)
+//   bit 15 / 16 A / B is MN-major          bits 17-22 N >> 3     bit 23 scale type (1 = e8m0)
+//   bits 24-28 M >> 4                      bits 29-30 byte of the A scale column
+__host__ __device__ inline uint32_t make_idesc_mx(uint32_t a_format, uint32_t b_format, uint32_t m, uint32_t n) {
+  return (a_format << 7) | (b_format << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+__host__ __device__ inline uint32_t idesc_mx_with_scale_byte(uint32_t idesc, uint32_t byte) {
+  return idesc | (byte << 4) | (byte << 29);
+}
+
 }  // namespace b200sd

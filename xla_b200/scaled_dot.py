@@ -22,9 +22,12 @@ from . import _native
 
 # XLA PrimitiveType / XLA_FFI_DataType numbers (xla/ffi/api/c_api.h:233-266).
 PRED, S8, S32, S64, F16, F32, F64, BF16, F8E5M2, F8E4M3FN = 1, 2, 4, 5, 10, 11, 12, 16, 19, 20
+F8E8M0FNU = 33
 
 TARGET_F8 = "b200$scaled_dot$f8"
 TARGET_S8 = "b200$dot$s8"
+TARGET_MX = "b200$block_scaled_dot$mx"
+MX_BLOCK_SIZE = 32  # BlockScalingRewriter::kBlockSizeMXFP8, xla/backends/gpu/transforms/block_scaling_rewriter.h
 XLA_WORKSPACE_BYTES = 32 * 1024 * 1024  # GemmConfig::kHopperWorkspace, xla/service/gpu/matmul_utils.h:103
 
 _STAGE_INSTANTIATE, _STAGE_PREPARE, _STAGE_INITIALIZE, _STAGE_EXECUTE = 0, 1, 2, 3
@@ -97,6 +100,8 @@ def _dtype_code(t) -> int:
         torch.float8_e4m3fn: F8E4M3FN, torch.float8_e5m2: F8E5M2, torch.int8: S8, torch.int32: S32,
         torch.float16: F16, torch.float32: F32, torch.bfloat16: BF16,
     }
+    if hasattr(torch, "float8_e8m0fnu"):
+        table[torch.float8_e8m0fnu] = F8E8M0FNU
     return table[t]
 
 
@@ -235,6 +240,15 @@ class Int8DotCall(FfiCall):
         })
 
 
+class BlockScaledDotCall(FfiCall):
+    """A `b200$block_scaled_dot$mx` call site: operands a, b, a_scale, b_scale; results D,
+    [workspace] -- the arrangement of `__cublas$lt$matmul$mx`
+    (xla/service/gpu/thunk_emitter.cc:939-988)."""
+
+    def __init__(self, operands: Sequence, results: Sequence, *, alpha_real: float = 1.0):
+        super().__init__(TARGET_MX, operands, results, {"alpha_real": float(alpha_real)})
+
+
 def _current_stream_and_device(t):
     torch = _torch()
     dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
@@ -300,6 +314,31 @@ def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=N
     call.run(stream, dev)
     call.close()
     return d, acc
+
+
+def cublas_lt_matmul_mx(a, b, a_scale, b_scale, *, out_dtype=None, alpha_real: float = 1.0, workspace=None, out=None):
+    """Runs one MX block-scaled dot on the current CUDA stream and returns D.
+
+    a: [m, k] or [batch, m, k] float8; b: [n, k] or [batch, n, k] float8 (the contracting dimension is
+    the minor one of both, as `__op$block_scaled_dot` fixes it); a_scale / b_scale: [..., rows, k / 32]
+    float8_e8m0fnu (uint8 tensors holding the code points are taken as such)."""
+    torch = _torch()
+    out_dtype = out_dtype or torch.float32
+    lead = tuple(a.shape[:-2])
+    d = out if out is not None else torch.empty(lead + (a.shape[-2], b.shape[-2]), dtype=out_dtype, device=a.device)
+
+    def scale_buffer(s):
+        if s.dtype == torch.uint8:
+            return Buffer(F8E8M0FNU, tuple(s.shape), s.data_ptr())
+        return s
+
+    operands = [a, b, scale_buffer(a_scale), scale_buffer(b_scale)]
+    results = [d] + ([workspace] if workspace is not None else [])
+    call = BlockScaledDotCall(operands, results, alpha_real=alpha_real)
+    stream, dev = _current_stream_and_device(a)
+    call.run(stream, dev)
+    call.close()
+    return d
 
 
 def device_status() -> int:
