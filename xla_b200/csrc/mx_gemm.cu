@@ -14,11 +14,14 @@
 //   warp 1      TMEM allocator; in the leader CTA the MMA issuer: per k-block three tcgen05.cp that
 //               move the block's scales from shared memory into TMEM, then four K=32 MMAs, each
 //               naming the byte of the scale columns that belongs to its 32 values.
-//   warp 2      scale loader: 4-byte asynchronous copies (cp.async) that gather the four scale bytes a
-//               row needs for one k-block straight into the layout tcgen05.cp wants: per 128 rows a
-//               block of 32 x 16 bytes, byte (r % 32) * 16 + (r / 32) * 4 + j holding the scale of row r
-//               and k-sub-block j.  Each CTA loads the scales of its own 128 rows of A and of all 256
-//               rows of B (every CTA of the pair multiplies by every column's scale).
+//   warps 2-3   scale loaders (alternate groups).  Scales travel in groups of four k-blocks through a ring of their own:
+//               one TMA box brings 16 scale bytes (four k-blocks) of each of the CTA's 128 A rows and
+//               of all 256 B rows of the tile (every CTA of the pair multiplies by every column's
+//               scale); the warp then rewrites the slot in place into the layout tcgen05.cp wants: per
+//               k-block and per 128 rows a block of 32 x 16 bytes, byte (r % 32) * 16 + (r / 32) * 4 + j
+//               holding the scale of row r and 32-value sub-block j.  One proxy fence and one arrival
+//               per group.  Scale rows that do not start on 16-byte boundaries (k not a multiple of
+//               512) are gathered with plain loads instead of the box.
 //   warps 4-11  epilogue: the whole 128 x 256 accumulator slice is pulled into registers (128 per
 //               thread), TMEM is handed back to the issuer at once, and only then are the values
 //               scaled, converted and stored.
@@ -64,26 +67,28 @@ constexpr int kMxTmemCols = 512;
 // k-block never lands on columns the MMAs of the block before may still be reading.
 constexpr int kMxTmemSfa = 256;            // + 16 * set: 4 columns
 constexpr int kMxTmemSfb = 288;            // + 16 * set: 8 columns
-constexpr int kMxSfLookahead = 3;          // k-blocks of scale copies in flight per CTA (< kMxStages)
-// Bulk scale path: one TMA box brings the scales of four k-blocks (16 bytes per row) at a time.
-constexpr int kMxRawSlots = 3;
+// Scales travel in groups of four k-blocks (16 bytes per row: what one TMA box can bring), one group
+// per slot of their own ring, so the loader runs well ahead of the operand stages.
+constexpr int kMxSfSlots = 5;
 constexpr int kMxRawSfaBytes = kMxBM * 16;               // 2 KiB: 128 rows of A
 constexpr int kMxRawSfbBytes = kMxBN * 16;               // 4 KiB: 256 rows of B
-constexpr int kMxRawSlotBytes = kMxRawSfaBytes + kMxRawSfbBytes;
+constexpr int kMxSfSlotBytes = 4 * kMxSfStageBytes;      // 6 KiB, as a landed box and as four rearranged k-blocks
+static_assert(kMxSfSlotBytes == kMxRawSfaBytes + kMxRawSfbBytes, "a box and its rearranged form share a slot");
 
 struct MxAux {
-  uint64_t full_bar[kMxStages];    // leader's: operands (both CTAs' TMA bytes) and both CTAs' scales have landed
+  uint64_t full_bar[kMxStages];    // leader's: both CTAs' operand bytes have landed
   uint64_t empty_bar[kMxStages];   // each CTA's: the MMAs that read the stage have completed
   uint64_t acc_full_bar;           // each CTA's: the tile's accumulator is complete
   uint64_t acc_empty_bar;          // leader's: all 16 epilogue warps of the pair have read the accumulator out
-  uint64_t raw_full_bar[kMxRawSlots];   // each CTA's: a four-k-block box of scales has landed
+  uint64_t raw_full_bar[kMxSfSlots];    // each CTA's: a box of scales has landed in the slot
+  uint64_t sf_full_bar[kMxSfSlots];     // leader's: both CTAs have rearranged the slot's scales
+  uint64_t sf_empty_bar[kMxSfSlots];    // each CTA's: the copies and MMAs that read the slot have completed
   uint32_t tmem_base;
   int abort_flag;
 };
 
 constexpr size_t MxSmemBytes() {
-  return 1024 + size_t(kMxStages) * (kMxAStageBytes + kMxBStageBytes + kMxSfStageBytes) + kMxRawSlots * kMxRawSlotBytes +
-         sizeof(MxAux);
+  return 1024 + size_t(kMxStages) * (kMxAStageBytes + kMxBStageBytes) + kMxSfSlots * kMxSfSlotBytes + sizeof(MxAux);
 }
 
 struct MxArgs {
@@ -102,7 +107,18 @@ struct MxArgs {
   int32_t d_dtype;
   int32_t vec_store_ok;
   uint32_t* status;
+  unsigned long long* timing;      // tuning build: kMxTimingSlots counters per CTA, else nullptr
 };
+
+// Tuning counters per CTA (cycles unless said otherwise): [0] issuer waiting for a full stage, [1] issuer
+// waiting for the accumulator to be read out, [2] issuer total, [3] producer waiting for a free stage,
+// [4] scale loader waiting for its box, [5] scale loader waiting for a free slot, [6] scale loader writing,
+// fencing and signalling, [7] epilogue waiting for the accumulator, [8] epilogue read-out, [9] epilogue stores,
+// [10] issuer waiting for a group of scales.
+constexpr int kMxTimingSlots = 16;
+#if B200SD_TUNING
+__device__ unsigned long long g_mx_timing[kMxTimingSlots * 512];
+#endif
 
 // Tile order: groups of `raster_group` row tiles are swept column by column, so the clusters that run at
 // the same time share a few row panels of A and a few column panels of B in L2.
@@ -173,8 +189,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem_a + kMxStages * kMxAStageBytes;
   uint8_t* smem_sf = smem_b + kMxStages * kMxBStageBytes;
-  uint8_t* smem_raw_sf = smem_sf + kMxStages * kMxSfStageBytes;
-  MxAux* aux = reinterpret_cast<MxAux*>(smem_raw_sf + kMxRawSlots * kMxRawSlotBytes);
+  MxAux* aux = reinterpret_cast<MxAux*>(smem_sf + kMxSfSlots * kMxSfSlotBytes);
   volatile int* abort_flag = &aux->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -186,12 +201,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMxStages; ++s) {
-      mbar_init(&aux->full_bar[s], 3);        // the leader's producer (with the byte count) + one scale loader per CTA
+      mbar_init(&aux->full_bar[s], 1);        // the leader's producer, with the byte count of both CTAs' loads
       mbar_init(&aux->empty_bar[s], 1);
     }
     mbar_init(&aux->acc_full_bar, 1);
     mbar_init(&aux->acc_empty_bar, 2 * kMxEpilogueWarps);
-    for (int s = 0; s < kMxRawSlots; ++s) mbar_init(&aux->raw_full_bar[s], 1);
+    for (int s = 0; s < kMxSfSlots; ++s) {
+      mbar_init(&aux->raw_full_bar[s], 1);
+      mbar_init(&aux->sf_full_bar[s], 2);     // one scale loader per CTA
+      mbar_init(&aux->sf_empty_bar[s], 1);
+    }
     aux->abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -214,13 +233,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prod_wait = 0;
       for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         int32_t mt, nt, bt;
         mx_tile_coords(tile, p, &mt, &nt, &bt);
         const int32_t row0 = mt * kMxTileM + int32_t(rank) * kMxBM;
         const int32_t col0 = nt * kMxBN + int32_t(rank) * (kMxBN / 2);
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          const long long tw = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          if (kTiming && p.timing) prod_wait += clock64() - tw;
           if (!ok) break;
           // Both CTAs' loads count on the leader's barrier; the leader announces the bytes of both.
           if (rank == 0) mbar_arrive_expect_tx(&aux->full_bar[stage], 2 * (kMxAStageBytes + kMxBStageBytes));
@@ -233,6 +255,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
+      if (kTiming && p.timing) p.timing[blockIdx.x * kMxTimingSlots + 3] = prod_wait;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -242,18 +265,33 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint64_t sf_desc0 = make_smem_desc_noswizzle(smem_u32(smem_sf), 128);
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0, set = 0;
+      uint32_t sf_group = 0;                     // groups of four k-blocks taken from the scale ring so far
       bool ok = true;
+      const bool timed = kTiming && p.timing != nullptr;
+      const long long t_begin = timed ? clock64() : 0;
+      long long wait_full = 0, wait_acc = 0, wait_sf = 0;
       for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const long long ta = timed ? clock64() : 0;
         ok = mbar_wait(&aux->acc_empty_bar, acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+        if (timed) wait_acc += clock64() - ta;
         if (!ok) break;
         tc_fence_after_sync();
         for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+          const uint32_t sf_slot = sf_group % kMxSfSlots;
+          if ((kb & 3) == 0) {                   // a new group of scales
+            const long long tq = timed ? clock64() : 0;
+            ok = mbar_wait(&aux->sf_full_bar[sf_slot], (sf_group / kMxSfSlots) & 1, abort_flag, p.status, kStatusMmaTimeout);
+            if (timed) wait_sf += clock64() - tq;
+            if (!ok) break;
+          }
+          const long long tf = timed ? clock64() : 0;
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
+          if (timed) wait_full += clock64() - tf;
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t a_desc = a_desc0 + uint64_t((stage * kMxAStageBytes) >> 4);
           const uint64_t b_desc = b_desc0 + uint64_t((stage * kMxBStageBytes) >> 4);
-          const uint64_t sf_desc = sf_desc0 + uint64_t((stage * kMxSfStageBytes) >> 4);
+          const uint64_t sf_desc = sf_desc0 + uint64_t((sf_slot * kMxSfSlotBytes + uint32_t(kb & 3) * kMxSfStageBytes) >> 4);
           const uint32_t sfa_t = tmem_base + kMxTmemSfa + 16 * set;
           const uint32_t sfb_t = tmem_base + kMxTmemSfb + 16 * set;
           tmem_cp_32x128b_pair(sfa_t, sf_desc);                                             // A rows of this CTA
@@ -268,6 +306,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           // The stage may be refilled once these copies and MMAs have read it -- in both CTAs.
           umma_commit_pair(map_to_cta(&aux->empty_bar[stage], 0));
           umma_commit_pair(map_to_cta(&aux->empty_bar[stage], 1));
+          if ((kb & 3) == 3 || kb == p.num_k_blocks - 1) {       // the group's scales have been copied out -- in both CTAs
+            umma_commit_pair(map_to_cta(&aux->sf_empty_bar[sf_slot], 0));
+            umma_commit_pair(map_to_cta(&aux->sf_empty_bar[sf_slot], 1));
+            ++sf_group;
+          }
           set ^= 1;
           if (++stage == kMxStages) {
             stage = 0;
@@ -279,155 +322,146 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         umma_commit_pair(map_to_cta(&aux->acc_full_bar, 1));
         acc_phase ^= 1;
       }
+      if (timed) {
+        p.timing[blockIdx.x * kMxTimingSlots + 0] = wait_full;
+        p.timing[blockIdx.x * kMxTimingSlots + 1] = wait_acc;
+        p.timing[blockIdx.x * kMxTimingSlots + 2] = clock64() - t_begin;
+        p.timing[blockIdx.x * kMxTimingSlots + 10] = wait_sf;
+      }
     }
-  } else if (warp == 2 && p.sf_bulk_ok) {
-    // ------------------------------------------------------------------ scale loader, bulk path
-    // Lane 0 keeps up to kMxRawSlots boxes in flight (16 scale bytes = four k-blocks of every row of
-    // this CTA's A rows and of the tile's B rows).  When a box has landed, every lane reads the 16
-    // bytes of its twelve rows into registers once and then, k-block by k-block, writes the three
-    // 16-byte pieces that make up its part of the layout tcgen05.cp reads.
-    const int32_t groups_per_tile = (p.num_k_blocks + 3) / 4;
-    int32_t issue_tile = cluster_id, issue_group = 0;      // next box to ask for
-    uint32_t issued = 0, consumed = 0;
-    int stage = 0;
-    uint32_t phase = 0;
+  } else if (warp == 2 || warp == 3) {
+    // ------------------------------------------------------------------ scale loader
+    // Works in groups of four k-blocks, one group per slot of a ring of kMxSfSlots.  A slot goes
+    // free -> box requested -> box landed -> rearranged (sf_full) -> read by tcgen05.cp -> free (sf_empty).
+    // Bulk path: lane 0 keeps boxes in flight (16 scale bytes = four k-blocks of each of this CTA's
+    // 128 A rows and of the tile's 256 B rows, row after row); when one has landed every lane
+    // reads the 16 bytes of its twelve rows and, once all lanes have read, writes them back into the
+    // same slot in the layout tcgen05.cp wants.  Gather path (rows of scales that do not start on
+    // 16-byte boundaries): the lanes fetch the bytes themselves.
+    // Warps 2 and 3 take alternate groups, so each has eight k-blocks' worth of time for one group.
+    const uint32_t groups_per_tile = uint32_t(p.num_k_blocks + 3) / 4;
+    const uint32_t my_tiles = cluster_id < num_tiles ? uint32_t(num_tiles - cluster_id + num_clusters - 1) / uint32_t(num_clusters) : 0u;
+    const uint32_t total_groups = my_tiles * groups_per_tile;
+    const uint32_t first_group = uint32_t(warp - 2);
+    uint32_t gi_issue = first_group;                        // next group whose box lane 0 asks for (bulk path)
     bool ok = true;
-    if (lane == 0) {
+    const bool timed = kTiming && p.timing != nullptr;
+    long long sf_wait_box = 0, sf_wait_slot = 0, sf_work = 0;
+    if (lane == 0 && p.sf_bulk_ok) {
       tma_prefetch_desc(&tmap_sfa);
       tma_prefetch_desc(&tmap_sfb);
     }
-    for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      for (int32_t grp = 0; grp < groups_per_tile && ok; ++grp) {
-        if (lane == 0) {
-          while (issue_tile < num_tiles && issued - consumed < uint32_t(kMxRawSlots)) {
-            int32_t mt, nt, bt;
-            mx_tile_coords(issue_tile, p, &mt, &nt, &bt);
-            const uint32_t slot = issued % kMxRawSlots;
-            uint8_t* raw = smem_raw_sf + slot * kMxRawSlotBytes;
-            mbar_arrive_expect_tx(&aux->raw_full_bar[slot], kMxRawSlotBytes);
-            tma_load_3d(raw, &tmap_sfa, &aux->raw_full_bar[slot], issue_group * 16, mt * kMxTileM + int32_t(rank) * kMxBM, bt);
-            tma_load_3d(raw + kMxRawSfaBytes, &tmap_sfb, &aux->raw_full_bar[slot], issue_group * 16, nt * kMxBN, bt);
-            ++issued;
-            if (++issue_group == groups_per_tile) {
-              issue_group = 0;
-              issue_tile += num_clusters;
+    for (uint32_t gi = first_group; gi < total_groups && ok; gi += 2) {
+      {
+        const uint32_t slot = gi % kMxSfSlots;
+        const uint32_t use = gi / kMxSfSlots;
+        const uint32_t slot_addr = smem_u32(smem_sf) + slot * kMxSfSlotBytes + uint32_t(lane) * 16;
+        uint32_t w[12][4];
+        if (p.sf_bulk_ok) {
+          if (lane == 0) {
+            while (gi_issue < total_groups && gi_issue - gi < uint32_t(kMxSfSlots)) {
+              const uint32_t islot = gi_issue % kMxSfSlots;
+              const uint32_t ipar = ((gi_issue / kMxSfSlots) & 1) ^ 1;
+              const long long ts = timed ? clock64() : 0;
+              if (gi_issue != gi) {              // this group's own box is already on its way: do not stall on a slot still in use
+                if (!mbar_try_wait(&aux->sf_empty_bar[islot], ipar)) break;
+              } else {
+                ok = mbar_wait(&aux->sf_empty_bar[islot], ipar, abort_flag, p.status, kStatusProducerTimeout);
+                if (!ok) break;
+              }
+              if (timed) sf_wait_slot += clock64() - ts;
+              int32_t imt, int_, ibt;
+              mx_tile_coords(cluster_id + int32_t(gi_issue / groups_per_tile) * num_clusters, p, &imt, &int_, &ibt);
+              const int32_t igrp = int32_t(gi_issue % groups_per_tile);
+              uint8_t* raw = smem_sf + islot * kMxSfSlotBytes;
+              mbar_arrive_expect_tx(&aux->raw_full_bar[islot], kMxSfSlotBytes);
+              tma_load_3d(raw, &tmap_sfa, &aux->raw_full_bar[islot], igrp * 16, imt * kMxTileM + int32_t(rank) * kMxBM, ibt);
+              tma_load_3d(raw + kMxRawSfaBytes, &tmap_sfb, &aux->raw_full_bar[islot], igrp * 16, int_ * kMxBN, ibt);
+              gi_issue += 2;
+            }
+            if (ok) {
+              const long long tb = timed ? clock64() : 0;
+              ok = mbar_wait(&aux->raw_full_bar[slot], use & 1, abort_flag, p.status, kStatusProducerTimeout);
+              if (timed) sf_wait_box += clock64() - tb;
             }
           }
-          ok = mbar_wait(&aux->raw_full_bar[consumed % kMxRawSlots], (consumed / kMxRawSlots) & 1, abort_flag, p.status,
-                         kStatusProducerTimeout);
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        (void)mbar_try_wait(&aux->raw_full_bar[consumed % kMxRawSlots], (consumed / kMxRawSlots) & 1);   // every lane observes the phase
-        const uint32_t raw = smem_u32(smem_raw_sf) + (consumed % kMxRawSlots) * kMxRawSlotBytes + uint32_t(lane) * 16;
-        uint32_t w[12][4];
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          (void)mbar_try_wait(&aux->raw_full_bar[slot], use & 1);   // every lane observes the phase
 #pragma unroll
-        for (int g = 0; g < 12; ++g) {      // row lane + 32 g of the box: g 0-3 rows of A, g 4-11 rows of B
-          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(w[g][0]), "=r"(w[g][1]), "=r"(w[g][2]), "=r"(w[g][3])
-                       : "r"(raw + uint32_t(g) * 512));
+          for (int g = 0; g < 12; ++g) {      // row lane + 32 g of the box: g 0-3 rows of A, g 4-11 rows of B
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[g][0]), "=r"(w[g][1]), "=r"(w[g][2]), "=r"(w[g][3])
+                         : "r"(slot_addr + uint32_t(g) * 512)
+                         : "memory");
+          }
+          __syncwarp();                        // every lane has read the box before anyone overwrites it
+        } else {
+          const long long ts = timed ? clock64() : 0;
+          if (lane == 0) ok = mbar_wait(&aux->sf_empty_bar[slot], (use & 1) ^ 1, abort_flag, p.status, kStatusProducerTimeout);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (timed) sf_wait_slot += clock64() - ts;
+          if (!ok) break;
+          int32_t mt, nt, bt;
+          mx_tile_coords(cluster_id + int32_t(gi / groups_per_tile) * num_clusters, p, &mt, &nt, &bt);
+          const int64_t a_row0 = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + lane;
+          const int64_t b_row0 = int64_t(nt) * kMxBN + lane;
+          const uint8_t* sfa_b = p.sfa + int64_t(bt) * p.m * p.scale_cols;
+          const uint8_t* sfb_b = p.sfb + int64_t(bt) * p.n * p.scale_cols;
+          const int64_t col0 = int64_t(gi % groups_per_tile) * 16;
+#pragma unroll
+          for (int g = 0; g < 12; ++g) {
+            const bool is_a = g < 4;
+            const int64_t row = is_a ? a_row0 + 32 * g : b_row0 + 32 * (g - 4);
+            const bool valid = row < (is_a ? p.m : p.n);
+            const uint8_t* src = (is_a ? sfa_b : sfb_b) + (valid ? row * p.scale_cols + col0 : 0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t v = 0;
+              if (valid && col0 + 4 * j < p.scale_cols) {
+                if (p.sf_words_ok) {
+                  v = __ldg(reinterpret_cast<const uint32_t*>(src + 4 * j));
+                } else {
+#pragma unroll
+                  for (int b = 0; b < 4; ++b) {
+                    if (col0 + 4 * j + b < p.scale_cols) v |= uint32_t(__ldg(src + 4 * j + b)) << (8 * b);
+                  }
+                }
+              }
+              w[g][j] = v;
+            }
+          }
         }
-        // The slot may be refilled: order this warp's reads before the next box's write.
-        fence_proxy_async_smem();
-        __syncwarp();
-        ++consumed;
+        const long long tw = timed ? clock64() : 0;
+        // Slot layout read by the issuer: k-block j at j * 1536; there the A rows' block, then the two B blocks;
+        // in a block this lane's 16 bytes are the j-th words of its four rows.
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if (grp * 4 + j < p.num_k_blocks && ok) {
-            if (lane == 0) ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (ok) {
-              const uint32_t dst = smem_u32(smem_sf) + uint32_t(stage) * kMxSfStageBytes + uint32_t(lane) * 16;
 #pragma unroll
-              for (int blk = 0; blk < 3; ++blk) {
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + uint32_t(blk) * kMxSfBlockBytes),
-                             "r"(w[4 * blk][j]), "r"(w[4 * blk + 1][j]), "r"(w[4 * blk + 2][j]), "r"(w[4 * blk + 3][j])
-                             : "memory");
-              }
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) mbar_arrive_cluster(map_to_cta(&aux->full_bar[stage], 0));
-              if (++stage == kMxStages) {
-                stage = 0;
-                phase ^= 1;
-              }
-            }
+          for (int blk = 0; blk < 3; ++blk) {
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(slot_addr + uint32_t(j) * kMxSfStageBytes + uint32_t(blk) * kMxSfBlockBytes),
+                         "r"(w[4 * blk][j]), "r"(w[4 * blk + 1][j]), "r"(w[4 * blk + 2][j]), "r"(w[4 * blk + 3][j])
+                         : "memory");
           }
         }
+        fence_proxy_async_smem();              // the tensor core reads these bytes through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(&aux->sf_full_bar[slot], 0));
+        if (timed) sf_work += clock64() - tw;
       }
     }
-    if (!ok && lane == 0) {
+    if (timed && lane == 0 && warp == 2) {
+      p.timing[blockIdx.x * kMxTimingSlots + 4] = sf_wait_box;
+      p.timing[blockIdx.x * kMxTimingSlots + 5] = sf_wait_slot;
+      p.timing[blockIdx.x * kMxTimingSlots + 6] = sf_work;
+    }
+    if (!ok && lane == 0 && p.sf_bulk_ok) {
       // Abort path: let boxes that were already requested land before the CTA's memory is released.
-      for (; consumed < issued; ++consumed) {
-        for (int i = 0; i < 100000 && !mbar_try_wait(&aux->raw_full_bar[consumed % kMxRawSlots], (consumed / kMxRawSlots) & 1); ++i) {
+      for (int sl = 0; sl < kMxSfSlots; ++sl) {
+        for (int i = 0; i < 100000 && !mbar_try_wait(&aux->raw_full_bar[sl], 0) && !mbar_try_wait(&aux->raw_full_bar[sl], 1); ++i) {
         }
       }
     }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ scale loader, gather path
-    const uint32_t sf_smem0 = smem_u32(smem_sf) + uint32_t(lane) * 16;
-    const int lookahead = p.sf_words_ok ? kMxSfLookahead : 0;
-    int stage = 0, sig_stage = 0, issued = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    auto signal_oldest = [&]() {
-      // The copies of the oldest outstanding k-block are complete for this lane; make them visible to
-      // the tensor core's reads of shared memory, then tell the leader.
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(&aux->full_bar[sig_stage], 0));
-      if (++sig_stage == kMxStages) sig_stage = 0;
-      --issued;
-    };
-    for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      int32_t mt, nt, bt;
-      mx_tile_coords(tile, p, &mt, &nt, &bt);
-      const int64_t a_row0 = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + lane;      // + 32 g
-      const int64_t b_row0 = int64_t(nt) * kMxBN + lane;                                  // + 32 g
-      const uint8_t* sfa_b = p.sfa + int64_t(bt) * p.m * p.scale_cols;
-      const uint8_t* sfb_b = p.sfb + int64_t(bt) * p.n * p.scale_cols;
-      for (int32_t kb = 0; kb < p.num_k_blocks; ++kb) {
-        if (lane == 0) ok = mbar_wait(&aux->empty_bar[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        const uint32_t dst = sf_smem0 + uint32_t(stage) * kMxSfStageBytes;
-        const int64_t kcol = int64_t(kb) * 4;
-#pragma unroll
-        for (int g = 0; g < 12; ++g) {
-          // g 0-3: rows of A (block 0); g 4-11: rows of B (blocks 1 and 2).  Within a block, row group
-          // g % 4 goes to bytes 4 * (g % 4) .. + 3 of every lane's 16.
-          const bool is_a = g < 4;
-          const int64_t row = is_a ? a_row0 + 32 * g : b_row0 + 32 * (g - 4);
-          const bool valid = row < (is_a ? p.m : p.n);
-          const uint8_t* src = (is_a ? sfa_b : sfb_b) + (valid ? row * p.scale_cols + kcol : 0);
-          const uint32_t d = dst + uint32_t(g / 4) * kMxSfBlockBytes + uint32_t(g % 4) * 4;
-          if (p.sf_words_ok) {
-            cp_async_4(d, src, valid ? 4u : 0u);
-          } else {
-            uint32_t w = 0;
-            if (valid) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (kcol + j < p.scale_cols) w |= uint32_t(__ldg(src + j)) << (8 * j);
-              }
-            }
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(d), "r"(w) : "memory");
-          }
-        }
-        cp_async_commit();
-        ++issued;
-        if (issued > lookahead) {
-          cp_async_wait<kMxSfLookahead>();
-          signal_oldest();
-        }
-        if (++stage == kMxStages) {
-          stage = 0;
-          phase ^= 1;
-        }
-      }
-    }
-    cp_async_wait<0>();
-    while (issued > 0) signal_oldest();
   } else if (warp >= kMxFirstEpilogueWarp) {
     // ------------------------------------------------------------------ epilogue (warps 4..11)
     const int q = warp & 3;                               // TMEM lane quarter this warp may access
@@ -435,11 +469,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(col_half * 128);
     uint32_t acc_phase = 0;
     bool ok = true;
+    const bool timed = kTiming && p.timing != nullptr;
+    long long ep_wait = 0, ep_read = 0, ep_store = 0;
     for (int32_t tile = cluster_id; tile < num_tiles; tile += num_clusters) {
       int32_t mt, nt, bt;
       mx_tile_coords(tile, p, &mt, &nt, &bt);
+      const long long t0 = timed ? clock64() : 0;
       if (lane == 0) ok = mbar_wait(&aux->acc_full_bar, acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      const long long t1 = timed ? clock64() : 0;
       if (!ok) break;
       (void)mbar_try_wait(&aux->acc_full_bar, acc_phase);     // every lane observes the completed phase
       tc_fence_after_sync();
@@ -460,6 +498,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         else mbar_arrive(&aux->acc_empty_bar);
       }
       acc_phase ^= 1;
+      const long long t2 = timed ? clock64() : 0;
       const int64_t row = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + q * 32 + lane;
       if (row < p.m) {
         const int64_t row_off = (int64_t(bt) * p.m + row) * p.n;
@@ -469,6 +508,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         mx_store_chunk(p, row_off, col + 64, r2);
         mx_store_chunk(p, row_off, col + 96, r3);
       }
+      if (timed) {
+        ep_wait += t1 - t0;
+        ep_read += t2 - t1;
+        ep_store += clock64() - t2;
+      }
+    }
+    if (timed && warp == kMxFirstEpilogueWarp && lane == 0) {
+      p.timing[blockIdx.x * kMxTimingSlots + 7] = ep_wait;
+      p.timing[blockIdx.x * kMxTimingSlots + 8] = ep_read;
+      p.timing[blockIdx.x * kMxTimingSlots + 9] = ep_store;
     }
   }
 
@@ -490,6 +539,14 @@ Status InitMxKernels() {
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(mx): ") + cudaGetErrorString(e));
   return Status::Ok();
 }
+
+#if B200SD_TUNING
+// Copies the tuning counters of the last block-scaled launch on the current device (kMxTimingSlots per CTA).
+extern "C" int b200sd_debug_read_mx_timing(unsigned long long* out, int count) {
+  cudaDeviceSynchronize();
+  return int(cudaMemcpyFromSymbol(out, g_mx_timing, sizeof(unsigned long long) * size_t(count)));
+}
+#endif
 
 Status ValidateMx(const MxProblem& g) {
   auto f8 = [](int32_t t) { return t == kF8E4M3FN || t == kF8E5M2; };
@@ -556,6 +613,14 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   const int64_t d_elt = g.d_dtype == kF32 ? 4 : 2;
   p.vec_store_ok = ((reinterpret_cast<uintptr_t>(g.d) & 15) == 0 && (g.n * d_elt) % 16 == 0) ? 1 : 0;
   p.status = StatusWordPtr();
+  p.timing = nullptr;
+#if B200SD_TUNING
+  static const bool timing_on = TuningEnvInt("B200SD_TIMING", 0) == 1;
+  if (timing_on) {
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p.timing), g_mx_timing);
+    cudaMemsetAsync(p.timing, 0, sizeof(unsigned long long) * kMxTimingSlots * 512, stream);
+  }
+#endif
 
   const int grid = 2 * int(tiles < max_pairs ? tiles : max_pairs);
   cudaLaunchConfig_t cfg{};

@@ -426,16 +426,6 @@ __host__ __device__ inline uint32_t make_idesc(uint32_t c_format, uint32_t a_for
 }
 
 // ----------------------------------------------------------------------------- MX block-scaled MMA
-// 4-byte asynchronous copy global -> shared; bytes past `src_bytes` (0..4) are written as zero.
-__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
-}
-
 // Shared-memory descriptor of an un-swizzled K-major block of 8-row x 16-byte core matrices that
 // follow one another every `sbo_bytes` (the source operand of tcgen05.cp for scale factors).
 __device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t sbo_bytes) {
