@@ -53,9 +53,10 @@ WORKLOAD_NAME = {
     "c2": "config 2: decode-shape FP8 dot, bf16 output",
     "c3": "config 3: int8 dot + per-row x per-column dequant to bf16",
     "c4": "config 4: row-parallel FP8 dot + sum of the bf16 partials across ranks",
+    "mx": "MX block-scaled FP8 dot (one e8m0 scale per 32 values along K), bf16 output",
 }
 DEFAULT_DIMS = {"c1": (8192, 8192, 8192), "plain": (8192, 8192, 8192), "c2": (64, 28672, 8192),
-                "c3": (4096, 4096, 4096), "c4": (8192, 8192, 28672)}
+                "c3": (4096, 4096, 4096), "c4": (8192, 8192, 28672), "mx": (8192, 8192, 8192)}
 FLOP_PER_CLK_PER_SM = 16384.0      # dense 8-bit tensor rate of one SM: 8192 multiply-adds per clock
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, each from one ncu capture of that kernel at
 # that size on one GPU (bytes).
@@ -84,6 +85,7 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-secondary", action="store_true", help="headline workload only (profiler captures)")
     p.add_argument("--no-sustained", action="store_true")
+    p.add_argument("--secondary-steps", type=int, default=200, help="timed launches per secondary configuration (launch-list captures use fewer)")
     p.add_argument("--sustained-seconds", type=float, default=2.2)
     p.add_argument("--counters", action="store_true", help="print the kernels' own wait counters of the last launch "
                    "(needs the tuning build: B200SD_LIBRARY=xla_b200/lib/libb200_scaled_dot_tuning.so B200SD_TIMING=1)")
@@ -117,6 +119,8 @@ def algorithmic_bytes(kind, m, n, k):
         return m * k + k * n + 2 * m * n + 4 * (m + n)
     if kind == "c1":
         return m * k + k * n + m * n + 2 * n    # e4m3 in, e4m3 out, bf16 bias
+    if kind == "mx":
+        return m * k + k * n + (m + n) * (k // 32) + 2 * m * n
     return m * k + k * n + 2 * m * n            # bf16 out
 
 
@@ -358,7 +362,8 @@ class Bench:
     def make_sets(self, kind, lm, ln, lk, kernel=0, emit_s32=False):
         """Two rotating operand/result sets of one workload, each bound to its own call site."""
         torch = self.torch
-        from xla_b200.scaled_dot import Epilogue, GemmBackendConfig, Int8DotCall, ScaledDotCall
+        from xla_b200.scaled_dot import (BlockScaledDotCall, Buffer, Epilogue, F8E8M0FNU, GemmBackendConfig, Int8DotCall,
+                                         ScaledDotCall)
 
         dev, sets = self.dev, []
         for i in range(2):
@@ -374,6 +379,16 @@ class Bench:
                 if emit_s32:
                     res = [d, torch.empty((lm, ln), dtype=torch.int32, device=dev), ws]
                 call = Int8DotCall(ops, res, selected_algorithm=kernel, emit_s32=emit_s32)
+            elif kind == "mx":
+                g = torch.Generator(device=dev).manual_seed(7000 + i)
+                a = torch.randn((lm, lk), device=dev, generator=g).mul_(4).to(torch.float8_e4m3fn)
+                b = torch.randn((ln, lk), device=dev, generator=g).mul_(4).to(torch.float8_e4m3fn)        # [n, k]: K minor on both
+                sa = torch.randint(121, 132, (lm, lk // 32), dtype=torch.uint8, device=dev, generator=g)
+                sb = torch.randint(121, 132, (ln, lk // 32), dtype=torch.uint8, device=dev, generator=g)
+                d = torch.empty((lm, ln), dtype=torch.bfloat16, device=dev)
+                ops, res = [a, b, sa, sb], [d, ws]
+                call = BlockScaledDotCall([a, b, Buffer(F8E8M0FNU, tuple(sa.shape), sa.data_ptr()),
+                                           Buffer(F8E8M0FNU, tuple(sb.shape), sb.data_ptr())], res)
             else:
                 a, sa = self.f8_operand((lm, lk), 1000 * i + 1)           # A replicated (same seed on every rank) unless K-split
                 b, sb = self.f8_operand((lk, ln), 1000 * i + 2 + 17 * self.rank)
@@ -508,7 +523,7 @@ class Bench:
 
         torch, world = self.torch, self.world
         out = {}
-        steps, warmup = 200, 5
+        steps, warmup = max(3, self.args.secondary_steps), 5
         # config 2: decode shapes, W N-split over the ranks
         k, n = 8192, 28672
         c2 = {}
@@ -549,13 +564,35 @@ class Bench:
                      "kernel": "dense_gemm_kernel<int8, pair>", "launches": int(launches), "n_gpus": 1}
         del sets, check
         torch.cuda.empty_cache()
+        # MX block-scaled dot (one GPU's worth of work per rank; reported for rank 0's device)
+        mm, mn, mk = DEFAULT_DIMS["mx"]
+        sets = self.make_sets("mx", mm, mn, mk)
+        ms, _, launches = self.time_steps(self.make_step("mx", sets, None), min(50, steps), 5)
+        call, ops, res = sets[0]
+        call.execute(self.stream, self.local_rank)
+        torch.cuda.synchronize()
+        rows = np.arange(5, mm, mm // 16)
+        a_np, b_np = ops[0][rows].view(torch.uint8).cpu().numpy(), ops[1].view(torch.uint8).cpu().numpy()
+        sa_np, sb_np = ops[2][rows].cpu().numpy(), ops[3].cpu().numpy()
+        exp = o.bf16_bits_to_f32(o.block_scaled_dot(a_np, b_np, sa_np, sb_np, out_dtype=o.BF16))
+        got = res[0][rows].float().cpu().numpy()
+        # per element: f32 summation-order slack 2^-16 of sum |a_k b_k|, plus one bf16 step
+        slack = np.matmul(np.abs(o.mx_dequantize(a_np, sa_np)), np.abs(o.mx_dequantize(b_np, sb_np)).T) * 2.0 ** -16 + np.abs(exp) * 2.0 ** -7
+        flops = 2.0 * mm * mn * mk
+        out["mx"] = {"workload": WORKLOAD_NAME["mx"], "m": mm, "n": mn, "k": mk, "ms": ms, "value": flops / ms / 1e9, "unit": "TFLOP/s",
+                     "frac": flops / ms / 1e9 / (2.0 * peaks["bf16_tflops"]), "frac_of_nominal_4500": flops / ms / 1e9 / 4500.0,
+                     "mismatches": int((np.abs(got - exp) > slack).sum()),
+                     "checked": f"{len(rows)} rows x {mn} columns against the CPU oracle, |diff| <= 2^-16 sum|a b| + one bf16 step",
+                     "kernel": "mx_gemm_kernel", "launches": int(launches), "n_gpus": 1}
+        del sets
+        torch.cuda.empty_cache()
         # config 4: K-split + sum across ranks
         if world > 1:
             m4, n4, k4 = DEFAULT_DIMS["c4"]
             lm, ln, lk = self.shard("c4", m4, n4, k4)
             sets = self.make_sets("c4", lm, ln, lk)
             runners, how = self.c4_runner(sets, lm, ln, self.args.overlap, self.args.multicast)
-            ms, _, launches = self.time_steps(self.make_step("c4", sets, runners), 50, 5)
+            ms, _, launches = self.time_steps(self.make_step("c4", sets, runners), min(50, steps), 5)
             flops = 2.0 * m4 * n4 * k4
             fp8_peak = 2.0 * peaks["bf16_tflops"]
             t_tensor = flops / world / (fp8_peak * 1e9)
@@ -627,8 +664,13 @@ def gpu_arm(args):
     e2e = None if args.no_e2e else B.e2e(kind, sets, runners, steps)
 
     flops = 2.0 * m * n * k
+    peaks = measured_peaks()
+    # The other configurations come BEFORE the seconds-long sustained run: that run drives the GPU into its power
+    # cap (SM clock about 1.2 GHz), and a bandwidth-bound decode launch timed right behind it is 20 % slower than
+    # on a GPU at its normal clocks.
+    secondary = None if (args.no_secondary or kind != "c1" or (args.m or args.n or args.k)) else B.secondary(peaks)
     sustained = None
-    if not args.no_sustained and kind in ("c1", "plain", "c3"):
+    if not args.no_sustained and kind in ("c1", "plain", "c3", "mx"):
         n_steps = max(steps, int(math.ceil(args.sustained_seconds * 1e3 / ms)))
         s_ms, s_clocks, _ = B.time_steps(step, n_steps, 3, sample_clocks=True)
         rate = flops / world / s_ms / 1e9
@@ -636,12 +678,9 @@ def gpu_arm(args):
                      "unit": "TFLOP/s" if kind != "c3" else "TOP/s", "clocks": s_clocks}
         if s_clocks and s_clocks.get("sm_mhz"):
             sustained["frac_of_tensor_rate_at_median_clock"] = rate * 1e12 / (148 * FLOP_PER_CLK_PER_SM * s_clocks["sm_mhz"] * 1e6)
-    peaks = measured_peaks()
-    if sustained is not None:
         sustained["frac_of_2x_bf16_sustained"] = flops / world / sustained["ms_per_step"] / 1e9 / (2.0 * peaks["bf16_tflops_sustained"])
     del sets, runners, step
     torch.cuda.empty_cache()
-    secondary = None if (args.no_secondary or kind != "c1" or (args.m or args.n or args.k)) else B.secondary(peaks)
     if rank != 0:
         if world > 1:
             B.dist.destroy_process_group()
@@ -677,7 +716,7 @@ def gpu_arm(args):
     roof["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get((kind, m, n, k)) if world == 1 else None
     c2_kernel = args.kernel or B.lib.select_kernel(lm, ln, lk)
     roof["kernel"] = {"c2": "skinny_gemm_kernel" if c2_kernel == 2 else "dense_gemm_kernel<fp8, single>",
-                      "c3": "dense_gemm_kernel<int8, pair>"}.get(kind, "dense_gemm_kernel<fp8, pair>")
+                      "c3": "dense_gemm_kernel<int8, pair>", "mx": "mx_gemm_kernel"}.get(kind, "dense_gemm_kernel<fp8, pair>")
     parallelism = ("single GPU" if world == 1 else
                    (f"K-split x{world}, sum {c4_how}" if kind == "c4" else f"N-split x{world}, no collective"))
     line = {
@@ -698,7 +737,7 @@ def gpu_arm(args):
         line["secondary"] = secondary
     if counters is not None:
         line["counters"] = counters
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and kind != "mx":
         line["cpu_baseline"] = cpu_arm((kind, (m, n, k)), budget_s=20.0, steps=3, warmup=1)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -752,6 +791,17 @@ def cublaslt_arm(args):
         if kind == "c3":
             sets.append((torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev, generator=g),
                          torch.randint(-127, 128, (k, n), dtype=torch.int8, device=dev, generator=g), None))
+        elif kind == "mx":
+            # cuBLASLt wants each scale tensor as 128-row x 4-column blocks stored as 32 x 16 bytes.
+            def blocked(s):
+                r, c = s.shape
+                t = s.view(r // 128, 128, c // 4, 4).permute(0, 2, 1, 3).reshape(-1, 4, 32, 4).transpose(1, 2)
+                return t.reshape(-1).contiguous().view(torch.float8_e8m0fnu)
+            a = torch.randn((m, k), device=dev, generator=g).to(torch.float8_e4m3fn)
+            bt = torch.randn((n, k), device=dev, generator=g).to(torch.float8_e4m3fn)
+            sa = torch.randint(121, 132, (m, k // 32), dtype=torch.uint8, device=dev, generator=g)
+            sb = torch.randint(121, 132, (n, k // 32), dtype=torch.uint8, device=dev, generator=g)
+            sets.append((a, bt, (blocked(sa), blocked(sb))))
         else:
             a = torch.randn((m, k), device=dev, generator=g).to(torch.float8_e4m3fn)
             bt = torch.randn((n, k), device=dev, generator=g).to(torch.float8_e4m3fn)     # column-major B, as cuBLASLt wants it
@@ -762,6 +812,8 @@ def cublaslt_arm(args):
         a, b, bias = sets[i & 1]
         if kind == "c3":
             torch._int_mm(a, b)
+        elif kind == "mx":
+            torch._scaled_mm(a, b.t(), scale_a=bias[0], scale_b=bias[1], out_dtype=torch.bfloat16)
         else:
             torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, bias=bias, out_dtype=torch.bfloat16, use_fast_accum=True)
 

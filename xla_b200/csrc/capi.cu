@@ -246,7 +246,8 @@ Status ValidateS8(const B200SD_DotS8& in, GemmProblem* g, bool check_pointers = 
   if (a.m % 16 || a.n % 16 || a.k % 16) return Status::Error(kInvalidArgument, "m, n and k must be multiples of 16");
   if (a.m > (1ll << 30) || a.n > (1ll << 30) || a.k > (1ll << 30)) return Status::Error(kInvalidArgument, "dimension too large");
   if (a.kernel == B200SD_KERNEL_SKINNY || a.kernel < B200SD_KERNEL_AUTO || a.kernel > B200SD_KERNEL_DENSE_STREAMK) return Status::Error(kInvalidArgument, "integer dots run on the dense kernel only");
-  if (a.k > 133144) return Status::Error(kInvalidArgument, "k too large for exact s32 accumulation of s8 products");
+  // |sum| <= k * (-128 * -128) = k * 2^14 must stay below 2^31.
+  if (a.k >= 131072) return Status::Error(kInvalidArgument, "k too large for exact s32 accumulation of s8 products (k must be below 131072)");
   if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return Status::Error(kInvalidArgument, "contracting dimensions must be 0 or 1");
   g->m = a.m; g->n = a.n; g->k = a.k;
   g->int8 = true;
