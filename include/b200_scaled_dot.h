@@ -245,7 +245,7 @@ int b200sd_stream_wait_counter(void* cuda_stream, const uint32_t* counter, uint3
  * xla/backends/gpu/collectives/nccl_communicator.cc:557-592 execute.
  *
  * Every rank calls this with its own K-shard in `args` (a, b, scales; args->d = d[rank]; bf16
- * result, no epilogue).  The rows are dealt out to the ranks in sub-blocks.  Rank r pushes the bf16
+ * result, no epilogue).  The rows are dealt out to the ranks in sub-blocks.  (Default, push mode:) rank r pushes the bf16
  * partial of the sub-blocks it does not own into the owner's `stage` buffer while its tensor cores
  * work on the next tile; for a sub-block it owns it adds the partials the others pushed (in rank
  * order, in f32, rounded once) and writes the finished rows into every rank's `d`.  When the
@@ -285,6 +285,14 @@ typedef struct B200SD_PeerReduce {
                           finished rows then leave this GPU once and the switch replicates them */
   /* Added later: a caller whose struct_size stops before this field gets the default. */
   uint32_t peer_wait_ms; /* limit of every wait for another rank, milliseconds; 0 = 10000 */
+  int32_t pull;          /* 1: partials stay in the producing rank's own `stage` buffer (at the rows of the block's owner) and
+                            the owner fetches them when it reaches its rows -- the reduce-scatter half of the multimem
+                            all-reduce of xla/stream_executor/gpu/all_reduce_kernel_lib.cu.h:99-357 done inside the dot's
+                            kernel.  Nothing is pushed from the epilogue of a foreign tile and, with `stage_multicast`, each
+                            partial crosses NVLink once and is added inside the switch */
+  void* stage_multicast; /* pull: optional NVSwitch multicast address bound to every rank's stage (same offset): the owner's
+                            fetch is one multimem.ld_reduce (f32 accumulation in the switch, one rounding to bf16; the order
+                            of the additions is the switch's).  NULL: plain peer loads added in rank order */
 } B200SD_PeerReduce;
 
 int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200SD_PeerReduce* peers, void* cuda_stream,

@@ -17,8 +17,11 @@ def _f8(shape, gen, dev):
     return torch.randn(shape, device=dev, generator=gen).to(torch.float8_e4m3fn)
 
 
+@pytest.mark.parametrize("pull", [0, 1])
 @pytest.mark.parametrize("world,m,n,k_per_rank", [(2, 1024, 768, 384), (4, 2048, 512, 256), (2, 512, 272, 128), (1, 512, 256, 256)])
-def test_emulated_ranks_match_sum_of_bf16_partials(cuda_device, world, m, n, k_per_rank):
+def test_emulated_ranks_match_sum_of_bf16_partials(cuda_device, world, m, n, k_per_rank, pull):
+    """pull = 1: the partials stay in the producing rank's staging buffer and the owner of the rows fetches them
+    (here, on one GPU, with plain loads in rank order; the in-switch sum needs real peers)."""
     dev = cuda_device
     gen = torch.Generator(device=dev).manual_seed(100 * world + m)
     lib = _native.product
@@ -45,7 +48,7 @@ def test_emulated_ranks_match_sum_of_bf16_partials(cuda_device, world, m, n, k_p
                                        a_dtype=20, b_dtype=20, d_dtype=16, lhs_contracting_dim=1, rhs_contracting_dim=0,
                                        epilogue=0, alpha=1.0, beta=0.0, kernel=0)
         peers = _native.PeerReduceArgs(struct_size=C.sizeof(_native.PeerReduceArgs), world=world, rank=0, emulate_ranks=world,
-                                       epoch=epoch)
+                                       epoch=epoch, pull=pull)
         for r in range(world):
             peers.d[r], peers.stage[r], peers.flags[r] = d[r].data_ptr(), stage[r].data_ptr(), flags[r].data_ptr()
             peers.emu_a[r], peers.emu_b[r] = a[r].data_ptr(), b[r].data_ptr()

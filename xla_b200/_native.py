@@ -98,6 +98,8 @@ class PeerReduceArgs(C.Structure):
         ("emu_a", C.c_void_p * 8), ("emu_b", C.c_void_p * 8),
         ("d_multicast", C.c_void_p),
         ("peer_wait_ms", C.c_uint32),
+        ("pull", C.c_int32),
+        ("stage_multicast", C.c_void_p),
     ]
 
 

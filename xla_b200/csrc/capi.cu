@@ -379,7 +379,11 @@ int b200sd_scaled_dot_f8_peer_reduce(const B200SD_ScaledDotF8* args, const B200S
   r.emulate = peers->emulate_ranks;
   r.epoch = peers->epoch;
   r.d_multicast = peers->d_multicast;
-  r.peer_wait_ms = peers->struct_size >= sizeof(B200SD_PeerReduce) ? peers->peer_wait_ms : 0;
+  r.peer_wait_ms = peers->struct_size >= offsetof(B200SD_PeerReduce, pull) ? peers->peer_wait_ms : 0;
+  if (peers->struct_size >= sizeof(B200SD_PeerReduce)) {
+    r.pull = peers->pull;
+    r.stage_multicast = peers->stage_multicast;
+  }
   if (r.peer_wait_ms > 600000u) return CopyStatus(Status::Error(kInvalidArgument, "peer_wait_ms above ten minutes"), err, err_len);
   for (int i = 0; i < kMaxPeers; ++i) {
     r.d[i] = peers->d[i];

@@ -98,6 +98,8 @@ struct ReduceArgs {
   uint64_t peer_wait_ns;          // limit of a wait for another rank
   uint16_t* d[kMaxPeers];
   uint16_t* d_multicast;          // optional: NVSwitch multicast address covering every rank's D
+  int32_t pull;                   // partials stay in the producing rank's staging buffer; the owner of the rows fetches them
+  uint16_t* stage_multicast;      // pull: optional multicast address covering every rank's staging buffer (in-switch sum)
   uint16_t* stage[kMaxPeers];
   uint32_t* flags[kMaxPeers];
   const CUtensorMap* emu_maps;    // emulate: A and B maps of rank r at [2r], [2r+1]
@@ -330,7 +332,7 @@ __device__ __forceinline__ void reduce_chunk(const DenseArgs& p, const uint32_t 
     const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale);
     w[i] = *reinterpret_cast<const uint32_t*>(&h);
   }
-  if (blk == my_rank && p.red.world > 1) {
+  if (blk == my_rank && p.red.world > 1 && !p.red.pull) {
     // The other ranks' partials are requested four ranks at a time before any is used: one memory
     // latency per group instead of one per rank.
     float acc[kChunk];
@@ -382,7 +384,18 @@ __device__ __forceinline__ void reduce_chunk(const DenseArgs& p, const uint32_t 
 // `byte_col` / `row` are the coordinates of the stage's first element in the destination matrix.
 __device__ __forceinline__ void flush_store_stage(const DenseArgs& p, const ReduceMaps& maps, const uint4* stage,
                                                   int32_t my_rank, int32_t blk, int64_t row0, int64_t row0_in_block,
-                                                  int64_t rows_per_block, int64_t col0, int lane) {
+                                                  int64_t rows_per_block, int64_t col0, int lane, bool partial_to_own_stage = false) {
+  if (partial_to_own_stage) {
+    // Pull mode: every partial, of foreign rows and of own rows alike, goes to THIS rank's staging buffer, at the
+    // rows of the block's owner; the owner fetches it from there.
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (col0 < p.n) tma_store_2d(&maps.stage[my_rank], stage, int32_t(col0 * 2), int32_t(int64_t(blk) * rows_per_block + row0_in_block));
+      tma_store_commit();
+    }
+    return;
+  }
   if (blk == my_rank && p.red.d_multicast != nullptr) {
     __syncwarp();
     const int unit = lane & 7;
@@ -991,7 +1004,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
           const int64_t prow = int64_t(own_mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
-          for (int32_t s = 0; s < p.red.world; ++s) {
+          for (int32_t s = 0; s < p.red.world && !p.red.pull; ++s) {
             if (s == my_rank) continue;
             const uint16_t* line = p.red.stage[my_rank] + (int64_t(s) * rows_per_block + prow) * p.n + col_base;
             if (col_base < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
@@ -1083,7 +1096,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           if ((ci & 3) == 3) {             // 64 columns staged: write them out as full lines
             const int64_t warp_row0r = row - lane;
             flush_store_stage(p, rmaps, store_stage, my_rank, blk, warp_row0r, own_row - lane, rows_per_block,
-                              col_base + c0 - 3 * kChunk, lane);
+                              col_base + c0 - 3 * kChunk, lane, p.red.pull != 0 && p.red.world > 1);
           }
         } else {
           flush_group(ci);
@@ -1096,7 +1109,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         // tile later, when its stores have long been performed.
         if (lane == 0) {
           if (pending_flag != nullptr) {
-            if (blk == my_rank && p.red.d_multicast != nullptr) tma_store_wait_all<0>();   // this tile added no groups
+            if (blk == my_rank && p.red.d_multicast != nullptr && !p.red.pull) tma_store_wait_all<0>();   // this tile added no groups
             else tma_store_wait_all<2>();                                                  // all but this tile's two
             asm volatile("fence.proxy.async.global;" ::: "memory");
             red_release_sys_add_u32(pending_flag, 1u);
@@ -1129,6 +1142,77 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if (++acc == kAccBufs) {
         acc = 0;
         acc_phase ^= 1;
+      }
+      if constexpr (kReduce) {
+        if (p.red.pull && blk == my_rank && p.red.world > 1) {
+          // Pull mode, own rows.  The accumulator is back with the issuer, this rank's partial is on its way to its
+          // own staging buffer, and every other rank has said (flag wait above) that its partial is in ITS staging
+          // buffer.  Fetch the sum -- one multimem.ld_reduce per 16 bytes when the staging buffers are bound to an
+          // NVSwitch multicast address, else plain peer loads added in rank order -- and send the finished rows
+          // to every rank's D the same way the push mode does.
+          if (lane == 0) {
+            tma_store_wait_all<0>();                                   // own partial (and everything before it) is in memory
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            if (pending_flag != nullptr) {
+              red_release_sys_add_u32(pending_flag, 1u);
+              pending_flag = nullptr;
+            }
+          }
+          __syncwarp();
+          const int unit = lane & 7;
+          const int64_t stage_row0 = int64_t(my_rank) * rows_per_block + own_row - lane;
+          const int64_t d_row0 = row - lane;
+#pragma unroll 1
+          for (int gi = 0; gi < kColsPerEpilogueWarp / 64; ++gi) {
+            const int64_t gcol0 = col_base + gi * 64;
+            const int64_t col = gcol0 + unit * 8;
+            uint4 v[8];
+            if (col < p.n) {
+              if (p.red.stage_multicast != nullptr) {
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const int rrow = it * 4 + (lane >> 3);
+                  v[it] = multimem_ld_reduce_bf16x8(p.red.stage_multicast + (stage_row0 + rrow) * p.n + col);
+                }
+              } else {
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const int rrow = it * 4 + (lane >> 3);
+                  float acc8[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) acc8[i] = 0.0f;
+                  for (int32_t s = 0; s < p.red.world; ++s) {
+                    const uint4 x = __ldcg(reinterpret_cast<const uint4*>(p.red.stage[s] + (stage_row0 + rrow) * p.n + col));
+                    const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[i]));
+                      acc8[2 * i] += f.x;
+                      acc8[2 * i + 1] += f.y;
+                    }
+                  }
+                  uint32_t o[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(acc8[2 * i], acc8[2 * i + 1]);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&h);
+                  }
+                  v[it] = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+              }
+            }
+            if (lane == 0) tma_store_wait_read<0>();      // the stage's previous contents have left
+            __syncwarp();
+            if (col < p.n) {
+#pragma unroll
+              for (int it = 0; it < 8; ++it) {
+                const int rrow = it * 4 + (lane >> 3);
+                store_stage[rrow * 8 + (unit ^ (rrow & 7))] = v[it];
+              }
+            }
+            flush_store_stage(p, rmaps, store_stage, my_rank, blk, d_row0, own_row - lane, rows_per_block, gcol0, lane);
+          }
+        }
       }
     }
     if constexpr (kReduce) {
@@ -1612,6 +1696,8 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
 #endif
   q.emu_maps = nullptr;
   q.d_multicast = r.emulate ? nullptr : static_cast<uint16_t*>(r.d_multicast);
+  q.pull = r.pull ? 1 : 0;
+  q.stage_multicast = (r.emulate || !r.pull) ? nullptr : static_cast<uint16_t*>(r.stage_multicast);
 
   auto make_maps = [&](const void* a, const void* b, CUtensorMap* ta, CUtensorMap* tb) {
     Status s = g.a_mn_major ? MakeBatchedByteMatrixMap(ta, a, 1, g.k, g.m, 128, kBK) : MakeBatchedByteMatrixMap(ta, a, 1, g.m, g.k, kBK, kBM);

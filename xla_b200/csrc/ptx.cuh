@@ -115,6 +115,17 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
                : "memory");
 }
 
+// One 16-byte load through an NVSwitch multicast address: the switch reads the eight bf16 values at this
+// offset in EVERY GPU bound to the address, adds them up in f32 and returns the sums rounded to bf16.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
 // Bounded wait until the counter has reached `target` (wrap-safe: counters only grow).  Same
 // abort / status protocol as mbar_wait.
 __device__ __forceinline__ bool counter_wait(const uint32_t* counter, uint32_t target, volatile int* abort_flag,

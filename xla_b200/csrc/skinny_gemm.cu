@@ -689,9 +689,8 @@ extern "C" int b200sd_scaled_dot_f8_decode_noalloc(const B200SD_ScaledDotF8* arg
   if (size_t(grid) * size_t(g.m) * kTileN * sizeof(float) > kStaticPartialBytes)
     return fail(kInvalidArgument, "problem does not fit the built-in scratch");
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  // The array still holds the previous call's flags; they must read zero before any CTA publishes.
-  e = cudaMemsetAsync(p.flags, 0, kFlagBytes, stream);
-  if (e != cudaSuccess) return fail(kInternal, std::string("cudaMemsetAsync(flags): ") + cudaGetErrorString(e));
+  // The array still holds the previous call's flags: they carry that call's epoch value, which no CTA of this
+  // call takes for its own, so nothing has to be cleared first.
   const size_t smem_bytes = 1024 + size_t(stages) * stage_bytes + sizeof(SkinnyAux);
   skinny_gemm_kernel<<<int(grid), kThreads, smem_bytes, stream>>>(tmap_w, tmap_a, p);
   e = cudaGetLastError();

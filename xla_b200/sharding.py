@@ -209,13 +209,18 @@ class PeerReducedRowParallelScaledDot:
     a mapping of every other rank's buffers.  All ranks must call the object the same number of
     times: the call count is the protocol's epoch.
 
+    `pull=True` selects the form in which no partial is pushed: every rank keeps its partials in its own
+    staging buffer and the owner of a row block fetches their sum (`multimem.ld_reduce` through the NVSwitch
+    when a multicast mapping exists, so each partial crosses NVLink once and is added in the switch).
+
     A rank that is late by more than `peer_wait_ms` makes its peers' waits give up: the kernels
     drain, the device status word gets bit 32 and the result is incomplete.  `check()` reads the
     status word; when it reports a failure on any rank, `rearm()` (a collective: every rank must
     call it) puts the protocol back to its initial state.
     """
 
-    def __init__(self, m: int, n: int, group=None, device=None, multicast: bool = True, peer_wait_ms: int = 0):
+    def __init__(self, m: int, n: int, group=None, device=None, multicast: bool = True, peer_wait_ms: int = 0,
+                 pull: bool = False):
         import ctypes as C
 
         import torch
@@ -250,6 +255,12 @@ class PeerReducedRowParallelScaledDot:
         mc = getattr(self._handles[0], "multicast_ptr", 0) if (multicast and self.world > 1) else 0
         self.peers.d_multicast = mc or None
         self.multicast = bool(mc)
+        # Pull mode: partials stay with their producer and the owner of the rows fetches them -- through the
+        # switch's in-network sum when the staging buffers have a multicast mapping, by peer loads otherwise.
+        self.peers.pull = 1 if pull else 0
+        smc = getattr(self._handles[1], "multicast_ptr", 0) if (pull and multicast and self.world > 1) else 0
+        self.peers.stage_multicast = smc or None
+        self.pull, self.in_switch_sum = bool(pull), bool(smc)
         self._err = C.create_string_buffer(512)
 
     def __call__(self, a_shard, b_shard, a_scale, b_scale, *, lhs_contracting_dim: int = 1, rhs_contracting_dim: int = 0):
