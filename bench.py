@@ -74,8 +74,9 @@ def parse_args():
     p.add_argument("--overlap", type=int, default=-1, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory, 1 = NCCL all-reduce of finished row blocks "
                    "on a second stream, 0 = dot then one NCCL all-reduce; default: 2 up to 4 GPUs, 0 beyond (measured faster)")
     p.add_argument("--multicast", type=int, default=0, help="c4 fused: write finished rows through the NVSwitch multicast mapping")
-    p.add_argument("--pull", type=int, default=-1, help="c4 fused: 1 = partials stay with their producer and the owner of the rows fetches their sum "
-                   "(in the switch with --multicast 1), 0 = partials are pushed to the owner; default: measured best per GPU count")
+    p.add_argument("--pull", type=int, default=-1, help="c4 fused: 1 / 2 = partials stay with their producer and the owner of the rows fetches their sum "
+                   "(in the switch with --multicast 1; 2 = piecewise during the next round), 0 = partials are pushed to the owner; "
+                   "default: measured best per GPU count")
     p.add_argument("--ar-rows", type=int, default=2048, help="c4 overlap: rows of D per all-reduce")
     p.add_argument("--gemm-ctas", type=int, default=132, help="c4 overlap: SMs the dot may occupy")
     p.add_argument("--nccl-ctas", type=int, default=16, help="c4 overlap: CTAs the collective may use (0 = NCCL's choice)")
@@ -420,14 +421,15 @@ class Bench:
             overlap = 2 if self.world <= 4 else 0
         if overlap == 2:
             pull = max(0, args.pull)
-            fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=self.dev, multicast=bool(multicast), pull=bool(pull))
+            fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=self.dev, multicast=bool(multicast), pull=int(pull))
                      for _ in sets]
             runners = [(lambda f=f, ops=ops: f(ops[0], ops[1], ops[2], ops[3])) for f, (_, ops, _) in zip(fused, sets)]
             for i, f in enumerate(fused):                            # results now land in the symmetric buffers
                 sets[i] = (sets[i][0], sets[i][1], [f.out] + list(sets[i][2][1:]))
             how = "formed inside the dot's kernel over peer memory (no collective launch"
             if pull:
-                how += ", partials fetched by the rows' owner" + (" and added in the NVSwitch" if fused[0].in_switch_sum else " with peer loads")
+                how += (", partials fetched by the rows' owner" if pull == 1 else ", partials fetched piecewise by all warps of the rows' owner during the next round") + \
+                    (" and added in the NVSwitch" if fused[0].in_switch_sum else " with peer loads")
             return runners, how + (", finished rows via NVSwitch multicast)" if fused[0].multicast else ")")
         if overlap == 1:
             group = None

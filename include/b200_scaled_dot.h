@@ -285,11 +285,15 @@ typedef struct B200SD_PeerReduce {
                           finished rows then leave this GPU once and the switch replicates them */
   /* Added later: a caller whose struct_size stops before this field gets the default. */
   uint32_t peer_wait_ms; /* limit of every wait for another rank, milliseconds; 0 = 10000 */
-  int32_t pull;          /* 1: partials stay in the producing rank's own `stage` buffer (at the rows of the block's owner) and
+  int32_t pull;          /* 1 or 2: partials stay in the producing rank's own `stage` buffer (at the rows of the block's owner) and
                             the owner fetches them when it reaches its rows -- the reduce-scatter half of the multimem
                             all-reduce of xla/stream_executor/gpu/all_reduce_kernel_lib.cu.h:99-357 done inside the dot's
                             kernel.  Nothing is pushed from the epilogue of a foreign tile and, with `stage_multicast`, each
-                            partial crosses NVLink once and is added inside the switch */
+                            partial crosses NVLink once and is added inside the switch.  1: the warp that computed a tile of
+                            own rows fetches that tile's sum; 2: the sums of one round's own rows are fetched in pieces of
+                            8 rows x 64 columns by all warps of the rank during the next round (two pieces per tile, loads
+                            issued before the tile's epilogue and sent on after it), so the reduction's traffic is spread
+                            over the kernel and only the last round's is left for its end */
   void* stage_multicast; /* pull: optional NVSwitch multicast address bound to every rank's stage (same offset): the owner's
                             fetch is one multimem.ld_reduce (f32 accumulation in the switch, one rounding to bf16; the order
                             of the additions is the switch's).  NULL: plain peer loads added in rank order */

@@ -45,15 +45,23 @@ def _worker(rank, world, port, m, n, k, multicast, pull):
             torch.cuda.synchronize()
             assert device_status() == 0
             if fused.pull and fused.in_switch_sum:
-                # The switch adds the bf16 partials in f32 in an order of its own and rounds once: the same value as the
-                # rank-order sum except where the f32 sums differ in their last bits across a bf16 rounding boundary.
+                # The switch adds the bf16 partials in f32 in an order of its own and rounds once, by a rule of its own:
+                # with two ranks the order cannot matter, and results still differ from round-to-nearest-even of the
+                # f32 sum -- by at most one bf16 step.
                 want = acc.bfloat16().float()
-                assert bool(((out.float() - want).abs() <= 2.0 ** -7 * want.abs() + 1e-30).all()), f"rank {rank} call {call}"
+                diff = (out.float() - want).abs()
+                bad = diff > 2.0 ** -7 * want.abs() + 1e-30
+                assert not bool(bad.any()), (f"rank {rank} call {call}: {int(bad.sum())} of {bad.numel()} beyond one bf16 step, "
+                                             f"largest difference {float(diff.max())} where the sum is {float(want[diff == diff.max()][0])}")
+                if rank == 0 and call == 0:
+                    print(f"in-switch sum: {int((diff > 0).sum())} of {diff.numel()} elements differ from the rank-order sum")
             else:
                 assert torch.equal(out, acc.bfloat16()), f"rank {rank} call {call}"
             # and close to the unsplit dot: each bf16 partial and the sum carry one rounding of 2^-9
             full = cublas_lt_matmul_f8(a, b, sa, sb, out_dtype=torch.float32)[0]
-            bound = 2.0 ** -8 * (sum(p.float().abs() for p in parts) + full.abs()) + 1e-6
+            # (the switch's final rounding is not round-to-nearest-even: one whole bf16 step there instead of half a step)
+            step = 2.0 ** -7 if (fused.pull and fused.in_switch_sum) else 2.0 ** -8
+            bound = step * (sum(p.float().abs() for p in parts) + full.abs()) + 1e-6
             assert bool(((out.float() - full).abs() <= bound).all())
             dist.barrier()                   # the next call's operands are regenerated; keep the ranks in step
     finally:
@@ -61,8 +69,9 @@ def _worker(rank, world, port, m, n, k, multicast, pull):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("multicast,pull", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("multicast,pull", [(False, 0), (True, 0), (False, 1), (True, 1), (False, 2), (True, 2)])
 def test_peer_reduced_dot_on_two_gpus(multicast, pull):
-    """push / pull, each with and without the NVSwitch multicast mappings (pull + multicast = in-switch sum)."""
+    """push / pull by the own tile's warp / pull spread over the next round, each with and without the NVSwitch
+    multicast mappings (pull + multicast = in-switch sum)."""
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), 1024, 768, 512, multicast, pull), nprocs=world, join=True)

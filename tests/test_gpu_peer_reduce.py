@@ -17,11 +17,13 @@ def _f8(shape, gen, dev):
     return torch.randn(shape, device=dev, generator=gen).to(torch.float8_e4m3fn)
 
 
-@pytest.mark.parametrize("pull", [0, 1])
-@pytest.mark.parametrize("world,m,n,k_per_rank", [(2, 1024, 768, 384), (4, 2048, 512, 256), (2, 512, 272, 128), (1, 512, 256, 256)])
+@pytest.mark.parametrize("pull", [0, 1, 2])
+@pytest.mark.parametrize("world,m,n,k_per_rank", [(2, 1024, 768, 384), (4, 2048, 512, 256), (2, 512, 272, 128), (1, 512, 256, 256),
+                                                  (2, 4096, 2048, 128)])      # several tiles per cluster and round
 def test_emulated_ranks_match_sum_of_bf16_partials(cuda_device, world, m, n, k_per_rank, pull):
-    """pull = 1: the partials stay in the producing rank's staging buffer and the owner of the rows fetches them
-    (here, on one GPU, with plain loads in rank order; the in-switch sum needs real peers)."""
+    """pull = 1 / 2: the partials stay in the producing rank's staging buffer and the owner of the rows fetches them,
+    tile by tile (1) or in pieces spread over the next round (2) -- here, on one GPU, with plain loads in rank order;
+    the in-switch sum needs real peers."""
     dev = cuda_device
     gen = torch.Generator(device=dev).manual_seed(100 * world + m)
     lib = _native.product

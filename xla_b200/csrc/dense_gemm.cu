@@ -38,6 +38,8 @@ constexpr int kAccBufs = 2;
 constexpr int kAStageBytes = kBM * kBK;          // 16 KiB
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kReducerWarps = 2;                     // peer-reduce instantiation only: warps that fetch and forward the sums of own rows
+constexpr int kReduceThreads = kThreads + 32 * kReducerWarps;
 constexpr int kColsPerEpilogueWarp = kBN / 2;    // warps 2-5 take columns 0-127, warps 6-9 columns 128-255
 constexpr int kTmemCols = 512;
 
@@ -634,7 +636,7 @@ __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t 
 }
 
 template <bool kInt8, bool kPair, bool kReduce = false>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kReduce ? kReduceThreads : kThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid_constant__ CUtensorMap tmap_b_param,
                   const DenseArgs p, const __grid_constant__ ReduceMaps rmaps) {
   static_assert(!kReduce || (kPair && !kInt8), "peer-reduce mode exists for the FP8 pair kernel only");
@@ -874,6 +876,106 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         p.timing[blockIdx.x * kTimingSlots + 11] = global_timer_ns();
       }
     }
+  } else if (kReduce && warp >= 2 + kEpilogueWarps) {
+    // ------------------------------------------------------------------ reducer warps (peer reduce, pull == 2)
+    // The rows this rank owns are cut into pieces of 8 rows x 64 columns, round by round; the reducer warps of
+    // the rank share them out.  A piece is complete when every rank -- this one included -- has raised the flag
+    // of the (tile, warp) part it lies in; its sum is then fetched (one multimem.ld_reduce per 16 bytes when the
+    // staging buffers have a multicast mapping: the switch reads every rank's partial and adds them up; else
+    // peer loads added in rank order) and written to every rank's D (multimem.st, else one store per rank).
+    // Nothing of this touches the accumulators, so the tensor cores never wait for NVLink: the traffic of round r
+    // flows while round r + 1 is computed, and only the last round's is left for the end of the kernel.
+    if constexpr (kReduce) {
+      if (p.red.pull == 2 && p.red.world > 1) {
+        constexpr int kBatch = 8;                                    // pieces in flight per warp (16 x 16 bytes per lane)
+        const int32_t mtps = p.red.m_tiles_per_block / p.red.stages;
+        const int64_t rows_per_block = int64_t(p.red.m_tiles_per_block) * S::kTileRows;
+        const int32_t ncp = int32_t((p.n + 63) / 64);
+        const int32_t pieces = mtps * (S::kTileRows / 8) * ncp;     // per round
+        const int32_t n_red = tile_step * 2 * kReducerWarps;        // reducer warps of this rank
+        const int32_t me = (first_tile * 2 + int32_t(rank)) * kReducerWarps + (warp - 2 - kEpilogueWarps);
+        bool ok = true;
+        for (int32_t round = 0; round < p.red.stages && ok; ++round) {
+          for (int32_t q0 = me; q0 < pieces && ok; q0 += kBatch * n_red) {
+            uint4 v[2 * kBatch];
+            uint32_t have = 0;
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+              const int32_t qi = q0 + u * n_red;
+              if (qi >= pieces || !ok) continue;
+              const int32_t row_piece = qi / ncp, col_piece = qi - row_piece * ncp;
+              const int32_t r_in_sub = row_piece * 8;
+              const int64_t col0p = int64_t(col_piece) * 64;
+              const int32_t f_slot = (round * mtps + r_in_sub / S::kTileRows) * p.num_n_tiles + int32_t(col0p / kBN);
+              const int32_t f_cta = (r_in_sub % S::kTileRows) / kBM;
+              const int32_t f_ew = int32_t((col0p % kBN) / kColsPerEpilogueWarp) * 4 + ((((r_in_sub % kBM) / 32) + 2) & 3);
+              const int32_t f_index = (f_slot * 2 + f_cta) * kEpilogueWarps + f_ew;
+              if (lane == 0) ok = counter_wait(p.red.flags[my_rank] + f_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
+              ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+              if (!ok) continue;
+              have |= 1u << u;
+              const int64_t own_row = int64_t(round) * mtps * S::kTileRows + r_in_sub;
+              const int64_t col = col0p + (lane & 7) * 8;
+              if (col >= p.n) continue;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int64_t off = (int64_t(my_rank) * rows_per_block + own_row + (lane >> 3) + 4 * h) * p.n + col;
+                if (p.red.stage_multicast != nullptr) {
+                  v[u * 2 + h] = multimem_ld_reduce_bf16x8(p.red.stage_multicast + off);
+                } else {
+                  float acc8[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) acc8[i] = 0.0f;
+                  for (int32_t sr = 0; sr < p.red.world; ++sr) {
+                    const uint4 x = __ldcg(reinterpret_cast<const uint4*>(p.red.stage[sr] + off));
+                    const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[i]));
+                      acc8[2 * i] += f.x;
+                      acc8[2 * i + 1] += f.y;
+                    }
+                  }
+                  uint32_t o[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(acc8[2 * i], acc8[2 * i + 1]);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                  }
+                  v[u * 2 + h] = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+              if (!(have & (1u << u))) continue;
+              const int32_t qi = q0 + u * n_red;
+              const int32_t row_piece = qi / ncp, col_piece = qi - row_piece * ncp;
+              const int64_t grow = (int64_t(round) * p.red.world + my_rank) * mtps * S::kTileRows + row_piece * 8;
+              const int64_t col = int64_t(col_piece) * 64 + (lane & 7) * 8;
+              if (col >= p.n) continue;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int64_t off = (grow + (lane >> 3) + 4 * h) * p.n + col;
+                if (p.red.d_multicast != nullptr) {
+                  multimem_st_v4(p.red.d_multicast + off, v[u * 2 + h]);
+                } else {
+                  for (int32_t j = 0; j < p.red.world; ++j) *reinterpret_cast<uint4*>(p.red.d[j] + off) = v[u * 2 + h];
+                }
+              }
+            }
+          }
+        }
+        // End of call, like the epilogue warps: this warp's rows are in every rank's D.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          for (int32_t j = 0; j < p.red.world; ++j) red_release_sys_add_u32(p.red.flags[j] + p.red.done_index, 1u);
+          (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
+        }
+        __syncwarp();
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;                      // TMEM lane quarter this warp may access
@@ -897,6 +999,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    // Peer reduce, pull == 2: the sums of own rows are fetched by the CTA's two reducer warps (below), not here;
+    // the epilogue only parks every partial in this rank's staging buffer and raises the flag -- also its own.
+    [[maybe_unused]] const bool spread = kReduce && p.red.pull == 2 && p.red.world > 1;
+
     // Stream-K: index of the item that finishes a tile other clusters worked on (-1: none).
     const int32_t fin_it = (!kReduce && work.fin_tile >= 0 && work.fin_kb0 > 0) ? work.n_items - 1 : -1;
     for (int32_t it = 0; it < work.n_items; ++it) {
@@ -989,7 +1095,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       uint32_t* const my_flag_base = kReduce ? p.red.flags[my_rank] : nullptr;
       const int32_t flag_index = (slot * 2 + int32_t(rank)) * kEpilogueWarps + ew;
       if constexpr (kReduce) {
-        if (blk == my_rank && p.red.world > 1) {
+        if (blk == my_rank && p.red.world > 1 && !spread) {
           // An own tile: the other ranks pushed their partials long ago.  Confirm that, and pull
           // them towards the L2 while the tensor cores are still busy with this tile.  A flag this
           // warp still owes another rank goes out first: no rank may wait for a peer while it
@@ -997,7 +1103,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           if (lane == 0 && pending_flag != nullptr) {
             tma_store_wait_all<0>();
             asm volatile("fence.proxy.async.global;" ::: "memory");
-            red_release_sys_add_u32(pending_flag, 1u);
+            red_relaxed_sys_add_u32(pending_flag, 1u);
             pending_flag = nullptr;
           }
           if (lane == 0) ok = counter_wait(my_flag_base + flag_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
@@ -1112,10 +1218,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
             if (blk == my_rank && p.red.d_multicast != nullptr && !p.red.pull) tma_store_wait_all<0>();   // this tile added no groups
             else tma_store_wait_all<2>();                                                  // all but this tile's two
             asm volatile("fence.proxy.async.global;" ::: "memory");
-            red_release_sys_add_u32(pending_flag, 1u);
+            red_relaxed_sys_add_u32(pending_flag, 1u);
             pending_flag = nullptr;
           }
-          if (blk != my_rank) pending_flag = p.red.flags[blk] + flag_index;
+          if (blk != my_rank || spread) pending_flag = p.red.flags[blk] + flag_index;
         }
       }
       if (!kReduce && item.mode == 1) {
@@ -1144,7 +1250,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         acc_phase ^= 1;
       }
       if constexpr (kReduce) {
-        if (p.red.pull && blk == my_rank && p.red.world > 1) {
+        if (p.red.pull == 1 && blk == my_rank && p.red.world > 1) {
           // Pull mode, own rows.  The accumulator is back with the issuer, this rank's partial is on its way to its
           // own staging buffer, and every other rank has said (flag wait above) that its partial is in ITS staging
           // buffer.  Fetch the sum -- one multimem.ld_reduce per 16 bytes when the staging buffers are bound to an
@@ -1154,7 +1260,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
             tma_store_wait_all<0>();                                   // own partial (and everything before it) is in memory
             asm volatile("fence.proxy.async.global;" ::: "memory");
             if (pending_flag != nullptr) {
-              red_release_sys_add_u32(pending_flag, 1u);
+              red_relaxed_sys_add_u32(pending_flag, 1u);
               pending_flag = nullptr;
             }
           }
@@ -1219,7 +1325,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       if (lane == 0) {
         tma_store_wait_all<0>();
         asm volatile("fence.proxy.async.global;" ::: "memory");
-        if (pending_flag != nullptr) red_release_sys_add_u32(pending_flag, 1u);
+        if (pending_flag != nullptr) red_relaxed_sys_add_u32(pending_flag, 1u);
+        pending_flag = nullptr;
       }
       // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
       // warp of every rank has said the same, so that D is complete here when the kernel ends and
@@ -1309,7 +1416,7 @@ cudaError_t LaunchOne(int grid, cudaStream_t stream, const CUtensorMap& ta, cons
   static const ReduceMaps no_maps{};
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kReduce ? kReduceThreads : kThreads, 1, 1);
   cfg.dynamicSmemBytes = DenseSmemBytes<kPair, kReduce>();
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1696,7 +1803,20 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
 #endif
   q.emu_maps = nullptr;
   q.d_multicast = r.emulate ? nullptr : static_cast<uint16_t*>(r.d_multicast);
-  q.pull = r.pull ? 1 : 0;
+  q.pull = ((r.pull == 1 || r.pull == 2) && r.world > 1) ? r.pull : 0;
+  if (q.pull == 2) {
+    q.flag_target = r.epoch * uint32_t(r.world);      // a rank's own partial counts like every other
+    q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps + kReducerWarps);
+    // As many rounds as leave every cluster about two tiles per round: the sums of a round flow while the next is
+    // computed, and only the last round's are left for the end of the kernel.
+    int best = 1;
+    for (int d = 1; d <= q.m_tiles_per_block; ++d) {
+      if (q.m_tiles_per_block % d == 0 && tiles / d >= 2ll * clusters_per_rank) best = d;
+    }
+    if (best == 1 && q.m_tiles_per_block % 2 == 0) best = 2;
+    q.stages = best;
+    if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
+  }
   q.stage_multicast = (r.emulate || !r.pull) ? nullptr : static_cast<uint16_t*>(r.stage_multicast);
 
   auto make_maps = [&](const void* a, const void* b, CUtensorMap* ta, CUtensorMap* tb) {

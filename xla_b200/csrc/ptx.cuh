@@ -108,6 +108,14 @@ __device__ __forceinline__ void red_release_sys_add_u32(uint32_t* p, uint32_t v)
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// The same add without release semantics, for a flag that follows bulk (TMA) stores whose COMPLETION the thread has
+// already waited for (cp.async.bulk.wait_group + fence.proxy.async): the data is performed at its destination's L2
+// before this instruction is issued, so nothing is left for a release to order -- and a system-scope release would
+// first wait for the acknowledgement of every earlier remote operation of the warp, one NVLink round trip per flag.
+__device__ __forceinline__ void red_relaxed_sys_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // One 16-byte store that NVSwitch replicates into every GPU bound to the multicast address.
 __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),

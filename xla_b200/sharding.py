@@ -209,9 +209,11 @@ class PeerReducedRowParallelScaledDot:
     a mapping of every other rank's buffers.  All ranks must call the object the same number of
     times: the call count is the protocol's epoch.
 
-    `pull=True` selects the form in which no partial is pushed: every rank keeps its partials in its own
-    staging buffer and the owner of a row block fetches their sum (`multimem.ld_reduce` through the NVSwitch
-    when a multicast mapping exists, so each partial crosses NVLink once and is added in the switch).
+    `pull` selects the forms in which no partial is pushed: every rank keeps its partials in its own staging
+    buffer and the owner of a row block fetches their sum (`multimem.ld_reduce` through the NVSwitch when a
+    multicast mapping exists, so each partial crosses NVLink once and is added in the switch).  pull=1: the warp
+    that computed an own tile fetches that tile's sum right away; pull=2: the sums of a round's own rows are
+    fetched in small pieces by all warps during the next round, which spreads the traffic over the kernel.
 
     A rank that is late by more than `peer_wait_ms` makes its peers' waits give up: the kernels
     drain, the device status word gets bit 32 and the result is incomplete.  `check()` reads the
@@ -220,7 +222,7 @@ class PeerReducedRowParallelScaledDot:
     """
 
     def __init__(self, m: int, n: int, group=None, device=None, multicast: bool = True, peer_wait_ms: int = 0,
-                 pull: bool = False):
+                 pull: int = 0):
         import ctypes as C
 
         import torch
@@ -257,10 +259,10 @@ class PeerReducedRowParallelScaledDot:
         self.multicast = bool(mc)
         # Pull mode: partials stay with their producer and the owner of the rows fetches them -- through the
         # switch's in-network sum when the staging buffers have a multicast mapping, by peer loads otherwise.
-        self.peers.pull = 1 if pull else 0
+        self.peers.pull = int(pull)
         smc = getattr(self._handles[1], "multicast_ptr", 0) if (pull and multicast and self.world > 1) else 0
         self.peers.stage_multicast = smc or None
-        self.pull, self.in_switch_sum = bool(pull), bool(smc)
+        self.pull, self.in_switch_sum = int(pull), bool(smc)
         self._err = C.create_string_buffer(512)
 
     def __call__(self, a_shard, b_shard, a_scale, b_scale, *, lhs_contracting_dim: int = 1, rhs_contracting_dim: int = 0):
