@@ -57,7 +57,6 @@ struct __align__(16) DenseAux {
   uint64_t empty_bar[Shape<kPair>::kStages];
   uint64_t acc_full_bar[kAccBufs];
   uint64_t acc_empty_bar[kAccBufs];
-  uint64_t preload_bar;      // stream-K: the finishing share's accumulator holds the earlier shares' sum
   uint64_t pad_;
   uint32_t tmem_base;
   int abort_flag;
@@ -208,9 +207,11 @@ __device__ __forceinline__ void tile_coords(int32_t tile, const DenseArgs& p, in
 }
 
 // What one cluster does, in order: its share of the stream-K tail that does NOT finish a tile
-// (accumulator dumped to the workspace), its whole tiles, then the share that finishes a tile
-// (earlier shares of that tile, dumped by lower-numbered clusters as the first thing they did,
-// are added before the epilogue).  Finishers therefore never wait for work that has not started.
+// (accumulator dumped to the workspace), then the share that finishes a tile (the earlier shares of
+// that tile, dumped by lower-numbered clusters as the first thing they did, are added in its
+// epilogue), then its whole tiles.  Finishers therefore never wait for work that has not started,
+// and both short epilogues run under the main loop of a following item: the one epilogue left
+// exposed at the end of the kernel is that of an ordinary tile.
 struct WorkItem {
   int32_t tile, kb0, kb1;
   int32_t mode;            // 0 whole tile, 1 dump a partial, 2 finish a tile others contributed to
@@ -271,11 +272,14 @@ __device__ __forceinline__ WorkItem get_item(const WorkList& w, const DenseArgs&
     }
     --it;
   }
-  if (it < w.dp_count) {
-    x.tile = w.first_tile + it * w.tile_step; x.kb0 = 0; x.kb1 = p.num_k_blocks; x.mode = 0;
-    return x;
+  if (w.fin_tile >= 0) {
+    if (it == 0) {
+      x.tile = w.fin_tile; x.kb0 = w.fin_kb0; x.kb1 = p.num_k_blocks; x.mode = w.fin_kb0 > 0 ? 2 : 0;
+      return x;
+    }
+    --it;
   }
-  x.tile = w.fin_tile; x.kb0 = w.fin_kb0; x.kb1 = p.num_k_blocks; x.mode = w.fin_kb0 > 0 ? 2 : 0;
+  x.tile = w.first_tile + it * w.tile_step; x.kb0 = 0; x.kb1 = p.num_k_blocks; x.mode = 0;
   return x;
 }
 
@@ -687,7 +691,6 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       mbar_init(&aux->acc_full_bar[b], 1);
       mbar_init(&aux->acc_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
-    mbar_init(&aux->preload_bar, kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     aux->abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -811,15 +814,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
         if (kTiming && p.timing) wait_acc += clock64() - tw0;
         if (!ok) break;
-        if (item.mode == 2) {       // the epilogue warps have put the earlier shares' sum into this accumulator
-          const long long tp0 = (kTiming && p.timing) ? clock64() : 0;
-          ok = mbar_wait(&aux->preload_bar, 0, abort_flag, p.status, kStatusMmaTimeout);
-          if (kTiming && p.timing) p.timing[blockIdx.x * kTimingSlots + 7] = clock64() - tp0;
-          if (!ok) break;
-        }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        const bool preloaded = item.mode == 2;
+        constexpr bool preloaded = false;
         for (int32_t kb = item.kb0; kb < item.kb1; ++kb) {
           const long long tw1 = (kTiming && p.timing) ? clock64() : 0;
           ok = mbar_wait(&aux->full_bar[stage], phase, abort_flag, p.status, kStatusMmaTimeout);
@@ -1003,78 +1000,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
     // the epilogue only parks every partial in this rank's staging buffer and raises the flag -- also its own.
     [[maybe_unused]] const bool spread = kReduce && p.red.pull == 2 && p.red.world > 1;
 
-    // Stream-K: index of the item that finishes a tile other clusters worked on (-1: none).
-    const int32_t fin_it = (!kReduce && work.fin_tile >= 0 && work.fin_kb0 > 0) ? work.n_items - 1 : -1;
     for (int32_t it = 0; it < work.n_items; ++it) {
-      if (!kReduce && fin_it > 0 && it == fin_it - 1) {
-        // The accumulator the finishing share will use is free (this warp has read item it-1's
-        // values out of its part).  Fill this warp's part with the sum of the shares that
-        // lower-numbered clusters dumped when they started, so that the MMAs continue from it and
-        // nothing is left to add at the end.  Runs under the main loop of item `it`.
-        constexpr int kWarpPartU4 = kColsPerEpilogueWarp * 32 / 4;
-        constexpr size_t kSlotU4 = kSkPartialBytes / sizeof(uint4);
-        const int warp_part = int(rank) * kEpilogueWarps + ew;
-        const int32_t clusters = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
-        const int64_t tile_start = int64_t(work.fin_tile - p.dp_tiles) * p.num_k_blocks;
-        int32_t first_contrib = cluster_id;
-        while (first_contrib > 0 && sk_bound(p, first_contrib, clusters) > tile_start) --first_contrib;
-        if (lane == 0) {
-          for (int32_t c = cluster_id - 1; c >= first_contrib && ok; --c) {
-            const unsigned long long* f = p.sk_flags + c * 2 * kEpilogueWarps + warp_part;
-            uint64_t t0 = 0;
-            uint32_t polls = 0;
-            while (ld_acquire_gpu_u64(f) != p.sk_epoch) {
-              if ((++polls & 1023u) == 0) {
-                const uint64_t now = global_timer_ns();
-                if (t0 == 0) t0 = now;
-                if (*abort_flag || now - t0 > kWaitLimitNs) {
-                  *abort_flag = 1;
-                  atomicOr(p.status, kStatusFixupTimeout);
-                  ok = false;
-                  break;
-                }
-              }
-            }
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        for (int32_t c = cluster_id - 1; c >= first_contrib; --c)    // every lane acquires before it reads the partials
-          (void)ld_acquire_gpu_u64(p.sk_flags + c * 2 * kEpilogueWarps + warp_part);
-        const uint32_t taddr_fin =
-            tmem_base + (uint32_t(q * 32) << 16) + uint32_t((fin_it & 1) * kBN + col_half * kColsPerEpilogueWarp);
-#pragma unroll 1
-        for (int c0 = 0; c0 < kColsPerEpilogueWarp; c0 += kChunk) {
-          uint32_t r[kChunk];
-#pragma unroll
-          for (int i = 0; i < kChunk; ++i) r[i] = 0u;
-          for (int32_t c = first_contrib; c < cluster_id; ++c) {
-            const uint4* src = p.sk_partials + size_t(c) * kSlotU4 + warp_part * kWarpPartU4 + (c0 / kChunk) * 128 + lane;
-            uint4 v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = __ldcg(src + j * 32);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (kInt8) {
-                r[4 * j] += v[j].x; r[4 * j + 1] += v[j].y; r[4 * j + 2] += v[j].z; r[4 * j + 3] += v[j].w;
-              } else {
-                r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(v[j].x));
-                r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(v[j].y));
-                r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(v[j].z));
-                r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(v[j].w));
-              }
-            }
-          }
-          tmem_st_32x16(taddr_fin + c0, r);
-        }
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if (kPair && rank != 0) mbar_arrive_cluster(map_to_cta(&aux->preload_bar, 0));
-          else mbar_arrive(&aux->preload_bar);
-        }
-      }
       const WorkItem item = get_item(work, p, it);
       const int32_t tile = item.tile;
       int32_t mt, nt, bt = 0;
@@ -1140,6 +1066,56 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
 #pragma unroll
         for (int j = 0; j < 4; ++j) dst[j * 32] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
       };
+      // The finishing share: the clusters [first_contrib, cluster_id) dumped the earlier shares of this tile as the
+      // first thing they did; their flags are confirmed here and their values added chunk by chunk below.
+      int32_t first_contrib = cluster_id;
+      if (!kReduce && item.mode == 2) {
+        const int32_t clusters = kPair ? int32_t(gridDim.x >> 1) : int32_t(gridDim.x);
+        const int64_t tile_start = int64_t(item.tile - p.dp_tiles) * p.num_k_blocks;
+        while (first_contrib > 0 && sk_bound(p, first_contrib, clusters) > tile_start) --first_contrib;
+        if (lane == 0) {
+          for (int32_t c = cluster_id - 1; c >= first_contrib && ok; --c) {
+            const unsigned long long* f = p.sk_flags + c * 2 * kEpilogueWarps + warp_part;
+            uint64_t t0 = 0;
+            uint32_t polls = 0;
+            while (ld_acquire_gpu_u64(f) != p.sk_epoch) {
+              if ((++polls & 1023u) == 0) {
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (*abort_flag || now - t0 > kWaitLimitNs) {
+                  *abort_flag = 1;
+                  atomicOr(p.status, kStatusFixupTimeout);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        for (int32_t c = cluster_id - 1; c >= first_contrib; --c)    // every lane acquires before it reads the partials
+          (void)ld_acquire_gpu_u64(p.sk_flags + c * 2 * kEpilogueWarps + warp_part);
+      }
+      auto sk_add = [&](uint32_t (&r)[kChunk], int c0) {
+        for (int32_t c = first_contrib; c < cluster_id; ++c) {
+          const uint4* src = p.sk_partials + size_t(c) * kSlotU4 + warp_part * kWarpPartU4 + (c0 / kChunk) * 128 + lane;
+          uint4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = __ldcg(src + j * 32);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (kInt8) {
+              r[4 * j] += v[j].x; r[4 * j + 1] += v[j].y; r[4 * j + 2] += v[j].z; r[4 * j + 3] += v[j].w;
+            } else {
+              r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + __uint_as_float(v[j].x));
+              r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + __uint_as_float(v[j].y));
+              r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + __uint_as_float(v[j].z));
+              r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + __uint_as_float(v[j].w));
+            }
+          }
+        }
+      };
 
       const int64_t row_in_batch = int64_t(mt) * S::kTileRows + int64_t(rank) * kBM + q * 32 + lane;
       const bool row_ok = row_in_batch < p.m;
@@ -1181,6 +1157,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         const long long tl1 = (kTiming && p.timing) ? clock64() : 0;
         ep_ld += tl1 - tl0;
         const int64_t col0 = col_base + c0;
+        if (!kReduce && item.mode == 2) sk_add(cur, c0);
         if (!kReduce && item.mode == 1) {
           sk_dump(cur, c0);
         } else if (col0 < p.n && row_ok) {
