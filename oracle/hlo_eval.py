@@ -30,6 +30,8 @@ _INT = {"s8": np.int8, "s32": np.int32, "s64": np.int64, "u8": np.uint8, "u32": 
 def _to_f32(t, v):
     if t in _KIND:
         return o.fp8_decode(v, _KIND[t])
+    if t == "f8e8m0fnu":
+        return o.e8m0_decode(v)
     if t == "bf16":
         return o.bf16_bits_to_f32(v)
     if t == "f16":
@@ -41,6 +43,8 @@ def _from_f32(t, x):
     x = np.asarray(x, np.float32)
     if t in _KIND:
         return o.fp8_encode(x, _KIND[t])
+    if t == "f8e8m0fnu":
+        return o.e8m0_encode(x)
     if t == "bf16":
         return o.f32_to_bf16_bits(x)
     if t == "f16":
@@ -306,6 +310,12 @@ def evaluate(text, params):
                 val = (t, _dot(np.asarray(lv, np.float64).astype(np.float32), np.asarray(rv, np.float64).astype(np.float32), lc, rc, lb, rb).astype(_INT[t]))
             else:
                 val = (t, _from_f32(t, _dot(_to_f32(lt, lv), _to_f32(rt, rv), lc, rc, lb, rb)))
+        elif op == "custom-call" and '"__op$block_scaled_dot"' in attrs:
+            # block_scaling_rewriter.h:30-77; evaluated as the expansion of block_scaling_rewriter.cc:194-262
+            (lt, lv), (rt, rv), (st, sv), (ut, uv) = a[:4]
+            assert len(a) == 4 and st == ut == "f8e8m0fnu", "only the MX form (f8e8m0fnu scales, no global scale) is evaluated"
+            code = {"f32": o.F32, "bf16": o.BF16, "f16": o.F16}[t]
+            val = (t, o.block_scaled_dot(lv, rv, sv, uv, a_kind=_KIND[lt], b_kind=_KIND[rt], out_dtype=code))
         elif op == "tuple":
             val = ("tuple", tuple(v for _, v in a))
         elif op == "get-tuple-element":

@@ -43,6 +43,8 @@ def make_inputs(hlo: str, seed: int):
         if t in ("f8e4m3fn", "f8e5m2"):
             v = rng.uniform(-0.25, 0.25, size=dims).astype(np.float32)
             out.append(o.fp8_encode(v, "e4m3fn" if t == "f8e4m3fn" else "e5m2"))
+        elif t == "f8e8m0fnu":
+            out.append(rng.integers(121, 132, size=dims, dtype=np.uint8))        # block scales 2^-6 .. 2^4
         elif t == "s8":
             out.append(rng.integers(-127, 128, size=dims, dtype=np.int8))
         elif t == "pred":
@@ -58,6 +60,8 @@ def make_inputs(hlo: str, seed: int):
 def to_f32(t: str, v):
     if t in ("f8e4m3fn", "f8e5m2"):
         return o.fp8_decode(v, "e4m3fn" if t == "f8e4m3fn" else "e5m2")
+    if t == "f8e8m0fnu":
+        return o.e8m0_decode(v)
     if t == "bf16":
         return o.bf16_bits_to_f32(v)
     if t == "f16":

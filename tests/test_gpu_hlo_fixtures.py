@@ -298,3 +298,19 @@ def test_two_layer_mlp_module(cuda_device):
     # the hidden activation is an e4m3 value: where the kernel's GELU lands on the other side of a rounding boundary it is one
     # e4m3 step (up to 12.5 %) away, which the second dot averages over 256 terms
     assert o.near_mismatches(o.bf16_bits_to_f32(exp), o.bf16_bits_to_f32(back(got)), 2e-2, 2e-2)[0] == 0
+
+
+def test_block_scaled_dot_module(cuda_device):
+    """`__op$block_scaled_dot` with MX operands: rewritten onto b200$block_scaled_dot$mx, run through the FFI boundary,
+    compared with the interpreter's evaluation of the same text (which equals the reference's expansion,
+    tests/test_mx_hlo.py)."""
+    text = load("block_scaled_dot_mx")
+    a, b, sa, sb = o.make_mx_operands(77, 16, 32, 256, batch=4)
+    exp = hlo_eval.evaluate(text, [a, b, sa, sb])
+    got, stats = hlo_runner.run_hlo_module(text, [to_dev(a, "f8e4m3fn", cuda_device), to_dev(b, "f8e4m3fn", cuda_device),
+                                                  to_dev(sa, "u8", cuda_device).view(torch.float8_e8m0fnu),
+                                                  to_dev(sb, "u8", cuda_device).view(torch.float8_e8m0fnu)], return_stats=True)
+    torch.cuda.synchronize()
+    assert stats["custom_calls"] == 1
+    absdot = np.matmul(np.abs(o.mx_dequantize(a, sa)).astype(np.float64), np.swapaxes(np.abs(o.mx_dequantize(b, sb)).astype(np.float64), -1, -2))
+    assert (np.abs(back(got).astype(np.float64) - exp) <= absdot * 2.0 ** -16 + np.abs(exp) * 2.0 ** -23).all()

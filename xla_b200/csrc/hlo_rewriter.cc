@@ -111,6 +111,7 @@ struct Gemm {
   int64_t batch = 0, m = 0, n = 0, k = 0;         // logical (unpadded) extents; m x n is the result AS COMPUTED
   bool has_c = false, has_bias = false, has_d_scale = false, has_dequant = false;
   bool swapped = false;                // operands were exchanged to produce a column-major result as D^T
+  bool mx = false;                     // MX block-scaled dot: operands a, b, a_scale, b_scale (thunk_emitter.cc:939-988)
   Instr* amax = nullptr;               // the f32[] second result, when damax
   Instr* acc = nullptr;                // the s32 second result, when emit_s32
   size_t ScaleIndex() const { return has_c ? 3 : 2; }
@@ -331,7 +332,7 @@ bool IsAnyF8(const std::string& t) { return t.rfind("f8", 0) == 0; }
 double F8Max(const std::string& t) { return t == "f8e4m3fn" ? 448.0 : 57344.0; }
 int TypeCode(const std::string& t) {       // xla::PrimitiveType numbers
   static const std::map<std::string, int> k = {{"pred", 1}, {"s8", 2}, {"s32", 4}, {"f16", 10}, {"f32", 11}, {"bf16", 16},
-                                               {"f8e5m2", 19}, {"f8e4m3fn", 20}};
+                                               {"f8e5m2", 19}, {"f8e4m3fn", 20}, {"f8e8m0fnu", 33}};
   auto it = k.find(t);
   return it == k.end() ? 0 : it->second;
 }
@@ -384,9 +385,10 @@ class Rewriter {
       else if (i->opcode == "add") HandleAdd(i);
       else if (i->opcode == "maximum") HandleMaximum(i);
       else if (i->opcode == "convert") HandleConvert(i);
+      else if (i->opcode == "custom-call" && i->attrs.find("\"__op$block_scaled_dot\"") != std::string::npos) HandleBlockScaledDot(i);
     }
     for (Instr* g : calls_) {
-      if (!IsLive(g)) continue;
+      if (!IsLive(g) || g->gemm->mx) continue;
       if (!g->gemm->f8) FoldInt8Dequantisation(g);
       FoldNarrowingConvert(g);
     }
@@ -479,7 +481,8 @@ class Rewriter {
     double v;
     return BcastConst(x, &v) && std::fabs(v - want) <= rel * std::max(1.0, std::fabs(want));
   }
-  static bool IsGemm(Instr* x) { return x != nullptr && x->gemm != nullptr; }
+  // A call this pass made that may still absorb users (the MX call takes no epilogue, thunk_emitter.cc:939-988).
+  static bool IsGemm(Instr* x) { return x != nullptr && x->gemm != nullptr && !x->gemm->mx; }
   static bool IsF8Gemm(Instr* x) { return IsGemm(x) && x->gemm->f8; }
   static Instr* Other(Instr* bin, Instr* a) {             // binary op with operands {a, other} in any order -> other
     if (bin->operands.size() != 2) return nullptr;
@@ -805,6 +808,49 @@ class Rewriter {
       result = Add("bitcast", dot->shape, {result}, "", "", "gemm_view");
     }
     Replace(dot, result);
+  }
+
+  // `__op$block_scaled_dot` (xla/backends/gpu/transforms/block_scaling_rewriter.h:30-77): operands lhs, rhs,
+  // lhs_scale, rhs_scale [, global_scale]; contracting dimension minor on both inputs, an optional batch
+  // dimension major.  The reference either expands it into dequantize + dot (block_scaling_rewriter.cc:194-262)
+  // or hands it to a library; with MX operands (FP8 values, one f8e8m0fnu scale per 32) it becomes this
+  // library's block-scaled call, which takes the four operands as they are.  Everything else is left alone.
+  void HandleBlockScaledDot(Instr* cc) {
+    if (cc->operands.size() == 5) return Refuse(cc, "block-scaled dot with a global scale: not taken by the MX call (exactly four operands, thunk_emitter.cc:939-988)");
+    if (cc->operands.size() != 4) return Refuse(cc, "block-scaled dot must have four operands");
+    const Shape& a = cc->operands[0]->shape;
+    const Shape& b = cc->operands[1]->shape;
+    const Shape& sa = cc->operands[2]->shape;
+    const Shape& sb = cc->operands[3]->shape;
+    const Shape& d = cc->shape;
+    if (!IsF8(a.type) || !IsF8(b.type)) return Refuse(cc, "block-scaled dot: only f8e4m3fn / f8e5m2 values are implemented, got " + a.type + " and " + b.type);
+    if (sa.type != "f8e8m0fnu" || sb.type != "f8e8m0fnu") return Refuse(cc, "block-scaled dot: scales must be f8e8m0fnu (MX), got " + sa.type + " and " + sb.type);
+    if (!(d.type == "f32" || d.type == "bf16" || d.type == "f16")) return Refuse(cc, "block-scaled dot: result must be f32, bf16 or f16");
+    const size_t rank = a.dims.size();
+    if ((rank != 2 && rank != 3) || b.dims.size() != rank || sa.dims.size() != rank || sb.dims.size() != rank || d.dims.size() != rank)
+      return Refuse(cc, "block-scaled dot: operands must have rank 2, or rank 3 with one leading batch dimension");
+    for (const Shape* sh : {&a, &b, &sa, &sb, &d})
+      if (!sh->IsDefaultLayout()) return Refuse(cc, "block-scaled dot: operands must be in the default (row-major) layout");
+    const size_t o = rank - 2;
+    const int64_t m = a.dims[o], k = a.dims[o + 1], n = b.dims[o];
+    if (b.dims[o + 1] != k) return Refuse(cc, "block-scaled dot: contracting dimensions differ");
+    if (k % 32 != 0 || sa.dims[o] != m || sb.dims[o] != n || sa.dims[o + 1] * 32 != k || sb.dims[o + 1] * 32 != k)
+      return Refuse(cc, "block-scaled dot: the block size must be 32 (scales [rows, k / 32])");
+    if (d.dims[o] != m || d.dims[o + 1] != n) return Refuse(cc, "block-scaled dot: result shape is not [m, n]");
+    if (rank == 3 && !(b.dims[0] == a.dims[0] && sa.dims[0] == a.dims[0] && sb.dims[0] == a.dims[0] && d.dims[0] == a.dims[0]))
+      return Refuse(cc, "block-scaled dot: batch dimensions differ");
+    auto g = std::make_unique<Gemm>();
+    g->f8 = true;
+    g->mx = true;
+    g->m = m; g->n = n; g->k = k;
+    g->batched = rank == 3;
+    g->batch = rank == 3 ? a.dims[0] : 0;
+    g->lhs_contracting = int(rank) - 1;
+    g->rhs_contracting = int(rank) - 1;
+    Instr* call = Add("custom-call", cc->shape, cc->operands, "", "", "mx_gemm");
+    call->gemm = std::move(g);
+    calls_.push_back(call);
+    Replace(cc, call);
   }
 
   // gemm, or slice(gemm), or bitcast(gemm), or bitcast(slice(gemm)) -- with one user each below the top.
@@ -1264,9 +1310,11 @@ std::string Rewriter::EmitHlo(const Module& m) const {
       const Gemm& g = *i->gemm;
       o << "  " << i->name << ".call = " << CallTupleShape(i).ToString() << " custom-call(";
       for (size_t k = 0; k < i->operands.size(); ++k) o << (k ? ", " : "") << i->operands[k]->name;
-      o << "), custom_call_target=\"" << (g.f8 ? "b200$scaled_dot$f8" : "b200$dot$s8")
+      o << "), custom_call_target=\"" << (g.mx ? "b200$block_scaled_dot$mx" : g.f8 ? "b200$scaled_dot$f8" : "b200$dot$s8")
         << "\", api_version=API_VERSION_TYPED_FFI, backend_config={";
-      if (g.f8) {
+      if (g.mx) {
+        o << "alpha_real = " << F64(g.alpha) << " : f64}\n";
+      } else if (g.f8) {
         o << "alpha_real = " << F64(g.alpha) << " : f64, beta = " << F64(g.beta) << " : f64, epilogue = " << g.epilogue
           << " : i32, lhs_contracting_dim = " << g.lhs_contracting << " : i64, rhs_contracting_dim = " << g.rhs_contracting
           << " : i64, damax_output = " << (g.damax ? "true" : "false")
@@ -1347,7 +1395,10 @@ std::string Rewriter::EmitJson() const {
     if (!IsLive(g)) continue;
     const Gemm& c = *g->gemm;
     std::vector<std::string> roles = {"a", "b"};
-    if (c.f8) {
+    if (c.mx) {
+      roles.push_back("a_scale");
+      roles.push_back("b_scale");
+    } else if (c.f8) {
       if (c.has_c) roles.push_back("c");
       roles.push_back("a_scale");
       roles.push_back("b_scale");
@@ -1358,7 +1409,7 @@ std::string Rewriter::EmitJson() const {
       roles.push_back("b_col_scale");
     }
     std::ostringstream j;
-    j << "{\"name\": " << JsonStr(g->name) << ", \"target\": " << JsonStr(c.f8 ? "b200$scaled_dot$f8" : "b200$dot$s8") << ", \"m\": " << c.m
+    j << "{\"name\": " << JsonStr(g->name) << ", \"target\": " << JsonStr(c.mx ? "b200$block_scaled_dot$mx" : c.f8 ? "b200$scaled_dot$f8" : "b200$dot$s8") << ", \"m\": " << c.m
       << ", \"n\": " << c.n << ", \"k\": " << c.k << ", \"batch\": " << c.batch << ", \"swapped\": " << (c.swapped ? "true" : "false")
       << ", \"operands\": [";
     for (size_t i = 0; i < g->operands.size(); ++i) j << (i ? ", " : "") << describe(g->operands[i], i < roles.size() ? roles[i] : "?");
@@ -1366,7 +1417,9 @@ std::string Rewriter::EmitJson() const {
     if (c.damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": []}";
     if (c.emit_s32) j << ", {\"role\": \"acc\", \"dtype\": 4, \"dims\": " << Dims(g->shape) << "}";
     j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "]}], \"attrs\": {";
-    if (c.f8) {
+    if (c.mx) {
+      j << "\"alpha_real\": " << F64(c.alpha);
+    } else if (c.f8) {
       j << "\"alpha_real\": " << F64(c.alpha) << ", \"beta\": " << F64(c.beta) << ", \"epilogue\": " << c.epilogue
         << ", \"lhs_contracting_dim\": " << c.lhs_contracting << ", \"rhs_contracting_dim\": " << c.rhs_contracting
         << ", \"damax_output\": " << (c.damax ? "true" : "false")

@@ -2,7 +2,7 @@
 
 The module text goes through `b200sd_rewrite_hlo` (the rewriter-lite in csrc/hlo_rewriter.cc, which
 restates xla/backends/gpu/transforms/gemm_rewriter.cc for this path).  The rewritten module is then
-executed instruction by instruction: every `custom-call` to "b200$scaled_dot$f8" / "b200$dot$s8" goes
+executed instruction by instruction: every `custom-call` to "b200$scaled_dot$f8" / "b200$dot$s8" / "b200$block_scaled_dot$mx" goes
 through the FFI boundary exactly like any other call site, and what is left around the calls -- the
 ops XLA would hand to its other emitters: data movement in front of a call (pad, slice, transpose,
 broadcast, select ...), the reciprocal or the f32 conversion of a scale, arithmetic the rewriter did
@@ -22,7 +22,7 @@ from typing import Sequence
 from . import _native
 from .scaled_dot import FfiCall, XlaFfiError
 
-_TARGETS = ("b200$scaled_dot$f8", "b200$dot$s8")
+_TARGETS = ("b200$scaled_dot$f8", "b200$dot$s8", "b200$block_scaled_dot$mx")
 
 
 def rewrite(hlo_text: str):
@@ -146,13 +146,16 @@ def _torch():
 
 def _dtype(name: str):
     torch = _torch()
-    return {"pred": torch.bool, "s8": torch.int8, "s32": torch.int32, "s64": torch.int64, "u8": torch.uint8, "f16": torch.float16,
-            "f32": torch.float32, "bf16": torch.bfloat16, "f8e5m2": torch.float8_e5m2, "f8e4m3fn": torch.float8_e4m3fn}[name]
+    table = {"pred": torch.bool, "s8": torch.int8, "s32": torch.int32, "s64": torch.int64, "u8": torch.uint8, "f16": torch.float16,
+             "f32": torch.float32, "bf16": torch.bfloat16, "f8e5m2": torch.float8_e5m2, "f8e4m3fn": torch.float8_e4m3fn}
+    if hasattr(torch, "float8_e8m0fnu"):
+        table["f8e8m0fnu"] = torch.float8_e8m0fnu
+    return table[name]
 
 
 def _is_f8(t) -> bool:
     torch = _torch()
-    return t.dtype in (torch.float8_e5m2, torch.float8_e4m3fn)
+    return t.dtype in (torch.float8_e5m2, torch.float8_e4m3fn) or t.dtype == getattr(torch, "float8_e8m0fnu", None)
 
 
 def _moved(t, fn):
