@@ -71,9 +71,10 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "cublaslt"])
     p.add_argument("--workload", default="c1", choices=sorted(WORKLOAD_NAME))
-    p.add_argument("--overlap", type=int, default=-1, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory, 1 = NCCL all-reduce of finished row blocks "
-                   "on a second stream, 0 = dot then one NCCL all-reduce; default: 2 up to 4 GPUs, 0 beyond (measured faster)")
-    p.add_argument("--multicast", type=int, default=0, help="c4 fused: write finished rows through the NVSwitch multicast mapping")
+    p.add_argument("--overlap", type=int, default=-1, help="c4, N>1: 2 = sum formed inside the dot's kernel over peer memory (default), 1 = NCCL all-reduce of "
+                   "finished row blocks on a second stream, 0 = dot then one NCCL all-reduce")
+    p.add_argument("--multicast", type=int, default=-1, help="c4 fused: use the NVSwitch multicast mappings (finished rows by multimem.st, pulled sums by "
+                   "multimem.ld_reduce); default: on with the pull forms")
     p.add_argument("--pull", type=int, default=-1, help="c4 fused: 1 / 2 = partials stay with their producer and the owner of the rows fetches their sum "
                    "(in the switch with --multicast 1; 2 = piecewise during the next round), 0 = partials are pushed to the owner; "
                    "default: measured best per GPU count")
@@ -418,9 +419,12 @@ class Bench:
 
         args, dist = self.args, self.dist
         if overlap < 0:
-            overlap = 2 if self.world <= 4 else 0
+            overlap = 2
         if overlap == 2:
-            pull = max(0, args.pull)
+            # Measured on 8192 x 28672 x 8192: 2 GPUs -- pull by the own tile's warp 0.72 ms, push 0.73; 4 GPUs -- push 0.48,
+            # pull 0.56; 8 GPUs -- pull by the reducer warps 0.52, push 0.57 (one NCCL all-reduce behind the dot: 0.92 / 0.66 / 0.54).
+            pull = args.pull if args.pull >= 0 else {2: 1, 4: 0}.get(self.world, 2 if self.world > 4 else 0)
+            multicast = multicast if multicast >= 0 else (1 if pull else 0)
             fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=self.dev, multicast=bool(multicast), pull=int(pull))
                      for _ in sets]
             runners = [(lambda f=f, ops=ops: f(ops[0], ops[1], ops[2], ops[3])) for f, (_, ops, _) in zip(fused, sets)]
