@@ -132,6 +132,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int ep_halves = (p.m % 32 == 0) ? 2 : 1;
   const int cols_per_warp = p.m / ep_halves;
   if (kTiming && p.timing && threadIdx.x == 64) p.timing[blockIdx.x * 16 + 1] = global_timer_ns();
+  // Programmatic dependent launch: the kernel behind this one in the stream may be scheduled as this one's CTAs
+  // retire; every role of this kernel sets itself up first and passes griddep_wait() before it touches global
+  // memory, so the set-up overlaps the tail of the kernel in front.
+  if (threadIdx.x == 0) griddep_launch_dependents();
 
   // The CTA walks its unit range [u_begin, u_end) backwards, one strip-segment at a time:
   //   segment = units of one strip, [max(u_begin, strip*KB), min(u_end, (strip+1)*KB)).
@@ -160,6 +164,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (elect_one()) {
       tma_prefetch_desc(&tmap_w);
       tma_prefetch_desc(&tmap_a);
+      griddep_wait();                                         // operands may be the previous kernel's results
       const uint64_t stream_once = l2_policy_evict_first();   // W passes through L2 exactly once
       const uint64_t keep = l2_policy_evict_last();           // A is re-read by every CTA
       int stage = 0;
@@ -207,6 +212,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     named_bar_sync(1, kThreads);                 // barriers initialised (warp 0) and TMEM allocated (warp 1)
     tc_fence_after_sync();
     const uint32_t tmem_base = aux->tmem_base;
+    griddep_wait();                              // from here on: scales, flags, partials and D in global memory
 
     if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
@@ -565,8 +571,17 @@ Status LaunchSkinny(const GemmProblem& g, cudaStream_t stream, LaunchStats* stat
     if (me != cudaSuccess) return Status::Error(kInternal, std::string("cudaMemsetAsync(split-K flags): ") + cudaGetErrorString(me));
   }
   const size_t smem_bytes = 1024 + size_t(stages) * stage_bytes + sizeof(SkinnyAux);
-  skinny_gemm_kernel<<<int(grid), kThreads, smem_bytes, stream>>>(tmap_w, tmap_a, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see griddep_wait() in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel, tmap_w, tmap_a, p);
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("skinny_gemm_kernel launch: ") + cudaGetErrorString(e));
   if (stats) {
     stats->kernel = kKernelSkinny;
