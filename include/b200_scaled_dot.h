@@ -61,8 +61,10 @@ enum {
   B200SD_KERNEL_SKINNY = 2,       /* split-K kernel for decode shapes */
   B200SD_KERNEL_DENSE_SINGLE = 3, /* one CTA per 128 x 256 tile */
   B200SD_KERNEL_DENSE_PAIR = 4,   /* two-CTA clusters on 256 x 256 tiles (tcgen05 cta_group::2) */
-  B200SD_KERNEL_DENSE_STREAMK = 5 /* DENSE_PAIR whose tiles past the last full wave are cut along K, one equal share per
+  B200SD_KERNEL_DENSE_STREAMK = 5,/* DENSE_PAIR whose tiles past the last full wave are cut along K, one equal share per
                                      cluster (needs the workspace; plain DENSE_PAIR when the shape has no such tail) */
+  B200SD_KERNEL_MX_256 = 6,       /* block-scaled dot only: 256 x 256 tiles, one accumulator in TMEM */
+  B200SD_KERNEL_MX_224 = 7        /* block-scaled dot only: 256 x 224 tiles, two accumulators (epilogue under the next main loop) */
 };
 
 /* Arguments of one FP8 scaled dot.
@@ -157,6 +159,7 @@ typedef struct B200SD_BlockScaledDotMx {
   int32_t d_dtype;               /* F32, BF16 or F16 */
   float alpha;                   /* GemmBackendConfig.alpha_real; XLA writes 1 */
   int32_t batch_count;           /* 0 or 1: plain matrices */
+  int32_t kernel;                /* B200SD_KERNEL_AUTO, B200SD_KERNEL_MX_256 or B200SD_KERNEL_MX_224 */
 } B200SD_BlockScaledDotMx;
 
 /* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the

@@ -85,6 +85,26 @@ def test_struct_layouts_match_the_header():
     assert _native.product.b200sd_check_dot_s8(C.byref(s), err, len(err)) == 3
 
 
+def test_block_scaled_entry_point_validates_without_a_device():
+    """b200sd_check_block_scaled_dot_mx: everything but the pointers, no device access."""
+    err = C.create_string_buffer(256)
+    chk = _native.product.b200sd_check_block_scaled_dot_mx
+
+    def args(**kw):
+        a = _native.BlockScaledDotMxArgs(struct_size=C.sizeof(_native.BlockScaledDotMxArgs), m=256, n=512, k=256, a_dtype=20, b_dtype=19,
+                                         scale_dtype=33, d_dtype=16, alpha=1.0, batch_count=0)
+        for k_, v in kw.items():
+            setattr(a, k_, v)
+        return a
+
+    assert chk(C.byref(args()), err, len(err)) == 0, err.value
+    assert chk(C.byref(args(batch_count=4, d_dtype=11)), err, len(err)) == 0
+    for bad, code in [(dict(struct_size=16), 3), (dict(k=250), 3), (dict(scale_dtype=20), 12), (dict(a_dtype=2), 12), (dict(d_dtype=20), 3),
+                      (dict(m=0), 3), (dict(batch_count=-1), 3)]:
+        assert chk(C.byref(args(**bad)), err, len(err)) == code, (bad, err.value)
+    assert chk(None, err, len(err)) == 3
+
+
 def test_registration_and_metadata():
     _native.ensure_registered()
     traits, minor = C.c_uint32(0), C.c_int(0)

@@ -33,9 +33,13 @@ def _abs_dot(a, b, sa, sb, ka, kb):
     return np.matmul(a_dq, np.swapaxes(b_dq, -1, -2))
 
 
-def _run(dev, a, b, sa, sb, ka="e4m3fn", kb="e4m3fn", out=torch.float32, alpha=1.0):
+MX_256, MX_224 = 6, 7          # B200SD_KERNEL_MX_256 / _224: one accumulator of 256 columns, two of 224
+WIDTHS = pytest.mark.parametrize("kernel", [MX_256, MX_224], ids=["tile256", "tile224"])
+
+
+def _run(dev, a, b, sa, sb, ka="e4m3fn", kb="e4m3fn", out=torch.float32, alpha=1.0, kernel=0):
     d = cublas_lt_matmul_mx(_dev(a, dev, F8[ka]), _dev(b, dev, F8[kb]), _dev(sa, dev), _dev(sb, dev), out_dtype=out,
-                            alpha_real=alpha)
+                            alpha_real=alpha, selected_algorithm=kernel)
     torch.cuda.synchronize()
     assert device_status() == 0
     return d
@@ -56,22 +60,24 @@ def _check(got_f32, want_f32, absdot, ulp):
     (384, 768, 512, 2),
     (128, 256, 128, 0),       # a single k-block; the pair's second CTA has no valid rows
 ])
-def test_mx_dot_f32(cuda_device, m, n, k, batch):
+@WIDTHS
+def test_mx_dot_f32(cuda_device, m, n, k, batch, kernel):
     a, b, sa, sb = o.make_mx_operands(m * 7 + n, m, n, k, batch=batch)
     want = o.block_scaled_dot(a, b, sa, sb)
-    got = _run(cuda_device, a, b, sa, sb).cpu().numpy()
+    got = _run(cuda_device, a, b, sa, sb, kernel=kernel).cpu().numpy()
     assert got.shape == want.shape
     _check(got, want, _abs_dot(a, b, sa, sb, "e4m3fn", "e4m3fn"), 2.0 ** -23)
 
 
-@pytest.mark.parametrize("m,n,k", [(200, 136, 160), (300, 260, 96), (77, 33, 32), (129, 257, 416)])
-def test_mx_dot_ragged_shapes(cuda_device, m, n, k):
+@pytest.mark.parametrize("m,n,k", [(200, 136, 160), (300, 260, 96), (77, 33, 32), (129, 257, 416), (520, 700, 1024)])
+@WIDTHS
+def test_mx_dot_ragged_shapes(cuda_device, m, n, k, kernel):
     """Rows, columns and k-blocks that fill no tile, rows of scales that start on odd addresses
     (k / 32 not a multiple of 4: the scale loader's byte path) and results whose rows are not 16-byte
     multiples (scalar stores)."""
     a, b, sa, sb = o.make_mx_operands(m + n + k, m, n, k)
     want = o.block_scaled_dot(a, b, sa, sb)
-    got = _run(cuda_device, a, b, sa, sb).cpu().numpy()
+    got = _run(cuda_device, a, b, sa, sb, kernel=kernel).cpu().numpy()
     _check(got, want, _abs_dot(a, b, sa, sb, "e4m3fn", "e4m3fn"), 2.0 ** -23)
 
 
@@ -85,16 +91,18 @@ def test_mx_dot_e5m2_operands(cuda_device, ka, kb):
 
 
 @pytest.mark.parametrize("out,code,ulp", [(torch.bfloat16, o.BF16, 2.0 ** -7), (torch.float16, o.F16, 2.0 ** -10)])
-def test_mx_dot_16_bit_results(cuda_device, out, code, ulp):
+@WIDTHS
+def test_mx_dot_16_bit_results(cuda_device, out, code, ulp, kernel):
     m, n, k = 512, 384, 256
     # scales near one keep every value inside f16's range
     a, b, sa, sb = o.make_mx_operands(11, m, n, k, scale_lo=122, scale_hi=128)
     want = o.output_to_f32(o.block_scaled_dot(a, b, sa, sb, out_dtype=code), code)
-    got = _run(cuda_device, a, b, sa, sb, out=out).float().cpu().numpy()
+    got = _run(cuda_device, a, b, sa, sb, out=out, kernel=kernel).float().cpu().numpy()
     _check(got, want, _abs_dot(a, b, sa, sb, "e4m3fn", "e4m3fn"), ulp)
 
 
-def test_mx_scale_semantics(cuda_device):
+@WIDTHS
+def test_mx_scale_semantics(cuda_device, kernel):
     """Known answers that isolate the scale bytes: all-ones operands make every output
     sum_blocks 32 * 2^(sa - 127) * 2^(sb - 127); one block scale at a time is changed."""
     m, n, k = 256, 256, 256
@@ -110,7 +118,7 @@ def test_mx_scale_semantics(cuda_device):
         c, j2 = int(rng.integers(n)), int(rng.integers(k // 32))
         sb[c, j2] = 127 + int(rng.integers(-6, 7))
     want = o.block_scaled_dot(a, b, sa, sb)
-    got = _run(cuda_device, a, b, sa, sb).cpu().numpy()
+    got = _run(cuda_device, a, b, sa, sb, kernel=kernel).cpu().numpy()
     assert (got == want).all()          # powers of two: exact whatever the summation order
     assert want.min() != want.max()
 
@@ -129,17 +137,18 @@ def test_mx_alpha_and_nan_scale(cuda_device):
     _check(got[keep], want[keep], 0.5 * _abs_dot(a, b, sa_ok, sb, "e4m3fn", "e4m3fn")[keep], 2.0 ** -23)
 
 
-def test_mx_dot_full_size_sampled(cuda_device):
+@WIDTHS
+def test_mx_dot_full_size_sampled(cuda_device, kernel):
     """4096^3: every output row block is produced by the same code path; 96 sampled rows are compared
     with the oracle and the whole result against a linearity property (doubling one operand's scales
     doubles D exactly)."""
     m = n = k = 4096
     a, b, sa, sb = o.make_mx_operands(4096, m, n, k, scale_lo=121, scale_hi=131)
-    d = _run(cuda_device, a, b, sa, sb)
+    d = _run(cuda_device, a, b, sa, sb, kernel=kernel)
     rows = np.random.default_rng(0).choice(m, 96, replace=False)
     want = o.block_scaled_dot(a[rows], b, sa[rows], sb)
     _check(d.cpu().numpy()[rows], want, _abs_dot(a[rows], b, sa[rows], sb, "e4m3fn", "e4m3fn"), 2.0 ** -23)
-    d2 = _run(cuda_device, a, b, (sa + 1).astype(np.uint8), sb)
+    d2 = _run(cuda_device, a, b, (sa + 1).astype(np.uint8), sb, kernel=kernel)
     assert torch.equal(d2, d * 2)
 
 

@@ -74,6 +74,7 @@ class BlockScaledDotMxArgs(C.Structure):
         ("a_dtype", C.c_int32), ("b_dtype", C.c_int32), ("scale_dtype", C.c_int32), ("d_dtype", C.c_int32),
         ("alpha", C.c_float),
         ("batch_count", C.c_int32),
+        ("kernel", C.c_int32),
     ]
 
 

@@ -321,6 +321,7 @@ Status ConvertMx(const B200SD_BlockScaledDotMx& a, MxProblem* g) {
   g->a_scale = a.a_scale; g->b_scale = a.b_scale;
   g->alpha = a.alpha;
   g->d = a.d; g->d_dtype = a.d_dtype;
+  g->kernel = a.kernel;
   if (a.batch_count < 0) return Status::Error(kInvalidArgument, "batch_count must not be negative");
   return ValidateMx(*g);
 }

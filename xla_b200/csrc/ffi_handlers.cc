@@ -317,6 +317,7 @@ ffi::Error DecodeMx(ffi::RemainingArgs operands, ffi::RemainingRets results, ffi
   B200SD_BlockScaledDotMx a{};
   a.struct_size = sizeof(a);
   a.alpha = static_cast<float>(GetFloat(attrs, "alpha_real").value_or(1.0));
+  a.kernel = static_cast<int32_t>(GetInt(attrs, "selected_config").value_or(0));
   if (operands.size() != 4) return MakeError(3, "expected operands (a, b, a_scale, b_scale), got " + std::to_string(operands.size()));
   if (results.size() < 1 || results.size() > 2) return MakeError(3, "expected results (D, [workspace]), got " + std::to_string(results.size()));
   auto lhs = operands.get<ffi::AnyBuffer>(0);

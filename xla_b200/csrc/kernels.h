@@ -141,7 +141,7 @@ uint32_t ProgressIncrement(const GemmProblem& g, int32_t block);
 
 // Kernel selection (stands in for cuBLASLt's algorithm index).
 enum KernelKind : int32_t { kKernelAuto = 0, kKernelDense = 1, kKernelSkinny = 2, kKernelDenseSingle = 3, kKernelDensePair = 4,
-                            kKernelDenseStreamK = 5, kKernelMxPair = 6 };
+                            kKernelDenseStreamK = 5, kKernelMxPair256 = 6, kKernelMxPair224 = 7 };
 
 struct LaunchStats {
   int32_t kernel = 0;     // KernelKind actually used
@@ -172,6 +172,7 @@ struct MxProblem {
   float alpha = 1.0f;
   void* d = nullptr;
   int32_t d_dtype = kF32;
+  int32_t kernel = kKernelAuto;      // kKernelAuto, kKernelMxPair256 or kKernelMxPair224
 };
 Status ValidateMx(const MxProblem& g);      // everything but the pointers
 Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats);

@@ -49,12 +49,14 @@ namespace {
 
 constexpr int kMxBM = 128;                 // rows of D per CTA per tile (= TMEM lanes)
 constexpr int kMxTileM = 2 * kMxBM;        // rows of D per pair per tile
-constexpr int kMxBN = 256;                 // columns of D per tile
+// Two tile widths.  256 columns: one accumulator (the scale columns leave no room for a second), the tensor pipe
+// waits while the epilogue reads it out.  224 columns: two accumulators (2 x 224 + 24 scale columns <= 512), the
+// epilogue of one tile runs under the main loop of the next, at the price of 14 % more A traffic per flop and a
+// ragged last column tile.  The host picks per shape; 256 wins wherever it does not need more rounds of tiles.
 constexpr int kMxBK = 128;                 // values of K per stage: one 128-byte swizzle row
 constexpr int kMxUmmaK = 32;               // K per MMA = one scale block
 constexpr int kMxStages = 6;
 constexpr int kMxAStageBytes = kMxBM * kMxBK;            // 16 KiB
-constexpr int kMxBStageBytes = (kMxBN / 2) * kMxBK;      // 16 KiB: this CTA's half of the tile's B rows
 constexpr int kMxSfBlockBytes = 512;                     // scales of 128 rows x 4 sub-blocks
 constexpr int kMxSfaStageBytes = kMxSfBlockBytes;        // this CTA's 128 rows of A
 constexpr int kMxSfbStageBytes = 2 * kMxSfBlockBytes;    // all 256 rows of B
@@ -63,23 +65,31 @@ constexpr int kMxEpilogueWarps = 8;
 constexpr int kMxFirstEpilogueWarp = 4;
 constexpr int kMxThreads = 32 * (kMxFirstEpilogueWarp + kMxEpilogueWarps);
 constexpr int kMxTmemCols = 512;
-// TMEM columns: accumulator 0-255; scale columns in two alternating sets so that the copy for one
-// k-block never lands on columns the MMAs of the block before may still be reading.
-constexpr int kMxTmemSfa = 256;            // + 16 * set: 4 columns
-constexpr int kMxTmemSfb = 288;            // + 16 * set: 8 columns
+template <int kBN_>
+struct MxCfg {
+  static constexpr int kBN = kBN_;                            // columns of D per tile
+  static constexpr int kAccBufs = kBN_ == 256 ? 1 : 2;
+  static constexpr int kBStageBytes = (kBN_ / 2) * kMxBK;     // this CTA's half of the tile's B rows: 16 or 14 KiB
+  static constexpr int kRawSfbBytes = kBN_ * 16;              // 16 scale bytes of every B row of the tile
+  // TMEM columns: accumulators at 0 and 256; scale columns in two alternating sets so that the copy for one
+  // k-block never lands on columns the MMAs of the block before may still be reading (A: 4 columns, B: 8).
+  static constexpr int kTmemAccStride = 256;
+  static constexpr int kTmemSfa = kAccBufs == 1 ? 256 : 480, kTmemSfaSet = kAccBufs == 1 ? 16 : 4;
+  static constexpr int kTmemSfb = kAccBufs == 1 ? 288 : 488, kTmemSfbSet = kAccBufs == 1 ? 16 : 8;
+  static constexpr int kColsHalf1 = kBN_ - 128;               // columns of the second group of epilogue warps: 128 or 96
+  static_assert(kBN_ == 256 || kBN_ == 224, "tile widths the epilogue is written for");
+};
 // Scales travel in groups of four k-blocks (16 bytes per row: what one TMA box can bring), one group
 // per slot of their own ring, so the loader runs well ahead of the operand stages.
 constexpr int kMxSfSlots = 5;
 constexpr int kMxRawSfaBytes = kMxBM * 16;               // 2 KiB: 128 rows of A
-constexpr int kMxRawSfbBytes = kMxBN * 16;               // 4 KiB: 256 rows of B
-constexpr int kMxSfSlotBytes = 4 * kMxSfStageBytes;      // 6 KiB, as a landed box and as four rearranged k-blocks
-static_assert(kMxSfSlotBytes == kMxRawSfaBytes + kMxRawSfbBytes, "a box and its rearranged form share a slot");
+constexpr int kMxSfSlotBytes = 4 * kMxSfStageBytes;      // 6 KiB: a landed box (2 KiB + 16 bytes per B row) and four rearranged k-blocks
 
 struct MxAux {
   uint64_t full_bar[kMxStages];    // leader's: both CTAs' operand bytes have landed
   uint64_t empty_bar[kMxStages];   // each CTA's: the MMAs that read the stage have completed
-  uint64_t acc_full_bar;           // each CTA's: the tile's accumulator is complete
-  uint64_t acc_empty_bar;          // leader's: all 16 epilogue warps of the pair have read the accumulator out
+  uint64_t acc_full_bar[2];        // each CTA's: the tile's accumulator is complete
+  uint64_t acc_empty_bar[2];       // leader's: all 16 epilogue warps of the pair have read the accumulator out
   uint64_t raw_full_bar[kMxSfSlots];    // each CTA's: a box of scales has landed in the slot
   uint64_t sf_full_bar[kMxSfSlots];     // leader's: both CTAs have rearranged the slot's scales
   uint64_t sf_empty_bar[kMxSfSlots];    // each CTA's: the copies and MMAs that read the slot have completed
@@ -87,8 +97,9 @@ struct MxAux {
   int abort_flag;
 };
 
+template <int kBN>
 constexpr size_t MxSmemBytes() {
-  return 1024 + size_t(kMxStages) * (kMxAStageBytes + kMxBStageBytes) + kMxSfSlots * kMxSfSlotBytes + sizeof(MxAux);
+  return 1024 + size_t(kMxStages) * (kMxAStageBytes + MxCfg<kBN>::kBStageBytes) + kMxSfSlots * kMxSfSlotBytes + sizeof(MxAux);
 }
 
 struct MxArgs {
@@ -181,9 +192,14 @@ __device__ __forceinline__ void mx_store_chunk(const MxArgs& p, int64_t row_off,
   }
 }
 
+template <int kBN>
 __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const MxArgs p) {
+  using Cfg = MxCfg<kBN>;
+  constexpr int kMxBN = Cfg::kBN;
+  constexpr int kMxBStageBytes = Cfg::kBStageBytes;
+  constexpr int kAccBufs = Cfg::kAccBufs;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -204,8 +220,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(&aux->full_bar[s], 1);        // the leader's producer, with the byte count of both CTAs' loads
       mbar_init(&aux->empty_bar[s], 1);
     }
-    mbar_init(&aux->acc_full_bar, 1);
-    mbar_init(&aux->acc_empty_bar, 2 * kMxEpilogueWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&aux->acc_full_bar[b], 1);
+      mbar_init(&aux->acc_empty_bar[b], 2 * kMxEpilogueWarps);
+    }
     for (int s = 0; s < kMxSfSlots; ++s) {
       mbar_init(&aux->raw_full_bar[s], 1);
       mbar_init(&aux->sf_full_bar[s], 2);     // one scale loader per CTA
@@ -265,6 +283,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const uint64_t sf_desc0 = make_smem_desc_noswizzle(smem_u32(smem_sf), 128);
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0, set = 0;
+      int acc = 0;
       uint32_t sf_group = 0;                     // groups of four k-blocks taken from the scale ring so far
       bool ok = true;
       const bool timed = kTiming && p.timing != nullptr;
@@ -272,7 +291,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       long long wait_full = 0, wait_acc = 0, wait_sf = 0;
       for (int32_t tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         const long long ta = timed ? clock64() : 0;
-        ok = mbar_wait(&aux->acc_empty_bar, acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
+        ok = mbar_wait(&aux->acc_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout);
         if (timed) wait_acc += clock64() - ta;
         if (!ok) break;
         tc_fence_after_sync();
@@ -292,15 +311,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint64_t a_desc = a_desc0 + uint64_t((stage * kMxAStageBytes) >> 4);
           const uint64_t b_desc = b_desc0 + uint64_t((stage * kMxBStageBytes) >> 4);
           const uint64_t sf_desc = sf_desc0 + uint64_t((sf_slot * kMxSfSlotBytes + uint32_t(kb & 3) * kMxSfStageBytes) >> 4);
-          const uint32_t sfa_t = tmem_base + kMxTmemSfa + 16 * set;
-          const uint32_t sfb_t = tmem_base + kMxTmemSfb + 16 * set;
+          const uint32_t sfa_t = tmem_base + Cfg::kTmemSfa + Cfg::kTmemSfaSet * set;
+          const uint32_t sfb_t = tmem_base + Cfg::kTmemSfb + Cfg::kTmemSfbSet * set;
           tmem_cp_32x128b_pair(sfa_t, sf_desc);                                             // A rows of this CTA
           tmem_cp_32x128b_pair(sfb_t, sf_desc + uint64_t(kMxSfaStageBytes >> 4));           // B rows 0-127
           tmem_cp_32x128b_pair(sfb_t + 4, sf_desc + uint64_t((kMxSfaStageBytes + kMxSfBlockBytes) >> 4));   // B rows 128-255
 #pragma unroll
           for (int j = 0; j < kMxBK / kMxUmmaK; ++j) {
             const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
-            umma_mxf8_pair(tmem_base, a_desc + uint64_t((j * kMxUmmaK) >> 4), b_desc + uint64_t((j * kMxUmmaK) >> 4),
+            umma_mxf8_pair(tmem_base + uint32_t(acc * Cfg::kTmemAccStride), a_desc + uint64_t((j * kMxUmmaK) >> 4), b_desc + uint64_t((j * kMxUmmaK) >> 4),
                            idesc_mx_with_scale_byte(p.idesc, uint32_t(j)), sfa_t, sfb_t, accumulate);
           }
           // The stage may be refilled once these copies and MMAs have read it -- in both CTAs.
@@ -318,9 +337,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
         if (!ok) break;
-        umma_commit_pair(map_to_cta(&aux->acc_full_bar, 0));     // accumulator complete (each CTA has its rows)
-        umma_commit_pair(map_to_cta(&aux->acc_full_bar, 1));
-        acc_phase ^= 1;
+        umma_commit_pair(map_to_cta(&aux->acc_full_bar[acc], 0));     // accumulator complete (each CTA has its rows)
+        umma_commit_pair(map_to_cta(&aux->acc_full_bar[acc], 1));
+        if (++acc == kAccBufs) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
       }
       if (timed) {
         p.timing[blockIdx.x * kMxTimingSlots + 0] = wait_full;
@@ -374,7 +396,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               mx_tile_coords(cluster_id + int32_t(gi_issue / groups_per_tile) * num_clusters, p, &imt, &int_, &ibt);
               const int32_t igrp = int32_t(gi_issue % groups_per_tile);
               uint8_t* raw = smem_sf + islot * kMxSfSlotBytes;
-              mbar_arrive_expect_tx(&aux->raw_full_bar[islot], kMxSfSlotBytes);
+              mbar_arrive_expect_tx(&aux->raw_full_bar[islot], kMxRawSfaBytes + Cfg::kRawSfbBytes);
               tma_load_3d(raw, &tmap_sfa, &aux->raw_full_bar[islot], igrp * 16, imt * kMxTileM + int32_t(rank) * kMxBM, ibt);
               tma_load_3d(raw + kMxRawSfaBytes, &tmap_sfb, &aux->raw_full_bar[islot], igrp * 16, int_ * kMxBN, ibt);
               gi_issue += 2;
@@ -466,8 +488,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ epilogue (warps 4..11)
     const int q = warp & 3;                               // TMEM lane quarter this warp may access
     const int col_half = (warp - kMxFirstEpilogueWarp) >> 2;
-    const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(col_half * 128);
+    const uint32_t t_addr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(col_half * 128);
     uint32_t acc_phase = 0;
+    int acc = 0;
     bool ok = true;
     const bool timed = kTiming && p.timing != nullptr;
     long long ep_wait = 0, ep_read = 0, ep_store = 0;
@@ -475,29 +498,34 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int32_t mt, nt, bt;
       mx_tile_coords(tile, p, &mt, &nt, &bt);
       const long long t0 = timed ? clock64() : 0;
-      if (lane == 0) ok = mbar_wait(&aux->acc_full_bar, acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      if (lane == 0) ok = mbar_wait(&aux->acc_full_bar[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       const long long t1 = timed ? clock64() : 0;
       if (!ok) break;
-      (void)mbar_try_wait(&aux->acc_full_bar, acc_phase);     // every lane observes the completed phase
+      (void)mbar_try_wait(&aux->acc_full_bar[acc], acc_phase);     // every lane observes the completed phase
+      const uint32_t t_addr = t_addr0 + uint32_t(acc * Cfg::kTmemAccStride);
+      const bool four = col_half == 0 || Cfg::kColsHalf1 == 128;      // this warp's group has 128 columns (else 96)
       tc_fence_after_sync();
       uint32_t r0[32], r1[32], r2[32], r3[32];
       tmem_ld_32x32(t_addr, r0);
       tmem_ld_32x32(t_addr + 32, r1);
       tmem_ld_32x32(t_addr + 64, r2);
-      tmem_ld_32x32(t_addr + 96, r3);
+      if (four) tmem_ld_32x32(t_addr + 96, r3);
       tmem_ld_wait_for(r0);
       tmem_ld_wait_for(r1);
       tmem_ld_wait_for(r2);
-      tmem_ld_wait_for(r3);
+      if (four) tmem_ld_wait_for(r3);
       // The accumulator is in registers: the issuer may start the next tile.
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
-        if (rank != 0) mbar_arrive_cluster(map_to_cta(&aux->acc_empty_bar, 0));
-        else mbar_arrive(&aux->acc_empty_bar);
+        if (rank != 0) mbar_arrive_cluster(map_to_cta(&aux->acc_empty_bar[acc], 0));
+        else mbar_arrive(&aux->acc_empty_bar[acc]);
       }
-      acc_phase ^= 1;
+      if (++acc == kAccBufs) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
       const long long t2 = timed ? clock64() : 0;
       const int64_t row = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + q * 32 + lane;
       if (row < p.m) {
@@ -506,7 +534,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         mx_store_chunk(p, row_off, col, r0);
         mx_store_chunk(p, row_off, col + 32, r1);
         mx_store_chunk(p, row_off, col + 64, r2);
-        mx_store_chunk(p, row_off, col + 96, r3);
+        if (four) mx_store_chunk(p, row_off, col + 96, r3);
       }
       if (timed) {
         ep_wait += t1 - t0;
@@ -534,8 +562,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 // ----------------------------------------------------------------------------- host side
 Status InitMxKernels() {
-  const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(mx_gemm_kernel),
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(MxSmemBytes()));
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(mx_gemm_kernel<256>),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, int(MxSmemBytes<256>()));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(reinterpret_cast<const void*>(mx_gemm_kernel<224>),
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, int(MxSmemBytes<224>()));
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("cudaFuncSetAttribute(mx): ") + cudaGetErrorString(e));
   return Status::Ok();
 }
@@ -559,6 +589,8 @@ Status ValidateMx(const MxProblem& g) {
   }
   if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch < 0) return Status::Error(kInvalidArgument, "block-scaled dot: empty or negative dimension");
   if (g.k % 32 != 0) return Status::Error(kInvalidArgument, "block-scaled dot: the contracting dimension must be a multiple of the block size 32");
+  if (g.kernel != kKernelAuto && g.kernel != kKernelMxPair256 && g.kernel != kKernelMxPair224)
+    return Status::Error(kInvalidArgument, "block-scaled dot: kernel must be AUTO, MX_256 or MX_224");
   if (g.m >= (1ll << 31) || g.n >= (1ll << 31) || g.k >= (1ll << 31)) return Status::Error(kInvalidArgument, "block-scaled dot: dimension too large");
   return Status::Ok();
 }
@@ -579,7 +611,20 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   CUtensorMap tmap_a, tmap_b;
   st = MakeBatchedByteMatrixMap(&tmap_a, g.a, batch, g.m, g.k, kMxBK, kMxBM);          // [m, k], box 128(k) x 128(m)
   if (!st.ok()) return st;
-  st = MakeBatchedByteMatrixMap(&tmap_b, g.b, batch, g.n, g.k, kMxBK, kMxBN / 2);      // [n, k], box 128(k) x 128(n)
+  // Tile width.  Measured (bf16 result): 8192^3 398 us with 256-column tiles against 415 us with 224 (16 rounds instead
+  // of 14, and 14 % more A traffic per flop on a kernel whose limit is the shared-memory fill rate); 4096^3 62.8 against
+  // 68.1; 2048 x 8192 x 4096, where both widths need four rounds, 80.1 against 74.6.  The accumulator read-out that
+  // the second accumulator hides costs the 256-column form about 800 cycles per tile in the end (the MMAs already
+  // queued cover the rest); the narrower tile costs 8 % per flop.
+  const int max_clusters = max_pairs;
+  auto rounds = [&](int bn) {
+    const int64_t t = batch * ((g.m + kMxTileM - 1) / kMxTileM) * ((g.n + bn - 1) / bn);
+    return double((t + max_clusters - 1) / max_clusters);
+  };
+  const double k_cycles = 512.0 * double((g.k + kMxBK - 1) / kMxBK);
+  const double cost256 = rounds(256) * (k_cycles + 800.0), cost224 = rounds(224) * k_cycles * (224.0 / 256.0) * 1.08;
+  const int bn = g.kernel == kKernelMxPair256 ? 256 : g.kernel == kKernelMxPair224 ? 224 : (cost224 < cost256 ? 224 : 256);
+  st = MakeBatchedByteMatrixMap(&tmap_b, g.b, batch, g.n, g.k, kMxBK, uint32_t(bn / 2));      // [n, k], box 128(k) x 128|112(n)
   if (!st.ok()) return st;
 
   MxArgs p{};
@@ -592,17 +637,17 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   if (p.sf_bulk_ok) {
     st = MakeBatchedPlainByteMap(&tmap_sfa, g.a_scale, batch, g.m, p.scale_cols, 16, kMxBM);
     if (!st.ok()) return st;
-    st = MakeBatchedPlainByteMap(&tmap_sfb, g.b_scale, batch, g.n, p.scale_cols, 16, kMxBN);
+    st = MakeBatchedPlainByteMap(&tmap_sfb, g.b_scale, batch, g.n, p.scale_cols, 16, uint32_t(bn));
     if (!st.ok()) return st;
   }
   p.batch = int32_t(batch);
   p.num_m_tiles = int32_t((g.m + kMxTileM - 1) / kMxTileM);
-  p.num_n_tiles = int32_t((g.n + kMxBN - 1) / kMxBN);
+  p.num_n_tiles = int32_t((g.n + bn - 1) / bn);
   p.num_k_blocks = int32_t((g.k + kMxBK - 1) / kMxBK);
   const int64_t tiles = batch * p.num_m_tiles * p.num_n_tiles;
   if (tiles > (1ll << 30)) return Status::Error(kInvalidArgument, "block-scaled dot: too many tiles");
   p.raster_group = 16;
-  p.idesc = make_idesc_mx(g.a_dtype == kF8E5M2 ? 1u : 0u, g.b_dtype == kF8E5M2 ? 1u : 0u, kMxTileM, kMxBN);
+  p.idesc = make_idesc_mx(g.a_dtype == kF8E5M2 ? 1u : 0u, g.b_dtype == kF8E5M2 ? 1u : 0u, kMxTileM, uint32_t(bn));
   p.sfa = static_cast<const uint8_t*>(g.a_scale);
   p.sfb = static_cast<const uint8_t*>(g.b_scale);
   p.sf_words_ok = (p.scale_cols % 4 == 0 && (reinterpret_cast<uintptr_t>(g.a_scale) & 3) == 0 &&
@@ -626,7 +671,7 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kMxThreads, 1, 1);
-  cfg.dynamicSmemBytes = MxSmemBytes();
+  cfg.dynamicSmemBytes = bn == 224 ? MxSmemBytes<224>() : MxSmemBytes<256>();
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -635,10 +680,11 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, mx_gemm_kernel, tmap_a, tmap_b, tmap_sfa, tmap_sfb, p);
+  const cudaError_t e = bn == 224 ? cudaLaunchKernelEx(&cfg, mx_gemm_kernel<224>, tmap_a, tmap_b, tmap_sfa, tmap_sfb, p)
+                                  : cudaLaunchKernelEx(&cfg, mx_gemm_kernel<256>, tmap_a, tmap_b, tmap_sfa, tmap_sfb, p);
   if (e != cudaSuccess) return Status::Error(kInternal, std::string("mx_gemm_kernel launch: ") + cudaGetErrorString(e));
   if (stats) {
-    stats->kernel = kKernelMxPair;
+    stats->kernel = bn == 224 ? kKernelMxPair224 : kKernelMxPair256;
     stats->grid = grid;
     stats->launches = 1;
   }

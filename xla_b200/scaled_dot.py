@@ -245,8 +245,8 @@ class BlockScaledDotCall(FfiCall):
     [workspace] -- the arrangement of `__cublas$lt$matmul$mx`
     (xla/service/gpu/thunk_emitter.cc:939-988)."""
 
-    def __init__(self, operands: Sequence, results: Sequence, *, alpha_real: float = 1.0):
-        super().__init__(TARGET_MX, operands, results, {"alpha_real": float(alpha_real)})
+    def __init__(self, operands: Sequence, results: Sequence, *, alpha_real: float = 1.0, selected_algorithm: int = 0):
+        super().__init__(TARGET_MX, operands, results, {"alpha_real": float(alpha_real), "selected_config": int(selected_algorithm)})
 
 
 def _current_stream_and_device(t):
@@ -316,7 +316,8 @@ def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=N
     return d, acc
 
 
-def cublas_lt_matmul_mx(a, b, a_scale, b_scale, *, out_dtype=None, alpha_real: float = 1.0, workspace=None, out=None):
+def cublas_lt_matmul_mx(a, b, a_scale, b_scale, *, out_dtype=None, alpha_real: float = 1.0, workspace=None, out=None,
+                        selected_algorithm: int = 0):
     """Runs one MX block-scaled dot on the current CUDA stream and returns D.
 
     a: [m, k] or [batch, m, k] float8; b: [n, k] or [batch, n, k] float8 (the contracting dimension is
@@ -334,7 +335,7 @@ def cublas_lt_matmul_mx(a, b, a_scale, b_scale, *, out_dtype=None, alpha_real: f
 
     operands = [a, b, scale_buffer(a_scale), scale_buffer(b_scale)]
     results = [d] + ([workspace] if workspace is not None else [])
-    call = BlockScaledDotCall(operands, results, alpha_real=alpha_real)
+    call = BlockScaledDotCall(operands, results, alpha_real=alpha_real, selected_algorithm=selected_algorithm)
     stream, dev = _current_stream_and_device(a)
     call.run(stream, dev)
     call.close()
