@@ -22,7 +22,9 @@ import os
 import re
 import sys
 
-ROOT = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XLA_ROOT", "")
+if not os.path.isdir(os.path.join(ROOT, "xla")):
+    sys.exit("usage: python " + os.path.basename(__file__) + " <xla checkout>   (or set XLA_ROOT)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

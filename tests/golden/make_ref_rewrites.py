@@ -34,7 +34,9 @@ import os
 import re
 import sys
 
-ROOT = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XLA_ROOT", "")
+if not os.path.isdir(os.path.join(ROOT, "xla")):
+    sys.exit("usage: python " + os.path.basename(__file__) + " <xla checkout>   (or set XLA_ROOT)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 FP8_TEST = "xla/backends/gpu/transforms/gemm_rewriter_fp8_test.cc"
 GEMM_TEST = "xla/backends/gpu/transforms/gemm_rewriter_test.cc"
