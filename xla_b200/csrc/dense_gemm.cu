@@ -639,6 +639,80 @@ __device__ __forceinline__ void finish_chunk(const DenseArgs& p, const uint32_t 
   }
 }
 
+// Peer reduce, pull == 2: fetches the sums of the (tile, warp) parts first, first + step, ... of one round's own rows
+// and writes them to every rank's D.  A part is the 32 rows x 128 columns one epilogue warp produces; it is complete
+// when every rank -- this one included -- has raised its flag.  Per part: one flag wait, sixteen 16-byte fetches
+// per lane (multimem.ld_reduce through the switch when the staging buffers have a multicast mapping, else peer
+// loads added in rank order), sixteen stores (multimem.st, else one store per rank).  Returns false when a wait
+// gave up.
+__device__ __forceinline__ bool reduce_parts(const DenseArgs& p, int32_t my_rank, int32_t round, int32_t first, int32_t step,
+                                             int lane, volatile int* abort_flag) {
+  constexpr int kTileRows = 2 * kBM;
+  const int32_t mtps = p.red.m_tiles_per_block / p.red.stages;
+  const int64_t rows_per_block = int64_t(p.red.m_tiles_per_block) * kTileRows;
+  const int32_t parts = mtps * p.num_n_tiles * 2 * kEpilogueWarps;
+  bool ok = true;
+  for (int32_t q = first; q < parts && ok; q += step) {
+    const int32_t t = q / (2 * kEpilogueWarps), w16 = q - t * 2 * kEpilogueWarps;
+    const int32_t cta = w16 / kEpilogueWarps, ew = w16 - cta * kEpilogueWarps;
+    const int32_t mt_local = t / p.num_n_tiles, nt = t - mt_local * p.num_n_tiles;
+    const int32_t own_mt = round * mtps + mt_local;
+    const int32_t f_index = ((own_mt * p.num_n_tiles + nt) * 2 + cta) * kEpilogueWarps + ew;
+    if (lane == 0) ok = counter_wait(p.red.flags[my_rank] + f_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) break;
+    const int32_t row_in_tile = cta * kBM + (((ew & 3) + 2) & 3) * 32;
+    const int64_t own_row0 = int64_t(own_mt) * kTileRows + row_in_tile;
+    const int64_t d_row0 = (int64_t(round) * p.red.world + my_rank) * mtps * kTileRows + int64_t(mt_local) * kTileRows + row_in_tile;
+    const int64_t col0 = int64_t(nt) * kBN + (ew >> 2) * kColsPerEpilogueWarp + (lane & 7) * 8;
+    uint4 v[16];
+#pragma unroll
+    for (int it = 0; it < 16; ++it) {
+      const int rrow = (it & 7) * 4 + (lane >> 3);
+      const int64_t col = col0 + (it >> 3) * 64;
+      if (col >= p.n) continue;
+      const int64_t off = (int64_t(my_rank) * rows_per_block + own_row0 + rrow) * p.n + col;
+      if (p.red.stage_multicast != nullptr) {
+        v[it] = multimem_ld_reduce_bf16x8(p.red.stage_multicast + off);
+      } else {
+        float acc8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc8[i] = 0.0f;
+        for (int32_t sr = 0; sr < p.red.world; ++sr) {
+          const uint4 x = __ldcg(reinterpret_cast<const uint4*>(p.red.stage[sr] + off));
+          const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[i]));
+            acc8[2 * i] += f.x;
+            acc8[2 * i + 1] += f.y;
+          }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(acc8[2 * i], acc8[2 * i + 1]);
+          o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        v[it] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < 16; ++it) {
+      const int rrow = (it & 7) * 4 + (lane >> 3);
+      const int64_t col = col0 + (it >> 3) * 64;
+      if (col >= p.n) continue;
+      const int64_t off = (d_row0 + rrow) * p.n + col;
+      if (p.red.d_multicast != nullptr) {
+        multimem_st_v4(p.red.d_multicast + off, v[it]);
+      } else {
+        for (int32_t j = 0; j < p.red.world; ++j) *reinterpret_cast<uint4*>(p.red.d[j] + off) = v[it];
+      }
+    }
+  }
+  return ok;
+}
+
 template <bool kInt8, bool kPair, bool kReduce = false>
 __global__ void __launch_bounds__(kReduce ? kReduceThreads : kThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid_constant__ CUtensorMap tmap_b_param,
@@ -875,94 +949,21 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
     }
   } else if (kReduce && warp >= 2 + kEpilogueWarps) {
     // ------------------------------------------------------------------ reducer warps (peer reduce, pull == 2)
-    // The rows this rank owns are cut into pieces of 8 rows x 64 columns, round by round; the reducer warps of
-    // the rank share them out.  A piece is complete when every rank -- this one included -- has raised the flag
-    // of the (tile, warp) part it lies in; its sum is then fetched (one multimem.ld_reduce per 16 bytes when the
-    // staging buffers have a multicast mapping: the switch reads every rank's partial and adds them up; else
-    // peer loads added in rank order) and written to every rank's D (multimem.st, else one store per rank).
-    // Nothing of this touches the accumulators, so the tensor cores never wait for NVLink: the traffic of round r
-    // flows while round r + 1 is computed, and only the last round's is left for the end of the kernel.
+    // They fetch and forward the sums of this rank's own rows (reduce_parts) round by round, as the flags of the
+    // parts complete.  Nothing of this touches the accumulators, so the tensor cores never wait for NVLink: the
+    // traffic of round r flows while round r + 1 is computed.  The LAST round's parts, which only complete when
+    // every rank has finished its last tiles, are shared out among all ten warps of every CTA: the epilogue warps
+    // take theirs when their tile loop ends.
     if constexpr (kReduce) {
       if (p.red.pull == 2 && p.red.world > 1) {
-        constexpr int kBatch = 8;                                    // pieces in flight per warp (16 x 16 bytes per lane)
-        const int32_t mtps = p.red.m_tiles_per_block / p.red.stages;
-        const int64_t rows_per_block = int64_t(p.red.m_tiles_per_block) * S::kTileRows;
-        const int32_t ncp = int32_t((p.n + 63) / 64);
-        const int32_t pieces = mtps * (S::kTileRows / 8) * ncp;     // per round
-        const int32_t n_red = tile_step * 2 * kReducerWarps;        // reducer warps of this rank
-        const int32_t me = (first_tile * 2 + int32_t(rank)) * kReducerWarps + (warp - 2 - kEpilogueWarps);
+        const int32_t n_ctas = tile_step * 2;                                          // CTAs of this rank
+        const int32_t cta_of_rank = first_tile * 2 + int32_t(rank);
+        const int32_t rw = warp - 2 - kEpilogueWarps;
         bool ok = true;
-        for (int32_t round = 0; round < p.red.stages && ok; ++round) {
-          for (int32_t q0 = me; q0 < pieces && ok; q0 += kBatch * n_red) {
-            uint4 v[2 * kBatch];
-            uint32_t have = 0;
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-              const int32_t qi = q0 + u * n_red;
-              if (qi >= pieces || !ok) continue;
-              const int32_t row_piece = qi / ncp, col_piece = qi - row_piece * ncp;
-              const int32_t r_in_sub = row_piece * 8;
-              const int64_t col0p = int64_t(col_piece) * 64;
-              const int32_t f_slot = (round * mtps + r_in_sub / S::kTileRows) * p.num_n_tiles + int32_t(col0p / kBN);
-              const int32_t f_cta = (r_in_sub % S::kTileRows) / kBM;
-              const int32_t f_ew = int32_t((col0p % kBN) / kColsPerEpilogueWarp) * 4 + ((((r_in_sub % kBM) / 32) + 2) & 3);
-              const int32_t f_index = (f_slot * 2 + f_cta) * kEpilogueWarps + f_ew;
-              if (lane == 0) ok = counter_wait(p.red.flags[my_rank] + f_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
-              ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-              if (!ok) continue;
-              have |= 1u << u;
-              const int64_t own_row = int64_t(round) * mtps * S::kTileRows + r_in_sub;
-              const int64_t col = col0p + (lane & 7) * 8;
-              if (col >= p.n) continue;
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int64_t off = (int64_t(my_rank) * rows_per_block + own_row + (lane >> 3) + 4 * h) * p.n + col;
-                if (p.red.stage_multicast != nullptr) {
-                  v[u * 2 + h] = multimem_ld_reduce_bf16x8(p.red.stage_multicast + off);
-                } else {
-                  float acc8[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) acc8[i] = 0.0f;
-                  for (int32_t sr = 0; sr < p.red.world; ++sr) {
-                    const uint4 x = __ldcg(reinterpret_cast<const uint4*>(p.red.stage[sr] + off));
-                    const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[i]));
-                      acc8[2 * i] += f.x;
-                      acc8[2 * i + 1] += f.y;
-                    }
-                  }
-                  uint32_t o[4];
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const __nv_bfloat162 hh = __floats2bfloat162_rn(acc8[2 * i], acc8[2 * i + 1]);
-                    o[i] = *reinterpret_cast<const uint32_t*>(&hh);
-                  }
-                  v[u * 2 + h] = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-              if (!(have & (1u << u))) continue;
-              const int32_t qi = q0 + u * n_red;
-              const int32_t row_piece = qi / ncp, col_piece = qi - row_piece * ncp;
-              const int64_t grow = (int64_t(round) * p.red.world + my_rank) * mtps * S::kTileRows + row_piece * 8;
-              const int64_t col = int64_t(col_piece) * 64 + (lane & 7) * 8;
-              if (col >= p.n) continue;
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int64_t off = (grow + (lane >> 3) + 4 * h) * p.n + col;
-                if (p.red.d_multicast != nullptr) {
-                  multimem_st_v4(p.red.d_multicast + off, v[u * 2 + h]);
-                } else {
-                  for (int32_t j = 0; j < p.red.world; ++j) *reinterpret_cast<uint4*>(p.red.d[j] + off) = v[u * 2 + h];
-                }
-              }
-            }
-          }
-        }
+        for (int32_t round = 0; round + 1 < p.red.stages && ok; ++round)
+          ok = reduce_parts(p, my_rank, round, cta_of_rank * kReducerWarps + rw, n_ctas * kReducerWarps, lane, abort_flag);
+        if (ok) ok = reduce_parts(p, my_rank, p.red.stages - 1, cta_of_rank * (kEpilogueWarps + kReducerWarps) + kEpilogueWarps + rw,
+                                  n_ctas * (kEpilogueWarps + kReducerWarps), lane, abort_flag);
         // End of call, like the epilogue warps: this warp's rows are in every rank's D.
         __threadfence_system();
         __syncwarp();
@@ -1304,6 +1305,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         asm volatile("fence.proxy.async.global;" ::: "memory");
         if (pending_flag != nullptr) red_relaxed_sys_add_u32(pending_flag, 1u);
         pending_flag = nullptr;
+      }
+      if (spread && ok) {          // this warp's share of the last round's sums (the reducer warps take the other rounds)
+        __syncwarp();
+        ok = reduce_parts(p, my_rank, p.red.stages - 1, (first_tile * 2 + int32_t(rank)) * (kEpilogueWarps + kReducerWarps) + ew,
+                          tile_step * 2 * (kEpilogueWarps + kReducerWarps), lane, abort_flag);
       }
       // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
       // warp of every rank has said the same, so that D is complete here when the kernel ends and
