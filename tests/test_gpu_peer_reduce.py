@@ -19,7 +19,8 @@ def _f8(shape, gen, dev):
 
 @pytest.mark.parametrize("pull", [0, 1, 2])
 @pytest.mark.parametrize("world,m,n,k_per_rank", [(2, 1024, 768, 384), (4, 2048, 512, 256), (2, 512, 272, 128), (1, 512, 256, 256),
-                                                  (2, 4096, 2048, 128)])      # several tiles per cluster and round
+                                                  (2, 4096, 2048, 128),       # several tiles per cluster and round
+                                                  (4, 4096, 8192, 128)])      # wide enough for rounds cut along the columns too
 def test_emulated_ranks_match_sum_of_bf16_partials(cuda_device, world, m, n, k_per_rank, pull):
     """pull = 1 / 2: the partials stay in the producing rank's staging buffer and the owner of the rows fetches them,
     tile by tile (1) or in pieces spread over the next round (2) -- here, on one GPU, with plain loads in rank order;

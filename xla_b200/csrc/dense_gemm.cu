@@ -93,6 +93,7 @@ struct ReduceArgs {
   int32_t world, rank, emulate;
   int32_t m_tiles_per_block;      // 256-row tiles each rank owns in all (its rows of the staging buffers)
   int32_t stages;                 // the rows are dealt out in `stages` rounds of world sub-blocks (see tile_coords_reduce)
+  int32_t col_rounds;             // ... each of which is further cut into this many groups of column tiles (a divisor of num_n_tiles)
   uint32_t flag_target;           // value a (tile, warp) flag reaches when every other rank has pushed: epoch * (world - 1)
   uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
   int32_t done_index;             // index of that counter in the flag array
@@ -293,7 +294,7 @@ __device__ __forceinline__ void st_release_gpu_u64(unsigned long long* p, unsign
 }
 
 // Peer-reduce order.  The rows are cut into stages x world sub-blocks; sub-block s*world + j belongs to
-// rank j.  In every stage rank r walks the sub-blocks of ranks r+1, r+2, ..., r (its own last): what it
+// rank j (and, with col_rounds > 1, each sub-block's column tiles into that many groups, one round each).  In every stage rank r walks the sub-blocks of ranks r+1, r+2, ..., r (its own last): what it
 // pushes first is what its neighbours need last, and when it reaches its own sub-block the others'
 // partials of it have arrived.  Several stages spread the broadcasts of finished rows over the
 // kernel instead of leaving them all for its end.  `blk` is the owner of the tile's rows, `own_mt`
@@ -301,25 +302,27 @@ __device__ __forceinline__ void st_release_gpu_u64(unsigned long long* p, unsign
 __device__ __forceinline__ void tile_coords_reduce(int32_t tile, const DenseArgs& p, int32_t my_rank, int32_t* mt,
                                                    int32_t* nt, int32_t* blk, int32_t* slot, int32_t* own_mt) {
   const int32_t mtps = p.red.m_tiles_per_block / p.red.stages;       // row tiles per sub-block
-  const int32_t per_sub = mtps * p.num_n_tiles;
-  const int32_t per_stage = per_sub * p.red.world;
-  const int32_t st = tile / per_stage;
-  const int32_t within = tile - st * per_stage;
+  const int32_t ntps = p.num_n_tiles / p.red.col_rounds;             // column tiles per sub-block
+  const int32_t per_sub = mtps * ntps;
+  const int32_t per_round = per_sub * p.red.world;
+  const int32_t round = tile / per_round;                            // row round major, column round minor
+  const int32_t rs = round / p.red.col_rounds, cs = round - rs * p.red.col_rounds;
+  const int32_t within = tile - round * per_round;
   const int32_t b = within / per_sub;
   const int32_t local = within - b * per_sub;
   int32_t owner = my_rank + 1 + b;
   if (owner >= p.red.world) owner -= p.red.world;
   const int32_t rg = min(p.raster_group, mtps);
-  const int32_t per_group = rg * p.num_n_tiles;
+  const int32_t per_group = rg * ntps;
   const int32_t g = local / per_group;
   const int32_t first_m = g * rg;
   const int32_t gsize = min(rg, mtps - first_m);
   const int32_t r = local - g * per_group;
   const int32_t mt_local = first_m + r % gsize;
-  *nt = r / gsize;
-  *mt = (st * p.red.world + owner) * mtps + mt_local;
+  *nt = cs * ntps + r / gsize;
+  *mt = (rs * p.red.world + owner) * mtps + mt_local;
   *blk = owner;
-  *own_mt = st * mtps + mt_local;
+  *own_mt = rs * mtps + mt_local;
   *slot = *own_mt * p.num_n_tiles + *nt;
 }
 
@@ -649,21 +652,23 @@ __device__ __forceinline__ bool reduce_parts(const DenseArgs& p, int32_t my_rank
                                              int lane, volatile int* abort_flag) {
   constexpr int kTileRows = 2 * kBM;
   const int32_t mtps = p.red.m_tiles_per_block / p.red.stages;
+  const int32_t ntps = p.num_n_tiles / p.red.col_rounds;
+  const int32_t rs = round / p.red.col_rounds, cs = round - rs * p.red.col_rounds;      // row round, column round
   const int64_t rows_per_block = int64_t(p.red.m_tiles_per_block) * kTileRows;
-  const int32_t parts = mtps * p.num_n_tiles * 2 * kEpilogueWarps;
+  const int32_t parts = mtps * ntps * 2 * kEpilogueWarps;
   bool ok = true;
   for (int32_t q = first; q < parts && ok; q += step) {
     const int32_t t = q / (2 * kEpilogueWarps), w16 = q - t * 2 * kEpilogueWarps;
     const int32_t cta = w16 / kEpilogueWarps, ew = w16 - cta * kEpilogueWarps;
-    const int32_t mt_local = t / p.num_n_tiles, nt = t - mt_local * p.num_n_tiles;
-    const int32_t own_mt = round * mtps + mt_local;
+    const int32_t mt_local = t / ntps, nt = cs * ntps + (t - mt_local * ntps);
+    const int32_t own_mt = rs * mtps + mt_local;
     const int32_t f_index = ((own_mt * p.num_n_tiles + nt) * 2 + cta) * kEpilogueWarps + ew;
     if (lane == 0) ok = counter_wait(p.red.flags[my_rank] + f_index, p.red.flag_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) break;
     const int32_t row_in_tile = cta * kBM + (((ew & 3) + 2) & 3) * 32;
     const int64_t own_row0 = int64_t(own_mt) * kTileRows + row_in_tile;
-    const int64_t d_row0 = (int64_t(round) * p.red.world + my_rank) * mtps * kTileRows + int64_t(mt_local) * kTileRows + row_in_tile;
+    const int64_t d_row0 = (int64_t(rs) * p.red.world + my_rank) * mtps * kTileRows + int64_t(mt_local) * kTileRows + row_in_tile;
     const int64_t col0 = int64_t(nt) * kBN + (ew >> 2) * kColsPerEpilogueWarp + (lane & 7) * 8;
     uint4 v[16];
 #pragma unroll
@@ -960,9 +965,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         const int32_t cta_of_rank = first_tile * 2 + int32_t(rank);
         const int32_t rw = warp - 2 - kEpilogueWarps;
         bool ok = true;
-        for (int32_t round = 0; round + 1 < p.red.stages && ok; ++round)
+        const int32_t rounds = p.red.stages * p.red.col_rounds;
+        for (int32_t round = 0; round + 1 < rounds && ok; ++round)
           ok = reduce_parts(p, my_rank, round, cta_of_rank * kReducerWarps + rw, n_ctas * kReducerWarps, lane, abort_flag);
-        if (ok) ok = reduce_parts(p, my_rank, p.red.stages - 1, cta_of_rank * (kEpilogueWarps + kReducerWarps) + kEpilogueWarps + rw,
+        if (ok) ok = reduce_parts(p, my_rank, rounds - 1, cta_of_rank * (kEpilogueWarps + kReducerWarps) + kEpilogueWarps + rw,
                                   n_ctas * (kEpilogueWarps + kReducerWarps), lane, abort_flag);
         // End of call, like the epilogue warps: this warp's rows are in every rank's D.
         __threadfence_system();
@@ -1308,7 +1314,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
       }
       if (spread && ok) {          // this warp's share of the last round's sums (the reducer warps take the other rounds)
         __syncwarp();
-        ok = reduce_parts(p, my_rank, p.red.stages - 1, (first_tile * 2 + int32_t(rank)) * (kEpilogueWarps + kReducerWarps) + ew,
+        ok = reduce_parts(p, my_rank, p.red.stages * p.red.col_rounds - 1, (first_tile * 2 + int32_t(rank)) * (kEpilogueWarps + kReducerWarps) + ew,
                           tile_step * 2 * (kEpilogueWarps + kReducerWarps), lane, abort_flag);
       }
       // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
@@ -1767,6 +1773,7 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   // broadcasts but add a rendezvous each).
   static const int env_stages = TuningEnvInt("B200SD_REDUCE_STAGES", 0);
   q.stages = q.m_tiles_per_block % 2 == 0 ? 2 : 1;
+  q.col_rounds = 1;
   if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
   q.flag_target = r.epoch * uint32_t(r.world - 1);
   q.done_index = int32_t(PeerReduceFlagWords(g.m, g.n, r.world)) - 32;
@@ -1790,15 +1797,18 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   if (q.pull == 2) {
     q.flag_target = r.epoch * uint32_t(r.world);      // a rank's own partial counts like every other
     q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps + kReducerWarps);
-    // As many rounds as leave every cluster about two tiles per round: the sums of a round flow while the next is
-    // computed, and only the last round's are left for the end of the kernel.
-    int best = 1;
-    for (int d = 1; d <= q.m_tiles_per_block; ++d) {
-      if (q.m_tiles_per_block % d == 0 && tiles / d >= 2ll * clusters_per_rank) best = d;
-    }
-    if (best == 1 && q.m_tiles_per_block % 2 == 0) best = 2;
-    q.stages = best;
+    // As many rounds as there are row tiles per rank: no warp waits for a peer inside the tile loop in this form, so
+    // rounds cost nothing, and only the last round's sums (1 / rounds of the traffic) are left for the end of the kernel.
+    q.stages = q.m_tiles_per_block;
     if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
+    // ... and each round's column tiles cut further, as long as a round keeps 64 tiles (the tiles that run at the same
+    // time still share a few operand panels in L2).
+    static const int env_cols = TuningEnvInt("B200SD_REDUCE_COL_ROUNDS", 0);
+    for (int d = 1; d <= p.num_n_tiles; ++d) {
+      const int64_t per_round = int64_t(r.world) * (q.m_tiles_per_block / q.stages) * (p.num_n_tiles / d);
+      if (p.num_n_tiles % d == 0 && per_round >= 64) q.col_rounds = d;
+    }
+    if (env_cols > 0 && p.num_n_tiles % env_cols == 0) q.col_rounds = env_cols;
   }
   q.stage_multicast = (r.emulate || !r.pull) ? nullptr : static_cast<uint16_t*>(r.stage_multicast);
 
