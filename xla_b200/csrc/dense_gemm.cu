@@ -94,6 +94,7 @@ struct ReduceArgs {
   int32_t m_tiles_per_block;      // 256-row tiles each rank owns in all (its rows of the staging buffers)
   int32_t stages;                 // the rows are dealt out in `stages` rounds of world sub-blocks (see tile_coords_reduce)
   int32_t col_rounds;             // ... each of which is further cut into this many groups of column tiles (a divisor of num_n_tiles)
+  int32_t debug;                  // tuning build only: 1 = reducers skip the fetches, 2 = skip the stores too (results are then wrong)
   uint32_t flag_target;           // value a (tile, warp) flag reaches when every other rank has pushed: epoch * (world - 1)
   uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
   int32_t done_index;             // index of that counter in the flag array
@@ -677,7 +678,9 @@ __device__ __forceinline__ bool reduce_parts(const DenseArgs& p, int32_t my_rank
       const int64_t col = col0 + (it >> 3) * 64;
       if (col >= p.n) continue;
       const int64_t off = (int64_t(my_rank) * rows_per_block + own_row0 + rrow) * p.n + col;
-      if (p.red.stage_multicast != nullptr) {
+      if (kTiming && p.red.debug >= 1) {
+        v[it] = make_uint4(0u, 0u, 0u, 0u);
+      } else if (p.red.stage_multicast != nullptr) {
         v[it] = multimem_ld_reduce_bf16x8(p.red.stage_multicast + off);
       } else {
         float acc8[8];
@@ -708,7 +711,8 @@ __device__ __forceinline__ bool reduce_parts(const DenseArgs& p, int32_t my_rank
       const int64_t col = col0 + (it >> 3) * 64;
       if (col >= p.n) continue;
       const int64_t off = (d_row0 + rrow) * p.n + col;
-      if (p.red.d_multicast != nullptr) {
+      if (kTiming && p.red.debug >= 2) {
+      } else if (p.red.d_multicast != nullptr) {
         multimem_st_v4(p.red.d_multicast + off, v[it]);
       } else {
         for (int32_t j = 0; j < p.red.world; ++j) *reinterpret_cast<uint4*>(p.red.d[j] + off) = v[it];
@@ -1774,6 +1778,7 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   static const int env_stages = TuningEnvInt("B200SD_REDUCE_STAGES", 0);
   q.stages = q.m_tiles_per_block % 2 == 0 ? 2 : 1;
   q.col_rounds = 1;
+  q.debug = TuningEnvInt("B200SD_REDUCE_DEBUG", 0);
   if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
   q.flag_target = r.epoch * uint32_t(r.world - 1);
   q.done_index = int32_t(PeerReduceFlagWords(g.m, g.n, r.world)) - 32;
