@@ -96,7 +96,8 @@ struct ReduceArgs {
   int32_t col_rounds;             // ... each of which is further cut into this many groups of column tiles (a divisor of num_n_tiles)
   int32_t debug;                  // tuning build only: 1 = reducers skip the fetches, 2 = skip the stores too (results are then wrong)
   uint32_t flag_target;           // value a (tile, warp) flag reaches when every other rank has pushed: epoch * (world - 1)
-  uint32_t done_target;           // value the end-of-call counter reaches when every warp of every rank is through
+  uint32_t done_target;           // value the end-of-call counter reaches when every rank is through: epoch * world
+  uint32_t done_local_target;     // value this rank's own CTA counter (the word behind it) reaches with its last CTA: epoch * CTAs
   int32_t done_index;             // index of that counter in the flag array
   uint64_t peer_wait_ns;          // limit of a wait for another rank
   uint16_t* d[kMaxPeers];
@@ -974,14 +975,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
           ok = reduce_parts(p, my_rank, round, cta_of_rank * kReducerWarps + rw, n_ctas * kReducerWarps, lane, abort_flag);
         if (ok) ok = reduce_parts(p, my_rank, rounds - 1, cta_of_rank * (kEpilogueWarps + kReducerWarps) + kEpilogueWarps + rw,
                                   n_ctas * (kEpilogueWarps + kReducerWarps), lane, abort_flag);
-        // End of call, like the epilogue warps: this warp's rows are in every rank's D.
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          for (int32_t j = 0; j < p.red.world; ++j) red_release_sys_add_u32(p.red.flags[j] + p.red.done_index, 1u);
-          (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
-        }
-        __syncwarp();
+        __threadfence_system();     // this warp's rows are in every rank's D before the CTA reports (end of the kernel)
       }
     }
   } else {
@@ -1321,16 +1315,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
         ok = reduce_parts(p, my_rank, p.red.stages * p.red.col_rounds - 1, (first_tile * 2 + int32_t(rank)) * (kEpilogueWarps + kReducerWarps) + ew,
                           tile_step * 2 * (kEpilogueWarps + kReducerWarps), lane, abort_flag);
       }
-      // End of call: this warp's rows are in every rank's D.  Tell every rank, then stay until every
-      // warp of every rank has said the same, so that D is complete here when the kernel ends and
-      // nobody overwrites a staging buffer that is still being read.
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) {
-        for (int32_t j = 0; j < p.red.world; ++j) red_release_sys_add_u32(p.red.flags[j] + p.red.done_index, 1u);
-        (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
-      }
-      __syncwarp();
+      __threadfence_system();       // this warp's rows are in every rank's D before the CTA reports (end of the kernel)
     }
     if (kTiming && p.timing && warp == 2 && lane == 0) {
       p.timing[blockIdx.x * kTimingSlots + 15] = global_timer_ns();        // column loops done, before the amax hand-shake
@@ -1374,6 +1359,23 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a_param, const __grid
 
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kReduce) {
+    // End of call.  Every warp of this CTA has put its rows into every rank's D and fenced them system-wide.  The CTAs
+    // of a rank count themselves on a word of their own GPU; the last one tells every rank (one remote add per rank and
+    // call -- warps reporting one by one meant world x 1480 system-scope adds onto one word of every GPU), and every
+    // CTA stays until all ranks have reported, so that D is complete here when the kernel ends and nobody overwrites
+    // a staging buffer that is still being read.
+    if (threadIdx.x == 0) {
+      uint32_t* const local = p.red.flags[my_rank] + p.red.done_index + 1;
+      uint32_t old;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(local) : "memory");
+      if (old + 1 == p.red.done_local_target) {
+        for (int32_t j = 0; j < p.red.world; ++j) red_release_sys_add_u32(p.red.flags[j] + p.red.done_index, 1u);
+      }
+      (void)counter_wait(p.red.flags[my_rank] + p.red.done_index, p.red.done_target, abort_flag, p.status, kStatusPeerTimeout, p.red.peer_wait_ns);
+    }
+    __syncthreads();
+  }
   if (kPair) cluster_sync_all();   // nobody leaves while the peer may still read this CTA's shared memory
   if (kTiming && p.timing && threadIdx.x == 0) p.timing[blockIdx.x * kTimingSlots + 13] = global_timer_ns();
   if (warp == 1) {
@@ -1782,7 +1784,8 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
   q.flag_target = r.epoch * uint32_t(r.world - 1);
   q.done_index = int32_t(PeerReduceFlagWords(g.m, g.n, r.world)) - 32;
-  q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps);
+  q.done_target = r.epoch * uint32_t(r.world);
+  q.done_local_target = r.epoch * uint32_t(2 * clusters_per_rank);
   q.peer_wait_ns = uint64_t(r.peer_wait_ms ? r.peer_wait_ms : kDefaultPeerWaitMs) * 1000000ull;
   for (int i = 0; i < r.world; ++i) {
     q.d[i] = static_cast<uint16_t*>(r.d[i]);
@@ -1801,7 +1804,6 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   q.pull = ((r.pull == 1 || r.pull == 2) && r.world > 1) ? r.pull : 0;
   if (q.pull == 2) {
     q.flag_target = r.epoch * uint32_t(r.world);      // a rank's own partial counts like every other
-    q.done_target = r.epoch * uint32_t(r.world) * uint32_t(2 * clusters_per_rank) * uint32_t(kEpilogueWarps + kReducerWarps);
     // As many rounds as there are row tiles per rank: no warp waits for a peer inside the tile loop in this form, so
     // rounds cost nothing, and only the last round's sums (1 / rounds of the traffic) are left for the end of the kernel.
     q.stages = q.m_tiles_per_block;
