@@ -14,6 +14,9 @@
 // (tcgen05.ld, scale / beta*C / bias / ReLU or GELU / amax / d_scale / cast, vector stores).
 // TMEM holds two 256-column accumulators so the epilogue of one tile overlaps the main loop of the
 // next.  Every wait is bounded; on expiry the kernel records a status bit and drains.
+// A third instantiation (pair, reduce) forms the sum of a contracting-dimension split over the GPUs of one box
+// inside the kernel, over peer memory: partials pushed to the rows' owner, or parked locally and fetched by the
+// owner -- with multimem.ld_reduce the NVSwitch adds them up -- by two extra reducer warps (384 threads).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>

@@ -125,7 +125,7 @@ struct PeerReduceProblem {
   uint32_t peer_wait_ms = 0;         // limit of a wait for another rank; 0 = kDefaultPeerWaitMs
   void* d[kMaxPeers] = {};
   void* d_multicast = nullptr;       // optional NVSwitch multicast mapping of all the d[i]
-  int32_t pull = 0;                  // partials stay with their producer; the owner of the rows fetches and adds them
+  int32_t pull = 0;                  // 1 / 2: partials stay with their producer; the owner of the rows fetches their sum (1: the own tile's warp, 2: reducer warps)
   void* stage_multicast = nullptr;   // pull: optional NVSwitch multicast mapping of all the stage[i] (in-switch sum)
   void* stage[kMaxPeers] = {};       // m*n bf16 each
   uint32_t* flags[kMaxPeers] = {};   // PeerReduceFlagWords() u32 each, zeroed once
