@@ -421,8 +421,8 @@ class Bench:
         if overlap < 0:
             overlap = 2
         if overlap == 2:
-            # Measured on 8192 x 28672 x 8192: 2 GPUs -- pull by the own tile's warp 0.72 ms, push 0.73, reducer warps 0.77;
-            # 4 GPUs -- reducer warps 0.43, push 0.46, own tile's warp 0.53; 8 GPUs -- reducer warps 0.52 (an earlier build of
+            # Measured on 8192 x 28672 x 8192: 2 GPUs -- pull by the own tile's warp 0.73 ms, push 0.73, reducer warps 0.76;
+            # 4 GPUs -- reducer warps 0.40, push 0.44, own tile's warp 0.51; 8 GPUs -- reducer warps 0.52 (an earlier build of
             # them), push 0.57 (one NCCL all-reduce behind the dot: 0.92 / 0.66 / 0.54).
             pull = args.pull if args.pull >= 0 else (1 if self.world == 2 else 2)
             multicast = multicast if multicast >= 0 else (1 if pull else 0)

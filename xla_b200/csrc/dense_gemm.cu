@@ -1807,17 +1807,26 @@ Status LaunchDenseReduce(const GemmProblem& g, const PeerReduceProblem& r, cudaS
   q.pull = ((r.pull == 1 || r.pull == 2) && r.world > 1) ? r.pull : 0;
   if (q.pull == 2) {
     q.flag_target = r.epoch * uint32_t(r.world);      // a rank's own partial counts like every other
-    // As many rounds as there are row tiles per rank: no warp waits for a peer inside the tile loop in this form, so
-    // rounds cost nothing, and only the last round's sums (1 / rounds of the traffic) are left for the end of the kernel.
-    q.stages = q.m_tiles_per_block;
-    if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
-    // ... and each round's column tiles cut further, as long as a round keeps 64 tiles (the tiles that run at the same
-    // time still share a few operand panels in L2).
-    static const int env_cols = TuningEnvInt("B200SD_REDUCE_COL_ROUNDS", 0);
-    for (int d = 1; d <= p.num_n_tiles; ++d) {
-      const int64_t per_round = int64_t(r.world) * (q.m_tiles_per_block / q.stages) * (p.num_n_tiles / d);
-      if (p.num_n_tiles % d == 0 && per_round >= 64) q.col_rounds = d;
+    // Rounds: no warp waits for a peer inside the tile loop in this form, so rounds cost no rendezvous, and only the last
+    // round's sums (1 / rounds of the traffic) are left for the end of the kernel.  A round gives every owner a
+    // sub-block of mtps x ntps tiles; the sub-block is kept as square as its 64 / world tiles allow, because the tiles
+    // of a round run at the same time and share the mtps row panels of A and ntps column panels of B in L2.
+    {
+      const int64_t want = std::max<int64_t>(1, 64 / r.world);
+      int best_m = q.m_tiles_per_block, best_n = p.num_n_tiles;
+      for (int mt = 1; mt <= q.m_tiles_per_block; ++mt) {
+        if (q.m_tiles_per_block % mt) continue;
+        for (int nt = 1; nt <= p.num_n_tiles; ++nt) {
+          if (p.num_n_tiles % nt || int64_t(mt) * nt < want) continue;
+          const bool better = mt + nt < best_m + best_n || (mt + nt == best_m + best_n && mt * nt < best_m * best_n);
+          if (better) { best_m = mt; best_n = nt; }
+        }
+      }
+      q.stages = q.m_tiles_per_block / best_m;
+      q.col_rounds = p.num_n_tiles / best_n;
     }
+    static const int env_cols = TuningEnvInt("B200SD_REDUCE_COL_ROUNDS", 0);
+    if (env_stages > 0 && q.m_tiles_per_block % env_stages == 0) q.stages = env_stages;
     if (env_cols > 0 && p.num_n_tiles % env_cols == 0) q.col_rounds = env_cols;
   }
   q.stage_multicast = (r.emulate || !r.pull) ? nullptr : static_cast<uint16_t*>(r.stage_multicast);
