@@ -116,6 +116,15 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def c4_link_bytes(world, m, n, in_switch):
+    """Bytes every rank must send over NVLink (per direction) to sum the bf16 [m, n] partials of a K-split and leave the sum
+    on every rank.  Without the switch's help: reduce-scatter + all-gather, 2 (N-1)/N of the result.  With the in-switch sum
+    (multimem.ld_reduce / multimem.st): every partial block leaves its producer once -- the own block too, it is added in
+    the switch like the others -- and every finished block once: (N + 1)/N of the result."""
+    full = float(m) * n * 2
+    return full * (world + 1) / world if in_switch else 2.0 * (world - 1) / world * full
+
+
 def algorithmic_bytes(kind, m, n, k):
     if kind == "c2":
         return k * n + m * k + 2 * m * n
@@ -422,8 +431,8 @@ class Bench:
             overlap = 2
         if overlap == 2:
             # Measured on 8192 x 28672 x 8192: 2 GPUs -- pull by the own tile's warp 0.73 ms, push 0.73, reducer warps 0.76;
-            # 4 GPUs -- reducer warps 0.40, push 0.44, own tile's warp 0.51; 8 GPUs -- reducer warps 0.52 (an earlier build of
-            # them), push 0.57 (one NCCL all-reduce behind the dot: 0.92 / 0.66 / 0.54).
+            # 4 GPUs -- reducer warps 0.40, push 0.44, own tile's warp 0.51; 8 GPUs -- reducer warps 0.36, push 0.41, own tile's
+            # warp 0.42 (one NCCL all-reduce behind the dot: 0.92 / 0.66 / 0.54).
             pull = args.pull if args.pull >= 0 else (1 if self.world == 2 else 2)
             multicast = multicast if multicast >= 0 else (1 if pull else 0)
             fused = [sharding.PeerReducedRowParallelScaledDot(lm, ln, device=self.dev, multicast=bool(multicast), pull=int(pull))
@@ -433,7 +442,7 @@ class Bench:
                 sets[i] = (sets[i][0], sets[i][1], [f.out] + list(sets[i][2][1:]))
             how = "formed inside the dot's kernel over peer memory (no collective launch"
             if pull:
-                how += (", partials fetched by the rows' owner" if pull == 1 else ", partials fetched piecewise by all warps of the rows' owner during the next round") + \
+                how += (", partials fetched by the rows' owner" if pull == 1 else ", partials fetched by the reducer warps of the rows' owner") + \
                     (" and added in the NVSwitch" if fused[0].in_switch_sum else " with peer loads")
             return runners, how + (", finished rows via NVSwitch multicast)" if fused[0].multicast else ")")
         if overlap == 1:
@@ -609,7 +618,7 @@ class Bench:
             flops = 2.0 * m4 * n4 * k4
             fp8_peak = 2.0 * peaks["bf16_tflops"]
             t_tensor = flops / world / (fp8_peak * 1e9)
-            link_bytes = 2.0 * (world - 1) / world * m4 * n4 * 2
+            link_bytes = c4_link_bytes(world, m4, n4, "NVSwitch" in how and "fetched" in how)
             t_link = link_bytes / 770e9 * 1e3
             out["c4"] = {"workload": WORKLOAD_NAME["c4"], "m": m4, "n": n4, "k": k4, "n_gpus": world, "ms": ms,
                          "value": flops / ms / 1e9, "unit": "TFLOP/s", "sum": how,
@@ -721,7 +730,7 @@ def gpu_arm(args):
         # tensor peak and the bytes every rank must send (reduce-scatter + all-gather of the bf16 [m, n] result)
         # at the measured peer-copy rate of this pool, 770 GB/s per direction.
         t_tensor_ms = flops / world / (fp8_peak * 1e9)
-        link_bytes = 2.0 * (world - 1) / world * m * n * 2
+        link_bytes = c4_link_bytes(world, m, n, "NVSwitch" in c4_how and "fetched" in c4_how)
         t_link_ms = link_bytes / 770e9 * 1e3
         roof["fused"] = {"bound": "tensor" if t_tensor_ms >= t_link_ms else "nvlink", "tensor_ms": t_tensor_ms, "nvlink_ms": t_link_ms,
                          "nvlink_bytes_per_rank": link_bytes, "target_ms": max(t_tensor_ms, t_link_ms),
