@@ -145,6 +145,9 @@ typedef struct B200SD_DotS8 {
  * the minor one of BOTH operands (A is [m,k], B is [n,k]), an optional batch dimension is the
  * major one, and each scale tensor is row-major [rows, k/32] of f8e8m0fnu -- the plain HLO
  * operand, not a library-specific swizzled form.  k must be a multiple of 32; m and n are free.
+ * The scale arrays may be padded ([batch, rows >= m|n, cols >= k/32], given by the *_scale_rows /
+ * *_scale_cols fields): only the leading [rows, k/32] corner is read, exactly the slice
+ * `BuildBlockScaledDotInput` takes (xla/backends/gpu/transforms/block_scaling_rewriter.cc:469-518).
  */
 typedef struct B200SD_BlockScaledDotMx {
   size_t struct_size;            /* sizeof(B200SD_BlockScaledDotMx) */
@@ -160,6 +163,11 @@ typedef struct B200SD_BlockScaledDotMx {
   float alpha;                   /* GemmBackendConfig.alpha_real; XLA writes 1 */
   int32_t batch_count;           /* 0 or 1: plain matrices */
   int32_t kernel;                /* B200SD_KERNEL_AUTO, B200SD_KERNEL_MX_256 or B200SD_KERNEL_MX_224 */
+  /* Fields below were added later: a caller whose struct_size stops before them gets 0 (no padding). */
+  int64_t a_scale_rows;          /* extents of a padded a_scale, [batch, a_scale_rows, a_scale_cols]; 0 = m and k/32 */
+  int64_t a_scale_cols;
+  int64_t b_scale_rows;          /* the same for b_scale; 0 = n and k/32 */
+  int64_t b_scale_cols;
 } B200SD_BlockScaledDotMx;
 
 /* One-time set-up for the current device (kernel attributes, SM count).  Called implicitly by the

@@ -315,7 +315,9 @@ def evaluate(text, params):
             (lt, lv), (rt, rv), (st, sv), (ut, uv) = a[:4]
             assert len(a) == 4 and st == ut == "f8e8m0fnu", "only the MX form (f8e8m0fnu scales, no global scale) is evaluated"
             code = {"f32": o.F32, "bf16": o.BF16, "f16": o.F16}[t]
-            val = (t, o.block_scaled_dot(lv, rv, sv, uv, a_kind=_KIND[lt], b_kind=_KIND[rt], out_dtype=code))
+            bs = re.search(r"block_size\W*(\d+)", attrs)          # explicit block size (block_scaling_rewriter.cc:613-621)
+            val = (t, o.block_scaled_dot(lv, rv, sv, uv, a_kind=_KIND[lt], b_kind=_KIND[rt], out_dtype=code,
+                                         block_size=int(bs.group(1)) if bs else None))
         elif op == "tuple":
             val = ("tuple", tuple(v for _, v in a))
         elif op == "get-tuple-element":

@@ -192,7 +192,7 @@ def mx_dequantize(codes: np.ndarray, scale_codes: np.ndarray, kind: str = "e4m3f
 
 
 def block_scaled_dot(a, b, a_scale, b_scale, *, a_kind="e4m3fn", b_kind="e4m3fn", out_dtype=F32,
-                     alpha=1.0):
+                     alpha=1.0, block_size=None):
     """`__op$block_scaled_dot` / `__cublas$lt$matmul$mx`
     (xla/backends/gpu/transforms/block_scaling_rewriter.h:30-77, xla/service/gpu/thunk_emitter.cc:939-988):
 
@@ -201,9 +201,25 @@ def block_scaled_dot(a, b, a_scale, b_scale, *, a_kind="e4m3fn", b_kind="e4m3fn"
     with both operands stored contracting-dimension-minor and an optional leading batch dimension.
     The reference's expansion (block_scaling_rewriter.cc:222-262) dequantizes into the RESULT type
     and then takes an ordinary dot, whose products the interpreter accumulates in f32
-    (hlo_evaluator_typed_visitor.h:1271-1340).  Returns D in the spelling of cast_output()."""
+    (hlo_evaluator_typed_visitor.h:1271-1340).  Scale arrays may be padded
+    (BuildBlockScaledDotInput, block_scaling_rewriter.cc:469-518): extra rows are always sliced
+    off; extra columns only when `block_size` is given explicitly (the backend config's
+    block_scaled_dot_backend_config.block_size), since otherwise the block size is the ratio of
+    the minor extents.  Returns D in the spelling of cast_output()."""
     a = np.asarray(a, dtype=np.uint8)
     b = np.asarray(b, dtype=np.uint8)
+    a_scale = np.asarray(a_scale, dtype=np.uint8)
+    b_scale = np.asarray(b_scale, dtype=np.uint8)
+    for x, s in ((a, a_scale), (b, b_scale)):
+        if s.shape[-2] < x.shape[-2] or s.shape[:-2] != x.shape[:-2]:
+            raise ValueError("scale rows must cover the operand's rows (block_scaling_rewriter.cc:489-493)")
+        if block_size is not None and s.shape[-1] * block_size < x.shape[-1]:
+            raise ValueError("scale columns must cover k / block_size (block_scaling_rewriter.cc:496-505)")
+    a_scale = a_scale[..., : a.shape[-2], :]
+    b_scale = b_scale[..., : b.shape[-2], :]
+    if block_size is not None:
+        a_scale = a_scale[..., : -(-a.shape[-1] // block_size)]
+        b_scale = b_scale[..., : -(-b.shape[-1] // block_size)]
     np_type = {F32: np.float32, F16: np.float16, BF16: None}[out_dtype]
     if np_type is None:      # bf16: dequantized values rounded to bf16, then widened for the dot
         a_dq = bf16_bits_to_f32(f32_to_bf16_bits(mx_dequantize(a, a_scale, a_kind)))

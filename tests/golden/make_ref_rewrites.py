@@ -28,6 +28,14 @@ The reference's tests run its rewriter for a Hopper target, which transposes B i
 column-major form cuBLASLt wants there; on Blackwell the rewriter inserts no transposes
 (gemm_rewriter.cc:1535-1554, NoTransposeOnBlackwellF8 at gemm_rewriter_fp8_test.cc:3065-3108).
 Consumers therefore compare operand roots and dimension numbers modulo `transpose`.
+
+A second file, tests/golden/ref_block_scaled.json, holds the `__op$block_scaled_dot` modules of
+  * xla/backends/gpu/transforms/block_scaling_rewriter_test.cc (what BlockScalingRewriter makes of each form) and
+  * xla/backends/gpu/transforms/block_scaling_rewriter_cudnn_test.cc (a library run compared with the expansion
+    under an ErrorSpec),
+each with `library`: whether the reference, given a library that supports block-scaled dots, hands this module to it
+(the test builds the pass with kCudnnSupportsBlockScaledDot / kCudnnVersion and its CHECK lines name
+`__cudnn$blockScaledDot` or a custom call) or expands it into dequantize + dot.
 """
 import json
 import os
@@ -291,7 +299,35 @@ def cases_of(rel_path, fixture_pattern, name_filter=None):
     return cases
 
 
+BLOCK_TESTS = ("xla/backends/gpu/transforms/block_scaling_rewriter_test.cc",
+               "xla/backends/gpu/transforms/block_scaling_rewriter_cudnn_test.cc")
+
+
+def block_scaled_cases():
+    cases = []
+    for rel_path in BLOCK_TESTS:
+        src = open(os.path.join(ROOT, rel_path)).read()
+        for name, line, body in split_tests(src, r"BlockScalingRewriter\w*Test"):
+            modules = [m for m in raw_strings(body) if "__op$block_scaled_dot" in m and re.search(r"\bparameter\(", m)]
+            if not modules:
+                continue
+            with_library = bool(re.search(r"kCudnnSupportsBlockScaledDot|kCudnnVersion\b", body))
+            library = with_library and bool(re.search(r"CHECK[^\n]*(__cudnn\$blockScaledDot|custom-call\()", body))
+            m = re.search(r"ErrorSpec\(\s*/\*aabs=\*/\s*([0-9.e+-]+)\s*,\s*/\*arel=\*/\s*([0-9.e+-]+)\s*\)", body)
+            cases.append({"name": name, "source": f"{rel_path}:{line}", "hlo": modules[0].strip() + "\n",
+                          "library": library, "numeric": "RunAndCompare" in body,
+                          "error_spec": [float(m.group(1)), float(m.group(2))] if m else None})
+    return cases
+
+
 def main():
+    blocks = block_scaled_cases()
+    with open(os.path.join(HERE, "ref_block_scaled.json"), "w") as f:
+        json.dump({"sources": list(BLOCK_TESTS),
+                   "note": "`__op$block_scaled_dot` modules of the reference's BlockScalingRewriter tests, extracted as text; "
+                           "`library` = handed to a block-scaled library kernel rather than expanded, see the generating script",
+                   "cases": blocks}, f, indent=1)
+    print(f"{len(blocks)} block-scaled cases, {sum(c['library'] for c in blocks)} taken by the library path")
     fp8 = cases_of(FP8_TEST, r"ParameterizedFp8GemmRewriteTest")
     int8 = cases_of(GEMM_TEST, r"\w*GemmRewriteTest\w*", name_filter=r"^Int8Gemm")
     out = {

@@ -251,6 +251,16 @@ def test_block_scaled_frames():
     ]
     for ops, res in ok:
         BlockScaledDotCall(ops, res).instantiate()
+    # padded scales (block_scaling_rewriter.cc:469-518): rows always, columns with the block size stated
+    pad_rows = [Buffer(F8E4M3FN, (4, 120, 96)), Buffer(F8E4M3FN, (4, 120, 96)), Buffer(E8, (4, 128, 3)), Buffer(E8, (4, 128, 3))]
+    pad_both = [Buffer(F8E4M3FN, (4, 120, 96)), Buffer(F8E4M3FN, (4, 120, 96)), Buffer(E8, (4, 128, 4)), Buffer(E8, (4, 128, 4))]
+    BlockScaledDotCall(pad_rows, [Buffer(F16, (4, 120, 120))]).instantiate()
+    BlockScaledDotCall(pad_both, [Buffer(F16, (4, 120, 120))], block_size=32).instantiate()
+    for ops, kw, code in [(pad_both, {}, 3), (pad_both, {"block_size": 16}, 12),
+                          (pad_rows[:2] + [Buffer(E8, (4, 100, 3)), Buffer(E8, (4, 128, 3))], {}, 3)]:
+        with pytest.raises(XlaFfiError) as e:
+            BlockScaledDotCall(ops, [Buffer(F16, (4, 120, 120))], **kw).instantiate()
+        assert e.value.code == code
     a, b = Buffer(F8E4M3FN, (8, 128)), Buffer(F8E4M3FN, (16, 128))
     sa, sb, d = Buffer(E8, (8, 4)), Buffer(E8, (16, 4)), Buffer(F32, (8, 16))
     for ops, res, code in [

@@ -37,9 +37,9 @@ MX_256, MX_224 = 6, 7          # B200SD_KERNEL_MX_256 / _224: one accumulator of
 WIDTHS = pytest.mark.parametrize("kernel", [MX_256, MX_224], ids=["tile256", "tile224"])
 
 
-def _run(dev, a, b, sa, sb, ka="e4m3fn", kb="e4m3fn", out=torch.float32, alpha=1.0, kernel=0):
+def _run(dev, a, b, sa, sb, ka="e4m3fn", kb="e4m3fn", out=torch.float32, alpha=1.0, kernel=0, block_size=None):
     d = cublas_lt_matmul_mx(_dev(a, dev, F8[ka]), _dev(b, dev, F8[kb]), _dev(sa, dev), _dev(sb, dev), out_dtype=out,
-                            alpha_real=alpha, selected_algorithm=kernel)
+                            alpha_real=alpha, selected_algorithm=kernel, block_size=block_size)
     torch.cuda.synchronize()
     assert device_status() == 0
     return d
@@ -152,6 +152,34 @@ def test_mx_dot_full_size_sampled(cuda_device, kernel):
     assert torch.equal(d2, d * 2)
 
 
+@pytest.mark.parametrize("m,n,k,batch,a_pad,b_pad", [
+    (120, 120, 96, 4, (128, 4), (128, 4)),        # the reference's CudnnScaledDotPaddedScales shapes (block_scaling_rewriter_test.cc:329-345): byte loads
+    (250, 250, 224, 0, (256, 8), (256, 8)),       # Mxfp8_PaddedScales (block_scaling_rewriter_cudnn_test.cc:105-121): 4-byte rows, 7 of 8 scales in use
+    (300, 260, 512, 0, (304, 32), (264, 32)),     # rows of 32 bytes, 16 in use: TMA boxes over a strided corner
+    (256, 512, 384, 0, (256, 16), (512, 16)),     # 12 of 16 in use: the box reaches past the corner, which must read as zero
+    (384, 768, 512, 2, (400, 20), (768, 16)),     # batched; A's scales padded in both directions (word loads), B's not at all
+    (200, 136, 1024, 2, (208, 48), (144, 64)),    # batched TMA path, two groups of four k-blocks, different padding per operand
+])
+@WIDTHS
+def test_mx_padded_scales(cuda_device, m, n, k, batch, a_pad, b_pad, kernel):
+    """Scale arrays larger than [rows, k / 32]: only the leading corner is read, as the reference slices it
+    (block_scaling_rewriter.cc:469-518).  The padding holds NaN codes, so one padded byte taken for a scale, even
+    against an all-zero block of values, shows in the result."""
+    a, b, sa, sb = o.make_mx_operands(m + 3 * n + k, m, n, k, batch=batch)
+    lead = (batch,) if batch else ()
+    sa_p = np.full(lead + a_pad, 0xFF, np.uint8)
+    sb_p = np.full(lead + b_pad, 0xFF, np.uint8)
+    sa_p[..., :m, : k // 32] = sa
+    sb_p[..., :n, : k // 32] = sb
+    want = o.block_scaled_dot(a, b, sa, sb)
+    assert np.array_equal(o.block_scaled_dot(a, b, sa_p, sb_p, block_size=32), want)
+    got = _run(cuda_device, a, b, sa_p, sb_p, kernel=kernel, block_size=32).cpu().numpy()
+    assert np.isfinite(got).all()
+    _check(got, want, _abs_dot(a, b, sa, sb, "e4m3fn", "e4m3fn"), 2.0 ** -23)
+    # and bit for bit what the same call gives on the unpadded arrays
+    assert np.array_equal(got, _run(cuda_device, a, b, sa, sb, kernel=kernel).cpu().numpy())
+
+
 def test_mx_call_frame_contract(cuda_device):
     """Operand count, scale shape and types are checked when the call site is instantiated."""
     dev = cuda_device
@@ -169,6 +197,15 @@ def test_mx_call_frame_contract(cuda_device):
         BlockScaledDotCall([a, b, sc(s4)], [d]).instantiate()
     with pytest.raises(XlaFfiError):          # block size 64
         BlockScaledDotCall([a, b, sc(s4, (64, 2)), sc(t4, (32, 2))], [d]).instantiate()
+    with pytest.raises(XlaFfiError):          # scales that do not cover the rows
+        BlockScaledDotCall([a, b, sc(s4, (60, 4)), sc(t4)], [d]).instantiate()
+    s8 = torch.zeros((72, 8), dtype=torch.uint8, device=dev)
+    BlockScaledDotCall([a, b, sc(s8, (72, 4)), sc(t4)], [d]).instantiate()                 # extra scale rows are taken as they are
+    BlockScaledDotCall([a, b, sc(s8), sc(t4)], [d], block_size=32).instantiate()          # extra columns once the block size is stated
+    with pytest.raises(XlaFfiError):          # ... and not otherwise: [72, 8] over k = 128 reads as block size 16
+        BlockScaledDotCall([a, b, sc(s8), sc(t4)], [d]).instantiate()
+    with pytest.raises(XlaFfiError):
+        BlockScaledDotCall([a, b, sc(s4), sc(t4)], [d], block_size=16).instantiate()
     with pytest.raises(XlaFfiError):          # f32 scales
         BlockScaledDotCall([a, b, torch.zeros((64, 4), device=dev), torch.zeros((32, 4), device=dev)], [d]).instantiate()
     with pytest.raises(XlaFfiError):          # FP8 result

@@ -75,6 +75,8 @@ class BlockScaledDotMxArgs(C.Structure):
         ("alpha", C.c_float),
         ("batch_count", C.c_int32),
         ("kernel", C.c_int32),
+        ("a_scale_rows", C.c_int64), ("a_scale_cols", C.c_int64),
+        ("b_scale_rows", C.c_int64), ("b_scale_cols", C.c_int64),
     ]
 
 

@@ -312,7 +312,11 @@ int b200sd_scaled_dot_f8(const B200SD_ScaledDotF8* args, void* cuda_stream, char
 
 namespace {
 Status ConvertMx(const B200SD_BlockScaledDotMx& a, MxProblem* g) {
-  if (a.struct_size < sizeof(B200SD_BlockScaledDotMx)) return Status::Error(kInvalidArgument, "B200SD_BlockScaledDotMx.struct_size is smaller than this library's struct");
+  if (a.struct_size < offsetof(B200SD_BlockScaledDotMx, a_scale_rows)) return Status::Error(kInvalidArgument, "B200SD_BlockScaledDotMx.struct_size is smaller than this library's struct");
+  if (a.struct_size >= sizeof(B200SD_BlockScaledDotMx)) {
+    g->a_scale_rows = a.a_scale_rows; g->a_scale_cols = a.a_scale_cols;
+    g->b_scale_rows = a.b_scale_rows; g->b_scale_cols = a.b_scale_cols;
+  }
   g->m = a.m; g->n = a.n; g->k = a.k;
   g->batch = a.batch_count > 1 ? a.batch_count : 1;
   g->a_dtype = a.a_dtype; g->b_dtype = a.b_dtype;

@@ -1478,15 +1478,18 @@ Status MakeBatchedByteMatrixMap(CUtensorMap* map, const void* base, int64_t batc
   return Status::Ok();
 }
 
-// The same 3-D view without a shared-memory swizzle: the box lands row after row, box_cols bytes each.
+// A 3-D byte view [batch, rows, cols] without a shared-memory swizzle: the box lands row after row, box_cols bytes
+// each.  Rows are row_stride bytes apart and batches batch_stride (both multiples of 16); cols itself may be anything,
+// bytes past it read as zero.
 Status MakeBatchedPlainByteMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
-                               uint32_t box_cols, uint32_t box_rows) {
+                               int64_t row_stride, int64_t batch_stride, uint32_t box_cols, uint32_t box_rows) {
   EncodeTiledFn encode = GetEncodeTiled();
   if (encode == nullptr) return Status::Error(kInternal, "cuTensorMapEncodeTiled is not available from this driver");
-  if (cols % 16 != 0 || box_cols % 16 != 0) return Status::Error(kInvalidArgument, "the minor dimension and the box width must be multiples of 16 bytes");
+  if (row_stride % 16 != 0 || batch_stride % 16 != 0 || box_cols % 16 != 0 || cols > row_stride)
+    return Status::Error(kInvalidArgument, "the row and batch strides and the box width must be multiples of 16 bytes");
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return Status::Error(kInvalidArgument, "base address must be 16-byte aligned");
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows) * static_cast<cuuint64_t>(cols)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride), static_cast<cuuint64_t>(batch_stride)};
   const cuuint32_t box[3] = {box_cols, box_rows, 1};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem_strides,

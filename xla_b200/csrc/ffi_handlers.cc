@@ -341,9 +341,21 @@ ffi::Error DecodeMx(ffi::RemainingArgs operands, ffi::RemainingRets results, ffi
   a.k = lhs->dimensions()[o + 1];
   a.n = rhs->dimensions()[o];
   if (rhs->dimensions()[o + 1] != a.k) return MakeError(3, "contracting (minor) dimensions of a and b differ");
-  if (a.k % 32 != 0 || ls->dimensions()[o] != a.m || ls->dimensions()[o + 1] != a.k / 32 || rs->dimensions()[o] != a.n ||
-      rs->dimensions()[o + 1] != a.k / 32)
-    return MakeError(3, "scales must be [rows, k / 32]: one scale per block of 32 along the contracting dimension");
+  // Padded scale arrays are taken as they are: the kernel reads the leading [rows, k / 32] corner.  Extra rows are
+  // always allowed; extra columns only when the call states its block size (the `block_size` attribute, from
+  // block_scaled_dot_backend_config), because otherwise the block size is the ratio of the minor extents
+  // (block_scaling_rewriter.cc:98-113, 489-505).
+  const auto block_size = GetInt(attrs, "block_size");
+  if (block_size.has_value() && *block_size != 32) return MakeError(12, "block_size must be 32 (MX)");
+  const bool cols_ok = block_size.has_value()
+                           ? (ls->dimensions()[o + 1] >= a.k / 32 && rs->dimensions()[o + 1] >= a.k / 32)
+                           : (ls->dimensions()[o + 1] == a.k / 32 && rs->dimensions()[o + 1] == a.k / 32);
+  if (a.k % 32 != 0 || ls->dimensions()[o] < a.m || rs->dimensions()[o] < a.n || !cols_ok)
+    return MakeError(3, "scales must cover [rows, k / 32]: one scale per block of 32 along the contracting dimension");
+  a.a_scale_rows = ls->dimensions()[o];
+  a.a_scale_cols = ls->dimensions()[o + 1];
+  a.b_scale_rows = rs->dimensions()[o];
+  a.b_scale_cols = rs->dimensions()[o + 1];
   if ((*d)->dimensions()[o] != a.m || (*d)->dimensions()[o + 1] != a.n) return MakeError(3, "result shape is not [m, n]");
   if (rank == 3 && (rhs->dimensions()[0] != batch || ls->dimensions()[0] != batch || rs->dimensions()[0] != batch ||
                     (*d)->dimensions()[0] != batch))

@@ -30,6 +30,7 @@
 //
 // Output: the rewritten module as HLO text and a JSON description of the custom calls.
 #include <algorithm>
+#include <cctype>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -111,6 +112,7 @@ struct Gemm {
   int64_t batch = 0, m = 0, n = 0, k = 0;         // logical (unpadded) extents; m x n is the result AS COMPUTED
   bool has_c = false, has_bias = false, has_d_scale = false, has_dequant = false;
   bool swapped = false;                // operands were exchanged to produce a column-major result as D^T
+  int64_t explicit_block = 0;          // MX: the block size the source call states in its backend config (0: implied by the shapes)
   bool mx = false;                     // MX block-scaled dot: operands a, b, a_scale, b_scale (thunk_emitter.cc:939-988)
   Instr* amax = nullptr;               // the f32[] second result, when damax
   Instr* acc = nullptr;                // the s32 second result, when emit_s32
@@ -834,7 +836,21 @@ class Rewriter {
     const size_t o = rank - 2;
     const int64_t m = a.dims[o], k = a.dims[o + 1], n = b.dims[o];
     if (b.dims[o + 1] != k) return Refuse(cc, "block-scaled dot: contracting dimensions differ");
-    if (k % 32 != 0 || sa.dims[o] != m || sb.dims[o] != n || sa.dims[o + 1] * 32 != k || sb.dims[o + 1] * 32 != k)
+    // An explicit block size comes in the backend config (block_scaling_rewriter.cc:613-621); it is what allows scale
+    // arrays padded along k.  Extra scale rows are allowed either way (block_scaling_rewriter.cc:489-493).  The
+    // call takes the padded arrays as they are and reads the leading [rows, k / 32] corner.
+    int64_t explicit_block = 0;
+    {
+      const size_t p = cc->attrs.find("block_size");
+      if (p != std::string::npos) {
+        size_t q = p + 10;
+        while (q < cc->attrs.size() && !std::isdigit(static_cast<unsigned char>(cc->attrs[q]))) ++q;
+        explicit_block = std::strtoll(cc->attrs.c_str() + q, nullptr, 10);
+        if (explicit_block != 32) return Refuse(cc, "block-scaled dot: the block size must be 32 (MX), got " + std::to_string(explicit_block));
+      }
+    }
+    if (k % 32 != 0 || sa.dims[o] < m || sb.dims[o] < n) return Refuse(cc, "block-scaled dot: the block size must be 32 (scales [rows, k / 32])");
+    if (explicit_block ? (sa.dims[o + 1] * 32 < k || sb.dims[o + 1] * 32 < k) : (sa.dims[o + 1] * 32 != k || sb.dims[o + 1] * 32 != k))
       return Refuse(cc, "block-scaled dot: the block size must be 32 (scales [rows, k / 32])");
     if (d.dims[o] != m || d.dims[o + 1] != n) return Refuse(cc, "block-scaled dot: result shape is not [m, n]");
     if (rank == 3 && !(b.dims[0] == a.dims[0] && sa.dims[0] == a.dims[0] && sb.dims[0] == a.dims[0] && d.dims[0] == a.dims[0]))
@@ -842,6 +858,7 @@ class Rewriter {
     auto g = std::make_unique<Gemm>();
     g->f8 = true;
     g->mx = true;
+    g->explicit_block = explicit_block;
     g->m = m; g->n = n; g->k = k;
     g->batched = rank == 3;
     g->batch = rank == 3 ? a.dims[0] : 0;
@@ -1313,7 +1330,9 @@ std::string Rewriter::EmitHlo(const Module& m) const {
       o << "), custom_call_target=\"" << (g.mx ? "b200$block_scaled_dot$mx" : g.f8 ? "b200$scaled_dot$f8" : "b200$dot$s8")
         << "\", api_version=API_VERSION_TYPED_FFI, backend_config={";
       if (g.mx) {
-        o << "alpha_real = " << F64(g.alpha) << " : f64}\n";
+        o << "alpha_real = " << F64(g.alpha) << " : f64";
+        if (g.explicit_block) o << ", block_size = " << g.explicit_block << " : i64";
+        o << "}\n";
       } else if (g.f8) {
         o << "alpha_real = " << F64(g.alpha) << " : f64, beta = " << F64(g.beta) << " : f64, epilogue = " << g.epilogue
           << " : i32, lhs_contracting_dim = " << g.lhs_contracting << " : i64, rhs_contracting_dim = " << g.rhs_contracting
@@ -1419,6 +1438,7 @@ std::string Rewriter::EmitJson() const {
     j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "]}], \"attrs\": {";
     if (c.mx) {
       j << "\"alpha_real\": " << F64(c.alpha);
+      if (c.explicit_block) j << ", \"block_size\": " << c.explicit_block;
     } else if (c.f8) {
       j << "\"alpha_real\": " << F64(c.alpha) << ", \"beta\": " << F64(c.beta) << ", \"epilogue\": " << c.epilogue
         << ", \"lhs_contracting_dim\": " << c.lhs_contracting << ", \"rhs_contracting_dim\": " << c.rhs_contracting

@@ -169,6 +169,10 @@ struct MxProblem {
   const void* b = nullptr;
   const void* a_scale = nullptr;
   const void* b_scale = nullptr;
+  // Extents of the scale arrays when they are padded ([batch, rows >= m | n, cols >= k / 32], the form the reference's
+  // BuildBlockScaledDotInput slices, block_scaling_rewriter.cc:469-518); 0 = exactly [rows, k / 32].
+  int64_t a_scale_rows = 0, a_scale_cols = 0;
+  int64_t b_scale_rows = 0, b_scale_cols = 0;
   float alpha = 1.0f;
   void* d = nullptr;
   int32_t d_dtype = kF32;

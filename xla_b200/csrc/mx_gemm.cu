@@ -42,7 +42,7 @@ namespace b200sd {
 Status MakeBatchedByteMatrixMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
                                 uint32_t box_cols, uint32_t box_rows);
 Status MakeBatchedPlainByteMap(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols,
-                               uint32_t box_cols, uint32_t box_rows);
+                               int64_t row_stride, int64_t batch_stride, uint32_t box_cols, uint32_t box_rows);
 int MaxPairClusters();
 
 namespace {
@@ -104,7 +104,9 @@ constexpr size_t MxSmemBytes() {
 
 struct MxArgs {
   int64_t m, n, k;
-  int64_t scale_cols;              // k / 32: bytes per row of SA and SB
+  int64_t scale_cols;              // k / 32: scales in use per row of SA and SB
+  int64_t sfa_ld, sfb_ld;          // bytes between rows of SA / SB (>= scale_cols; more when the arrays are padded)
+  int64_t sfa_batch, sfb_batch;    // bytes between batches
   int32_t batch;
   int32_t num_m_tiles, num_n_tiles, num_k_blocks;
   int32_t raster_group;
@@ -428,15 +430,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           mx_tile_coords(cluster_id + int32_t(gi / groups_per_tile) * num_clusters, p, &mt, &nt, &bt);
           const int64_t a_row0 = int64_t(mt) * kMxTileM + int64_t(rank) * kMxBM + lane;
           const int64_t b_row0 = int64_t(nt) * kMxBN + lane;
-          const uint8_t* sfa_b = p.sfa + int64_t(bt) * p.m * p.scale_cols;
-          const uint8_t* sfb_b = p.sfb + int64_t(bt) * p.n * p.scale_cols;
+          const uint8_t* sfa_b = p.sfa + int64_t(bt) * p.sfa_batch;
+          const uint8_t* sfb_b = p.sfb + int64_t(bt) * p.sfb_batch;
           const int64_t col0 = int64_t(gi % groups_per_tile) * 16;
 #pragma unroll
           for (int g = 0; g < 12; ++g) {
             const bool is_a = g < 4;
             const int64_t row = is_a ? a_row0 + 32 * g : b_row0 + 32 * (g - 4);
             const bool valid = row < (is_a ? p.m : p.n);
-            const uint8_t* src = (is_a ? sfa_b : sfb_b) + (valid ? row * p.scale_cols + col0 : 0);
+            const uint8_t* src = (is_a ? sfa_b : sfb_b) + (valid ? row * (is_a ? p.sfa_ld : p.sfb_ld) + col0 : 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint32_t v = 0;
@@ -589,6 +591,10 @@ Status ValidateMx(const MxProblem& g) {
   }
   if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch < 0) return Status::Error(kInvalidArgument, "block-scaled dot: empty or negative dimension");
   if (g.k % 32 != 0) return Status::Error(kInvalidArgument, "block-scaled dot: the contracting dimension must be a multiple of the block size 32");
+  if (g.a_scale_rows < 0 || g.a_scale_cols < 0 || g.b_scale_rows < 0 || g.b_scale_cols < 0 ||
+      (g.a_scale_rows > 0 && g.a_scale_rows < g.m) || (g.b_scale_rows > 0 && g.b_scale_rows < g.n) ||
+      (g.a_scale_cols > 0 && g.a_scale_cols < g.k / 32) || (g.b_scale_cols > 0 && g.b_scale_cols < g.k / 32))
+    return Status::Error(kInvalidArgument, "block-scaled dot: padded scale extents must cover [rows, k / 32]");
   if (g.kernel != kKernelAuto && g.kernel != kKernelMxPair256 && g.kernel != kKernelMxPair224)
     return Status::Error(kInvalidArgument, "block-scaled dot: kernel must be AUTO, MX_256 or MX_224");
   if (g.m >= (1ll << 31) || g.n >= (1ll << 31) || g.k >= (1ll << 31)) return Status::Error(kInvalidArgument, "block-scaled dot: dimension too large");
@@ -630,14 +636,20 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   MxArgs p{};
   p.m = g.m; p.n = g.n; p.k = g.k;
   p.scale_cols = g.k / 32;
-  // Scale rows that start on 16-byte boundaries can be fetched as TMA boxes of 16 bytes x 128 / 256 rows.
-  p.sf_bulk_ok = (p.scale_cols % 16 == 0 && (reinterpret_cast<uintptr_t>(g.a_scale) & 15) == 0 &&
-                  (reinterpret_cast<uintptr_t>(g.b_scale) & 15) == 0) ? 1 : 0;
+  // Padded scale arrays: only the leading [rows, k / 32] corner is read, the rest is stepped over.
+  p.sfa_ld = g.a_scale_cols > 0 ? g.a_scale_cols : p.scale_cols;
+  p.sfb_ld = g.b_scale_cols > 0 ? g.b_scale_cols : p.scale_cols;
+  p.sfa_batch = (g.a_scale_rows > 0 ? g.a_scale_rows : g.m) * p.sfa_ld;
+  p.sfb_batch = (g.b_scale_rows > 0 ? g.b_scale_rows : g.n) * p.sfb_ld;
+  // Scale rows that start on 16-byte boundaries can be fetched as TMA boxes of 16 bytes x 128 / 256 rows (the map's
+  // extents are the corner in use, so padding reads as zero like everything else outside it).
+  p.sf_bulk_ok = (p.sfa_ld % 16 == 0 && p.sfb_ld % 16 == 0 && p.sfa_batch % 16 == 0 && p.sfb_batch % 16 == 0 &&
+                  (reinterpret_cast<uintptr_t>(g.a_scale) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.b_scale) & 15) == 0) ? 1 : 0;
   CUtensorMap tmap_sfa = tmap_a, tmap_sfb = tmap_b;       // placeholders the gather path never touches
   if (p.sf_bulk_ok) {
-    st = MakeBatchedPlainByteMap(&tmap_sfa, g.a_scale, batch, g.m, p.scale_cols, 16, kMxBM);
+    st = MakeBatchedPlainByteMap(&tmap_sfa, g.a_scale, batch, g.m, p.scale_cols, p.sfa_ld, p.sfa_batch, 16, kMxBM);
     if (!st.ok()) return st;
-    st = MakeBatchedPlainByteMap(&tmap_sfb, g.b_scale, batch, g.n, p.scale_cols, 16, uint32_t(bn));
+    st = MakeBatchedPlainByteMap(&tmap_sfb, g.b_scale, batch, g.n, p.scale_cols, p.sfb_ld, p.sfb_batch, 16, uint32_t(bn));
     if (!st.ok()) return st;
   }
   p.batch = int32_t(batch);
@@ -650,7 +662,7 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   p.idesc = make_idesc_mx(g.a_dtype == kF8E5M2 ? 1u : 0u, g.b_dtype == kF8E5M2 ? 1u : 0u, kMxTileM, uint32_t(bn));
   p.sfa = static_cast<const uint8_t*>(g.a_scale);
   p.sfb = static_cast<const uint8_t*>(g.b_scale);
-  p.sf_words_ok = (p.scale_cols % 4 == 0 && (reinterpret_cast<uintptr_t>(g.a_scale) & 3) == 0 &&
+  p.sf_words_ok = (p.scale_cols % 4 == 0 && p.sfa_ld % 4 == 0 && p.sfb_ld % 4 == 0 && (reinterpret_cast<uintptr_t>(g.a_scale) & 3) == 0 &&
                    (reinterpret_cast<uintptr_t>(g.b_scale) & 3) == 0) ? 1 : 0;
   p.alpha = g.alpha;
   p.d = g.d;

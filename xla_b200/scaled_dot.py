@@ -245,8 +245,12 @@ class BlockScaledDotCall(FfiCall):
     [workspace] -- the arrangement of `__cublas$lt$matmul$mx`
     (xla/service/gpu/thunk_emitter.cc:939-988)."""
 
-    def __init__(self, operands: Sequence, results: Sequence, *, alpha_real: float = 1.0, selected_algorithm: int = 0):
-        super().__init__(TARGET_MX, operands, results, {"alpha_real": float(alpha_real), "selected_config": int(selected_algorithm)})
+    def __init__(self, operands: Sequence, results: Sequence, *, alpha_real: float = 1.0, selected_algorithm: int = 0,
+                 block_size: Optional[int] = None):
+        attrs = {"alpha_real": float(alpha_real), "selected_config": int(selected_algorithm)}
+        if block_size is not None:      # block_scaled_dot_backend_config.block_size: states the block size, allows padded scale columns
+            attrs["block_size"] = int(block_size)
+        super().__init__(TARGET_MX, operands, results, attrs)
 
 
 def _current_stream_and_device(t):
@@ -317,12 +321,15 @@ def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=N
 
 
 def cublas_lt_matmul_mx(a, b, a_scale, b_scale, *, out_dtype=None, alpha_real: float = 1.0, workspace=None, out=None,
-                        selected_algorithm: int = 0):
+                        selected_algorithm: int = 0, block_size: Optional[int] = None):
     """Runs one MX block-scaled dot on the current CUDA stream and returns D.
 
     a: [m, k] or [batch, m, k] float8; b: [n, k] or [batch, n, k] float8 (the contracting dimension is
     the minor one of both, as `__op$block_scaled_dot` fixes it); a_scale / b_scale: [..., rows, k / 32]
-    float8_e8m0fnu (uint8 tensors holding the code points are taken as such)."""
+    float8_e8m0fnu (uint8 tensors holding the code points are taken as such).  Scale tensors may be
+    padded: extra rows always, extra columns when `block_size=32` states the block size (otherwise it
+    is implied by the shapes); only the leading [rows, k / 32] corner is used, like the slice in
+    xla/backends/gpu/transforms/block_scaling_rewriter.cc:469-518."""
     torch = _torch()
     out_dtype = out_dtype or torch.float32
     lead = tuple(a.shape[:-2])
@@ -335,7 +342,7 @@ def cublas_lt_matmul_mx(a, b, a_scale, b_scale, *, out_dtype=None, alpha_real: f
 
     operands = [a, b, scale_buffer(a_scale), scale_buffer(b_scale)]
     results = [d] + ([workspace] if workspace is not None else [])
-    call = BlockScaledDotCall(operands, results, alpha_real=alpha_real, selected_algorithm=selected_algorithm)
+    call = BlockScaledDotCall(operands, results, alpha_real=alpha_real, selected_algorithm=selected_algorithm, block_size=block_size)
     stream, dev = _current_stream_and_device(a)
     call.run(stream, dev)
     call.close()
