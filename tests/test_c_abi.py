@@ -221,10 +221,49 @@ def test_attribute_spellings():
         FfiCall("b200$scaled_dot$f8", ops, res, {"alpha_imag": 1.0}).instantiate()
 
 
+def test_batch_strides_of_the_backend_config():
+    """GemmBackendConfig.lhs_stride / rhs_stride (backend_configs.proto:121-122) are what the reference's rewriter
+    always writes, rows * cols of one batch entry (gemm_rewriter.cc:705-721): accepted in that form, refused otherwise."""
+    ops = [Buffer(F8E4M3FN, (2, 64, 128)), Buffer(F8E4M3FN, (2, 128, 32)), Buffer(F32, ()), Buffer(F32, ())]
+    res = [Buffer(BF16, (2, 64, 32))]
+    base = {"lhs_batch_dims": [0], "rhs_batch_dims": [0], "lhs_contracting_dim": 2, "rhs_contracting_dim": 1}
+    FfiCall("b200$scaled_dot$f8", ops, res, dict(base, lhs_stride=64 * 128, rhs_stride=128 * 32)).instantiate()
+    FfiCall("b200$scaled_dot$f8", ops[:1] + ops[1:], res, dict(base, lhs_stride=64 * 128)).instantiate()
+    for bad in ({"lhs_stride": 64 * 128 + 16}, {"rhs_stride": 0}):
+        with pytest.raises(XlaFfiError) as e:
+            FfiCall("b200$scaled_dot$f8", ops, res, dict(base, **bad)).instantiate()
+        assert e.value.code == 12 and "stride" in e.value.message
+    # rank 2: the same fields describe the one matrix
+    ops2, res2 = _f8_frame()
+    a_dims, b_dims = ops2[0].dims, ops2[1].dims
+    FfiCall("b200$scaled_dot$f8", ops2, res2, {"lhs_stride": a_dims[0] * a_dims[1], "rhs_stride": b_dims[0] * b_dims[1]}).instantiate()
+    s8 = [Buffer(S8, (3, 64, 128)), Buffer(S8, (3, 128, 32))]
+    Int8DotCall(s8, [Buffer(S32, (3, 64, 32))], batched=True, lhs_contracting_dim=2, rhs_contracting_dim=1).instantiate()
+    with pytest.raises(XlaFfiError) as e:
+        FfiCall("b200$dot$s8", s8, [Buffer(S32, (3, 64, 32))], dict(base, lhs_stride=1)).instantiate()
+    assert e.value.code == 12
+
+
 def test_int8_frames():
     Int8DotCall([Buffer(S8, (64, 128)), Buffer(S8, (128, 32))], [Buffer(S32, (64, 32))]).instantiate()
     Int8DotCall([Buffer(S8, (64, 128)), Buffer(S8, (128, 32)), Buffer(F32, (64,)), Buffer(F32, (32,))],
                 [Buffer(BF16, (64, 32)), Buffer(S32, (64, 32))], emit_s32=True).instantiate()
+    # one leading batch dimension, as for the FP8 call; contracting dimensions index the rank-3 operands
+    Int8DotCall([Buffer(S8, (3, 64, 128)), Buffer(S8, (3, 128, 32))], [Buffer(S32, (3, 64, 32))], batched=True,
+                lhs_contracting_dim=2, rhs_contracting_dim=1).instantiate()
+    Int8DotCall([Buffer(S8, (3, 64, 128)), Buffer(S8, (3, 32, 128))], [Buffer(S32, (3, 64, 32)), Buffer(S32, (3, 64, 32))], batched=True,
+                lhs_contracting_dim=2, rhs_contracting_dim=2, emit_s32=True).instantiate()
+    b3 = [Buffer(S8, (3, 64, 128)), Buffer(S8, (3, 128, 32))]
+    for ops, res, kw, code in [
+        (b3, [Buffer(S32, (3, 64, 32))], {"lhs_contracting_dim": 2, "rhs_contracting_dim": 1}, 12),        # rank 3 without batch dims
+        (b3, [Buffer(S32, (2, 64, 32))], {"batched": True, "lhs_contracting_dim": 2, "rhs_contracting_dim": 1}, 3),
+        (b3, [Buffer(S32, (3, 64, 32))], {"batched": True, "lhs_contracting_dim": 0, "rhs_contracting_dim": 1}, 3),   # contracting the batch dimension
+        (b3, [Buffer(S32, (3, 64, 32)), Buffer(S32, (64, 32))], {"batched": True, "lhs_contracting_dim": 2, "rhs_contracting_dim": 1, "emit_s32": True}, 3),
+        ([Buffer(S8, (64, 128)), Buffer(S8, (128, 32))], [Buffer(S32, (64, 32))], {"batched": True}, 3),   # batch dims on rank 2
+    ]:
+        with pytest.raises(XlaFfiError) as e:
+            Int8DotCall(ops, res, **kw).instantiate()
+        assert e.value.code == code, (kw, e.value)
     for ops, res, kw, code in [
         ([Buffer(S8, (64, 128)), Buffer(F8E4M3FN, (128, 32))], [Buffer(S32, (64, 32))], {}, 3),
         ([Buffer(S8, (64, 128)), Buffer(S8, (128, 32)), Buffer(F32, (64,)), Buffer(F32, (32,))], [Buffer(S32, (64, 32))], {}, 3),

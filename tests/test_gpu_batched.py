@@ -140,3 +140,31 @@ def test_batched_int8_through_the_plain_c_entry_point(cuda_device):
     for i in range(batch):
         assert np.array_equal(got[i], o.dot_s8(a8[i], b8[i])), f"batch {i}"
     assert device_status() == 0
+
+
+@pytest.mark.parametrize("rhs_contracting_dim", [1, 2])
+def test_batched_int8_through_the_ffi_call(cuda_device, rhs_contracting_dim):
+    """Rank-3 s8 operands through `b200$dot$s8` (lhs_batch_dims = rhs_batch_dims = {0}), with the s32 copy and the
+    dequantised bf16 result; the scale vectors are shared by the batches."""
+    from xla_b200 import cublas_lt_matmul_s8
+
+    batch, m, k, n = 4, 80, 192, 112
+    rng = np.random.default_rng(31)
+    a8 = rng.integers(-128, 128, (batch, m, k), dtype=np.int8)
+    b8 = rng.integers(-128, 128, (batch, k, n), dtype=np.int8)
+    rs = rng.uniform(0.001, 0.01, m).astype(np.float32)
+    cs = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    b_in = b8 if rhs_contracting_dim == 1 else np.ascontiguousarray(np.swapaxes(b8, 1, 2))
+    a, b = torch.from_numpy(a8).to(cuda_device), torch.from_numpy(b_in).to(cuda_device)
+    d, acc = cublas_lt_matmul_s8(a, b, rhs_contracting_dim=rhs_contracting_dim)
+    torch.cuda.synchronize()
+    want = np.stack([o.dot_s8(a8[i], b8[i]) for i in range(batch)])
+    assert acc is None and d.dtype == torch.int32 and np.array_equal(d.cpu().numpy(), want)
+    d, acc = cublas_lt_matmul_s8(a, b, rhs_contracting_dim=rhs_contracting_dim, emit_s32=True,
+                                 a_row_scale=torch.from_numpy(rs).to(cuda_device), b_col_scale=torch.from_numpy(cs).to(cuda_device))
+    torch.cuda.synchronize()
+    assert np.array_equal(acc.cpu().numpy(), want)
+    got_bits = d.view(torch.int16).cpu().numpy().view(np.uint16)
+    for i in range(batch):
+        assert np.array_equal(got_bits[i], o.dequant_s32_to_bf16(want[i], rs, cs)), f"batch {i}"
+    assert device_status() == 0

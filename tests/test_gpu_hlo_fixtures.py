@@ -249,6 +249,18 @@ def test_tiny_int8_module(cuda_device):
     assert np.array_equal(got.cpu().numpy(), a.astype(np.int32) @ b.astype(np.int32))     # bit-exact
 
 
+def test_batched_int8_module(cuda_device):
+    text = load("batched_int8")
+    rng = np.random.default_rng(24)
+    a = rng.integers(-128, 128, (3, 40, 64), dtype=np.int8)
+    b = rng.integers(-128, 128, (3, 64, 24), dtype=np.int8)
+    got, stats = hlo_runner.run_hlo_module(text, [torch.from_numpy(a).to(cuda_device), torch.from_numpy(b).to(cuda_device)], return_stats=True)
+    torch.cuda.synchronize()
+    assert stats["custom_calls"] == 1 and tuple(got.shape) == (3, 40, 24)
+    assert np.array_equal(got.cpu().numpy(), hlo_eval.evaluate(text, [a, b]))          # bit-exact
+    assert np.array_equal(got.cpu().numpy(), np.stack([o.dot_s8(a[i], b[i]) for i in range(3)]))
+
+
 def test_bitcast_operand_module(cuda_device):
     text = load("bitcast_operand")
     rng = np.random.default_rng(21)

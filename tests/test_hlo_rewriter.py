@@ -278,6 +278,22 @@ def test_tiny_int8_dot_is_padded_and_sliced():
     assert np.array_equal(hlo_eval.evaluate(text, [a, b]), a.astype(np.int32) @ b.astype(np.int32))
 
 
+def test_batched_int8_dot_keeps_its_batch_dimension():
+    """s8 x s8 -> s32 is in the type table for batched dots as for plain ones (gemm_rewriter.cc:2425-2677 does not look
+    at the rank); the call carries the same batch attributes as the FP8 call."""
+    text = load("batched_int8")
+    hlo, plan = hlo_runner.rewrite(text)
+    (c,) = plan["calls"]
+    assert c["target"] == "b200$dot$s8" and (c["batch"], c["m"], c["n"], c["k"]) == (3, 40, 24, 64)
+    assert c["attrs"]["lhs_batch_dims"] == [0] and c["attrs"]["rhs_batch_dims"] == [0]
+    assert (c["attrs"]["lhs_contracting_dim"], c["attrs"]["rhs_contracting_dim"]) == (2, 1)
+    assert [s["dims"] for s in c["operands"]] == [[3, 48, 64], [3, 64, 32]] and "slice={[0:3], [0:40], [0:24]}" in hlo
+    rng = np.random.default_rng(23)
+    a = rng.integers(-127, 128, (3, 40, 64), dtype=np.int8)
+    b = rng.integers(-127, 128, (3, 64, 24), dtype=np.int8)
+    assert np.array_equal(hlo_eval.evaluate(text, [a, b]), np.matmul(a.astype(np.int32), b.astype(np.int32)))
+
+
 def test_bitcast_between_dequantisation_and_dot():
     """ScaledABUnscaledDBitcastF8 (gemm_rewriter_fp8_test.cc:579-612)."""
     text = load("bitcast_operand")
@@ -366,7 +382,7 @@ FIXTURES = ["c0_scaled_dot_f8", "c1_fp8_linear_gelu_amax", "c2_decode_m64", "c3_
             "c4_row_parallel_rank_of_2", "scaled_ab_divide_bias_relu_e5m2", "unscaled_matrix_bias_f32",
             "batched_scaled_ab_f32", "scaled_ab_alpha_f32", "unscaled_ab_scaled_f32_d", "bare_fp8_dot",
             "matrix_bias_scaled_d_amax", "relu_amax_e5m2_out", "precision_1600x3200x1600", "int8_12x4x8", "bitcast_operand",
-            "rank3_vector_bias", "two_layer_mlp"]
+            "rank3_vector_bias", "two_layer_mlp", "batched_int8", "block_scaled_dot_mx"]
 
 
 @pytest.mark.parametrize("name", FIXTURES)
@@ -380,7 +396,7 @@ def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
     assert plan["rewritten"], plan
     comps, entry = hlo_runner.parse_module(hlo)
     shapes = {i["name"]: i["shape"] for i in comps[entry]}
-    code = {"pred": 1, "s8": 2, "s32": 4, "f16": 10, "f32": 11, "bf16": 16, "f8e5m2": 19, "f8e4m3fn": 20}
+    code = {"pred": 1, "s8": 2, "s32": 4, "f16": 10, "f32": 11, "bf16": 16, "f8e5m2": 19, "f8e4m3fn": 20, "f8e8m0fnu": 33}
     n = 0
     for ins in comps[entry]:
         if ins["opcode"] != "custom-call":

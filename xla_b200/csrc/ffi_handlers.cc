@@ -73,6 +73,18 @@ struct DecodedF8 {
   B200SD_ScaledDotF8 args;
 };
 
+// GemmBackendConfig.lhs_stride / rhs_stride (backend_configs.proto:121-122): the reference's rewriter always writes the
+// dense extent of one batch entry, rows * cols (gemm_rewriter.cc:705-721).  Accepted when they say exactly that;
+// batches that are not packed back to back are not implemented.
+ffi::Error CheckDenseStrides(const ffi::Dictionary& attrs, const ffi::AnyBuffer& lhs, const ffi::AnyBuffer& rhs, size_t bo) {
+  const auto ls = GetInt(attrs, "lhs_stride"), rs = GetInt(attrs, "rhs_stride");
+  if (ls.has_value() && *ls != lhs.dimensions()[bo] * lhs.dimensions()[bo + 1])
+    return MakeError(12, "lhs_stride must be the dense extent of one batch entry of a (rows * cols)");
+  if (rs.has_value() && *rs != rhs.dimensions()[bo] * rhs.dimensions()[bo + 1])
+    return MakeError(12, "rhs_stride must be the dense extent of one batch entry of b (rows * cols)");
+  return ffi::Error::Success();
+}
+
 // Decodes and checks a scaled-dot call frame.  Works with null data pointers (instantiate stage).
 ffi::Error DecodeF8(ffi::RemainingArgs operands, ffi::RemainingRets results, const ffi::Dictionary& attrs,
                     B200SD_ScaledDotF8* out) {
@@ -131,6 +143,7 @@ ffi::Error DecodeF8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   a.batch_count = rank == 3 ? static_cast<int32_t>(lhs->dimensions()[0]) : 1;
   if (rank == 3 && (rhs->dimensions()[0] != lhs->dimensions()[0] || (*d)->dimensions()[0] != lhs->dimensions()[0]))
     return MakeError(3, "batch dimensions of a, b and the result differ");
+  if (ffi::Error e = CheckDenseStrides(attrs, *lhs, *rhs, static_cast<size_t>(bo)); e.failure()) return e;
   a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(bo + 1) - bo);
   a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(bo) - bo);
   if (a.lhs_contracting_dim != 0 && a.lhs_contracting_dim != 1) return MakeError(3, "lhs_contracting_dim must be one of the two matrix dimensions");
@@ -203,8 +216,6 @@ ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
                     B200SD_DotS8* out) {
   B200SD_DotS8 a{};
   a.struct_size = sizeof(a);
-  a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(1));
-  a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(0));
   a.kernel = static_cast<int32_t>(GetInt(attrs, "selected_config").value_or(B200SD_KERNEL_AUTO));
   const bool emit_s32 = GetBool(attrs, "emit_s32", false);
   if (GetFloat(attrs, "alpha_real").value_or(1.0) != 1.0 || GetFloat(attrs, "beta").value_or(0.0) != 0.0)
@@ -222,14 +233,33 @@ ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   if (!d.has_value()) return d.error();
   if (lhs->element_type() != ffi::DataType::S8 || rhs->element_type() != ffi::DataType::S8)
     return MakeError(3, "operands must be S8");
-  if (lhs->dimensions().size() != 2 || rhs->dimensions().size() != 2 || (*d)->dimensions().size() != 2)
-    return MakeError(12, "only rank-2 operands are implemented");
-  if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return MakeError(3, "contracting dimensions must be 0 or 1");
-  a.k = lhs->dimensions()[a.lhs_contracting_dim];
-  a.m = lhs->dimensions()[1 - a.lhs_contracting_dim];
-  a.n = rhs->dimensions()[1 - a.rhs_contracting_dim];
-  if (rhs->dimensions()[a.rhs_contracting_dim] != a.k) return MakeError(3, "contracting dimensions of a and b differ");
-  if ((*d)->dimensions()[0] != a.m || (*d)->dimensions()[1] != a.n) return MakeError(3, "result shape is not [m, n]");
+  // Rank 2, or rank 3 with one leading batch dimension on a, b, D and the s32 copy (lhs_batch_dims = rhs_batch_dims
+  // = {0}), exactly as for the FP8 call; contracting dimensions index the operand as it is.
+  const size_t rank = lhs->dimensions().size();
+  if ((rank != 2 && rank != 3) || rhs->dimensions().size() != rank || (*d)->dimensions().size() != rank)
+    return MakeError(12, "operands and result must all have rank 2, or rank 3 with one leading batch dimension");
+  const int64_t bo = rank == 3 ? 1 : 0;
+  {
+    auto lb = GetIntArray(attrs, "lhs_batch_dims"), rb = GetIntArray(attrs, "rhs_batch_dims");
+    const bool want = rank == 3;
+    auto ok = [&](const std::optional<std::vector<int64_t>>& v) {
+      if (!v.has_value()) return !want;
+      return want ? (v->size() == 1 && (*v)[0] == 0) : v->empty();
+    };
+    if (!ok(lb) || !ok(rb)) return MakeError(want ? 12 : 3, "lhs_batch_dims and rhs_batch_dims must be {0} for rank-3 operands and empty for rank-2");
+  }
+  a.batch_count = rank == 3 ? lhs->dimensions()[0] : 1;
+  if (rank == 3 && (rhs->dimensions()[0] != lhs->dimensions()[0] || (*d)->dimensions()[0] != lhs->dimensions()[0]))
+    return MakeError(3, "batch dimensions of a, b and the result differ");
+  if (ffi::Error e = CheckDenseStrides(attrs, *lhs, *rhs, static_cast<size_t>(bo)); e.failure()) return e;
+  a.lhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "lhs_contracting_dim").value_or(bo + 1) - bo);
+  a.rhs_contracting_dim = static_cast<int32_t>(GetInt(attrs, "rhs_contracting_dim").value_or(bo) - bo);
+  if ((a.lhs_contracting_dim | 1) != 1 || (a.rhs_contracting_dim | 1) != 1) return MakeError(3, "contracting dimensions must be the two matrix dimensions");
+  a.k = lhs->dimensions()[bo + a.lhs_contracting_dim];
+  a.m = lhs->dimensions()[bo + 1 - a.lhs_contracting_dim];
+  a.n = rhs->dimensions()[bo + 1 - a.rhs_contracting_dim];
+  if (rhs->dimensions()[bo + a.rhs_contracting_dim] != a.k) return MakeError(3, "contracting dimensions of a and b differ");
+  if ((*d)->dimensions()[bo] != a.m || (*d)->dimensions()[bo + 1] != a.n) return MakeError(3, "result shape is not [m, n]");
   a.a = lhs->untyped_data();
   a.b = rhs->untyped_data();
   a.d = (*d)->untyped_data();
@@ -250,9 +280,10 @@ ffi::Error DecodeS8(ffi::RemainingArgs operands, ffi::RemainingRets results, con
   if (emit_s32) {
     auto acc = results.get<ffi::AnyBuffer>(1);
     if (!acc.has_value()) return acc.error();
-    if ((*acc)->element_type() != ffi::DataType::S32 || (*acc)->dimensions().size() != 2 ||
-        (*acc)->dimensions()[0] != a.m || (*acc)->dimensions()[1] != a.n)
-      return MakeError(3, "the emit_s32 result must be s32[m, n]");
+    if ((*acc)->element_type() != ffi::DataType::S32 || (*acc)->dimensions().size() != rank ||
+        (*acc)->dimensions()[bo] != a.m || (*acc)->dimensions()[bo + 1] != a.n ||
+        (rank == 3 && (*acc)->dimensions()[0] != lhs->dimensions()[0]))
+      return MakeError(3, "the emit_s32 result must be s32[(batch,) m, n]");
     a.acc_out = static_cast<int32_t*>((*acc)->untyped_data());
   }
   if (results.size() == want_results + 1) {       // trailing s8[workspace], as GemmWorkspaceRewriteVisitor appends

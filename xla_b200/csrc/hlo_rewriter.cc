@@ -1329,6 +1329,13 @@ std::string Rewriter::EmitHlo(const Module& m) const {
       for (size_t k = 0; k < i->operands.size(); ++k) o << (k ? ", " : "") << i->operands[k]->name;
       o << "), custom_call_target=\"" << (g.mx ? "b200$block_scaled_dot$mx" : g.f8 ? "b200$scaled_dot$f8" : "b200$dot$s8")
         << "\", api_version=API_VERSION_TYPED_FFI, backend_config={";
+      // lhs_stride / rhs_stride as the reference's rewriter writes them: the dense extent of one batch entry of each
+      // operand as passed (gemm_rewriter.cc:705-721).
+      auto entry_extent = [](const Instr* x) {
+        const auto& d = x->shape.dims;
+        return d.size() >= 2 ? d[d.size() - 2] * d[d.size() - 1] : int64_t(0);
+      };
+      const int64_t lhs_stride = entry_extent(i->operands[0]), rhs_stride = entry_extent(i->operands[1]);
       if (g.mx) {
         o << "alpha_real = " << F64(g.alpha) << " : f64";
         if (g.explicit_block) o << ", block_size = " << g.explicit_block << " : i64";
@@ -1337,10 +1344,13 @@ std::string Rewriter::EmitHlo(const Module& m) const {
         o << "alpha_real = " << F64(g.alpha) << " : f64, beta = " << F64(g.beta) << " : f64, epilogue = " << g.epilogue
           << " : i32, lhs_contracting_dim = " << g.lhs_contracting << " : i64, rhs_contracting_dim = " << g.rhs_contracting
           << " : i64, damax_output = " << (g.damax ? "true" : "false")
-          << (g.batched ? ", lhs_batch_dims = array<i64: 0>, rhs_batch_dims = array<i64: 0>" : "") << ", selected_config = 0 : i64}\n";
+          << (g.batched ? ", lhs_batch_dims = array<i64: 0>, rhs_batch_dims = array<i64: 0>" : "") << ", lhs_stride = " << lhs_stride
+          << " : i64, rhs_stride = " << rhs_stride << " : i64, selected_config = 0 : i64}\n";
       } else {
         o << "lhs_contracting_dim = " << g.lhs_contracting << " : i64, rhs_contracting_dim = " << g.rhs_contracting
-          << " : i64, emit_s32 = " << (g.emit_s32 ? "true" : "false") << "}\n";
+          << " : i64, emit_s32 = " << (g.emit_s32 ? "true" : "false")
+          << (g.batched ? ", lhs_batch_dims = array<i64: 0>, rhs_batch_dims = array<i64: 0>" : "") << ", lhs_stride = " << lhs_stride
+          << " : i64, rhs_stride = " << rhs_stride << " : i64}\n";
       }
       o << lead << i->name << " = " << i->shape.ToString() << " get-tuple-element(" << i->name << ".call), index=0\n";
       return;
@@ -1436,6 +1446,12 @@ std::string Rewriter::EmitJson() const {
     if (c.damax) j << ", {\"role\": \"amax\", \"dtype\": 11, \"dims\": []}";
     if (c.emit_s32) j << ", {\"role\": \"acc\", \"dtype\": 4, \"dims\": " << Dims(g->shape) << "}";
     j << ", {\"role\": \"workspace\", \"dtype\": 2, \"dims\": [" << kWorkspaceBytes << "]}], \"attrs\": {";
+    auto entry_extent = [](const Instr* x) {
+      const auto& d = x->shape.dims;
+      return d.size() >= 2 ? d[d.size() - 2] * d[d.size() - 1] : int64_t(0);
+    };
+    std::ostringstream strides;
+    strides << ", \"lhs_stride\": " << entry_extent(g->operands[0]) << ", \"rhs_stride\": " << entry_extent(g->operands[1]);
     if (c.mx) {
       j << "\"alpha_real\": " << F64(c.alpha);
       if (c.explicit_block) j << ", \"block_size\": " << c.explicit_block;
@@ -1443,10 +1459,10 @@ std::string Rewriter::EmitJson() const {
       j << "\"alpha_real\": " << F64(c.alpha) << ", \"beta\": " << F64(c.beta) << ", \"epilogue\": " << c.epilogue
         << ", \"lhs_contracting_dim\": " << c.lhs_contracting << ", \"rhs_contracting_dim\": " << c.rhs_contracting
         << ", \"damax_output\": " << (c.damax ? "true" : "false")
-        << (c.batched ? ", \"lhs_batch_dims\": [0], \"rhs_batch_dims\": [0]" : "");
+        << (c.batched ? ", \"lhs_batch_dims\": [0], \"rhs_batch_dims\": [0]" : "") << strides.str();
     } else {
       j << "\"lhs_contracting_dim\": " << c.lhs_contracting << ", \"rhs_contracting_dim\": " << c.rhs_contracting << ", \"emit_s32\": "
-        << (c.emit_s32 ? "true" : "false");
+        << (c.emit_s32 ? "true" : "false") << (c.batched ? ", \"lhs_batch_dims\": [0], \"rhs_batch_dims\": [0]" : "") << strides.str();
     }
     j << "}}";
     if (n_calls == 0) first = j.str();

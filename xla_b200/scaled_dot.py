@@ -65,6 +65,8 @@ class GemmBackendConfig:
     rhs_batch_dimensions: Sequence[int] = ()
     epilogue: Epilogue = Epilogue.DEFAULT
     damax_output: bool = False
+    lhs_stride: Optional[int] = None      # elements between batch entries; only the dense rows * cols the reference writes is accepted
+    rhs_stride: Optional[int] = None
     selected_algorithm: int = 0  # 0 automatic; 1 dense; 2 split-K; 3 dense single-CTA; 4 dense CTA-pair
 
 
@@ -201,6 +203,10 @@ def _config_attrs(cfg: GemmBackendConfig) -> dict:
     batch = {}
     if tuple(cfg.lhs_batch_dimensions) or tuple(cfg.rhs_batch_dimensions):
         batch = {"lhs_batch_dims": list(cfg.lhs_batch_dimensions), "rhs_batch_dims": list(cfg.rhs_batch_dimensions)}
+    if cfg.lhs_stride is not None:
+        batch["lhs_stride"] = int(cfg.lhs_stride)
+    if cfg.rhs_stride is not None:
+        batch["rhs_stride"] = int(cfg.rhs_stride)
     return {
         **batch,
         "alpha_real": float(cfg.alpha_real),
@@ -228,16 +234,20 @@ class ScaledDotCall(FfiCall):
 
 class Int8DotCall(FfiCall):
     """A `b200$dot$s8` call site: operands a, b, [a_row_scale, b_col_scale]; results D, [acc s32],
-    [workspace]."""
+    [workspace].  Rank-3 operands carry one leading batch dimension (`batched=True` sets
+    lhs_batch_dims = rhs_batch_dims = {0}; the contracting dimensions then index the rank-3 operand)."""
 
     def __init__(self, operands: Sequence, results: Sequence, *, lhs_contracting_dim=1, rhs_contracting_dim=0,
-                 emit_s32=False, selected_algorithm=0):
-        super().__init__(TARGET_S8, operands, results, {
+                 emit_s32=False, selected_algorithm=0, batched=False):
+        attrs = {
             "lhs_contracting_dim": int(lhs_contracting_dim),
             "rhs_contracting_dim": int(rhs_contracting_dim),
             "emit_s32": bool(emit_s32),
             "selected_config": int(selected_algorithm),
-        })
+        }
+        if batched:
+            attrs.update({"lhs_batch_dims": [0], "rhs_batch_dims": [0]})
+        super().__init__(TARGET_S8, operands, results, attrs)
 
 
 class BlockScaledDotCall(FfiCall):
@@ -296,24 +306,29 @@ def cublas_lt_matmul_f8(a, b, a_scale, b_scale, *, c=None, bias=None, d_scale=No
 
 
 def cublas_lt_matmul_s8(a, b, *, a_row_scale=None, b_col_scale=None, out_dtype=None, emit_s32=False,
-                        lhs_contracting_dim=1, rhs_contracting_dim=0, selected_algorithm=0, workspace=None):
+                        lhs_contracting_dim=None, rhs_contracting_dim=None, selected_algorithm=0, workspace=None):
     """s8 x s8 dot; returns (D, acc or None).  `workspace` (an int8 tensor) becomes the trailing
-    scratch result of the call site, as in XLA."""
+    scratch result of the call site, as in XLA.  Rank-3 operands are a batch of dots (leading
+    dimension); the contracting dimensions index the operands as given (default: the last of a, the
+    first matrix dimension of b)."""
     torch = _torch()
-    m, n = a.shape[1 - lhs_contracting_dim], b.shape[1 - rhs_contracting_dim]
+    bo = a.dim() - 2
+    lc = bo + 1 if lhs_contracting_dim is None else lhs_contracting_dim
+    rc = bo if rhs_contracting_dim is None else rhs_contracting_dim
+    m, n = a.shape[2 * bo + 1 - lc], b.shape[2 * bo + 1 - rc]
+    lead = tuple(a.shape[:bo])
     out_dtype = out_dtype or (torch.int32 if a_row_scale is None else torch.bfloat16)
-    d = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    d = torch.empty(lead + (m, n), dtype=out_dtype, device=a.device)
     operands = [a, b] + ([a_row_scale, b_col_scale] if a_row_scale is not None else [])
     results = [d]
     acc = None
     if emit_s32:
-        acc = torch.empty((m, n), dtype=torch.int32, device=a.device)
+        acc = torch.empty(lead + (m, n), dtype=torch.int32, device=a.device)
         results.append(acc)
     if workspace is not None:
         results.append(workspace)
-    call = Int8DotCall(operands, results, lhs_contracting_dim=lhs_contracting_dim,
-                       rhs_contracting_dim=rhs_contracting_dim, emit_s32=emit_s32,
-                       selected_algorithm=selected_algorithm)
+    call = Int8DotCall(operands, results, lhs_contracting_dim=lc, rhs_contracting_dim=rc, emit_s32=emit_s32,
+                       selected_algorithm=selected_algorithm, batched=bo == 1)
     stream, dev = _current_stream_and_device(a)
     call.run(stream, dev)
     call.close()
