@@ -171,6 +171,39 @@ def _dot(lhs, rhs, lc, rc, lb, rb):
     return o.dot_f32(lhs, rhs, lc, rc)
 
 
+def _scaled_dot(t, lhs, rhs, lhs_scale, rhs_scale, lc, rc, lb, rb):
+    """The `scaled-dot` instruction as the interpreter defines it (HandleScaledDot,
+    hlo_evaluator_typed_visitor.h:1783-1990).  All four operands are first converted to the result type; a scale of
+    rank 0 counts as 1; a scale entry covers dim / scale_dim consecutive indices in every dimension; each result
+    element is the sum over k, in order, of ((lhs * lhs_scale) * rhs) * rhs_scale in f32.  `lhs` .. `rhs_scale` are
+    (type, value) pairs; returns f32 values [batch..., lhs free, rhs free]."""
+    def prepared(v, sc):
+        x = _to_f32(t, _from_f32(t, _to_f32(*v)))
+        if np.ndim(sc[1]) == 0:
+            return x, np.ones_like(x)
+        y = _to_f32(t, _from_f32(t, _to_f32(*sc)))
+        assert y.ndim == x.ndim and all(d % e == 0 for d, e in zip(x.shape, y.shape)), (x.shape, y.shape)
+        for axis, (d, e) in enumerate(zip(x.shape, y.shape)):
+            if d != e:
+                y = np.repeat(y, d // e, axis=axis)
+        return x, y
+
+    (a, sa), (b, sb) = prepared(lhs, lhs_scale), prepared(rhs, rhs_scale)
+    nb = len(lb)
+    lfree = [d for d in range(a.ndim) if d not in lb and d != lc]
+    rfree = [d for d in range(b.ndim) if d not in rb and d != rc]
+    lperm, rperm = list(lb) + lfree + [lc], list(rb) + rfree + [rc]
+    a, sa, b, sb = a.transpose(lperm), sa.transpose(lperm), b.transpose(rperm), sb.transpose(rperm)
+    bshape, mshape, nshape, k = a.shape[:nb], a.shape[nb:-1], b.shape[nb:-1], a.shape[-1]
+    a, sa = a.reshape(bshape + (-1, 1, k)), sa.reshape(bshape + (-1, 1, k))
+    b, sb = b.reshape(bshape + (1, -1, k)), sb.reshape(bshape + (1, -1, k))
+    acc = np.zeros(bshape + (a.shape[-3], b.shape[-2]), np.float32)
+    with np.errstate(over="ignore", invalid="ignore", under="ignore"):
+        for i in range(k):
+            acc += ((a[..., i] * sa[..., i]) * b[..., i]) * sb[..., i]
+    return acc.reshape(bshape + mshape + nshape)
+
+
 def evaluate(text, params):
     """Runs the ENTRY computation on `params` (list, in parameter order, in the representation
     described in the module docstring).  Returns the root value, or a tuple of values."""
@@ -310,6 +343,11 @@ def evaluate(text, params):
                 val = (t, _dot(np.asarray(lv, np.float64).astype(np.float32), np.asarray(rv, np.float64).astype(np.float32), lc, rc, lb, rb).astype(_INT[t]))
             else:
                 val = (t, _from_f32(t, _dot(_to_f32(lt, lv), _to_f32(rt, rv), lc, rc, lb, rb)))
+        elif op == "scaled-dot":
+            lc = _attr_dims(attrs, "lhs_contracting_dims")[0]
+            rc = _attr_dims(attrs, "rhs_contracting_dims")[0]
+            lb, rb = _attr_dims(attrs, "lhs_batch_dims") or (), _attr_dims(attrs, "rhs_batch_dims") or ()
+            val = (t, _from_f32(t, _scaled_dot(t, a[0], a[1], a[2], a[3], lc, rc, lb, rb)))
         elif op == "custom-call" and '"__op$block_scaled_dot"' in attrs:
             # block_scaling_rewriter.h:30-77; evaluated as the expansion of block_scaling_rewriter.cc:194-262
             (lt, lv), (rt, rv), (st, sv), (ut, uv) = a[:4]

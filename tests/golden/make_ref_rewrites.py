@@ -36,6 +36,11 @@ A second file, tests/golden/ref_block_scaled.json, holds the `__op$block_scaled_
 each with `library`: whether the reference, given a library that supports block-scaled dots, hands this module to it
 (the test builds the pass with kCudnnSupportsBlockScaledDot / kCudnnVersion and its CHECK lines name
 `__cudnn$blockScaledDot` or a custom call) or expands it into dequantize + dot.
+The same file's `scaled_dot` list holds the modules built on the `scaled-dot` instruction:
+  * the CudnnFusion* tests of block_scaling_rewriter_test.cc (`supported`: what the test expects of
+    CudnnScaledDotHelper::IsSupported) and
+  * xla/backends/gpu/autotuner/mx_scaled_dot_execution_test.cc, whose modules the test expects to end up as
+    `__cublas$lt$matmul$mx` (or a Triton fusion) and compares with the expansion under an ErrorSpec (`mx_call`: true).
 """
 import json
 import os
@@ -320,14 +325,44 @@ def block_scaled_cases():
     return cases
 
 
+MX_EXECUTION_TEST = "xla/backends/gpu/autotuner/mx_scaled_dot_execution_test.cc"
+ERROR_SPEC = r"ErrorSpec\(\s*/\*aabs=\*/\s*([0-9.e+-]+)\s*,\s*/\*arel=\*/\s*([0-9.e+-]+)\s*\)"
+
+
+def scaled_dot_cases():
+    cases = []
+    src = open(os.path.join(ROOT, BLOCK_TESTS[0])).read()
+    for name, line, body in split_tests(src, r"BlockScalingRewriter\w*Test"):
+        modules = [m for m in raw_strings(body) if "scaled-dot(" in m]
+        verdict = re.search(r"EXPECT_(TRUE|FALSE)\(\s*CudnnScaledDotHelper::IsSupported", body)
+        if modules and verdict:
+            cases.append({"name": name, "source": f"{BLOCK_TESTS[0]}:{line}", "hlo": modules[0].strip() + "\n",
+                          "supported": verdict.group(1) == "TRUE", "mx_call": None, "error_spec": None})
+    # Modules held in named constants, each used by one TEST_F through RunMxCorrectnessTest(constant, ErrorSpec(..)).
+    src = open(os.path.join(ROOT, MX_EXECUTION_TEST)).read()
+    constants = {m.group(1): (m.group(2), src[:m.start()].count("\n") + 1)
+                 for m in re.finditer(r'constexpr absl::string_view (k\w+) =\s*R"\((.*?)\)";', src, flags=re.S)}
+    for name, line, body in split_tests(src, r"MxScaledDotExecutionTest"):
+        use = re.search(r"RunMxCorrectnessTest\(\s*(k\w+)\s*,\s*" + ERROR_SPEC, body)
+        if not use or use.group(1) not in constants:
+            continue
+        text, at = constants[use.group(1)]
+        cases.append({"name": name, "source": f"{MX_EXECUTION_TEST}:{at}", "hlo": text.strip() + "\n", "supported": None,
+                      "mx_call": True, "error_spec": [float(use.group(2)), float(use.group(3))]})
+    return cases
+
+
 def main():
     blocks = block_scaled_cases()
+    scaled = scaled_dot_cases()
     with open(os.path.join(HERE, "ref_block_scaled.json"), "w") as f:
         json.dump({"sources": list(BLOCK_TESTS),
+                   "sources_scaled_dot": [BLOCK_TESTS[0], MX_EXECUTION_TEST],
                    "note": "`__op$block_scaled_dot` modules of the reference's BlockScalingRewriter tests, extracted as text; "
                            "`library` = handed to a block-scaled library kernel rather than expanded, see the generating script",
-                   "cases": blocks}, f, indent=1)
-    print(f"{len(blocks)} block-scaled cases, {sum(c['library'] for c in blocks)} taken by the library path")
+                   "cases": blocks, "scaled_dot": scaled}, f, indent=1)
+    print(f"{len(blocks)} block-scaled cases, {sum(c['library'] for c in blocks)} taken by the library path; "
+          f"{len(scaled)} scaled-dot cases")
     fp8 = cases_of(FP8_TEST, r"ParameterizedFp8GemmRewriteTest")
     int8 = cases_of(GEMM_TEST, r"\w*GemmRewriteTest\w*", name_filter=r"^Int8Gemm")
     out = {

@@ -21,8 +21,21 @@ import ref_cases
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 with open(os.path.join(HERE, "golden", "ref_block_scaled.json")) as f:
-    CASES = json.load(f)["cases"]
+    _FIXTURE = json.load(f)
+CASES = _FIXTURE["cases"]
+SCALED_DOT = _FIXTURE["scaled_dot"]          # modules built on the `scaled-dot` instruction
 BY_NAME = {c["name"]: c for c in CASES}
+# What the rewriter-lite makes of each `scaled-dot` module, with the reason where it differs from a cuDNN verdict.
+SCALED_DOT_TAKEN = {
+    "CudnnFusionSupportedE4M3": True,
+    "CudnnFusionUnsupportedE5M2": True,          # a cuDNN restriction; tcgen05 kind::mxf8f6f4 multiplies e5m2 x e5m2 (tests/test_gpu_mx.py)
+    "CudnnFusionUnsupportedDimensions": False,   # rhs contracting dimension is the major one
+    "CudnnFusionUnupportedLayout": False,        # column-major lhs
+    "CudnnFusionUnsupportedInputs": True,        # a rule about cuDNN fusion inputs (a broadcast); a custom call takes any value
+    "MxFp8Correctness": True, "MxFp8BatchedCorrectness": True, "MxFp8MixedTypesBatchedCorrectness": True,
+    "MxFp8ReshapedOperandsCorrectness": True,
+    "MxFp4Correctness": False, "MxFp4BatchedCorrectness": False, "MxFp4Fp8MixedBatchedCorrectness": False,   # 4-bit values: not implemented
+}
 
 
 def is_mx_fp8(case) -> bool:
@@ -105,3 +118,59 @@ def test_padded_scales_need_the_explicit_block_size():
     assert not plan["rewritten"] and "block size" in plan["not_rewritten"][0]["reason"]
     _, plan = hlo_runner.rewrite(case["hlo"].replace("block_size:32", "block_size:16"))
     assert not plan["rewritten"] and "block size" in plan["not_rewritten"][0]["reason"]
+
+
+@pytest.mark.parametrize("case", SCALED_DOT, ids=[c["name"] for c in SCALED_DOT])
+def test_scaled_dot_instruction_becomes_the_mx_call(case):
+    """The reference turns a `scaled-dot` into `__cublas$lt$matmul$mx` when a BLAS library wins its autotuning
+    (autotuner/hipblaslt.cc:430-505; mx_scaled_dot_execution_test.cc expects that call or a Triton fusion for every
+    module listed with `mx_call`).  The rewriter-lite takes the MXFP8 ones in the form that call has."""
+    hlo, plan = hlo_runner.rewrite(case["hlo"])
+    taken = SCALED_DOT_TAKEN[case["name"]]
+    assert plan["rewritten"] == taken
+    if case["mx_call"] and "f4e2m1fn" not in case["hlo"]:
+        assert taken                       # every FP8 module the reference runs through the MX call is taken
+    if case["supported"]:
+        assert taken                       # and everything cuDNN's helper accepts
+    if taken:
+        (c,) = plan["calls"]
+        assert c["target"] == "b200$block_scaled_dot$mx" and "scaled-dot(" not in hlo
+        assert [x["role"] for x in c["operands"]] == ["a", "b", "a_scale", "b_scale"]
+    else:
+        assert "scaled-dot" in plan["not_rewritten"][0]["reason"]
+
+
+def test_scaled_dot_interpreter_against_the_block_scaled_oracle():
+    """`scaled-dot` evaluated term by term as HandleScaledDot does (hlo_evaluator_typed_visitor.h:1783-1990) against the
+    oracle's dequantize-then-dot: the same products (exact in f32), summed in a different order."""
+    for name, kind_b in (("MxFp8Correctness", "e4m3fn"), ("MxFp8MixedTypesBatchedCorrectness", "e5m2"),
+                         ("MxFp8ReshapedOperandsCorrectness", "e4m3fn")):
+        case = next(c for c in SCALED_DOT if c["name"] == name)
+        a, b, sa, sb = ref_cases.make_inputs(case["hlo"], 9)
+        got = hlo_eval.evaluate(case["hlo"], [a, b, sa, sb])
+        a2, b2 = a.reshape(sa.shape[:-1] + (-1,)), b.reshape(sb.shape[:-1] + (-1,))
+        want = o.block_scaled_dot(a2, b2, sa, sb, b_kind=kind_b)
+        absdot = np.matmul(np.abs(o.mx_dequantize(a2, sa)).astype(np.float64),
+                           np.swapaxes(np.abs(o.mx_dequantize(b2, sb, kind_b)).astype(np.float64), -1, -2))
+        assert got.shape == want.shape
+        assert (np.abs(got.astype(np.float64) - want) <= absdot * 2.0 ** -20).all()
+    # coarser scales (one per 32 rows x 256 columns, scaled_dot_rewriter_test.cc:57-67) and a scalar scale (= 1)
+    text = """HloModule m
+ENTRY main {
+  lhs = f8e4m3fn[64,512] parameter(0)
+  rhs = f8e4m3fn[32,512] parameter(1)
+  lhs_scale = f8e8m0fnu[2,2] parameter(2)
+  rhs_scale = f8e8m0fnu[] parameter(3)
+  ROOT d = f32[64,32] scaled-dot(lhs, rhs, lhs_scale, rhs_scale), lhs_contracting_dims={1}, rhs_contracting_dims={1}
+}
+"""
+    rng = np.random.default_rng(4)
+    a = o.fp8_encode(rng.uniform(-1, 1, (64, 512)).astype(np.float32))
+    b = o.fp8_encode(rng.uniform(-1, 1, (32, 512)).astype(np.float32))
+    sa = np.array([[126, 128], [127, 129]], np.uint8)
+    got = hlo_eval.evaluate(text, [a, b, sa, np.uint8(140)])
+    scale = np.repeat(np.repeat(o.e8m0_decode(sa), 32, axis=0), 256, axis=1)
+    want = (o.fp8_decode(a).astype(np.float64) * scale) @ o.fp8_decode(b).astype(np.float64).T
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-4)
+    _, plan = hlo_runner.rewrite(text)
+    assert not plan["rewritten"] and "scalar scale" in plan["not_rewritten"][0]["reason"]

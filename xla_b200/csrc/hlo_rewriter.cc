@@ -388,6 +388,7 @@ class Rewriter {
       else if (i->opcode == "maximum") HandleMaximum(i);
       else if (i->opcode == "convert") HandleConvert(i);
       else if (i->opcode == "custom-call" && i->attrs.find("\"__op$block_scaled_dot\"") != std::string::npos) HandleBlockScaledDot(i);
+      else if (i->opcode == "scaled-dot") HandleScaledDot(i);
     }
     for (Instr* g : calls_) {
       if (!IsLive(g) || g->gemm->mx) continue;
@@ -817,44 +818,76 @@ class Rewriter {
   // dimension major.  The reference either expands it into dequantize + dot (block_scaling_rewriter.cc:194-262)
   // or hands it to a library; with MX operands (FP8 values, one f8e8m0fnu scale per 32) it becomes this
   // library's block-scaled call, which takes the four operands as they are.  Everything else is left alone.
+  // `__op$block_scaled_dot` (block_scaling_rewriter.h:30-77): the contracting dimension is the minor one of both
+  // operands by definition of the call.
   void HandleBlockScaledDot(Instr* cc) {
     if (cc->operands.size() == 5) return Refuse(cc, "block-scaled dot with a global scale: not taken by the MX call (exactly four operands, thunk_emitter.cc:939-988)");
     if (cc->operands.size() != 4) return Refuse(cc, "block-scaled dot must have four operands");
+    // An explicit block size comes in the backend config (block_scaling_rewriter.cc:613-621); it is what allows scale
+    // arrays padded along k.  Extra scale rows are allowed either way (block_scaling_rewriter.cc:489-493).  The
+    // call takes the padded arrays as they are and reads the leading [rows, k / 32] corner.
+    int64_t explicit_block = 0;
+    const size_t p = cc->attrs.find("block_size");
+    if (p != std::string::npos) {
+      size_t q = p + 10;
+      while (q < cc->attrs.size() && !std::isdigit(static_cast<unsigned char>(cc->attrs[q]))) ++q;
+      explicit_block = std::strtoll(cc->attrs.c_str() + q, nullptr, 10);
+      if (explicit_block != 32) return Refuse(cc, "block-scaled dot: the block size must be 32 (MX), got " + std::to_string(explicit_block));
+    }
+    TakeMxDot(cc, "block-scaled dot", explicit_block);
+  }
+
+  // The `scaled-dot` instruction (lhs, rhs, lhs_scale, rhs_scale + dot dimension numbers), which the reference turns
+  // into `__cublas$lt$matmul$mx` when a BLAS library wins its autotuning (autotuner/hipblaslt.cc:430-505; run against
+  // the expansion in autotuner/mx_scaled_dot_execution_test.cc).  Taken in the form that call has: one contracting
+  // dimension, the minor one of both operands, and at most one leading batch dimension.
+  void HandleScaledDot(Instr* sd) {
+    if (sd->operands.size() != 4) return Refuse(sd, "scaled-dot must have four operands");
+    const std::vector<int64_t> lc = AttrList(sd->attrs, "lhs_contracting_dims"), rc = AttrList(sd->attrs, "rhs_contracting_dims");
+    const std::vector<int64_t> lb = AttrList(sd->attrs, "lhs_batch_dims"), rb = AttrList(sd->attrs, "rhs_batch_dims");
+    const int64_t rank = int64_t(sd->operands[0]->shape.dims.size());
+    if (lc.size() != 1 || rc.size() != 1) return Refuse(sd, "scaled-dot: A and B must have one contracting dimension each");
+    if (int64_t(sd->operands[1]->shape.dims.size()) != rank) return Refuse(sd, "scaled-dot: operand ranks differ");
+    if (lc[0] != rank - 1 || rc[0] != rank - 1)
+      return Refuse(sd, "scaled-dot: the contracting dimension must be the minor one of both operands (the form of the MX call)");
+    const bool batch_ok = rank == 3 ? (lb == std::vector<int64_t>{0} && rb == std::vector<int64_t>{0}) : (lb.empty() && rb.empty());
+    if (!batch_ok) return Refuse(sd, "scaled-dot: batch dimensions must be {0} on rank-3 operands and absent on rank-2 ones");
+    for (int k = 2; k < 4; ++k)
+      if (sd->operands[k]->shape.dims.empty()) return Refuse(sd, "scaled-dot: a scalar scale means no scaling; not the MX form");
+    // The instruction's scales may be coarser in any dimension (one scale per dim / scale_dim indices,
+    // hlo_evaluator_typed_visitor.h:1831-1879); the MX form has one per row.
+    for (int k = 0; k < 2; ++k) {
+      const Shape& v = sd->operands[k]->shape;
+      const Shape& sc = sd->operands[k + 2]->shape;
+      if (int64_t(sc.dims.size()) != rank || sc.dims[rank - 2] != v.dims[rank - 2])
+        return Refuse(sd, "scaled-dot: the block size must be 32 along k and 1 along the rows (scales [rows, k / 32])");
+    }
+    TakeMxDot(sd, "scaled-dot", 0);
+  }
+
+  void TakeMxDot(Instr* cc, const std::string& what, int64_t explicit_block) {
     const Shape& a = cc->operands[0]->shape;
     const Shape& b = cc->operands[1]->shape;
     const Shape& sa = cc->operands[2]->shape;
     const Shape& sb = cc->operands[3]->shape;
     const Shape& d = cc->shape;
-    if (!IsF8(a.type) || !IsF8(b.type)) return Refuse(cc, "block-scaled dot: only f8e4m3fn / f8e5m2 values are implemented, got " + a.type + " and " + b.type);
-    if (sa.type != "f8e8m0fnu" || sb.type != "f8e8m0fnu") return Refuse(cc, "block-scaled dot: scales must be f8e8m0fnu (MX), got " + sa.type + " and " + sb.type);
-    if (!(d.type == "f32" || d.type == "bf16" || d.type == "f16")) return Refuse(cc, "block-scaled dot: result must be f32, bf16 or f16");
+    if (!IsF8(a.type) || !IsF8(b.type)) return Refuse(cc, what + ": only f8e4m3fn / f8e5m2 values are implemented, got " + a.type + " and " + b.type);
+    if (sa.type != "f8e8m0fnu" || sb.type != "f8e8m0fnu") return Refuse(cc, what + ": scales must be f8e8m0fnu (MX), got " + sa.type + " and " + sb.type);
+    if (!(d.type == "f32" || d.type == "bf16" || d.type == "f16")) return Refuse(cc, what + ": result must be f32, bf16 or f16");
     const size_t rank = a.dims.size();
     if ((rank != 2 && rank != 3) || b.dims.size() != rank || sa.dims.size() != rank || sb.dims.size() != rank || d.dims.size() != rank)
-      return Refuse(cc, "block-scaled dot: operands must have rank 2, or rank 3 with one leading batch dimension");
+      return Refuse(cc, what + ": operands must have rank 2, or rank 3 with one leading batch dimension");
     for (const Shape* sh : {&a, &b, &sa, &sb, &d})
-      if (!sh->IsDefaultLayout()) return Refuse(cc, "block-scaled dot: operands must be in the default (row-major) layout");
+      if (!sh->IsDefaultLayout()) return Refuse(cc, what + ": operands must be in the default (row-major) layout");
     const size_t o = rank - 2;
     const int64_t m = a.dims[o], k = a.dims[o + 1], n = b.dims[o];
-    if (b.dims[o + 1] != k) return Refuse(cc, "block-scaled dot: contracting dimensions differ");
-    // An explicit block size comes in the backend config (block_scaling_rewriter.cc:613-621); it is what allows scale
-    // arrays padded along k.  Extra scale rows are allowed either way (block_scaling_rewriter.cc:489-493).  The
-    // call takes the padded arrays as they are and reads the leading [rows, k / 32] corner.
-    int64_t explicit_block = 0;
-    {
-      const size_t p = cc->attrs.find("block_size");
-      if (p != std::string::npos) {
-        size_t q = p + 10;
-        while (q < cc->attrs.size() && !std::isdigit(static_cast<unsigned char>(cc->attrs[q]))) ++q;
-        explicit_block = std::strtoll(cc->attrs.c_str() + q, nullptr, 10);
-        if (explicit_block != 32) return Refuse(cc, "block-scaled dot: the block size must be 32 (MX), got " + std::to_string(explicit_block));
-      }
-    }
-    if (k % 32 != 0 || sa.dims[o] < m || sb.dims[o] < n) return Refuse(cc, "block-scaled dot: the block size must be 32 (scales [rows, k / 32])");
+    if (b.dims[o + 1] != k) return Refuse(cc, what + ": contracting dimensions differ");
+    if (k % 32 != 0 || sa.dims[o] < m || sb.dims[o] < n) return Refuse(cc, what + ": the block size must be 32 (scales [rows, k / 32])");
     if (explicit_block ? (sa.dims[o + 1] * 32 < k || sb.dims[o + 1] * 32 < k) : (sa.dims[o + 1] * 32 != k || sb.dims[o + 1] * 32 != k))
-      return Refuse(cc, "block-scaled dot: the block size must be 32 (scales [rows, k / 32])");
-    if (d.dims[o] != m || d.dims[o + 1] != n) return Refuse(cc, "block-scaled dot: result shape is not [m, n]");
+      return Refuse(cc, what + ": the block size must be 32 (scales [rows, k / 32])");
+    if (d.dims[o] != m || d.dims[o + 1] != n) return Refuse(cc, what + ": result shape is not [m, n]");
     if (rank == 3 && !(b.dims[0] == a.dims[0] && sa.dims[0] == a.dims[0] && sb.dims[0] == a.dims[0] && d.dims[0] == a.dims[0]))
-      return Refuse(cc, "block-scaled dot: batch dimensions differ");
+      return Refuse(cc, what + ": batch dimensions differ");
     auto g = std::make_unique<Gemm>();
     g->f8 = true;
     g->mx = true;
