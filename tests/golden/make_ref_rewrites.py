@@ -334,10 +334,10 @@ def scaled_dot_cases():
     src = open(os.path.join(ROOT, BLOCK_TESTS[0])).read()
     for name, line, body in split_tests(src, r"BlockScalingRewriter\w*Test"):
         modules = [m for m in raw_strings(body) if "scaled-dot(" in m]
-        verdict = re.search(r"EXPECT_(TRUE|FALSE)\(\s*CudnnScaledDotHelper::IsSupported", body)
-        if modules and verdict:
+        expected = re.search(r"EXPECT_(TRUE|FALSE)\(\s*CudnnScaledDotHelper::IsSupported", body)
+        if modules and expected:
             cases.append({"name": name, "source": f"{BLOCK_TESTS[0]}:{line}", "hlo": modules[0].strip() + "\n",
-                          "supported": verdict.group(1) == "TRUE", "mx_call": None, "error_spec": None})
+                          "supported": expected.group(1) == "TRUE", "mx_call": None, "error_spec": None})
     # Modules held in named constants, each used by one TEST_F through RunMxCorrectnessTest(constant, ErrorSpec(..)).
     src = open(os.path.join(ROOT, MX_EXECUTION_TEST)).read()
     constants = {m.group(1): (m.group(2), src[:m.start()].count("\n") + 1)

@@ -25,7 +25,7 @@ with open(os.path.join(HERE, "golden", "ref_block_scaled.json")) as f:
 CASES = _FIXTURE["cases"]
 SCALED_DOT = _FIXTURE["scaled_dot"]          # modules built on the `scaled-dot` instruction
 BY_NAME = {c["name"]: c for c in CASES}
-# What the rewriter-lite makes of each `scaled-dot` module, with the reason where it differs from a cuDNN verdict.
+# What the rewriter-lite makes of each `scaled-dot` module, with the reason where it differs from cuDNN's answer.
 SCALED_DOT_TAKEN = {
     "CudnnFusionSupportedE4M3": True,
     "CudnnFusionUnsupportedE5M2": True,          # a cuDNN restriction; tcgen05 kind::mxf8f6f4 multiplies e5m2 x e5m2 (tests/test_gpu_mx.py)
