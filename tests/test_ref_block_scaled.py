@@ -29,7 +29,7 @@ BY_NAME = {c["name"]: c for c in CASES}
 SCALED_DOT_TAKEN = {
     "CudnnFusionSupportedE4M3": True,
     "CudnnFusionUnsupportedE5M2": True,          # a cuDNN restriction; tcgen05 kind::mxf8f6f4 multiplies e5m2 x e5m2 (tests/test_gpu_mx.py)
-    "CudnnFusionUnsupportedDimensions": False,   # rhs contracting dimension is the major one
+    "CudnnFusionUnsupportedDimensions": True,    # rhs is [k, n]: transposed (with its scales) in front of the call
     "CudnnFusionUnupportedLayout": False,        # column-major lhs
     "CudnnFusionUnsupportedInputs": True,        # a rule about cuDNN fusion inputs (a broadcast); a custom call takes any value
     "MxFp8Correctness": True, "MxFp8BatchedCorrectness": True, "MxFp8MixedTypesBatchedCorrectness": True,
@@ -136,6 +136,10 @@ def test_scaled_dot_instruction_becomes_the_mx_call(case):
         (c,) = plan["calls"]
         assert c["target"] == "b200$block_scaled_dot$mx" and "scaled-dot(" not in hlo
         assert [x["role"] for x in c["operands"]] == ["a", "b", "a_scale", "b_scale"]
+        if case["name"] == "CudnnFusionUnsupportedDimensions":
+            assert c["operands"][1]["chain"] == ["transpose"] and c["operands"][3]["chain"] == ["transpose"]
+            assert c["operands"][1]["dims"] == [128, 256] and c["operands"][3]["dims"] == [128, 8]
+            assert (c["m"], c["n"], c["k"]) == (128, 128, 256)
     else:
         assert "scaled-dot" in plan["not_rewritten"][0]["reason"]
 

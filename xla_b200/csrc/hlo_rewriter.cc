@@ -848,46 +848,70 @@ class Rewriter {
     const int64_t rank = int64_t(sd->operands[0]->shape.dims.size());
     if (lc.size() != 1 || rc.size() != 1) return Refuse(sd, "scaled-dot: A and B must have one contracting dimension each");
     if (int64_t(sd->operands[1]->shape.dims.size()) != rank) return Refuse(sd, "scaled-dot: operand ranks differ");
-    if (lc[0] != rank - 1 || rc[0] != rank - 1)
-      return Refuse(sd, "scaled-dot: the contracting dimension must be the minor one of both operands (the form of the MX call)");
+    if (rank != 2 && rank != 3) return Refuse(sd, "scaled-dot: operands must have rank 2, or rank 3 with one leading batch dimension");
     const bool batch_ok = rank == 3 ? (lb == std::vector<int64_t>{0} && rb == std::vector<int64_t>{0}) : (lb.empty() && rb.empty());
     if (!batch_ok) return Refuse(sd, "scaled-dot: batch dimensions must be {0} on rank-3 operands and absent on rank-2 ones");
+    const int64_t contracting[2] = {lc[0], rc[0]};
+    for (int k = 0; k < 2; ++k)
+      if (contracting[k] != rank - 1 && contracting[k] != rank - 2) return Refuse(sd, "scaled-dot: the contracting dimension must be one of the two matrix dimensions");
     for (int k = 2; k < 4; ++k)
       if (sd->operands[k]->shape.dims.empty()) return Refuse(sd, "scaled-dot: a scalar scale means no scaling; not the MX form");
     // The instruction's scales may be coarser in any dimension (one scale per dim / scale_dim indices,
-    // hlo_evaluator_typed_visitor.h:1831-1879); the MX form has one per row.
+    // hlo_evaluator_typed_visitor.h:1831-1879); the MX form has one per row and per 32 values along k.
     for (int k = 0; k < 2; ++k) {
       const Shape& v = sd->operands[k]->shape;
       const Shape& sc = sd->operands[k + 2]->shape;
-      if (int64_t(sc.dims.size()) != rank || sc.dims[rank - 2] != v.dims[rank - 2])
+      const int64_t free_dim = contracting[k] == rank - 1 ? rank - 2 : rank - 1;
+      if (int64_t(sc.dims.size()) != rank || sc.dims[free_dim] != v.dims[free_dim])
         return Refuse(sd, "scaled-dot: the block size must be 32 along k and 1 along the rows (scales [rows, k / 32])");
     }
-    TakeMxDot(sd, "scaled-dot", 0);
+    // The MX call wants k minor on both operands.  An operand given [k, rows] is transposed in front of the call
+    // together with its scales (one extra pass over that operand; the library the reference calls takes a
+    // transposed operand through its matrix layouts instead).
+    const std::vector<Instr*> original = sd->operands;
+    for (int k = 0; k < 2; ++k) {
+      if (contracting[k] == rank - 1) continue;
+      for (int which : {k, k + 2}) {
+        Instr* x = sd->operands[which];
+        if (!x->shape.IsDefaultLayout()) { sd->operands = original; return Refuse(sd, "scaled-dot: operands must be in the default (row-major) layout"); }
+        std::vector<int64_t> perm, dims;
+        for (int64_t d = 0; d < rank - 2; ++d) perm.push_back(d);
+        perm.push_back(rank - 1);
+        perm.push_back(rank - 2);
+        for (int64_t d : perm) dims.push_back(x->shape.dims[d]);
+        sd->operands[which] = Add("transpose", MakeShape(x->shape.type, dims), {x}, "dimensions={" + JoinInts(perm) + "}", "", x->name + "_k_minor");
+      }
+    }
+    if (!TakeMxDot(sd, "scaled-dot", 0)) sd->operands = original;
   }
 
-  void TakeMxDot(Instr* cc, const std::string& what, int64_t explicit_block) {
+  bool Declined(Instr* i, const std::string& why) {
+    Refuse(i, why);
+    return false;
+  }
+  bool TakeMxDot(Instr* cc, const std::string& what, int64_t explicit_block) {
     const Shape& a = cc->operands[0]->shape;
     const Shape& b = cc->operands[1]->shape;
     const Shape& sa = cc->operands[2]->shape;
     const Shape& sb = cc->operands[3]->shape;
     const Shape& d = cc->shape;
-    if (!IsF8(a.type) || !IsF8(b.type)) return Refuse(cc, what + ": only f8e4m3fn / f8e5m2 values are implemented, got " + a.type + " and " + b.type);
-    if (sa.type != "f8e8m0fnu" || sb.type != "f8e8m0fnu") return Refuse(cc, what + ": scales must be f8e8m0fnu (MX), got " + sa.type + " and " + sb.type);
-    if (!(d.type == "f32" || d.type == "bf16" || d.type == "f16")) return Refuse(cc, what + ": result must be f32, bf16 or f16");
+    if (!IsF8(a.type) || !IsF8(b.type)) return Declined(cc, what + ": only f8e4m3fn / f8e5m2 values are implemented, got " + a.type + " and " + b.type);
+    if (sa.type != "f8e8m0fnu" || sb.type != "f8e8m0fnu") return Declined(cc, what + ": scales must be f8e8m0fnu (MX), got " + sa.type + " and " + sb.type);
+    if (!(d.type == "f32" || d.type == "bf16" || d.type == "f16")) return Declined(cc, what + ": result must be f32, bf16 or f16");
     const size_t rank = a.dims.size();
     if ((rank != 2 && rank != 3) || b.dims.size() != rank || sa.dims.size() != rank || sb.dims.size() != rank || d.dims.size() != rank)
-      return Refuse(cc, what + ": operands must have rank 2, or rank 3 with one leading batch dimension");
+      return Declined(cc, what + ": operands must have rank 2, or rank 3 with one leading batch dimension");
     for (const Shape* sh : {&a, &b, &sa, &sb, &d})
-      if (!sh->IsDefaultLayout()) return Refuse(cc, what + ": operands must be in the default (row-major) layout");
+      if (!sh->IsDefaultLayout()) return Declined(cc, what + ": operands must be in the default (row-major) layout");
     const size_t o = rank - 2;
     const int64_t m = a.dims[o], k = a.dims[o + 1], n = b.dims[o];
-    if (b.dims[o + 1] != k) return Refuse(cc, what + ": contracting dimensions differ");
-    if (k % 32 != 0 || sa.dims[o] < m || sb.dims[o] < n) return Refuse(cc, what + ": the block size must be 32 (scales [rows, k / 32])");
+    if (b.dims[o + 1] != k) return Declined(cc, what + ": contracting dimensions differ");
+    if (k % 32 != 0 || sa.dims[o] < m || sb.dims[o] < n) return Declined(cc, what + ": the block size must be 32 (scales [rows, k / 32])");
     if (explicit_block ? (sa.dims[o + 1] * 32 < k || sb.dims[o + 1] * 32 < k) : (sa.dims[o + 1] * 32 != k || sb.dims[o + 1] * 32 != k))
-      return Refuse(cc, what + ": the block size must be 32 (scales [rows, k / 32])");
-    if (d.dims[o] != m || d.dims[o + 1] != n) return Refuse(cc, what + ": result shape is not [m, n]");
+      return Declined(cc, what + ": the block size must be 32 (scales [rows, k / 32])");
+    if (d.dims[o] != m || d.dims[o + 1] != n) return Declined(cc, what + ": result shape is not [m, n]");
     if (rank == 3 && !(b.dims[0] == a.dims[0] && sa.dims[0] == a.dims[0] && sb.dims[0] == a.dims[0] && d.dims[0] == a.dims[0]))
-      return Refuse(cc, what + ": batch dimensions differ");
+      return Declined(cc, what + ": batch dimensions differ");
     auto g = std::make_unique<Gemm>();
     g->f8 = true;
     g->mx = true;
@@ -901,6 +925,7 @@ class Rewriter {
     call->gemm = std::move(g);
     calls_.push_back(call);
     Replace(cc, call);
+    return true;
   }
 
   // gemm, or slice(gemm), or bitcast(gemm), or bitcast(slice(gemm)) -- with one user each below the top.
