@@ -200,8 +200,14 @@ size_t b200sd_workspace_bytes(int64_t m, int64_t n, int64_t k);
  * (xla/backends/gpu/autotuner/cublaslt.cc:84-189). */
 int b200sd_select_kernel(int64_t m, int64_t n, int64_t k);
 
+/* The tile form (B200SD_KERNEL_MX_256 / _224) the tuned table holds for an MX block-scaled dot of
+ * this shape, or B200SD_KERNEL_AUTO when it has no entry: the launch then chooses from the tile
+ * counts and the number of CTA pairs the device runs at once. */
+int b200sd_tuned_kernel_mx(int64_t m, int64_t n, int64_t k);
+
 /* Replaces the tuned kernel choices of this process with those in a text file, one per line:
  *     f8|s8  m  n  k  kernel          (kernel = B200SD_KERNEL_* 1..5; `#` starts a comment)
+ *     mx     m  n  k  kernel          (kernel = B200SD_KERNEL_MX_256 or _MX_224)
  * B200SD_KERNEL_AUTO then uses an entry whose (type, m, n, k) matches exactly and the static rule
  * otherwise.  The file is what a persisted autotuning result is to the reference
  * (docs/persisted_autotuning.md; the cuBLASLt backend of the autotuner,

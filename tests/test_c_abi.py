@@ -369,10 +369,22 @@ def test_config_table_overrides_the_static_choice(tmp_path):
     with pytest.raises(XlaFfiError):
         (tmp_path / "s8skinny.txt").write_text("s8 64 4096 4096 2\n")
         xla_b200.load_config_table(tmp_path / "s8skinny.txt")
+    # the MX block-scaled dot has its own type and its own two tile forms
+    assert xla_b200.tuned_kernel_mx(2048, 8192, 4096) == 0
+    mx = tmp_path / "mx.txt"
+    mx.write_text("mx 2048 8192 4096 7\nmx 8192 8192 8192 6\nf8 2048 8192 4096 4\n")
+    assert xla_b200.load_config_table(mx) == 3
+    assert xla_b200.tuned_kernel_mx(2048, 8192, 4096) == 7 and xla_b200.tuned_kernel_mx(8192, 8192, 8192) == 6
+    assert xla_b200.tuned_kernel_mx(4096, 4096, 4096) == 0 and xla_b200.select_kernel(2048, 8192, 4096) == 4
+    for text in ("mx 2048 8192 4096 4\n", "f8 2048 8192 4096 6\n", "s8 256 256 256 7\n", "mxf 256 256 256 6\n"):
+        (tmp_path / "badmx.txt").write_text(text)
+        with pytest.raises(XlaFfiError):
+            xla_b200.load_config_table(tmp_path / "badmx.txt")
+    assert xla_b200.tuned_kernel_mx(2048, 8192, 4096) == 7            # a bad file changes nothing
     empty = tmp_path / "empty.txt"
     empty.write_text("# nothing\n")
     assert xla_b200.load_config_table(empty) == 0                     # and back to the static rule for later tests
-    assert xla_b200.select_kernel(64, 14336, 8192) == 2
+    assert xla_b200.select_kernel(64, 14336, 8192) == 2 and xla_b200.tuned_kernel_mx(2048, 8192, 4096) == 0
 
 
 def test_ctypes_mirrors_match_the_header_as_a_c_compiler_sees_it(tmp_path):

@@ -23,4 +23,5 @@ from .scaled_dot import (  # noqa: F401
     launch_count,
     load_config_table,
     select_kernel,
+    tuned_kernel_mx,
 )

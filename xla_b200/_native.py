@@ -120,6 +120,7 @@ product.b200sd_check_block_scaled_dot_mx.argtypes = [C.POINTER(BlockScaledDotMxA
 product.b200sd_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
 product.b200sd_workspace_bytes.restype = C.c_size_t
 product.b200sd_select_kernel.argtypes = [C.c_int64, C.c_int64, C.c_int64]
+product.b200sd_tuned_kernel_mx.argtypes = [C.c_int64, C.c_int64, C.c_int64]
 product.b200sd_load_config_table.argtypes = [C.c_char_p, C.POINTER(C.c_int32), *_ERR]
 product.b200sd_launch_count.restype = C.c_uint64
 product.b200sd_device_status.argtypes = [C.POINTER(C.c_uint32), *_ERR]

@@ -138,7 +138,7 @@ Status LaunchWaitProbe(uint64_t limit_ns, cudaStream_t stream) {
   return Status::Ok();
 }
 
-// Tuned kernel choices keyed by (integer?, m, n, k): what `selected_algorithm` of a persisted
+// Tuned kernel choices keyed by (type: 0 f8, 1 s8, 2 mx; m, n, k): what `selected_algorithm` of a persisted
 // autotuning result is to the reference (xla/backends/gpu/autotuner/cublaslt.cc:84-189 picks an
 // algorithm by timing, docs/persisted_autotuning.md stores it).  Filled by b200sd_load_config_table;
 // read-mostly, so lookups take a shared lock only.
@@ -174,6 +174,14 @@ int SelectKernelFor(bool int8, int64_t m, int64_t n, int64_t k) {
   return kKernelDense;
 }
 int SelectKernel(int64_t m, int64_t n, int64_t k) { return SelectKernelFor(false, m, n, k); }
+
+// The tuned tile form of the block-scaled kernel for this shape, or kKernelAuto when the table has no entry (the
+// launch then decides from the number of CTA pairs the device runs at once).
+int TunedMxKernel(int64_t m, int64_t n, int64_t k) {
+  std::shared_lock<std::shared_mutex> lock(g_config_mutex);
+  auto it = g_config_table.find(ConfigKey{2, m, n, k});
+  return it != g_config_table.end() ? it->second : kKernelAuto;
+}
 
 Status ValidateF8(const B200SD_ScaledDotF8& in, GemmProblem* g, bool check_pointers = true) {
   // The struct grew by batch_count; older callers pass the shorter size and get a plain matrix product.
@@ -456,6 +464,8 @@ size_t b200sd_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 
 int b200sd_select_kernel(int64_t m, int64_t n, int64_t k) { return SelectKernel(m, n, k); }
 
+int b200sd_tuned_kernel_mx(int64_t m, int64_t n, int64_t k) { return TunedMxKernel(m, n, k); }
+
 int b200sd_load_config_table(const char* path, int32_t* entries, char* err, size_t err_len) {
   if (entries != nullptr) *entries = 0;
   if (path == nullptr) return CopyStatus(Status::Error(kInvalidArgument, "path is null"), err, err_len);
@@ -473,13 +483,17 @@ int b200sd_load_config_table(const char* path, int32_t* entries, char* err, size
     char type[8];
     long long m, n, k;
     int kernel;
-    if (std::sscanf(p, "%7s %lld %lld %lld %d", type, &m, &n, &k, &kernel) != 5 || (std::strcmp(type, "f8") != 0 && std::strcmp(type, "s8") != 0) ||
-        m <= 0 || n <= 0 || k <= 0 || kernel < B200SD_KERNEL_DENSE || kernel > B200SD_KERNEL_DENSE_STREAMK ||
-        (type[0] == 's' && kernel == B200SD_KERNEL_SKINNY)) {
-      st = Status::Error(kInvalidArgument, std::string(path) + ":" + std::to_string(lineno) + ": expected `f8|s8 m n k kernel` with kernel 1..5");
+    const bool parsed = std::sscanf(p, "%7s %lld %lld %lld %d", type, &m, &n, &k, &kernel) == 5;
+    const int type_code = !parsed ? -1 : std::strcmp(type, "f8") == 0 ? 0 : std::strcmp(type, "s8") == 0 ? 1 : std::strcmp(type, "mx") == 0 ? 2 : -1;
+    const bool kernel_ok = type_code == 2 ? (kernel == B200SD_KERNEL_MX_256 || kernel == B200SD_KERNEL_MX_224)
+                                          : (kernel >= B200SD_KERNEL_DENSE && kernel <= B200SD_KERNEL_DENSE_STREAMK &&
+                                             !(type_code == 1 && kernel == B200SD_KERNEL_SKINNY));
+    if (type_code < 0 || m <= 0 || n <= 0 || k <= 0 || !kernel_ok) {
+      st = Status::Error(kInvalidArgument, std::string(path) + ":" + std::to_string(lineno) +
+                                               ": expected `f8|s8 m n k kernel` with kernel 1..5, or `mx m n k kernel` with kernel 6 or 7");
       break;
     }
-    table[ConfigKey{type[0] == 's' ? 1 : 0, m, n, k}] = kernel;
+    table[ConfigKey{type_code, m, n, k}] = kernel;
   }
   std::fclose(f);
   if (!st.ok()) return CopyStatus(st, err, err_len);          // a bad file changes nothing

@@ -178,6 +178,7 @@ struct MxProblem {
   int32_t d_dtype = kF32;
   int32_t kernel = kKernelAuto;      // kKernelAuto, kKernelMxPair256 or kKernelMxPair224
 };
+int TunedMxKernel(int64_t m, int64_t n, int64_t k);      // the tuned table's tile form for this shape, or kKernelAuto
 Status ValidateMx(const MxProblem& g);      // everything but the pointers
 Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats);
 

@@ -629,7 +629,9 @@ Status LaunchMx(const MxProblem& g, cudaStream_t stream, LaunchStats* stats) {
   };
   const double k_cycles = 512.0 * double((g.k + kMxBK - 1) / kMxBK);
   const double cost256 = rounds(256) * (k_cycles + 800.0), cost224 = rounds(224) * k_cycles * (224.0 / 256.0) * 1.08;
-  const int bn = g.kernel == kKernelMxPair256 ? 256 : g.kernel == kKernelMxPair224 ? 224 : (cost224 < cost256 ? 224 : 256);
+  // A tuned table entry for exactly this shape (single dots only) wins over the cost estimate.
+  const int want = g.kernel != kKernelAuto ? g.kernel : (batch == 1 ? TunedMxKernel(g.m, g.n, g.k) : kKernelAuto);
+  const int bn = want == kKernelMxPair256 ? 256 : want == kKernelMxPair224 ? 224 : (cost224 < cost256 ? 224 : 256);
   st = MakeBatchedByteMatrixMap(&tmap_b, g.b, batch, g.n, g.k, kMxBK, uint32_t(bn / 2));      // [n, k], box 128(k) x 128|112(n)
   if (!st.ok()) return st;
 

@@ -391,3 +391,9 @@ def load_config_table(path: str) -> int:
 def select_kernel(m: int, n: int, k: int) -> int:
     """What selected_config = 0 resolves to for an FP8 dot of this shape."""
     return int(_native.product.b200sd_select_kernel(m, n, k))
+
+
+def tuned_kernel_mx(m: int, n: int, k: int) -> int:
+    """The tile form (6 / 7) the tuned table holds for an MX block-scaled dot of this shape; 0 when it has none and
+    the launch decides."""
+    return int(_native.product.b200sd_tuned_kernel_mx(m, n, k))
