@@ -278,6 +278,23 @@ def test_tiny_int8_dot_is_padded_and_sliced():
     assert np.array_equal(hlo_eval.evaluate(text, [a, b]), a.astype(np.int32) @ b.astype(np.int32))
 
 
+def test_operands_written_as_nested_instructions():
+    """HLO text may spell an operand as a whole instruction (`dot(f32[..] convert(x), ...)`, as the reference's
+    block_scaling_rewriter_cudnn_test.cc:147-165 does); the parser gives such operands names of their own."""
+    text = """HloModule nested
+ENTRY main {
+  x = f8e4m3fn[64,128] parameter(0)
+  w = f8e4m3fn[128,32] parameter(1)
+  ROOT d = f32[64,32] dot(f32[64,128] convert(x), f32[128,32] convert(f8e4m3fn[128,32] copy(w))), lhs_contracting_dims={1}, rhs_contracting_dims={0}
+}
+"""
+    hlo, plan = hlo_runner.rewrite(text)
+    (c,) = plan["calls"]
+    assert c["target"] == "b200$scaled_dot$f8" and (c["m"], c["n"], c["k"]) == (64, 32, 128)
+    assert [op["param"] for op in c["operands"][:2]] == [0, 1] and c["operands"][1]["chain"] == ["copy"]
+    assert " dot(" not in hlo
+
+
 def test_batched_int8_dot_keeps_its_batch_dimension():
     """s8 x s8 -> s32 is in the type table for batched dots as for plain ones (gemm_rewriter.cc:2425-2677 does not look
     at the rank); the call carries the same batch attributes as the FP8 call."""

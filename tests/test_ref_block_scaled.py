@@ -15,7 +15,6 @@ import pytest
 from oracle import hlo_eval
 from oracle import scaled_dot_oracle as o
 from xla_b200 import hlo_runner
-from xla_b200.scaled_dot import XlaFfiError
 
 import ref_cases
 
@@ -59,13 +58,12 @@ def test_the_fixture_holds_the_reference_tests():
 
 @pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
 def test_rewriter_decides_as_the_reference_does(case):
-    if "f4e2m1fn" in case["hlo"]:
-        # NVFP4: 4-bit values, not implemented; the module also spells an operand as a nested instruction, which the
-        # rewriter-lite's parser refuses.  Either way nothing is rewritten.
-        with pytest.raises(XlaFfiError):
-            hlo_runner.rewrite(case["hlo"])
-        return
     hlo, plan = hlo_runner.rewrite(case["hlo"])
+    if "f4e2m1fn" in case["hlo"]:
+        # NVFP4 (4-bit values, e4m3 scales per 16, optionally a global scale): not implemented, left to the expansion.
+        # (These modules also spell operands as nested instructions, `convert(f16[..] multiply(%p0, %mult))`.)
+        assert not plan["rewritten"] and "block-scaled" in plan["not_rewritten"][0]["reason"]
+        return
     if case["library"] and is_mx_fp8(case):
         assert plan["rewritten"] and not plan["not_rewritten"], case["name"]
         (c,) = plan["calls"]

@@ -125,6 +125,7 @@ struct Instr {
   std::string opcode;
   std::vector<Instr*> operands;
   std::vector<std::string> operand_names;   // as parsed, before resolution
+  std::vector<std::string> nested;          // operands written as whole instructions, to be parsed in front of this one
   std::string attrs;                // everything after the closing parenthesis, verbatim
   std::string literal;              // constant(...) / parameter(...) payload
   bool is_root = false;
@@ -242,6 +243,16 @@ bool ParseInstr(const std::string& line_in, Instr* in, std::string* err) {
       else cur += c;
     }
     if (!Trim(cur).empty()) in->operand_names.push_back(Trim(cur));
+    for (size_t i = 0; i < in->operand_names.size(); ++i) {
+      // An operand spelled as an instruction of its own, "f16[8] multiply(%a, %b)": the caller parses it as a
+      // separate instruction under a made-up name.
+      std::string& o = in->operand_names[i];
+      if (!o.empty() && o.back() == ')') {
+        const std::string nested_name = in->name + ".operand" + std::to_string(i);
+        in->nested.emplace_back(nested_name + " = " + o);
+        o = nested_name;
+      }
+    }
     for (std::string& o : in->operand_names) {            // "f32[4] %x" or "%x" or "x"
       size_t sp = o.find_last_of(' ');
       if (sp != std::string::npos) o = o.substr(sp + 1);
@@ -302,9 +313,17 @@ bool ParseModule(const std::string& text, Module* m, std::string* err) {
       closes_after = true;
     }
     cur->raw += "  " + t + "\n";
-    auto in = std::make_unique<Instr>();
-    if (!ParseInstr(t, in.get(), err)) return false;
-    cur->instrs.push_back(std::move(in));
+    // Operands written as nested instructions come out as instructions of their own, in front of their user.
+    std::function<bool(const std::string&)> add = [&](const std::string& line) {
+      auto in = std::make_unique<Instr>();
+      if (!ParseInstr(line, in.get(), err)) return false;
+      for (const std::string& inner : in->nested)
+        if (!add(inner)) return false;
+      in->nested.clear();
+      cur->instrs.push_back(std::move(in));
+      return true;
+    };
+    if (!add(t)) return false;
     if (closes_after) { cur->raw += "}\n"; cur = nullptr; }
   }
   if (m->computations.empty()) { *err = "module has no computation"; return false; }
