@@ -118,18 +118,31 @@ def _parse(text):
         root = t.startswith("ROOT ")
         if root:
             t = t[5:].strip()
-        name, rest = t.split(" = ", 1)
-        m = re.match(r"(\(.*?\)\s|[a-z0-9]+\[[0-9, ]*\](?:\{[^}]*\})?\s)?\s*([a-z\-]+)\((.*)$", rest)
-        assert m, rest
-        shape, opcode, tail = m.group(1), m.group(2), m.group(3)
-        depth, i = 1, 0
-        while depth:
-            depth += {"(": 1, ")": -1}.get(tail[i], 0)
-            i += 1
-        args, attrs = tail[: i - 1], tail[i:].lstrip(", ")
-        operands = [a.strip().split(" ")[-1].lstrip("%") for a in _split(args)] if opcode not in ("constant", "parameter") else []
-        cur.append(dict(name=name.strip().lstrip("%"), shape=shape.strip() if shape else None, opcode=opcode, operands=operands,
-                        literal=args.strip(), attrs=attrs, root=root))
+
+        def add(line, is_root):
+            name, rest = line.split(" = ", 1)
+            name = name.strip().lstrip("%")
+            m = re.match(r"(\(.*?\)\s|[a-z0-9]+\[[0-9, ]*\](?:\{[^}]*\})?\s)?\s*([a-z\-]+)\((.*)$", rest)
+            assert m, rest
+            shape, opcode, tail = m.group(1), m.group(2), m.group(3)
+            depth, i = 1, 0
+            while depth:
+                depth += {"(": 1, ")": -1}.get(tail[i], 0)
+                i += 1
+            args, attrs = tail[: i - 1], tail[i:].lstrip(", ")
+            operands = []
+            if opcode not in ("constant", "parameter"):
+                for k, a in enumerate(_split(args)):
+                    a = a.strip()
+                    if a.endswith(")"):          # an operand written as an instruction of its own: evaluated first, under a made-up name
+                        nested = f"{name}.operand{k}"
+                        add(f"{nested} = {a}", False)
+                        a = nested
+                    operands.append(a.split(" ")[-1].lstrip("%"))
+            cur.append(dict(name=name, shape=shape.strip() if shape else None, opcode=opcode, operands=operands,
+                            literal=args.strip(), attrs=attrs, root=is_root))
+
+        add(t, root)
         if closes:
             cur = None
     return comps, entry or last

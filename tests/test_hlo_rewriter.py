@@ -293,6 +293,13 @@ ENTRY main {
     assert c["target"] == "b200$scaled_dot$f8" and (c["m"], c["n"], c["k"]) == (64, 32, 128)
     assert [op["param"] for op in c["operands"][:2]] == [0, 1] and c["operands"][1]["chain"] == ["copy"]
     assert " dot(" not in hlo
+    # the interpreter reads the same spelling, and gives what it gives for the module written out flat
+    flat = text.replace("dot(f32[64,128] convert(x), f32[128,32] convert(f8e4m3fn[128,32] copy(w)))", "dot(xf, wf)").replace(
+        "  ROOT d", "  xf = f32[64,128] convert(x)\n  wf = f32[128,32] convert(w)\n  ROOT d")
+    rng = np.random.default_rng(29)
+    x = o.fp8_encode(rng.standard_normal((64, 128), dtype=np.float32), "e4m3fn")
+    w = o.fp8_encode(rng.standard_normal((128, 32), dtype=np.float32), "e4m3fn")
+    assert np.array_equal(hlo_eval.evaluate(text, [x, w]), hlo_eval.evaluate(flat, [x, w]))
 
 
 def test_batched_int8_dot_keeps_its_batch_dimension():
