@@ -81,3 +81,55 @@ ENTRY main {
 """
     hlo, plan = hlo_runner.rewrite(text)
     assert sorted(c["target"] for c in plan["calls"]) == ["b200$block_scaled_dot$mx", "b200$scaled_dot$f8"]
+
+
+def _mx_module(m, n, k, batch, a_rows, a_cols, b_rows, b_cols, out="f32", block_size=None):
+    lead = f"{batch}," if batch else ""
+    cfg = f', backend_config={{"block_scaled_dot_backend_config":{{block_size:{block_size}}}}}' if block_size else ""
+    return f"""HloModule generated
+ENTRY main {{
+  lhs = f8e4m3fn[{lead}{m},{k}] parameter(0)
+  rhs = f8e5m2[{lead}{n},{k}] parameter(1)
+  lhs_scale = f8e8m0fnu[{lead}{a_rows},{a_cols}] parameter(2)
+  rhs_scale = f8e8m0fnu[{lead}{b_rows},{b_cols}] parameter(3)
+  ROOT result = {out}[{lead}{m},{n}] custom-call(lhs, rhs, lhs_scale, rhs_scale), custom_call_target="__op$block_scaled_dot"{cfg}
+}}
+"""
+
+
+def test_generated_mx_modules_padding_and_block_size():
+    """Shapes drawn at random: the call is taken exactly when the scales cover [rows, k / 32] -- extra rows always,
+    extra columns only with the explicit block size (block_scaling_rewriter.cc:469-518) -- and the interpreter's
+    result does not depend on what the padding holds."""
+    rng = np.random.default_rng(2024)
+    for trial in range(40):
+        m, n = int(rng.integers(1, 70)), int(rng.integers(1, 70))
+        k = 32 * int(rng.integers(1, 6))
+        batch = int(rng.integers(0, 3))
+        pad_rows_a, pad_rows_b = int(rng.integers(0, 9)) * int(rng.integers(0, 2)), int(rng.integers(0, 9)) * int(rng.integers(0, 2))
+        pad_cols = int(rng.integers(0, 4)) * int(rng.integers(0, 2))
+        explicit = bool(rng.integers(0, 2))
+        text = _mx_module(m, n, k, batch, m + pad_rows_a, k // 32 + pad_cols, n + pad_rows_b, k // 32 + pad_cols,
+                          out=("f32", "bf16", "f16")[trial % 3], block_size=32 if explicit else None)
+        _, plan = hlo_runner.rewrite(text)
+        want_taken = explicit or pad_cols == 0
+        assert plan["rewritten"] == want_taken, text
+        if want_taken:
+            (c,) = plan["calls"]
+            assert (c["m"], c["n"], c["k"], c["batch"]) == (m, n, k, batch)
+            assert c["operands"][2]["dims"][-2:] == [m + pad_rows_a, k // 32 + pad_cols]
+            assert c["attrs"].get("block_size") == (32 if explicit else None)
+        if not explicit and pad_cols:
+            continue                      # block size implied by the shapes is not 32: only the generic expansion applies
+        args = ref_cases.make_inputs(text, trial)
+        a, b, sa, sb = args
+        base = hlo_eval.evaluate(text, [a, b, sa, sb])
+        sa2, sb2 = sa.copy(), sb.copy()
+        sa2[..., m:, :] = 0xFF
+        sb2[..., n:, :] = 0xFF
+        if explicit:
+            sa2[..., k // 32:] = 0xFF
+            sb2[..., k // 32:] = 0xFF
+        assert np.array_equal(hlo_eval.evaluate(text, [a, b, sa2, sb2]), base), text
+        code = {"f32": o.F32, "bf16": o.BF16, "f16": o.F16}[("f32", "bf16", "f16")[trial % 3]]
+        assert np.array_equal(base, o.block_scaled_dot(a, b, sa[..., :m, : k // 32], sb[..., :n, : k // 32], b_kind="e5m2", out_dtype=code))
