@@ -348,7 +348,11 @@ def evaluate(text, params):
             rc = _attr_dims(attrs, "rhs_contracting_dims")[0]
             lb, rb = _attr_dims(attrs, "lhs_batch_dims") or (), _attr_dims(attrs, "rhs_batch_dims") or ()
             (lt, lv), (rt, rv) = a
-            if lt == "s8" and not lb and np.asarray(lv).ndim == 2 and np.asarray(rv).ndim == 2:
+            if lt in _INT and t not in _INT:
+                # integer operands, floating-point result: the interpreter converts the operands to the result type
+                # and accumulates there (hlo_evaluator_typed_visitor.h:1271-1340); sums stay exact below 2^24
+                val = (t, _from_f32(t, _dot(np.asarray(lv).astype(np.float32), np.asarray(rv).astype(np.float32), lc, rc, lb, rb)))
+            elif lt == "s8" and not lb and np.asarray(lv).ndim == 2 and np.asarray(rv).ndim == 2:
                 val = (t, o.dot_s8(lv, rv, lc, rc))
             elif lt in _INT and not lb:        # several free dimensions: exact integer contraction
                 val = (t, np.tensordot(np.asarray(lv, np.int64), np.asarray(rv, np.int64), axes=([lc], [rc])).astype(_INT[t]))

@@ -278,6 +278,33 @@ def test_tiny_int8_dot_is_padded_and_sliced():
     assert np.array_equal(hlo_eval.evaluate(text, [a, b]), a.astype(np.int32) @ b.astype(np.int32))
 
 
+def test_int8_dot_with_an_f32_result():
+    """s8 x s8 -> f32 is a row of the run-time type table next to s8 x s8 -> s32 (cuda_blas_lt.cc:444-445): taken by the
+    s8 call with an f32 D; epilogue ops behind it (here a ReLU) are not folded into the integer call."""
+    text = """HloModule int8_f32
+ENTRY main {
+  a = s8[48,64] parameter(0)
+  b = s8[64,32] parameter(1)
+  d = f32[48,32] dot(a, b), lhs_contracting_dims={1}, rhs_contracting_dims={0}
+  z = f32[] constant(0)
+  zb = f32[48,32] broadcast(z), dimensions={}
+  ROOT r = f32[48,32] maximum(d, zb)
+}
+"""
+    hlo, plan = hlo_runner.rewrite(text)
+    (c,) = plan["calls"]
+    assert c["target"] == "b200$dot$s8" and c["results"][0]["dtype"] == 11 and (c["m"], c["n"], c["k"]) == (48, 32, 64)
+    assert len(c["operands"]) == 2 and c["attrs"]["emit_s32"] is False
+    assert "maximum(" in hlo and " dot(" not in hlo                  # the ReLU stays an HLO op
+    from xla_b200.scaled_dot import Buffer, Int8DotCall
+    Int8DotCall([Buffer(2, (48, 64)), Buffer(2, (64, 32))], [Buffer(11, (48, 32)), Buffer(2, (1 << 20,))]).instantiate()
+    rng = np.random.default_rng(33)
+    a = rng.integers(-128, 128, (48, 64), dtype=np.int8)
+    b = rng.integers(-128, 128, (64, 32), dtype=np.int8)
+    want = np.maximum(a.astype(np.int64) @ b.astype(np.int64), 0).astype(np.float32)
+    assert np.array_equal(hlo_eval.evaluate(text, [a, b]), want)
+
+
 def test_operands_written_as_nested_instructions():
     """HLO text may spell an operand as a whole instruction (`dot(f32[..] convert(x), ...)`, as the reference's
     block_scaling_rewriter_cudnn_test.cc:147-165 does); the parser gives such operands names of their own."""

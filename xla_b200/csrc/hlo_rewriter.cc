@@ -731,7 +731,9 @@ class Rewriter {
     Instr* rhs = dot->operands[1];
     const std::vector<int64_t> lc = AttrList(dot->attrs, "lhs_contracting_dims"), rc = AttrList(dot->attrs, "rhs_contracting_dims");
     const std::vector<int64_t> lb = AttrList(dot->attrs, "lhs_batch_dims"), rb = AttrList(dot->attrs, "rhs_batch_dims");
-    const bool int8 = lhs->shape.type == "s8" && rhs->shape.type == "s8" && dot->shape.type == "s32";
+    // s8 x s8 -> s32, and s8 x s8 -> f32 (both rows of the run-time type table, cuda_blas_lt.cc:444-445): the f32 form
+    // is the exact s32 sum converted once.
+    const bool int8 = lhs->shape.type == "s8" && rhs->shape.type == "s8" && (dot->shape.type == "s32" || dot->shape.type == "f32");
 
     Fp8Param a, b;
     std::string why;
@@ -957,7 +959,7 @@ class Rewriter {
     Instr* cur = x;
     if (cur->opcode == "bitcast" && cur->operands.size() == 1) { t->bitcast = cur; cur = cur->operands[0]; }
     if (cur->opcode == "slice" && cur->operands.size() == 1) { t->slice = cur; cur = cur->operands[0]; }
-    if (!IsGemm(cur)) return false;
+    if (!IsF8Gemm(cur)) return false;          // epilogues are fused into the FP8 call only
     t->gemm = cur;
     if (need_one_user_each) {
       if (UserCount(cur) != 1) return false;
@@ -998,7 +1000,7 @@ class Rewriter {
       Instr* g = instr->operands[side];
       Instr* other = instr->operands[1 - side];
       double alpha;
-      if (IsGemm(g) && UserCount(g) == 1 && UserCount(other) == 1 && BcastConst(other, &alpha) && g->shape.type != "s32" &&
+      if (IsF8Gemm(g) && UserCount(g) == 1 && UserCount(other) == 1 && BcastConst(other, &alpha) &&
           g->gemm->beta == 0.0 && g->gemm->epilogue == 0 && !g->gemm->has_d_scale) {
         g->gemm->alpha *= alpha;
         Replace(instr, g);
