@@ -15,6 +15,9 @@ Sources, read as text:
   * xla/service/gpu/backend_configs.proto -- `enum Epilogue { ... }` of GemmBackendConfig, and
     xla/ffi/api/c_api.h -- `XLA_FFI_DataType`, `XLA_FFI_Error_Code`: the numbers the boundary
     (include/b200_scaled_dot.h) must use (interface_enums.json).
+  * xla/hlo/evaluator/hlo_evaluator_test.cc -- the three known-answer tests of the `scaled-dot` instruction
+    (ScaledDot, ScaledDotWithOneMissingScale, ScaledDotWithBatchDim): operand extents and start values of the
+    `FillUnique` arrays, dot dimension numbers and the expected result (scaled_dot_known_answers.json).
 """
 import json
 import math
@@ -90,6 +93,37 @@ def write_interface_enums():
         json.dump(out, f, indent=1, sort_keys=True)
 
 
+def write_scaled_dot_known_answers():
+    """Each operand of the tests is `BF16Array2D(b, rows, cols, start)`, `BF16Array3D(b, batch, rows, cols, start)`
+    (arrays filled by FillUnique, xla/array2d.h:78-85 and xla/array3d.h:65-76) or a BF16 scalar constant."""
+    rel = "xla/hlo/evaluator/hlo_evaluator_test.cc"
+    src = open(os.path.join(ROOT, rel)).read()
+    tests = []
+    for m in re.finditer(r"TEST_F\(HloEvaluatorTest, (ScaledDot\w*)\) \{(.*?)\n\}\n", src, flags=re.S):
+        name, body = m.group(1), m.group(2)
+        operands = {}
+        for om in re.finditer(r"auto (\w+)_instr =\s*(.*?);", body, flags=re.S):
+            which, expr = om.group(1), " ".join(om.group(2).split())
+            a = re.search(r"BF16Array([23])D\(b, ([0-9, ]+), ([0-9.]+)f\)", expr)
+            if a:
+                operands[which] = {"dims": [int(x) for x in a.group(2).split(",")], "start": float(a.group(3))}
+            else:
+                c = re.search(r"CreateR0\(BF16, ([0-9.]+)f\)", expr)
+                assert c, expr
+                operands[which] = {"scalar": float(c.group(1))}
+        assert sorted(operands) == ["lhs", "lhs_scale", "rhs", "rhs_scale"], (name, operands)
+        dnums = {k: [int(x) for x in re.findall(r"add_%s\((\d+)\)" % k, body)]
+                 for k in ("lhs_batch_dimensions", "rhs_batch_dimensions", "lhs_contracting_dimensions", "rhs_contracting_dimensions")}
+        shape = [int(x) for x in re.search(r"MakeShape\(BF16, \{([0-9, ]+)\}\)", body).group(1).split(",")]
+        exp = re.search(r"Array[23]D<float>\((\{.*?\})\);", body, flags=re.S).group(1)
+        expected = [float(x) for x in re.findall(r"([0-9.]+)f", exp)]
+        tests.append({"name": name, "line": src[: m.start()].count("\n") + 1, "operands": operands, "dot_dimension_numbers": dnums,
+                      "result_type": "bf16", "result_dims": shape, "expected_f32_before_rounding_to_bf16": expected})
+    assert [t["name"] for t in tests] == ["ScaledDot", "ScaledDotWithOneMissingScale", "ScaledDotWithBatchDim"], tests
+    with open(os.path.join(HERE, "scaled_dot_known_answers.json"), "w") as f:
+        json.dump({"source": rel, "operand_type": "bf16", "tests": tests}, f, indent=1)
+
+
 def main():
     src = open(os.path.join(ROOT, "xla/tests/convert_test.cc")).read()
     out = {"source": "xla/tests/convert_test.cc", "tables": {}}
@@ -125,6 +159,7 @@ def main():
     with open(os.path.join(HERE, "s8_known_answer.json"), "w") as f:
         json.dump(known, f, indent=1)
     write_interface_enums()
+    write_scaled_dot_known_answers()
     print("wrote", sorted(os.listdir(HERE)))
 
 

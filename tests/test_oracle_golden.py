@@ -217,3 +217,54 @@ def test_near_comparison_rule():
     assert o.near_mismatches(np.array([np.inf]), np.array([1e30]), 1e-2, 1e-2)[0] == 1
     assert o.near_mismatches(np.array([1.0]), np.array([np.nan]), 1e-2, 1e-2)[0] == 1
     assert o.fp8_within_n_values(np.array([0x38, 0x38, 0x81], np.uint8), np.array([0x39, 0x3A, 0x01], np.uint8), 1) == 2
+
+
+def _fill_unique(dims, start):
+    """Array2D::FillUnique / Array3D::FillUnique (xla/array2d.h:78-85, xla/array3d.h:65-76): every index shifted into
+    its own bit field, plus the start value."""
+    def log2ceil(n):
+        return int(math.ceil(math.log2(n))) if n > 1 else 0
+
+    out = np.zeros(dims, np.float32)
+    if len(dims) == 2:
+        shift = log2ceil(dims[1])
+        for i0 in range(dims[0]):
+            for i1 in range(dims[1]):
+                out[i0, i1] = ((i0 << shift) | i1) + start
+    else:
+        shift2, shift3 = log2ceil(dims[1]), log2ceil(dims[2])
+        for i0 in range(dims[0]):
+            for i1 in range(dims[1]):
+                for i2 in range(dims[2]):
+                    out[i0, i1, i2] = ((i0 << (shift3 + shift2)) | (i1 << shift2) | i2) + start
+    return out
+
+
+def test_scaled_dot_instruction_known_answers():
+    """The `scaled-dot` known answers of xla/hlo/evaluator/hlo_evaluator_test.cc:2251-2409 (block scales in either
+    contracting position, a scalar scale meaning none, a scale shared by the batch entries): the interpreter in
+    oracle/hlo_eval.py must return exactly the reference's expected literal."""
+    from oracle import hlo_eval
+
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scaled_dot_known_answers.json")) as f:
+        golden = json.load(f)
+    assert [t["name"] for t in golden["tests"]] == ["ScaledDot", "ScaledDotWithOneMissingScale", "ScaledDotWithBatchDim"]
+    for t in golden["tests"]:
+        lines, args = [], []
+        for i, which in enumerate(("lhs", "rhs", "lhs_scale", "rhs_scale")):
+            spec = t["operands"][which]
+            if "scalar" in spec:
+                lines.append(f"  {which} = bf16[] parameter({i})")
+                args.append(o.f32_to_bf16_bits(np.float32(spec["scalar"])))
+            else:
+                lines.append(f"  {which} = bf16[{','.join(map(str, spec['dims']))}] parameter({i})")
+                args.append(o.f32_to_bf16_bits(_fill_unique(spec["dims"], spec["start"])))
+        d = t["dot_dimension_numbers"]
+        attrs = ", ".join(f"{k.replace('_dimensions', '_dims')}={{{','.join(map(str, v))}}}" for k, v in d.items() if v)
+        text = ("HloModule known_answer\nENTRY main {\n" + "\n".join(lines) +
+                f"\n  ROOT d = bf16[{','.join(map(str, t['result_dims']))}] scaled-dot(lhs, rhs, lhs_scale, rhs_scale), {attrs}\n}}\n")
+        got = hlo_eval.evaluate(text, args)
+        want = o.f32_to_bf16_bits(np.asarray(t["expected_f32_before_rounding_to_bf16"], np.float32).reshape(t["result_dims"]))
+        assert np.array_equal(np.asarray(got), want), (t["name"], o.bf16_bits_to_f32(np.asarray(got)).tolist())
+    # the third test's exact sum is 1140, which is not a bf16 value: the expected literal is the rounded 1136
+    assert golden["tests"][2]["expected_f32_before_rounding_to_bf16"] == [428.0, 1136.0]
