@@ -17,7 +17,8 @@ Sources, read as text:
     (include/b200_scaled_dot.h) must use (interface_enums.json).
   * xla/hlo/evaluator/hlo_evaluator_test.cc -- the three known-answer tests of the `scaled-dot` instruction
     (ScaledDot, ScaledDotWithOneMissingScale, ScaledDotWithBatchDim): operand extents and start values of the
-    `FillUnique` arrays, dot dimension numbers and the expected result (scaled_dot_known_answers.json).
+    `FillUnique` arrays, dot dimension numbers and the expected result (scaled_dot_known_answers.json); and the
+    DoesClamp and DotRank2AndRank2 known answers of the same file (evaluator_known_answers.json).
 """
 import json
 import math
@@ -124,6 +125,39 @@ def write_scaled_dot_known_answers():
         json.dump({"source": rel, "operand_type": "bf16", "tests": tests}, f, indent=1)
 
 
+def write_evaluator_known_answers():
+    rel = "xla/hlo/evaluator/hlo_evaluator_test.cc"
+    src = open(os.path.join(ROOT, rel)).read()
+
+    def body_of(name):
+        m = re.search(r"TEST_P\(HloEvaluatorBf16Test, %s\) \{(.*?)\n\}\n" % name, src, flags=re.S)
+        return m.group(1), src[: m.start()].count("\n") + 1
+
+    def matrix(text):
+        return [[float(x.rstrip("f")) for x in re.findall(r"-?[0-9.]+f?", row)] for row in re.findall(r"\{([^{}]*)\}", text)]
+
+    clamp, clamp_line = body_of("DoesClamp")
+    lits = {k: matrix(re.search(r"auto %s = LiteralUtil::CreateR2<float>\((\{.*?\})\);" % k, clamp, flags=re.S).group(1))
+            for k in ("low", "value", "high", "expected")}
+    assert "HloOpcode::kClamp, c1, c2, c3" in clamp                      # clamp(low, value, high)
+    dot, dot_line = body_of("DotRank2AndRank2")
+    arrays = [(int(a), int(b), float(c)) for a, b, c in
+              re.findall(r"Array2D<float>>\((\d+), (\d+)\);\s*\w+->FillUnique\(([0-9.]+)f\)", dot)]
+    assert len(arrays) == 2, arrays
+    expected = matrix(re.search(r"auto expected_array = Array2D<float>\((\{.*?\})\);", dot, flags=re.S).group(1))
+    out = {
+        "source": rel,
+        "DoesClamp": dict(lits, line=clamp_line),
+        "DotRank2AndRank2": {"line": dot_line, "lhs": {"dims": list(arrays[0][:2]), "start": arrays[0][2]},
+                             "rhs": {"dims": list(arrays[1][:2]), "start": arrays[1][2]},
+                             "lhs_contracting_dimensions": [int(x) for x in re.findall(r"add_lhs_contracting_dimensions\((\d+)\)", dot)],
+                             "rhs_contracting_dimensions": [int(x) for x in re.findall(r"add_rhs_contracting_dimensions\((\d+)\)", dot)],
+                             "expected": expected},
+    }
+    with open(os.path.join(HERE, "evaluator_known_answers.json"), "w") as f:
+        json.dump(out, f, indent=1)
+
+
 def main():
     src = open(os.path.join(ROOT, "xla/tests/convert_test.cc")).read()
     out = {"source": "xla/tests/convert_test.cc", "tables": {}}
@@ -160,6 +194,7 @@ def main():
         json.dump(known, f, indent=1)
     write_interface_enums()
     write_scaled_dot_known_answers()
+    write_evaluator_known_answers()
     print("wrote", sorted(os.listdir(HERE)))
 
 

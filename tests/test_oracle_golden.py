@@ -268,3 +268,38 @@ def test_scaled_dot_instruction_known_answers():
         assert np.array_equal(np.asarray(got), want), (t["name"], o.bf16_bits_to_f32(np.asarray(got)).tolist())
     # the third test's exact sum is 1140, which is not a bf16 value: the expected literal is the rounded 1136
     assert golden["tests"][2]["expected_f32_before_rounding_to_bf16"] == [428.0, 1136.0]
+
+
+def test_evaluator_known_answers_for_clamp_and_dot():
+    """DoesClamp and DotRank2AndRank2 of xla/hlo/evaluator/hlo_evaluator_test.cc (the test fixture runs each in f32 and
+    in bf16): the interpreter's clamp(low, value, high) operand order and its dot over `lhs_contracting_dims={1},
+    rhs_contracting_dims={0}` must give the reference's expected literals exactly, in both types."""
+    from oracle import hlo_eval
+
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "evaluator_known_answers.json")) as f:
+        golden = json.load(f)
+    for t in ("f32", "bf16"):
+        conv = (lambda x: np.asarray(x, np.float32)) if t == "f32" else (lambda x: o.f32_to_bf16_bits(np.asarray(x, np.float32)))
+        back = (lambda x: np.asarray(x, np.float32)) if t == "f32" else (lambda x: o.bf16_bits_to_f32(np.asarray(x)))
+        c = golden["DoesClamp"]
+        text = f"""HloModule clamp
+ENTRY main {{
+  low = {t}[2,2] parameter(0)
+  value = {t}[2,2] parameter(1)
+  high = {t}[2,2] parameter(2)
+  ROOT r = {t}[2,2] clamp(low, value, high)
+}}
+"""
+        got = hlo_eval.evaluate(text, [conv(c["low"]), conv(c["value"]), conv(c["high"])])
+        assert np.array_equal(back(got), np.asarray(c["expected"], np.float32)), t
+        d = golden["DotRank2AndRank2"]
+        lhs, rhs = _fill_unique(d["lhs"]["dims"], d["lhs"]["start"]), _fill_unique(d["rhs"]["dims"], d["rhs"]["start"])
+        text = f"""HloModule dot
+ENTRY main {{
+  lhs = {t}[{d['lhs']['dims'][0]},{d['lhs']['dims'][1]}] parameter(0)
+  rhs = {t}[{d['rhs']['dims'][0]},{d['rhs']['dims'][1]}] parameter(1)
+  ROOT r = {t}[{d['lhs']['dims'][0]},{d['rhs']['dims'][1]}] dot(lhs, rhs), lhs_contracting_dims={{{d['lhs_contracting_dimensions'][0]}}}, rhs_contracting_dims={{{d['rhs_contracting_dimensions'][0]}}}
+}}
+"""
+        got = hlo_eval.evaluate(text, [conv(lhs), conv(rhs)])
+        assert np.array_equal(back(got), np.asarray(d["expected"], np.float32)), t
