@@ -19,6 +19,8 @@ Sources, read as text:
     (ScaledDot, ScaledDotWithOneMissingScale, ScaledDotWithBatchDim): operand extents and start values of the
     `FillUnique` arrays, dot dimension numbers and the expected result (scaled_dot_known_answers.json); and the
     DoesClamp and DotRank2AndRank2 known answers of the same file (evaluator_known_answers.json).
+  * xla/literal_comparison_test.cc -- CompareNear_NotEqual_1ulp / _4ulps: for each FP8 type the value next to 1.0 that
+    `within_n_values = 1` must accept and the value that needs `within_n_values = 4` (within_n_values_known.json).
 """
 import json
 import math
@@ -158,6 +160,23 @@ def write_evaluator_known_answers():
         json.dump(out, f, indent=1)
 
 
+def write_within_n_values_known():
+    rel = "xla/literal_comparison_test.cc"
+    src = open(os.path.join(ROOT, rel)).read()
+    out = {"source": rel, "actual": 1.0, "tests": {}}
+    for name, accept_n in (("CompareNear_NotEqual_1ulp", 1), ("CompareNear_NotEqual_4ulps", 4)):
+        m = re.search(r"TYPED_TEST\(LiteralComparisonTest, %s\) \{(.*?)\n\}\n" % name, src, flags=re.S)
+        body = m.group(1)
+        default = float(re.search(r"float expV = ([0-9.]+);", body).group(1))
+        e5m2 = float(re.search(r"type == F8E5M2 \|\| type == F8E5M2FNUZ\)\s*expV = ([0-9.]+);", body).group(1))
+        e8m0 = float(re.search(r"type == F8E8M0FNU\)\s*expV = ([0-9.]+);", body).group(1))
+        out["tests"][name] = {"line": src[: m.start()].count("\n") + 1, "accepted_with_within_n_values": accept_n,
+                              "rejected_with_within_n_values": 0 if accept_n == 1 else 1,
+                              "expected": {"f8e4m3fn": default, "f8e5m2": e5m2, "f8e8m0fnu": e8m0}}
+    with open(os.path.join(HERE, "within_n_values_known.json"), "w") as f:
+        json.dump(out, f, indent=1)
+
+
 def main():
     src = open(os.path.join(ROOT, "xla/tests/convert_test.cc")).read()
     out = {"source": "xla/tests/convert_test.cc", "tables": {}}
@@ -195,6 +214,7 @@ def main():
     write_interface_enums()
     write_scaled_dot_known_answers()
     write_evaluator_known_answers()
+    write_within_n_values_known()
     print("wrote", sorted(os.listdir(HERE)))
 
 

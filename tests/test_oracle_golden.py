@@ -303,3 +303,20 @@ ENTRY main {{
 """
         got = hlo_eval.evaluate(text, [conv(lhs), conv(rhs)])
         assert np.array_equal(back(got), np.asarray(d["expected"], np.float32)), t
+
+
+def test_within_n_values_rule_against_the_reference_cases():
+    """CompareNear_NotEqual_1ulp / _4ulps of xla/literal_comparison_test.cc:54-102: next to 1.0, the neighbouring FP8
+    value is a mismatch under ErrorSpec(0, 0) and accepted with within_n_values = 1; the value four steps away is a
+    mismatch with within_n_values = 1 and accepted with 4.  `fp8_within_n_values` is what the FP8-output GPU tests
+    judge by."""
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "within_n_values_known.json")) as f:
+        golden = json.load(f)
+    for kind, type_name in (("e4m3fn", "f8e4m3fn"), ("e5m2", "f8e5m2")):
+        actual = o.fp8_encode(np.float32([golden["actual"]]), kind)
+        for t in golden["tests"].values():
+            expected = o.fp8_encode(np.float32([t["expected"][type_name]]), kind)
+            assert float(o.fp8_decode(expected, kind)[0]) == t["expected"][type_name]        # representable as written
+            assert o.fp8_within_n_values(expected, actual, t["accepted_with_within_n_values"]) == 0
+            assert o.fp8_within_n_values(expected, actual, t["rejected_with_within_n_values"]) == 1
+            assert abs(int(o.fp8_ordinal(expected)[0]) - int(o.fp8_ordinal(actual)[0])) == t["accepted_with_within_n_values"]
