@@ -21,6 +21,8 @@ Sources, read as text:
     DoesClamp and DotRank2AndRank2 known answers of the same file (evaluator_known_answers.json).
   * xla/literal_comparison_test.cc -- CompareNear_NotEqual_1ulp / _4ulps: for each FP8 type the value next to 1.0 that
     `within_n_values = 1` must accept and the value that needs `within_n_values = 4` (within_n_values_known.json).
+  * xla/service/gpu/matmul_utils_test.cc -- the GetMatrixSizeRewriteThresholdTest cases: dot shapes, dimension numbers
+    and whether IsMatrixMultiplicationTooSmallForRewriting(dot, 100) holds (rewrite_threshold_known.json).
 """
 import json
 import math
@@ -177,6 +179,30 @@ def write_within_n_values_known():
         json.dump(out, f, indent=1)
 
 
+def write_rewrite_threshold_known():
+    rel = "xla/service/gpu/matmul_utils_test.cc"
+    src = open(os.path.join(ROOT, rel)).read()
+    cases = []
+    heads = list(re.finditer(r"^TEST(?:_F|_P)?\(\s*(\w+)\s*,\s*(\w+)\s*\) \{", src, flags=re.M))
+    for m, nxt in zip(heads, heads[1:] + [None]):
+        if m.group(1) != "GetMatrixSizeRewriteThresholdTest":
+            continue
+        name, body = m.group(2), src[m.end(): nxt.start() if nxt else len(src)]      # the module text holds a "}" line of its own
+        verdict = re.search(r"IsMatrixMultiplicationTooSmallForRewriting\(\*dot, (\d+)\),\s*absl_testing::IsOkAndHolds\((true|false)\)", body)
+        if not verdict:
+            continue
+        x = re.search(r"x = \w+\[([0-9,]+)\] parameter\(0\)", body).group(1)
+        y = re.search(r"y = \w+\[([0-9,]+)\] parameter\(1\)", body).group(1)
+        dot = re.search(r"ROOT dot = \w+\[([0-9,]+)\] dot\(x, y\), (.*)", body)
+        cases.append({"name": name, "line": src[: m.start()].count("\n") + 1, "threshold": int(verdict.group(1)),
+                      "too_small": verdict.group(2) == "true", "x_dims": [int(v) for v in x.split(",")],
+                      "y_dims": [int(v) for v in y.split(",")], "result_dims": [int(v) for v in dot.group(1).split(",")],
+                      "dimension_numbers": dot.group(2).strip()})
+    assert len(cases) == 4 and sum(c["too_small"] for c in cases) == 1, cases
+    with open(os.path.join(HERE, "rewrite_threshold_known.json"), "w") as f:
+        json.dump({"source": rel, "cases": cases}, f, indent=1)
+
+
 def main():
     src = open(os.path.join(ROOT, "xla/tests/convert_test.cc")).read()
     out = {"source": "xla/tests/convert_test.cc", "tables": {}}
@@ -215,6 +241,7 @@ def main():
     write_scaled_dot_known_answers()
     write_evaluator_known_answers()
     write_within_n_values_known()
+    write_rewrite_threshold_known()
     print("wrote", sorted(os.listdir(HERE)))
 
 

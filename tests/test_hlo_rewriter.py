@@ -460,3 +460,30 @@ def test_every_emitted_call_instantiates_through_the_ffi_boundary(name):
         call.close()
         n += 1
     assert n == len(plan["calls"])
+
+
+def test_small_dot_threshold_against_the_reference_cases():
+    """GetMatrixSizeRewriteThresholdTest of xla/service/gpu/matmul_utils_test.cc:250-360 (tests/golden/rewrite_threshold_known.json):
+    the same shapes and dimension numbers as FP8 dots -- the rewriter-lite leaves a dot to the elementwise emitters exactly
+    where IsMatrixMultiplicationTooSmallForRewriting(dot, 100) holds (per batch entry, (m + n) * k < 100)."""
+    import json
+
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rewrite_threshold_known.json")) as f:
+        cases = json.load(f)["cases"]
+    assert len(cases) == 4
+    for c in cases:
+        x, y, r = (",".join(map(str, c[k])) for k in ("x_dims", "y_dims", "result_dims"))
+        text = f"""HloModule threshold
+ENTRY main {{
+  x = f8e4m3fn[{x}] parameter(0)
+  y = f8e4m3fn[{y}] parameter(1)
+  xf = f32[{x}] convert(x)
+  yf = f32[{y}] convert(y)
+  ROOT dot = f32[{r}] dot(xf, yf), {c['dimension_numbers']}
+}}
+"""
+        _, plan = hlo_runner.rewrite(text)
+        assert c["threshold"] == 100
+        assert plan["rewritten"] == (not c["too_small"]), c["name"]
+        if c["too_small"]:
+            assert "too small" in plan["not_rewritten"][0]["reason"]
