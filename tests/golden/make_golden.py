@@ -14,7 +14,8 @@ Sources, read as text:
     known answer: m = n = k = 32, all-ones operands, every output == k.
   * xla/service/gpu/backend_configs.proto -- `enum Epilogue { ... }` of GemmBackendConfig, and
     xla/ffi/api/c_api.h -- `XLA_FFI_DataType`, `XLA_FFI_Error_Code`: the numbers the boundary
-    (include/b200_scaled_dot.h) must use (interface_enums.json).
+    (include/b200_scaled_dot.h) must use (interface_enums.json); with them the custom-call target names of
+    xla/service/gpu/cublas_cudnn.h and xla/backends/gpu/transforms/block_scaling_rewriter.h and the MXFP8 block size.
   * xla/hlo/evaluator/hlo_evaluator_test.cc -- the three known-answer tests of the `scaled-dot` instruction
     (ScaledDot, ScaledDotWithOneMissingScale, ScaledDotWithBatchDim): operand extents and start values of the
     `FillUnique` arrays, dot dimension numbers and the expected result (scaled_dot_known_answers.json); and the
@@ -87,12 +88,23 @@ def write_interface_enums():
     d0, d1, dtypes = c_enum(capi, "  XLA_FFI_DataType_INVALID = 0", "XLA_FFI_DataType_")
     e0, e1, codes = c_enum(capi, "  XLA_FFI_Error_Code_OK = 0", "XLA_FFI_Error_Code_")
     scale_mode = re.search(r"int32 scale_mode = (\d+);", proto)
+    # The custom-call target names this library stands in for or consumes.
+    cudnn_h = open(os.path.join(ROOT, "xla/service/gpu/cublas_cudnn.h")).read()
+    rewriter_h = open(os.path.join(ROOT, "xla/backends/gpu/transforms/block_scaling_rewriter.h")).read()
+    call_targets = {}
+    for text in (cudnn_h, rewriter_h):
+        for m in re.finditer(r"absl::string_view (k\w+(?:CallTarget|CustomCallTarget)) =\s*\"([^\"]+)\";", text):
+            if re.search(r"Matmul|Gemm|BlockScaledDot|Quantize", m.group(1)) and "Grouped" not in m.group(1):
+                call_targets[m.group(1)] = m.group(2)
+    assert call_targets["kCublasLtMatmulF8CallTarget"] and call_targets["kBlockScaledDotCustomCallTarget"]
     assert epilogue["DEFAULT"] == 0 and len(epilogue) == 10 and dtypes["F8E4M3FN"] == 20 and codes["UNIMPLEMENTED"] == 12
     out = {
         "epilogue": {"source": f"xla/service/gpu/backend_configs.proto:{base + l0}-{base + l1}", "values": epilogue},
         "data_type": {"source": f"xla/ffi/api/c_api.h:{d0}-{d1}", "values": dtypes},
         "error_code": {"source": f"xla/ffi/api/c_api.h:{e0}-{e1}", "values": codes},
         "scale_mode_field_number": int(scale_mode.group(1)),
+        "call_targets": call_targets,
+        "block_size_mxfp8": int(re.search(r"kBlockSizeMXFP8 = (\d+);", rewriter_h).group(1)),
     }
     with open(os.path.join(HERE, "interface_enums.json"), "w") as f:
         json.dump(out, f, indent=1, sort_keys=True)

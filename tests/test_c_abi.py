@@ -52,6 +52,33 @@ def test_interface_numbers_are_the_reference_s():
         assert int(re.search(cname + r"\s*=\s*(\d+)", kernels_h).group(1)) == golden["error_code"]["values"][gname]
 
 
+def test_call_target_names_are_the_reference_s():
+    """The custom-call names this library stands in for (`__cublas$lt$matmul$f8`, `$mx`) or consumes
+    (`__op$block_scaled_dot`) and the MX block size, as xla/service/gpu/cublas_cudnn.h:119-131 and
+    block_scaling_rewriter.h:86-95 spell them (tests/golden/interface_enums.json)."""
+    import json
+
+    from oracle import scaled_dot_oracle as o
+
+    golden = json.load(open(os.path.join(ROOT, "tests", "golden", "interface_enums.json")))
+    names = golden["call_targets"]
+    assert names["kCublasLtMatmulF8CallTarget"] == "__cublas$lt$matmul$f8" and names["kCublasLtMatmulMxCallTarget"] == "__cublas$lt$matmul$mx"
+    rewriter = open(os.path.join(ROOT, "xla_b200", "csrc", "hlo_rewriter.cc")).read()
+    assert '\\"' + names["kBlockScaledDotCustomCallTarget"] + '\\"' in rewriter          # the call the rewriter-lite looks for
+    evaluator = open(os.path.join(ROOT, "oracle", "hlo_eval.py")).read()
+    assert '"' + names["kBlockScaledDotCustomCallTarget"] + '"' in evaluator
+    header = open(os.path.join(ROOT, "include", "b200_scaled_dot.h")).read()
+    for key in ("kCublasLtMatmulMxCallTarget",):
+        assert names[key] in header
+    integration = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    for key in ("kCublasLtMatmulF8CallTarget", "kCublasLtMatmulMxCallTarget", "kCublasLtMatmulCallTarget"):
+        assert names[key] in integration
+    assert o.MX_BLOCK == golden["block_size_mxfp8"] == 32
+    # nothing of this library registers under a reference name
+    for target in ("b200$scaled_dot$f8", "b200$dot$s8", "b200$block_scaled_dot$mx"):
+        assert target not in names.values()
+
+
 def test_reference_epilogue_numbers_decode_as_the_reference_means_them():
     """A call frame carrying the reference's own numbers: 0 (DEFAULT) is accepted without a bias operand,
     6 (BIAS_GELU) wants the bias, 5 / 7 (the AUX forms) and 8 / 9 (SILU) are UNIMPLEMENTED, 10 is unknown."""
